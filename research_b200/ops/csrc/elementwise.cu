@@ -1,0 +1,724 @@
+// Bandwidth-bound kernels of the training step for sm_100a: RMSNorm (+ residual add), QK-RMSNorm
+// fused with interleaved-pair RoPE, SwiGLU, embedding gather / scatter-add, masked cross-entropy
+// with z-loss that leaves dlogits in place, flat-arena AdamW with bf16 shadow write, sum of squares.
+// All use 128-bit global accesses; reductions are warp shuffles, fp32 throughout.
+//
+// Math restated from the reference: RMSNorm and its scale (models/components/norm.py:12-38), RoPE over
+// even/odd pairs (models/components/position.py:9-39), QK-norm before RoPE
+// (models/components/attention.py:112-126, 228-234), SwiGLU (models/components/ffn.py:13-51), masked CE in
+// fp32 log-softmax (steps/eval.py:27-37), z-loss (steps/train.py:597-602), AdamW (optim/build.py:29-31).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace {
+
+constexpr int kWarpsPerBlock = 8;
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 v;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return v;
+}
+__device__ __forceinline__ void load8f(const float* p, float (&f)[8]) {
+  float4 a = *reinterpret_cast<const float4*>(p);
+  float4 b = *reinterpret_cast<const float4*>(p + 4);
+  f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w;
+  f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
+// ------------------------------------------------------------------------------------------------
+// RMSNorm forward: optionally res_out = x + delta first.  One warp per row, H % 8 == 0.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ delta,
+                   const float* __restrict__ w, __nv_bfloat16* __restrict__ res_out, __nv_bfloat16* __restrict__ y,
+                   float* __restrict__ rstd_out, int rows, int H, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int nvec = H >> 3;
+  for (long long row = (long long)blockIdx.x * kWarpsPerBlock + warp; row < rows;
+       row += (long long)gridDim.x * kWarpsPerBlock) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
+    const uint4* dr = delta ? reinterpret_cast<const uint4*>(delta + row * H) : nullptr;
+    uint4* rr = res_out ? reinterpret_cast<uint4*>(res_out + row * H) : nullptr;
+    float ss = 0.f;
+    for (int v = lane; v < nvec; v += 32) {
+      float f[8];
+      unpack8(xr[v], f);
+      if (dr) {
+        float g[8];
+        unpack8(dr[v], g);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] += g[i];
+        uint4 s = pack8(f);
+        rr[v] = s;
+        unpack8(s, f);  // normalise exactly what was stored
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+    }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)H + eps);
+    if (lane == 0 && rstd_out) rstd_out[row] = rstd;
+    const uint4* src = dr ? reinterpret_cast<const uint4*>(res_out + row * H) : xr;
+    uint4* yr = reinterpret_cast<uint4*>(y + row * H);
+    for (int v = lane; v < nvec; v += 32) {
+      float f[8], wv[8];
+      unpack8(src[v], f);
+      load8f(w + v * 8, wv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] = f[i] * rstd * wv[i];
+      yr[v] = pack8(f);
+    }
+  }
+}
+
+// RMSNorm backward.  dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) (+ dres if given); dw += sum_rows dy*xhat
+// NV > 0: H == NV * 256 and every lane keeps its dw partial sums in registers over all of its rows;
+// NV == 0: any H % 8 == 0, partial sums go through shared-memory atomics.  Either way a block folds its
+// partials in shared memory and issues one fp32 atomicAdd per column.
+template <int NV>
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
+                   const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dy,
+                   const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx, float* __restrict__ dw,
+                   int rows, int H) {
+  extern __shared__ float dw_smem[];  // H floats
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int nvec = H >> 3;
+  constexpr int NACC = NV > 0 ? NV : 1;
+  float acc[NACC][8];
+#pragma unroll
+  for (int j = 0; j < NACC; ++j)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[j][i] = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) dw_smem[i] = 0.f;
+  __syncthreads();
+  for (long long row = (long long)blockIdx.x * kWarpsPerBlock + warp; row < rows;
+       row += (long long)gridDim.x * kWarpsPerBlock) {
+    const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
+    const uint4* gr = reinterpret_cast<const uint4*>(dy + row * H);
+    const float rstd = rstd_in[row];
+    float dot = 0.f;
+    for (int v = lane; v < nvec; v += 32) {
+      float f[8], g[8], wv[8];
+      unpack8(xr[v], f);
+      unpack8(gr[v], g);
+      load8f(w + v * 8, wv);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) dot += g[i] * wv[i] * f[i] * rstd;
+    }
+    dot = warp_sum(dot) / (float)H;
+    const uint4* rr = dres ? reinterpret_cast<const uint4*>(dres + row * H) : nullptr;
+    uint4* dxr = reinterpret_cast<uint4*>(dx + row * H);
+    if constexpr (NV > 0) {
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        const int v = lane + 32 * j;
+        float f[8], g[8], wv[8], o[8];
+        unpack8(xr[v], f);
+        unpack8(gr[v], g);
+        load8f(w + v * 8, wv);
+        float r[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (rr) unpack8(rr[v], r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float xhat = f[i] * rstd;
+          o[i] = rstd * (g[i] * wv[i] - xhat * dot) + r[i];
+          acc[j][i] += g[i] * xhat;
+        }
+        dxr[v] = pack8(o);
+      }
+    } else {
+      for (int v = lane; v < nvec; v += 32) {
+        float f[8], g[8], wv[8], o[8];
+        unpack8(xr[v], f);
+        unpack8(gr[v], g);
+        load8f(w + v * 8, wv);
+        float r[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (rr) unpack8(rr[v], r);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float xhat = f[i] * rstd;
+          o[i] = rstd * (g[i] * wv[i] - xhat * dot) + r[i];
+          atomicAdd(&dw_smem[v * 8 + i], g[i] * xhat);
+        }
+        dxr[v] = pack8(o);
+      }
+    }
+  }
+  if constexpr (NV > 0) {
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) atomicAdd(&dw_smem[(lane + 32 * j) * 8 + i], acc[j][i]);
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float v = dw_smem[i];
+    if (v != 0.f) atomicAdd(&dw[i], v);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// QK-RMSNorm + RoPE (interleaved pairs) over the head dimension.  One warp handles one (token, head)
+// vector of D elements (D % 8 == 0, D <= 256): lane l owns elements [8l, 8l+8) = 4 rotation pairs.
+// in : [tokens, in_stride] with heads at column h*D;   out: [tokens, out_stride]
+// w  : [D] fp32 norm scale or nullptr (no norm).  positions: [tokens] int32.  rope: 0 = skip rotation.
+// Angle of pair i at position p: p * theta^(-2i/D).
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ in, long long in_stride, __nv_bfloat16* __restrict__ out,
+                       long long out_stride, const float* __restrict__ w, const int* __restrict__ positions,
+                       float* __restrict__ rstd_out, long long tokens, int heads, int D, float eps, float log2_theta,
+                       int rope) {
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const long long total = tokens * heads;
+  const bool active = lane * 8 < D;
+  for (long long idx = (long long)blockIdx.x * kWarpsPerBlock + warp; idx < total;
+       idx += (long long)gridDim.x * kWarpsPerBlock) {
+    const long long t = idx / heads;
+    const int h = (int)(idx - t * heads);
+    float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (active) unpack8(*reinterpret_cast<const uint4*>(in + t * in_stride + (long long)h * D + lane * 8), f);
+    float rstd = 1.f;
+    if (w) {
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+      ss = warp_sum(ss);
+      rstd = rsqrtf(ss / (float)D + eps);
+      if (lane == 0 && rstd_out) rstd_out[idx] = rstd;
+      if (active) {
+        float wv[8];
+        load8f(w + lane * 8, wv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) f[i] = f[i] * rstd * wv[i];
+      }
+    }
+    if (rope && active) {
+      const float pos = (float)positions[t];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int pair = lane * 4 + i;
+        const float inv_freq = exp2f(-log2_theta * (2.f * (float)pair) / (float)D);
+        float s, c;
+        sincosf(pos * inv_freq, &s, &c);
+        const float a = f[2 * i], b = f[2 * i + 1];
+        f[2 * i] = a * c - b * s;
+        f[2 * i + 1] = a * s + b * c;
+      }
+    }
+    if (active) *reinterpret_cast<uint4*>(out + t * out_stride + (long long)h * D + lane * 8) = pack8(f);
+  }
+}
+
+// backward of the above: grad wrt the pre-norm input, and dw (atomic fp32 adds, D columns)
+__global__ void __launch_bounds__(kWarpsPerBlock * 32)
+qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ in, long long in_stride,
+                       const __nv_bfloat16* __restrict__ dout, long long dout_stride,
+                       __nv_bfloat16* __restrict__ din, long long din_stride, const float* __restrict__ w,
+                       const int* __restrict__ positions, const float* __restrict__ rstd_in,
+                       float* __restrict__ dw, long long tokens, int heads, int D, float log2_theta, int rope) {
+  __shared__ float dw_smem[256];
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const long long total = tokens * heads;
+  const bool active = lane * 8 < D;
+  if (threadIdx.x < 256) dw_smem[threadIdx.x] = 0.f;
+  __syncthreads();
+  float dw_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  for (long long idx = (long long)blockIdx.x * kWarpsPerBlock + warp; idx < total;
+       idx += (long long)gridDim.x * kWarpsPerBlock) {
+    const long long t = idx / heads;
+    const int h = (int)(idx - t * heads);
+    float g[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (active) unpack8(*reinterpret_cast<const uint4*>(dout + t * dout_stride + (long long)h * D + lane * 8), g);
+    if (rope && active) {
+      const float pos = (float)positions[t];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int pair = lane * 4 + i;
+        const float inv_freq = exp2f(-log2_theta * (2.f * (float)pair) / (float)D);
+        float s, c;
+        sincosf(pos * inv_freq, &s, &c);
+        const float a = g[2 * i], b = g[2 * i + 1];  // transpose of the rotation
+        g[2 * i] = a * c + b * s;
+        g[2 * i + 1] = -a * s + b * c;
+      }
+    }
+    if (w) {
+      float f[8] = {0, 0, 0, 0, 0, 0, 0, 0}, wv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      if (active) {
+        unpack8(*reinterpret_cast<const uint4*>(in + t * in_stride + (long long)h * D + lane * 8), f);
+        load8f(w + lane * 8, wv);
+      }
+      const float rstd = rstd_in[idx];
+      float dot = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) dot += g[i] * wv[i] * f[i] * rstd;
+      dot = warp_sum(dot) / (float)D;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float xhat = f[i] * rstd;
+        dw_acc[i] += g[i] * xhat;
+        g[i] = rstd * (g[i] * wv[i] - xhat * dot);
+      }
+    }
+    if (active) *reinterpret_cast<uint4*>(din + t * din_stride + (long long)h * D + lane * 8) = pack8(g);
+  }
+  if (w && dw) {
+    if (active) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) atomicAdd(&dw_smem[lane * 8 + i], dw_acc[i]);
+    }
+    __syncthreads();
+    if (threadIdx.x < D) atomicAdd(&dw[threadIdx.x], dw_smem[threadIdx.x]);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// SwiGLU on a fused [rows, 2*I] gate|up buffer: h = silu(g) * u.
+// ------------------------------------------------------------------------------------------------
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ h, long long rows,
+                                  int I) {
+  const int nvec = I >> 3;
+  const long long total = rows * nvec;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / nvec;
+    const int v = (int)(i - r * nvec);
+    const __nv_bfloat16* base = gu + r * 2 * I;
+    float g[8], u[8], o[8];
+    unpack8(*reinterpret_cast<const uint4*>(base + v * 8), g);
+    unpack8(*reinterpret_cast<const uint4*>(base + I + v * 8), u);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) o[k] = g[k] / (1.f + __expf(-g[k])) * u[k];
+    *reinterpret_cast<uint4*>(h + r * I + v * 8) = pack8(o);
+  }
+}
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ gu, const __nv_bfloat16* __restrict__ dh,
+                                  __nv_bfloat16* __restrict__ dgu, long long rows, int I) {
+  const int nvec = I >> 3;
+  const long long total = rows * nvec;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / nvec;
+    const int v = (int)(i - r * nvec);
+    const __nv_bfloat16* base = gu + r * 2 * I;
+    float g[8], u[8], d[8], dg[8], du[8];
+    unpack8(*reinterpret_cast<const uint4*>(base + v * 8), g);
+    unpack8(*reinterpret_cast<const uint4*>(base + I + v * 8), u);
+    unpack8(*reinterpret_cast<const uint4*>(dh + r * I + v * 8), d);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float sig = 1.f / (1.f + __expf(-g[k]));
+      const float silu = g[k] * sig;
+      du[k] = d[k] * silu;
+      dg[k] = d[k] * u[k] * (sig + silu * (1.f - sig));
+    }
+    *reinterpret_cast<uint4*>(dgu + r * 2 * I + v * 8) = pack8(dg);
+    *reinterpret_cast<uint4*>(dgu + r * 2 * I + I + v * 8) = pack8(du);
+  }
+}
+
+// out = a * sigmoid(gate) (attention output gate) and its backward
+__global__ void sigmoid_gate_fwd_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ gate,
+                                        __nv_bfloat16* __restrict__ out, long long nvec) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float x[8], g[8];
+    unpack8(reinterpret_cast<const uint4*>(a)[i], x);
+    unpack8(reinterpret_cast<const uint4*>(gate)[i], g);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) x[k] = x[k] / (1.f + __expf(-g[k]));
+    reinterpret_cast<uint4*>(out)[i] = pack8(x);
+  }
+}
+__global__ void sigmoid_gate_bwd_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ gate,
+                                        const __nv_bfloat16* __restrict__ dout, __nv_bfloat16* __restrict__ da,
+                                        __nv_bfloat16* __restrict__ dgate, long long nvec) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec; i += (long long)gridDim.x * blockDim.x) {
+    float x[8], g[8], d[8], o1[8], o2[8];
+    unpack8(reinterpret_cast<const uint4*>(a)[i], x);
+    unpack8(reinterpret_cast<const uint4*>(gate)[i], g);
+    unpack8(reinterpret_cast<const uint4*>(dout)[i], d);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float sig = 1.f / (1.f + __expf(-g[k]));
+      o1[k] = d[k] * sig;
+      o2[k] = d[k] * x[k] * sig * (1.f - sig);
+    }
+    reinterpret_cast<uint4*>(da)[i] = pack8(o1);
+    reinterpret_cast<uint4*>(dgate)[i] = pack8(o2);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Embedding gather (bf16 table) with optional scale, and scatter-add of gradients into fp32.
+// ------------------------------------------------------------------------------------------------
+__global__ void embedding_fwd_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ table,
+                                     __nv_bfloat16* __restrict__ out, long long tokens, int H, float scale) {
+  const int nvec = H >> 3;
+  const long long total = tokens * nvec;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / nvec;
+    const int v = (int)(i - t * nvec);
+    uint4 val = *reinterpret_cast<const uint4*>(table + (long long)ids[t] * H + v * 8);
+    if (scale != 1.f) {
+      float f[8];
+      unpack8(val, f);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) f[k] *= scale;
+      val = pack8(f);
+    }
+    *reinterpret_cast<uint4*>(out + t * H + v * 8) = val;
+  }
+}
+__global__ void embedding_bwd_kernel(const int* __restrict__ ids, const __nv_bfloat16* __restrict__ dout,
+                                     float* __restrict__ dtable, long long tokens, int H, float scale) {
+  const int nvec = H >> 3;
+  const long long total = tokens * nvec;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / nvec;
+    const int v = (int)(i - t * nvec);
+    float f[8];
+    unpack8(*reinterpret_cast<const uint4*>(dout + t * H + v * 8), f);
+    float* dst = dtable + (long long)ids[t] * H + v * 8;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) atomicAdd(dst + k, f[k] * scale);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Masked cross-entropy + z-loss over one chunk of logits [rows, V] (bf16, row stride ld), in place:
+//   loss_i = lse_i - logit_i[target_i];  z_i = lse_i^2            (only rows with mask != 0 count)
+//   logits <- dlogits = grad_scale * mask_i * ((1 + 2 z_w lse_i) softmax - onehot)
+// One block per row; three passes over the row (max, sum, write); the row stays in L1/L2.
+// Sums are written per row (loss_row, z_row) so that the host-visible reduction is deterministic.
+// vocab_offset/vocab_total support vocab-parallel logits: then max and sum come in precomputed
+// (global_max / global_sum per row) and phase selects which pass runs.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(512)
+ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, long long ld, const int* __restrict__ targets,
+                  const uint8_t* __restrict__ mask, float* __restrict__ loss_row, float* __restrict__ z_row,
+                  float* __restrict__ lse_row, int V, float grad_scale, float z_weight, int write_grad) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  __nv_bfloat16* lr = logits + row * ld;
+  const int nvec = V >> 3;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const bool masked = mask[row] == 0;
+  if (masked && !write_grad) {
+    if (threadIdx.x == 0) { loss_row[row] = 0.f; z_row[row] = 0.f; if (lse_row) lse_row[row] = 0.f; }
+    return;
+  }
+  if (masked) {  // zero gradient row, no loss
+    const uint4 z = make_uint4(0, 0, 0, 0);
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) reinterpret_cast<uint4*>(lr)[v] = z;
+    for (int c = nvec * 8 + threadIdx.x; c < V; c += blockDim.x) lr[c] = __float2bfloat16(0.f);
+    if (threadIdx.x == 0) { loss_row[row] = 0.f; z_row[row] = 0.f; if (lse_row) lse_row[row] = 0.f; }
+    return;
+  }
+  // pass 1: max
+  float m = -INFINITY;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    float f[8];
+    unpack8(reinterpret_cast<const uint4*>(lr)[v], f);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) m = fmaxf(m, f[k]);
+  }
+  for (int c = nvec * 8 + threadIdx.x; c < V; c += blockDim.x) m = fmaxf(m, __bfloat162float(lr[c]));
+  m = warp_max(m);
+  if (lane == 0) red[warp] = m;
+  __syncthreads();
+  m = (lane < nwarps) ? red[lane] : -INFINITY;
+  m = warp_max(m);
+  __syncthreads();
+  // pass 2: sum exp
+  float s = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    float f[8];
+    unpack8(reinterpret_cast<const uint4*>(lr)[v], f);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) s += __expf(f[k] - m);
+  }
+  for (int c = nvec * 8 + threadIdx.x; c < V; c += blockDim.x) s += __expf(__bfloat162float(lr[c]) - m);
+  s = warp_sum(s);
+  if (lane == 0) red[warp] = s;
+  __syncthreads();
+  s = (lane < nwarps) ? red[lane] : 0.f;
+  s = warp_sum(s);
+  const float lse = m + logf(s);
+  const int tgt = targets[row];
+  const float tl = __bfloat162float(lr[tgt]);
+  __syncthreads();  // everyone has read the target logit before it is overwritten
+  if (threadIdx.x == 0) {
+    loss_row[row] = lse - tl;
+    z_row[row] = lse * lse;
+    if (lse_row) lse_row[row] = lse;
+  }
+  if (!write_grad) return;
+  // pass 3: gradient in place
+  const float coef = grad_scale * (1.f + 2.f * z_weight * lse);
+  const float inv_s = 1.f / s;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    float f[8];
+    unpack8(reinterpret_cast<const uint4*>(lr)[v], f);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      f[k] = coef * __expf(f[k] - m) * inv_s;
+      if (v * 8 + k == tgt) f[k] -= grad_scale;
+    }
+    reinterpret_cast<uint4*>(lr)[v] = pack8(f);
+  }
+  for (int c = nvec * 8 + threadIdx.x; c < V; c += blockDim.x) {
+    float g = coef * __expf(__bfloat162float(lr[c]) - m) * inv_s;
+    if (c == tgt) g -= grad_scale;
+    lr[c] = __float2bfloat16(g);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Flat-arena AdamW: p, m, v fp32 [n]; g bf16 or fp32 [n]; writes the bf16 shadow of p.
+//   g' = g * gscale[0] (clip factor, device scalar; nullptr = 1)
+//   m = b1 m + (1-b1) g';  v = b2 v + (1-b2) g'^2;  p -= lr * (mhat / (sqrt(vhat) + eps) + wd p)
+// lr, bias corrections come from the host each step (schedule evaluated at the old step count).
+// ------------------------------------------------------------------------------------------------
+template <typename GT>
+__global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
+                             const GT* __restrict__ g, __nv_bfloat16* __restrict__ shadow,
+                             const float* __restrict__ gscale, long long n, float lr, float b1, float b2, float eps,
+                             float wd, float bc1, float bc2) {
+  const float gs = gscale ? gscale[0] : 1.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float gi;
+    if constexpr (sizeof(GT) == 2)
+      gi = __bfloat162float(g[i]) * gs;
+    else
+      gi = g[i] * gs;
+    const float mi = b1 * m[i] + (1.f - b1) * gi;
+    const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
+    m[i] = mi;
+    v[i] = vi;
+    const float mhat = mi / bc1;
+    const float vhat = vi / bc2;
+    float pi = p[i];
+    pi -= lr * (mhat / (sqrtf(vhat) + eps) + wd * pi);
+    p[i] = pi;
+    if (shadow) shadow[i] = __float2bfloat16(pi);
+  }
+}
+
+// sum of squares, two deterministic stages: per-block partials, then one block folds them
+template <typename T>
+__global__ void sumsq_partial_kernel(const T* __restrict__ x, long long n, float* __restrict__ partial) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float f;
+    if constexpr (sizeof(T) == 2)
+      f = __bfloat162float(x[i]);
+    else
+      f = x[i];
+    s += f * f;
+  }
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    s = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    s = warp_sum(s);
+    if (threadIdx.x == 0) partial[blockIdx.x] = s;
+  }
+}
+__global__ void sumsq_final_kernel(const float* __restrict__ partial, int nparts, float* __restrict__ out,
+                                   int accumulate) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (int i = threadIdx.x; i < nparts; i += blockDim.x) s += partial[i];
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    s = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+    s = warp_sum(s);
+    if (threadIdx.x == 0) out[0] = accumulate ? out[0] + s : s;
+  }
+}
+
+// fp32 -> bf16 cast with scale (used for the bf16 shadow of Muon-updated weights and grad casts)
+__global__ void cast_f32_bf16_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ y, long long n,
+                                     float scale) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    y[i] = __float2bfloat16(x[i] * scale);
+}
+
+inline int grid_for(long long work_items, int block, int per_sm = 8) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  long long blocks = (work_items + block - 1) / block;
+  long long cap = (long long)sms * per_sm;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (int)blocks;
+}
+
+}  // namespace
+
+#define STREAM(s) reinterpret_cast<cudaStream_t>(s)
+#define LAST_ERR() static_cast<int>(cudaGetLastError())
+
+extern "C" int b200_rmsnorm_fwd(const void* x, const void* delta, const void* w, void* res_out, void* y, void* rstd,
+                                int rows, int H, float eps, void* stream) {
+  if (H % 8) return -2;
+  const int grid = grid_for((long long)rows, kWarpsPerBlock, 8);
+  rmsnorm_fwd_kernel<<<grid, kWarpsPerBlock * 32, 0, STREAM(stream)>>>(
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)delta, (const float*)w, (__nv_bfloat16*)res_out,
+      (__nv_bfloat16*)y, (float*)rstd, rows, H, eps);
+  return LAST_ERR();
+}
+extern "C" int b200_rmsnorm_bwd(const void* x, const void* w, const void* rstd, const void* dy, const void* dres,
+                                void* dx, void* dw, int rows, int H, void* stream) {
+  if (H % 8 || H * 4 > 48 * 1024) return -2;
+  const int grid = grid_for((long long)rows, kWarpsPerBlock, 2);
+#define RMS_BWD(NV)                                                                                     \
+  rmsnorm_bwd_kernel<NV><<<grid, kWarpsPerBlock * 32, H * sizeof(float), STREAM(stream)>>>(              \
+      (const __nv_bfloat16*)x, (const float*)w, (const float*)rstd, (const __nv_bfloat16*)dy,            \
+      (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, (float*)dw, rows, H)
+  switch (H) {
+    case 256: RMS_BWD(1); break;
+    case 512: RMS_BWD(2); break;
+    case 1024: RMS_BWD(4); break;
+    case 2048: RMS_BWD(8); break;
+    case 4096: RMS_BWD(16); break;
+    default: RMS_BWD(0); break;
+  }
+#undef RMS_BWD
+  return LAST_ERR();
+}
+extern "C" int b200_qknorm_rope_fwd(const void* in, long long in_stride, void* out, long long out_stride,
+                                    const void* w, const void* positions, void* rstd, long long tokens, int heads,
+                                    int D, float eps, float theta, int rope, void* stream) {
+  if (D % 8 || D > 256) return -2;
+  const int grid = grid_for(tokens * heads, kWarpsPerBlock, 8);
+  qknorm_rope_fwd_kernel<<<grid, kWarpsPerBlock * 32, 0, STREAM(stream)>>>(
+      (const __nv_bfloat16*)in, in_stride, (__nv_bfloat16*)out, out_stride, (const float*)w, (const int*)positions,
+      (float*)rstd, tokens, heads, D, eps, log2f(theta), rope);
+  return LAST_ERR();
+}
+extern "C" int b200_qknorm_rope_bwd(const void* in, long long in_stride, const void* dout, long long dout_stride,
+                                    void* din, long long din_stride, const void* w, const void* positions,
+                                    const void* rstd, void* dw, long long tokens, int heads, int D, float theta,
+                                    int rope, void* stream) {
+  if (D % 8 || D > 256) return -2;
+  const int grid = grid_for(tokens * heads, kWarpsPerBlock, 4);
+  qknorm_rope_bwd_kernel<<<grid, kWarpsPerBlock * 32, 0, STREAM(stream)>>>(
+      (const __nv_bfloat16*)in, in_stride, (const __nv_bfloat16*)dout, dout_stride, (__nv_bfloat16*)din, din_stride,
+      (const float*)w, (const int*)positions, (const float*)rstd, (float*)dw, tokens, heads, D, log2f(theta), rope);
+  return LAST_ERR();
+}
+extern "C" int b200_swiglu_fwd(const void* gu, void* h, long long rows, int I, void* stream) {
+  if (I % 8) return -2;
+  swiglu_fwd_kernel<<<grid_for(rows * (I / 8), 256), 256, 0, STREAM(stream)>>>((const __nv_bfloat16*)gu,
+                                                                                (__nv_bfloat16*)h, rows, I);
+  return LAST_ERR();
+}
+extern "C" int b200_swiglu_bwd(const void* gu, const void* dh, void* dgu, long long rows, int I, void* stream) {
+  if (I % 8) return -2;
+  swiglu_bwd_kernel<<<grid_for(rows * (I / 8), 256), 256, 0, STREAM(stream)>>>(
+      (const __nv_bfloat16*)gu, (const __nv_bfloat16*)dh, (__nv_bfloat16*)dgu, rows, I);
+  return LAST_ERR();
+}
+extern "C" int b200_sigmoid_gate_fwd(const void* a, const void* gate, void* out, long long n, void* stream) {
+  if (n % 8) return -2;
+  sigmoid_gate_fwd_kernel<<<grid_for(n / 8, 256), 256, 0, STREAM(stream)>>>(
+      (const __nv_bfloat16*)a, (const __nv_bfloat16*)gate, (__nv_bfloat16*)out, n / 8);
+  return LAST_ERR();
+}
+extern "C" int b200_sigmoid_gate_bwd(const void* a, const void* gate, const void* dout, void* da, void* dgate,
+                                     long long n, void* stream) {
+  if (n % 8) return -2;
+  sigmoid_gate_bwd_kernel<<<grid_for(n / 8, 256), 256, 0, STREAM(stream)>>>(
+      (const __nv_bfloat16*)a, (const __nv_bfloat16*)gate, (const __nv_bfloat16*)dout, (__nv_bfloat16*)da,
+      (__nv_bfloat16*)dgate, n / 8);
+  return LAST_ERR();
+}
+extern "C" int b200_embedding_fwd(const void* ids, const void* table, void* out, long long tokens, int H,
+                                  float scale, void* stream) {
+  if (H % 8) return -2;
+  embedding_fwd_kernel<<<grid_for(tokens * (H / 8), 256), 256, 0, STREAM(stream)>>>(
+      (const int*)ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, tokens, H, scale);
+  return LAST_ERR();
+}
+extern "C" int b200_embedding_bwd(const void* ids, const void* dout, void* dtable, long long tokens, int H,
+                                  float scale, void* stream) {
+  if (H % 8) return -2;
+  embedding_bwd_kernel<<<grid_for(tokens * (H / 8), 256), 256, 0, STREAM(stream)>>>(
+      (const int*)ids, (const __nv_bfloat16*)dout, (float*)dtable, tokens, H, scale);
+  return LAST_ERR();
+}
+extern "C" int b200_ce_fwd_bwd(void* logits, long long ld, const void* targets, const void* mask, void* loss_row,
+                               void* z_row, void* lse_row, int rows, int V, float grad_scale, float z_weight,
+                               int write_grad, void* stream) {
+  if (rows <= 0) return 0;
+  if (ld % 8) return -1;  // rows must stay 16-byte aligned for the vector path
+  ce_fwd_bwd_kernel<<<rows, 512, 0, STREAM(stream)>>>((__nv_bfloat16*)logits, ld, (const int*)targets,
+                                                      (const uint8_t*)mask, (float*)loss_row, (float*)z_row,
+                                                      (float*)lse_row, V, grad_scale, z_weight, write_grad);
+  return LAST_ERR();
+}
+extern "C" int b200_adamw(void* p, void* m, void* v, const void* g, int g_is_bf16, void* shadow, const void* gscale,
+                          long long n, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
+                          void* stream) {
+  if (n <= 0) return 0;
+  const int grid = grid_for(n, 256, 8);
+  if (g_is_bf16)
+    adamw_kernel<__nv_bfloat16><<<grid, 256, 0, STREAM(stream)>>>((float*)p, (float*)m, (float*)v,
+                                                                   (const __nv_bfloat16*)g, (__nv_bfloat16*)shadow,
+                                                                   (const float*)gscale, n, lr, b1, b2, eps, wd, bc1, bc2);
+  else
+    adamw_kernel<float><<<grid, 256, 0, STREAM(stream)>>>((float*)p, (float*)m, (float*)v, (const float*)g,
+                                                           (__nv_bfloat16*)shadow, (const float*)gscale, n, lr, b1, b2,
+                                                           eps, wd, bc1, bc2);
+  return LAST_ERR();
+}
+// scratch: at least 1024 floats.  out[0] (+)= sum(x^2)
+extern "C" int b200_sumsq(const void* x, int is_bf16, long long n, void* scratch, void* out, int accumulate,
+                          void* stream) {
+  int grid = grid_for(n, 512, 4);
+  if (grid > 1024) grid = 1024;
+  if (is_bf16)
+    sumsq_partial_kernel<__nv_bfloat16><<<grid, 512, 0, STREAM(stream)>>>((const __nv_bfloat16*)x, n, (float*)scratch);
+  else
+    sumsq_partial_kernel<float><<<grid, 512, 0, STREAM(stream)>>>((const float*)x, n, (float*)scratch);
+  sumsq_final_kernel<<<1, 256, 0, STREAM(stream)>>>((const float*)scratch, grid, (float*)out, accumulate);
+  return LAST_ERR();
+}
+extern "C" int b200_cast_f32_bf16(const void* x, void* y, long long n, float scale, void* stream) {
+  if (n <= 0) return 0;
+  cast_f32_bf16_kernel<<<grid_for(n, 256, 8), 256, 0, STREAM(stream)>>>((const float*)x, (__nv_bfloat16*)y, n, scale);
+  return LAST_ERR();
+}

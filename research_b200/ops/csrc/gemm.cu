@@ -1,0 +1,323 @@
+// bf16 GEMM for sm_100a: C[b] (+)= op(A[b]) * op(B[b]), fp32 accumulation in tensor memory.
+//
+// One persistent CTA per SM, 6 warps with fixed roles:
+//   warp 0    TMA producer   : streams 128 x 64 (A) and BN x 64 (B) bf16 tiles into a 4-stage
+//                              shared-memory ring (128-byte swizzle), one elected lane
+//   warp 1    MMA issuer     : one lane issues tcgen05.mma (M=128, N=BN, K=16) into one of two
+//                              TMEM accumulators and commits completion to mbarriers
+//   warps 2-5 epilogue       : tcgen05.ld the finished accumulator (each warp owns its 32-lane
+//                              TMEM quadrant = 32 output rows), convert, stage through swizzled
+//                              shared memory and write with TMA (store, or reduce-add when
+//                              accumulating into C); overlaps the next tile's main loop.
+//
+// Operand layouts (all row-major in global memory, leading strides multiples of 16 bytes):
+//   a_mn = 0 : A stored [M][K]   (K contiguous, "K-major")      a_mn = 1 : A stored [K][M]
+//   b_mn = 0 : B stored [N][K]   (the y = x W^T weight layout)  b_mn = 1 : B stored [K][N]
+// which covers forward (NT), data-gradient (NN) and weight-gradient (TN) products without a
+// transpose pass.  No cluster launch and no multicast loads: the same code runs on any number of
+// GPUs.  The role this plays in the reference is XLA's cuBLAS dot; the hand-written comparator in
+// its vendored tree is third_party/ThunderKittens/kernels/gemm/bf16_b200/bf16_b200_gemm.cu.
+#include "b200.cuh"
+#include "host_util.cuh"
+
+using namespace b200;
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int STAGES = 4;
+constexpr int A_TILE_BYTES = BM * BK * 2;
+constexpr int EPI_WARPS = 4;
+constexpr int STAGING_BYTES = 32 * 128;  // 32 rows x 128 bytes per epilogue warp buffer
+constexpr int NUM_THREADS = 32 * (2 + EPI_WARPS);
+constexpr int GROUP_M = 8;
+
+template <int BN>
+struct SmemLayout {
+  static constexpr int B_TILE_BYTES = BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+  static constexpr int STAGING_OFF = STAGES * STAGE_BYTES;
+  static constexpr int BAR_OFF = STAGING_OFF + EPI_WARPS * 2 * STAGING_BYTES;
+  static constexpr int TOTAL = BAR_OFF + 256;
+};
+
+struct GemmParams {
+  int M, N, K, batch;
+  int accumulate;
+  int* status;
+};
+
+template <int BN, bool A_MN, bool B_MN, bool OUT_F32>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const __grid_constant__ CUtensorMap tmC, const GemmParams p) {
+  using L = SmemLayout<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tfull = empty + STAGES;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const AbortCtx ab{abort_flag, p.status};
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  const int tiles_m = (p.M + BM - 1) / BM;
+  const int tiles_n = (p.N + BN - 1) / BN;
+  const int per_batch = tiles_m * tiles_n;
+  const int total_tiles = per_batch * p.batch;
+  const int k_blocks = (p.K + BK - 1) / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], EPI_WARPS);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto tile_coords = [&](int t, int& b, int& m0, int& n0) {
+    b = t / per_batch;
+    const int r = t - b * per_batch;
+    const int group_size = GROUP_M * tiles_n;
+    const int g = r / group_size;
+    const int first_m = g * GROUP_M;
+    const int gm = min(GROUP_M, tiles_m - first_m);
+    const int in_group = r - g * group_size;
+    m0 = (first_m + in_group % gm) * BM;
+    n0 = (in_group / gm) * BN;
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int b, m0, n0;
+        tile_coords(t, b, m0, n0);
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&empty[s], ph ^ 1, ab, ERR_WAIT_EMPTY)) { ok = false; break; }
+          uint8_t* sA = smem + s * L::STAGE_BYTES;
+          uint8_t* sB = sA + A_TILE_BYTES;
+          mbar_expect_tx(&full[s], L::STAGE_BYTES);
+          if (!A_MN) {
+            tma_load_3d(sA, &tmA, &full[s], kb * BK, m0, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_3d(sA + j * 8192, &tmA, &full[s], m0 + j * 64, kb * BK, b);
+          }
+          if (!B_MN) {
+            tma_load_3d(sB, &tmB, &full[s], kb * BK, n0, b);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_3d(sB + j * 8192, &tmB, &full[s], n0 + j * 64, kb * BK, b);
+          }
+        }
+      }
+      if (!ok) {
+        // give copies already in flight time to land before the CTA's shared memory goes away
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      uint32_t it = 0;
+      uint32_t tile_iter = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_iter) {
+        const uint32_t acc = tile_iter & 1;
+        const uint32_t acc_ph = (tile_iter >> 1) & 1;
+        if (!mbar_wait(&tempty[acc], acc_ph ^ 1, ab, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full[s], ph, ab, ERR_WAIT_FULL)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_base = smem_u32(smem + s * L::STAGE_BYTES);
+          const uint32_t b_base = a_base + A_TILE_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t adesc = make_smem_desc_sw128(a_base + (A_MN ? k * 2048 : k * 32), A_MN ? 8192 : 16, 1024);
+            const uint64_t bdesc = make_smem_desc_sw128(b_base + (B_MN ? k * 2048 : k * 32), B_MN ? 8192 : 16, 1024);
+            tc_mma_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          tc_commit(&empty[s]);  // stage reusable once these MMAs have read it
+        }
+        if (ok) tc_commit(&tfull[acc]);  // accumulator complete
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int q = warp & 3;  // TMEM lane quadrant this warp may access
+    constexpr int COLS_PER_BOX = OUT_F32 ? 32 : 64;
+    uint8_t* stage0 = smem + L::STAGING_OFF + (warp - 2) * 2 * STAGING_BYTES;
+    uint32_t tile_iter = 0;
+    uint32_t box_iter = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_iter) {
+      int b, m0, n0;
+      tile_coords(t, b, m0, n0);
+      const uint32_t acc = tile_iter & 1;
+      const uint32_t acc_ph = (tile_iter >> 1) & 1;
+      if (!mbar_wait(&tfull[acc], acc_ph, ab, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+      const int row0 = m0 + q * 32;
+#pragma unroll 1
+      for (int j = 0; j < BN / COLS_PER_BOX; ++j) {
+        const int col0 = n0 + j * COLS_PER_BOX;
+        if (col0 >= p.N || row0 >= p.M) break;  // warp-uniform: nothing of this box is in range
+        uint8_t* buf = stage0 + (box_iter & 1) * STAGING_BYTES;
+        ++box_iter;
+        if (lane == 0) tma_wait_group_read<1>();  // the store that last read this buffer is done
+        __syncwarp();
+        if (OUT_F32) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(t_row + j * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            *reinterpret_cast<uint4*>(buf + sw128_offset(lane, c)) = make_uint4(r[4 * c], r[4 * c + 1], r[4 * c + 2], r[4 * c + 3]);
+        } else {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(t_row + j * 64 + h * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint4 v;
+              v.x = pack_bf16x2(__uint_as_float(r[8 * c + 0]), __uint_as_float(r[8 * c + 1]));
+              v.y = pack_bf16x2(__uint_as_float(r[8 * c + 2]), __uint_as_float(r[8 * c + 3]));
+              v.z = pack_bf16x2(__uint_as_float(r[8 * c + 4]), __uint_as_float(r[8 * c + 5]));
+              v.w = pack_bf16x2(__uint_as_float(r[8 * c + 6]), __uint_as_float(r[8 * c + 7]));
+              *reinterpret_cast<uint4*>(buf + sw128_offset(lane, h * 4 + c)) = v;
+            }
+          }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (p.accumulate)
+            tma_reduce_add_3d(&tmC, buf, col0, row0, b);
+          else
+            tma_store_3d(&tmC, buf, col0, row0, b);
+          tma_commit_group();
+        }
+      }
+      // every tcgen05.ld of this accumulator has completed: hand it back to the MMA issuer
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+    }
+    if (lane == 0) tma_wait_group<0>();
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+template <int BN, bool A_MN, bool B_MN, bool OUT_F32>
+int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const GemmParams& p, int grid,
+           cudaStream_t stream) {
+  using L = SmemLayout<BN>;
+  auto* kern = gemm_bf16_kernel<BN, A_MN, B_MN, OUT_F32>;
+  static bool configured = false;
+  constexpr int smem_bytes = L::TOTAL + 1024;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    configured = true;
+  }
+  kern<<<grid, NUM_THREADS, smem_bytes, stream>>>(tmA, tmB, tmC, p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+template <int BN>
+int dispatch(bool a_mn, bool b_mn, bool out_f32, const CUtensorMap& tmA, const CUtensorMap& tmB,
+             const CUtensorMap& tmC, const GemmParams& p, int grid, cudaStream_t s) {
+#define GEMM_CASE(A, B, F) \
+  if (a_mn == A && b_mn == B && out_f32 == F) return launch<BN, A, B, F>(tmA, tmB, tmC, p, grid, s);
+  GEMM_CASE(false, false, false)
+  GEMM_CASE(false, false, true)
+  GEMM_CASE(false, true, false)
+  GEMM_CASE(false, true, true)
+  GEMM_CASE(true, false, false)
+  GEMM_CASE(true, false, true)
+  GEMM_CASE(true, true, false)
+  GEMM_CASE(true, true, true)
+#undef GEMM_CASE
+  return b200host::RC_BAD_SHAPE;
+}
+
+}  // namespace
+
+// C[b] (+)= op(A[b]) op(B[b]) for b in [0, batch).  Leading strides (lda/ldb/ldc) and batch strides
+// are in elements.  out_f32: C is fp32 (else bf16).  accumulate: add into C with TMA reduce-add.
+// `status` is a device int the kernel sets non-zero if one of its bounded waits ran out.
+extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int batch, long long lda,
+                              long long ldb, long long ldc, long long stride_a, long long stride_b,
+                              long long stride_c, int a_mn, int b_mn, int out_f32, int accumulate, int bn_hint,
+                              int* status, void* stream) {
+  using namespace b200host;
+  if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return RC_BAD_SHAPE;
+  const int BN = (bn_hint == 128 || bn_hint == 256) ? bn_hint : (N > 128 ? 256 : 128);
+  CUtensorMap tmA, tmB, tmC;
+  int rc;
+  const CUtensorMapDataType bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  if (!a_mn)
+    rc = make_map_3d(&tmA, bf, A, K, M, batch, lda * 2, stride_a * 2, BK, BM);
+  else
+    rc = make_map_3d(&tmA, bf, A, M, K, batch, lda * 2, stride_a * 2, 64, BK);
+  if (rc) return rc;
+  if (!b_mn)
+    rc = make_map_3d(&tmB, bf, B, K, N, batch, ldb * 2, stride_b * 2, BK, BN);
+  else
+    rc = make_map_3d(&tmB, bf, B, N, K, batch, ldb * 2, stride_b * 2, 64, BK);
+  if (rc) return rc;
+  if (out_f32)
+    rc = make_map_3d(&tmC, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, C, N, M, batch, ldc * 4, stride_c * 4, 32, 32);
+  else
+    rc = make_map_3d(&tmC, bf, C, N, M, batch, ldc * 2, stride_c * 2, 64, 32);
+  if (rc) return rc;
+
+  GemmParams p{M, N, K, batch, accumulate, status};
+  const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * batch;
+  const int grid = tiles < sm_count() ? tiles : sm_count();
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (BN == 256) return dispatch<256>(a_mn, b_mn, out_f32, tmA, tmB, tmC, p, grid, s);
+  return dispatch<128>(a_mn, b_mn, out_f32, tmA, tmB, tmC, p, grid, s);
+}

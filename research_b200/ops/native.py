@@ -1,0 +1,330 @@
+"""ctypes binding of the in-tree sm_100a kernel library (``ops/_lib/libb200ops.so``).
+
+Every wrapper takes torch CUDA tensors, launches on torch's current stream and raises
+:class:`KernelError` if the launcher rejects its arguments.  Kernels with bounded device-side waits
+report through a per-device status word that :func:`check_status` reads (a synchronising call meant
+for tests and for the end of a step, not for the hot path).
+
+``LAUNCHES`` counts kernel launches issued through this module; ``bench.py`` reports it.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import threading
+from pathlib import Path
+
+import torch
+
+from research_b200.errors import KernelError
+
+_LIB_PATH = Path(__file__).resolve().parent / "_lib" / "libb200ops.so"
+_lib: ctypes.CDLL | None = None
+_lock = threading.Lock()
+_status: dict[int, torch.Tensor] = {}
+_scratch: dict[tuple[int, str], torch.Tensor] = {}
+
+LAUNCHES = 0
+
+c_void_p, c_int, c_ll, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+
+
+def lib_path() -> Path:
+    return _LIB_PATH
+
+
+def available() -> bool:
+    return _LIB_PATH.exists()
+
+
+def load() -> ctypes.CDLL:
+    """Load the kernel library, building it first when the shared object is missing."""
+
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is None:
+            if not _LIB_PATH.exists():
+                from research_b200.kernels.build import build_all
+
+                build_all()
+            if not _LIB_PATH.exists():
+                raise KernelError(f"native kernel library is missing: {_LIB_PATH}")
+            lib = ctypes.CDLL(str(_LIB_PATH))
+            _declare(lib)
+            _lib = lib
+    return _lib
+
+
+def _declare(lib: ctypes.CDLL) -> None:
+    def sig(name: str, *argtypes) -> None:
+        fn = getattr(lib, name, None)
+        if fn is None:
+            return
+        fn.argtypes = list(argtypes)
+        fn.restype = c_int
+
+    sig("b200_gemm_bf16", c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll,
+        c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p)
+    sig("b200_rmsnorm_fwd", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p)
+    sig("b200_rmsnorm_bwd", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p)
+    sig("b200_qknorm_rope_fwd", c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int,
+        c_float, c_float, c_int, c_void_p)
+    sig("b200_qknorm_rope_bwd", c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p,
+        c_ll, c_int, c_int, c_float, c_int, c_void_p)
+    sig("b200_swiglu_fwd", c_void_p, c_void_p, c_ll, c_int, c_void_p)
+    sig("b200_swiglu_bwd", c_void_p, c_void_p, c_void_p, c_ll, c_int, c_void_p)
+    sig("b200_sigmoid_gate_fwd", c_void_p, c_void_p, c_void_p, c_ll, c_void_p)
+    sig("b200_sigmoid_gate_bwd", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_void_p)
+    sig("b200_embedding_fwd", c_void_p, c_void_p, c_void_p, c_ll, c_int, c_float, c_void_p)
+    sig("b200_embedding_bwd", c_void_p, c_void_p, c_void_p, c_ll, c_int, c_float, c_void_p)
+    sig("b200_ce_fwd_bwd", c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
+        c_float, c_int, c_void_p)
+    sig("b200_adamw", c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_ll, c_float, c_float, c_float,
+        c_float, c_float, c_float, c_float, c_void_p)
+    sig("b200_sumsq", c_void_p, c_int, c_ll, c_void_p, c_void_p, c_int, c_void_p)
+    sig("b200_cast_f32_bf16", c_void_p, c_void_p, c_ll, c_float, c_void_p)
+    sig("b200_attn_fwd", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+        c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_float, c_int, c_int, c_void_p, c_void_p)
+    sig("b200_attn_bwd", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+        c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll,
+        c_ll, c_ll, c_ll, c_float, c_int, c_int, c_void_p, c_void_p)
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def status_word(device: torch.device | int | None = None) -> torch.Tensor:
+    dev = torch.cuda.current_device() if device is None else torch.device(device).index
+    if dev is None:
+        dev = torch.cuda.current_device()
+    buf = _status.get(dev)
+    if buf is None:
+        buf = torch.zeros(4, dtype=torch.int32, device=f"cuda:{dev}")
+        _status[dev] = buf
+    return buf
+
+
+def check_status(device: torch.device | int | None = None) -> None:
+    """Synchronise and raise if a kernel's bounded wait ran out since the last check."""
+
+    buf = status_word(device)
+    code = int(buf[0].item())
+    if code != 0:
+        buf.zero_()
+        raise KernelError(f"device-side bounded wait ran out (status code {code})")
+
+
+def scratch(name: str, numel: int, dtype: torch.dtype, device: torch.device) -> torch.Tensor:
+    key = (device.index if device.index is not None else torch.cuda.current_device(), name)
+    buf = _scratch.get(key)
+    if buf is None or buf.numel() < numel or buf.dtype != dtype:
+        buf = torch.empty(numel, dtype=dtype, device=device)
+        _scratch[key] = buf
+    return buf
+
+
+def _check(rc: int, what: str) -> None:
+    global LAUNCHES
+    if rc != 0:
+        raise KernelError(f"{what} failed with code {rc}")
+    LAUNCHES += 1
+
+
+# --------------------------------------------------------------------------------------------------
+# GEMM
+# --------------------------------------------------------------------------------------------------
+def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bool = True,
+         out: torch.Tensor | None = None, out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False,
+         bn: int = 0) -> torch.Tensor:
+    """``C = op(A) @ op(B)`` with bf16 inputs and fp32 accumulation on the tcgen05 tensor cores.
+
+    ``trans_a=False``: ``a`` is ``[..., M, K]``; ``True``: ``a`` is ``[..., K, M]``.
+    ``trans_b=True`` : ``b`` is ``[..., N, K]`` (``y = x @ w.T``); ``False``: ``b`` is ``[..., K, N]``.
+    Leading batch dimension (at most one) must match.  Rows may be strided; the last dim is dense.
+    """
+
+    lib = load()
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        raise KernelError("gemm expects bf16 operands")
+    if a.dim() == 2:
+        a3, b3 = a.unsqueeze(0), b.unsqueeze(0)
+    else:
+        a3, b3 = a, b
+    if a3.dim() != 3 or b3.dim() != 3 or a3.shape[0] != b3.shape[0]:
+        raise KernelError(f"gemm batch shapes do not match: {tuple(a.shape)} x {tuple(b.shape)}")
+    if a3.stride(-1) != 1 or b3.stride(-1) != 1:
+        raise KernelError("gemm operands need a dense last dimension")
+    batch = a3.shape[0]
+    M, K = (a3.shape[2], a3.shape[1]) if trans_a else (a3.shape[1], a3.shape[2])
+    N, Kb = (b3.shape[1], b3.shape[2]) if trans_b else (b3.shape[2], b3.shape[1])
+    if K != Kb:
+        raise KernelError(f"gemm inner dimensions differ: {K} vs {Kb}")
+    if out is None:
+        shape = (batch, M, N) if a.dim() == 3 else (M, N)
+        out = torch.empty(shape, dtype=out_dtype, device=a.device)
+        if accumulate:
+            out.zero_()
+    c3 = out.unsqueeze(0) if out.dim() == 2 else out
+    if c3.stride(-1) != 1 or c3.shape != (batch, M, N):
+        raise KernelError("gemm output has the wrong shape or a strided last dimension")
+    rc = lib.b200_gemm_bf16(
+        a3.data_ptr(), b3.data_ptr(), c3.data_ptr(), M, N, K, batch,
+        a3.stride(1), b3.stride(1), c3.stride(1),
+        a3.stride(0) if batch > 1 else 0, b3.stride(0) if batch > 1 else 0, c3.stride(0) if batch > 1 else 0,
+        int(trans_a), int(not trans_b), int(out.dtype == torch.float32), int(accumulate), bn,
+        status_word(a.device).data_ptr(), _stream())
+    _check(rc, "b200_gemm_bf16")
+    return out
+
+
+# --------------------------------------------------------------------------------------------------
+# normalisation / activation / embedding / loss / optimizer
+# --------------------------------------------------------------------------------------------------
+def rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor, eps: float, delta: torch.Tensor | None = None):
+    """Returns ``(y, rstd, residual)``; ``residual = x + delta`` when ``delta`` is given, else ``x``."""
+
+    lib = load()
+    H = x.shape[-1]
+    rows = x.numel() // H
+    y = torch.empty_like(x)
+    rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+    res = torch.empty_like(x) if delta is not None else None
+    rc = lib.b200_rmsnorm_fwd(x.data_ptr(), _ptr(delta), w.data_ptr(), _ptr(res), y.data_ptr(), rstd.data_ptr(), rows, H,
+                              eps, _stream())
+    _check(rc, "b200_rmsnorm_fwd")
+    return y, rstd, (res if res is not None else x)
+
+
+def rmsnorm_bwd(x: torch.Tensor, w: torch.Tensor, rstd: torch.Tensor, dy: torch.Tensor, dw: torch.Tensor,
+                dres: torch.Tensor | None = None) -> torch.Tensor:
+    """dx (+ dres); ``dw`` (fp32) is accumulated into."""
+
+    lib = load()
+    H = x.shape[-1]
+    rows = x.numel() // H
+    dx = torch.empty_like(x)
+    rc = lib.b200_rmsnorm_bwd(x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dy.data_ptr(), _ptr(dres), dx.data_ptr(),
+                              dw.data_ptr(), rows, H, _stream())
+    _check(rc, "b200_rmsnorm_bwd")
+    return dx
+
+
+def qknorm_rope_fwd(inp: torch.Tensor, out: torch.Tensor, w: torch.Tensor | None, positions: torch.Tensor,
+                    heads: int, head_dim: int, eps: float, theta: float, rope: bool):
+    """inp/out: 2-D ``[tokens, row_stride]`` views whose first ``heads*head_dim`` columns are the heads."""
+
+    lib = load()
+    tokens = inp.shape[0]
+    rstd = torch.empty(tokens * heads, dtype=torch.float32, device=inp.device) if w is not None else None
+    rc = lib.b200_qknorm_rope_fwd(inp.data_ptr(), inp.stride(0), out.data_ptr(), out.stride(0), _ptr(w),
+                                  positions.data_ptr(), _ptr(rstd), tokens, heads, head_dim, eps, theta, int(rope),
+                                  _stream())
+    _check(rc, "b200_qknorm_rope_fwd")
+    return rstd
+
+
+def qknorm_rope_bwd(inp: torch.Tensor, dout: torch.Tensor, din: torch.Tensor, w: torch.Tensor | None,
+                    positions: torch.Tensor, rstd: torch.Tensor | None, dw: torch.Tensor | None, heads: int,
+                    head_dim: int, theta: float, rope: bool) -> None:
+    lib = load()
+    rc = lib.b200_qknorm_rope_bwd(inp.data_ptr(), inp.stride(0), dout.data_ptr(), dout.stride(0), din.data_ptr(),
+                                  din.stride(0), _ptr(w), positions.data_ptr(), _ptr(rstd), _ptr(dw), inp.shape[0],
+                                  heads, head_dim, theta, int(rope), _stream())
+    _check(rc, "b200_qknorm_rope_bwd")
+
+
+def swiglu_fwd(gu: torch.Tensor) -> torch.Tensor:
+    lib = load()
+    inter = gu.shape[-1] // 2
+    rows = gu.numel() // (2 * inter)
+    h = torch.empty(*gu.shape[:-1], inter, dtype=gu.dtype, device=gu.device)
+    _check(lib.b200_swiglu_fwd(gu.data_ptr(), h.data_ptr(), rows, inter, _stream()), "b200_swiglu_fwd")
+    return h
+
+
+def swiglu_bwd(gu: torch.Tensor, dh: torch.Tensor) -> torch.Tensor:
+    lib = load()
+    inter = gu.shape[-1] // 2
+    rows = gu.numel() // (2 * inter)
+    dgu = torch.empty_like(gu)
+    _check(lib.b200_swiglu_bwd(gu.data_ptr(), dh.data_ptr(), dgu.data_ptr(), rows, inter, _stream()), "b200_swiglu_bwd")
+    return dgu
+
+
+def sigmoid_gate_fwd(a: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    lib = load()
+    out = torch.empty_like(a)
+    _check(lib.b200_sigmoid_gate_fwd(a.data_ptr(), gate.data_ptr(), out.data_ptr(), a.numel(), _stream()),
+           "b200_sigmoid_gate_fwd")
+    return out
+
+
+def sigmoid_gate_bwd(a: torch.Tensor, gate: torch.Tensor, dout: torch.Tensor):
+    lib = load()
+    da, dg = torch.empty_like(a), torch.empty_like(gate)
+    _check(lib.b200_sigmoid_gate_bwd(a.data_ptr(), gate.data_ptr(), dout.data_ptr(), da.data_ptr(), dg.data_ptr(),
+                                     a.numel(), _stream()), "b200_sigmoid_gate_bwd")
+    return da, dg
+
+
+def embedding_fwd(ids: torch.Tensor, table: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    lib = load()
+    H = table.shape[1]
+    out = torch.empty(*ids.shape, H, dtype=table.dtype, device=table.device)
+    _check(lib.b200_embedding_fwd(ids.data_ptr(), table.data_ptr(), out.data_ptr(), ids.numel(), H, scale, _stream()),
+           "b200_embedding_fwd")
+    return out
+
+
+def embedding_bwd(ids: torch.Tensor, dout: torch.Tensor, dtable: torch.Tensor, scale: float = 1.0) -> None:
+    lib = load()
+    H = dtable.shape[1]
+    _check(lib.b200_embedding_bwd(ids.data_ptr(), dout.data_ptr(), dtable.data_ptr(), ids.numel(), H, scale, _stream()),
+           "b200_embedding_bwd")
+
+
+def ce_fwd_bwd(logits: torch.Tensor, targets: torch.Tensor, mask: torch.Tensor, grad_scale: float, z_weight: float,
+               write_grad: bool = True):
+    """Per-row loss and lse^2 for one ``[rows, V]`` bf16 chunk; ``logits`` becomes ``dlogits`` in place."""
+
+    lib = load()
+    rows, V = logits.shape
+    loss = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    z = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    lse = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    rc = lib.b200_ce_fwd_bwd(logits.data_ptr(), logits.stride(0), targets.data_ptr(), mask.data_ptr(), loss.data_ptr(),
+                             z.data_ptr(), lse.data_ptr(), rows, V, grad_scale, z_weight, int(write_grad), _stream())
+    _check(rc, "b200_ce_fwd_bwd")
+    return loss, z, lse
+
+
+def adamw(p: torch.Tensor, m: torch.Tensor, v: torch.Tensor, g: torch.Tensor, shadow: torch.Tensor | None,
+          gscale: torch.Tensor | None, lr: float, b1: float, b2: float, eps: float, wd: float, step: int) -> None:
+    lib = load()
+    bc1 = 1.0 - b1 ** step
+    bc2 = 1.0 - b2 ** step
+    rc = lib.b200_adamw(p.data_ptr(), m.data_ptr(), v.data_ptr(), g.data_ptr(), int(g.dtype == torch.bfloat16),
+                        _ptr(shadow), _ptr(gscale), p.numel(), lr, b1, b2, eps, wd, bc1, bc2, _stream())
+    _check(rc, "b200_adamw")
+
+
+def sumsq(x: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+    global LAUNCHES
+    lib = load()
+    sc = scratch("sumsq", 1024, torch.float32, x.device)
+    rc = lib.b200_sumsq(x.data_ptr(), int(x.dtype == torch.bfloat16), x.numel(), sc.data_ptr(), out.data_ptr(),
+                        int(accumulate), _stream())
+    _check(rc, "b200_sumsq")
+    LAUNCHES += 1
+
+
+def cast_f32_bf16(x: torch.Tensor, y: torch.Tensor, scale: float = 1.0) -> None:
+    lib = load()
+    _check(lib.b200_cast_f32_bf16(x.data_ptr(), y.data_ptr(), x.numel(), scale, _stream()), "b200_cast_f32_bf16")

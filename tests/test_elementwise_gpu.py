@@ -1,0 +1,145 @@
+"""Bandwidth-bound kernels against fp32 PyTorch restatements of the same math."""
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _bf(shape, seed, scale=1.0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(shape, generator=g, device="cuda") * scale).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("H", [128, 2048, 4096, 1000])
+def test_rmsnorm_fwd_bwd(H):
+    from research_b200.ops import native
+
+    rows, eps = 77, 1e-6
+    x, delta, dy = _bf((rows, H), 1), _bf((rows, H), 2), _bf((rows, H), 3)
+    w = torch.rand(H, device="cuda") + 0.5
+    y, rstd, res = native.rmsnorm_fwd(x, w, eps, delta)
+    resf = (x.float() + delta.float()).to(torch.bfloat16).float()
+    ref = resf * torch.rsqrt(resf.pow(2).mean(-1, keepdim=True) + eps) * w
+    assert torch.allclose(res.float(), resf, atol=1e-2, rtol=1e-2)
+    assert torch.allclose(y.float(), ref, atol=3e-2, rtol=2e-2)
+    xr = res.float().requires_grad_(True)
+    wr = w.clone().requires_grad_(True)
+    yr = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + eps) * wr
+    yr.backward(dy.float())
+    dw = torch.zeros(H, device="cuda")
+    dx = native.rmsnorm_bwd(res, w, rstd, dy, dw)
+    assert torch.allclose(dx.float(), xr.grad, atol=3e-2, rtol=3e-2)
+    assert torch.allclose(dw, wr.grad, atol=5e-2, rtol=2e-2)
+
+
+def _rope_ref(x, pos, theta):
+    D = x.shape[-1]
+    inv = theta ** (-torch.arange(0, D, 2, device=x.device, dtype=torch.float32) / D)
+    ang = pos.float()[:, None, None] * inv
+    c, s = ang.cos(), ang.sin()
+    a, b = x[..., 0::2], x[..., 1::2]
+    return torch.stack([a * c - b * s, a * s + b * c], dim=-1).flatten(-2)
+
+
+@pytest.mark.parametrize("D", [32, 64, 128])
+def test_qknorm_rope(D):
+    from research_b200.ops import native
+
+    T, heads, theta, eps = 50, 6, 10000.0, 1e-6
+    stride = heads * D + 64
+    buf = _bf((T, stride), 4)
+    pos = torch.arange(T, device="cuda", dtype=torch.int32) * 3
+    w = torch.rand(D, device="cuda") + 0.5
+    out = torch.zeros(T, heads * D, dtype=torch.bfloat16, device="cuda")
+    rstd = native.qknorm_rope_fwd(buf, out, w, pos, heads, D, eps, theta, True)
+    xin = buf[:, : heads * D].float().view(T, heads, D).requires_grad_(True)
+    wr = w.clone().requires_grad_(True)
+    xn = xin * torch.rsqrt(xin.pow(2).mean(-1, keepdim=True) + eps) * wr
+    ref = _rope_ref(xn, pos, theta)
+    assert torch.allclose(out.float().view(T, heads, D), ref, atol=3e-2, rtol=3e-2)
+    dout = _bf((T, heads * D), 5)
+    ref.backward(dout.float().view(T, heads, D))
+    din = torch.zeros(T, heads * D, dtype=torch.bfloat16, device="cuda")
+    dw = torch.zeros(D, device="cuda")
+    native.qknorm_rope_bwd(buf, dout, din, w, pos, rstd, dw, heads, D, theta, True)
+    assert torch.allclose(din.float().view(T, heads, D), xin.grad, atol=4e-2, rtol=4e-2)
+    assert torch.allclose(dw, wr.grad, atol=0.15, rtol=3e-2)
+
+
+def test_swiglu_and_gate():
+    from research_b200.ops import native
+
+    rows, inter = 33, 256
+    gu, dh = _bf((rows, 2 * inter), 6), _bf((rows, inter), 7)
+    h = native.swiglu_fwd(gu)
+    g = gu[:, :inter].float().requires_grad_(True)
+    u = gu[:, inter:].float().requires_grad_(True)
+    ref = torch.nn.functional.silu(g) * u
+    assert torch.allclose(h.float(), ref, atol=2e-2, rtol=2e-2)
+    ref.backward(dh.float())
+    dgu = native.swiglu_bwd(gu, dh)
+    assert torch.allclose(dgu[:, :inter].float(), g.grad, atol=3e-2, rtol=3e-2)
+    assert torch.allclose(dgu[:, inter:].float(), u.grad, atol=3e-2, rtol=3e-2)
+    a, gate, dout = _bf((rows, inter), 8), _bf((rows, inter), 9), _bf((rows, inter), 10)
+    out = native.sigmoid_gate_fwd(a, gate)
+    assert torch.allclose(out.float(), a.float() * torch.sigmoid(gate.float()), atol=2e-2, rtol=2e-2)
+    da, dg = native.sigmoid_gate_bwd(a, gate, dout)
+    sg = torch.sigmoid(gate.float())
+    assert torch.allclose(da.float(), dout.float() * sg, atol=2e-2, rtol=2e-2)
+    assert torch.allclose(dg.float(), dout.float() * a.float() * sg * (1 - sg), atol=2e-2, rtol=3e-2)
+
+
+def test_embedding_and_ce():
+    from research_b200.ops import native
+
+    V, H, T = 1000, 64, 40
+    table = _bf((V, H), 11)
+    ids = torch.randint(0, V, (T,), device="cuda", dtype=torch.int32)
+    out = native.embedding_fwd(ids, table, 2.0)
+    assert torch.allclose(out.float(), table[ids.long()].float() * 2.0, atol=1e-2, rtol=1e-2)
+    dtable = torch.zeros(V, H, device="cuda")
+    native.embedding_bwd(ids, out, dtable, 1.0)
+    ref = torch.zeros(V, H, device="cuda").index_add_(0, ids.long(), out.float())
+    assert torch.allclose(dtable, ref, atol=1e-3, rtol=1e-3)
+
+    V2 = 50304
+    logits = _bf((T, V2), 12, 2.0)
+    tgt = torch.randint(0, V2, (T,), device="cuda", dtype=torch.int32)
+    mask = (torch.rand(T, device="cuda") > 0.2).to(torch.uint8)
+    zw, gs = 1e-4, 1.0 / float(mask.sum().item())
+    lf = logits.float().requires_grad_(True)
+    lse = torch.logsumexp(lf, -1)
+    ce = (lse - lf.gather(1, tgt.long()[:, None])[:, 0]) * mask
+    obj = (ce.sum() + zw * (lse.pow(2) * mask).sum()) * gs
+    obj.backward()
+    loss, z, lse_k = native.ce_fwd_bwd(logits, tgt, mask, gs, zw)
+    assert torch.allclose(loss, ce.detach(), atol=2e-3, rtol=1e-3)
+    assert torch.allclose(z, (lse.pow(2) * mask).detach(), atol=1e-2, rtol=1e-3)
+    assert torch.allclose(logits.float(), lf.grad, atol=2e-4, rtol=5e-2)
+
+
+def test_adamw_sumsq_cast():
+    from research_b200.ops import native
+
+    n = 100_003
+    p = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda").to(torch.bfloat16)
+    m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    shadow = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+    pr = p.clone().requires_grad_(True)
+    opt = torch.optim.AdamW([pr], lr=1e-2, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.1)
+    for step in range(1, 4):
+        pr.grad = g.float()
+        opt.step()
+        native.adamw(p, m, v, g, shadow, None, 1e-2, 0.9, 0.999, 1e-8, 0.1, step)
+    assert torch.allclose(p, pr.detach(), atol=1e-5, rtol=1e-4)
+    assert torch.allclose(shadow.float(), p, atol=1e-2, rtol=1e-2)
+    out = torch.zeros(1, device="cuda")
+    native.sumsq(g, out)
+    assert math.isclose(out.item(), g.float().pow(2).sum().item(), rel_tol=1e-4)
+    y = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+    native.cast_f32_bf16(p, y, 0.5)
+    assert torch.allclose(y.float(), p * 0.5, atol=1e-2, rtol=1e-2)

@@ -1,0 +1,86 @@
+"""tcgen05 GEMM against a plain fp32 PyTorch reference, all four operand layouts, tails, batch, accumulate."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(a, b, trans_a, trans_b):
+    af = a.float().transpose(-1, -2) if trans_a else a.float()
+    bf = b.float().transpose(-1, -2) if trans_b else b.float()
+    return af @ bf
+
+
+def _rand(shape, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(shape, generator=g, device="cuda") * 0.5).to(torch.bfloat16)
+
+
+@pytest.mark.parametrize("trans_a,trans_b", [(False, True), (False, False), (True, False), (True, True)])
+@pytest.mark.parametrize("mnk", [(128, 256, 64), (256, 512, 256), (384, 320, 192), (200, 136, 72), (1024, 2048, 512)])
+def test_gemm_layouts(trans_a, trans_b, mnk):
+    from research_b200.ops import native
+
+    M, N, K = mnk
+    a = _rand((K, M) if trans_a else (M, K), 1)
+    b = _rand((N, K) if trans_b else (K, N), 2)
+    out = native.gemm(a, b, trans_a=trans_a, trans_b=trans_b)
+    native.check_status()
+    ref = _ref(a, b, trans_a, trans_b)
+    err = (out.float() - ref).abs().max().item()
+    scale = ref.abs().max().item()
+    assert err <= 1e-2 * scale + 1e-2, (err, scale)
+
+
+@pytest.mark.parametrize("bn", [128, 256])
+def test_gemm_fp32_out_and_accumulate(bn):
+    from research_b200.ops import native
+
+    M, N, K = 512, 768, 320
+    a, b = _rand((M, K), 3), _rand((N, K), 4)
+    out = native.gemm(a, b, out_dtype=torch.float32, bn=bn)
+    ref = _ref(a, b, False, True)
+    assert (out - ref).abs().max().item() <= 2e-3 * ref.abs().max().item() + 1e-3
+    native.gemm(a, b, out=out, accumulate=True, bn=bn)
+    native.check_status()
+    assert (out - 2 * ref).abs().max().item() <= 4e-3 * ref.abs().max().item() + 2e-3
+
+
+def test_gemm_batched_and_strided_rows():
+    from research_b200.ops import native
+
+    B, M, N, K = 3, 256, 384, 128
+    a, b = _rand((B, M, K), 5), _rand((B, N, K), 6)
+    out = native.gemm(a, b)
+    ref = _ref(a, b, False, True)
+    assert (out.float() - ref).abs().max().item() <= 1e-2 * ref.abs().max().item() + 1e-2
+    wide = _rand((M, 2 * K), 7)
+    a2 = wide[:, :K]  # row stride 2K
+    out2 = native.gemm(a2, b[0])
+    native.check_status()
+    ref2 = _ref(a2, b[0], False, True)
+    assert (out2.float() - ref2).abs().max().item() <= 1e-2 * ref2.abs().max().item() + 1e-2
+
+
+def test_gemm_large_matches_and_is_timed():
+    from research_b200.ops import native
+
+    M = N = K = 4096
+    a, b = _rand((M, K), 8), _rand((N, K), 9)
+    out = native.gemm(a, b)
+    ref = (a @ b.t()).float()
+    assert (out.float() - ref).abs().max().item() <= 2e-2 * ref.abs().max().item()
+    for _ in range(3):
+        native.gemm(a, b, out=out)
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(10):
+        native.gemm(a, b, out=out)
+    e.record()
+    torch.cuda.synchronize()
+    native.check_status()
+    tflops = 10 * 2 * M * N * K / (s.elapsed_time(e) * 1e-3) / 1e12
+    print(f"gemm 4096^3: {tflops:.1f} TFLOP/s")
+    assert tflops > 50
