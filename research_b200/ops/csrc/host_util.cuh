@@ -70,22 +70,26 @@ inline int make_map_3d(CUtensorMap* out, CUtensorMapDataType dt, const void* bas
   return RC_OK;
 }
 
-// 4-D variant used by attention: [d3][d2][d1][d0], box {b0, b1, 1, 1}
+// Rank-4 tensor [d3][d2][d1][d0] with byte strides s1 <= s2 <= s3 (each a multiple of the one before,
+// which is why attention orders its dims as head_dim, head, token, batch); box {b0, b1, b2, 1}.
 inline int make_map_4d(CUtensorMap* out, CUtensorMapDataType dt, const void* base, uint64_t d0, uint64_t d1,
                        uint64_t d2, uint64_t d3, uint64_t s1_bytes, uint64_t s2_bytes, uint64_t s3_bytes, uint32_t b0,
-                       uint32_t b1, CUtensorMapSwizzle swz = CU_TENSOR_MAP_SWIZZLE_128B) {
+                       uint32_t b1, uint32_t b2, CUtensorMapSwizzle swz = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return RC_NO_DRIVER_ENTRY;
   if ((reinterpret_cast<uintptr_t>(base) & 15) || (s1_bytes & 15) || (s2_bytes & 15) || (s3_bytes & 15))
     return RC_BAD_ALIGNMENT;
   cuuint64_t dims[4] = {d0, d1, d2, d3};
   cuuint64_t strides[3] = {s1_bytes, s2_bytes, s3_bytes};
-  cuuint32_t box[4] = {b0, b1, 1, 1};
+  cuuint32_t box[4] = {b0, b1, b2, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = fn(out, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
-    fprintf(stderr, "research_b200: cuTensorMapEncodeTiled(4d) failed (%d)\n", (int)r);
+    fprintf(stderr,
+            "research_b200: cuTensorMapEncodeTiled(4d) failed (%d) dims=(%llu,%llu,%llu,%llu) strides=(%llu,%llu,%llu)\n",
+            (int)r, (unsigned long long)d0, (unsigned long long)d1, (unsigned long long)d2, (unsigned long long)d3,
+            (unsigned long long)s1_bytes, (unsigned long long)s2_bytes, (unsigned long long)s3_bytes);
     return RC_TENSORMAP_FAILED;
   }
   return RC_OK;

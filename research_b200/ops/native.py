@@ -328,3 +328,75 @@ def sumsq(x: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
 def cast_f32_bf16(x: torch.Tensor, y: torch.Tensor, scale: float = 1.0) -> None:
     lib = load()
     _check(lib.b200_cast_f32_bf16(x.data_ptr(), y.data_ptr(), x.numel(), scale, _stream()), "b200_cast_f32_bf16")
+
+
+# --------------------------------------------------------------------------------------------------
+# attention
+# --------------------------------------------------------------------------------------------------
+def _check_bshd(t: torch.Tensor, name: str) -> None:
+    if t.dim() != 4 or t.stride(3) != 1 or t.stride(2) != t.shape[3]:
+        raise KernelError(f"{name} must be a [B,S,H,D] view with heads D elements apart and a dense last dim")
+
+
+def attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool = True,
+             lo: torch.Tensor | None = None, scale: float | None = None):
+    """Flash attention forward.  q: ``[B,S,Hq,D]``, k/v: ``[B,S,Hkv,D]`` (views into a packed buffer are fine).
+
+    ``lo`` (int32 ``[B,S]``, non-decreasing along S) is the first kv position each query row may attend to.
+    Returns ``(o [B,S,Hq,D] bf16, lse [B,Hq,S] fp32)``.
+    """
+
+    lib = load()
+    for t, n in ((q, "q"), (k, "k"), (v, "v")):
+        _check_bshd(t, n)
+    B, S, Hq, D = q.shape
+    Hkv = k.shape[2]
+    o = torch.empty((B, S, Hq, D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, Hq, S), dtype=torch.float32, device=q.device)
+    if scale is None:
+        scale = D ** -0.5
+    rc = lib.b200_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), _ptr(lo), B, S, Hq,
+                           Hkv, D, q.stride(1), q.stride(0), k.stride(1), k.stride(0), v.stride(1), v.stride(0),
+                           o.stride(1), o.stride(0), scale, int(causal), 0, status_word(q.device).data_ptr(), _stream())
+    _check(rc, "b200_attn_fwd")
+    return o, lse
+
+
+def kv_visibility_upper_bound(lo: torch.Tensor) -> torch.Tensor:
+    """kv-side view of a per-query lower bound: ``hi[b,k]`` = last query position that may attend to kv ``k``.
+
+    ``lo`` must be non-decreasing along the sequence, so ``hi[k] = #{q : lo[q] <= k} - 1``.
+    """
+
+    B, S = lo.shape
+    k = torch.arange(S, device=lo.device, dtype=lo.dtype).expand(B, S).contiguous()
+    return (torch.searchsorted(lo.contiguous(), k, right=True) - 1).to(torch.int32)
+
+
+def attn_bwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor, d_o: torch.Tensor,
+             lse: torch.Tensor, *, causal: bool = True, lo: torch.Tensor | None = None,
+             hi: torch.Tensor | None = None, scale: float | None = None):
+    """Flash attention backward; returns dense ``(dq, dk, dv)`` shaped like q, k, v."""
+
+    global LAUNCHES
+    lib = load()
+    for t, n in ((q, "q"), (k, "k"), (v, "v"), (o, "o"), (d_o, "d_o")):
+        _check_bshd(t, n)
+    B, S, Hq, D = q.shape
+    Hkv = k.shape[2]
+    if scale is None:
+        scale = D ** -0.5
+    if lo is not None and hi is None:
+        hi = kv_visibility_upper_bound(lo)
+    dq = torch.empty((B, S, Hq, D), dtype=q.dtype, device=q.device)
+    dk = torch.empty((B, S, Hkv, D), dtype=q.dtype, device=q.device)
+    dv = torch.empty((B, S, Hkv, D), dtype=q.dtype, device=q.device)
+    delta = torch.empty((B, Hq, S), dtype=torch.float32, device=q.device)
+    rc = lib.b200_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(), lse.data_ptr(),
+                           delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _ptr(lo), _ptr(hi), B, S, Hq,
+                           Hkv, D, q.stride(1), q.stride(0), k.stride(1), k.stride(0), v.stride(1), v.stride(0),
+                           o.stride(1), o.stride(0), d_o.stride(1), d_o.stride(0), scale, int(causal), 0,
+                           status_word(q.device).data_ptr(), _stream())
+    _check(rc, "b200_attn_bwd")
+    LAUNCHES += 2
+    return dq, dk, dv
