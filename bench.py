@@ -1,0 +1,241 @@
+"""Headline benchmark: training throughput (tokens/s, MFU) of the dense ~1.3B decoder on N GPUs of one node.
+
+Config (weak scaling, per-GPU work fixed): 24 layers, d_model 2048, 16 query / 8 KV heads (head_dim 128), SwiGLU
+5632, RMSNorm, RoPE, QK-norm, vocab 50304, normal(0, 0.02) init; bf16 compute with fp32 masters; seq_len 4096
+with document-boundary attention masks from geometric(mean 1500) document lengths and uniform random token ids;
+8 sequences per GPU (global batch 64 at 8 GPUs), grad-accum 1; mesh fsdp=N; Muon on 2-D weights (distributed
+over the fsdp axis), AdamW on embeddings, lm_head and norms.
+
+Prints ONE JSON line on rank 0.  ``value`` is device-timed (CUDA events on the compute stream, max over ranks)
+over K optimizer steps whose host batches were prepared beforehand; ``e2e`` times K more steps through the public
+``Trainer.train_step()`` call with the wall clock between barriers + synchronizes, including the data pipeline,
+the pinned host->device copy of every step's tokens and the device->host read of the step's loss.
+
+``--impl reference`` runs the unmodified reference from ``baseline/_ref`` when it can be imported there.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+
+def reference_arm(args) -> int:
+    ref = ROOT / "baseline" / "_ref"
+    reason = None
+    if not (ref / "jaxtitan").is_dir():
+        reason = "baseline/_ref/jaxtitan is missing (offline pip install of the reference did not run)"
+    else:
+        sys.path.insert(0, str(ref))
+        try:
+            import jax  # noqa: F401
+            import jaxtitan.runtime.training  # noqa: F401
+        except Exception as exc:  # jax / flax / optax / orbax / grain are not installable offline
+            reason = f"reference imports fail in this image: {type(exc).__name__}: {exc}"
+    if reason is None:
+        reason = "reference importable but its JAX runtime path is not wired for this benchmark"
+    if int(os.environ.get("RANK", "0")) == 0:
+        print(json.dumps({"impl": "reference", "unavailable": reason}))
+    return 0
+
+
+class ClockSampler:
+    """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.rows: list[list[str]] = []
+        self.proc = None
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        def pump():
+            for line in self.proc.stdout:
+                self.rows.append([c.strip() for c in line.split(",")])
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1])); mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, r[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def dense_1p3b_spec(n_gpus: int, manifest: Path, steps_total: int, per_gpu_batch: int, seq_len: int, optimizer: str):
+    from research_b200.config import run_spec_from_mapping
+
+    gb = per_gpu_batch * n_gpus
+    raw = {
+        "run": {"id": "bench-dense-1p3b", "seed": 0, "output_dir": "/tmp/research_b200_bench"},
+        "model": {"name": "decoder", "variant": "dense-1p3b", "vocab_size": 50304, "hidden_size": 2048,
+                  "intermediate_size": 5632, "num_layers": 24, "num_heads": 16, "n_kv_heads": 8,
+                  "max_seq_len": seq_len, "rope_theta": 10000.0, "init": "normal_0.02", "attention_doc_mask": True,
+                  "compute_dtype": "bfloat16", "param_dtype": "float32", "remat": "none"},
+        "optimizer": {"name": optimizer, "weight_decay": 0.0, "grad_clip_norm": 1.0,
+                      "schedule": {"name": "constant", "peak_lr": 3e-4, "warmup_steps": 10}},
+        "data": {"train_manifest": str(manifest), "order": "document_buffer", "shuffle_seed": 0,
+                 "document_buffer_size": 128, "document_refill_size": 128},
+        "training": {"seq_len": seq_len, "global_batch_size": gb, "target_tokens": gb * seq_len * steps_total,
+                     "precision": "bf16", "gradient_accumulation_steps": 1},
+        "mesh": {"axis_names": ["fsdp"], "axis_sizes": [n_gpus]},
+        "parallelism": {"mode": "fsdp"},
+    }
+    return run_spec_from_mapping(raw)
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--per-gpu-batch", type=int, default=8)
+    ap.add_argument("--seq-len", type=int, default=4096)
+    ap.add_argument("--optimizer", default="muon", choices=["muon", "adamw", "dion"])
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from research_b200.data.synthetic import generate_synthetic_dataset
+    from research_b200.ops import native
+    from research_b200.parallel.mesh import init_distributed
+    from research_b200.runtime.flops import estimate_flops_per_token, estimate_flops_per_token_exact
+    from research_b200.runtime.trainer import Trainer
+
+    rank, world = init_distributed()
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torch.distributed.run for N>1")
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    K, W = args.steps, max(args.warmup, 3)
+    steps_total = W + 2 * K + 2
+    gb = args.per_gpu_batch * world
+    tokens_needed = gb * (args.seq_len + 1) * steps_total
+    data_dir = Path(tempfile.gettempdir()) / f"research_b200_bench_data_{world}_{args.seq_len}_{steps_total}"
+    manifest = data_dir / "manifest.json"
+    if rank == 0 and not manifest.exists():
+        docs = int(tokens_needed / 1400 * 1.25) + 256
+        generate_synthetic_dataset(data_dir, seed=0, num_documents=docs, mean_length=1500, min_length=16,
+                                   max_length=16384, vocab_size=50304, eos_id=50303, val_fraction=0.02, overwrite=True)
+    if world > 1:
+        dist.barrier()
+    spec = dense_1p3b_spec(world, manifest, steps_total, args.per_gpu_batch, args.seq_len, args.optimizer)
+    trainer = Trainer(spec)
+    tokens_per_step = gb * args.seq_len
+
+    def sync():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(W):
+        trainer.train_step()
+    native.check_status()
+    # ---- device-timed region: batches prepared on the host beforehand ------------------------------
+    prepared = [trainer.next_accumulated_batch() for _ in range(K)]
+    sampler = ClockSampler(local_rank)
+    sync()
+    sampler.start()
+    launches0 = native.LAUNCHES
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    last = None
+    for batches in prepared:
+        last = trainer.train_on(batches)
+    end.record()
+    sync()
+    launches = native.LAUNCHES - launches0
+    dev_ms = start.elapsed_time(end)
+    # ---- end-to-end region through the public API ---------------------------------------------------
+    h2d0, d2h0 = trainer.train_step_fn.h2d_bytes[0], trainer.train_step_fn.d2h_bytes[0]
+    sync()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        last = trainer.train_step()
+    sync()
+    e2e_s = time.perf_counter() - t0
+    clocks = sampler.stop()
+    native.check_status()
+    h2d = (trainer.train_step_fn.h2d_bytes[0] - h2d0) / K
+    d2h = (trainer.train_step_fn.d2h_bytes[0] - d2h0) / K
+    times = torch.tensor([dev_ms, e2e_s * 1e3], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_ms = times.tolist()
+    value = tokens_per_step * K / (dev_ms * 1e-3)
+    e2e_value = tokens_per_step * K / (e2e_ms * 1e-3)
+    fpt = estimate_flops_per_token(spec.model, args.seq_len)
+    fpt_exact = estimate_flops_per_token_exact(spec.model, args.seq_len)
+    peak = 2.25e15 * world
+    if rank == 0:
+        out = {
+            "metric": "train_tokens_per_sec", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,
+            "steps": K, "warmup": W, "ms_per_step": round(dev_ms / K, 3), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "impl": "native",
+            "config": {"model": "dense-1.3B decoder (24L, d2048, 16q/8kv heads, ffn 5632, vocab 50304)",
+                       "global_batch": gb, "seq_len": args.seq_len, "parallelism": f"fsdp{world}",
+                       "optimizer": args.optimizer, "grad_accum": 1, "doc_masks": "geometric(mean 1500)",
+                       "timing": "CUDA events, max over ranks; inputs larger than L2 (activations of 32K tokens/GPU)"},
+            "mfu": round(100.0 * fpt * value / peak, 2), "mfu_exact": round(100.0 * fpt_exact * value / peak, 2),
+            "flops_per_token": fpt, "peak_flops_per_gpu": 2.25e15,
+            "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms / K, 3),
+                    "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
+            "gpu_launches": int(launches), "clocks": clocks,
+            "final_loss": None if last is None else round(last.loss, 4),
+            "baseline_note": "the reference publishes no B200 number and no number for this config; nearest published: "
+                             "dense 1.666B FSDP2xTP2 Muon 8,136 tok/s on 4xH100",
+        }
+        print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

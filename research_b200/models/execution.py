@@ -1,0 +1,229 @@
+"""Execution policy of a model replica: which process groups split activations and how.
+
+One process drives one GPU; the named mesh axes are ``torch.distributed`` groups (see
+:mod:`research_b200.parallel.mesh`).  This object carries the groups a model needs and implements the
+activation-side collectives as differentiable functions:
+
+* tensor parallel with Megatron-style sequence parallelism (reference: models/execution.py:183-250): the residual
+  stream is ``[B, S/tp, H]`` between blocks, all-gathered along S before column-parallel projections and
+  reduce-scattered after row-parallel ones; the lm_head is vocab-parallel;
+* context parallel: the sequence is split across ``cp`` ranks for every per-token op and attention sees the
+  keys/values of all earlier ranks (reference shards and lets XLA gather: models/execution.py:227-240);
+* expert parallel: policy fields consumed by :mod:`research_b200.models.moe`.
+
+The collectives here are the NCCL (or gloo, on CPU) baseline; fused compute+collective kernels replace them
+where ``fused`` is enabled and the tensors are CUDA bf16.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+from research_b200.ops import functional as Fn
+
+EP_DISPATCHERS = ("all_to_all", "rdep_static", "psum")
+
+
+def _world(group) -> int:
+    return 1 if group is None else dist.get_world_size(group)
+
+
+def _rank(group) -> int:
+    return 0 if group is None else dist.get_rank(group)
+
+
+class _AllGatherDim(torch.autograd.Function):
+    """Forward: all-gather along ``dim``; backward: reduce-scatter (sum) along ``dim``."""
+
+    @staticmethod
+    def forward(ctx, x, group, dim):
+        n = dist.get_world_size(group)
+        ctx.group, ctx.dim, ctx.n = group, dim, n
+        xt = x.movedim(dim, 0).contiguous()
+        out = torch.empty((n * xt.shape[0],) + tuple(xt.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, xt, group=group)
+        return out.movedim(0, dim)
+
+    @staticmethod
+    def backward(ctx, g):
+        gt = g.movedim(ctx.dim, 0).contiguous()
+        out = torch.empty((gt.shape[0] // ctx.n,) + tuple(gt.shape[1:]), dtype=g.dtype, device=g.device)
+        _reduce_scatter(out, gt, ctx.group)
+        return out.movedim(0, ctx.dim), None, None
+
+
+class _ReduceScatterDim(torch.autograd.Function):
+    """Forward: reduce-scatter (sum) along ``dim``; backward: all-gather along ``dim``."""
+
+    @staticmethod
+    def forward(ctx, x, group, dim):
+        n = dist.get_world_size(group)
+        ctx.group, ctx.dim, ctx.n = group, dim, n
+        xt = x.movedim(dim, 0).contiguous()
+        out = torch.empty((xt.shape[0] // n,) + tuple(xt.shape[1:]), dtype=x.dtype, device=x.device)
+        _reduce_scatter(out, xt, group)
+        return out.movedim(0, dim)
+
+    @staticmethod
+    def backward(ctx, g):
+        gt = g.movedim(ctx.dim, 0).contiguous()
+        out = torch.empty((ctx.n * gt.shape[0],) + tuple(gt.shape[1:]), dtype=g.dtype, device=g.device)
+        dist.all_gather_into_tensor(out, gt, group=ctx.group)
+        return out.movedim(0, ctx.dim), None, None
+
+
+def _reduce_scatter(out: torch.Tensor, inp: torch.Tensor, group) -> None:
+    if inp.is_cuda:
+        dist.reduce_scatter_tensor(out, inp, group=group)
+    else:  # gloo has no reduce_scatter: all-reduce then slice
+        tmp = inp.clone()
+        dist.all_reduce(tmp, group=group)
+        n, r = dist.get_world_size(group), dist.get_rank(group)
+        out.copy_(tmp.chunk(n, dim=0)[r])
+
+
+class _AllReduceSum(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        out = x.clone()
+        dist.all_reduce(out, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+class _CopyToGroup(torch.autograd.Function):
+    """Identity forward, all-reduce backward (input replicated, consumers hold partial gradients)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.clone()
+        dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
+class _SliceDim(torch.autograd.Function):
+    """Forward: keep this rank's chunk along ``dim``; backward: all-gather the chunk gradients."""
+
+    @staticmethod
+    def forward(ctx, x, group, dim):
+        n, r = dist.get_world_size(group), dist.get_rank(group)
+        ctx.group, ctx.dim = group, dim
+        return x.chunk(n, dim=dim)[r].contiguous()
+
+    @staticmethod
+    def backward(ctx, g):
+        return _AllGatherDim.apply(g, ctx.group, ctx.dim), None, None
+
+
+def all_gather_dim(x, group, dim):
+    return x if _world(group) == 1 else _AllGatherDim.apply(x, group, dim)
+
+
+def reduce_scatter_dim(x, group, dim):
+    return x if _world(group) == 1 else _ReduceScatterDim.apply(x, group, dim)
+
+
+def all_reduce_sum(x, group):
+    return x if _world(group) == 1 else _AllReduceSum.apply(x, group)
+
+
+def copy_to_group(x, group):
+    return x if _world(group) == 1 else _CopyToGroup.apply(x, group)
+
+
+def slice_dim(x, group, dim):
+    return x if _world(group) == 1 else _SliceDim.apply(x, group, dim)
+
+
+@dataclass
+class ExecutionContext:
+    """Groups and switches a model forward needs.  The default is a single device with nothing split."""
+
+    tp_group: Any = None
+    cp_group: Any = None
+    ep_group: Any = None
+    expert_fsdp_group: Any = None
+    sequence_parallel: bool = True
+    ep_dispatcher: str = "all_to_all"
+    ep_axis_name: str | None = None
+    ep_axis_sharing: str | None = None
+    fused: bool = True                      # use fused compute+collective kernels where available
+    extras: dict[str, Any] = field(default_factory=dict)
+
+    # ---- sizes -----------------------------------------------------------------------------------
+    @property
+    def tp_size(self) -> int:
+        return _world(self.tp_group)
+
+    @property
+    def tp_rank(self) -> int:
+        return _rank(self.tp_group)
+
+    @property
+    def cp_size(self) -> int:
+        return _world(self.cp_group)
+
+    @property
+    def cp_rank(self) -> int:
+        return _rank(self.cp_group)
+
+    @property
+    def ep_size(self) -> int:
+        return _world(self.ep_group)
+
+    @property
+    def ep_rank(self) -> int:
+        return _rank(self.ep_group)
+
+    @property
+    def sp(self) -> bool:
+        return self.tp_size > 1 and self.sequence_parallel and self.cp_size == 1
+
+    # ---- tensor / sequence parallel activations ------------------------------------------------------
+    def scatter_sequence(self, x: torch.Tensor) -> torch.Tensor:
+        """Replicated ``[B,S,H]`` -> this rank's ``[B,S/tp,H]`` (start of the sequence-parallel region)."""
+
+        return slice_dim(x, self.tp_group, 1) if self.sp else x
+
+    def gather_sequence(self, x: torch.Tensor) -> torch.Tensor:
+        """Before a column-parallel projection: SP shard -> full sequence (or mark the replicated input)."""
+
+        if self.tp_size == 1:
+            return x
+        if self.sp:
+            return all_gather_dim(x, self.tp_group, 1)
+        return copy_to_group(x, self.tp_group)
+
+    def reduce_scatter_sequence(self, x: torch.Tensor) -> torch.Tensor:
+        """After a row-parallel projection: sum the partial outputs (and go back to the SP shard)."""
+
+        if self.tp_size == 1:
+            return x
+        if self.sp:
+            return reduce_scatter_dim(x, self.tp_group, 1)
+        return all_reduce_sum(x, self.tp_group)
+
+    def gather_vocab(self, logits: torch.Tensor) -> torch.Tensor:
+        return all_gather_dim(logits, self.tp_group, logits.dim() - 1) if self.tp_size > 1 else logits
+
+    # ---- attention (local, or context parallel) ------------------------------------------------------
+    def attention(self, qkv, wq, wk, positions, *, B, S, hq, hkv, D, eps, theta, rope, lo, hi):
+        if self.cp_size == 1:
+            return Fn.attention_block(qkv, wq, wk, positions, B=B, S=S, hq=hq, hkv=hkv, D=D, eps=eps, theta=theta,
+                                      rope=rope, causal=True, lo=lo, hi=hi)
+        from research_b200.parallel.context import context_parallel_attention
+
+        return context_parallel_attention(self, qkv, wq, wk, positions, B=B, S=S, hq=hq, hkv=hkv, D=D, eps=eps,
+                                          theta=theta, rope=rope, lo=lo)

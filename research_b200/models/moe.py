@@ -1,0 +1,204 @@
+"""Sparse mixture-of-experts feed-forward layer.
+
+Router, expert math, statistics and the sequence balance loss restate the reference
+(src/jaxtitan/models/components/moe.py:98-147 router, 150-195 experts, 367-479 layer, 794-840 statistics):
+``scores = sigmoid(x W_r)``; experts are picked by ``top_k(scores + expert_bias)`` but weighted by the
+unbiased scores, normalised over the selected experts and multiplied by ``route_scale``; ``expert_bias`` gets
+no gradient.  Added here (optional, off by default): a softmax router, capacity-factor token dropping and a
+Switch-style load-balance loss.
+
+Dispatch is expert-major: assignments are sorted by expert, every expert's rows are padded to a multiple
+of 128 so that one grouped tcgen05 GEMM (B operand picked per row tile) covers all local experts; with
+expert parallelism the sorted rows travel through an all-to-all first (:mod:`research_b200.parallel.expert`).
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from research_b200.config.specs import ModelSpec, TrinityMoeSpec
+from research_b200.errors import ContractError
+from research_b200.models.output import AuxLoss, RouterStats
+from research_b200.ops import functional as Fn
+
+
+def router_stats(name: str, layer_index: int, expert_ids: torch.Tensor, weights: torch.Tensor, num_experts: int,
+                 dropped: torch.Tensor | None = None) -> RouterStats:
+    ids = expert_ids.reshape(-1).long()
+    counts = torch.zeros(num_experts, dtype=torch.float32, device=ids.device).index_add_(
+        0, ids, torch.ones_like(ids, dtype=torch.float32))
+    importance = torch.zeros(num_experts, dtype=torch.float32, device=ids.device).index_add_(
+        0, ids, weights.reshape(-1).float())
+    total = counts.sum()
+    mean = total / num_experts
+    load_max, load_min = counts.max(), counts.min()
+    max_vio = (load_max - mean) / mean.clamp_min(1e-6)
+    prob = counts / total.clamp_min(1e-6)
+    entropy = -(torch.where(prob > 0, prob * torch.log(torch.where(prob > 0, prob, torch.ones_like(prob))),
+                            torch.zeros_like(prob))).sum()
+    return RouterStats(name=name, layer_index=layer_index, expert_counts=counts, importance=importance,
+                       total_assignments=total, load_min=load_min, load_max=load_max, load_mean=mean,
+                       max_vio=max_vio, load_entropy=entropy, dropped=dropped)
+
+
+def sequence_balance_loss(expert_ids: torch.Tensor, scores: torch.Tensor, top_k: int, seq_groups=()) -> torch.Tensor:
+    """``sum_e f_e p_e`` per sequence, averaged over the batch; scores: [B,S,E], expert_ids: [B,S,k].
+
+    ``seq_groups``: process groups that split the sequence dimension; the per-sequence sums are all-reduced
+    over them so that a sharded sequence gives the same loss as the whole one.
+    """
+
+    from research_b200.models.execution import all_reduce_sum
+
+    if scores.dim() != 3:
+        raise ContractError(f"router scores must have shape [batch, seq, experts], got {tuple(scores.shape)}")
+    B, S, E = scores.shape
+    selected = F.one_hot(expert_ids.long(), E).float().sum(dim=-2)      # [B,S,E]
+    sel_sum = selected.sum(dim=1)                                        # [B,E]
+    normalised = scores / scores.sum(dim=-1, keepdim=True).clamp_min(1e-20)
+    p_sum = normalised.sum(dim=1)
+    total_S = S
+    for group in seq_groups:
+        sel_sum = all_reduce_sum(sel_sum, group)
+        p_sum = all_reduce_sum(p_sum, group)
+        total_S *= torch.distributed.get_world_size(group)
+    f = (E / (top_k * total_S)) * sel_sum
+    p = p_sum / total_S
+    return (f * p).sum() / B
+
+
+def switch_balance_loss(expert_ids: torch.Tensor, probs: torch.Tensor, top_k: int) -> torch.Tensor:
+    """Switch-transformer style ``E * sum_e (fraction routed to e) * (mean router probability of e)``."""
+
+    E = probs.shape[-1]
+    flat_ids = expert_ids.reshape(-1).long()
+    f = torch.zeros(E, dtype=torch.float32, device=probs.device).index_add_(
+        0, flat_ids, torch.ones_like(flat_ids, dtype=torch.float32)) / max(flat_ids.numel(), 1)
+    p = probs.reshape(-1, E).float().mean(dim=0)
+    return E * (f * p).sum()
+
+
+class Router(nn.Module):
+    def __init__(self, hidden: int, num_experts: int, top_k: int, route_scale: float, kind: str):
+        super().__init__()
+        if top_k <= 0 or num_experts <= 0 or top_k > num_experts:
+            raise ContractError("router top_k must be positive and <= num_experts")
+        self.proj = nn.Parameter(torch.empty(num_experts, hidden, dtype=torch.float32))
+        self.num_experts, self.top_k, self.route_scale, self.kind = num_experts, top_k, float(route_scale), kind
+
+    def forward(self, x: torch.Tensor, expert_bias: torch.Tensor):
+        """x: [..., H] -> (expert_ids [...,k] int64, weights [...,k] fp32, scores [...,E] fp32)."""
+
+        logits = F.linear(x.float(), self.proj.float()) if not Fn.use_native(x) else Fn.linear(x, self.proj).float()
+        if self.kind == "softmax":
+            scores = torch.softmax(logits, dim=-1)
+        else:
+            scores = torch.sigmoid(logits)
+        _, expert_ids = torch.topk(scores + expert_bias.detach().float(), self.top_k, dim=-1)
+        top = scores.gather(-1, expert_ids)
+        if self.kind == "softmax":
+            weights = top * self.route_scale
+        else:
+            weights = top / (top.sum(dim=-1, keepdim=True) + 1e-20) * self.route_scale
+        return expert_ids, weights, scores
+
+
+class Experts(nn.Module):
+    """``E_local`` SwiGLU experts with fused gate|up storage ``[E, 2I, H]`` and down ``[E, H, I]``."""
+
+    def __init__(self, hidden: int, inter: int, num_local: int):
+        super().__init__()
+        self.hidden, self.inter, self.num_local = hidden, inter, num_local
+        self.w_gate_up = nn.Parameter(torch.empty(num_local, 2 * inter, hidden, dtype=torch.float32))
+        self.w_down = nn.Parameter(torch.empty(num_local, hidden, inter, dtype=torch.float32))
+
+    def forward(self, rows: torch.Tensor, counts: torch.Tensor) -> torch.Tensor:
+        """rows: [R, H] sorted by local expert; counts: [E_local] rows per expert (host or device ints)."""
+
+        from research_b200.ops.grouped import grouped_expert_ffn
+
+        return grouped_expert_ffn(rows, counts, self.w_gate_up, self.w_down)
+
+
+class SharedSwiGLU(nn.Module):
+    def __init__(self, hidden: int, inter: int, ex):
+        super().__init__()
+        tp = ex.tp_size
+        self.w_gate_up = nn.Parameter(torch.empty(2 * (inter // tp), hidden, dtype=torch.float32))
+        self.w_down = nn.Parameter(torch.empty(hidden, inter // tp, dtype=torch.float32))
+
+    def forward(self, x: torch.Tensor, ex) -> torch.Tensor:
+        h = Fn.swiglu(Fn.linear(x, self.w_gate_up))
+        return Fn.linear(h, self.w_down)
+
+
+class SparseMoE(nn.Module):
+    def __init__(self, spec: ModelSpec, moe: TrinityMoeSpec, ex):
+        super().__init__()
+        if moe.expert_intermediate_size is None:
+            raise ContractError("model.trinity.moe.expert_intermediate_size must be resolved before model construction")
+        self.moe = moe
+        self.hidden = spec.hidden_size
+        self.num_experts = moe.num_experts
+        ep = ex.ep_size
+        if self.num_experts % ep != 0:
+            raise ContractError(f"num_experts ({self.num_experts}) must be divisible by the expert axis size ({ep})")
+        self.num_local = self.num_experts // ep
+        self.router = Router(spec.hidden_size, moe.num_experts, moe.top_k, moe.route_scale, moe.router)
+        self.expert_bias = nn.Parameter(torch.zeros(moe.num_experts, dtype=torch.float32), requires_grad=False)
+        self.experts = Experts(spec.hidden_size, moe.expert_intermediate_size, self.num_local)
+        self.shared_experts = None
+        if moe.num_shared_experts > 0:
+            self.shared_experts = SharedSwiGLU(spec.hidden_size, moe.expert_intermediate_size * moe.num_shared_experts, ex)
+
+    def forward(self, x: torch.Tensor, ex, *, name: str, layer_index: int):
+        """x: this rank's ``[B, S_local, H]`` shard of the residual stream -> (y, aux_losses, router_stats).
+
+        Routed experts work on the local tokens (under sequence parallelism every tensor-parallel rank routes
+        its own slice); the shared expert is an ordinary tensor-parallel SwiGLU on the gathered sequence.
+        """
+
+        from research_b200.models.execution import all_reduce_sum
+        from research_b200.parallel.expert import dispatch_and_combine
+
+        B, S, H = x.shape
+        expert_ids, weights, scores = self.router(x, self.expert_bias)
+        dropped = None
+        if self.moe.capacity_factor is not None:
+            weights, dropped = apply_capacity(expert_ids, weights, self.num_experts, self.moe.capacity_factor)
+        y = dispatch_and_combine(self.experts, x.reshape(B * S, H), expert_ids.reshape(B * S, -1),
+                                 weights.reshape(B * S, -1), num_experts=self.num_experts, ex=ex).view(B, S, H)
+        if self.shared_experts is not None:
+            y = y + ex.reduce_scatter_sequence(self.shared_experts(ex.gather_sequence(x), ex))
+        stats = router_stats(name, layer_index, expert_ids, weights, self.num_experts, dropped)
+        aux = []
+        bal = self.moe.balance
+        seq_groups = [g for g in ((ex.tp_group if ex.sp else None), ex.cp_group) if g is not None]
+        if bal.name == "smebu" and bal.sequence_aux_loss_weight > 0.0:
+            aux.append(AuxLoss("moe_sequence_balance",
+                               sequence_balance_loss(expert_ids, scores, self.moe.top_k, seq_groups),
+                               float(bal.sequence_aux_loss_weight)))
+        if self.moe.aux_loss_coef > 0.0:
+            aux.append(AuxLoss("moe_load_balance", switch_balance_loss(expert_ids, scores, self.moe.top_k),
+                               float(self.moe.aux_loss_coef)))
+        return y, tuple(aux), (stats,)
+
+
+def apply_capacity(expert_ids: torch.Tensor, weights: torch.Tensor, num_experts: int, capacity_factor: float):
+    """Zero the weights of assignments beyond each expert's capacity (token order priority).
+
+    Capacity = ceil(capacity_factor * tokens * k / E).  Returns (weights, number of dropped assignments).
+    """
+
+    shape = expert_ids.shape
+    k = shape[-1]
+    flat = expert_ids.reshape(-1).long()
+    tokens = flat.numel() // k
+    capacity = int(-(-capacity_factor * tokens * k // num_experts))
+    onehot = F.one_hot(flat, num_experts)
+    position = (onehot.cumsum(dim=0) * onehot).sum(dim=-1) - 1     # rank of each assignment inside its expert
+    keep = position < capacity
+    w = weights.reshape(-1) * keep.to(weights.dtype)
+    return w.view(shape), (~keep).sum()

@@ -465,14 +465,16 @@ int launch_bwd(const CUtensorMap& x1, const CUtensorMap& x2, const CUtensorMap& 
 }  // namespace
 
 // All tensors are [B,S,H,D] views (heads D apart, dense last dim) given by base pointer + element
-// strides between tokens (`*_row`) and batches (`*_batch`).  dq/dk/dv are written (not accumulated).
+// strides between tokens (`*_row`) and batches (`*_batch`), outputs included (so dq/dk/dv may be column
+// ranges of one packed gradient buffer).  dq/dk/dv are written (not accumulated).
 // delta: [B,Hq,S] fp32 scratch that this call fills.  lo / hi: int32 [B,S] or null.
 extern "C" int b200_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
                              const void* lse, void* delta, void* dq, void* dk, void* dv, const void* lo,
                              const void* hi, int B, int S, int Hq, int Hkv, int D, long long q_row, long long q_batch,
                              long long k_row, long long k_batch, long long v_row, long long v_batch, long long o_row,
-                             long long o_batch, long long do_row, long long do_batch, float scale, int causal,
-                             int reserved, int* status, void* stream) {
+                             long long o_batch, long long do_row, long long do_batch, long long dq_row,
+                             long long dq_batch, long long dk_row, long long dk_batch, long long dv_row,
+                             long long dv_batch, float scale, int causal, int reserved, int* status, void* stream) {
   using namespace b200host;
   (void)reserved;
   if (B <= 0 || S <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv) return RC_BAD_SHAPE;
@@ -494,10 +496,9 @@ extern "C" int b200_attn_bwd(const void* q, const void* k, const void* v, const 
   if ((rc = make_map_4d(&tK, bf, k, D, Hkv, S, B, hs, k_row * 2, k_batch * 2, 64, 1, 128))) return rc;
   if ((rc = make_map_4d(&tV, bf, v, D, Hkv, S, B, hs, v_row * 2, v_batch * 2, 64, 1, 128))) return rc;
   if ((rc = make_map_4d(&tdO, bf, d_o, D, Hq, S, B, hs, do_row * 2, do_batch * 2, 64, 1, 128))) return rc;
-  // outputs are dense [B,S,H,D]
-  if ((rc = make_map_4d(&tdQ, bf, dq, D, Hq, S, B, hs, (uint64_t)Hq * D * 2, (uint64_t)S * Hq * D * 2, 64, 1, 32))) return rc;
-  if ((rc = make_map_4d(&tdK, bf, dk, D, Hkv, S, B, hs, (uint64_t)Hkv * D * 2, (uint64_t)S * Hkv * D * 2, 64, 1, 32))) return rc;
-  if ((rc = make_map_4d(&tdV, bf, dv, D, Hkv, S, B, hs, (uint64_t)Hkv * D * 2, (uint64_t)S * Hkv * D * 2, 64, 1, 32))) return rc;
+  if ((rc = make_map_4d(&tdQ, bf, dq, D, Hq, S, B, hs, dq_row * 2, dq_batch * 2, 64, 1, 32))) return rc;
+  if ((rc = make_map_4d(&tdK, bf, dk, D, Hkv, S, B, hs, dk_row * 2, dk_batch * 2, 64, 1, 32))) return rc;
+  if ((rc = make_map_4d(&tdV, bf, dv, D, Hkv, S, B, hs, dv_row * 2, dv_batch * 2, 64, 1, 32))) return rc;
   BwdParams p{B, S, Hq, Hkv, causal, scale, (const int*)lo, (const int*)hi, (const float*)lse, (const float*)delta, status};
   if (D == 128) {
     if ((rc = launch_bwd<128, false>(tQ, tdO, tK, tV, tdQ, tdQ, p, s))) return rc;

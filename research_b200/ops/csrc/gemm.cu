@@ -46,6 +46,13 @@ struct GemmParams {
   int M, N, K, batch;
   int accumulate;
   int* status;
+  // Grouped modes (both optional, device arrays):
+  //  tile_group[m_tile]: batch index of the B operand for that 128-row tile of A/C (A and C are 2-D, rows of
+  //                      each group padded to a multiple of 128); a negative entry skips the tile.
+  //  k_range[2*b], k_range[2*b+1]: the K interval [begin, end) of batch b (multiples of 64), A and B are 2-D
+  //                      and share the K axis (variable-length contraction, e.g. per-expert weight gradients).
+  const int* tile_group;
+  const int* k_range;
 };
 
 template <int BN, bool A_MN, bool B_MN, bool OUT_F32>
@@ -94,6 +101,24 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // returns false when the tile has no work (skipped group tile or empty K interval)
+  auto tile_extent = [&](int b, int m0, int& bB, int& zAC, int& kb_begin, int& kb_end) -> bool {
+    bB = b;
+    zAC = b;
+    kb_begin = 0;
+    kb_end = k_blocks;
+    if (p.tile_group) {
+      bB = p.tile_group[m0 / BM];
+      zAC = 0;
+      if (bB < 0) return false;
+    }
+    if (p.k_range) {
+      kb_begin = p.k_range[2 * b] / BK;
+      kb_end = (p.k_range[2 * b + 1] + BK - 1) / BK;
+      if (kb_end <= kb_begin) return false;
+    }
+    return true;
+  };
   auto tile_coords = [&](int t, int& b, int& m0, int& n0) {
     b = t / per_batch;
     const int r = t - b * per_batch;
@@ -114,9 +139,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t it = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-        int b, m0, n0;
+        int b, m0, n0, bB, zAC, kb0, kb1;
         tile_coords(t, b, m0, n0);
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        if (!tile_extent(b, m0, bB, zAC, kb0, kb1)) continue;
+        const int zA = p.k_range ? 0 : zAC;
+        const int zB = p.k_range ? 0 : bB;
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&empty[s], ph ^ 1, ab, ERR_WAIT_EMPTY)) { ok = false; break; }
@@ -124,16 +152,16 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint8_t* sB = sA + A_TILE_BYTES;
           mbar_expect_tx(&full[s], L::STAGE_BYTES);
           if (!A_MN) {
-            tma_load_3d(sA, &tmA, &full[s], kb * BK, m0, b);
+            tma_load_3d(sA, &tmA, &full[s], kb * BK, m0, zA);
           } else {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tma_load_3d(sA + j * 8192, &tmA, &full[s], m0 + j * 64, kb * BK, b);
+            for (int j = 0; j < BM / 64; ++j) tma_load_3d(sA + j * 8192, &tmA, &full[s], m0 + j * 64, kb * BK, zA);
           }
           if (!B_MN) {
-            tma_load_3d(sB, &tmB, &full[s], kb * BK, n0, b);
+            tma_load_3d(sB, &tmB, &full[s], kb * BK, n0, zB);
           } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_3d(sB + j * 8192, &tmB, &full[s], n0 + j * 64, kb * BK, b);
+            for (int j = 0; j < BN / 64; ++j) tma_load_3d(sB + j * 8192, &tmB, &full[s], n0 + j * 64, kb * BK, zB);
           }
         }
       }
@@ -150,13 +178,17 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t it = 0;
       uint32_t tile_iter = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_iter) {
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        int b, m0, n0, bB, zAC, kb0, kb1;
+        tile_coords(t, b, m0, n0);
+        if (!tile_extent(b, m0, bB, zAC, kb0, kb1)) continue;
         const uint32_t acc = tile_iter & 1;
         const uint32_t acc_ph = (tile_iter >> 1) & 1;
+        ++tile_iter;
         if (!mbar_wait(&tempty[acc], acc_ph ^ 1, ab, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&full[s], ph, ab, ERR_WAIT_FULL)) { ok = false; break; }
@@ -167,7 +199,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           for (int k = 0; k < BK / 16; ++k) {
             const uint64_t adesc = make_smem_desc_sw128(a_base + (A_MN ? k * 2048 : k * 32), A_MN ? 8192 : 16, 1024);
             const uint64_t bdesc = make_smem_desc_sw128(b_base + (B_MN ? k * 2048 : k * 32), B_MN ? 8192 : 16, 1024);
-            tc_mma_ss(d_tmem, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+            tc_mma_ss(d_tmem, adesc, bdesc, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
           }
           tc_commit(&empty[s]);  // stage reusable once these MMAs have read it
         }
@@ -182,11 +214,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t tile_iter = 0;
     uint32_t box_iter = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++tile_iter) {
-      int b, m0, n0;
+    for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      int b, m0, n0, bB, zAC, kb0, kb1;
       tile_coords(t, b, m0, n0);
+      if (!tile_extent(b, m0, bB, zAC, kb0, kb1)) continue;
       const uint32_t acc = tile_iter & 1;
       const uint32_t acc_ph = (tile_iter >> 1) & 1;
+      ++tile_iter;
       if (!mbar_wait_warp(&tfull[acc], acc_ph, ab, ERR_WAIT_TMEM_FULL)) { ok = false; break; }
       tc_fence_after();
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
@@ -227,9 +261,9 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         __syncwarp();
         if (lane == 0) {
           if (p.accumulate)
-            tma_reduce_add_3d(&tmC, buf, col0, row0, b);
+            tma_reduce_add_3d(&tmC, buf, col0, row0, zAC);
           else
-            tma_store_3d(&tmC, buf, col0, row0, b);
+            tma_store_3d(&tmC, buf, col0, row0, zAC);
           tma_commit_group();
         }
       }
@@ -289,10 +323,42 @@ int dispatch(bool a_mn, bool b_mn, bool out_f32, const CUtensorMap& tmA, const C
 // C[b] (+)= op(A[b]) op(B[b]) for b in [0, batch).  Leading strides (lda/ldb/ldc) and batch strides
 // are in elements.  out_f32: C is fp32 (else bf16).  accumulate: add into C with TMA reduce-add.
 // `status` is a device int the kernel sets non-zero if one of its bounded waits ran out.
+static int gemm_impl(const void* A, const void* B, void* C, int M, int N, int K, int batch, int batch_a, int batch_b,
+                     int batch_c, long long lda, long long ldb, long long ldc, long long stride_a, long long stride_b,
+                     long long stride_c, int a_mn, int b_mn, int out_f32, int accumulate, int bn_hint,
+                     const int* tile_group, const int* k_range, int* status, void* stream);
+
 extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int batch, long long lda,
                               long long ldb, long long ldc, long long stride_a, long long stride_b,
                               long long stride_c, int a_mn, int b_mn, int out_f32, int accumulate, int bn_hint,
                               int* status, void* stream) {
+  return gemm_impl(A, B, C, M, N, K, batch, batch, batch, batch, lda, ldb, ldc, stride_a, stride_b, stride_c, a_mn,
+                   b_mn, out_f32, accumulate, bn_hint, nullptr, nullptr, status, stream);
+}
+
+// Grouped forward / data-gradient product: A [M_pad, K] and C [M_pad, N] are 2-D with every group's rows
+// padded to a multiple of 128; B is [groups, ...]; tile_group[m_tile] names the group of each row tile.
+extern "C" int b200_gemm_bf16_grouped_rows(const void* A, const void* B, void* C, int M_pad, int N, int K, int groups,
+                                           long long lda, long long ldb, long long ldc, long long stride_b, int b_mn,
+                                           int out_f32, int accumulate, const int* tile_group, int* status,
+                                           void* stream) {
+  return gemm_impl(A, B, C, M_pad, N, K, 1, 1, groups, 1, lda, ldb, ldc, 0, stride_b, 0, 0, b_mn, out_f32, accumulate,
+                   0, tile_group, nullptr, status, stream);
+}
+
+// Grouped weight-gradient product: C[g] (+)= A[k0_g:k1_g, :M]^T B[k0_g:k1_g, :N]; A [K_total, M] and B [K_total, N]
+// are 2-D and share the row (contraction) axis; k_range holds (k0, k1) per group, multiples of 64.
+extern "C" int b200_gemm_bf16_grouped_k(const void* A, const void* B, void* C, int M, int N, int K_total, int groups,
+                                        long long lda, long long ldb, long long ldc, long long stride_c, int out_f32,
+                                        int accumulate, const int* k_range, int* status, void* stream) {
+  return gemm_impl(A, B, C, M, N, K_total, groups, 1, 1, groups, lda, ldb, ldc, 0, 0, stride_c, 1, 1, out_f32,
+                   accumulate, 0, nullptr, k_range, status, stream);
+}
+
+static int gemm_impl(const void* A, const void* B, void* C, int M, int N, int K, int batch, int batch_a, int batch_b,
+                     int batch_c, long long lda, long long ldb, long long ldc, long long stride_a, long long stride_b,
+                     long long stride_c, int a_mn, int b_mn, int out_f32, int accumulate, int bn_hint,
+                     const int* tile_group, const int* k_range, int* status, void* stream) {
   using namespace b200host;
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return RC_BAD_SHAPE;
   const int BN = (bn_hint == 128 || bn_hint == 256) ? bn_hint : (N > 128 ? 256 : 128);
@@ -300,22 +366,22 @@ extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, int M, int 
   int rc;
   const CUtensorMapDataType bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   if (!a_mn)
-    rc = make_map_3d(&tmA, bf, A, K, M, batch, lda * 2, stride_a * 2, BK, BM);
+    rc = make_map_3d(&tmA, bf, A, K, M, batch_a, lda * 2, stride_a * 2, BK, BM);
   else
-    rc = make_map_3d(&tmA, bf, A, M, K, batch, lda * 2, stride_a * 2, 64, BK);
+    rc = make_map_3d(&tmA, bf, A, M, K, batch_a, lda * 2, stride_a * 2, 64, BK);
   if (rc) return rc;
   if (!b_mn)
-    rc = make_map_3d(&tmB, bf, B, K, N, batch, ldb * 2, stride_b * 2, BK, BN);
+    rc = make_map_3d(&tmB, bf, B, K, N, batch_b, ldb * 2, stride_b * 2, BK, BN);
   else
-    rc = make_map_3d(&tmB, bf, B, N, K, batch, ldb * 2, stride_b * 2, 64, BK);
+    rc = make_map_3d(&tmB, bf, B, N, K, batch_b, ldb * 2, stride_b * 2, 64, BK);
   if (rc) return rc;
   if (out_f32)
-    rc = make_map_3d(&tmC, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, C, N, M, batch, ldc * 4, stride_c * 4, 32, 32);
+    rc = make_map_3d(&tmC, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, C, N, M, batch_c, ldc * 4, stride_c * 4, 32, 32);
   else
-    rc = make_map_3d(&tmC, bf, C, N, M, batch, ldc * 2, stride_c * 2, 64, 32);
+    rc = make_map_3d(&tmC, bf, C, N, M, batch_c, ldc * 2, stride_c * 2, 64, 32);
   if (rc) return rc;
 
-  GemmParams p{M, N, K, batch, accumulate, status};
+  GemmParams p{M, N, K, batch, accumulate, status, tile_group, k_range};
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * batch;
   const int grid = tiles < sm_count() ? tiles : sm_count();
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);

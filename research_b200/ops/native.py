@@ -85,11 +85,15 @@ def _declare(lib: ctypes.CDLL) -> None:
         c_float, c_float, c_float, c_float, c_void_p)
     sig("b200_sumsq", c_void_p, c_int, c_ll, c_void_p, c_void_p, c_int, c_void_p)
     sig("b200_cast_f32_bf16", c_void_p, c_void_p, c_ll, c_float, c_void_p)
+    sig("b200_gemm_bf16_grouped_rows", c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_ll,
+        c_int, c_int, c_int, c_void_p, c_void_p, c_void_p)
+    sig("b200_gemm_bf16_grouped_k", c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_ll,
+        c_int, c_int, c_void_p, c_void_p, c_void_p)
     sig("b200_attn_fwd", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
         c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_float, c_int, c_int, c_void_p, c_void_p)
     sig("b200_attn_bwd", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
         c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll,
-        c_ll, c_ll, c_ll, c_float, c_int, c_int, c_void_p, c_void_p)
+        c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_float, c_int, c_int, c_void_p, c_void_p)
 
 
 def _stream() -> int:
@@ -375,8 +379,13 @@ def kv_visibility_upper_bound(lo: torch.Tensor) -> torch.Tensor:
 
 def attn_bwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor, d_o: torch.Tensor,
              lse: torch.Tensor, *, causal: bool = True, lo: torch.Tensor | None = None,
-             hi: torch.Tensor | None = None, scale: float | None = None):
-    """Flash attention backward; returns dense ``(dq, dk, dv)`` shaped like q, k, v."""
+             hi: torch.Tensor | None = None, scale: float | None = None,
+             out: tuple[torch.Tensor, torch.Tensor, torch.Tensor] | None = None):
+    """Flash attention backward; returns ``(dq, dk, dv)`` shaped like q, k, v.
+
+    ``out`` may give three ``[B,S,H,D]`` views to write into (for example column ranges of one packed
+    gradient buffer); otherwise dense tensors are allocated.
+    """
 
     global LAUNCHES
     lib = load()
@@ -388,14 +397,20 @@ def attn_bwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor,
         scale = D ** -0.5
     if lo is not None and hi is None:
         hi = kv_visibility_upper_bound(lo)
-    dq = torch.empty((B, S, Hq, D), dtype=q.dtype, device=q.device)
-    dk = torch.empty((B, S, Hkv, D), dtype=q.dtype, device=q.device)
-    dv = torch.empty((B, S, Hkv, D), dtype=q.dtype, device=q.device)
+    if out is None:
+        dq = torch.empty((B, S, Hq, D), dtype=q.dtype, device=q.device)
+        dk = torch.empty((B, S, Hkv, D), dtype=q.dtype, device=q.device)
+        dv = torch.empty((B, S, Hkv, D), dtype=q.dtype, device=q.device)
+    else:
+        dq, dk, dv = out
+        for t, n in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
+            _check_bshd(t, n)
     delta = torch.empty((B, Hq, S), dtype=torch.float32, device=q.device)
     rc = lib.b200_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(), lse.data_ptr(),
                            delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _ptr(lo), _ptr(hi), B, S, Hq,
                            Hkv, D, q.stride(1), q.stride(0), k.stride(1), k.stride(0), v.stride(1), v.stride(0),
-                           o.stride(1), o.stride(0), d_o.stride(1), d_o.stride(0), scale, int(causal), 0,
+                           o.stride(1), o.stride(0), d_o.stride(1), d_o.stride(0), dq.stride(1), dq.stride(0),
+                           dk.stride(1), dk.stride(0), dv.stride(1), dv.stride(0), scale, int(causal), 0,
                            status_word(q.device).data_ptr(), _stream())
     _check(rc, "b200_attn_bwd")
     LAUNCHES += 2

@@ -1,0 +1,279 @@
+"""The optimizer step over a :class:`ParamStore`: global-norm clip, AdamW, Muon, distributed Muon, Dion2.
+
+Update rules restate the reference transforms: AdamW with decoupled decay ``-lr * wd * p`` and bias correction
+(optax semantics, src/jaxtitan/optim/build.py:29-31); Muon ``m <- 0.95 m + 0.05 g``, Nesterov input
+``0.05 g + 0.95 m``, five Newton-Schulz steps in bf16, step ``-lr * 0.2 sqrt(max(rows, cols)) * O - lr * wd * p``
+(optim/muon.py:65-167, 482-526); Dion2 ``m <- m + g``, top quarter of rows/columns by L1 norm, Polar Express,
+scatter with ``sqrt(rows/cols)``, selected momentum scaled by 0.95 (optim/dion2.py:34-125).  The learning rate
+is the schedule at the *old* count (steps/train.py:227).
+
+Where the work happens: AdamW is one flat-arena kernel launch per section (fp32 master, moments and the compute
+copy updated in one pass); matrix optimizers run per logical matrix on the rank that owns it, with every
+product on the tcgen05 GEMM.  Tensor-parallel shards either gather the logical matrix (``duplicated``) or
+all-reduce the Gram matrices of their shards (``distributed``; optim/muon.py:354-463).
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+from research_b200.errors import ContractError
+from research_b200.models.build import ROUTED_EXPERT_TAGS
+from research_b200.ops import native
+from research_b200.optim import orthogonalize as orth
+from research_b200.optim.build import ADAMW_B1, ADAMW_B2, ADAMW_EPS, OptimizerBuildResult
+from research_b200.parallel.sharding import ParamStore, Section, StorageEntry
+
+
+def _sumsq(x: torch.Tensor, out: torch.Tensor, index: int) -> None:
+    if x.numel() == 0:
+        return
+    if x.is_cuda and x.dtype in (torch.float32, torch.bfloat16) and x.is_contiguous():
+        native.sumsq(x.reshape(-1), out[index:index + 1], accumulate=True)
+    else:
+        out[index] += x.float().pow(2).sum()
+
+
+class Optimizer:
+    def __init__(self, build: OptimizerBuildResult, store: ParamStore):
+        self.build = build
+        self.store = store
+        self.spec = build.spec
+        self.count = 0
+        self.mesh = store.mesh
+        self.routes = {a.name: a for a in build.route_assignments}
+        dev = store.device
+        self.state: dict[int, dict[str, torch.Tensor]] = {}
+        for i, sec in enumerate(store.sections):
+            lo, hi = store.local_master_range(sec)
+            n = hi - lo
+            if sec.backend == "adamw":
+                self.state[i] = {"mu": torch.zeros(n, dtype=torch.float32, device=dev),
+                                 "nu": torch.zeros(n, dtype=torch.float32, device=dev)}
+            elif sec.backend in ("muon", "dion2"):
+                self.state[i] = {"momentum": torch.zeros(n, dtype=torch.float32, device=dev)}
+            else:
+                self.state[i] = {}
+        self._norm_buf = torch.zeros(len(store.sections), dtype=torch.float32, device=dev)
+        self._clip = torch.ones(1, dtype=torch.float32, device=dev)
+        self.tp_group = store.result.execution.tp_group
+        self.tp_size = store.result.execution.tp_size
+
+    # ---- norms -----------------------------------------------------------------------------------
+    def _sum_axes(self, sec: Section) -> list[str]:
+        axes = []
+        if sec.shard_axis is not None and self.mesh.size(sec.shard_axis) > 1:
+            axes.append(sec.shard_axis)
+        if self.tp_size > 1 and "tp" not in sec.reduce_axes:
+            axes.append("tp")
+        ep_axis = self.store.ep_axis
+        if ep_axis and self.mesh.size(ep_axis) > 1 and any(e.is_expert for e in sec.entries) and ep_axis not in axes:
+            axes.append(ep_axis)
+        return axes
+
+    def _global_sumsq(self, arena: torch.Tensor | None, use_master: bool = False) -> torch.Tensor:
+        """Sum of squares over all distinct parameters' values in ``arena`` (or the fp32 masters)."""
+
+        buf = self._norm_buf
+        buf.zero_()
+        for i, sec in enumerate(self.store.sections):
+            if sec.backend == "frozen" or sec.length == 0:
+                continue
+            lo, hi = self.store.local_master_range(sec)
+            src = sec.master if use_master else arena[lo:hi]
+            _sumsq(src, buf, i)
+        axes_needed: dict[str, list[int]] = {}
+        for i, sec in enumerate(self.store.sections):
+            for axis in self._sum_axes(sec):
+                axes_needed.setdefault(axis, []).append(i)
+        for axis, idx in axes_needed.items():
+            group = self.mesh.group(axis)
+            if group is None:
+                continue
+            part = buf[idx].clone()
+            dist.all_reduce(part, group=group)
+            buf[idx] = part
+        return buf.sum()
+
+    # ---- the step ----------------------------------------------------------------------------------
+    @torch.no_grad()
+    def step(self, *, diagnostics: bool = False) -> dict[str, Any]:
+        store, spec = self.store, self.spec
+        lr = float(self.build.schedule(self.count))
+        fb = self.build.adamw_fallback_schedule
+        adamw_lr = lr if (fb is None or spec.name == "adamw") else float(fb(self.count))
+        grad_sq = self._global_sumsq(store.grad_arena)
+        grad_norm = grad_sq.sqrt()
+        if spec.grad_clip_norm is not None:
+            clip = float(spec.grad_clip_norm)
+            self._clip.copy_((clip / torch.clamp(grad_norm, min=clip)).reshape(1))
+        else:
+            self._clip.fill_(1.0)
+        before = None
+        if diagnostics:
+            before = [sec.master.clone() if sec.backend != "frozen" else None for sec in store.sections]
+        for i, sec in enumerate(store.sections):
+            if sec.backend == "adamw":
+                self._adamw(i, sec, adamw_lr)
+            elif sec.backend in ("muon", "dion2"):
+                for e in sec.entries:
+                    if store.owns(sec, e):
+                        self._matrix_entry(i, sec, e, lr)
+        store.gather_compute_weights()
+        self.count += 1
+        out: dict[str, Any] = {"lr": lr, "adamw_lr": adamw_lr, "grad_norm": grad_norm, "clip_scale": self._clip[0]}
+        if diagnostics:
+            out["param_norm"] = self._global_sumsq(None, use_master=True).sqrt().clone()
+            upd = torch.zeros(1, dtype=torch.float32, device=store.device)
+            buf = self._norm_buf
+            buf.zero_()
+            for i, sec in enumerate(store.sections):
+                if before[i] is not None:
+                    _sumsq((sec.master - before[i]).contiguous(), buf, i)
+            for axis in {a for sec in store.sections for a in self._sum_axes(sec)}:
+                group = self.mesh.group(axis)
+                idx = [i for i, sec in enumerate(store.sections) if axis in self._sum_axes(sec)]
+                if group is not None and idx:
+                    part = buf[idx].clone()
+                    dist.all_reduce(part, group=group)
+                    buf[idx] = part
+            out["update_norm"] = buf.sum().sqrt().clone()
+            del upd
+        return out
+
+    # ---- AdamW -------------------------------------------------------------------------------------
+    def _adamw(self, i: int, sec: Section, lr: float) -> None:
+        store = self.store
+        lo, hi = store.local_master_range(sec)
+        if hi <= lo:
+            return
+        st = self.state[i]
+        g = store.grad_arena[lo:hi]
+        p = sec.master
+        wd = float(self.spec.weight_decay)
+        step = self.count + 1
+        separate = store.compute_dtype != torch.float32
+        if p.is_cuda:
+            shadow = store.compute_arena[lo:hi] if separate else None
+            native.adamw(p, st["mu"], st["nu"], g, shadow, self._clip, lr, ADAMW_B1, ADAMW_B2, ADAMW_EPS, wd, step)
+            return
+        gs = g * self._clip
+        st["mu"].mul_(ADAMW_B1).add_(gs, alpha=1 - ADAMW_B1)
+        st["nu"].mul_(ADAMW_B2).addcmul_(gs, gs, value=1 - ADAMW_B2)
+        mhat = st["mu"] / (1 - ADAMW_B1 ** step)
+        vhat = st["nu"] / (1 - ADAMW_B2 ** step)
+        p.sub_(lr * (mhat / (vhat.sqrt() + ADAMW_EPS) + wd * p))
+        if separate:
+            store.compute_arena[lo:hi].copy_(p)
+
+    # ---- matrix optimizers -------------------------------------------------------------------------
+    def _matrix_entry(self, i: int, sec: Section, e: StorageEntry, lr: float) -> None:
+        store = self.store
+        master = store.master_view(sec, e)
+        if master is None:
+            raise ContractError(f"matrix parameter {e.name} is not fully resident on its owner")
+        lo, _ = store.local_master_range(sec)
+        mom = self.state[i]["momentum"][e.offset - lo:e.offset - lo + e.numel].view(e.param.shape)
+        grad = e.param.main_grad
+        wd = float(self.spec.weight_decay)
+        clip = self._clip
+        for meta in e.metas:
+            route = self.routes[meta.name]
+            sl = (slice(None),) if meta.rows is None else (
+                (slice(None), slice(*meta.rows)) if master.dim() == 3 else (slice(*meta.rows),))
+            g = grad[sl] * clip
+            m = mom[sl]
+            w = master[sl]
+            decay = wd if route.weight_decay else 0.0
+            if sec.backend == "dion2":
+                self._dion2_update(meta, route, g, m, w, lr, decay)
+            else:
+                self._muon_update(meta, route, g, m, w, lr, decay)
+        if store.compute_dtype != torch.float32:
+            e.param.data.copy_(master)
+
+    def _muon_update(self, meta, route, g, m, w, lr: float, wd: float) -> None:
+        m.mul_(orth.MUON_MOMENTUM).add_(g, alpha=1.0 - orth.MUON_MOMENTUM)
+        u = (1.0 - orth.MUON_MOMENTUM) * g + orth.MUON_MOMENTUM * m if orth.MUON_NESTEROV else m
+        # storage is [out, in] = transpose of the logical [in, out]; orthogonalisation commutes with transposition
+        logical_shape = meta.shape
+        if route.backend == "dist_muon" and self.tp_size > 1:
+            storage_axis = (len(meta.shape) - 1 - route.matrix_axis) if meta.transposed else route.matrix_axis
+            if self.spec.muon_tp_mode == "distributed":
+                o = _sharded_newton_schulz(u.to(torch.bfloat16), storage_axis, self.tp_group)
+            else:
+                full = _all_gather_axis(u.to(torch.bfloat16).contiguous(), storage_axis, self.tp_group)
+                o_full = orth.zeropower_via_newton_schulz(full)
+                o = o_full.chunk(self.tp_size, dim=storage_axis)[dist.get_rank(self.tp_group)]
+        else:
+            o = orth.zeropower_via_newton_schulz(u.to(torch.bfloat16))
+        scale = lr * orth.rms_match_scale(logical_shape)
+        if wd != 0.0:
+            w.mul_(1.0 - lr * wd)
+        w.add_(o.to(w.dtype), alpha=-scale)
+
+    def _dion2_update(self, meta, route, g, m, w, lr: float, wd: float) -> None:
+        m.add_(g)
+        if m.dim() == 3:
+            for e in range(m.shape[0]):
+                self._dion2_matrix(meta, route, m[e], w[e], lr, wd)
+        else:
+            self._dion2_matrix(meta, route, m, w, lr, wd)
+
+    def _dion2_matrix(self, meta, route, m, w, lr: float, wd: float) -> None:
+        logical_axis = route.matrix_axis if route.matrix_axis is not None else 0
+        if len(meta.shape) == 3:
+            logical_axis -= 1
+        storage_axis = (1 - logical_axis) if meta.transposed else logical_axis
+        selected, idx = orth.select_dion2_slices(m, select_axis=storage_axis)
+        o = orth.polar_express(selected).to(w.dtype)
+        rows, cols = meta.shape[-2], meta.shape[-1]
+        if wd != 0.0:
+            w.mul_(1.0 - lr * wd)
+        w.index_add_(storage_axis, idx, o, alpha=-lr * math.sqrt(rows / cols))
+        m.index_copy_(storage_axis, idx, selected * orth.DION2_EF_DECAY)
+
+    # ---- checkpoint state ---------------------------------------------------------------------------
+    def state_dict(self) -> dict[str, Any]:
+        return {"count": self.count,
+                "sections": {str(i): {k: v for k, v in st.items()} for i, st in self.state.items()}}
+
+    def load_state_dict(self, raw: dict[str, Any]) -> None:
+        self.count = int(raw["count"])
+        for i, st in raw["sections"].items():
+            for k, v in st.items():
+                self.state[int(i)][k].copy_(v)
+
+
+def _all_gather_axis(x: torch.Tensor, axis: int, group) -> torch.Tensor:
+    n = dist.get_world_size(group)
+    xt = x.movedim(axis, 0).contiguous()
+    out = torch.empty((n * xt.shape[0],) + tuple(xt.shape[1:]), dtype=x.dtype, device=x.device)
+    dist.all_gather_into_tensor(out, xt, group=group)
+    return out.movedim(0, axis).contiguous()
+
+
+def _sharded_newton_schulz(x: torch.Tensor, shard_axis: int, group) -> torch.Tensor:
+    """Newton-Schulz on a matrix split along ``shard_axis`` over ``group``: the Gram matrix contracts over the
+    split axis, so it is the sum of the shards' Grams (one all-reduce per step); the norm is global."""
+
+    sq = x.float().pow(2).sum().reshape(1)
+    dist.all_reduce(sq, group=group)
+    x = x / torch.clamp(sq.sqrt(), min=orth.MUON_NS_EPS).to(x.dtype)
+    a, b, c = orth.MUON_NS_COEFFICIENTS
+    for _ in range(orth.MUON_NS_STEPS):
+        if shard_axis == x.dim() - 1:      # columns split: left Gram X X^T
+            gram = (x @ x.transpose(-1, -2)).float()
+            dist.all_reduce(gram, group=group)
+            gram = gram.to(x.dtype)
+            x = a * x + (b * gram + c * (gram @ gram)) @ x
+        else:                              # rows split: right Gram X^T X
+            gram = (x.transpose(-1, -2) @ x).float()
+            dist.all_reduce(gram, group=group)
+            gram = gram.to(x.dtype)
+            x = a * x + x @ (b * gram + c * (gram @ gram))
+    return x

@@ -1,0 +1,169 @@
+"""``Trainer``: everything one rank needs to train from a :class:`RunSpec` - mesh, model, parameter store,
+optimizer, data pipelines, train / eval steps - behind the small API the host loop, preflight, the benchmark
+and the tests all use.
+
+Build order mirrors the reference's ``_run_training_initialized`` (src/jaxtitan/runtime/training.py:271-346):
+schedule steps resolved from ``target_tokens``, data pipeline, mesh, model (seeded), sharding plan, optimizer,
+train state, step functions.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import replace
+from typing import Any
+
+import torch
+
+from research_b200.config.specs import RunSpec
+from research_b200.contracts import Batch, RngState, StepMetrics
+from research_b200.data.pipeline import DataPipelineState, PipelineBatch, build_prepared_token_pipeline
+from research_b200.errors import ContractError
+from research_b200.models.build import ModelBuildResult, build_model
+from research_b200.optim.build import OptimizerBuildResult, build_optimizer
+from research_b200.optim.optimizer import Optimizer
+from research_b200.parallel.mesh import MeshContext, build_mesh_context, execution_context_for
+from research_b200.config.specs import resolve_expert_parallel_axis
+from research_b200.parallel.sharding import ParamStore
+from research_b200.steps.eval import EvalStep
+from research_b200.steps.moe_balance import init_moe_balance
+from research_b200.steps.train import TrainStep
+
+
+def with_runtime_schedule_steps(spec: RunSpec) -> RunSpec:
+    """cosine / wsd schedules without ``total_steps`` get ``ceil(target_tokens / tokens_per_step)``
+    (reference: runtime/training.py:653-665)."""
+
+    tokens_per_step = (spec.training.global_batch_size * spec.training.seq_len *
+                       spec.training.gradient_accumulation_steps)
+    total = math.ceil(spec.training.target_tokens / tokens_per_step)
+
+    def fix(schedule):
+        if schedule is None or schedule.name == "constant" or schedule.total_steps is not None:
+            return schedule
+        return replace(schedule, total_steps=total)
+
+    optimizer = replace(spec.optimizer, schedule=fix(spec.optimizer.schedule),
+                        adamw_fallback_schedule=fix(spec.optimizer.adamw_fallback_schedule))
+    return replace(spec, optimizer=optimizer)
+
+
+def compute_dtype_for(spec: RunSpec, device: torch.device) -> torch.dtype:
+    """``training.precision`` decides the compute dtype: ``fp32`` -> float32; ``bf16`` / ``mixed_bf16`` ->
+    the model's ``compute_dtype`` (bfloat16 by default) with fp32 master weights."""
+
+    if spec.training.precision == "fp32" or spec.model.compute_dtype == "float32":
+        return torch.float32
+    return torch.bfloat16
+
+
+class Trainer:
+    def __init__(self, spec: RunSpec, *, mesh: MeshContext | None = None, device: torch.device | str | None = None,
+                 build_data: bool = True):
+        self.spec = spec = with_runtime_schedule_steps(spec)
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+        self.device = torch.device(device)
+        self.mesh = mesh or build_mesh_context(spec.mesh, device=self.device)
+        self.execution = execution_context_for(self.mesh, spec.parallelism)
+        self.compute_dtype = compute_dtype_for(spec, self.device)
+        self.result: ModelBuildResult = build_model(spec.model, seed=spec.seed, execution=self.execution,
+                                                    device=self.device)
+        self.optimizer_build: OptimizerBuildResult = build_optimizer(spec.optimizer, self.result.metadata,
+                                                                     tp_size=self.execution.tp_size)
+        ep = resolve_expert_parallel_axis(spec.parallelism, self.mesh.sizes)
+        self.store = ParamStore(self.result, self.mesh, mode=spec.parallelism.mode, compute_dtype=self.compute_dtype,
+                                backend_of=self.optimizer_build.backend_by_name(), ep_axis=ep.axis)
+        self.optimizer = Optimizer(self.optimizer_build, self.store)
+        moe = spec.model.trinity.moe if spec.model.trinity is not None else None
+        self.moe_balance = init_moe_balance(self.result.model, None if moe is None else moe.balance)
+        self.train_step_fn = TrainStep(spec, self.result, self.store, self.optimizer, self.mesh, self.moe_balance)
+        self.eval_step_fn = EvalStep(self.result, self.store, self.mesh)
+        self.rng = RngState.from_seed(spec.seed)
+        self.step = 0
+        self.tokens_seen = 0
+        self.data = None
+        self.data_state: DataPipelineState | None = None
+        self.last_provenance: list[Any] = []
+        if build_data:
+            self.data = self.build_pipeline("train")
+            self.data_state = self.data.initial_state()
+
+    # ---- data --------------------------------------------------------------------------------------
+    def build_pipeline(self, split: str):
+        d, t = self.spec.data, self.spec.training
+        if d.mode != "prepared":
+            from research_b200.data.streaming import build_hf_streaming_pipeline
+
+            if split == "train":
+                return build_hf_streaming_pipeline(d, seq_len=t.seq_len, batch_size=t.global_batch_size)
+        manifest = d.train_manifest if (split == "train" or d.validation_manifest is None) else d.validation_manifest
+        if manifest is None:
+            raise ContractError("a prepared manifest is required for this split")
+        order = d.order if split == "train" else "sequential"
+        return build_prepared_token_pipeline(
+            manifest, tokenizer_id=d.tokenizer_id, split=split, seq_len=t.seq_len, batch_size=t.global_batch_size,
+            order=order, shuffle_seed=d.shuffle_seed if split == "train" else None,
+            document_buffer_size=d.document_buffer_size if split == "train" else None,
+            document_refill_size=d.document_refill_size if split == "train" else None)
+
+    def next_accumulated_batch(self) -> list[Batch]:
+        """The microbatches of one optimizer step (reference: runtime/training.py:744-757)."""
+
+        if self.data is None or self.data_state is None:
+            raise ContractError("this trainer was built without a data pipeline")
+        batches, prov = [], []
+        for _ in range(self.spec.training.gradient_accumulation_steps):
+            try:
+                pb: PipelineBatch = self.data.next_batch(self.data_state)
+            except StopIteration as exc:
+                raise ContractError(f"training data exhausted before target_tokens was reached: {exc}") from exc
+            self.data_state = pb.state
+            batches.append(pb.batch)
+            prov.append(pb.provenance)
+        self.last_provenance = prov
+        return batches
+
+    # ---- steps -------------------------------------------------------------------------------------
+    def train_on(self, batches: list[Batch], *, diagnostics: bool = False) -> StepMetrics:
+        metrics = self.train_step_fn.run(batches, diagnostics=diagnostics)
+        self.step += 1
+        self.tokens_seen += sum(int(b.input_ids.shape[0] * b.input_ids.shape[1]) for b in batches)
+        return metrics
+
+    def train_step(self, *, diagnostics: bool = False) -> StepMetrics:
+        """Public one-call step: pull the next microbatches from the data pipeline and train on them."""
+
+        return self.train_on(self.next_accumulated_batch(), diagnostics=diagnostics)
+
+    def evaluate(self, num_batches: int) -> dict[str, float]:
+        pipeline = self.build_pipeline("val")
+        state = pipeline.initial_state()
+        loss_sum = token_count = 0.0
+        done = 0
+        self.result.model.eval()
+        try:
+            for _ in range(num_batches):
+                try:
+                    pb = pipeline.next_batch(state)
+                except StopIteration:
+                    break
+                state = pb.state
+                m = self.eval_step_fn.run(pb.batch)
+                loss_sum += m.loss_sum
+                token_count += m.token_count
+                done += 1
+        finally:
+            self.result.model.train()
+            pipeline.close()
+        if done == 0:
+            raise ContractError("validation split has no full batch")
+        return {"loss_sum": loss_sum, "token_count": token_count, "loss": loss_sum / max(token_count, 1.0),
+                "num_batches": done}
+
+    @property
+    def is_writer(self) -> bool:
+        return self.mesh.rank == 0
+
+    def parameter_count(self) -> int:
+        return self.result.parameter_count()

@@ -1,0 +1,256 @@
+"""One optimizer step: gradient accumulation over microbatches, token-sum loss, z-loss, aux losses,
+data-parallel gradient reduction, optimizer update, SMEBU bias update, metrics.
+
+Loss semantics follow the reference step (src/jaxtitan/steps/train.py:98-283): the objective of a microbatch is
+``ce_sum + z_weight * z_sum + aux * token_count`` and the accumulated gradient is divided by the **global**
+masked-token count of the whole optimizer step (train.py:120, 204-205).  Here the division is folded into the
+backward pass (``grad_scale = 1 / global_count``), which is known up front because every rank derives the
+global batch from the same deterministic data pipeline.
+
+Each microbatch's tokens are copied from pinned host memory on a side stream while the previous microbatch
+computes; loss scalars stay on the device until the step's single device-to-host read.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from research_b200.config.specs import RunSpec
+from research_b200.contracts import Batch, StepMetrics
+from research_b200.models.build import ModelBuildResult
+from research_b200.ops import functional as Fn
+from research_b200.optim.optimizer import Optimizer
+from research_b200.parallel.mesh import MeshContext
+from research_b200.parallel.sharding import ParamStore
+from research_b200.steps.moe_balance import MoeBalanceState, apply_moe_balance_update, router_diagnostics
+
+
+@dataclass
+class DeviceBatch:
+    input_ids: torch.Tensor
+    target_ids: torch.Tensor
+    loss_mask: torch.Tensor
+    token_doc_ids: torch.Tensor | None
+    local_token_count: float
+
+
+def local_batch_slices(mesh: MeshContext, batch_rows: int, seq_len: int) -> tuple[slice, slice]:
+    """Rows of the global microbatch and the sequence range this rank works on.
+
+    The batch is split over the ``data`` and ``fsdp`` axes (``data`` major), the sequence over ``cp``.
+    """
+
+    dp = mesh.size("data") * mesh.size("fsdp")
+    dp_rank = mesh.coord("data") * mesh.size("fsdp") + mesh.coord("fsdp")
+    rows = batch_rows // dp
+    cp, cp_rank = mesh.size("cp"), mesh.coord("cp")
+    seq = seq_len // cp
+    return slice(dp_rank * rows, (dp_rank + 1) * rows), slice(cp_rank * seq, (cp_rank + 1) * seq)
+
+
+class BatchStager:
+    """Pinned host buffers + a copy stream: host->device copies of microbatch k+1 overlap compute of k."""
+
+    def __init__(self, device: torch.device, bytes_counter: list[int]):
+        self.device = device
+        self.cuda = device.type == "cuda"
+        self.stream = torch.cuda.Stream(device) if self.cuda else None
+        self.pinned: dict[tuple, torch.Tensor] = {}
+        self.bytes_counter = bytes_counter
+
+    def _to_device(self, key: str, array: np.ndarray, dtype: torch.dtype) -> torch.Tensor:
+        host = torch.from_numpy(np.ascontiguousarray(array)).to(dtype)
+        if not self.cuda:
+            return host
+        k = (key, tuple(host.shape), dtype)
+        buf = self.pinned.get(k)
+        if buf is None:
+            buf = torch.empty(host.shape, dtype=dtype, pin_memory=True)
+            self.pinned[k] = buf
+        buf.copy_(host)
+        self.bytes_counter[0] += buf.numel() * buf.element_size()
+        return buf.to(self.device, non_blocking=True)
+
+    def stage(self, batch: Batch, rows: slice, cols: slice, slot: int) -> DeviceBatch:
+        ids = np.asarray(batch.input_ids)[rows, cols]
+        tgt = np.asarray(batch.target_ids)[rows, cols]
+        msk = np.asarray(batch.loss_mask)[rows, cols]
+        docs = None if batch.token_doc_ids is None else np.asarray(batch.token_doc_ids)[rows]
+        ctx = torch.cuda.stream(self.stream) if self.cuda else _NullCtx()
+        with ctx:
+            out = DeviceBatch(
+                input_ids=self._to_device(f"ids{slot}", ids, torch.int32),
+                target_ids=self._to_device(f"tgt{slot}", tgt, torch.int32),
+                loss_mask=self._to_device(f"msk{slot}", msk, torch.uint8),
+                token_doc_ids=None if docs is None else self._to_device(f"doc{slot}", docs, torch.int32),
+                local_token_count=float(msk.sum()),
+            )
+        return out
+
+    def wait(self) -> None:
+        if self.cuda:
+            torch.cuda.current_stream(self.device).wait_stream(self.stream)
+
+
+class _NullCtx:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+class TrainStep:
+    def __init__(self, spec: RunSpec, result: ModelBuildResult, store: ParamStore, optimizer: Optimizer,
+                 mesh: MeshContext, moe_balance: MoeBalanceState | None = None):
+        self.spec = spec
+        self.result = result
+        self.model = result.model
+        self.store = store
+        self.optimizer = optimizer
+        self.mesh = mesh
+        self.moe_balance = moe_balance
+        self.device = store.device
+        self.h2d_bytes = [0]
+        self.d2h_bytes = [0]
+        self.stager = BatchStager(self.device, self.h2d_bytes)
+        self.z_weight = float(spec.training.loss.z_loss_weight)
+        self.native = self.device.type == "cuda" and store.compute_dtype == torch.bfloat16
+        self.loss_axes = [a for a in ("data", "fsdp", "cp") if mesh.size(a) > 1]
+        if result.execution.sp:
+            self.loss_axes.append("tp")
+
+    # ------------------------------------------------------------------------------------------------
+    def _microbatch(self, db: DeviceBatch, grad_scale: float, global_mb_tokens: float, dp_world: int):
+        model, ex = self.model, self.result.execution
+        h, aux_losses, stats = model.hidden_states(db.input_ids, db.token_doc_ids)
+        targets, mask = db.target_ids, db.loss_mask
+        if ex.sp:  # the final hidden states are sequence-sharded over tp: shard targets the same way
+            n, r = ex.tp_size, ex.tp_rank
+            targets = targets.chunk(n, dim=1)[r].contiguous()
+            mask = mask.chunk(n, dim=1)[r].contiguous()
+        head = self._head_weight()
+        ce_sum, z_sum = Fn.lm_head_cross_entropy(h, head, targets, mask, grad_scale=grad_scale,
+                                                 z_weight=self.z_weight)
+        native_path = Fn.use_native(h)
+        objective = Fn.objective_from_sums(ce_sum, z_sum, grad_scale=grad_scale, z_weight=self.z_weight,
+                                           native_path=native_path)
+        aux_total = None
+        for aux in aux_losses:
+            term = aux.value.float() * aux.weight
+            aux_total = term if aux_total is None else aux_total + term
+        if aux_total is not None:
+            objective = objective + aux_total * (global_mb_tokens / dp_world) * grad_scale
+        objective.backward()
+        return ce_sum.detach(), z_sum.detach(), (None if aux_total is None else aux_total.detach()), stats
+
+    def _head_weight(self):
+        return self.model.head_weight()
+
+    def run(self, batches: list[Batch], *, diagnostics: bool = False) -> StepMetrics:
+        """``batches``: the step's microbatches as **global** host batches (every rank passes the same ones)."""
+
+        mesh = self.mesh
+        B, S = batches[0].input_ids.shape
+        rows, cols = local_batch_slices(mesh, B, S)
+        global_counts = [float(np.asarray(b.loss_mask).sum()) for b in batches]
+        global_count = max(sum(global_counts), 1.0)
+        grad_scale = 1.0 / global_count
+        dp_world = mesh.size("data") * mesh.size("fsdp") * mesh.size("cp")
+        self.store.zero_grads()
+        staged = self.stager.stage(batches[0], rows, cols, 0)
+        ce_sums, z_sums, aux_vals = [], [], []
+        all_stats = []
+        for k in range(len(batches)):
+            self.stager.wait()
+            current = staged
+            if k + 1 < len(batches):
+                staged = self.stager.stage(batches[k + 1], rows, cols, (k + 1) % 2)
+            ce, z, aux, stats = self._microbatch(current, grad_scale, global_counts[k], dp_world)
+            ce_sums.append(ce)
+            z_sums.append(z)
+            aux_vals.append(aux)
+            all_stats.append(stats)
+        if not self.native:
+            self.store.collect_autograd_grads()
+        self.store.reduce_gradients()
+        opt = self.optimizer.step(diagnostics=diagnostics)
+        # ---- metrics: one small device vector, one reduction, one device-to-host read ------------
+        mb = len(batches)
+        vec = [torch.stack(ce_sums).float(), torch.stack(z_sums).float()]
+        has_aux = aux_vals[0] is not None
+        if has_aux:
+            vec.append(torch.stack(aux_vals).float())
+        packed = torch.cat(vec)
+        for axis in self.loss_axes:
+            group = mesh.group(axis)
+            if group is not None:
+                dist.all_reduce(packed, group=group)
+        extras = [opt["grad_norm"].reshape(1).float(), opt["clip_scale"].reshape(1).float()]
+        if diagnostics:
+            extras += [opt["param_norm"].reshape(1).float(), opt["update_norm"].reshape(1).float()]
+        router_payload = self._router_metrics(all_stats) if all_stats and all_stats[0] else {}
+        router_keys = sorted(k for k, v in router_payload.items() if torch.is_tensor(v) and v.dim() == 0)
+        extras += [router_payload[k].reshape(1).float() for k in router_keys]
+        flat = torch.cat([packed] + extras)
+        host = flat.detach().cpu().tolist()
+        self.d2h_bytes[0] += flat.numel() * 4
+        ce_host, z_host = host[:mb], host[mb:2 * mb]
+        pos = 2 * mb
+        aux_host = None
+        if has_aux:
+            n_aux_ranks = dp_world * (mesh.size("tp") if self.result.execution.sp else 1)
+            aux_host = [v / n_aux_ranks for v in host[pos:pos + mb]]
+            pos += mb
+        grad_norm, clip_scale = host[pos], host[pos + 1]
+        pos += 2
+        param_norm = update_norm = None
+        if diagnostics:
+            param_norm, update_norm = host[pos], host[pos + 1]
+            pos += 2
+        router_host = {k: host[pos + i] for i, k in enumerate(router_keys)}
+        metrics = StepMetrics(
+            loss_sum=float(sum(ce_host)), token_count=float(sum(global_counts)), lr=opt["lr"], grad_norm=grad_norm,
+            param_norm=param_norm, update_norm=update_norm, z_loss_sum=float(sum(z_host)),
+            microbatch_loss_sums=[float(v) for v in ce_host], microbatch_token_counts=global_counts,
+        )
+        if aux_host is not None:
+            weights = [c / global_count for c in global_counts]
+            metrics.aux_loss = float(sum(a * w for a, w in zip(aux_host, weights)))
+            metrics.moe_aux_loss = metrics.aux_loss
+        metrics.router = router_host
+        metrics.router_layers = router_payload.get("layers", [])
+        metrics.smebu = {k: v for k, v in router_host.items() if k.startswith("smebu_")}
+        metrics.optimizer_groups = []
+        metrics.router["clip_scale"] = clip_scale
+        return metrics
+
+    # ------------------------------------------------------------------------------------------------
+    def _router_metrics(self, all_stats) -> dict[str, Any]:
+        """Sum per-layer expert counts over microbatches and replicas; apply the SMEBU update."""
+
+        layers: dict[int, list] = {}
+        for stats in all_stats:
+            for st in stats:
+                layers.setdefault(st.layer_index, []).append(st)
+        if not layers:
+            return {}
+        order = sorted(layers)
+        counts = torch.stack([torch.stack([s.expert_counts for s in layers[i]]).sum(0) for i in order])
+        importance = torch.stack([torch.stack([s.importance for s in layers[i]]).sum(0) for i in order])
+        both = torch.stack([counts, importance])
+        for axis in self.loss_axes:
+            group = self.mesh.group(axis)
+            if group is not None:
+                dist.all_reduce(both, group=group)
+        counts, importance = both[0], both[1]
+        out = router_diagnostics(counts, importance)
+        out.update(apply_moe_balance_update(self.moe_balance, counts))
+        out["layers"] = [{"layer_index": i, "counts": counts[k], "importance": importance[k]}
+                         for k, i in enumerate(order)]
+        return out
