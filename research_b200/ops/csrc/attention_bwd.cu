@@ -507,3 +507,47 @@ extern "C" int b200_attn_bwd(const void* q, const void* k, const void* v, const 
   if ((rc = launch_bwd<64, false>(tQ, tdO, tK, tV, tdQ, tdQ, p, s))) return rc;
   return launch_bwd<64, true>(tK, tV, tQ, tdO, tdK, tdV, p, s);
 }
+
+// ---------------------------------------------------------------------------------------------------
+// Allocation-free variant (see attention_bwd_noalloc.h): the delta scratch is a fixed array in the library
+// image instead of a caller-allocated buffer.
+// ---------------------------------------------------------------------------------------------------
+#include "attention_bwd_noalloc.h"
+
+static __device__ __align__(256) float g_attn_bwd_delta_scratch[B200_ATTN_NOALLOC_MAX_ROWS];
+
+extern "C" int b200_attn_bwd_noalloc(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                                     const void* lse, void* dq, void* dk, void* dv, const void* lo, const void* hi,
+                                     int B, int S, int Hq, int Hkv, int D, long long q_row, long long q_batch,
+                                     long long k_row, long long k_batch, long long v_row, long long v_batch,
+                                     long long o_row, long long o_batch, long long do_row, long long do_batch,
+                                     long long dq_row, long long dq_batch, long long dk_row, long long dk_batch,
+                                     long long dv_row, long long dv_batch, float scale, int causal, int* status,
+                                     void* stream) {
+  if (B <= 0 || S <= 0 || Hq <= 0) return b200host::RC_BAD_SHAPE;
+  const long long rows = (long long)B * Hq * S;
+  if (rows > (long long)B200_ATTN_NOALLOC_MAX_ROWS) {
+    fprintf(stderr,
+            "b200_attn_bwd_noalloc: B*Hq*S = %lld exceeds the built-in scratch of %d rows; use b200_attn_bwd with a "
+            "caller-provided delta buffer\n",
+            rows, (int)B200_ATTN_NOALLOC_MAX_ROWS);
+    return B200_ATTN_NOALLOC_TOO_LARGE;
+  }
+  // In host code the array's name is only a handle; the kernels need its device address, which differs per
+  // device.  Looked up once per device (with that device current) and cached.
+  static float* scratch_ptr[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B200_ATTN_NOALLOC_SYMBOL_FAILED;
+  if (scratch_ptr[dev] == nullptr) {
+    float* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_attn_bwd_delta_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      fprintf(stderr, "b200_attn_bwd_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e));
+      return B200_ATTN_NOALLOC_SYMBOL_FAILED;
+    }
+    scratch_ptr[dev] = ptr;
+  }
+  return b200_attn_bwd(q, k, v, o, d_o, lse, scratch_ptr[dev], dq, dk, dv, lo, hi, B, S, Hq, Hkv, D, q_row, q_batch,
+                       k_row, k_batch, v_row, v_batch, o_row, o_batch, do_row, do_batch, dq_row, dq_batch, dk_row,
+                       dk_batch, dv_row, dv_batch, scale, causal, 0, status, stream);
+}

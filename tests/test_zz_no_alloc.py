@@ -1,0 +1,83 @@
+"""The allocation-free attention-backward entry point, called through its exported C symbol.
+
+Some hosts that load the kernel library may not allocate device memory (their memory belongs to a pool they
+do not own, or they run where cudaMalloc is forbidden).  ``b200_attn_bwd_noalloc`` serves them by keeping the
+backward pass's ``delta`` scratch in a fixed array inside the library.  This test checks, on two calls in a
+row (the array is shared and keeps the previous call's contents), that it produces what the ordinary entry
+point produces, and that oversize problems are refused.  The file name makes pytest collect it last.
+"""
+
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _bf(shape, seed, scale=1.0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(shape, generator=g, device="cuda") * scale).to(torch.bfloat16)
+
+
+def _symbol():
+    from research_b200.ops import native
+
+    lib = native.load()
+    fn = lib.b200_attn_bwd_noalloc
+    vp, ci, ll, cf = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+    fn.argtypes = [vp] * 11 + [ci] * 5 + [ll] * 16 + [cf, ci, vp, vp]
+    fn.restype = ci
+    return fn
+
+
+def _call(fn, q, k, v, o, d_o, lse, causal):
+    from research_b200.ops import native
+
+    B, S, Hq, D = q.shape
+    Hkv = k.shape[2]
+    dq, dk, dv = torch.zeros_like(q), torch.zeros_like(k), torch.zeros_like(v)
+    rc = fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(), lse.data_ptr(), dq.data_ptr(),
+            dk.data_ptr(), dv.data_ptr(), None, None, B, S, Hq, Hkv, D, q.stride(1), q.stride(0), k.stride(1),
+            k.stride(0), v.stride(1), v.stride(0), o.stride(1), o.stride(0), d_o.stride(1), d_o.stride(0),
+            dq.stride(1), dq.stride(0), dk.stride(1), dk.stride(0), dv.stride(1), dv.stride(0), D ** -0.5,
+            int(causal), native.status_word(q.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+    return rc, dq, dk, dv
+
+
+def test_noalloc_matches_regular_entry_point_twice():
+    from research_b200.ops import native
+
+    fn = _symbol()
+    for call, (S, seed) in enumerate(((384, 1), (640, 2))):  # second call reuses the same scratch array
+        B, Hq, Hkv, D = 2, 4, 2, 128
+        q, k, v = _bf((B, S, Hq, D), seed), _bf((B, S, Hkv, D), seed + 10), _bf((B, S, Hkv, D), seed + 20)
+        d_o = _bf((B, S, Hq, D), seed + 30, 0.5)
+        o, lse = native.attn_fwd(q, k, v, causal=True)
+        ref = native.attn_bwd(q, k, v, o, d_o, lse, causal=True)
+        rc, dq, dk, dv = _call(fn, q, k, v, o, d_o, lse, True)
+        assert rc == 0, (call, rc)
+        native.check_status()
+        for name, got, want in zip(("dq", "dk", "dv"), (dq, dk, dv), ref):
+            err = (got.float() - want.float()).abs().max().item()
+            scale = want.float().abs().max().item()
+            assert err <= 2e-2 * scale + 2e-2, (call, name, err, scale)
+
+
+def test_noalloc_rejects_oversize_problem():
+    fn = _symbol()
+    B, S, Hq, Hkv, D = 1, 128, 2, 2, 128
+    q, k, v = _bf((B, S, Hq, D), 1), _bf((B, S, Hkv, D), 2), _bf((B, S, Hkv, D), 3)
+    o, d_o = torch.zeros_like(q), torch.zeros_like(q)
+    lse = torch.zeros(B, Hq, S, device="cuda")
+    from research_b200.ops import native
+
+    dq, dk, dv = torch.zeros_like(q), torch.zeros_like(k), torch.zeros_like(v)
+    # claim a sequence so long that B * Hq * S exceeds the built-in scratch: must be refused before any launch
+    rc = fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(), lse.data_ptr(), dq.data_ptr(),
+            dk.data_ptr(), dv.data_ptr(), None, None, 64, 1 << 20, Hq, Hkv, D, q.stride(1), q.stride(0), k.stride(1),
+            k.stride(0), v.stride(1), v.stride(0), o.stride(1), o.stride(0), d_o.stride(1), d_o.stride(0),
+            dq.stride(1), dq.stride(0), dk.stride(1), dk.stride(0), dv.stride(1), dv.stride(0), D ** -0.5, 1,
+            native.status_word(q.device).data_ptr(), torch.cuda.current_stream().cuda_stream)
+    assert rc == -5
+    torch.cuda.synchronize()
