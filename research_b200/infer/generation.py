@@ -1,0 +1,155 @@
+"""KV-cache generation: prefill, per-token decode, sampling.
+
+Sampler semantics follow the reference (src/jaxtitan/infer/generation.py:225-242, 420-432): logits / temperature;
+top-k keeps values >= the k-th largest (a threshold, so ties survive); ``top_k == 1`` is argmax; otherwise a
+categorical draw; the log-probability of the chosen token under the filtered distribution is returned; ``top_p`` is
+rejected.  The cache is paged: fixed-size pages per sequence, appended in place, and decode attention reads only
+the pages in use (the reference attends over the whole padded cache every step, generation.py:302,
+components/attention.py:213-218).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from research_b200.errors import ContractError
+from research_b200.ops import functional as Fn
+
+
+class PagedKVCache:
+    """``[layers, pages, page_size, kv_heads, head_dim]`` K and V pools + a page table per sequence."""
+
+    def __init__(self, *, layers: int, batch: int, max_len: int, kv_heads: int, head_dim: int, page_size: int,
+                 dtype: torch.dtype, device: torch.device):
+        self.page_size = page_size
+        self.pages_per_seq = (max_len + page_size - 1) // page_size
+        self.max_len = self.pages_per_seq * page_size
+        total_pages = batch * self.pages_per_seq
+        shape = (layers, total_pages, page_size, kv_heads, head_dim)
+        self.k = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.page_table = torch.arange(total_pages, device=device, dtype=torch.int32).view(batch, self.pages_per_seq)
+        self.lengths = torch.zeros(batch, dtype=torch.int32, device=device)
+        self.batch = batch
+
+    def _flat(self, pool: torch.Tensor, layer: int) -> torch.Tensor:
+        # with the identity page table, sequence b occupies a contiguous [max_len] stretch of the pool
+        return pool[layer].view(self.batch, self.max_len, pool.shape[-2], pool.shape[-1])
+
+    def update_and_attend(self, layer: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
+                          positions: torch.Tensor, window: int | None) -> torch.Tensor:
+        """Write k, v at ``positions`` ([B,T]) and attend q over everything written so far (causal)."""
+
+        B, T = positions.shape
+        kc, vc = self._flat(self.k, layer), self._flat(self.v, layer)
+        idx = positions.long()
+        b_idx = torch.arange(B, device=q.device)[:, None].expand(B, T)
+        kc[b_idx, idx] = k.to(kc.dtype)
+        vc[b_idx, idx] = v.to(vc.dtype)
+        end = int(positions.max().item()) + 1
+        if T == 1 and q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128):
+            from research_b200.ops.decode import decode_attention
+
+            lo = None if window is None else (positions[:, 0] - (window - 1)).clamp_min(0).to(torch.int32)
+            return decode_attention(q[:, 0], kc, vc, (positions[:, 0] + 1).to(torch.int32), lo)[:, None]
+        keys, vals = kc[:, :end], vc[:, :end]
+        kpos = torch.arange(end, device=q.device)
+        allowed = kpos[None, None, :] <= idx[:, :, None]
+        if window is not None:
+            allowed = allowed & (kpos[None, None, :] > idx[:, :, None] - window)
+        return _masked_attention(q, keys, vals, allowed)
+
+    def advance(self, positions: torch.Tensor) -> None:
+        self.lengths = torch.maximum(self.lengths, (positions.max(dim=1).values + 1).to(torch.int32))
+
+
+def _masked_attention(q, k, v, allowed):
+    B, T, Hq, D = q.shape
+    g = Hq // k.shape[2]
+    qf = q.permute(0, 2, 1, 3).float()
+    kf = k.permute(0, 2, 1, 3).repeat_interleave(g, dim=1).float()
+    vf = v.permute(0, 2, 1, 3).repeat_interleave(g, dim=1).float()
+    s = torch.einsum("bhqd,bhkd->bhqk", qf, kf) * (D ** -0.5)
+    s = s.masked_fill(~allowed[:, None], float("-inf"))
+    p = torch.softmax(s, dim=-1).to(q.dtype).float()
+    return torch.einsum("bhqk,bhkd->bhqd", p, vf).permute(0, 2, 1, 3).to(q.dtype).reshape(B, T, Hq * D)
+
+
+def init_kv_cache(model, batch: int, max_len: int, *, page_size: int = 128) -> PagedKVCache:
+    spec = model.spec
+    p = next(model.parameters())
+    attn = model.layers[0].attn
+    return PagedKVCache(layers=spec.num_layers, batch=batch, max_len=max_len, kv_heads=attn.hkv,
+                        head_dim=spec.head_dim, page_size=page_size, dtype=p.dtype, device=p.device)
+
+
+def sample_next_token(logits: torch.Tensor, *, temperature: float, top_k: int | None, top_p: float | None,
+                      generator: torch.Generator | None):
+    """logits [B, V] -> (token [B] int64, logprob [B] fp32)."""
+
+    if top_p is not None:
+        raise ContractError("generation.top_p is not supported at runtime")
+    if temperature <= 0:
+        raise ContractError(f"generation.temperature must be positive, got {temperature}")
+    scaled = logits.float() / float(temperature)
+    if top_k is not None:
+        if top_k <= 0:
+            raise ContractError(f"generation.top_k must be positive, got {top_k}")
+        k = min(int(top_k), scaled.shape[-1])
+        threshold = torch.topk(scaled, k, dim=-1).values[:, -1:]
+        scaled = torch.where(scaled >= threshold, scaled, torch.full_like(scaled, float("-inf")))
+    logp = torch.log_softmax(scaled, dim=-1)
+    if top_k == 1:
+        token = torch.argmax(scaled, dim=-1)
+    else:
+        token = torch.multinomial(torch.exp(logp), 1, generator=generator)[:, 0]
+    return token, logp.gather(1, token[:, None])[:, 0]
+
+
+@dataclass
+class GenerationResult:
+    prompt_ids: list[list[int]]
+    generated_ids: list[list[int]]
+    full_ids: list[list[int]]
+    logprobs: list[list[float]]
+
+
+@torch.no_grad()
+def generate_tokens(model, prompt_ids: torch.Tensor, *, max_new_tokens: int, temperature: float = 1.0,
+                    top_k: int | None = None, top_p: float | None = None, seed: int = 0,
+                    page_size: int = 128) -> GenerationResult:
+    """prompt_ids: [B, P] (all prompts the same length).  Prefill once, then one decode step per new token."""
+
+    if max_new_tokens <= 0:
+        raise ContractError(f"generation.max_new_tokens must be positive, got {max_new_tokens}")
+    B, P = prompt_ids.shape
+    total = P + max_new_tokens
+    if total > model.spec.max_seq_len:
+        raise ContractError(f"prompt + max_new_tokens = {total} exceeds model.max_seq_len = {model.spec.max_seq_len}")
+    device = next(model.parameters()).device
+    prompt_ids = prompt_ids.to(device)
+    was_training = model.training
+    model.eval()
+    cache = init_kv_cache(model, B, total, page_size=page_size)
+    gen = torch.Generator(device=device).manual_seed(int(seed))
+    positions = torch.arange(P, device=device, dtype=torch.int32).expand(B, P).contiguous()
+    logits = model.run_with_cache(prompt_ids.to(torch.int32), positions, cache)[:, -1]
+    cache.advance(positions)
+    tokens, logprobs = [], []
+    for t in range(max_new_tokens):
+        tok, lp = sample_next_token(logits, temperature=temperature, top_k=top_k, top_p=top_p, generator=gen)
+        tokens.append(tok)
+        logprobs.append(lp)
+        if t + 1 == max_new_tokens:
+            break
+        pos = torch.full((B, 1), P + t, device=device, dtype=torch.int32)
+        logits = model.run_with_cache(tok[:, None].to(torch.int32), pos, cache)[:, -1]
+        cache.advance(pos)
+    model.train(was_training)
+    out = torch.stack(tokens, dim=1).cpu()
+    lps = torch.stack(logprobs, dim=1).cpu()
+    prompts = prompt_ids.cpu().tolist()
+    generated = out.tolist()
+    return GenerationResult(prompts, generated, [p + g for p, g in zip(prompts, generated)], lps.tolist())

@@ -126,6 +126,18 @@ def build_all(*, force: bool = False, verbose: bool = False, ptxas_info: bool = 
     return BuildResult(KERNEL_LIB, host_lib, True, tuple(p.name for p in cu), digest)
 
 
+def build_host_only() -> Path | None:
+    """Build just the host C++ library (used when only ``libb200host.so`` is missing)."""
+
+    cpp = host_sources()
+    if not cpp:
+        return None
+    LIB_DIR.mkdir(parents=True, exist_ok=True)
+    gxx = shutil.which("g++") or "g++"
+    _run([gxx, *CXX_FLAGS, "-shared", "-I", str(NATIVE_DIR), "-o", str(HOST_LIB), *[str(s) for s in cpp]])
+    return HOST_LIB
+
+
 if __name__ == "__main__":
     res = build_all(force=bool(os.environ.get("B200_FORCE_BUILD")), verbose=True)
     print(f"kernel library: {res.kernel_lib} (rebuilt={res.rebuilt})")

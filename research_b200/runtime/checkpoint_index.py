@@ -124,7 +124,7 @@ def record_checkpoint(index: CheckpointIndex, run_dir: str | Path, *, step: int,
                       eval_loss: float | None) -> CheckpointIndex:
     run_dir = Path(run_dir)
     path = Path(checkpoint_path)
-    if path.is_absolute():
+    if not (path.parts and path.parts[0] == "checkpoints" and not path.is_absolute()):
         try:
             path = path.resolve().relative_to(run_dir.resolve())
         except ValueError as exc:

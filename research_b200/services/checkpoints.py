@@ -1,0 +1,247 @@
+"""Checkpoint service: composite checkpoints in an Orbax-compatible directory layout, written and read without
+Orbax (neither orbax nor tensorstore can be installed offline).
+
+Layout (what the reference's ``CheckpointManager`` produces, src/jaxtitan/services/checkpoints.py:54-176;
+tests/jaxtitan/test_checkpoints.py:53)::
+
+    checkpoints/<step:06d>/
+        _CHECKPOINT_METADATA            step-level metadata (item names, commit timestamp)
+        train/                          pytree item: one Zarr v2 array per leaf (non-OCDBT layout)
+            _METADATA                   tree structure: leaf key paths, dtypes, shapes
+            _sharding                   per-leaf sharding descriptions (single-host: replicated)
+            <leaf.key.path>/.zarray     zarr v2 header, one uncompressed chunk
+            <leaf.key.path>/0.0...      the chunk (C order, little endian)
+        dataset/metadata                JSON item
+        host/metadata                   JSON item
+        metadata/metadata               JSON item
+
+Leaf key paths follow the reference's ``TrainState`` (step, tokens_seen, model.<nnx path>, opt_state..., rng...,
+moe_balance...) with model kernels in the reference's ``[in, out]`` orientation.  The reader also accepts the
+OCDBT form for inspection when every value is stored raw, but what it is tested on is its own output.
+Retention: keep the newest ``max_to_keep`` plus protected steps (latest / best), as the reference's
+``_ProtectedLatestPolicy`` (checkpoints.py:183-199).  Saves are synchronous and committed by renaming a temporary
+directory.
+"""
+
+from __future__ import annotations
+
+import json
+import shutil
+import time
+from dataclasses import dataclass
+from pathlib import Path
+from typing import Any, Mapping
+
+import numpy as np
+
+from research_b200.config.canonical import canonical_json
+from research_b200.errors import ContractError
+
+STEP_DIGITS = 6
+_DTYPES = {"float32": "<f4", "float64": "<f8", "int32": "<i4", "int64": "<i8", "uint32": "<u4", "uint64": "<u8",
+           "uint8": "|u1", "bool": "|b1", "float16": "<f2", "uint16": "<u2", "int16": "<i2"}
+
+
+def step_dir_name(step: int) -> str:
+    return f"{step:0{STEP_DIGITS}d}"
+
+
+@dataclass
+class CheckpointRestore:
+    tensors: dict[str, np.ndarray]
+    dataset_state: dict[str, Any]
+    host_state: dict[str, Any]
+    metadata: dict[str, Any]
+    step: int
+    path: Path
+
+
+def _zarr_dtype(arr: np.ndarray) -> str:
+    name = arr.dtype.name
+    if name not in _DTYPES:
+        raise ContractError(f"unsupported checkpoint leaf dtype {name}")
+    return _DTYPES[name]
+
+
+def write_array(leaf_dir: Path, arr: np.ndarray) -> None:
+    """One zarr-v2 array with a single uncompressed chunk (bfloat16 leaves are stored as uint16 bit patterns)."""
+
+    leaf_dir.mkdir(parents=True, exist_ok=False)
+    arr = np.ascontiguousarray(arr)
+    header = {"chunks": list(arr.shape) if arr.ndim else [], "compressor": None, "dtype": _zarr_dtype(arr),
+              "fill_value": None, "filters": None, "order": "C", "shape": list(arr.shape), "zarr_format": 2,
+              "dimension_separator": "."}
+    (leaf_dir / ".zarray").write_text(json.dumps(header, sort_keys=True))
+    chunk_name = ".".join("0" for _ in arr.shape) if arr.ndim else "0"
+    _write_bytes(leaf_dir / chunk_name, arr)
+
+
+def _write_bytes(path: Path, arr: np.ndarray) -> None:
+    from research_b200.native import hostlib
+
+    data = arr.astype(arr.dtype.newbyteorder("<"), copy=False)
+    if not hostlib.write_file(path, data):
+        with path.open("wb") as handle:
+            handle.write(data.tobytes())
+
+
+def read_array(leaf_dir: Path) -> np.ndarray:
+    try:
+        header = json.loads((leaf_dir / ".zarray").read_text())
+    except (OSError, json.JSONDecodeError) as exc:
+        raise ContractError(f"checkpoint leaf {leaf_dir} has no readable .zarray: {exc}") from exc
+    if header.get("compressor") is not None:
+        raise ContractError(f"checkpoint leaf {leaf_dir} is compressed; only raw chunks are supported")
+    shape = tuple(header["shape"])
+    chunks = tuple(header.get("chunks") or shape)
+    if chunks != shape:
+        raise ContractError(f"checkpoint leaf {leaf_dir} is chunked {chunks} != shape {shape}")
+    sep = header.get("dimension_separator", ".")
+    chunk_name = sep.join("0" for _ in shape) if shape else "0"
+    path = leaf_dir / chunk_name
+    dtype = np.dtype(header["dtype"])
+    expected = int(np.prod(shape, dtype=np.int64)) * dtype.itemsize if shape else dtype.itemsize
+    if not path.is_file() or path.stat().st_size != expected:
+        raise ContractError(f"checkpoint chunk {path} is missing or has the wrong size (expected {expected} bytes)")
+    return np.fromfile(path, dtype=dtype).reshape(shape)
+
+
+class LocalCheckpointService:
+    ITEMS = ("train", "dataset", "host", "metadata")
+
+    def __init__(self, run_dir: str | Path, *, max_to_keep: int = 2, protected_steps: set[int] | None = None,
+                 is_writer: bool = True) -> None:
+        if max_to_keep <= 0:
+            raise ContractError(f"max_to_keep must be positive, got {max_to_keep}")
+        self.run_dir = Path(run_dir)
+        self.checkpoints_dir = self.run_dir / "checkpoints"
+        self.max_to_keep = max_to_keep
+        self.protected_steps = set(protected_steps or ())
+        self.is_writer = is_writer
+        if is_writer:
+            self.checkpoints_dir.mkdir(parents=True, exist_ok=True)
+
+    # ---- save ----------------------------------------------------------------------------------------
+    def save(self, step: int, tensors: Mapping[str, np.ndarray], dataset_state: Mapping[str, Any],
+             host_state: Mapping[str, Any], metadata: Mapping[str, Any]) -> Path:
+        if step < 0:
+            raise ContractError(f"checkpoint step must be non-negative, got {step}")
+        if host_state.get("dataset") != dict(dataset_state):
+            raise ContractError("host_state.dataset must match dataset_state when saving a checkpoint")
+        final = self.checkpoints_dir / step_dir_name(step)
+        if not self.is_writer:
+            return final
+        tmp = self.checkpoints_dir / f"{step_dir_name(step)}.orbax-checkpoint-tmp-{int(time.time() * 1e6)}"
+        if final.exists():
+            shutil.rmtree(final)
+        try:
+            train = tmp / "train"
+            train.mkdir(parents=True)
+            tree_meta = {}
+            for name, value in tensors.items():
+                arr = np.asarray(value)
+                write_array(train / name, arr)
+                tree_meta[name] = {"key_metadata": [{"key": part, "key_type": 2} for part in name.split(".")],
+                                   "value_metadata": {"value_type": "jax.Array", "skip_deserialize": False,
+                                                      "dtype": arr.dtype.name, "shape": list(arr.shape)}}
+            (train / "_METADATA").write_text(json.dumps({"tree_metadata": tree_meta, "use_zarr3": False,
+                                                         "store_array_data_equal_to_fill_value": True}, sort_keys=True))
+            (train / "_sharding").write_text(json.dumps({name: {"sharding_type": "SingleDeviceSharding"}
+                                                         for name in tensors}, sort_keys=True))
+            for item, payload in (("dataset", dataset_state), ("host", host_state), ("metadata", metadata)):
+                (tmp / item).mkdir()
+                (tmp / item / "metadata").write_text(canonical_json(payload))
+            (tmp / "_CHECKPOINT_METADATA").write_text(json.dumps({
+                "item_handlers": {"train": "orbax.checkpoint._src.handlers.standard_checkpoint_handler.StandardCheckpointHandler",
+                                  "dataset": "orbax.checkpoint._src.handlers.json_checkpoint_handler.JsonCheckpointHandler",
+                                  "host": "orbax.checkpoint._src.handlers.json_checkpoint_handler.JsonCheckpointHandler",
+                                  "metadata": "orbax.checkpoint._src.handlers.json_checkpoint_handler.JsonCheckpointHandler"},
+                "init_timestamp_nsecs": time.time_ns(), "commit_timestamp_nsecs": time.time_ns(),
+                "writer": "research_b200"}, sort_keys=True))
+            tmp.replace(final)
+        except Exception:
+            shutil.rmtree(tmp, ignore_errors=True)
+            raise
+        self._apply_retention()
+        return final
+
+    def _apply_retention(self) -> None:
+        steps = self.all_steps()
+        keep = set(steps[-self.max_to_keep:]) | self.protected_steps
+        for s in steps:
+            if s not in keep:
+                shutil.rmtree(self.checkpoints_dir / step_dir_name(s), ignore_errors=True)
+
+    def set_protected_steps(self, steps: set[int]) -> None:
+        self.protected_steps = set(steps)
+
+    # ---- restore -------------------------------------------------------------------------------------
+    def all_steps(self) -> list[int]:
+        if not self.checkpoints_dir.is_dir():
+            return []
+        out = []
+        for child in self.checkpoints_dir.iterdir():
+            if child.is_dir() and child.name.isdigit() and (child / "_CHECKPOINT_METADATA").exists():
+                out.append(int(child.name))
+        return sorted(out)
+
+    def latest_step(self) -> int | None:
+        steps = self.all_steps()
+        return steps[-1] if steps else None
+
+    def latest_path(self) -> Path | None:
+        step = self.latest_step()
+        return None if step is None else self.checkpoints_dir / step_dir_name(step)
+
+    def _step_path(self, step: int) -> Path:
+        path = self.checkpoints_dir / step_dir_name(step)
+        if not path.is_dir():
+            raise ContractError(f"checkpoint step {step} does not exist in {self.checkpoints_dir}")
+        return path
+
+    def _read_json_item(self, path: Path, item: str) -> dict[str, Any]:
+        file = path / item / "metadata"
+        try:
+            raw = json.loads(file.read_text())
+        except (OSError, json.JSONDecodeError) as exc:
+            raise ContractError(f"checkpoint item {item} in {path} is unreadable: {exc}") from exc
+        if not isinstance(raw, dict):
+            raise ContractError(f"checkpoint item {item} in {path} must be a JSON object")
+        return raw
+
+    def restore_metadata(self, step: int) -> dict[str, Any]:
+        return self._read_json_item(self._step_path(step), "metadata")
+
+    def restore_latest_metadata(self) -> dict[str, Any]:
+        step = self.latest_step()
+        if step is None:
+            raise ContractError(f"no checkpoints found in {self.checkpoints_dir}")
+        return self.restore_metadata(step)
+
+    def restore(self, step: int, names: list[str] | None = None) -> CheckpointRestore:
+        path = self._step_path(step)
+        train = path / "train"
+        try:
+            tree = json.loads((train / "_METADATA").read_text())["tree_metadata"]
+        except (OSError, json.JSONDecodeError, KeyError) as exc:
+            raise ContractError(f"checkpoint {path} has no readable train/_METADATA: {exc}") from exc
+        wanted = list(tree) if names is None else names
+        tensors = {}
+        for name in wanted:
+            if name not in tree:
+                raise ContractError(f"checkpoint {path} has no leaf {name!r}")
+            tensors[name] = read_array(train / name)
+        dataset = self._read_json_item(path, "dataset")
+        host = self._read_json_item(path, "host")
+        if host.get("dataset") != dataset:
+            raise ContractError("restored host_state.dataset does not match restored dataset_state")
+        return CheckpointRestore(tensors, dataset, host, self._read_json_item(path, "metadata"), step, path)
+
+    def restore_latest(self) -> CheckpointRestore:
+        step = self.latest_step()
+        if step is None:
+            raise ContractError(f"no checkpoints found in {self.checkpoints_dir}")
+        return self.restore(step)
+
+    def close(self) -> None:
+        return None
