@@ -44,9 +44,10 @@ class AttentionConfig:
 class ForwardInputs:
     """Per-batch tensors shared by every layer."""
 
-    positions: torch.Tensor              # int32 [B*S]
+    positions: torch.Tensor              # int32 [B*S], local indices
     B: int
     S: int
+    q_offset: int = 0                    # global position of local row 0 (context parallelism)
     lo_causal: torch.Tensor | None = None    # int32 [B,S]: document starts (or None)
     hi_causal: torch.Tensor | None = None
     lo_window: dict[int, tuple[torch.Tensor, torch.Tensor | None]] | None = None  # per window size
@@ -58,7 +59,7 @@ class ForwardInputs:
             self.lo_window = {}
         if window not in self.lo_window:
             pos = self.positions.view(self.B, self.S)
-            idx = torch.arange(self.S, device=pos.device, dtype=torch.int32).expand(self.B, self.S)
+            idx = torch.arange(self.S, device=pos.device, dtype=torch.int32).expand(self.B, self.S) + self.q_offset
             lo = (idx - (window - 1)).clamp_min(0)
             if self.lo_causal is not None:
                 lo = torch.maximum(lo, self.lo_causal)
@@ -257,14 +258,17 @@ class TransformerLM(nn.Module):
         B, S = input_ids.shape
         dev = input_ids.device
         positions = torch.arange(S, device=dev, dtype=torch.int32).repeat(B)
+        q_offset = self.ex.cp_rank * S if self.ex.cp_size > 1 else 0
         lo = hi = None
         if token_doc_ids is not None and self.spec.attention_doc_mask:
-            d = token_doc_ids.to(dev)
-            change = torch.ones(B, S, dtype=torch.bool, device=dev)
+            d = token_doc_ids.to(dev)                      # document ids of the WHOLE sequence, [B, S_full]
+            full = d.shape[1]
+            change = torch.ones(B, full, dtype=torch.bool, device=dev)
             change[:, 1:] = d[:, 1:] != d[:, :-1]
-            idx = torch.arange(S, device=dev, dtype=torch.int32).expand(B, S)
-            lo = torch.cummax(torch.where(change, idx, torch.zeros_like(idx)), dim=1).values.to(torch.int32).contiguous()
-        return ForwardInputs(positions=positions, B=B, S=S, lo_causal=lo, hi_causal=hi)
+            idx = torch.arange(full, device=dev, dtype=torch.int32).expand(B, full)
+            lo = torch.cummax(torch.where(change, idx, torch.zeros_like(idx)), dim=1).values.to(torch.int32)
+            lo = lo[:, q_offset:q_offset + S].contiguous()  # this rank's rows, global kv positions
+        return ForwardInputs(positions=positions, B=B, S=S, q_offset=q_offset, lo_causal=lo, hi_causal=hi)
 
     def hidden_states(self, input_ids: torch.Tensor, token_doc_ids: torch.Tensor | None = None):
         """Returns the final-normed hidden states ``[B, S(/tp), H]`` plus aux losses and router stats."""

@@ -45,7 +45,7 @@ struct BwdSmem {
 };
 
 struct BwdParams {
-  int B, S, Hq, Hkv;
+  int B, S, Skv, q_off, Hq, Hkv;  // S = query rows, Skv = kv rows, q_off = global position of query row 0
   int causal;
   float scale;
   const int* lo;       // [B,S] or nullptr
@@ -81,7 +81,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int G = p.Hq / p.Hkv;
-  const int tiles = (p.S + TILE - 1) / TILE;
+  const int q_tiles = (p.S + TILE - 1) / TILE;
+  const int kv_tiles = (p.Skv + TILE - 1) / TILE;
+  const int tiles = DKV ? kv_tiles : q_tiles;  // resident tiles per (batch, head)
 
   // ---- which resident tile, which stream range -------------------------------------------------
   int b, h_res, r0;            // batch, head of the resident tile, first row of the resident tile
@@ -94,8 +96,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
     b = bh / p.Hq;
     r0 = qt * TILE;
     blk_begin = p.lo ? p.lo[(long long)b * p.S + r0] / TILE : 0;
-    int end = tiles;
-    if (p.causal) end = min(end, (min(r0 + TILE, p.S) - 1) / TILE + 1);
+    int end = kv_tiles;
+    if (p.causal) end = min(end, (p.q_off + min(r0 + TILE, p.S) - 1) / TILE + 1);
     blk_count = max(end - blk_begin, 0);
     n_total = blk_count;
   } else {
@@ -104,9 +106,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
     h_res = bh % p.Hkv;
     b = bh / p.Hkv;
     r0 = kt * TILE;
-    blk_begin = p.causal ? kt : 0;
-    int end = tiles;
-    if (p.hi) end = min(end, p.hi[(long long)b * p.S + min(r0 + TILE, p.S) - 1] / TILE + 1);
+    // query blocks are in local rows; a query row r sits at global position q_off + r
+    blk_begin = p.causal ? max(0, (r0 - p.q_off) / TILE) : 0;
+    int end = q_tiles;
+    if (p.hi) {
+      const int last_q = p.hi[(long long)b * p.Skv + min(r0 + TILE, p.Skv) - 1] - p.q_off;  // local row, may be < 0
+      end = last_q < 0 ? 0 : min(end, last_q / TILE + 1);
+    }
     blk_count = max(end - blk_begin, 0);
     n_total = blk_count * G;
   }
@@ -231,7 +237,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
     const int quad = warp & 3;
     const int half = (warp - 2) >> 2;
     const int row = quad * 32 + lane;
-    const int g_row = r0 + row;  // global position of this thread's row (q for dQ, kv for dKV)
+    const int g_row = r0 + row;  // this thread's row: local query row (dQ) or kv position (dKV)
+    const int q_pos = p.q_off + g_row;  // dQ only: global position of the query row
     const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
     const float scale_log2 = p.scale * kLog2e;
     float lse2_row = 0.f, delta_row = 0.f;
@@ -254,9 +261,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
       tc_fence_after();
       if (!DKV) {
         // rows = queries, columns = kv
-        const bool need_mask = (p.causal && blk * TILE + TILE - 1 > g_row) || (blk * TILE < lo_row) ||
-                               (blk * TILE + TILE > p.S) || (g_row >= p.S);
-        const int hi_col = g_row >= p.S ? -1 : (p.causal ? min(g_row, p.S - 1) : p.S - 1);
+        const bool need_mask = (p.causal && blk * TILE + TILE - 1 > q_pos) || (blk * TILE < lo_row) ||
+                               (blk * TILE + TILE > p.Skv) || (g_row >= p.S);
+        const int hi_col = g_row >= p.S ? -1 : (p.causal ? min(q_pos, p.Skv - 1) : p.Skv - 1);
         if (n > 0 && !mbar_wait_warp(acc_done, ph ^ 1, ab, ERR_WAIT_O_READY)) { ok = false; break; }
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -297,7 +304,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
         const int hq = hkv * G + g;
         const long long vec_base = ((long long)b * p.Hq + hq) * p.S;
         const int q_first = blk * TILE, q_last = min(blk * TILE + TILE, p.S) - 1;
-        bool need_mask = (p.causal && q_first < r0 + TILE - 1) || (blk * TILE + TILE > p.S) || (r0 + TILE > p.S);
+        bool need_mask = (p.causal && p.q_off + q_first < r0 + TILE - 1) || (blk * TILE + TILE > p.S) ||
+                         (r0 + TILE > p.Skv);
         if (p.lo) need_mask = need_mask || (p.lo[(long long)b * p.S + q_last] > r0);
         float pv[64];
 #pragma unroll
@@ -311,7 +319,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
             const float lse2 = q < p.S ? __ldg(p.lse + vec_base + q) * kLog2e : 0.f;
             float pr = exp2f(__uint_as_float(r1[i]) * scale_log2 - lse2);
             if (need_mask) {
-              bool allowed = q < p.S && g_row < p.S && (!p.causal || q >= g_row);
+              bool allowed = q < p.S && g_row < p.Skv && (!p.causal || p.q_off + q >= g_row);
               if (allowed && p.lo) allowed = g_row >= __ldg(p.lo + (long long)b * p.S + q);
               if (!allowed) pr = 0.f;
             }
@@ -392,7 +400,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
         }
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0 && slab_row < p.S) {
+        if (lane == 0 && slab_row < (DKV ? p.Skv : p.S)) {
           tma_store_4d(which == 0 ? &tmOut1 : &tmOut2, slab, half * 64, h_res, slab_row, b);
           tma_commit_group();
           tma_wait_group_read<0>();
@@ -456,7 +464,7 @@ int launch_bwd(const CUtensorMap& x1, const CUtensorMap& x2, const CUtensorMap& 
     if (e != cudaSuccess) return static_cast<int>(e);
     configured = true;
   }
-  const int tiles = (p.S + TILE - 1) / TILE;
+  const int tiles = ((DKV ? p.Skv : p.S) + TILE - 1) / TILE;
   const int grid = tiles * (DKV ? p.Hkv : p.Hq) * p.B;
   kern<<<grid, NUM_THREADS, smem_bytes, stream>>>(x1, x2, y1, y2, o1, o2, p);
   return static_cast<int>(cudaGetLastError());
@@ -474,9 +482,12 @@ extern "C" int b200_attn_bwd(const void* q, const void* k, const void* v, const 
                              long long k_row, long long k_batch, long long v_row, long long v_batch, long long o_row,
                              long long o_batch, long long do_row, long long do_batch, long long dq_row,
                              long long dq_batch, long long dk_row, long long dk_batch, long long dv_row,
-                             long long dv_batch, float scale, int causal, int reserved, int* status, void* stream) {
+                             long long dv_batch, float scale, int causal, long long skv_and_qoff, int* status,
+                             void* stream) {
   using namespace b200host;
-  (void)reserved;
+  const int Skv = (skv_and_qoff & 0xffffffffLL) ? (int)(skv_and_qoff & 0xffffffffLL) : S;
+  const int q_off = (int)(skv_and_qoff >> 32);
+  if (q_off % 128 != 0 || q_off < 0) return RC_BAD_SHAPE;
   if (B <= 0 || S <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv) return RC_BAD_SHAPE;
   if (D != 128 && D != 64) return RC_BAD_SHAPE;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
@@ -493,13 +504,13 @@ extern "C" int b200_attn_bwd(const void* q, const void* k, const void* v, const 
   CUtensorMap tQ, tK, tV, tdO, tdQ, tdK, tdV;
   int rc;
   if ((rc = make_map_4d(&tQ, bf, q, D, Hq, S, B, hs, q_row * 2, q_batch * 2, 64, 1, 128))) return rc;
-  if ((rc = make_map_4d(&tK, bf, k, D, Hkv, S, B, hs, k_row * 2, k_batch * 2, 64, 1, 128))) return rc;
-  if ((rc = make_map_4d(&tV, bf, v, D, Hkv, S, B, hs, v_row * 2, v_batch * 2, 64, 1, 128))) return rc;
+  if ((rc = make_map_4d(&tK, bf, k, D, Hkv, Skv, B, hs, k_row * 2, k_batch * 2, 64, 1, 128))) return rc;
+  if ((rc = make_map_4d(&tV, bf, v, D, Hkv, Skv, B, hs, v_row * 2, v_batch * 2, 64, 1, 128))) return rc;
   if ((rc = make_map_4d(&tdO, bf, d_o, D, Hq, S, B, hs, do_row * 2, do_batch * 2, 64, 1, 128))) return rc;
   if ((rc = make_map_4d(&tdQ, bf, dq, D, Hq, S, B, hs, dq_row * 2, dq_batch * 2, 64, 1, 32))) return rc;
-  if ((rc = make_map_4d(&tdK, bf, dk, D, Hkv, S, B, hs, dk_row * 2, dk_batch * 2, 64, 1, 32))) return rc;
-  if ((rc = make_map_4d(&tdV, bf, dv, D, Hkv, S, B, hs, dv_row * 2, dv_batch * 2, 64, 1, 32))) return rc;
-  BwdParams p{B, S, Hq, Hkv, causal, scale, (const int*)lo, (const int*)hi, (const float*)lse, (const float*)delta, status};
+  if ((rc = make_map_4d(&tdK, bf, dk, D, Hkv, Skv, B, hs, dk_row * 2, dk_batch * 2, 64, 1, 32))) return rc;
+  if ((rc = make_map_4d(&tdV, bf, dv, D, Hkv, Skv, B, hs, dv_row * 2, dv_batch * 2, 64, 1, 32))) return rc;
+  BwdParams p{B, S, Skv, q_off, Hq, Hkv, causal, scale, (const int*)lo, (const int*)hi, (const float*)lse, (const float*)delta, status};
   if (D == 128) {
     if ((rc = launch_bwd<128, false>(tQ, tdO, tK, tV, tdQ, tdQ, p, s))) return rc;
     return launch_bwd<128, true>(tK, tV, tQ, tdO, tdK, tdV, p, s);
@@ -549,5 +560,5 @@ extern "C" int b200_attn_bwd_noalloc(const void* q, const void* k, const void* v
   }
   return b200_attn_bwd(q, k, v, o, d_o, lse, scratch_ptr[dev], dq, dk, dv, lo, hi, B, S, Hq, Hkv, D, q_row, q_batch,
                        k_row, k_batch, v_row, v_batch, o_row, o_batch, do_row, do_batch, dq_row, dq_batch, dk_row,
-                       dk_batch, dv_row, dv_batch, scale, causal, 0, status, stream);
+                       dk_batch, dv_row, dv_batch, scale, causal, 0LL, status, stream);
 }

@@ -43,7 +43,7 @@ struct FwdSmem {
 };
 
 struct FwdParams {
-  int B, S, Hq, Hkv;
+  int B, S, Skv, q_off, Hq, Hkv;  // S = query rows; Skv = kv rows; q_off = global position of query row 0
   int causal;
   float scale_log2;  // softmax scale * log2(e)
   const int* lo;     // [B, S] or nullptr
@@ -81,11 +81,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int hkv = h / (p.Hq / p.Hkv);
   const int q0 = qt * NT * TILE_M;
 
-  // kv block range of this CTA
+  // kv block range of this CTA (kv positions are global; query row r sits at global position q_off + r)
   int kv_begin = 0;
   if (p.lo) kv_begin = p.lo[(long long)b * p.S + q0] / BLOCK_N;
-  int kv_end = (p.S + BLOCK_N - 1) / BLOCK_N;
-  if (p.causal) kv_end = min(kv_end, (min(q0 + NT * TILE_M, p.S) - 1) / BLOCK_N + 1);
+  int kv_end = (p.Skv + BLOCK_N - 1) / BLOCK_N;
+  if (p.causal) kv_end = min(kv_end, (p.q_off + min(q0 + NT * TILE_M, p.S) - 1) / BLOCK_N + 1);
   const int n_blocks = max(kv_end - kv_begin, 0);
 
   if (threadIdx.x == 0) {
@@ -213,7 +213,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const int t = (warp - 2) >> 2;
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
-    const int q_row = q0 + t * TILE_M + row;
+    const int q_row = q0 + t * TILE_M + row;       // local row (indexes lo / lse / O)
+    const int q_pos = p.q_off + q_row;             // global position (compared with kv positions)
     const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t tS = tmem_S + t * 128 + lane_sel;
     const uint32_t tO = tmem_O + t * D + lane_sel;
@@ -227,8 +228,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int kv0 = (kv_begin + j) * BLOCK_N;
       if (!mbar_wait_warp(&s_full[t], j & 1, ab, ERR_WAIT_S_READY)) { ok = false; break; }
       tc_fence_after();
-      const bool need_mask = (p.causal && kv0 + BLOCK_N - 1 > q_row) || (kv0 < lo_row) || (kv0 + BLOCK_N > p.S);
-      const int hi = p.causal ? min(q_row, p.S - 1) : p.S - 1;
+      const bool need_mask = (p.causal && kv0 + BLOCK_N - 1 > q_pos) || (kv0 < lo_row) || (kv0 + BLOCK_N > p.Skv);
+      const int hi = p.causal ? min(q_pos, p.Skv - 1) : p.Skv - 1;
       // pass 1: block maximum of the scaled, masked scores
       float bm = -INFINITY;
 #pragma unroll
@@ -372,23 +373,28 @@ int launch_fwd(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap
 }  // namespace
 
 // q: [B,S,Hq,D] view with element strides (q_row = between tokens, q_batch = between batches; heads are D
-// apart); k, v: [B,S,Hkv,D] likewise; o: dense [B,S,Hq,D]; lse: [B,Hq,S] fp32; lo: [B,S] int32 or null.
+// apart); k, v: [B,Skv,Hkv,D] likewise; o: [B,S,Hq,D]; lse: [B,Hq,S] fp32; lo: [B,S] int32 or null.
+// skv_and_qoff packs the kv length and the global position of query row 0 for context-parallel callers
+// (0 = same length as the queries, offset 0): low 32 bits Skv, high 32 bits q_off (a multiple of 128).
 extern "C" int b200_attn_fwd(const void* q, const void* k, const void* v, void* o, void* lse, const void* lo, int B,
                              int S, int Hq, int Hkv, int D, long long q_row, long long q_batch, long long k_row,
                              long long k_batch, long long v_row, long long v_batch, long long o_row,
-                             long long o_batch, float scale, int causal, int reserved, int* status, void* stream) {
+                             long long o_batch, float scale, int causal, long long skv_and_qoff, int* status,
+                             void* stream) {
   using namespace b200host;
-  (void)reserved;
+  const int Skv = (skv_and_qoff & 0xffffffffLL) ? (int)(skv_and_qoff & 0xffffffffLL) : S;
+  const int q_off = (int)(skv_and_qoff >> 32);
+  if (q_off % 128 != 0 || q_off < 0) return RC_BAD_SHAPE;
   if (B <= 0 || S <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv) return RC_BAD_SHAPE;
   if (D != 128 && D != 64) return RC_BAD_SHAPE;
   const CUtensorMapDataType bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   CUtensorMap tmQ, tmK, tmV, tmO;
   int rc;
   if ((rc = make_map_4d(&tmQ, bf, q, D, Hq, S, B, (uint64_t)D * 2, q_row * 2, q_batch * 2, 64, 1, 128))) return rc;
-  if ((rc = make_map_4d(&tmK, bf, k, D, Hkv, S, B, (uint64_t)D * 2, k_row * 2, k_batch * 2, 64, 1, 128))) return rc;
-  if ((rc = make_map_4d(&tmV, bf, v, D, Hkv, S, B, (uint64_t)D * 2, v_row * 2, v_batch * 2, 64, 1, 128))) return rc;
+  if ((rc = make_map_4d(&tmK, bf, k, D, Hkv, Skv, B, (uint64_t)D * 2, k_row * 2, k_batch * 2, 64, 1, 128))) return rc;
+  if ((rc = make_map_4d(&tmV, bf, v, D, Hkv, Skv, B, (uint64_t)D * 2, v_row * 2, v_batch * 2, 64, 1, 128))) return rc;
   if ((rc = make_map_4d(&tmO, bf, o, D, Hq, S, B, (uint64_t)D * 2, o_row * 2, o_batch * 2, 64, 1, 32))) return rc;
-  FwdParams p{B, S, Hq, Hkv, causal, scale * 1.4426950408889634f, (const int*)lo, (float*)lse, status};
+  FwdParams p{B, S, Skv, q_off, Hq, Hkv, causal, scale * 1.4426950408889634f, (const int*)lo, (float*)lse, status};
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (D == 128) return launch_fwd<128>(tmQ, tmK, tmV, tmO, p, s);
   return launch_fwd<64>(tmQ, tmK, tmV, tmO, p, s);

@@ -90,10 +90,10 @@ def _declare(lib: ctypes.CDLL) -> None:
     sig("b200_gemm_bf16_grouped_k", c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_ll,
         c_int, c_int, c_void_p, c_void_p, c_void_p)
     sig("b200_attn_fwd", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-        c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_float, c_int, c_int, c_void_p, c_void_p)
+        c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_float, c_int, c_ll, c_void_p, c_void_p)
     sig("b200_attn_bwd", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
         c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll,
-        c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_float, c_int, c_int, c_void_p, c_void_p)
+        c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_float, c_int, c_ll, c_void_p, c_void_p)
 
 
 def _stream() -> int:
@@ -343,11 +343,12 @@ def _check_bshd(t: torch.Tensor, name: str) -> None:
 
 
 def attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool = True,
-             lo: torch.Tensor | None = None, scale: float | None = None):
+             lo: torch.Tensor | None = None, scale: float | None = None, q_offset: int = 0):
     """Flash attention forward.  q: ``[B,S,Hq,D]``, k/v: ``[B,S,Hkv,D]`` (views into a packed buffer are fine).
 
     ``lo`` (int32 ``[B,S]``, non-decreasing along S) is the first kv position each query row may attend to.
-    Returns ``(o [B,S,Hq,D] bf16, lse [B,Hq,S] fp32)``.
+    k/v may be longer than q (context parallelism): ``q_offset`` (a multiple of 128) is the global position of
+    query row 0 among the kv positions.  Returns ``(o [B,S,Hq,D] bf16, lse [B,Hq,S] fp32)``.
     """
 
     lib = load()
@@ -361,26 +362,27 @@ def attn_fwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool 
         scale = D ** -0.5
     rc = lib.b200_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), lse.data_ptr(), _ptr(lo), B, S, Hq,
                            Hkv, D, q.stride(1), q.stride(0), k.stride(1), k.stride(0), v.stride(1), v.stride(0),
-                           o.stride(1), o.stride(0), scale, int(causal), 0, status_word(q.device).data_ptr(), _stream())
+                           o.stride(1), o.stride(0), scale, int(causal), k.shape[1] | (int(q_offset) << 32),
+                           status_word(q.device).data_ptr(), _stream())
     _check(rc, "b200_attn_fwd")
     return o, lse
 
 
-def kv_visibility_upper_bound(lo: torch.Tensor) -> torch.Tensor:
-    """kv-side view of a per-query lower bound: ``hi[b,k]`` = last query position that may attend to kv ``k``.
-
-    ``lo`` must be non-decreasing along the sequence, so ``hi[k] = #{q : lo[q] <= k} - 1``.
+def kv_visibility_upper_bound(lo: torch.Tensor, kv_len: int | None = None, q_offset: int = 0) -> torch.Tensor:
+    """kv-side view of a per-query lower bound: ``hi[b,k]`` = last (global) query position that may attend to
+    kv ``k``.  ``lo`` must be non-decreasing along the sequence, so ``hi[k] = q_offset + #{q : lo[q] <= k} - 1``.
     """
 
     B, S = lo.shape
-    k = torch.arange(S, device=lo.device, dtype=lo.dtype).expand(B, S).contiguous()
-    return (torch.searchsorted(lo.contiguous(), k, right=True) - 1).to(torch.int32)
+    n = S if kv_len is None else kv_len
+    k = torch.arange(n, device=lo.device, dtype=lo.dtype).expand(B, n).contiguous()
+    return (torch.searchsorted(lo.contiguous(), k, right=True) - 1 + q_offset).to(torch.int32)
 
 
 def attn_bwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor, d_o: torch.Tensor,
              lse: torch.Tensor, *, causal: bool = True, lo: torch.Tensor | None = None,
              hi: torch.Tensor | None = None, scale: float | None = None,
-             out: tuple[torch.Tensor, torch.Tensor, torch.Tensor] | None = None):
+             out: tuple[torch.Tensor, torch.Tensor, torch.Tensor] | None = None, q_offset: int = 0):
     """Flash attention backward; returns ``(dq, dk, dv)`` shaped like q, k, v.
 
     ``out`` may give three ``[B,S,H,D]`` views to write into (for example column ranges of one packed
@@ -399,8 +401,8 @@ def attn_bwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor,
         hi = kv_visibility_upper_bound(lo)
     if out is None:
         dq = torch.empty((B, S, Hq, D), dtype=q.dtype, device=q.device)
-        dk = torch.empty((B, S, Hkv, D), dtype=q.dtype, device=q.device)
-        dv = torch.empty((B, S, Hkv, D), dtype=q.dtype, device=q.device)
+        dk = torch.empty((B, k.shape[1], Hkv, D), dtype=q.dtype, device=q.device)
+        dv = torch.empty((B, k.shape[1], Hkv, D), dtype=q.dtype, device=q.device)
     else:
         dq, dk, dv = out
         for t, n in ((dq, "dq"), (dk, "dk"), (dv, "dv")):
@@ -410,7 +412,8 @@ def attn_bwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor,
                            delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), _ptr(lo), _ptr(hi), B, S, Hq,
                            Hkv, D, q.stride(1), q.stride(0), k.stride(1), k.stride(0), v.stride(1), v.stride(0),
                            o.stride(1), o.stride(0), d_o.stride(1), d_o.stride(0), dq.stride(1), dq.stride(0),
-                           dk.stride(1), dk.stride(0), dv.stride(1), dv.stride(0), scale, int(causal), 0,
+                           dk.stride(1), dk.stride(0), dv.stride(1), dv.stride(0), scale, int(causal),
+                           k.shape[1] | (int(q_offset) << 32),
                            status_word(q.device).data_ptr(), _stream())
     _check(rc, "b200_attn_bwd")
     LAUNCHES += 2

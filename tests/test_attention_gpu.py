@@ -130,3 +130,35 @@ def test_attn_bwd_speed():
     ms = s.elapsed_time(e) / 10
     flops = 10 * B * Hq * S * S * D / 2
     print(f"attn bwd causal B8 S4096 H16 D128: {ms:.3f} ms, {flops / ms / 1e9:.1f} TFLOP/s (5-GEMM count)")
+
+
+@pytest.mark.parametrize("docs", [False, True])
+def test_attn_context_parallel_offsets(docs):
+    """Queries of a later sequence chunk against all earlier keys: the same numbers as the full computation."""
+
+    from research_b200.ops import native
+
+    B, S, Hq, Hkv, D, chunks = 1, 1024, 4, 2, 128, 4
+    q, k, v = _bf((B, S, Hq, D), 1), _bf((B, S, Hkv, D), 2), _bf((B, S, Hkv, D), 3)
+    d_o = _bf((B, S, Hq, D), 4, 0.5)
+    lo = doc_lo(B, S, 200, 5) if docs else None
+    o_full, lse_full = native.attn_fwd(q, k, v, causal=True, lo=lo)
+    dq_full, dk_full, dv_full = native.attn_bwd(q, k, v, o_full, d_o, lse_full, causal=True, lo=lo)
+    n = S // chunks
+    dk_sum, dv_sum = torch.zeros_like(k, dtype=torch.float32), torch.zeros_like(v, dtype=torch.float32)
+    for r in range(chunks):
+        qs = slice(r * n, (r + 1) * n)
+        kv_len = (r + 1) * n
+        lo_r = None if lo is None else lo[:, qs].contiguous()
+        o, lse = native.attn_fwd(q[:, qs], k[:, :kv_len], v[:, :kv_len], causal=True, lo=lo_r, q_offset=r * n)
+        assert torch.allclose(o.float(), o_full[:, qs].float(), atol=2e-2, rtol=2e-2)
+        assert torch.allclose(lse, lse_full[:, :, qs], atol=2e-2, rtol=1e-3)
+        hi = None if lo_r is None else native.kv_visibility_upper_bound(lo_r, kv_len, r * n)
+        dq, dk, dv = native.attn_bwd(q[:, qs], k[:, :kv_len], v[:, :kv_len], o, d_o[:, qs], lse, causal=True, lo=lo_r,
+                                     hi=hi, q_offset=r * n)
+        assert torch.allclose(dq.float(), dq_full[:, qs].float(), atol=3e-2, rtol=3e-2)
+        dk_sum[:, :kv_len] += dk.float()
+        dv_sum[:, :kv_len] += dv.float()
+    native.check_status()
+    assert (dk_sum - dk_full.float()).abs().max() <= 3e-2 * dk_full.float().abs().max() + 3e-2
+    assert (dv_sum - dv_full.float()).abs().max() <= 3e-2 * dv_full.float().abs().max() + 3e-2
