@@ -127,6 +127,55 @@ class _SliceDim(torch.autograd.Function):
         return _AllGatherDim.apply(g, ctx.group, ctx.dim), None, None
 
 
+class _SliceDimLocal(torch.autograd.Function):
+    """Forward: keep this rank's chunk along ``dim``; backward: that chunk's gradient, zeros elsewhere.
+
+    For replicated inputs whose parameter gradients are summed over the group afterwards (the embedding in front
+    of a sequence-parallel region): every rank contributes only the tokens it owns."""
+
+    @staticmethod
+    def forward(ctx, x, group, dim):
+        n, r = dist.get_world_size(group), dist.get_rank(group)
+        ctx.n, ctx.r, ctx.dim = n, r, dim
+        return x.chunk(n, dim=dim)[r].contiguous()
+
+    @staticmethod
+    def backward(ctx, g):
+        shape = list(g.shape)
+        shape[ctx.dim] *= ctx.n
+        full = g.new_zeros(shape)
+        full.narrow(ctx.dim, ctx.r * g.shape[ctx.dim], g.shape[ctx.dim]).copy_(g)
+        return full, None, None
+
+
+class _AllGatherReplicated(torch.autograd.Function):
+    """Forward: all-gather along ``dim``; backward: this rank's slice of the gradient, without a reduction.
+
+    For results that feed a computation replicated over the group: every rank holds the same gradient of the
+    gathered tensor, so summing it would count the downstream loss once per rank."""
+
+    @staticmethod
+    def forward(ctx, x, group, dim):
+        n, r = dist.get_world_size(group), dist.get_rank(group)
+        ctx.n, ctx.r, ctx.dim = n, r, dim
+        xt = x.movedim(dim, 0).contiguous()
+        out = torch.empty((n * xt.shape[0],) + tuple(xt.shape[1:]), dtype=x.dtype, device=x.device)
+        dist.all_gather_into_tensor(out, xt, group=group)
+        return out.movedim(0, dim)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g.chunk(ctx.n, dim=ctx.dim)[ctx.r].contiguous(), None, None
+
+
+def all_gather_replicated(x, group, dim):
+    return x if _world(group) == 1 else _AllGatherReplicated.apply(x, group, dim)
+
+
+def slice_dim_local(x, group, dim):
+    return x if _world(group) == 1 else _SliceDimLocal.apply(x, group, dim)
+
+
 def all_gather_dim(x, group, dim):
     return x if _world(group) == 1 else _AllGatherDim.apply(x, group, dim)
 
@@ -195,7 +244,7 @@ class ExecutionContext:
     def scatter_sequence(self, x: torch.Tensor) -> torch.Tensor:
         """Replicated ``[B,S,H]`` -> this rank's ``[B,S/tp,H]`` (start of the sequence-parallel region)."""
 
-        return slice_dim(x, self.tp_group, 1) if self.sp else x
+        return slice_dim_local(x, self.tp_group, 1) if self.sp else x
 
     def gather_sequence(self, x: torch.Tensor) -> torch.Tensor:
         """Before a column-parallel projection: SP shard -> full sequence (or mark the replicated input)."""

@@ -68,7 +68,7 @@ class Optimizer:
         axes = []
         if sec.shard_axis is not None and self.mesh.size(sec.shard_axis) > 1:
             axes.append(sec.shard_axis)
-        if self.tp_size > 1 and "tp" not in sec.reduce_axes:
+        if self.tp_size > 1 and sec.entries and any(m.tp_axis is not None for m in sec.entries[0].metas):
             axes.append("tp")
         ep_axis = self.store.ep_axis
         if ep_axis and self.mesh.size(ep_axis) > 1 and any(e.is_expert for e in sec.entries) and ep_axis not in axes:

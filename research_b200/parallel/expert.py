@@ -53,6 +53,27 @@ def dispatch_and_combine(experts, x: torch.Tensor, expert_ids: torch.Tensor, wei
     ep = ex.ep_size
     if ep == 1:
         return _local_dispatch(experts, x, expert_ids, weights, num_experts)
+    if ex.ep_axis_sharing == "dedicated_ep" and not ex.extras.get("_ep_sliced"):
+        # With a dedicated ``ep`` axis everything outside the routed experts is replicated over it: split the
+        # tokens over the axis for the dispatch (the reference slices the sequence inside its shard_map,
+        # components/moe.py:538-696) and gather the results back.
+        from research_b200.models.execution import all_gather_replicated, slice_dim
+
+        T = x.shape[0]
+        pad = (-T) % ep
+        if pad:
+            x = torch.cat([x, x.new_zeros(pad, x.shape[1])])
+            expert_ids = torch.cat([expert_ids, expert_ids.new_zeros(pad, expert_ids.shape[1])])
+            weights = torch.cat([weights, weights.new_zeros(pad, weights.shape[1])])
+        ex.extras["_ep_sliced"] = True
+        try:
+            y = dispatch_and_combine(experts, slice_dim(x, ex.ep_group, 0),
+                                     expert_ids.chunk(ep, dim=0)[ex.ep_rank].contiguous(),
+                                     slice_dim(weights, ex.ep_group, 0), num_experts=num_experts, ex=ex)
+        finally:
+            ex.extras["_ep_sliced"] = False
+        y = all_gather_replicated(y, ex.ep_group, 0)
+        return y[:T] if pad else y
     group = ex.ep_group
     rank = ex.ep_rank
     e_local = num_experts // ep

@@ -116,8 +116,12 @@ class ParamStore:
     def _layout(self) -> None:
         sections: dict[tuple, Section] = {}
         order = {"adamw": 0, "muon": 1, "dion2": 2, "frozen": 3}
-        for e in sorted(self.entries, key=lambda e: (order[e.backend], e.reduce_axes, str(e.shard_axis))):
-            key = (e.backend, e.reduce_axes, e.shard_axis)
+        tp_sharded = lambda e: any(m.tp_axis is not None for m in e.metas)  # noqa: E731
+        for e in sorted(self.entries, key=lambda e: (order[e.backend], e.reduce_axes, str(e.shard_axis),
+                                                     e.is_expert, tp_sharded(e))):
+            # expert and tensor-parallel-sharded parameters are disjoint across their axis, the rest is replicated:
+            # they must not share a section because norms are summed per section
+            key = (e.backend, e.reduce_axes, e.shard_axis, e.is_expert, tp_sharded(e))
             sections.setdefault(key, Section(key, e.backend, e.reduce_axes, e.shard_axis)).entries.append(e)
         cursor = 0
         self.sections: list[Section] = []

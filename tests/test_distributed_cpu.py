@@ -1,0 +1,55 @@
+"""Parity of distributed layouts against one process, on CPU ranks over gloo (the reference checks the same
+thing on four fake devices: tests/jaxtitan/test_train_step.py:943-1051): same global batch, same token count,
+loss sums within 1e-4 and the whole updated parameter tree close after a few optimizer steps."""
+
+import pytest
+import torch
+
+from tests.helpers import run_gloo, tiny_dataset, tiny_raw_config, train_and_collect
+
+STEPS = 3
+
+
+def _single(raw):
+    from research_b200.parallel import mesh  # noqa: F401
+
+    return train_and_collect(0, 1, raw, STEPS)
+
+
+def _compare(ref, got, tol=2e-4):
+    assert ref["token_count"] == got["token_count"]
+    for a, b in zip(ref["loss_sum"], got["loss_sum"]):
+        assert abs(a - b) <= 1e-3 * max(1.0, abs(a)), (ref["loss_sum"], got["loss_sum"])
+    for name, want in ref["model"].items():
+        have = got["model"][name]
+        assert have.shape == want.shape, name
+        err = (have - want).abs().max().item()
+        assert err <= tol * (1.0 + want.abs().max().item()), (name, err)
+
+
+CASES = [
+    ("ddp2", "decoder", "adamw", {"data": 2}, {"mode": "ddp"}),
+    ("zero2", "decoder", "adamw", {"fsdp": 2}, {"mode": "zero2"}),
+    ("fsdp2_muon", "decoder", "muon", {"fsdp": 2}, {"mode": "fsdp"}),
+    ("tp2", "decoder", "adamw", {"tp": 2}, {"mode": "ddp", "tensor_parallel": True}),
+    ("tp2_muon_duplicated", "decoder", "muon", {"tp": 2}, {"mode": "ddp", "tensor_parallel": True}),
+    ("cp2", "decoder", "adamw", {"cp": 2}, {"mode": "ddp", "context_parallel": True}),
+    ("ep2_moe", "trinity", "adamw", {"ep": 2}, {"mode": "ddp", "expert_parallel": True}),
+    ("fsdp2_folded_ep_moe", "trinity", "adamw", {"fsdp": 2}, {"mode": "fsdp", "expert_parallel": True}),
+]
+
+
+@pytest.mark.parametrize("name,kind,optimizer,mesh,parallelism", CASES, ids=[c[0] for c in CASES])
+def test_layout_matches_single_process(tmp_path, name, kind, optimizer, mesh, parallelism):
+    manifest = tiny_dataset(tmp_path)
+    base = tiny_raw_config(manifest, kind=kind, optimizer=optimizer, steps=STEPS + 1)
+    ref = _single(base)
+    raw = tiny_raw_config(manifest, kind=kind, optimizer=optimizer, mesh=mesh, parallelism=parallelism,
+                          steps=STEPS + 1)
+    results = run_gloo(2, train_and_collect, raw, STEPS)
+    tol = 2e-3 if optimizer == "muon" else 2e-4
+    for got in results:
+        _compare(ref, got, tol)
+    # every rank ends with the same logical parameters
+    for name_, t in results[0]["model"].items():
+        assert torch.equal(t, results[1]["model"][name_]), name_
