@@ -1,0 +1,189 @@
+"""Prepared-token manifests and the deterministic pipelines."""
+
+import json
+import struct
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from research_b200.data import (build_prepared_token_pipeline, generate_synthetic_dataset, read_token_range,
+                                validate_dataset_manifest)
+from research_b200.errors import ContractError
+from tests.helpers import tiny_dataset
+
+
+def naive_document_buffer(tokens, offsets, split, seq_len, batch_size, seed, buffer_size, refill_size, batches):
+    """Straight restatement of the reference packer (src/jaxtitan/data/pipeline.py:528-704) on Python lists."""
+
+    start, end = split
+    spans = {}
+    for d in range(len(offsets) - 1):
+        a, b = max(int(offsets[d]), start), min(int(offsets[d + 1]), end)
+        if b > a:
+            spans[d] = (a, b)
+    ids = list(spans)
+    rng = np.random.default_rng(seed)
+    order = [int(v) for v in rng.permutation(np.asarray(ids, dtype=np.int64)).tolist()]
+    cursor, queue, active = 0, [], []
+
+    def fill():
+        nonlocal cursor, queue
+        while len(active) < min(buffer_size, len(ids)):
+            if not queue:
+                if cursor >= len(order):
+                    return
+                stop = min(cursor + refill_size, len(order))
+                queue = order[cursor:stop]
+                cursor = stop
+            d = queue.pop(0)
+            active.append({"doc_id": d, "cursor": spans[d][0], "end": spans[d][1]})
+
+    fill()
+    out = []
+    for _ in range(batches):
+        rows = []
+        for _ in range(batch_size):
+            vals, docs = [], []
+            while len(vals) < seq_len + 1:
+                fill()
+                i = int(rng.integers(0, len(active)))
+                a = active[i]
+                take = min(seq_len + 1 - len(vals), a["end"] - a["cursor"])
+                vals.extend(int(v) for v in tokens[a["cursor"]:a["cursor"] + take])
+                docs.extend([a["doc_id"]] * take)
+                a["cursor"] += take
+                if a["cursor"] >= a["end"]:
+                    del active[i]
+            rows.append((vals, docs))
+        out.append(rows)
+    return out
+
+
+def test_document_buffer_matches_reference_algorithm(tmp_path):
+    manifest_path = tiny_dataset(tmp_path)
+    manifest = validate_dataset_manifest(manifest_path, verify_checksums=True)
+    tokens = read_token_range(manifest, 0, manifest.num_tokens)
+    offsets = np.fromfile(manifest.data_dir / "document_offsets.u64", dtype="<u8")
+    pipe = build_prepared_token_pipeline(manifest_path, tokenizer_id=None, split="train", seq_len=24, batch_size=3,
+                                         order="document_buffer", shuffle_seed=11, document_buffer_size=5,
+                                         document_refill_size=3)
+    want = naive_document_buffer(tokens, offsets, (manifest.train.start, manifest.train.end), 24, 3, 11, 5, 3, 6)
+    state = pipe.initial_state()
+    for rows in want:
+        pb = pipe.next_batch(state)
+        state = pb.state
+        for r, (vals, docs) in enumerate(rows):
+            assert pb.batch.input_ids[r].tolist() == vals[:-1]
+            assert pb.batch.target_ids[r].tolist() == vals[1:]
+            assert pb.batch.loss_mask[r].tolist() == [docs[i] == docs[i + 1] for i in range(24)]
+            assert pb.batch.token_doc_ids[r].tolist() == docs[:-1]
+
+
+@pytest.mark.parametrize("order", ["sequential", "shuffle", "document_buffer"])
+def test_state_roundtrip_gives_the_same_next_batch(tmp_path, order):
+    manifest_path = tiny_dataset(tmp_path)
+    kw = dict(tokenizer_id="synthetic-uniform", split="train", seq_len=16, batch_size=4, order=order)
+    if order != "sequential":
+        kw["shuffle_seed"] = 3
+    if order == "document_buffer":
+        kw.update(document_buffer_size=8, document_refill_size=4)
+    pipe = build_prepared_token_pipeline(manifest_path, **kw)
+    s = pipe.initial_state()
+    s = pipe.next_batch(s).state
+    again = pipe.state_from_json(json.loads(json.dumps(pipe.state_to_json(s))))
+    a, b = pipe.next_batch(s), pipe.next_batch(again)
+    assert np.array_equal(a.batch.input_ids, b.batch.input_ids)
+    assert a.state == b.state
+    other = build_prepared_token_pipeline(manifest_path, **{**kw, "seq_len": 8})
+    with pytest.raises(ContractError, match="data pipeline state seq_len mismatch"):
+        other.state_from_json(pipe.state_to_json(s))
+
+
+def test_sequential_windows_and_exhaustion(tmp_path):
+    manifest_path = tiny_dataset(tmp_path, documents=40)
+    manifest = validate_dataset_manifest(manifest_path)
+    pipe = build_prepared_token_pipeline(manifest_path, tokenizer_id=None, split="val", seq_len=16, batch_size=2)
+    s = pipe.initial_state()
+    pb = pipe.next_batch(s)
+    start = manifest.val.start
+    want = read_token_range(manifest, start, start + 17)
+    assert pb.batch.input_ids[0].tolist() == want[:-1].tolist()
+    assert pb.provenance.row_start_offsets == (start, start + 16)
+    with pytest.raises(StopIteration):
+        for _ in range(10_000):
+            s = pipe.next_batch(s).state
+
+
+def _corrupt(path: Path, fn):
+    raw = json.loads(path.read_text())
+    fn(raw)
+    path.write_text(json.dumps(raw))
+
+
+@pytest.mark.parametrize("fn,message", [
+    (lambda r: r.update(kind="tokens"), "kind must be training_tokens"),
+    (lambda r: r.update(dtype="uint16"), "dtype must be uint32"),
+    (lambda r: r["shards"][0].update(start=1), "shards must be contiguous"),
+    (lambda r: r["shards"][0].update(path="/abs.bin"), "path must be relative"),
+    (lambda r: r["shards"][0].update(path="../x.bin"), "must stay inside the manifest directory"),
+    (lambda r: r["splits"]["val"].update(start=0, tokens=r["splits"]["val"]["end"]), "train/val splits overlap"),
+    (lambda r: r.update(num_tokens=5), "does not match shard total"),
+    (lambda r: r["documents"].update(count=3), "does not match documents.count"),
+    (lambda r: r["files"].pop("document_offsets"), "documents metadata requires files.document_offsets"),
+])
+def test_manifest_corruptions_are_rejected(tmp_path, fn, message):
+    manifest_path = tiny_dataset(tmp_path, documents=30)
+    _corrupt(manifest_path, fn)
+    with pytest.raises(ContractError, match=message):
+        validate_dataset_manifest(manifest_path)
+
+
+def test_checksum_and_tokenizer_mismatch(tmp_path):
+    manifest_path = tiny_dataset(tmp_path, documents=30)
+    with pytest.raises(ContractError, match="does not match config tokenizer"):
+        validate_dataset_manifest(manifest_path, tokenizer_id="gpt2")
+    shard = manifest_path.parent / "tokens-00000.bin"
+    data = bytearray(shard.read_bytes())
+    data[0:4] = struct.pack("<I", 7)
+    shard.write_bytes(bytes(data))
+    validate_dataset_manifest(manifest_path)
+    with pytest.raises(ContractError, match="checksum mismatch"):
+        validate_dataset_manifest(manifest_path, verify_checksums=True)
+
+
+def test_prepare_text_source_with_byte_tokenizer(tmp_path):
+    from research_b200.data.prepare import prepare_dataset
+
+    (tmp_path / "corpus.txt").write_text("\n".join(f"document number {i} says hello" for i in range(200)))
+    cfg = tmp_path / "prep.toml"
+    cfg.write_text('[source]\ntype = "text"\npaths = ["corpus.txt"]\n[tokenizer]\nname = "byte-level"\n'
+                   '[output]\npath = "%s"\nmax_tokens = 4000\nval_fraction = 0.1\nshard_tokens = 1500\n'
+                   '[tokenization]\nworkers = 1\n' % (tmp_path / "out").as_posix())
+    summary = prepare_dataset(cfg)
+    assert summary["num_tokens"] == 4000 and summary["shard_count"] == 3 and summary["document_aware"]
+    manifest = validate_dataset_manifest(tmp_path / "out" / "manifest.json", tokenizer_id="byte-level",
+                                         verify_checksums=True)
+    assert manifest.train.end == manifest.val.start
+    with pytest.raises(ContractError, match="already exists"):
+        prepare_dataset(cfg)
+
+
+def test_native_window_gather_matches_numpy(tmp_path):
+    from research_b200.native import hostlib
+
+    if hostlib.load() is None:
+        pytest.skip("host library not built")
+    manifest_path = generate_synthetic_dataset(tmp_path / "multi", seed=1, num_documents=50, mean_length=100,
+                                               min_length=8, max_length=300, vocab_size=300, eos_id=299,
+                                               shard_tokens=1000)
+    manifest = validate_dataset_manifest(manifest_path)
+    shards = [np.fromfile(manifest.data_dir / s.path, dtype="<u4") for s in manifest.shards]
+    bounds = [s.start for s in manifest.shards] + [manifest.num_tokens]
+    starts = np.asarray([0, 990, 1500, 2995], dtype=np.int64)
+    inp = np.zeros((4, 32), dtype=np.int32)
+    tgt = np.zeros((4, 32), dtype=np.int32)
+    assert hostlib.gather_windows(shards, bounds, starts, 33, inp, tgt)
+    for r, s in enumerate(starts):
+        want = read_token_range(manifest, int(s), int(s) + 33).astype(np.int32)
+        assert np.array_equal(inp[r], want[:-1]) and np.array_equal(tgt[r], want[1:])

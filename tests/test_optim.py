@@ -1,0 +1,104 @@
+"""Schedules, orthogonalisation, Dion2 selection, routing, AdamW against torch."""
+
+import math
+
+import pytest
+import torch
+
+from research_b200.config import run_spec_from_mapping
+from research_b200.config.specs import OptimizerSpec, ParamRouteRule, ScheduleSpec
+from research_b200.errors import ContractError
+from research_b200.models.build import build_model
+from research_b200.optim import orthogonalize as orth
+from research_b200.optim.build import build_optimizer, optimizer_policy_summary, route_assignments
+from research_b200.optim.schedules import build_lr_schedule
+from tests.helpers import tiny_raw_config
+from pathlib import Path
+
+
+def test_schedules():
+    const = build_lr_schedule(ScheduleSpec(peak_lr=1.0, warmup_steps=4))
+    assert [const(i) for i in range(6)] == [0.25, 0.5, 0.75, 1.0, 1.0, 1.0]
+    cos = build_lr_schedule(ScheduleSpec(peak_lr=1.0, name="cosine", warmup_steps=2, total_steps=6, min_lr_ratio=0.1))
+    assert cos(0) == 0.5 and cos(1) == 1.0 and cos(2) == pytest.approx(1.0)
+    assert cos(5) == pytest.approx(0.1) and cos(100) == pytest.approx(0.1)
+    assert cos(3) == pytest.approx(0.1 + 0.9 * 0.5 * (1 + math.cos(math.pi / 3)))
+    wsd = build_lr_schedule(ScheduleSpec(peak_lr=2.0, name="wsd", warmup_steps=1, stable_steps=2, total_steps=6))
+    assert [round(wsd(i), 6) for i in range(3)] == [2.0, 2.0, 2.0] and wsd(5) == pytest.approx(0.0)
+    with pytest.raises(ContractError, match="total_steps is required"):
+        build_lr_schedule(ScheduleSpec(peak_lr=1.0, name="cosine"))
+
+
+@pytest.mark.parametrize("shape", [(48, 96), (96, 48), (3, 32, 64)])
+def test_newton_schulz_pushes_singular_values_towards_one(shape):
+    torch.manual_seed(0)
+    x = torch.randn(shape)
+    o = orth.zeropower_via_newton_schulz(x, precision="float32")
+    s = torch.linalg.svdvals(o)
+    assert s.max() < 1.3 and s.min() > 0.5
+    # transposition commutes with the iteration (storage is [out, in], the reference's is [in, out])
+    ot = orth.zeropower_via_newton_schulz(x.transpose(-1, -2).contiguous(), precision="float32")
+    assert torch.allclose(ot.transpose(-1, -2), o, atol=1e-4)
+
+
+def test_polar_express_and_dion2_selection():
+    torch.manual_seed(1)
+    x = torch.randn(32, 80)
+    s = torch.linalg.svdvals(orth.polar_express(x).float())
+    assert s.max() < 1.3 and s.min() > 0.4
+    m = torch.zeros(8, 4)
+    m[2] = 5.0
+    m[5] = -3.0
+    rows, idx = orth.select_dion2_slices(m, select_axis=0)
+    assert sorted(idx.tolist()) == [2, 5] and rows.shape == (2, 4)
+    cols, cidx = orth.select_dion2_slices(m.t().contiguous(), select_axis=1)
+    assert sorted(cidx.tolist()) == [2, 5] and cols.shape == (4, 2)
+    with pytest.raises(ValueError):
+        orth.select_dion2_slices(m, select_axis=2)
+    assert orth.rms_match_scale((64, 256)) == pytest.approx(0.2 * 16.0)
+
+
+def test_routing_by_tag():
+    spec = run_spec_from_mapping(tiny_raw_config(Path("m.json"), kind="trinity", optimizer="muon"))
+    res = build_model(spec.model, seed=0)
+    built = build_optimizer(spec.optimizer, res.metadata)
+    by = {a.name: a for a in built.route_assignments}
+    assert by["embed.embedding"].backend == "adamw" and by["embed.embedding"].fallback_reason == "embedding"
+    assert by["lm_head.kernel"].backend == "adamw" and by["norm.scale"].fallback_reason == "norm"
+    assert by["layers.0.attn.q.kernel"].backend == "muon" and by["layers.1.mlp.experts.gate"].backend == "muon"
+    assert by["layers.1.mlp.router.proj.kernel"].backend == "adamw"
+    assert by["layers.1.mlp.expert_bias"].weight_decay is False
+    summary = optimizer_policy_summary(built)
+    assert summary["backend_parameter_counts"]["muon"] > 0 and summary["muon"]["newton_schulz_steps"] == 5
+    tp = route_assignments(spec.optimizer, res.metadata, tp_size=2)
+    assert {a.name: a for a in tp}["layers.0.attn.o.kernel"].backend == "dist_muon"
+    dion = build_optimizer(OptimizerSpec(name="dion", schedule=ScheduleSpec(peak_lr=1e-3)), res.metadata)
+    assert {a.name: a for a in dion.route_assignments}["layers.0.mlp.down.kernel"].backend == "dion2"
+    with pytest.raises(ContractError, match="does not match any model parameter"):
+        route_assignments(OptimizerSpec(name="adamw", schedule=ScheduleSpec(peak_lr=1e-3),
+                                        route_rules=(ParamRouteRule("nope", "adamw"),)), res.metadata)
+    with pytest.raises(ContractError, match="no runtime adapter"):
+        build_optimizer(OptimizerSpec(name="soap", schedule=ScheduleSpec(peak_lr=1e-3)), res.metadata)
+
+
+def test_adamw_step_matches_torch(tmp_path):
+    from tests.helpers import tiny_dataset
+    from research_b200.runtime.trainer import Trainer
+
+    manifest = tiny_dataset(tmp_path)
+    raw = tiny_raw_config(manifest, clip=None)
+    raw["optimizer"]["schedule"] = {"peak_lr": 1e-2}
+    trainer = Trainer(run_spec_from_mapping(raw), device="cpu")
+    params = [e.param for e in trainer.store.entries]
+    ref = [p.detach().clone().requires_grad_(True) for p in params]
+    opt = torch.optim.AdamW(ref, lr=1e-2, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.01)
+    for _ in range(2):
+        trainer.store.zero_grads()
+        for p, r in zip(params, ref):
+            g = torch.randn_like(p)
+            p.main_grad.copy_(g)
+            r.grad = g.clone()
+        trainer.optimizer.step()
+        opt.step()
+    for p, r in zip(params, ref):
+        assert torch.allclose(p, r, atol=1e-6, rtol=1e-5)
