@@ -89,6 +89,10 @@ def _declare(lib: ctypes.CDLL) -> None:
         c_int, c_int, c_int, c_void_p, c_void_p, c_void_p)
     sig("b200_gemm_bf16_grouped_k", c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_ll,
         c_int, c_int, c_void_p, c_void_p, c_void_p)
+    sig("b200_muon_momentum", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_float, c_int, c_void_p)
+    sig("b200_muon_apply", c_void_p, c_void_p, c_void_p, c_ll, c_float, c_float, c_void_p)
+    sig("b200_scale_by_inv_norm", c_void_p, c_void_p, c_ll, c_int, c_float, c_void_p)
+    sig("b200_affine_identity", c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p)
     sig("b200_attn_fwd", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
         c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_float, c_int, c_ll, c_void_p, c_void_p)
     sig("b200_attn_bwd", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -418,3 +422,41 @@ def attn_bwd(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor,
     _check(rc, "b200_attn_bwd")
     LAUNCHES += 2
     return dq, dk, dv
+
+
+# --------------------------------------------------------------------------------------------------
+# Muon element-wise stages
+# --------------------------------------------------------------------------------------------------
+def muon_momentum(g: torch.Tensor, m: torch.Tensor, u: torch.Tensor, sumsq_slot: torch.Tensor,
+                  clip: torch.Tensor | None, beta: float, nesterov: bool) -> None:
+    """g, m: fp32 contiguous; u: bf16 contiguous (same numel); sumsq_slot: 1-element fp32 accumulator."""
+
+    lib = load()
+    _check(lib.b200_muon_momentum(g.data_ptr(), m.data_ptr(), u.data_ptr(), sumsq_slot.data_ptr(), _ptr(clip),
+                                  g.numel(), beta, int(nesterov), _stream()), "b200_muon_momentum")
+
+
+def muon_apply(w: torch.Tensor, o: torch.Tensor, shadow: torch.Tensor | None, decay: float, step: float) -> None:
+    lib = load()
+    _check(lib.b200_muon_apply(w.data_ptr(), o.data_ptr(), _ptr(shadow), w.numel(), decay, step, _stream()),
+           "b200_muon_apply")
+
+
+def scale_by_inv_norm(x: torch.Tensor, sumsq_vec: torch.Tensor, eps: float) -> None:
+    """x: [batch, ...] bf16 contiguous; every slab is divided by max(sqrt(sumsq[b]), eps)."""
+
+    lib = load()
+    batch = x.shape[0]
+    _check(lib.b200_scale_by_inv_norm(x.data_ptr(), sumsq_vec.data_ptr(), x.numel() // batch, batch, eps, _stream()),
+           "b200_scale_by_inv_norm")
+
+
+def affine_identity(a: torch.Tensor, alpha: float, beta: float, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``alpha * I + beta * a`` for a stack of square bf16 matrices ``[batch, d, d]``."""
+
+    lib = load()
+    if out is None:
+        out = torch.empty_like(a)
+    _check(lib.b200_affine_identity(a.data_ptr(), out.data_ptr(), a.shape[-1], a.numel() // (a.shape[-1] ** 2), alpha,
+                                    beta, _stream()), "b200_affine_identity")
+    return out

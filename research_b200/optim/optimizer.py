@@ -120,9 +120,11 @@ class Optimizer:
             if sec.backend == "adamw":
                 self._adamw(i, sec, adamw_lr)
             elif sec.backend in ("muon", "dion2"):
-                for e in sec.entries:
-                    if store.owns(sec, e):
-                        self._matrix_entry(i, sec, e, lr)
+                slow = [e for e in sec.entries if store.owns(sec, e)]
+                if sec.backend == "muon" and self._fast_muon_ok():
+                    slow = self._muon_section_fast(i, sec, slow, lr)
+                for e in slow:
+                    self._matrix_entry(i, sec, e, lr)
         store.gather_compute_weights()
         self.count += 1
         out: dict[str, Any] = {"lr": lr, "adamw_lr": adamw_lr, "grad_norm": grad_norm, "clip_scale": self._clip[0]}
@@ -171,6 +173,59 @@ class Optimizer:
             store.compute_arena[lo:hi].copy_(p)
 
     # ---- matrix optimizers -------------------------------------------------------------------------
+    def _fast_muon_ok(self) -> bool:
+        return self.store.device.type == "cuda" and self.store.compute_dtype == torch.bfloat16
+
+    def _muon_section_fast(self, i: int, sec: Section, entries: list[StorageEntry], lr: float) -> list[StorageEntry]:
+        """Batched Muon for plain 2-D matrices: logical matrices of equal shape are stacked so that each
+        Newton-Schulz step is three batched GEMMs; returns the entries this path does not handle."""
+
+        store = self.store
+        lo, _ = store.local_master_range(sec)
+        leftovers: list[StorageEntry] = []
+        groups: dict[tuple[int, int], list[tuple[StorageEntry, Any, int, int]]] = {}
+        for e in entries:
+            master = store.master_view(sec, e)
+            simple = master is not None and master.dim() == 2 and e.numel % 4 == 0 and all(
+                self.routes[m.name].backend == "muon" for m in e.metas)
+            if not simple:
+                leftovers.append(e)
+                continue
+            cols = e.param.shape[1]
+            for meta in e.metas:
+                a, b = meta.rows if meta.rows is not None else (0, e.param.shape[0])
+                if (b - a) % 8 or cols % 8:
+                    simple = False
+            if not simple:
+                leftovers.append(e)
+                continue
+            for meta in e.metas:
+                a, b = meta.rows if meta.rows is not None else (0, e.param.shape[0])
+                groups.setdefault((b - a, cols), []).append((e, meta, a, b))
+        wd = float(self.spec.weight_decay)
+        mom_all = self.state[i]["momentum"]
+        for (rows, cols), items in groups.items():
+            n = len(items)
+            stack = native.scratch(f"muon_stack_{rows}x{cols}", n * rows * cols, torch.bfloat16, store.device)
+            stack = stack[: n * rows * cols].view(n, rows, cols)
+            sq = torch.zeros(n, dtype=torch.float32, device=store.device)
+            for k, (e, meta, a, b) in enumerate(items):
+                off = e.offset - lo + a * cols
+                cnt = rows * cols
+                g = store.grad_arena[e.offset + a * cols:e.offset + a * cols + cnt]
+                native.muon_momentum(g, mom_all[off:off + cnt], stack[k], sq[k:k + 1], self._clip, orth.MUON_MOMENTUM,
+                                     orth.MUON_NESTEROV)
+            native.scale_by_inv_norm(stack, sq, orth.MUON_NS_EPS)
+            out = orth.newton_schulz_stack_(stack)
+            step = lr * orth.rms_match_scale((rows, cols))
+            for k, (e, meta, a, b) in enumerate(items):
+                off = e.offset - lo + a * cols
+                cnt = rows * cols
+                decay = 1.0 - lr * wd if self.routes[meta.name].weight_decay else 1.0
+                shadow = store.compute_arena[e.offset + a * cols:e.offset + a * cols + cnt]
+                native.muon_apply(sec.master[off:off + cnt], out[k], shadow, decay, step)
+        return leftovers
+
     def _matrix_entry(self, i: int, sec: Section, e: StorageEntry, lr: float) -> None:
         store = self.store
         master = store.master_view(sec, e)

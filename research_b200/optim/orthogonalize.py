@@ -66,6 +66,30 @@ def _iterate(x: torch.Tensor, coefficients) -> torch.Tensor:
     return x
 
 
+def newton_schulz_stack_(x: torch.Tensor, coefficients=None) -> torch.Tensor:
+    """Newton-Schulz on an already normalised bf16 stack ``[batch, m, n]`` with three batched tcgen05 GEMMs per step.
+
+    Uses ``a X + (b G + c G^2) X = ((b I + c G) G + a I) X`` so that no step needs an accumulate pass:
+    ``G = X X^T`` (or ``X^T X`` when tall), ``Q = (b I + c G) G``, ``X <- (Q + a I) X``.
+    """
+
+    coefficients = coefficients or (MUON_NS_COEFFICIENTS,) * MUON_NS_STEPS
+    tall = x.shape[-2] > x.shape[-1]
+    for a, b, c in coefficients:
+        if tall:
+            gram = native.gemm(x, x, trans_a=True, trans_b=False)
+        else:
+            gram = native.gemm(x, x, trans_b=True)
+        lhs = native.affine_identity(gram, b, c)                  # b I + c G
+        q = native.gemm(lhs, gram, trans_b=True)                  # G symmetric: (bI + cG) G^T = bG + cG^2
+        native.affine_identity(q, a, 1.0, out=q)                  # + a I
+        if tall:
+            x = native.gemm(x, q, trans_b=True)                   # X Q   (Q symmetric)
+        else:
+            x = native.gemm(q, x, trans_b=False)                  # Q X
+    return x
+
+
 def zeropower_via_newton_schulz(value: torch.Tensor, *, precision: str = MUON_NS_PRECISION) -> torch.Tensor:
     """Approximate ``U V^T`` of ``value = U S V^T`` (rank 2, or rank 3 = one matrix per expert)."""
 
