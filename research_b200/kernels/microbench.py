@@ -1,0 +1,138 @@
+"""Single-kernel micro-benchmarks with roofline fractions: ``python -m research_b200.kernels.microbench <op> ...``.
+
+Each case runs one native kernel on inputs larger than L2, times it with CUDA events after warm-up, and prints
+one JSON line with the achieved TFLOP/s or GB/s and the fraction of the measured peak (``MEASURED_PEAKS.json`` at
+the repository root when present, else 6.65 TB/s and 1.59 PFLOP/s).  The same command lines are what the ncu
+summaries under ``profiles/`` were captured with (``--iters`` small so that a capture ends by itself).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+from pathlib import Path
+
+import torch
+
+from research_b200.ops import native
+
+ROOT = Path(__file__).resolve().parent.parent.parent
+
+
+def peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        raw = json.loads(path.read_text())
+        return {"hbm_gbs": raw["hbm_gbs"], "bf16_tflops": raw["bf16_tflops"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def timed(fn, warmup: int, iters: int) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(iters):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters
+
+
+def bf(shape, scale=1.0):
+    return (torch.randn(shape, device="cuda") * scale).to(torch.bfloat16)
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("op", choices=["gemm", "attn_fwd", "attn_bwd", "rmsnorm", "swiglu", "ce", "adamw", "decode"])
+    ap.add_argument("--m", type=int, default=16384)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--layout", default="nt", choices=["nt", "nn", "tn"])
+    ap.add_argument("--batch", type=int, default=2)
+    ap.add_argument("--seq", type=int, default=4096)
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--rows", type=int, default=32768)
+    ap.add_argument("--hidden", type=int, default=2048)
+    ap.add_argument("--vocab", type=int, default=50304)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--iters", type=int, default=10)
+    args = ap.parse_args()
+    pk = peaks()
+    out: dict = {"op": args.op, "peaks": pk}
+    if args.op == "gemm":
+        M, N, K = args.m, args.n, args.k
+        if args.layout == "nt":
+            a, b = bf((M, K)), bf((N, K))
+            fn = lambda: native.gemm(a, b, out=c)
+        elif args.layout == "nn":
+            a, b = bf((M, K)), bf((K, N))
+            fn = lambda: native.gemm(a, b, trans_b=False, out=c)
+        else:
+            a, b = bf((K, M)), bf((K, N))
+            fn = lambda: native.gemm(a, b, trans_a=True, trans_b=False, out=c)
+        c = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        ms = timed(fn, args.warmup, args.iters)
+        tf = 2.0 * M * N * K / ms / 1e9
+        out.update(shape=[M, N, K], layout=args.layout, ms=ms, tflops=tf, frac_of_peak=tf / pk["bf16_tflops"])
+    elif args.op in ("attn_fwd", "attn_bwd"):
+        B, S, H, Hkv, D = args.batch, args.seq, args.heads, args.kv_heads, args.head_dim
+        q, k, v = bf((B, S, H, D)), bf((B, S, Hkv, D)), bf((B, S, Hkv, D))
+        d_o = bf((B, S, H, D))
+        o, lse = native.attn_fwd(q, k, v, causal=True)
+        if args.op == "attn_fwd":
+            ms = timed(lambda: native.attn_fwd(q, k, v, causal=True), args.warmup, args.iters)
+            flops = 4.0 * B * H * S * S * D / 2
+        else:
+            ms = timed(lambda: native.attn_bwd(q, k, v, o, d_o, lse, causal=True), args.warmup, args.iters)
+            flops = 10.0 * B * H * S * S * D / 2
+        tf = flops / ms / 1e9
+        out.update(shape=[B, S, H, Hkv, D], causal=True, ms=ms, tflops=tf, frac_of_peak=tf / pk["bf16_tflops"])
+    elif args.op == "rmsnorm":
+        x, w = bf((args.rows, args.hidden)), torch.ones(args.hidden, device="cuda")
+        ms = timed(lambda: native.rmsnorm_fwd(x, w, 1e-6), args.warmup, args.iters)
+        gbs = 2 * x.numel() * 2 / ms / 1e6
+        out.update(shape=[args.rows, args.hidden], ms=ms, gbs=gbs, frac_of_peak=gbs / pk["hbm_gbs"])
+    elif args.op == "swiglu":
+        gu = bf((args.rows, 2 * args.hidden))
+        ms = timed(lambda: native.swiglu_fwd(gu), args.warmup, args.iters)
+        gbs = 3 * args.rows * args.hidden * 2 / ms / 1e6
+        out.update(shape=[args.rows, args.hidden], ms=ms, gbs=gbs, frac_of_peak=gbs / pk["hbm_gbs"])
+    elif args.op == "ce":
+        rows = min(args.rows, 4096)
+        logits = bf((rows, args.vocab), 2.0)
+        tgt = torch.randint(0, args.vocab, (rows,), device="cuda", dtype=torch.int32)
+        mask = torch.ones(rows, device="cuda", dtype=torch.uint8)
+        ms = timed(lambda: native.ce_fwd_bwd(logits, tgt, mask, 1.0 / rows, 0.0), args.warmup, args.iters)
+        gbs = 2 * logits.numel() * 2 / ms / 1e6
+        out.update(shape=[rows, args.vocab], ms=ms, gbs=gbs, frac_of_peak=gbs / pk["hbm_gbs"],
+                   note="algorithmic bytes = one read + one write of the logits; the kernel reads the row three times")
+    elif args.op == "adamw":
+        n = args.rows * args.hidden
+        p, m, v = (torch.zeros(n, device="cuda") for _ in range(3))
+        g = torch.randn(n, device="cuda")
+        sh = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+        ms = timed(lambda: native.adamw(p, m, v, g, sh, None, 1e-3, 0.9, 0.999, 1e-8, 0.0, 1), args.warmup, args.iters)
+        gbs = n * (4 * 4 + 3 * 4 + 2) / ms / 1e6
+        out.update(elements=n, ms=ms, gbs=gbs, frac_of_peak=gbs / pk["hbm_gbs"])
+    elif args.op == "decode":
+        from research_b200.ops.decode import decode_attention
+
+        B, S, H, Hkv, D = args.batch, args.seq, args.heads, args.kv_heads, args.head_dim
+        q = bf((B, H, D))
+        kc, vc = bf((B, S, Hkv, D)), bf((B, S, Hkv, D))
+        lens = torch.full((B,), S, device="cuda", dtype=torch.int32)
+        ms = timed(lambda: decode_attention(q, kc, vc, lens, None), args.warmup, args.iters)
+        gbs = 2 * kc.numel() * 2 / ms / 1e6
+        out.update(shape=[B, S, H, Hkv, D], ms=ms, gbs=gbs, frac_of_peak=gbs / pk["hbm_gbs"])
+    native.check_status()
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -1,25 +1,35 @@
 // Flash attention backward for sm_100a (tcgen05 + TMEM + TMA): two kernels from one template.
 //
 //   dQ  kernel (DKV = false): a CTA keeps one 128-row query tile (Q_i, dO_i) resident and streams the
-//        kv blocks:  S = Q K^T,  dP = dO V^T,  dS = P o (dP - delta) * scale,  dQ += dS K.
+//        kv blocks:  S = Q K^T,  dP = dO V^T,  dS = P o (dP - delta),  dQ = scale * sum dS K.
 //   dKV kernel (DKV = true) : a CTA keeps one 128-row kv tile (K_j, V_j) resident and streams the query
 //        blocks of every query head that shares the kv head, working on transposed tiles so that the
-//        thread-per-row softmax math lines up with kv rows:
-//        S^T = K Q^T,  dP^T = V dO^T,  P^T -> dV += P^T dO,  dS^T = P^T o (dP^T - delta) * scale -> dK += dS^T Q.
+//        thread-per-row math lines up with kv rows:
+//        S^T = K Q^T,  dP^T = V dO^T,  dV = sum P^T dO,  dS^T = P^T o (dP^T - delta),  dK = scale * sum dS^T Q.
 // Both recompute P from the saved log-sum-exp, so no atomics are needed and results are deterministic.
 //
-// Roles: warp 0 TMA producer (resident tiles once, stream operands through a 4-slot ring), warp 1 MMA
+// Roles: warp 0 TMA producer (resident tiles once, streamed operands through a 4-slot ring), warp 1 MMA
 // issuer, warps 2-9 element-wise stage: warp w owns TMEM lane quadrant w % 4 and one 64-column half of
-// the 128 x 128 score tile, so two warps share each row.  P / dS go to 128-byte swizzled shared memory as
-// the K-major A operand of the accumulate MMAs; the streamed operand is consumed a second time as an
-// MN-major B operand straight from its ring slot (no transposed copy).
+// the 128 x 128 score tile, so two warps share each row.
+//
+// Software pipeline: the score MMA of block n+1 is issued as soon as the element-wise warps have copied
+// S(n) out of tensor memory, so the tensor pipe works on block n+1 while block n's exponentials run.
+// dS goes back to tensor memory as packed bf16 (in place over dP in the dKV kernel, where all 512 columns
+// are taken) and is the A operand of the accumulate MMA straight from there; only P^T of the dKV kernel
+// takes the trip through 128-byte swizzled shared memory.  The streamed operand is consumed a second time
+// as an MN-major B operand from its ring slot (no transposed copy).  Per-query statistics of the dKV
+// kernel (lse, delta of the streamed block) are staged through a small double-buffered shared array one
+// block ahead.
 //
 // Masks as in the forward kernel: query row q sees kv positions [lo[q], q] (causal) or [lo[q], S).
-// `hi` (int32 [B,S], non-decreasing) is the kv-side view: the last query position that can see kv k.
+// `hi` (int32 [B,Skv], non-decreasing) is the kv-side view: the last query position that can see kv k;
+// the dKV kernel masks with it alone, so it must be given whenever `lo` is.
 //
 // Oracle: autograd of softmax(QK^T * scale) V in fp32 (reference attention:
 // models/components/attention.py:269-278).  The reference's only hand-written backward is Hopper wgmma
 // (third_party/ThunderKittens/kernels/attention/mha_h100/mha_h100.cu:254-483).
+#include <math_constants.h>
+
 #include "b200.cuh"
 #include "host_util.cuh"
 
@@ -36,11 +46,12 @@ constexpr float kLog2e = 1.4426950408889634f;
 template <int D>
 struct BwdSmem {
   static constexpr int TILE_BYTES = TILE * D * 2;
-  static constexpr int BUF_BYTES = TILE * TILE * 2;  // P / dS staging, also the epilogue staging
+  static constexpr int BUF_BYTES = TILE * TILE * 2;  // P^T staging (dKV), also the epilogue staging
   static constexpr int X_OFF = 0;                    // two resident tiles
   static constexpr int RING_OFF = X_OFF + 2 * TILE_BYTES;
   static constexpr int BUF_OFF = RING_OFF + RING * TILE_BYTES;
-  static constexpr int BAR_OFF = BUF_OFF + BUF_BYTES;
+  static constexpr int STAT_OFF = BUF_OFF + BUF_BYTES;  // [2][lse2[128], delta[128]] fp32
+  static constexpr int BAR_OFF = STAT_OFF + 2 * 2 * TILE * 4;
   static constexpr int TOTAL = BAR_OFF + 256;
 };
 
@@ -48,8 +59,8 @@ struct BwdParams {
   int B, S, Skv, q_off, Hq, Hkv;  // S = query rows, Skv = kv rows, q_off = global position of query row 0
   int causal;
   float scale;
-  const int* lo;       // [B,S] or nullptr
-  const int* hi;       // [B,S] or nullptr (dKV kernel)
+  const int* lo;       // [B,S] or nullptr (dQ kernel)
+  const int* hi;       // [B,Skv] or nullptr (dKV kernel)
   const float* lse;    // [B,Hq,S]
   const float* delta;  // [B,Hq,S]
   int* status;
@@ -63,18 +74,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
                 const BwdParams p) {
   using L = BwdSmem<D>;
   constexpr int NBOX = D / 64;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // The swizzled tiles need 1024-byte alignment and the budget has no room for a round-up, so the
+  // alignment of the dynamic window is checked instead of assumed.
+  extern __shared__ __align__(1024) uint8_t smem[];
+  if (smem_u32(smem) & 1023u) {
+    if (threadIdx.x == 0) atomicCAS(p.status, 0, ERR_BAD_ARG);
+    return;
+  }
   uint64_t* x_full = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   uint64_t* full = x_full + 1;
   uint64_t* empty = full + RING;
-  uint64_t* t_full = empty + RING;
-  uint64_t* t_free = t_full + 1;
-  uint64_t* p_ready = t_free + 1;
-  uint64_t* dv_done = p_ready + 1;
-  uint64_t* ds_ready = dv_done + 1;
-  uint64_t* acc_done = ds_ready + 1;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_done + 1);
+  uint64_t* s_full = empty + RING;     // S(n) is in tensor memory
+  uint64_t* dp_full = s_full + 1;      // dP(n) is in tensor memory
+  uint64_t* t1_free = dp_full + 1;     // S(n) has been copied out
+  uint64_t* p_ready = t1_free + 1;     // P^T(n) is in shared memory (dKV)
+  uint64_t* dv_done = p_ready + 1;     // the MMA that read P^T(n) has finished (dKV)
+  uint64_t* ds_ready = dv_done + 1;    // dS(n) is in tensor memory
+  uint64_t* acc_done = ds_ready + 1;   // every MMA has finished
+  uint64_t* stat_ready = acc_done + 1; // statistics of block n are in shared memory (dKV)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(stat_ready + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const AbortCtx ab{abort_flag, p.status};
 
@@ -85,36 +103,40 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
   const int kv_tiles = (p.Skv + TILE - 1) / TILE;
   const int tiles = DKV ? kv_tiles : q_tiles;  // resident tiles per (batch, head)
 
-  // ---- which resident tile, which stream range -------------------------------------------------
+  // ---- which resident tile, which stream range.  Tiles are handed out heaviest first over the whole
+  //      grid (all heads of the longest tile, then the next), which balances the tail. ----------------
   int b, h_res, r0;            // batch, head of the resident tile, first row of the resident tile
   int blk_begin, blk_count;    // streamed block range (per query head for DKV)
   int n_total;                 // streamed blocks in total
-  if (!DKV) {
-    const int qt = tiles - 1 - (int)(blockIdx.x % tiles);  // heavy tiles first
-    const int bh = blockIdx.x / tiles;
-    h_res = bh % p.Hq;
-    b = bh / p.Hq;
-    r0 = qt * TILE;
-    blk_begin = p.lo ? p.lo[(long long)b * p.S + r0] / TILE : 0;
-    int end = kv_tiles;
-    if (p.causal) end = min(end, (p.q_off + min(r0 + TILE, p.S) - 1) / TILE + 1);
-    blk_count = max(end - blk_begin, 0);
-    n_total = blk_count;
-  } else {
-    const int kt = (int)(blockIdx.x % tiles);  // early kv tiles have the most query blocks
-    const int bh = blockIdx.x / tiles;
-    h_res = bh % p.Hkv;
-    b = bh / p.Hkv;
-    r0 = kt * TILE;
-    // query blocks are in local rows; a query row r sits at global position q_off + r
-    blk_begin = p.causal ? max(0, (r0 - p.q_off) / TILE) : 0;
-    int end = q_tiles;
-    if (p.hi) {
-      const int last_q = p.hi[(long long)b * p.Skv + min(r0 + TILE, p.Skv) - 1] - p.q_off;  // local row, may be < 0
-      end = last_q < 0 ? 0 : min(end, last_q / TILE + 1);
+  {
+    const int nbh = p.B * (DKV ? p.Hkv : p.Hq);
+    const int t_idx = (int)(blockIdx.x / nbh);
+    const int bh = (int)(blockIdx.x % nbh);
+    if (!DKV) {
+      const int qt = tiles - 1 - t_idx;
+      h_res = bh % p.Hq;
+      b = bh / p.Hq;
+      r0 = qt * TILE;
+      blk_begin = p.lo ? p.lo[(long long)b * p.S + r0] / TILE : 0;
+      int end = kv_tiles;
+      if (p.causal) end = min(end, (p.q_off + min(r0 + TILE, p.S) - 1) / TILE + 1);
+      blk_count = max(end - blk_begin, 0);
+      n_total = blk_count;
+    } else {
+      const int kt = t_idx;
+      h_res = bh % p.Hkv;
+      b = bh / p.Hkv;
+      r0 = kt * TILE;
+      // query blocks are in local rows; a query row r sits at global position q_off + r
+      blk_begin = p.causal ? max(0, (r0 - p.q_off) / TILE) : 0;
+      int end = q_tiles;
+      if (p.hi) {
+        const int last_q = p.hi[(long long)b * p.Skv + min(r0 + TILE, p.Skv) - 1] - p.q_off;  // local row, may be < 0
+        end = last_q < 0 ? 0 : min(end, last_q / TILE + 1);
+      }
+      blk_count = max(end - blk_begin, 0);
+      n_total = blk_count * G;
     }
-    blk_count = max(end - blk_begin, 0);
-    n_total = blk_count * G;
   }
   const int hkv = DKV ? h_res : h_res / G;
 
@@ -124,12 +146,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    mbar_init(t_full, 1);
-    mbar_init(t_free, EW_WARPS);
+    mbar_init(s_full, 1);
+    mbar_init(dp_full, 1);
+    mbar_init(t1_free, EW_WARPS);
     mbar_init(p_ready, EW_WARPS);
     mbar_init(dv_done, 1);
     mbar_init(ds_ready, EW_WARPS);
     mbar_init(acc_done, 1);
+    mbar_init(stat_ready, EW_WARPS);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -142,6 +166,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tm_T1 = tmem_base, tm_T2 = tmem_base + 128, tm_A1 = tmem_base + 256, tm_A2 = tmem_base + 256 + D;
+  // packed bf16 dS: warp half h writes 32 columns at tm_DS + 64 h.  The dKV kernel has no free columns
+  // and overwrites the first half of each warp's own dP columns; the dQ kernel uses the unused quarter.
+  const uint32_t tm_DS = DKV ? tm_T2 : tmem_base + 384;
 
   uint8_t* sX1 = smem + L::X_OFF;
   uint8_t* sX2 = sX1 + L::TILE_BYTES;
@@ -183,7 +210,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
     // ---------------------------------------------------------------- MMA issuer
     if (lane == 0 && n_total > 0) {
       constexpr uint32_t idesc_t = make_idesc_bf16(TILE, TILE, false, false);  // X * Y^T, both K-major over D
-      constexpr uint32_t idesc_a = make_idesc_bf16(TILE, D, false, true);      // buf (K-major) * Y (MN-major)
+      constexpr uint32_t idesc_a = make_idesc_bf16(TILE, D, false, true);      // K-major A * Y (MN-major)
+      auto ybuf = [&](int item) -> const uint8_t* { return smem + L::RING_OFF + (item % RING) * L::TILE_BYTES; };
+      auto ring_wait = [&](int item) { return mbar_wait(&full[item % RING], (item / RING) & 1, ab, ERR_WAIT_FULL); };
       auto issue_t = [&](uint32_t d_tmem, const uint8_t* x, const uint8_t* y) {
         const uint32_t a_base = smem_u32(x), b_base = smem_u32(y);
 #pragma unroll
@@ -193,7 +222,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
                     idesc_t, kk != 0 ? 1u : 0u);
         }
       };
-      auto issue_acc = [&](uint32_t d_tmem, const uint8_t* y, bool accumulate) {
+      // A = P^T in shared memory
+      auto issue_acc_ss = [&](uint32_t d_tmem, const uint8_t* y, bool accumulate) {
         const uint32_t a_base = smem_u32(sBuf), b_base = smem_u32(y);
 #pragma unroll
         for (int kk = 0; kk < TILE / 16; ++kk) {
@@ -202,47 +232,82 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
                     make_smem_desc_sw128(b_base + kk * 2048, 16384, 1024), idesc_a, (accumulate || kk != 0) ? 1u : 0u);
         }
       };
+      // A = packed dS in tensor memory: 16 K-elements are 8 columns; the two 64-element halves sit 64 columns apart
+      auto issue_acc_ts = [&](uint32_t d_tmem, const uint8_t* y, bool accumulate) {
+        const uint32_t b_base = smem_u32(y);
+#pragma unroll
+        for (int kk = 0; kk < TILE / 16; ++kk) {
+          tc_mma_ts(d_tmem, tm_DS + (kk >> 2) * 64 + (kk & 3) * 8, make_smem_desc_sw128(b_base + kk * 2048, 16384, 1024),
+                    idesc_a, (accumulate || kk != 0) ? 1u : 0u);
+        }
+      };
       bool ok = mbar_wait(x_full, 0, ab, ERR_WAIT_FULL);
+      if (ok) ok = ring_wait(0);
+      if (ok) {
+        tc_fence_after();
+        issue_t(tm_T1, sX1, ybuf(0));
+        tc_commit(s_full);
+        ok = ring_wait(1);
+      }
+      if (ok) {
+        issue_t(tm_T2, sX2, ybuf(1));
+        tc_commit(dp_full);
+        if (!DKV) tc_commit(&empty[1]);  // V is only read by dP
+      }
       for (int n = 0; n < n_total && ok; ++n) {
         const uint32_t ph = n & 1;
-        const int s1 = (2 * n) % RING, s2 = (2 * n + 1) % RING;
-        const uint32_t ring_ph = ((2 * n) / RING) & 1;
-        const uint8_t* y1 = smem + L::RING_OFF + s1 * L::TILE_BYTES;
-        const uint8_t* y2 = smem + L::RING_OFF + s2 * L::TILE_BYTES;
-        if (!mbar_wait(&full[s1], ring_ph, ab, ERR_WAIT_FULL)) { ok = false; break; }
-        if (!mbar_wait(&full[s2], ring_ph, ab, ERR_WAIT_FULL)) { ok = false; break; }
-        if (n > 0 && !mbar_wait(t_free, ph ^ 1, ab, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
-        tc_fence_after();
-        issue_t(tm_T1, sX1, y1);
-        issue_t(tm_T2, sX2, y2);
-        tc_commit(t_full);
-        if (!DKV) {
-          tc_commit(&empty[s2]);  // V is only read by dP
-        } else {
+        const bool has_next = n + 1 < n_total;
+        const int it_s = 2 * n + 2, it_p = 2 * n + 3;
+        bool s_issued = !has_next;
+        // S(n+1) ahead of everything else when its operands are already there
+        if (has_next && mbar_try_wait(&full[it_s % RING], (it_s / RING) & 1) && mbar_try_wait(t1_free, ph)) {
+          tc_fence_after();
+          issue_t(tm_T1, sX1, ybuf(it_s));
+          tc_commit(s_full);
+          s_issued = true;
+        }
+        if (DKV) {
           if (!mbar_wait(p_ready, ph, ab, ERR_WAIT_P_READY)) { ok = false; break; }
           tc_fence_after();
-          issue_acc(tm_A2, y2, n > 0);  // dV += P^T dO
+          issue_acc_ss(tm_A2, ybuf(2 * n + 1), n > 0);  // dV += P^T dO
           tc_commit(dv_done);
-          tc_commit(&empty[s2]);
+          tc_commit(&empty[(2 * n + 1) % RING]);
+        }
+        if (!s_issued) {
+          if (!ring_wait(it_s)) { ok = false; break; }
+          if (!mbar_wait(t1_free, ph, ab, ERR_WAIT_TMEM_EMPTY)) { ok = false; break; }
+          tc_fence_after();
+          issue_t(tm_T1, sX1, ybuf(it_s));
+          tc_commit(s_full);
         }
         if (!mbar_wait(ds_ready, ph, ab, ERR_WAIT_P_READY)) { ok = false; break; }
         tc_fence_after();
-        issue_acc(tm_A1, y1, n > 0);  // dQ += dS K   or   dK += dS^T Q
-        tc_commit(acc_done);
-        tc_commit(&empty[s1]);
+        issue_acc_ts(tm_A1, ybuf(2 * n), n > 0);  // dQ += dS K   or   dK += dS^T Q
+        tc_commit(&empty[(2 * n) % RING]);
+        if (has_next) {
+          // after the accumulate MMA in issue order: in the dKV kernel dP(n+1) overwrites the dS it read
+          if (!ring_wait(it_p)) { ok = false; break; }
+          issue_t(tm_T2, sX2, ybuf(it_p));
+          tc_commit(dp_full);
+          if (!DKV) tc_commit(&empty[it_p % RING]);
+        }
       }
+      if (ok) tc_commit(acc_done);
     }
   } else {
     // ---------------------------------------------------------------- element-wise stage + epilogue
     const int quad = warp & 3;
     const int half = (warp - 2) >> 2;
     const int row = quad * 32 + lane;
-    const int g_row = r0 + row;  // this thread's row: local query row (dQ) or kv position (dKV)
+    const int g_row = r0 + row;         // this thread's row: local query row (dQ) or kv position (dKV)
     const int q_pos = p.q_off + g_row;  // dQ only: global position of the query row
+    const int t_ew = threadIdx.x - 64;  // 0..255 among the element-wise threads
     const uint32_t lane_sel = static_cast<uint32_t>(quad * 32) << 16;
     const float scale_log2 = p.scale * kLog2e;
+    float* stats = reinterpret_cast<float*>(smem + L::STAT_OFF);
     float lse2_row = 0.f, delta_row = 0.f;
     int lo_row = 0;
+    int q_min = 0, q_max = p.S - 1;  // dKV only: local query rows this kv row is visible to
     if (!DKV) {
       if (g_row < p.S) {
         const long long idx = ((long long)b * p.Hq + h_res) * p.S + g_row;
@@ -250,83 +315,84 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
         delta_row = p.delta[idx];
         if (p.lo) lo_row = p.lo[(long long)b * p.S + g_row];
       }
+    } else {
+      if (p.causal) q_min = max(0, g_row - p.q_off);
+      if (p.hi && g_row < p.Skv) q_max = min(q_max, p.hi[(long long)b * p.Skv + g_row] - p.q_off);
     }
+    // dKV: thread t < 128 fetches lse * log2(e) of query t of block n, thread t >= 128 its delta;
+    // rows past the end get lse = +inf, which makes P exactly zero there.
+    auto load_stat = [&](int n) -> float {
+      const int g = n / blk_count;
+      const int blk = blk_begin + n % blk_count;
+      const int q = blk * TILE + (t_ew & 127);
+      const long long idx = ((long long)b * p.Hq + hkv * G + g) * p.S + q;
+      if (t_ew < 128) return q < p.S ? __ldg(p.lse + idx) * kLog2e : CUDART_INF_F;
+      return q < p.S ? __ldg(p.delta + idx) : 0.f;
+    };
     bool ok = n_total > 0;
+    if (DKV && ok) {
+      stats[t_ew] = load_stat(0);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(stat_ready);
+    }
     for (int n = 0; n < n_total && ok; ++n) {
       const uint32_t ph = n & 1;
-      const int g = DKV ? n / blk_count : 0;
       const int blk = blk_begin + (DKV ? n % blk_count : n);
-      const int c_base = blk * TILE + half * 64;  // global position of this warp's first column
-      if (!mbar_wait_warp(t_full, ph, ab, ERR_WAIT_S_READY)) { ok = false; break; }
+      float stat_next = 0.f;
+      if (DKV && n + 1 < n_total) stat_next = load_stat(n + 1);
+      const float* st = stats + (n & 1) * 256 + half * 64;  // lse2 of this warp's 64 columns; delta 128 floats on
+      if (DKV && !mbar_wait_warp(stat_ready, ph, ab, ERR_WAIT_S_READY)) { ok = false; break; }
+      if (!mbar_wait_warp(s_full, ph, ab, ERR_WAIT_S_READY)) { ok = false; break; }
       tc_fence_after();
+      float pv[64];
+      {
+        uint32_t ra[32], rb[32];
+        tmem_ld_32x32b_x32(tm_T1 + lane_sel + half * 64, ra);
+        tmem_ld_32x32b_x32(tm_T1 + lane_sel + half * 64 + 32, rb);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(t1_free);
+        if (!DKV) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            pv[i] = ex2_approx(fmaf(__uint_as_float(ra[i]), scale_log2, -lse2_row));
+            pv[32 + i] = ex2_approx(fmaf(__uint_as_float(rb[i]), scale_log2, -lse2_row));
+          }
+        } else {
+#pragma unroll
+          for (int i4 = 0; i4 < 8; ++i4) {
+            const float4 la = *reinterpret_cast<const float4*>(st + 4 * i4);
+            const float4 lb = *reinterpret_cast<const float4*>(st + 32 + 4 * i4);
+            pv[4 * i4 + 0] = ex2_approx(fmaf(__uint_as_float(ra[4 * i4 + 0]), scale_log2, -la.x));
+            pv[4 * i4 + 1] = ex2_approx(fmaf(__uint_as_float(ra[4 * i4 + 1]), scale_log2, -la.y));
+            pv[4 * i4 + 2] = ex2_approx(fmaf(__uint_as_float(ra[4 * i4 + 2]), scale_log2, -la.z));
+            pv[4 * i4 + 3] = ex2_approx(fmaf(__uint_as_float(ra[4 * i4 + 3]), scale_log2, -la.w));
+            pv[32 + 4 * i4 + 0] = ex2_approx(fmaf(__uint_as_float(rb[4 * i4 + 0]), scale_log2, -lb.x));
+            pv[32 + 4 * i4 + 1] = ex2_approx(fmaf(__uint_as_float(rb[4 * i4 + 1]), scale_log2, -lb.y));
+            pv[32 + 4 * i4 + 2] = ex2_approx(fmaf(__uint_as_float(rb[4 * i4 + 2]), scale_log2, -lb.z));
+            pv[32 + 4 * i4 + 3] = ex2_approx(fmaf(__uint_as_float(rb[4 * i4 + 3]), scale_log2, -lb.w));
+          }
+        }
+      }
+      const int c0 = blk * TILE + half * 64;  // first column of this warp: kv position (dQ) or local query row (dKV)
       if (!DKV) {
         // rows = queries, columns = kv
-        const bool need_mask = (p.causal && blk * TILE + TILE - 1 > q_pos) || (blk * TILE < lo_row) ||
-                               (blk * TILE + TILE > p.Skv) || (g_row >= p.S);
         const int hi_col = g_row >= p.S ? -1 : (p.causal ? min(q_pos, p.Skv - 1) : p.Skv - 1);
-        if (n > 0 && !mbar_wait_warp(acc_done, ph ^ 1, ab, ERR_WAIT_O_READY)) { ok = false; break; }
+        if (__any_sync(0xffffffffu, c0 + 63 > hi_col || c0 < lo_row)) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t r1[32], r2[32];
-          tmem_ld_32x32b_x32(tm_T1 + lane_sel + half * 64 + c * 32, r1);
-          tmem_ld_32x32b_x32(tm_T2 + lane_sel + half * 64 + c * 32, r2);
-          tmem_ld_wait();
-          float ds[32];
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float pr = exp2f(__uint_as_float(r1[i]) * scale_log2 - lse2_row);
-            float v = pr * (__uint_as_float(r2[i]) - delta_row) * p.scale;
-            if (need_mask) {
-              const int col = c_base + c * 32 + i;
-              if (col > hi_col || col < lo_row) v = 0.f;
-            }
-            ds[i] = v;
-          }
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            uint4 v;
-            v.x = pack_bf16x2(ds[8 * k + 0], ds[8 * k + 1]);
-            v.y = pack_bf16x2(ds[8 * k + 2], ds[8 * k + 3]);
-            v.z = pack_bf16x2(ds[8 * k + 4], ds[8 * k + 5]);
-            v.w = pack_bf16x2(ds[8 * k + 6], ds[8 * k + 7]);
-            *reinterpret_cast<uint4*>(sBuf + half * 16384 + sw128_offset(row, c * 4 + k)) = v;
-          }
-        }
-        tc_fence_before();
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(t_free);
-          mbar_arrive(ds_ready);
+          for (int i = 0; i < 64; ++i)
+            if (c0 + i > hi_col || c0 + i < lo_row) pv[i] = 0.f;
         }
       } else {
-        // rows = kv, columns = queries of head hq
-        const int hq = hkv * G + g;
-        const long long vec_base = ((long long)b * p.Hq + hq) * p.S;
-        const int q_first = blk * TILE, q_last = min(blk * TILE + TILE, p.S) - 1;
-        bool need_mask = (p.causal && p.q_off + q_first < r0 + TILE - 1) || (blk * TILE + TILE > p.S) ||
-                         (r0 + TILE > p.Skv);
-        if (p.lo) need_mask = need_mask || (p.lo[(long long)b * p.S + q_last] > r0);
-        float pv[64];
+        // rows = kv, columns = queries.  kv rows past Skv need no mask: they only reach output rows
+        // that the store clips.
+        if (__any_sync(0xffffffffu, c0 < q_min || c0 + 63 > q_max)) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t r1[32];
-          tmem_ld_32x32b_x32(tm_T1 + lane_sel + half * 64 + c * 32, r1);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int q = c_base + c * 32 + i;
-            const float lse2 = q < p.S ? __ldg(p.lse + vec_base + q) * kLog2e : 0.f;
-            float pr = exp2f(__uint_as_float(r1[i]) * scale_log2 - lse2);
-            if (need_mask) {
-              bool allowed = q < p.S && g_row < p.Skv && (!p.causal || p.q_off + q >= g_row);
-              if (allowed && p.lo) allowed = g_row >= __ldg(p.lo + (long long)b * p.S + q);
-              if (!allowed) pr = 0.f;
-            }
-            pv[c * 32 + i] = pr;
-          }
+          for (int i = 0; i < 64; ++i)
+            if (c0 + i < q_min || c0 + i > q_max) pv[i] = 0.f;
         }
-        if (n > 0 && !mbar_wait_warp(acc_done, ph ^ 1, ab, ERR_WAIT_O_READY)) { ok = false; break; }
+        if (n > 0 && !mbar_wait_warp(dv_done, ph ^ 1, ab, ERR_WAIT_O_READY)) { ok = false; break; }
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           uint4 v;
@@ -339,45 +405,60 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(p_ready);
+      }
+      if (!mbar_wait_warp(dp_full, ph, ab, ERR_WAIT_S_READY)) { ok = false; break; }
+      tc_fence_after();
+      {
+        uint32_t ra[32], rb[32], packed[32];
+        tmem_ld_32x32b_x32(tm_T2 + lane_sel + half * 64, ra);
+        tmem_ld_32x32b_x32(tm_T2 + lane_sel + half * 64 + 32, rb);
+        tmem_ld_wait();
+        if (!DKV) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t r2[32];
-          tmem_ld_32x32b_x32(tm_T2 + lane_sel + half * 64 + c * 32, r2);
-          tmem_ld_wait();
+          for (int i = 0; i < 16; ++i) {
+            packed[i] = pack_bf16x2(pv[2 * i] * (__uint_as_float(ra[2 * i]) - delta_row),
+                                    pv[2 * i + 1] * (__uint_as_float(ra[2 * i + 1]) - delta_row));
+            packed[16 + i] = pack_bf16x2(pv[32 + 2 * i] * (__uint_as_float(rb[2 * i]) - delta_row),
+                                         pv[32 + 2 * i + 1] * (__uint_as_float(rb[2 * i + 1]) - delta_row));
+          }
+        } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int q = c_base + c * 32 + i;
-            const float dl = q < p.S ? __ldg(p.delta + vec_base + q) : 0.f;
-            pv[c * 32 + i] = pv[c * 32 + i] * (__uint_as_float(r2[i]) - dl) * p.scale;
+          for (int i4 = 0; i4 < 8; ++i4) {
+            const float4 da = *reinterpret_cast<const float4*>(st + 128 + 4 * i4);
+            const float4 db = *reinterpret_cast<const float4*>(st + 128 + 32 + 4 * i4);
+            packed[2 * i4] = pack_bf16x2(pv[4 * i4] * (__uint_as_float(ra[4 * i4]) - da.x),
+                                         pv[4 * i4 + 1] * (__uint_as_float(ra[4 * i4 + 1]) - da.y));
+            packed[2 * i4 + 1] = pack_bf16x2(pv[4 * i4 + 2] * (__uint_as_float(ra[4 * i4 + 2]) - da.z),
+                                             pv[4 * i4 + 3] * (__uint_as_float(ra[4 * i4 + 3]) - da.w));
+            packed[16 + 2 * i4] = pack_bf16x2(pv[32 + 4 * i4] * (__uint_as_float(rb[4 * i4]) - db.x),
+                                              pv[32 + 4 * i4 + 1] * (__uint_as_float(rb[4 * i4 + 1]) - db.y));
+            packed[16 + 2 * i4 + 1] = pack_bf16x2(pv[32 + 4 * i4 + 2] * (__uint_as_float(rb[4 * i4 + 2]) - db.z),
+                                                  pv[32 + 4 * i4 + 3] * (__uint_as_float(rb[4 * i4 + 3]) - db.w));
           }
         }
-        tc_fence_before();
+        tmem_st_32x32b_x32(tm_DS + lane_sel + half * 64, packed);
+        tmem_st_wait();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_ready);
+      if (DKV && n + 1 < n_total) {
+        stats[((n + 1) & 1) * 256 + t_ew] = stat_next;
         __syncwarp();
-        if (lane == 0) mbar_arrive(t_free);
-        if (!mbar_wait_warp(dv_done, ph, ab, ERR_WAIT_O_READY)) { ok = false; break; }
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          uint4 v;
-          v.x = pack_bf16x2(pv[8 * k + 0], pv[8 * k + 1]);
-          v.y = pack_bf16x2(pv[8 * k + 2], pv[8 * k + 3]);
-          v.z = pack_bf16x2(pv[8 * k + 4], pv[8 * k + 5]);
-          v.w = pack_bf16x2(pv[8 * k + 6], pv[8 * k + 7]);
-          *reinterpret_cast<uint4*>(sBuf + half * 16384 + sw128_offset(row, k)) = v;
-        }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(ds_ready);
+        if (lane == 0) mbar_arrive(stat_ready);
       }
     }
     // ---- epilogue: accumulators -> bf16 -> global.  Warp (quad, half) owns rows quad*32.. and the
-    //      64-column box `half` of the D columns (for D = 64 only half 0 has columns).
-    if (n_total > 0 && ok) ok = mbar_wait_warp(acc_done, (n_total - 1) & 1, ab, ERR_WAIT_O_READY);
+    //      64-column box `half` of the D columns (for D = 64 only half 0 has columns).  The softmax scale
+    //      that dS left out is applied here (dQ and dK; dV has none).
+    if (n_total > 0 && ok) ok = mbar_wait_warp(acc_done, 0, ab, ERR_WAIT_O_READY);
     if ((n_total == 0 || ok) && half < NBOX) {
       tc_fence_after();
       const int slab_row = r0 + quad * 32;
       uint8_t* slab = sBuf + half * 16384 + quad * 32 * 128;
       for (int which = 0; which < (DKV ? 2 : 1); ++which) {
         const uint32_t acc = (which == 0 ? tm_A1 : tm_A2) + lane_sel + half * 64;
+        const float mul = which == 0 ? p.scale : 1.f;
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           uint32_t r[32];
@@ -391,10 +472,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             uint4 v;
-            v.x = pack_bf16x2(__uint_as_float(r[8 * k + 0]), __uint_as_float(r[8 * k + 1]));
-            v.y = pack_bf16x2(__uint_as_float(r[8 * k + 2]), __uint_as_float(r[8 * k + 3]));
-            v.z = pack_bf16x2(__uint_as_float(r[8 * k + 4]), __uint_as_float(r[8 * k + 5]));
-            v.w = pack_bf16x2(__uint_as_float(r[8 * k + 6]), __uint_as_float(r[8 * k + 7]));
+            v.x = pack_bf16x2(__uint_as_float(r[8 * k + 0]) * mul, __uint_as_float(r[8 * k + 1]) * mul);
+            v.y = pack_bf16x2(__uint_as_float(r[8 * k + 2]) * mul, __uint_as_float(r[8 * k + 3]) * mul);
+            v.z = pack_bf16x2(__uint_as_float(r[8 * k + 4]) * mul, __uint_as_float(r[8 * k + 5]) * mul);
+            v.w = pack_bf16x2(__uint_as_float(r[8 * k + 6]) * mul, __uint_as_float(r[8 * k + 7]) * mul);
             *reinterpret_cast<uint4*>(slab + sw128_offset(lane, c * 4 + k)) = v;
           }
         }
@@ -457,7 +538,7 @@ int launch_bwd(const CUtensorMap& x1, const CUtensorMap& x2, const CUtensorMap& 
                const CUtensorMap& o1, const CUtensorMap& o2, const BwdParams& p, cudaStream_t stream) {
   using L = BwdSmem<D>;
   auto* kern = attn_bwd_kernel<D, DKV>;
-  constexpr int smem_bytes = L::TOTAL + 1024;
+  constexpr int smem_bytes = L::TOTAL;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
@@ -490,6 +571,7 @@ extern "C" int b200_attn_bwd(const void* q, const void* k, const void* v, const 
   if (q_off % 128 != 0 || q_off < 0) return RC_BAD_SHAPE;
   if (B <= 0 || S <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv) return RC_BAD_SHAPE;
   if (D != 128 && D != 64) return RC_BAD_SHAPE;
+  if (lo != nullptr && hi == nullptr) return RC_BAD_SHAPE;  // the dKV kernel masks with the kv-side bound
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   {
     const long long rows = (long long)B * S * Hq;

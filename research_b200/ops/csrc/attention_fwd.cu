@@ -253,7 +253,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const bool need = bm > m_ref + kRescaleThreshold;
       if (__any_sync(0xffffffffu, need)) {
         const float m_new = need ? bm : m_ref;
-        const float alpha = exp2f(m_ref - m_new);
+        const float alpha = ex2_approx(m_ref - m_new);
         if (j > 0) {
           if (!mbar_wait_warp(&pv_done[t], (j - 1) & 1, ab, ERR_WAIT_O_READY)) { ok = false; break; }
           tc_fence_after();
@@ -289,7 +289,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             const int col = kv0 + c * 32 + i;
             if (col > hi || col < lo_row) v = -INFINITY;
           }
-          e[i] = exp2f(v);
+          e[i] = ex2_approx(v);
           sum += e[i];
         }
 #pragma unroll
