@@ -190,50 +190,67 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
 // w  : [D] fp32 norm scale or nullptr (no norm).  positions: [tokens] int32.  rope: 0 = skip rotation.
 // Angle of pair i at position p: p * theta^(-2i/D).
 // ------------------------------------------------------------------------------------------------
+// sin and cos of an angle of any size: Cody-Waite reduction by 2*pi to [-pi, pi], then the special-function unit
+__device__ __forceinline__ void sincos_reduced(float x, float* s, float* c) {
+  const float k = rintf(x * 0.15915494309189535f);
+  x = fmaf(k, -6.28318548202514648f, x);
+  x = fmaf(k, 1.74845553e-7f, x);
+  __sincosf(x, s, c);
+}
+
+// A head of D <= 256 elements is handled by `lph` lanes (a power of two, 8 elements per lane), so a warp works on
+// 32 / lph heads at once; reductions stay inside the lane group.
+__device__ __forceinline__ float group_sum(float v, int lph) {
+  for (int off = lph >> 1; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+  return v;
+}
+
 __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ in, long long in_stride, __nv_bfloat16* __restrict__ out,
                        long long out_stride, const float* __restrict__ w, const int* __restrict__ positions,
                        float* __restrict__ rstd_out, long long tokens, int heads, int D, float eps, float log2_theta,
-                       int rope) {
+                       int rope, int lph) {
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
+  const int hpw = 32 / lph;
+  const int sub = lane / lph, l = lane % lph;
   const long long total = tokens * heads;
-  const bool active = lane * 8 < D;
-  for (long long idx = (long long)blockIdx.x * kWarpsPerBlock + warp; idx < total;
-       idx += (long long)gridDim.x * kWarpsPerBlock) {
+  const bool has_cols = l * 8 < D;
+  float inv_freq[4], wv[8] = {1, 1, 1, 1, 1, 1, 1, 1};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) inv_freq[i] = exp2f(-log2_theta * (2.f * (float)(l * 4 + i)) / (float)D);
+  if (w && has_cols) load8f(w + l * 8, wv);
+  const long long groups = (total + hpw - 1) / hpw;
+  for (long long gidx = (long long)blockIdx.x * kWarpsPerBlock + warp; gidx < groups;
+       gidx += (long long)gridDim.x * kWarpsPerBlock) {
+    const long long idx = gidx * hpw + sub;
+    const bool active = has_cols && idx < total;
     const long long t = idx / heads;
     const int h = (int)(idx - t * heads);
     float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    if (active) unpack8(*reinterpret_cast<const uint4*>(in + t * in_stride + (long long)h * D + lane * 8), f);
-    float rstd = 1.f;
+    if (active) unpack8(*reinterpret_cast<const uint4*>(in + t * in_stride + (long long)h * D + l * 8), f);
     if (w) {
       float ss = 0.f;
 #pragma unroll
       for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
-      ss = warp_sum(ss);
-      rstd = rsqrtf(ss / (float)D + eps);
-      if (lane == 0 && rstd_out) rstd_out[idx] = rstd;
-      if (active) {
-        float wv[8];
-        load8f(w + lane * 8, wv);
+      ss = group_sum(ss, lph);
+      const float rstd = rsqrtf(ss / (float)D + eps);
+      if (l == 0 && rstd_out && idx < total) rstd_out[idx] = rstd;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] = f[i] * rstd * wv[i];
-      }
+      for (int i = 0; i < 8; ++i) f[i] = f[i] * rstd * wv[i];
     }
     if (rope && active) {
       const float pos = (float)positions[t];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int pair = lane * 4 + i;
-        const float inv_freq = exp2f(-log2_theta * (2.f * (float)pair) / (float)D);
         float s, c;
-        sincosf(pos * inv_freq, &s, &c);
+        sincos_reduced(pos * inv_freq[i], &s, &c);
         const float a = f[2 * i], b = f[2 * i + 1];
         f[2 * i] = a * c - b * s;
         f[2 * i + 1] = a * s + b * c;
       }
     }
-    if (active) *reinterpret_cast<uint4*>(out + t * out_stride + (long long)h * D + lane * 8) = pack8(f);
+    if (active) *reinterpret_cast<uint4*>(out + t * out_stride + (long long)h * D + l * 8) = pack8(f);
   }
 }
 
@@ -243,45 +260,50 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ in, long long in_stride
                        const __nv_bfloat16* __restrict__ dout, long long dout_stride,
                        __nv_bfloat16* __restrict__ din, long long din_stride, const float* __restrict__ w,
                        const int* __restrict__ positions, const float* __restrict__ rstd_in,
-                       float* __restrict__ dw, long long tokens, int heads, int D, float log2_theta, int rope) {
+                       float* __restrict__ dw, long long tokens, int heads, int D, float log2_theta, int rope,
+                       int lph) {
   __shared__ float dw_smem[256];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
+  const int hpw = 32 / lph;
+  const int sub = lane / lph, l = lane % lph;
   const long long total = tokens * heads;
-  const bool active = lane * 8 < D;
+  const bool has_cols = l * 8 < D;
   if (threadIdx.x < 256) dw_smem[threadIdx.x] = 0.f;
   __syncthreads();
+  float inv_freq[4], wv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) inv_freq[i] = exp2f(-log2_theta * (2.f * (float)(l * 4 + i)) / (float)D);
+  if (w && has_cols) load8f(w + l * 8, wv);
   float dw_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  for (long long idx = (long long)blockIdx.x * kWarpsPerBlock + warp; idx < total;
-       idx += (long long)gridDim.x * kWarpsPerBlock) {
+  const long long groups = (total + hpw - 1) / hpw;
+  for (long long gidx = (long long)blockIdx.x * kWarpsPerBlock + warp; gidx < groups;
+       gidx += (long long)gridDim.x * kWarpsPerBlock) {
+    const long long idx = gidx * hpw + sub;
+    const bool active = has_cols && idx < total;
     const long long t = idx / heads;
     const int h = (int)(idx - t * heads);
     float g[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    if (active) unpack8(*reinterpret_cast<const uint4*>(dout + t * dout_stride + (long long)h * D + lane * 8), g);
+    if (active) unpack8(*reinterpret_cast<const uint4*>(dout + t * dout_stride + (long long)h * D + l * 8), g);
     if (rope && active) {
       const float pos = (float)positions[t];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int pair = lane * 4 + i;
-        const float inv_freq = exp2f(-log2_theta * (2.f * (float)pair) / (float)D);
         float s, c;
-        sincosf(pos * inv_freq, &s, &c);
+        sincos_reduced(pos * inv_freq[i], &s, &c);
         const float a = g[2 * i], b = g[2 * i + 1];  // transpose of the rotation
         g[2 * i] = a * c + b * s;
         g[2 * i + 1] = -a * s + b * c;
       }
     }
     if (w) {
-      float f[8] = {0, 0, 0, 0, 0, 0, 0, 0}, wv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-      if (active) {
-        unpack8(*reinterpret_cast<const uint4*>(in + t * in_stride + (long long)h * D + lane * 8), f);
-        load8f(w + lane * 8, wv);
-      }
-      const float rstd = rstd_in[idx];
+      float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      if (active) unpack8(*reinterpret_cast<const uint4*>(in + t * in_stride + (long long)h * D + l * 8), f);
+      const float rstd = idx < total ? rstd_in[idx] : 0.f;
       float dot = 0.f;
 #pragma unroll
       for (int i = 0; i < 8; ++i) dot += g[i] * wv[i] * f[i] * rstd;
-      dot = warp_sum(dot) / (float)D;
+      dot = group_sum(dot, lph) / (float)D;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const float xhat = f[i] * rstd;
@@ -289,12 +311,12 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ in, long long in_stride
         g[i] = rstd * (g[i] * wv[i] - xhat * dot);
       }
     }
-    if (active) *reinterpret_cast<uint4*>(din + t * din_stride + (long long)h * D + lane * 8) = pack8(g);
+    if (active) *reinterpret_cast<uint4*>(din + t * din_stride + (long long)h * D + l * 8) = pack8(g);
   }
   if (w && dw) {
-    if (active) {
+    if (has_cols) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) atomicAdd(&dw_smem[lane * 8 + i], dw_acc[i]);
+      for (int i = 0; i < 8; ++i) atomicAdd(&dw_smem[l * 8 + i], dw_acc[i]);
     }
     __syncthreads();
     if (threadIdx.x < D) atomicAdd(&dw[threadIdx.x], dw_smem[threadIdx.x]);
@@ -619,14 +641,20 @@ extern "C" int b200_rmsnorm_bwd(const void* x, const void* w, const void* rstd, 
 #undef RMS_BWD
   return LAST_ERR();
 }
+static int lanes_per_head(int D) {
+  int lph = 1;
+  while (lph * 8 < D) lph <<= 1;
+  return lph;
+}
 extern "C" int b200_qknorm_rope_fwd(const void* in, long long in_stride, void* out, long long out_stride,
                                     const void* w, const void* positions, void* rstd, long long tokens, int heads,
                                     int D, float eps, float theta, int rope, void* stream) {
   if (D % 8 || D > 256) return -2;
-  const int grid = grid_for(tokens * heads, kWarpsPerBlock, 8);
+  const int lph = lanes_per_head(D);
+  const int grid = grid_for((tokens * heads + 32 / lph - 1) / (32 / lph), kWarpsPerBlock, 8);
   qknorm_rope_fwd_kernel<<<grid, kWarpsPerBlock * 32, 0, STREAM(stream)>>>(
       (const __nv_bfloat16*)in, in_stride, (__nv_bfloat16*)out, out_stride, (const float*)w, (const int*)positions,
-      (float*)rstd, tokens, heads, D, eps, log2f(theta), rope);
+      (float*)rstd, tokens, heads, D, eps, log2f(theta), rope, lph);
   return LAST_ERR();
 }
 extern "C" int b200_qknorm_rope_bwd(const void* in, long long in_stride, const void* dout, long long dout_stride,
@@ -634,10 +662,12 @@ extern "C" int b200_qknorm_rope_bwd(const void* in, long long in_stride, const v
                                     const void* rstd, void* dw, long long tokens, int heads, int D, float theta,
                                     int rope, void* stream) {
   if (D % 8 || D > 256) return -2;
-  const int grid = grid_for(tokens * heads, kWarpsPerBlock, 4);
+  const int lph = lanes_per_head(D);
+  const int grid = grid_for((tokens * heads + 32 / lph - 1) / (32 / lph), kWarpsPerBlock, 4);
   qknorm_rope_bwd_kernel<<<grid, kWarpsPerBlock * 32, 0, STREAM(stream)>>>(
       (const __nv_bfloat16*)in, in_stride, (const __nv_bfloat16*)dout, dout_stride, (__nv_bfloat16*)din, din_stride,
-      (const float*)w, (const int*)positions, (const float*)rstd, (float*)dw, tokens, heads, D, log2f(theta), rope);
+      (const float*)w, (const int*)positions, (const float*)rstd, (float*)dw, tokens, heads, D, log2f(theta), rope,
+      lph);
   return LAST_ERR();
 }
 extern "C" int b200_swiglu_fwd(const void* gu, void* h, long long rows, int I, void* stream) {

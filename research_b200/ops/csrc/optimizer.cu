@@ -108,6 +108,29 @@ __global__ void affine_identity_kernel(const __nv_bfloat16* __restrict__ a, __nv
   }
 }
 
+// d a multiple of 8: one 16-byte chunk of a row per thread; the diagonal element of row r sits in chunk r / 8
+__global__ void affine_identity_vec8_kernel(const uint4* __restrict__ a, uint4* __restrict__ p, int d,
+                                            long long chunks, float alpha, float beta) {
+  const unsigned cpr = (unsigned)d >> 3;                       // chunks per row
+  const unsigned long long cpm = (unsigned long long)cpr * d;  // chunks per matrix
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < chunks;
+       i += (long long)gridDim.x * blockDim.x) {
+    const unsigned r = (unsigned)((unsigned long long)i % cpm);
+    const unsigned row = r / cpr, ch = r - row * cpr;
+    uint4 v = a[i];
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&v);
+    const int diag = (row >> 3) == ch ? (int)(row & 7u) : -1;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float2 f = __bfloat1622float2(h[k]);
+      f.x = beta * f.x + (diag == 2 * k ? alpha : 0.f);
+      f.y = beta * f.y + (diag == 2 * k + 1 ? alpha : 0.f);
+      h[k] = __floats2bfloat162_rn(f.x, f.y);
+    }
+    p[i] = v;
+  }
+}
+
 int blocks_for(long long items, int block, int per_sm) {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -144,7 +167,13 @@ extern "C" int b200_scale_by_inv_norm(void* x, const void* sumsq, long long per,
 extern "C" int b200_affine_identity(const void* a, void* p, int d, int batch, float alpha, float beta, void* stream) {
   const long long total = (long long)batch * d * d;
   if (total <= 0) return -2;
-  affine_identity_kernel<<<blocks_for(total, 256, 8), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      (const __nv_bfloat16*)a, (__nv_bfloat16*)p, d, total, alpha, beta);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const bool vec = (d % 8 == 0) && (reinterpret_cast<uintptr_t>(a) % 16 == 0) && (reinterpret_cast<uintptr_t>(p) % 16 == 0);
+  if (vec)
+    affine_identity_vec8_kernel<<<blocks_for(total / 8, 256, 8), 256, 0, s>>>((const uint4*)a, (uint4*)p, d, total / 8,
+                                                                            alpha, beta);
+  else
+    affine_identity_kernel<<<blocks_for(total, 256, 8), 256, 0, s>>>((const __nv_bfloat16*)a, (__nv_bfloat16*)p, d,
+                                                                     total, alpha, beta);
   return static_cast<int>(cudaGetLastError());
 }
