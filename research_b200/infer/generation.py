@@ -48,12 +48,22 @@ class PagedKVCache:
         b_idx = torch.arange(B, device=q.device)[:, None].expand(B, T)
         kc[b_idx, idx] = k.to(kc.dtype)
         vc[b_idx, idx] = v.to(vc.dtype)
-        end = int(positions.max().item()) + 1
         if T == 1 and q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128):
             from research_b200.ops.decode import decode_attention
 
             lo = None if window is None else (positions[:, 0] - (window - 1)).clamp_min(0).to(torch.int32)
             return decode_attention(q[:, 0], kc, vc, (positions[:, 0] + 1).to(torch.int32), lo)[:, None]
+        if (T > 1 and q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128)
+                and bool((positions == torch.arange(T, device=q.device, dtype=positions.dtype)).all())):
+            # prefill from position 0: the flash kernel over the rows just written
+            from research_b200.ops import native
+
+            lo = None
+            if window is not None:
+                lo = (positions - (window - 1)).clamp_min(0).to(torch.int32).contiguous()
+            o, _ = native.attn_fwd(q.contiguous(), kc[:, :T], vc[:, :T], causal=True, lo=lo)
+            return o.reshape(B, T, -1)
+        end = int(positions.max().item()) + 1
         keys, vals = kc[:, :end], vc[:, :end]
         kpos = torch.arange(end, device=q.device)
         allowed = kpos[None, None, :] <= idx[:, :, None]

@@ -1,0 +1,227 @@
+// Decode attention over a KV cache for sm_100a: one new query token per sequence, GQA, split-KV.
+//
+// The op is bandwidth bound (every cached K and V row is read once per step), so it runs on the SIMT pipes
+// with 16-byte loads: a group of D/8 lanes owns one cache row at a time (8 bf16 per lane), a warp works on
+// 32/(D/8) rows at once and keeps an online softmax state (m, l, acc[8]) per query head of the GQA group in
+// registers, so K and V are read once for all G heads that share them.  The kv range of a sequence is cut
+// into `splits` chunks across CTAs; a second small kernel merges the chunk results with their log-sum-exp
+// weights.  Only rows in [lo[b], lengths[b]) are touched: nothing is read from unused pages.
+//
+// Oracle: softmax(q K^T / sqrt(D)) V in fp32 over the valid rows (reference decode path:
+// infer/generation.py:302, models/components/attention.py:213-218, which attends over the whole padded
+// cache with a mask).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+namespace {
+
+constexpr int kWarps = 4;
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ float ex2f(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(h[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+
+struct DecodeParams {
+  const __nv_bfloat16* q;  // [B, Hq, D]
+  const __nv_bfloat16* k;  // [B, rows, Hkv, D] by strides
+  const __nv_bfloat16* v;
+  const int* lengths;      // [B]
+  const int* lo;           // [B] or nullptr
+  float* part_o;           // [B, Hq, splits, D]
+  float* part_ml;          // [B, Hq, splits, 2]  (m in log2 units, l)
+  long long k_row, k_batch, v_row, v_batch;  // element strides
+  int B, Hq, Hkv, splits;
+  float scale_log2;
+};
+
+template <int D, int G>
+__global__ void __launch_bounds__(kWarps * 32) decode_attn_partial_kernel(const DecodeParams p) {
+  constexpr int LPR = D / 8;      // lanes per cache row
+  constexpr int RPW = 32 / LPR;   // rows per warp per step
+  constexpr int GROUPS = kWarps * RPW;
+  __shared__ float s_acc[GROUPS][G][D];
+  __shared__ float s_ml[GROUPS][G][2];
+
+  const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane / LPR, l = lane % LPR;
+  const int grp = warp * RPW + sub;
+  // lane groups run different numbers of rows, so shuffles name only the lanes of the own group
+  const uint32_t gmask = LPR == 32 ? 0xffffffffu : (((1u << LPR) - 1u) << (sub * LPR));
+
+  const int len = p.lengths[b];
+  const int first = p.lo ? max(p.lo[b], 0) : 0;
+  const int span = max(len - first, 0);
+  int chunk = (span + p.splits - 1) / p.splits;
+  chunk = (chunk + GROUPS - 1) / GROUPS * GROUPS;
+  const int begin = first + split * chunk;
+  const int end = min(begin + chunk, len);
+
+  float q[G][8], acc[G][8], m[G], lsum[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const __nv_bfloat16* qp = p.q + ((long long)b * p.Hq + hkv * G + g) * D + l * 8;
+    unpack8(*reinterpret_cast<const uint4*>(qp), q[g]);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      q[g][i] *= p.scale_log2;
+      acc[g][i] = 0.f;
+    }
+    m[g] = -CUDART_INF_F;
+    lsum[g] = 0.f;
+  }
+  const __nv_bfloat16* kb = p.k + b * p.k_batch + (long long)hkv * D + l * 8;
+  const __nv_bfloat16* vb = p.v + b * p.v_batch + (long long)hkv * D + l * 8;
+
+  constexpr int UNROLL = 4;
+  for (int r0 = begin + grp; r0 < end; r0 += GROUPS * UNROLL) {
+    uint4 kr[UNROLL], vr[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int r = r0 + u * GROUPS;
+      if (r < end) {
+        kr[u] = __ldg(reinterpret_cast<const uint4*>(kb + r * p.k_row));
+        vr[u] = __ldg(reinterpret_cast<const uint4*>(vb + r * p.v_row));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int r = r0 + u * GROUPS;
+      if (r >= end) break;  // uniform inside a lane group
+      float kf[8], vf[8];
+      unpack8(kr[u], kf);
+      unpack8(vr[u], vf);
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s = fmaf(q[g][i], kf[i], s);
+#pragma unroll
+        for (int off = LPR >> 1; off > 0; off >>= 1) s += __shfl_xor_sync(gmask, s, off, LPR);
+        const float m_new = fmaxf(m[g], s);
+        const float alpha = ex2f(m[g] - m_new);
+        const float pr = ex2f(s - m_new);
+        m[g] = m_new;
+        lsum[g] = lsum[g] * alpha + pr;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(acc[g][i], alpha, pr * vf[i]);
+      }
+    }
+  }
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s_acc[grp][g][l * 8 + i] = acc[g][i];
+    if (l == 0) {
+      s_ml[grp][g][0] = m[g];
+      s_ml[grp][g][1] = lsum[g];
+    }
+  }
+  __syncthreads();
+  // merge the GROUPS partial states of this CTA: one thread per (g, d)
+  for (int idx = threadIdx.x; idx < G * D; idx += kWarps * 32) {
+    const int g = idx / D, d = idx % D;
+    float mm = -CUDART_INF_F;
+#pragma unroll
+    for (int j = 0; j < GROUPS; ++j) mm = fmaxf(mm, s_ml[j][g][0]);
+    float o = 0.f, ls = 0.f;
+    if (mm > -CUDART_INF_F) {
+#pragma unroll
+      for (int j = 0; j < GROUPS; ++j) {
+        const float w = ex2f(s_ml[j][g][0] - mm);
+        o = fmaf(s_acc[j][g][d], w, o);
+        ls = fmaf(s_ml[j][g][1], w, ls);
+      }
+    }
+    const long long slot = ((long long)b * p.Hq + hkv * G + g) * p.splits + split;
+    p.part_o[slot * D + d] = o;
+    if (d == 0) {
+      p.part_ml[slot * 2] = mm;
+      p.part_ml[slot * 2 + 1] = ls;
+    }
+  }
+}
+
+// out[b,h,:] = sum_s w_s o_s / sum_s w_s l_s with w_s = 2^(m_s - max m); a row with no valid kv gives zeros
+__global__ void decode_attn_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                         __nv_bfloat16* __restrict__ out, int splits, int D) {
+  const long long bh = blockIdx.x;
+  const int d = threadIdx.x;
+  if (d >= D) return;
+  float mm = -CUDART_INF_F;
+  for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part_ml[(bh * splits + s) * 2]);
+  float o = 0.f, ls = 0.f;
+  if (mm > -CUDART_INF_F) {
+    for (int s = 0; s < splits; ++s) {
+      const float w = ex2f(part_ml[(bh * splits + s) * 2] - mm);
+      o = fmaf(part_o[(bh * splits + s) * D + d], w, o);
+      ls = fmaf(part_ml[(bh * splits + s) * 2 + 1], w, ls);
+    }
+  }
+  out[bh * D + d] = __float2bfloat16(ls > 0.f ? o / ls : 0.f);
+}
+
+template <int D>
+int launch_partial(const DecodeParams& p, int G, cudaStream_t s) {
+  const dim3 grid(p.splits, p.Hkv, p.B);
+  switch (G) {
+    case 1: decode_attn_partial_kernel<D, 1><<<grid, kWarps * 32, 0, s>>>(p); break;
+    case 2: decode_attn_partial_kernel<D, 2><<<grid, kWarps * 32, 0, s>>>(p); break;
+    case 4: decode_attn_partial_kernel<D, 4><<<grid, kWarps * 32, 0, s>>>(p); break;
+    case 8: decode_attn_partial_kernel<D, 8><<<grid, kWarps * 32, 0, s>>>(p); break;
+    default: return -2;
+  }
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace
+
+// Suggested number of kv splits so that the grid fills the device a few times over.
+extern "C" int b200_decode_attn_splits(int B, int Hkv, int max_rows) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int base = B * Hkv > 0 ? B * Hkv : 1;
+  int splits = (sms * 8 + base - 1) / base;
+  const int by_rows = (max_rows + 255) / 256;  // at least 256 rows per split
+  if (splits > by_rows) splits = by_rows;
+  if (splits > 64) splits = 64;
+  return splits < 1 ? 1 : splits;
+}
+
+// q, out: [B,Hq,D] bf16 contiguous.  k, v: cache views [B, rows, Hkv, D] given by element strides between rows
+// and between sequences.  lengths: int32 [B] (rows valid per sequence), lo: int32 [B] or null (first visible row).
+// part_o: fp32 [B*Hq*splits*D], part_ml: fp32 [B*Hq*splits*2] scratch.  Hq/Hkv must be 1, 2, 4 or 8; D is 64 or 128.
+extern "C" int b200_decode_attn(const void* q, const void* k, const void* v, void* out, const void* lengths,
+                                const void* lo, void* part_o, void* part_ml, int B, int Hq, int Hkv, int D,
+                                long long k_row, long long k_batch, long long v_row, long long v_batch, float scale,
+                                int splits, void* stream) {
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || splits < 1) return -2;
+  if ((k_row % 8) || (k_batch % 8) || (v_row % 8) || (v_batch % 8)) return -1;  // 16-byte loads
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) return -1;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  DecodeParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (const int*)lengths,
+                 (const int*)lo, (float*)part_o, (float*)part_ml, k_row, k_batch, v_row, v_batch, B, Hq, Hkv, splits,
+                 scale * kLog2e};
+  int rc;
+  if (D == 128) rc = launch_partial<128>(p, Hq / Hkv, s);
+  else if (D == 64) rc = launch_partial<64>(p, Hq / Hkv, s);
+  else return -2;
+  if (rc) return rc;
+  decode_attn_merge_kernel<<<B * Hq, D, 0, s>>>((const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, splits, D);
+  return static_cast<int>(cudaGetLastError());
+}

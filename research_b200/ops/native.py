@@ -93,6 +93,9 @@ def _declare(lib: ctypes.CDLL) -> None:
     sig("b200_muon_apply", c_void_p, c_void_p, c_void_p, c_ll, c_float, c_float, c_void_p)
     sig("b200_scale_by_inv_norm", c_void_p, c_void_p, c_ll, c_int, c_float, c_void_p)
     sig("b200_affine_identity", c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p)
+    sig("b200_decode_attn_splits", c_int, c_int, c_int)
+    sig("b200_decode_attn", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+        c_int, c_int, c_ll, c_ll, c_ll, c_ll, c_float, c_int, c_void_p)
     sig("b200_attn_fwd", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
         c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_float, c_int, c_ll, c_void_p, c_void_p)
     sig("b200_attn_bwd", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,

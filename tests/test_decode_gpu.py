@@ -1,0 +1,98 @@
+"""Decode attention kernel and GPU generation against fp32 restatements."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("D,Hq,Hkv", [(128, 16, 8), (128, 8, 8), (64, 16, 4), (64, 32, 4), (128, 4, 1)])
+def test_decode_attention_matches_reference(D, Hq, Hkv):
+    from research_b200.ops import native
+    from research_b200.ops.decode import decode_attention, decode_attention_reference
+
+    torch.manual_seed(0)
+    B, rows = 5, 700
+    q = torch.randn(B, Hq, D, device="cuda").bfloat16()
+    # caches as views into a wider packed buffer, like the paged pool
+    kc = torch.randn(B, rows, Hkv, D, device="cuda").bfloat16()
+    vc = torch.randn(B, rows, Hkv, D, device="cuda").bfloat16()
+    lengths = torch.tensor([1, 17, 256, 699, 700], device="cuda", dtype=torch.int32)
+    for lo in (None, torch.tensor([0, 3, 100, 650, 0], device="cuda", dtype=torch.int32)):
+        out = decode_attention(q, kc, vc, lengths, lo)
+        ref = decode_attention_reference(q, kc, vc, lengths, lo)
+        native.check_status()
+        assert out.shape == (B, Hq * D)
+        assert torch.allclose(out.float(), ref.float(), atol=2e-2, rtol=2e-2), (out.float() - ref.float()).abs().max()
+
+
+def test_decode_attention_empty_window_gives_zeros():
+    from research_b200.ops.decode import decode_attention
+
+    q = torch.randn(2, 4, 64, device="cuda").bfloat16()
+    kc = torch.randn(2, 64, 4, 64, device="cuda").bfloat16()
+    vc = torch.randn(2, 64, 4, 64, device="cuda").bfloat16()
+    out = decode_attention(q, kc, vc, torch.tensor([0, 5], device="cuda", dtype=torch.int32),
+                           torch.tensor([0, 9], device="cuda", dtype=torch.int32))
+    assert torch.count_nonzero(out) == 0
+
+
+def test_generation_native_decode_matches_masked_attention(monkeypatch):
+    """Teacher-forced logits with the native prefill/decode kernels against the dense masked-attention path."""
+
+    from research_b200.config import run_spec_from_mapping
+    from research_b200.infer import generation
+    from research_b200.ops import native
+    from research_b200.runtime.trainer import Trainer
+
+    raw = {
+        "run": {"id": "gen-parity"},
+        "model": {"name": "decoder", "variant": "t", "vocab_size": 512, "hidden_size": 256, "intermediate_size": 512,
+                  "num_layers": 2, "num_heads": 4, "n_kv_heads": 2, "max_seq_len": 512, "init": "normal_0.02"},
+        "optimizer": {"name": "adamw", "schedule": {"peak_lr": 1e-3}},
+        "data": {"train_manifest": "unused.json"},
+        "training": {"seq_len": 256, "global_batch_size": 2, "target_tokens": 2 * 256 * 4, "precision": "bf16"},
+    }
+    trainer = Trainer(run_spec_from_mapping(raw), build_data=False)
+    model = trainer.result.model
+    prompts = torch.randint(0, 512, (3, 200), device="cuda", dtype=torch.int32)
+    follow = torch.randint(0, 512, (3, 6), device="cuda", dtype=torch.int32)
+
+    class _NoNative(generation.PagedKVCache):
+        def update_and_attend(self, layer, q, k, v, positions, window):
+            B, T = positions.shape
+            kc, vc = self._flat(self.k, layer), self._flat(self.v, layer)
+            idx = positions.long()
+            b_idx = torch.arange(B, device=q.device)[:, None].expand(B, T)
+            kc[b_idx, idx] = k.to(kc.dtype)
+            vc[b_idx, idx] = v.to(vc.dtype)
+            end = int(positions.max().item()) + 1
+            kpos = torch.arange(end, device=q.device)
+            allowed = kpos[None, None, :] <= idx[:, :, None]
+            return generation._masked_attention(q, kc[:, :end], vc[:, :end], allowed)
+
+    def teacher_forced(cache_cls):
+        monkeypatch.setattr(generation, "PagedKVCache", cache_cls)
+        cache = generation.init_kv_cache(model, 3, 256)
+        pos = torch.arange(200, device="cuda", dtype=torch.int32).expand(3, 200).contiguous()
+        outs = []
+        with torch.no_grad():
+            outs.append(model.run_with_cache(prompts, pos, cache)[:, -1].float())
+            cache.advance(pos)
+            for t in range(follow.shape[1]):
+                p1 = torch.full((3, 1), 200 + t, device="cuda", dtype=torch.int32)
+                outs.append(model.run_with_cache(follow[:, t:t + 1], p1, cache)[:, -1].float())
+                cache.advance(p1)
+        return torch.stack(outs)
+
+    model.eval()
+    fast = teacher_forced(generation.PagedKVCache)
+    native.check_status()
+    slow = teacher_forced(_NoNative)
+    lp_fast, lp_slow = torch.log_softmax(fast, -1), torch.log_softmax(slow, -1)
+    assert (lp_fast - lp_slow).abs().max().item() < 5e-2, (lp_fast - lp_slow).abs().max().item()
+    # and the sampling loop runs end to end on the native path
+    monkeypatch.setattr(generation, "PagedKVCache", generation.PagedKVCache)
+    res = generation.generate_tokens(model, prompts, max_new_tokens=8, temperature=1.0, top_k=50, seed=0)
+    native.check_status()
+    assert len(res.generated_ids) == 3 and all(len(g) == 8 for g in res.generated_ids)
