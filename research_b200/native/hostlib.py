@@ -38,6 +38,13 @@ def load():
         lib.b200h_gather_windows.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p,
                                              ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]
         lib.b200h_gather_windows.restype = ctypes.c_int
+        if hasattr(lib, "b200h_fd_serve"):
+            lib.b200h_fd_serve.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.c_int]
+            lib.b200h_fd_serve.restype = ctypes.c_int
+            lib.b200h_fd_serve_join.argtypes = [ctypes.c_int]
+            lib.b200h_fd_serve_join.restype = ctypes.c_int
+            lib.b200h_fd_fetch.argtypes = [ctypes.c_char_p, ctypes.c_int]
+            lib.b200h_fd_fetch.restype = ctypes.c_int
         _lib = lib
     return _lib
 

@@ -1,0 +1,338 @@
+// Communication runtime for one node: device-memory arenas that every local rank can map (CUDA virtual
+// memory management with POSIX file-descriptor handles), and the two pull collectives built on them.
+//
+//   b200c_vmm_alloc / import / free   one physical allocation per rank, exported as a descriptor that the
+//                                     peers import and map read-write (the descriptor travels through the
+//                                     unix-socket broker of the host library)
+//   b200c_reduce_scatter_pull         out = scale * sum_r src_r  for the slice this rank owns, reading the
+//                                     peers' fp32 gradient arenas over NVLink in a fixed rank order
+//                                     (deterministic), with the sum of squares of the result for the
+//                                     gradient norm folded into the same pass
+//   b200c_all_gather_pull             every rank copies the peers' shards into its full buffer
+//
+// Cross-GPU ordering uses per-rank flag blocks inside the arenas (comm.cuh): a kernel announces "my buffer
+// holds epoch e" to every peer, waits (bounded) for the same from them before the first remote read, and
+// its last CTA announces "done reading" and waits (bounded) until every peer has finished reading this
+// rank's buffer, so the buffer may be overwritten as soon as the kernel has ended.
+//
+// Counterparts in the reference: third_party/ThunderKittens/include/types/system/vmm.cuh:15-93 (arena),
+// ipc.cuh:59-139 (handle exchange), kernels/parallel/reduce_scatter/reduce_scatter.cu:8-55 and
+// all_gather/all_gather.cu:8-51 (NVLS versions of the two collectives).
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "comm.cuh"
+
+using namespace b200comm;
+
+namespace {
+
+template <typename Fn>
+Fn driver_fn(const char* name) {
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint(name, &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+    return nullptr;
+  return reinterpret_cast<Fn>(p);
+}
+
+struct Driver {
+  CUresult (*getGranularity)(size_t*, const CUmemAllocationProp*, CUmemAllocationGranularity_flags) = nullptr;
+  CUresult (*create)(CUmemGenericAllocationHandle*, size_t, const CUmemAllocationProp*, unsigned long long) = nullptr;
+  CUresult (*release)(CUmemGenericAllocationHandle) = nullptr;
+  CUresult (*reserve)(CUdeviceptr*, size_t, size_t, CUdeviceptr, unsigned long long) = nullptr;
+  CUresult (*addressFree)(CUdeviceptr, size_t) = nullptr;
+  CUresult (*map)(CUdeviceptr, size_t, size_t, CUmemGenericAllocationHandle, unsigned long long) = nullptr;
+  CUresult (*unmap)(CUdeviceptr, size_t) = nullptr;
+  CUresult (*setAccess)(CUdeviceptr, size_t, const CUmemAccessDesc*, size_t) = nullptr;
+  CUresult (*exportHandle)(void*, CUmemGenericAllocationHandle, CUmemAllocationHandleType, unsigned long long) = nullptr;
+  CUresult (*importHandle)(CUmemGenericAllocationHandle*, void*, CUmemAllocationHandleType) = nullptr;
+  bool ok = false;
+};
+
+const Driver& driver() {
+  static Driver d;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    d.getGranularity = driver_fn<decltype(d.getGranularity)>("cuMemGetAllocationGranularity");
+    d.create = driver_fn<decltype(d.create)>("cuMemCreate");
+    d.release = driver_fn<decltype(d.release)>("cuMemRelease");
+    d.reserve = driver_fn<decltype(d.reserve)>("cuMemAddressReserve");
+    d.addressFree = driver_fn<decltype(d.addressFree)>("cuMemAddressFree");
+    d.map = driver_fn<decltype(d.map)>("cuMemMap");
+    d.unmap = driver_fn<decltype(d.unmap)>("cuMemUnmap");
+    d.setAccess = driver_fn<decltype(d.setAccess)>("cuMemSetAccess");
+    d.exportHandle = driver_fn<decltype(d.exportHandle)>("cuMemExportToShareableHandle");
+    d.importHandle = driver_fn<decltype(d.importHandle)>("cuMemImportFromShareableHandle");
+    d.ok = d.getGranularity && d.create && d.release && d.reserve && d.addressFree && d.map && d.unmap &&
+           d.setAccess && d.exportHandle && d.importHandle;
+  }
+  return d;
+}
+
+CUmemAllocationProp arena_prop(int dev) {
+  CUmemAllocationProp prop = {};
+  prop.type = CU_MEM_ALLOCATION_TYPE_PINNED;
+  prop.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  prop.location.id = dev;
+  prop.requestedHandleTypes = CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR;
+  return prop;
+}
+
+int map_rw(const Driver& d, CUmemGenericAllocationHandle h, size_t padded, int dev, void** out) {
+  CUdeviceptr va = 0;
+  if (d.reserve(&va, padded, 0, 0, 0) != CUDA_SUCCESS) return -12;
+  if (d.map(va, padded, 0, h, 0) != CUDA_SUCCESS) {
+    d.addressFree(va, padded);
+    return -13;
+  }
+  CUmemAccessDesc acc = {};
+  acc.location.type = CU_MEM_LOCATION_TYPE_DEVICE;
+  acc.location.id = dev;
+  acc.flags = CU_MEM_ACCESS_FLAGS_PROT_READWRITE;
+  if (d.setAccess(va, padded, &acc, 1) != CUDA_SUCCESS) {
+    d.unmap(va, padded);
+    d.addressFree(va, padded);
+    return -14;
+  }
+  *out = reinterpret_cast<void*>(va);
+  return 0;
+}
+
+struct PeerPtrs {
+  const void* src[kMaxPeers];
+  FlagBlock* flags[kMaxPeers];
+};
+
+// Prologue shared by the pull kernels: announce, then wait for every peer's announcement.
+__device__ __forceinline__ bool announce_and_wait_ready(const PeerPtrs& pp, int world, int rank, uint32_t epoch,
+                                                        int* status, int* s_ok) {
+  if (threadIdx.x == 0) *s_ok = 1;
+  __syncthreads();
+  if (blockIdx.x == 0 && threadIdx.x < world && (int)threadIdx.x != rank) {
+    __threadfence_system();
+    st_release_sys(&pp.flags[threadIdx.x]->ready[rank], epoch);
+  }
+  if (threadIdx.x < world && (int)threadIdx.x != rank) {
+    if (!wait_sys(&pp.flags[rank]->ready[threadIdx.x], epoch, status, ERR_PEER_READY)) *s_ok = 0;
+  }
+  __syncthreads();
+  return *s_ok != 0;
+}
+
+// Epilogue: the CTA that finishes last tells every peer that this rank is done reading, then waits until every
+// peer is done reading this rank's buffer.  `counter` must be zero on entry and is left zero.
+__device__ __forceinline__ void finish_and_wait_done(const PeerPtrs& pp, int world, int rank, uint32_t epoch,
+                                                     uint32_t* counter, int* status) {
+  __shared__ int s_last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    s_last = atomicAdd(counter, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  if (threadIdx.x < world && (int)threadIdx.x != rank) {
+    st_release_sys(&pp.flags[threadIdx.x]->done[rank], epoch);
+    wait_sys(&pp.flags[rank]->done[threadIdx.x], epoch, status, ERR_PEER_DONE);
+  }
+  if (threadIdx.x == 0) *counter = 0u;
+}
+
+__global__ void __launch_bounds__(512)
+reduce_scatter_pull_kernel(const PeerPtrs pp, float* __restrict__ out, long long n4, float scale,
+                           float* __restrict__ sumsq, float* __restrict__ partials, uint32_t* counter, int world,
+                           int rank, uint32_t epoch, int* status) {
+  __shared__ int s_ok;
+  __shared__ float s_red[16];
+  const bool ok = announce_and_wait_ready(pp, world, rank, epoch, status, &s_ok);
+  float ss = 0.f;
+  if (ok) {
+    float4* o4 = reinterpret_cast<float4*>(out);
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int r = 0; r < kMaxPeers; ++r) {
+        if (r < world) {
+          const float4 v = reinterpret_cast<const float4*>(pp.src[r])[i];
+          acc.x += v.x;
+          acc.y += v.y;
+          acc.z += v.z;
+          acc.w += v.w;
+        }
+      }
+      acc.x *= scale;
+      acc.y *= scale;
+      acc.z *= scale;
+      acc.w *= scale;
+      o4[i] = acc;
+      ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+    }
+  }
+  // deterministic sum of squares: per-CTA partials, added up in CTA order by the last CTA (below)
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+  if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) t += s_red[w];
+    partials[blockIdx.x] = t;
+  }
+  __shared__ int s_last;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    s_last = atomicAdd(counter, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (sumsq) {
+      float t = 0.f;
+      for (unsigned b = 0; b < gridDim.x; ++b) t += reinterpret_cast<volatile float*>(partials)[b];
+      *sumsq += t;
+    }
+    *counter = 0u;
+  }
+  if (threadIdx.x < world && (int)threadIdx.x != rank) {
+    st_release_sys(&pp.flags[threadIdx.x]->done[rank], epoch);
+    wait_sys(&pp.flags[rank]->done[threadIdx.x], epoch, status, ERR_PEER_DONE);
+  }
+}
+
+__global__ void __launch_bounds__(512)
+all_gather_pull_kernel(const PeerPtrs pp, uint4* __restrict__ dst, long long n16_per_rank, uint32_t* counter,
+                       int world, int rank, uint32_t epoch, int copy_self, int* status) {
+  __shared__ int s_ok;
+  const bool ok = announce_and_wait_ready(pp, world, rank, epoch, status, &s_ok);
+  if (ok) {
+    const long long total = n16_per_rank * world;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+      // start each rank at a different peer so that the pulls spread over the links
+      const int r = (int)((i / n16_per_rank + rank + 1) % world);
+      const long long j = i % n16_per_rank;
+      if (r == rank && !copy_self) continue;
+      dst[(long long)r * n16_per_rank + j] = reinterpret_cast<const uint4*>(pp.src[r])[j];
+    }
+  }
+  finish_and_wait_done(pp, world, rank, epoch, counter, status);
+}
+
+int grid_for_bytes(long long items, int block) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  long long b = (items + block - 1) / block;
+  const long long cap = (long long)sms * 2;
+  if (b > cap) b = cap;
+  return b < 1 ? 1 : (int)b;
+}
+
+}  // namespace
+
+extern "C" {
+
+// Allocates `bytes` (rounded up to the allocation granularity, returned in *padded) of device memory on the
+// current device, mapped read-write, and exports it as a POSIX file descriptor in *fd (the caller closes it).
+int b200c_vmm_alloc(unsigned long long bytes, void** ptr, int* fd, unsigned long long* padded) {
+  const Driver& d = driver();
+  if (!d.ok) return -3;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -10;
+  cudaFree(nullptr);  // make sure the primary context exists
+  CUmemAllocationProp prop = arena_prop(dev);
+  size_t gran = 0;
+  if (d.getGranularity(&gran, &prop, CU_MEM_ALLOC_GRANULARITY_RECOMMENDED) != CUDA_SUCCESS || gran == 0) return -11;
+  const size_t size = (static_cast<size_t>(bytes) + gran - 1) / gran * gran;
+  CUmemGenericAllocationHandle h;
+  if (d.create(&h, size, &prop, 0) != CUDA_SUCCESS) return -15;
+  int rc = map_rw(d, h, size, dev, ptr);
+  if (rc == 0) {
+    int out_fd = -1;
+    if (d.exportHandle(&out_fd, h, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0) != CUDA_SUCCESS) {
+      d.unmap(reinterpret_cast<CUdeviceptr>(*ptr), size);
+      d.addressFree(reinterpret_cast<CUdeviceptr>(*ptr), size);
+      rc = -16;
+    } else {
+      *fd = out_fd;
+      *padded = size;
+    }
+  }
+  d.release(h);  // the mapping keeps the memory alive
+  return rc;
+}
+
+// Maps a peer's allocation (descriptor received through the broker) read-write into this process.
+int b200c_vmm_import(int fd, unsigned long long padded, void** ptr) {
+  const Driver& d = driver();
+  if (!d.ok) return -3;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -10;
+  cudaFree(nullptr);
+  CUmemGenericAllocationHandle h;
+  if (d.importHandle(&h, reinterpret_cast<void*>(static_cast<uintptr_t>(fd)), CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR) !=
+      CUDA_SUCCESS)
+    return -17;
+  const int rc = map_rw(d, h, static_cast<size_t>(padded), dev, ptr);
+  d.release(h);
+  return rc;
+}
+
+int b200c_vmm_free(void* ptr, unsigned long long padded) {
+  const Driver& d = driver();
+  if (!d.ok) return -3;
+  if (d.unmap(reinterpret_cast<CUdeviceptr>(ptr), static_cast<size_t>(padded)) != CUDA_SUCCESS) return -18;
+  if (d.addressFree(reinterpret_cast<CUdeviceptr>(ptr), static_cast<size_t>(padded)) != CUDA_SUCCESS) return -19;
+  return 0;
+}
+
+int b200c_flag_block_bytes() { return static_cast<int>(sizeof(FlagBlock)); }
+
+// src[r]: rank r's copy of the slice this rank owns (n fp32, n % 4 == 0, 16-byte aligned); flags[r]: rank r's
+// flag block of this channel, as mapped here.  scratch: uint32 counter (zero) followed by >= 512 floats.
+int b200c_reduce_scatter_pull(const void* const* src, void* out, long long n, float scale, void* sumsq,
+                              void* const* flags, int world, int rank, unsigned epoch, void* scratch, int* status,
+                              void* stream) {
+  if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world || n <= 0 || (n & 3)) return -2;
+  PeerPtrs pp = {};
+  for (int r = 0; r < world; ++r) {
+    if ((reinterpret_cast<uintptr_t>(src[r]) & 15) || !flags[r]) return -1;
+    pp.src[r] = src[r];
+    pp.flags[r] = static_cast<FlagBlock*>(flags[r]);
+  }
+  if (reinterpret_cast<uintptr_t>(out) & 15) return -1;
+  uint32_t* counter = static_cast<uint32_t*>(scratch);
+  float* partials = reinterpret_cast<float*>(counter + 4);
+  const int grid = grid_for_bytes(n / 4, 512);
+  reduce_scatter_pull_kernel<<<grid, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      pp, static_cast<float*>(out), n / 4, scale, static_cast<float*>(sumsq), partials, counter, world, rank, epoch,
+      status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// src[r]: rank r's shard (bytes_per_rank bytes, multiple of 16); dst: this rank's full buffer of world shards.
+// copy_self = 0 when this rank's shard already sits at its place in dst.
+int b200c_all_gather_pull(const void* const* src, void* dst, long long bytes_per_rank, void* const* flags, int world,
+                          int rank, unsigned epoch, int copy_self, void* scratch, int* status, void* stream) {
+  if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world || bytes_per_rank <= 0 || (bytes_per_rank & 15))
+    return -2;
+  PeerPtrs pp = {};
+  for (int r = 0; r < world; ++r) {
+    if ((reinterpret_cast<uintptr_t>(src[r]) & 15) || !flags[r]) return -1;
+    pp.src[r] = src[r];
+    pp.flags[r] = static_cast<FlagBlock*>(flags[r]);
+  }
+  if (reinterpret_cast<uintptr_t>(dst) & 15) return -1;
+  const long long n16 = bytes_per_rank / 16;
+  const int grid = grid_for_bytes(n16 * world, 512);
+  all_gather_pull_kernel<<<grid, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      pp, static_cast<uint4*>(dst), n16, static_cast<uint32_t*>(scratch), world, rank, epoch, copy_self, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // extern "C"

@@ -1,0 +1,99 @@
+"""Descriptor broker (CPU, two processes) and symmetric-arena collectives (GPU ranks as child processes)."""
+
+import os
+import subprocess
+import sys
+import tempfile
+from pathlib import Path
+
+import pytest
+import torch
+
+from tests.helpers import run_gloo
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _broker_worker(rank: int, world: int, tmp: str) -> None:
+    import torch.distributed as dist
+
+    from research_b200.parallel.symmetric import exchange_descriptors
+
+    path = os.path.join(tmp, f"payload-{rank}.txt")
+    with open(path, "w") as f:
+        f.write(f"hello from rank {rank}")
+    fd = os.open(path, os.O_RDONLY)
+    fds = exchange_descriptors(dist.group.WORLD, fd, tag="test")
+    assert len(fds) == world
+    for r, got in enumerate(fds):
+        os.lseek(got, 0, os.SEEK_SET)
+        assert os.read(got, 64).decode() == f"hello from rank {r}"
+        if r != rank:
+            os.close(got)
+    os.close(fd)
+
+
+def test_descriptor_broker_passes_open_files_between_ranks(tmp_path):
+    run_gloo(3, _broker_worker, str(tmp_path))
+
+
+def test_descriptor_fetch_gives_up_without_a_server(tmp_path):
+    from research_b200.native import hostlib
+
+    host = hostlib.load()
+    assert host is not None
+    rc = host.b200h_fd_fetch(str(tmp_path / "nobody.sock").encode(), 200)
+    assert rc < 0  # -ETIMEDOUT / -ENOENT path: bounded, no hang
+
+
+_GPU_SCRIPT = r"""
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[1])
+from research_b200.ops import native
+from research_b200.parallel.symmetric import SymmetricArena
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+n = 1 << 20
+arena = SymmetricArena(dist.group.WORLD, world * n * 4 + world * n * 2 + 4096)
+grads, g_off = arena.carve(world * n, torch.float32)
+weights, w_off = arena.carve(world * n, torch.bfloat16)
+for it in range(3):
+    torch.manual_seed(100 * it + rank)
+    grads.copy_(torch.randn(world * n, device="cuda"))
+    ref = grads.clone()
+    dist.all_reduce(ref)
+    ref = ref[rank * n:(rank + 1) * n] * 0.5
+    sumsq = torch.zeros(1, device="cuda")
+    arena.reduce_scatter(g_off, n, scale=0.5, sumsq=sumsq)
+    native.check_status()
+    got = grads[rank * n:(rank + 1) * n]
+    assert torch.allclose(got, ref, atol=1e-5, rtol=1e-5), (got - ref).abs().max().item()
+    assert abs(sumsq.item() - ref.double().pow(2).sum().item()) <= 1e-3 * ref.double().pow(2).sum().item()
+    weights.zero_()
+    weights[rank * n:(rank + 1) * n] = (rank + 1 + it)
+    arena.all_gather(w_off, n * 2)
+    native.check_status()
+    want = torch.arange(1, world + 1, device="cuda").repeat_interleave(n).to(torch.bfloat16) + it
+    assert torch.equal(weights, want)
+torch.cuda.synchronize()
+dist.barrier()
+arena.close()
+dist.destroy_process_group()
+print("RANK_OK", rank)
+"""
+
+
+@pytest.mark.gpu
+def test_symmetric_arena_collectives_on_all_visible_gpus(tmp_path):
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    script = tmp_path / "arena_ranks.py"
+    script.write_text(_GPU_SCRIPT)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", "29731", str(script), str(ROOT)]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    assert proc.stdout.count("RANK_OK") == world
