@@ -17,6 +17,8 @@ Sections group parameters that share an optimizer backend and the same set of gr
 
 from __future__ import annotations
 
+import os
+
 import math
 from dataclasses import dataclass, field
 from typing import Any
@@ -155,10 +157,37 @@ class ParamStore:
             self.sections.append(sec)
         self.total = cursor
 
+    def _symmetric_group(self):
+        """The process group whose ranks exchange shards through peer memory, or None (NCCL / gloo path).
+
+        Used when the tensors live on CUDA, exactly one mesh axis shards the store, and the environment does not
+        switch it off (``RESEARCH_B200_PEER_COLLECTIVES=0``)."""
+
+        if self.device.type != "cuda" or os.environ.get("RESEARCH_B200_PEER_COLLECTIVES", "1") == "0":
+            return None
+        axes = {sec.shard_axis for sec in self.sections if sec.shard_axis is not None and sec.backend != "frozen"}
+        if len(axes) != 1:
+            return None
+        axis = axes.pop()
+        group = self.mesh.group(axis)
+        if group is None or self.mesh.size(axis) < 2 or self.mesh.size(axis) > 8:
+            return None
+        return group
+
     def _materialise(self) -> None:
         dev = self.device
-        self.compute_arena = torch.zeros(self.total, dtype=self.compute_dtype, device=dev)
-        self.grad_arena = torch.zeros(self.total, dtype=torch.float32, device=dev)
+        self.arena = None
+        group = self._symmetric_group()
+        if group is not None:
+            from research_b200.parallel.symmetric import SymmetricArena
+
+            esize = torch.empty((), dtype=self.compute_dtype).element_size()
+            self.arena = SymmetricArena(group, self.total * (4 + esize) + 8192, device=dev, tag="params")
+            self.grad_arena, self._grad_off = self.arena.carve(self.total, torch.float32)
+            self.compute_arena, self._compute_off = self.arena.carve(self.total, self.compute_dtype)
+        else:
+            self.compute_arena = torch.zeros(self.total, dtype=self.compute_dtype, device=dev)
+            self.grad_arena = torch.zeros(self.total, dtype=torch.float32, device=dev)
         separate_master = self.compute_dtype != torch.float32
         for sec in self.sections:
             lo, hi = self.local_master_range(sec)
@@ -237,7 +266,10 @@ class ParamStore:
                     n, r = self.mesh.size(axis), self.mesh.coord(axis)
                     per = sec.length // n
                     out = buf[r * per:(r + 1) * per]
-                    if buf.is_cuda:
+                    if self.arena is not None:
+                        # one kernel: pull the peers' copies of the local slice over NVLink and sum in rank order
+                        self.arena.reduce_scatter(self._grad_off + 4 * sec.start, per, channel=0)
+                    elif buf.is_cuda:
                         dist.reduce_scatter_tensor(out, buf, group=group)
                     else:
                         dist.all_reduce(buf, group=group)
@@ -256,7 +288,11 @@ class ParamStore:
             n, r = self.shard_coords(sec)[1], self.shard_coords(sec)[0]
             buf = self.compute_arena[sec.start:sec.start + sec.length]
             per = sec.length // n
-            dist.all_gather_into_tensor(buf, buf[r * per:(r + 1) * per].clone(), group=group)
+            if self.arena is not None:
+                esize = buf.element_size()
+                self.arena.all_gather(self._compute_off + esize * sec.start, per * esize, channel=1)
+            else:
+                dist.all_gather_into_tensor(buf, buf[r * per:(r + 1) * per].clone(), group=group)
 
     def describe(self) -> dict[str, Any]:
         return {
