@@ -97,3 +97,92 @@ def test_symmetric_arena_collectives_on_all_visible_gpus(tmp_path):
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     assert proc.stdout.count("RANK_OK") == world
+
+
+_TP_SCRIPT = r"""
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[1])
+from research_b200.ops import native
+from research_b200.parallel.tensor_fused import TensorParallelFusion, column_linear, row_linear
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+B, S, H, I = 2, 512 * world, 512, 1024          # I = this rank's slice of the intermediate size
+s_local = S // world
+fusion = TensorParallelFusion(dist.group.WORLD, max_shard_elems=B * s_local * max(H, I), max_out_elems=B * s_local * max(H, I))
+
+def gather_seq(t):   # [B, S/tp, C] -> [B, S, C]
+    out = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(out, t.contiguous())
+    return torch.cat(out, dim=1)
+
+def scatter_sum_seq(t):   # [B, S, C] partial -> [B, S/tp, C] summed
+    full = t.float().clone()
+    dist.all_reduce(full)
+    return full[:, rank * s_local:(rank + 1) * s_local]
+
+for it in range(3):
+    torch.manual_seed(1000 * it + rank)
+    x = (torch.randn(B, s_local, H, device="cuda") * 0.5).bfloat16()
+    w1 = (torch.randn(I, H, device="cuda") * 0.05).bfloat16()
+    w2 = (torch.randn(H, I, device="cuda") * 0.05).bfloat16()
+    # raw kernels, both operand layouts
+    y, x_full = fusion.gather_gemm(x.reshape(B * s_local, H), w1, b_mn=False, chunk_rows=s_local)
+    native.check_status()
+    xg = gather_seq(x).reshape(B * S, H)
+    assert torch.equal(x_full, xg), "gathered operand differs"
+    ref = xg.float() @ w1.float().t()
+    assert torch.allclose(y.float(), ref, atol=3e-2, rtol=3e-2), (y.float() - ref).abs().max().item()
+    y_t, _ = fusion.gather_gemm(x.reshape(B * s_local, H), w1.t().contiguous(), b_mn=True, chunk_rows=s_local)
+    assert torch.allclose(y_t.float(), ref, atol=3e-2, rtol=3e-2)
+    h = (torch.randn(B, S, I, device="cuda") * 0.5).bfloat16()
+    z = fusion.gemm_scatter(h.reshape(B * S, I), w2, b_mn=False, chunk_rows=s_local)
+    native.check_status()
+    zref = scatter_sum_seq((h.float() @ w2.float().t())).reshape(B * s_local, H)
+    assert torch.allclose(z.float(), zref, atol=6e-2, rtol=3e-2), (z.float() - zref).abs().max().item()
+    # autograd chain: column-parallel then row-parallel, against the collective formulation in fp32
+    p1 = torch.nn.Parameter(w1.clone()); p2 = torch.nn.Parameter(w2.clone())
+    p1.main_grad = torch.zeros(I, H, device="cuda"); p2.main_grad = torch.zeros(H, I, device="cuda")
+    xr = x.clone().requires_grad_(True)
+    out = row_linear(torch.nn.functional.silu(column_linear(xr, p1, fusion)), p2, fusion)
+    g = (torch.randn_like(out.float()) * 0.1).bfloat16()
+    out.backward(g)
+    native.check_status()
+    xf = x.float().clone().requires_grad_(True)
+    w1f = w1.float().clone().requires_grad_(True); w2f = w2.float().clone().requires_grad_(True)
+    class _G(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, t): return gather_seq(t)
+        @staticmethod
+        def backward(ctx, d): return scatter_sum_seq(d)
+    class _S(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, t): return scatter_sum_seq(t)
+        @staticmethod
+        def backward(ctx, d): return gather_seq(d.contiguous())
+    ref_out = _S.apply(torch.nn.functional.silu(_G.apply(xf) @ w1f.t()) @ w2f.t())
+    ref_out.backward(g.float())
+    assert torch.allclose(out.float(), ref_out, atol=6e-2, rtol=5e-2), (out.float() - ref_out).abs().max().item()
+    assert torch.allclose(xr.grad.float(), xf.grad, atol=3e-2, rtol=5e-2), (xr.grad.float() - xf.grad).abs().max().item()
+    for mg, rg in ((p1.main_grad, w1f.grad), (p2.main_grad, w2f.grad)):
+        assert (mg - rg).abs().max().item() <= 0.03 * rg.abs().max().item() + 1e-3
+torch.cuda.synchronize()
+dist.barrier()
+dist.destroy_process_group()
+print("RANK_OK", rank)
+"""
+
+
+@pytest.mark.gpu
+def test_fused_tensor_parallel_gemms_match_collective_formulation(tmp_path):
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    script = tmp_path / "tp_ranks.py"
+    script.write_text(_TP_SCRIPT)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", "29733", str(script), str(ROOT)]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    assert proc.stdout.count("RANK_OK") == world
