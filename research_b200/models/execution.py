@@ -17,6 +17,7 @@ where ``fused`` is enabled and the tensors are CUDA bf16.
 
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import Any
 
@@ -263,6 +264,50 @@ class ExecutionContext:
         if self.sp:
             return reduce_scatter_dim(x, self.tp_group, 1)
         return all_reduce_sum(x, self.tp_group)
+
+    # ---- fused tensor-parallel linears ----------------------------------------------------------------
+    def _fusion_for(self, x: torch.Tensor, rows_local: int, width: int):
+        """The fused-GEMM workspace of the tp group, or None when the NCCL formulation must run.
+
+        Fused kernels need CUDA bf16 activations, sequence parallelism, shards in whole 128-row blocks and
+        64-column multiples; the workspace is (re)built collectively the first time a larger shard shows up."""
+
+        if not (self.fused and self.sp and x.is_cuda and x.dtype == torch.bfloat16 and Fn.use_native(x)):
+            return None
+        if os.environ.get("RESEARCH_B200_PEER_COLLECTIVES", "1") == "0" or self.tp_size > 8:
+            return None
+        if rows_local % 128 or width % 64:
+            return None
+        need = x.shape[0] * rows_local * width
+        ws = self.extras.get("tp_fusion")
+        if ws is None or ws.stage.numel() < need:
+            from research_b200.parallel.tensor_fused import TensorParallelFusion
+
+            ws = TensorParallelFusion(self.tp_group, max_shard_elems=need, max_out_elems=need, device=x.device)
+            self.extras["tp_fusion"] = ws
+        return ws
+
+    def column_linear(self, x: torch.Tensor, p: torch.Tensor) -> torch.Tensor:
+        """Column-parallel ``y = gather_seq(x) W^T`` for a sequence-parallel shard ``[B, S/tp, H]``."""
+
+        if self.tp_size > 1 and x.dim() == 3 and p.shape[0] % 64 == 0:
+            ws = self._fusion_for(x, x.shape[1], max(x.shape[2], 64))
+            if ws is not None:
+                from research_b200.parallel.tensor_fused import column_linear
+
+                return column_linear(x.contiguous(), p, ws)
+        return Fn.linear(self.gather_sequence(x), p)
+
+    def row_linear(self, h: torch.Tensor, p: torch.Tensor) -> torch.Tensor:
+        """Row-parallel ``y = reduce_scatter_seq(h W^T)`` for ``h`` ``[B, S, K/tp]``."""
+
+        if self.tp_size > 1 and h.dim() == 3 and h.shape[1] % self.tp_size == 0 and h.shape[2] % 64 == 0:
+            ws = self._fusion_for(h, h.shape[1] // self.tp_size, p.shape[0])
+            if ws is not None:
+                from research_b200.parallel.tensor_fused import row_linear
+
+                return row_linear(h, p, ws)
+        return self.reduce_scatter_sequence(Fn.linear(h, p))
 
     def gather_vocab(self, logits: torch.Tensor) -> torch.Tensor:
         return all_gather_dim(logits, self.tp_group, logits.dim() - 1) if self.tp_size > 1 else logits

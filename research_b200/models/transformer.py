@@ -106,10 +106,16 @@ class Attention(nn.Module):
         self.wgate = nn.Parameter(torch.empty(self.hq * D, self.hidden, dtype=torch.float32)) if cfg.gate else None
 
     def forward(self, x: torch.Tensor, inp: ForwardInputs, ex: ExecutionContext) -> torch.Tensor:
-        x = ex.gather_sequence(x)                       # SP: [B, S/tp, H] -> [B, S, H]
-        B, S = x.shape[0], x.shape[1]
-        x2 = x.reshape(B * S, self.hidden)
-        qkv = Fn.linear(x2, self.wqkv)
+        if self.wgate is None and ex.sp:
+            # SP: [B, S/tp, H] -> [B, S, 3 groups of local heads]; the row gather runs inside the GEMM kernel
+            qkv3 = ex.column_linear(x, self.wqkv)
+            B, S = qkv3.shape[0], qkv3.shape[1]
+            qkv, x2 = qkv3.reshape(B * S, -1), None
+        else:
+            x = ex.gather_sequence(x)                   # SP: [B, S/tp, H] -> [B, S, H]
+            B, S = x.shape[0], x.shape[1]
+            x2 = x.reshape(B * S, self.hidden)
+            qkv = Fn.linear(x2, self.wqkv)
         window = self.cfg.local_window if self.cfg.mask == "sliding_window" else None
         lo, hi = inp.bounds(window)
         o = ex.attention(qkv, self.q_norm, self.k_norm, inp.positions, B=B, S=S, hq=self.hq, hkv=self.hkv,
@@ -117,8 +123,7 @@ class Attention(nn.Module):
                          lo=lo, hi=hi)
         if self.wgate is not None:
             o = Fn.sigmoid_gate(o.reshape(B * S, -1), Fn.linear(x2, self.wgate)).view(B, S, -1)
-        out = Fn.linear(o, self.wo)
-        return ex.reduce_scatter_sequence(out)          # row-parallel partial sums -> SP shard
+        return ex.row_linear(o if o.dim() == 3 else o.view(B, S, -1), self.wo)  # partial sums -> SP shard
 
     # ---- inference -------------------------------------------------------------------------------
     def project_qkv(self, x: torch.Tensor, positions: torch.Tensor):
@@ -151,9 +156,8 @@ class SwiGLU(nn.Module):
         self.w_down = nn.Parameter(torch.empty(hidden, self.inter, dtype=torch.float32))
 
     def forward(self, x: torch.Tensor, ex: ExecutionContext) -> torch.Tensor:
-        x = ex.gather_sequence(x)
-        h = Fn.swiglu(Fn.linear(x, self.w_gate_up))
-        return ex.reduce_scatter_sequence(Fn.linear(h, self.w_down))
+        h = Fn.swiglu(ex.column_linear(x, self.w_gate_up))
+        return ex.row_linear(h, self.w_down)
 
 
 class DecoderBlock(nn.Module):

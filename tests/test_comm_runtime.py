@@ -186,3 +186,71 @@ def test_fused_tensor_parallel_gemms_match_collective_formulation(tmp_path):
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     assert proc.stdout.count("RANK_OK") == world
+
+
+_TRAIN_SCRIPT = r"""
+import json, os, sys, numpy as np, torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[1])
+from research_b200.config import run_spec_from_mapping
+from research_b200.contracts import Batch
+from research_b200.ops import native
+from research_b200.parallel.mesh import init_distributed
+from research_b200.runtime.trainer import Trainer
+axes, sizes, flags = json.loads(sys.argv[2]), json.loads(sys.argv[3]), json.loads(sys.argv[4])
+init_distributed()
+rank = dist.get_rank()
+raw = {
+    "run": {"id": "fused-parity"},
+    "model": {"name": "decoder", "variant": "t", "vocab_size": 1024, "hidden_size": 256, "intermediate_size": 512,
+              "num_layers": 2, "num_heads": 4, "n_kv_heads": 2, "max_seq_len": 512, "init": "normal_0.02"},
+    "optimizer": {"name": flags.get("optimizer", "adamw"), "grad_clip_norm": 1.0, "schedule": {"peak_lr": 1e-3}},
+    "data": {"train_manifest": "unused.json"},
+    "training": {"seq_len": 512, "global_batch_size": 4, "target_tokens": 4 * 512 * 8, "precision": "bf16"},
+    "mesh": {"axis_names": axes, "axis_sizes": sizes},
+    "parallelism": flags.get("parallelism", {}),
+}
+trainer = Trainer(run_spec_from_mapping(raw), build_data=False)
+rng = np.random.default_rng(0)
+losses = []
+for step in range(4):
+    ids = rng.integers(0, 1024, size=(4, 513)).astype(np.int32)
+    batch = Batch(input_ids=ids[:, :-1], target_ids=ids[:, 1:], loss_mask=np.ones((4, 512), dtype=bool))
+    m = trainer.train_on([batch])
+    losses.append(float(m.loss))
+native.check_status()
+if rank == 0:
+    print("LOSSES", json.dumps(losses))
+dist.barrier()
+dist.destroy_process_group()
+"""
+
+
+def _run_training(tmp_path, world, axes, sizes, flags, peer, port):
+    script = tmp_path / "train_ranks.py"
+    script.write_text(_TRAIN_SCRIPT)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", RESEARCH_B200_PEER_COLLECTIVES="1" if peer else "0")
+    import json
+
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), str(script), str(ROOT), json.dumps(axes),
+           json.dumps(sizes), json.dumps(flags)]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    line = [l for l in proc.stdout.splitlines() if l.startswith("LOSSES")][-1]
+    return json.loads(line.split(" ", 1)[1])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name,axes,sizes,flags", [
+    ("tp2", ["tp"], [2], {"parallelism": {"mode": "ddp", "tensor_parallel": True}}),
+    ("fsdp2_muon", ["fsdp"], [2], {"parallelism": {"mode": "fsdp"}, "optimizer": "muon"}),
+])
+def test_training_with_peer_memory_kernels_matches_nccl_path(tmp_path, name, axes, sizes, flags):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    fused = _run_training(tmp_path, 2, axes, sizes, flags, True, 29741)
+    plain = _run_training(tmp_path, 2, axes, sizes, flags, False, 29743)
+    assert len(fused) == len(plain) == 4
+    for a, b in zip(fused, plain):
+        assert abs(a - b) <= 2e-2 * max(1.0, abs(b)), (name, fused, plain)
+    assert fused[-1] < fused[0]
