@@ -1,9 +1,9 @@
 // Tensor-parallel GEMMs fused with their collective, for sm_100a and NVLink peer memory.
 //
 //   MODE_GATHER  (all-gather -> GEMM):  C = gather_rows(A_r) * op(B).  Every rank holds a row shard of A in its
-//       symmetric arena.  A few CTAs at the end of the grid are transfer CTAs: one thread each pulls remote
-//       128 x 64 boxes with TMA (plain loads from the peer's memory, no cluster multicast) through a
-//       shared-memory ring into the local gathered buffer and publishes one flag per 128-row block.  The
+//       symmetric arena.  The first few CTAs of the grid are transfer CTAs: four threads each run a pipeline
+//       that pulls remote 8 KB boxes with TMA (plain loads from the peer's memory, no cluster multicast)
+//       through a shared-memory ring into the local gathered buffer and publishes one flag per 128-row block.  The
 //       compute CTAs are the usual persistent tcgen05 pipeline; they walk the row blocks in arrival order
 //       (own rows first, read straight from the local shard, then rank+1, rank+2, ...) and their TMA producer
 //       waits on a block's flag only before the first load of a tile that needs it.  The transfer therefore
@@ -43,21 +43,28 @@ constexpr int NUM_THREADS = 32 * (2 + EPI_WARPS);
 constexpr int GROUP_M = 8;
 constexpr int MODE_GATHER = 1;
 constexpr int MODE_SCATTER = 2;
-constexpr int XFER_BUFS = 10;  // 16 KB boxes in flight per transfer CTA
+// transfer CTAs: XFER_PIPES issuing threads, each with its own ring of XFER_BUFS boxes of XFER_BOX_BYTES
+constexpr int XFER_PIPES = 4;
+constexpr int XFER_BUFS = 6;
 constexpr int XFER_LAG = XFER_BUFS - 2;
+constexpr int XFER_BOX_BYTES = 8192;
+constexpr int XFER_RING_BYTES = XFER_PIPES * XFER_BUFS * XFER_BOX_BYTES;
+constexpr int MAP_C = kMaxPeers;          // PeerMaps slots beyond the per-rank ones (gather mode)
+constexpr int MAP_OWN = kMaxPeers + 1;    //   own shard, swizzled, for the producer
+constexpr int MAP_FULL = kMaxPeers + 2;   //   gathered buffer, transfer geometry
 
 template <int BN>
 struct SmemLayout {
   static constexpr int B_TILE_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
   static constexpr int STAGING_OFF = STAGES * STAGE_BYTES;
-  static constexpr int BAR_OFF = STAGING_OFF + EPI_WARPS * 2 * STAGING_BYTES;
-  static constexpr int TOTAL = BAR_OFF + 256;
-  static_assert(XFER_BUFS * A_TILE_BYTES <= BAR_OFF, "transfer ring must fit below the barriers");
+  static constexpr int PIPE_END = STAGING_OFF + EPI_WARPS * 2 * STAGING_BYTES;
+  static constexpr int BAR_OFF = PIPE_END > XFER_RING_BYTES ? PIPE_END : XFER_RING_BYTES;
+  static constexpr int TOTAL = BAR_OFF + 512;
 };
 
 struct PeerMaps {
-  CUtensorMap m[kMaxPeers + 1];  // one per rank; the last slot carries C in gather mode
+  CUtensorMap m[kMaxPeers + 3];  // one per rank, then MAP_C / MAP_OWN / MAP_FULL
 };
 
 struct CommGemmParams {
@@ -66,6 +73,8 @@ struct CommGemmParams {
   int chunk_blocks;          // 128-row blocks per (batch, rank) stretch
   int blocks_per_rank;       // M / 128 / world
   int n_xfer;                // transfer CTAs (gather mode)
+  int copy_own;              // transfer CTAs also copy this rank's own rows into the gathered buffer
+  int xfer_cols, xfer_rows;  // box of the transfer maps: xfer_cols * xfer_rows * 2 == XFER_BOX_BYTES
   uint32_t epoch;
   uint32_t* row_flags;       // [M / 128] local flags, gather mode
   uint32_t* counter;         // zero on entry, left zero
@@ -95,8 +104,8 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* empty = full + STAGES;
   uint64_t* tfull = empty + STAGES;
   uint64_t* tempty = tfull + 2;
-  uint64_t* xbar = tempty + 2;  // XFER_BUFS barriers of the transfer ring
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xbar + XFER_BUFS);
+  uint64_t* xbar = tempty + 2;  // barriers of the transfer rings
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xbar + XFER_PIPES * XFER_BUFS);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   const AbortCtx ab{abort_flag, p.status};
 
@@ -122,7 +131,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(&tfull[a], 1);
       mbar_init(&tempty[a], EPI_WARPS);
     }
-    for (int i = 0; i < XFER_BUFS; ++i) mbar_init(&xbar[i], 1);
+    for (int i = 0; i < XFER_PIPES * XFER_BUFS; ++i) mbar_init(&xbar[i], 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -152,41 +161,52 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   if (is_xfer) {
     // ------------------------------------------------------------------ transfer CTA (gather mode)
-    if (threadIdx.x == 0) {
-      const int x = (int)blockIdx.x;
+    if (lane == 0 && warp < XFER_PIPES) {
+      // one pipeline per issuing thread: load a box from the owner's shard, store it into the gathered buffer
+      const int pipe = (int)blockIdx.x * XFER_PIPES + warp;
+      const int n_pipes = p.n_xfer * XFER_PIPES;
+      uint8_t* ring = smem + warp * XFER_BUFS * XFER_BOX_BYTES;
+      uint64_t* bar = xbar + warp * XFER_BUFS;
       const int remote_blocks = (p.world - 1) * p.blocks_per_rank;
-      // this CTA's blocks: logical indices blocks_per_rank + x, + n_xfer, ...; then a share of the own rows
-      int my_remote = remote_blocks > x ? (remote_blocks - x + p.n_xfer - 1) / p.n_xfer : 0;
-      int my_own = p.blocks_per_rank > x ? (p.blocks_per_rank - x + p.n_xfer - 1) / p.n_xfer : 0;
-      const long long total = (long long)(my_remote + my_own) * k_blocks;
+      // this pipeline's blocks: remote logical indices blocks_per_rank + pipe, + n_pipes, ...; then own rows
+      const int my_remote = remote_blocks > pipe ? (remote_blocks - pipe + n_pipes - 1) / n_pipes : 0;
+      const int my_own =
+          (p.copy_own && p.blocks_per_rank > pipe) ? (p.blocks_per_rank - pipe + n_pipes - 1) / n_pipes : 0;
+      const int col_boxes = p.K / p.xfer_cols, row_boxes = BM / p.xfer_rows;
+      const int boxes = col_boxes * row_boxes;  // per 128-row block
+      const long long total = (long long)(my_remote + my_own) * boxes;
+      auto locate = [&](long long i, int& owner, int& local, int& global, int& col, int& row, bool& last) {
+        const int blk = (int)(i / boxes), bx = (int)(i % boxes);
+        const int logical = blk < my_remote ? p.blocks_per_rank + pipe + blk * n_pipes : pipe + (blk - my_remote) * n_pipes;
+        map_block(p, logical, 0, owner, local, global);
+        col = (bx % col_boxes) * p.xfer_cols;
+        row = (bx / col_boxes) * p.xfer_rows;
+        last = bx == boxes - 1;
+      };
       bool ok = true;
       uint32_t ready_mask = 1u << p.rank;
       for (long long i = 0; i < total + XFER_LAG && ok; ++i) {
+        int owner, local, global, col, row;
+        bool last;
         if (i < total) {
-          const int blk = (int)(i / k_blocks), kb = (int)(i % k_blocks);
-          const int logical = blk < my_remote ? p.blocks_per_rank + x + blk * p.n_xfer : x + (blk - my_remote) * p.n_xfer;
-          int owner, local, global;
-          map_block(p, logical, 0, owner, local, global);
+          locate(i, owner, local, global, col, row, last);
           if (!(ready_mask >> owner & 1u)) {
             if (!wait_sys(&p.flags[p.rank]->ready[owner], p.epoch, p.status, ERR_PEER_READY)) { ok = false; break; }
             ready_mask |= 1u << owner;
           }
           const int buf = (int)(i % XFER_BUFS);
           if (i >= XFER_BUFS) tma_wait_group_read<1>();  // the store that last read this buffer is done
-          mbar_expect_tx(&xbar[buf], A_TILE_BYTES);
-          tma_load_3d(smem + buf * A_TILE_BYTES, &peers.m[owner], &xbar[buf], kb * BK, local * BM, 0);
+          mbar_expect_tx(&bar[buf], XFER_BOX_BYTES);
+          tma_load_3d(ring + buf * XFER_BOX_BYTES, &peers.m[owner], &bar[buf], col, local * BM + row, 0);
         }
         const long long j = i - XFER_LAG;
         if (j >= 0 && j < total) {
-          const int blk = (int)(j / k_blocks), kb = (int)(j % k_blocks);
-          const int logical = blk < my_remote ? p.blocks_per_rank + x + blk * p.n_xfer : x + (blk - my_remote) * p.n_xfer;
-          int owner, local, global;
-          map_block(p, logical, 0, owner, local, global);
+          locate(j, owner, local, global, col, row, last);
           const int buf = (int)(j % XFER_BUFS);
-          if (!mbar_wait(&xbar[buf], (uint32_t)(j / XFER_BUFS) & 1u, ab, ERR_WAIT_FULL)) { ok = false; break; }
-          tma_store_3d(&tmA, smem + buf * A_TILE_BYTES, kb * BK, global * BM, 0);
+          if (!mbar_wait(&bar[buf], (uint32_t)(j / XFER_BUFS) & 1u, ab, ERR_WAIT_FULL)) { ok = false; break; }
+          tma_store_3d(&peers.m[MAP_FULL], ring + buf * XFER_BOX_BYTES, col, global * BM + row, 0);
           tma_commit_group();
-          if (kb == k_blocks - 1) {
+          if (last) {
             // the whole row block has been issued: wait until it is in memory, then publish it
             tma_wait_group<0>();
             fence_proxy_async_all();
@@ -199,9 +219,9 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const uint64_t t0 = globaltimer_ns();
         while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
       }
-      // last transfer CTA: this rank has finished reading its peers' shards
+      // last pipeline to finish: this rank has finished reading its peers' shards
       __threadfence();
-      if (atomicAdd(p.counter, 1u) == (uint32_t)p.n_xfer - 1u) {
+      if (atomicAdd(p.counter, 1u) == (uint32_t)n_pipes - 1u) {
         *p.counter = 0u;
         for (int r = 0; r < p.world; ++r)
           if (r != p.rank) st_release_sys(&p.flags[r]->done[p.rank], p.epoch);
@@ -237,7 +257,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint8_t* sB = sA + A_TILE_BYTES;
           mbar_expect_tx(&full[s], L::STAGE_BYTES);
           if (own_shard)
-            tma_load_3d(sA, &peers.m[p.rank], &full[s], kb * BK, local * BM, 0);  // own rows: straight from the shard
+            tma_load_3d(sA, &peers.m[MAP_OWN], &full[s], kb * BK, local * BM, 0);  // own rows: straight from the shard
           else
             tma_load_3d(sA, &tmA, &full[s], kb * BK, global * BM, 0);
           if (!B_MN) {
@@ -314,7 +334,7 @@ comm_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
       const int out_row = (MODE == MODE_GATHER ? global : local) * BM + q * 32;
-      const CUtensorMap* out_map = MODE == MODE_GATHER ? &peers.m[kMaxPeers] : &peers.m[owner];
+      const CUtensorMap* out_map = MODE == MODE_GATHER ? &peers.m[MAP_C] : &peers.m[owner];
 #pragma unroll 1
       for (int j = 0; j < BN / 64; ++j) {
         const int col0 = n0 + j * 64;
@@ -413,6 +433,8 @@ int fill_common(CommGemmParams& p, int M, int N, int K, int world, int rank, int
   p.chunk_blocks = chunk_blocks;
   p.blocks_per_rank = blocks_per_rank;
   p.n_xfer = 0;
+  p.xfer_cols = p.xfer_rows = 0;
+  p.copy_own = 0;
   p.epoch = epoch;
   p.row_flags = nullptr;
   p.counter = static_cast<uint32_t*>(counter);
@@ -425,30 +447,40 @@ int fill_common(CommGemmParams& p, int M, int N, int K, int world, int rank, int
 
 // C[M,N] = gather(A shards)[M,K] * op(B).  a_shards[r]: rank r's [M/world, K] bf16 shard as mapped here
 // (a_shards[rank] is the local one); a_full: local [M,K] buffer the remote rows are gathered into (complete when
-// the kernel has ended, own rows included); B: [N,K] (b_mn = 0) or [K,N] (b_mn = 1); C: local [M,N] bf16.
+// the kernel has ended; own rows are copied too when copy_own is set, else they are the caller's job); B: [N,K] (b_mn = 0) or [K,N] (b_mn = 1); C: local [M,N] bf16.
 // row_flags: M/128 uint32 in local memory (values from earlier epochs are fine); counter: one zeroed uint32.
 extern "C" int b200_gemm_allgather(const void* const* a_shards, void* a_full, const void* B, void* C, int M, int N,
                                    int K, long long ldb, int b_mn, int world, int rank, int chunk_blocks, int n_xfer,
-                                   void* row_flags, void* counter, void* const* flags, unsigned epoch, int* status,
+                                   int copy_own, void* row_flags, void* counter, void* const* flags, unsigned epoch, int* status,
                                    void* stream) {
   using namespace b200host;
   CommGemmParams p;
   int rc = fill_common(p, M, N, K, world, rank, chunk_blocks, epoch, flags, counter, status);
   if (rc) return rc;
   const int sms = sm_count();
-  if (n_xfer <= 0) n_xfer = 8;
+  if (n_xfer <= 0) n_xfer = 16;
   if (n_xfer > sms / 4) n_xfer = sms / 4;
   p.n_xfer = n_xfer;
+  p.copy_own = copy_own;
   p.row_flags = static_cast<uint32_t*>(row_flags);
   const CUtensorMapDataType bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const int BN = N > 128 ? 256 : 128;
   CUtensorMap tmA, tmB;
   PeerMaps peers = {};
+  // transfer boxes: rows as wide as the column count allows (up to 512 bytes), no swizzle
+  p.xfer_cols = K % 256 == 0 ? 256 : (K % 128 == 0 ? 128 : 64);
+  p.xfer_rows = XFER_BOX_BYTES / 2 / p.xfer_cols;
   if ((rc = make_map_3d(&tmA, bf, a_full, K, M, 1, (uint64_t)K * 2, 0, BK, BM))) return rc;
   for (int r = 0; r < world; ++r)
-    if ((rc = make_map_3d(&peers.m[r], bf, a_shards[r], K, M / world, 1, (uint64_t)K * 2, 0, BK, BM))) return rc;
-  if (world == kMaxPeers) return RC_BAD_SHAPE;  // the last map slot carries C in this mode
-  if ((rc = make_map_3d(&peers.m[kMaxPeers], bf, C, N, M, 1, (uint64_t)N * 2, 0, 64, 32))) return rc;
+    if ((rc = make_map_3d(&peers.m[r], bf, a_shards[r], K, M / world, 1, (uint64_t)K * 2, 0, p.xfer_cols, p.xfer_rows,
+                          CU_TENSOR_MAP_SWIZZLE_NONE)))
+      return rc;
+  if ((rc = make_map_3d(&peers.m[MAP_FULL], bf, a_full, K, M, 1, (uint64_t)K * 2, 0, p.xfer_cols, p.xfer_rows,
+                        CU_TENSOR_MAP_SWIZZLE_NONE)))
+    return rc;
+  if ((rc = make_map_3d(&peers.m[MAP_OWN], bf, a_shards[rank], K, M / world, 1, (uint64_t)K * 2, 0, BK, BM))) return rc;
+  if ((rc = make_map_3d(&peers.m[MAP_C], bf, C, N, M, 1, (uint64_t)N * 2, 0, 64, 32))) return rc;
+  if (p.xfer_cols <= 0 || p.xfer_rows <= 0 || BM % p.xfer_rows || K % p.xfer_cols) return RC_BAD_SHAPE;
   if (!b_mn)
     rc = make_map_3d(&tmB, bf, B, K, N, 1, ldb * 2, 0, BK, BN);
   else

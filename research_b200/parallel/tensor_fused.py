@@ -32,7 +32,7 @@ def _declare(lib) -> None:
         return
     vp, ci, ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
     pvp = ctypes.POINTER(vp)
-    lib.b200_gemm_allgather.argtypes = [pvp, vp, vp, vp, ci, ci, ci, ll, ci, ci, ci, ci, ci, vp, vp, pvp,
+    lib.b200_gemm_allgather.argtypes = [pvp, vp, vp, vp, ci, ci, ci, ll, ci, ci, ci, ci, ci, ci, vp, vp, pvp,
                                         ctypes.c_uint, vp, vp]
     lib.b200_gemm_allgather.restype = ci
     lib.b200_gemm_reducescatter.argtypes = [vp, vp, pvp, ci, ci, ci, ll, ll, ci, ci, ci, ci, vp, pvp, ctypes.c_uint,
@@ -45,7 +45,7 @@ class TensorParallelFusion:
     """Workspace of one tensor-parallel group: a symmetric arena with a staging shard and an output shard."""
 
     def __init__(self, group, *, max_shard_elems: int, max_out_elems: int, device: torch.device | None = None,
-                 transfer_ctas: int = 8):
+                 transfer_ctas: int = 16):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -83,11 +83,13 @@ class TensorParallelFusion:
         stage = self.stage[:x_shard.numel()].view(m_local, K)
         stage.copy_(x_shard)
         x_full = torch.empty((M, K), dtype=torch.bfloat16, device=self.device)
+        # own rows go into the gathered operand here (one strided local copy); the kernel moves only remote rows
+        x_full.view(-1, self.world, chunk_rows, K)[:, self.rank].copy_(x_shard.view(-1, chunk_rows, K))
         y = torch.empty((M, N), dtype=torch.bfloat16, device=self.device)
         shards = self._ptrs([self.arena.peer_ptr(r, self.stage_off) for r in range(self.world)])
         flags = self._ptrs(self.arena.flag_ptrs(GATHER_CHANNEL))
         rc = self.lib.b200_gemm_allgather(shards, x_full.data_ptr(), w.data_ptr(), y.data_ptr(), M, N, K, w.stride(0),
-                                          int(b_mn), self.world, self.rank, chunk_rows // 128, self.transfer_ctas,
+                                          int(b_mn), self.world, self.rank, chunk_rows // 128, self.transfer_ctas, 0,
                                           self.row_flags.data_ptr(), self.counter.data_ptr(), flags,
                                           self.arena.next_epoch(GATHER_CHANNEL),
                                           native.status_word(self.device).data_ptr(), native._stream())
