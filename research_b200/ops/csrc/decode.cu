@@ -49,7 +49,7 @@ struct DecodeParams {
 };
 
 template <int D, int G>
-__global__ void __launch_bounds__(kWarps * 32) decode_attn_partial_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(kWarps * 32, (G <= 2 ? 6 : (G == 4 ? 4 : 2))) decode_attn_partial_kernel(const DecodeParams p) {
   constexpr int LPR = D / 8;      // lanes per cache row
   constexpr int RPW = 32 / LPR;   // rows per warp per step
   constexpr int GROUPS = kWarps * RPW;
@@ -87,39 +87,52 @@ __global__ void __launch_bounds__(kWarps * 32) decode_attn_partial_kernel(const 
   const __nv_bfloat16* kb = p.k + b * p.k_batch + (long long)hkv * D + l * 8;
   const __nv_bfloat16* vb = p.v + b * p.v_batch + (long long)hkv * D + l * 8;
 
-  constexpr int UNROLL = 4;
-  for (int r0 = begin + grp; r0 < end; r0 += GROUPS * UNROLL) {
-    uint4 kr[UNROLL], vr[UNROLL];
+  // Software pipeline: the loads of the next UNROLL rows are in flight while the current ones are reduced.
+  constexpr int UNROLL = 2;
+  constexpr int STEP = GROUPS * UNROLL;
+  uint4 kr[UNROLL], vr[UNROLL], kn[UNROLL], vn[UNROLL];
+  auto fetch = [&](int r0, uint4 (&kd)[UNROLL], uint4 (&vd)[UNROLL]) {
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       const int r = r0 + u * GROUPS;
       if (r < end) {
-        kr[u] = __ldg(reinterpret_cast<const uint4*>(kb + r * p.k_row));
-        vr[u] = __ldg(reinterpret_cast<const uint4*>(vb + r * p.v_row));
+        kd[u] = __ldg(reinterpret_cast<const uint4*>(kb + r * p.k_row));
+        vd[u] = __ldg(reinterpret_cast<const uint4*>(vb + r * p.v_row));
+      }
+    }
+  };
+  int r0 = begin + grp;
+  fetch(r0, kr, vr);
+  for (; r0 < end; r0 += STEP) {
+    fetch(r0 + STEP, kn, vn);
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int r = r0 + u * GROUPS;
+      if (r < end) {  // uniform inside a lane group
+        float kf[8], vf[8];
+        unpack8(kr[u], kf);
+        unpack8(vr[u], vf);
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          float s = 0.f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) s = fmaf(q[g][i], kf[i], s);
+#pragma unroll
+          for (int off = LPR >> 1; off > 0; off >>= 1) s += __shfl_xor_sync(gmask, s, off, LPR);
+          const float m_new = fmaxf(m[g], s);
+          const float alpha = ex2f(m[g] - m_new);
+          const float pr = ex2f(s - m_new);
+          m[g] = m_new;
+          lsum[g] = lsum[g] * alpha + pr;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(acc[g][i], alpha, pr * vf[i]);
+        }
       }
     }
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
-      const int r = r0 + u * GROUPS;
-      if (r >= end) break;  // uniform inside a lane group
-      float kf[8], vf[8];
-      unpack8(kr[u], kf);
-      unpack8(vr[u], vf);
-#pragma unroll
-      for (int g = 0; g < G; ++g) {
-        float s = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) s = fmaf(q[g][i], kf[i], s);
-#pragma unroll
-        for (int off = LPR >> 1; off > 0; off >>= 1) s += __shfl_xor_sync(gmask, s, off, LPR);
-        const float m_new = fmaxf(m[g], s);
-        const float alpha = ex2f(m[g] - m_new);
-        const float pr = ex2f(s - m_new);
-        m[g] = m_new;
-        lsum[g] = lsum[g] * alpha + pr;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(acc[g][i], alpha, pr * vf[i]);
-      }
+      kr[u] = kn[u];
+      vr[u] = vn[u];
     }
   }
 #pragma unroll
@@ -196,7 +209,7 @@ extern "C" int b200_decode_attn_splits(int B, int Hkv, int max_rows) {
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int base = B * Hkv > 0 ? B * Hkv : 1;
-  int splits = (sms * 8 + base - 1) / base;
+  int splits = (sms * 12 + base - 1) / base;
   const int by_rows = (max_rows + 255) / 256;  // at least 256 rows per split
   if (splits > by_rows) splits = by_rows;
   if (splits > 64) splits = 64;
