@@ -118,6 +118,40 @@ def sample_next_token(logits: torch.Tensor, *, temperature: float, top_k: int | 
     return token, logp.gather(1, token[:, None])[:, 0]
 
 
+class GraphedDecodeStep:
+    """One decode step (embedding -> layers -> logits of the new token) captured in a CUDA graph.
+
+    A decode step of a small batch is a few hundred short kernels, so its cost is launch latency, not work; the
+    captured graph replays them with one launch.  Token and position live in static device buffers that are
+    overwritten before each replay; sampling stays outside the graph.  Shapes are fixed at capture (batch size,
+    cache capacity)."""
+
+    def __init__(self, model, cache: PagedKVCache, first_token: torch.Tensor, first_position: int):
+        B = first_token.shape[0]
+        dev = first_token.device
+        self.token = first_token.reshape(B, 1).to(torch.int32).clone()
+        self.position = torch.full((B, 1), int(first_position), device=dev, dtype=torch.int32)
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side), torch.no_grad():
+            for _ in range(2):  # warm-up with the real inputs: the cache writes are idempotent
+                model.run_with_cache(self.token, self.position, cache, last_only=True)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph), torch.no_grad():
+            self.logits = model.run_with_cache(self.token, self.position, cache, last_only=True)[:, -1]
+
+    def __call__(self, token: torch.Tensor, position: int) -> torch.Tensor:
+        self.token.copy_(token.reshape(-1, 1))
+        self.position.fill_(int(position))
+        self.graph.replay()
+        return self.logits
+
+
+def _graph_ok(model, device: torch.device) -> bool:
+    return device.type == "cuda" and getattr(model, "compute_dtype", None) == torch.bfloat16
+
+
 @dataclass
 class GenerationResult:
     prompt_ids: list[list[int]]
@@ -145,17 +179,23 @@ def generate_tokens(model, prompt_ids: torch.Tensor, *, max_new_tokens: int, tem
     cache = init_kv_cache(model, B, total, page_size=page_size)
     gen = torch.Generator(device=device).manual_seed(int(seed))
     positions = torch.arange(P, device=device, dtype=torch.int32).expand(B, P).contiguous()
-    logits = model.run_with_cache(prompt_ids.to(torch.int32), positions, cache)[:, -1]
+    logits = model.run_with_cache(prompt_ids.to(torch.int32), positions, cache, last_only=True)[:, -1]
     cache.advance(positions)
     tokens, logprobs = [], []
+    step = None
     for t in range(max_new_tokens):
         tok, lp = sample_next_token(logits, temperature=temperature, top_k=top_k, top_p=top_p, generator=gen)
         tokens.append(tok)
         logprobs.append(lp)
         if t + 1 == max_new_tokens:
             break
+        if _graph_ok(model, device):
+            if step is None:
+                step = GraphedDecodeStep(model, cache, tok, P + t)
+            logits = step(tok, P + t)
+            continue
         pos = torch.full((B, 1), P + t, device=device, dtype=torch.int32)
-        logits = model.run_with_cache(tok[:, None].to(torch.int32), pos, cache)[:, -1]
+        logits = model.run_with_cache(tok[:, None].to(torch.int32), pos, cache, last_only=True)[:, -1]
         cache.advance(pos)
     model.train(was_training)
     out = torch.stack(tokens, dim=1).cpu()

@@ -317,8 +317,10 @@ class TransformerLM(nn.Module):
             m = layer.mlp(h, self.ex)
         return x, layer.ffn_post_norm(m)
 
-    def run_with_cache(self, token_ids: torch.Tensor, positions: torch.Tensor, cache: Any) -> torch.Tensor:
-        """token_ids, positions: [B,T].  Writes K/V for those positions into ``cache`` and returns logits [B,T,V]."""
+    def run_with_cache(self, token_ids: torch.Tensor, positions: torch.Tensor, cache: Any, *,
+                       last_only: bool = False) -> torch.Tensor:
+        """token_ids, positions: [B,T].  Writes K/V for those positions into ``cache`` and returns logits [B,T,V]
+        (``[B,1,V]`` for the last position only when ``last_only``: a prefill needs no other row)."""
 
         x = Fn.embedding(token_ids, self.embed, self.embed_scale, self.compute_dtype)
         delta = None
@@ -330,4 +332,6 @@ class TransformerLM(nn.Module):
                 return attn.finish(o, x2)
             x, delta = self._infer_block(layer, x, delta, positions, attend)
         h, _ = self.norm.add_forward(x, delta)
+        if last_only:
+            h = h[:, -1:].contiguous()
         return Fn.linear(h, self.head_weight())

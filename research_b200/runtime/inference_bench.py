@@ -21,9 +21,17 @@ from research_b200.infer import generation
 
 
 def run_inference_bench(spec, *, batch: int, prompt: int, new_tokens: int, temperature: float, top_k: int | None,
-                        warmup: int = 1, repeats: int = 3, seed: int = 0, device: str | None = None) -> dict:
+                        warmup: int = 1, repeats: int = 3, seed: int = 0, device: str | None = None,
+                        use_graph: bool = True) -> dict:
+    import dataclasses
+    import os
+
+    from research_b200.config.specs import MeshSpec, ParallelismSpec
     from research_b200.runtime.trainer import Trainer
 
+    if int(os.environ.get("WORLD_SIZE", "1")) == 1:
+        # generation runs on one replica: drop the training mesh of the config
+        spec = dataclasses.replace(spec, mesh=MeshSpec(), parallelism=ParallelismSpec())
     trainer = Trainer(spec, build_data=False, device=device)
     model = trainer.result.model
     model.eval()
@@ -43,7 +51,7 @@ def run_inference_bench(spec, *, batch: int, prompt: int, new_tokens: int, tempe
             pos = torch.arange(prompt, device=dev, dtype=torch.int32).expand(batch, prompt).contiguous()
             sync()
             t0 = time.perf_counter()
-            logits = model.run_with_cache(prompts, pos, cache)[:, -1]
+            logits = model.run_with_cache(prompts, pos, cache, last_only=True)[:, -1]
             cache.advance(pos)
             sync()
             t_prefill = time.perf_counter() - t0
@@ -52,10 +60,18 @@ def run_inference_bench(spec, *, batch: int, prompt: int, new_tokens: int, tempe
             sync()
             t_first = time.perf_counter() - t0
             t1 = time.perf_counter()
+            step = None
+            if use_graph and cuda:
+                step = generation.GraphedDecodeStep(model, cache, tok, prompt)  # capture is outside the timed loop
+                sync()
+                t1 = time.perf_counter()
             for t in range(new_tokens - 1):
-                p1 = torch.full((batch, 1), prompt + t, device=dev, dtype=torch.int32)
-                logits = model.run_with_cache(tok[:, None].to(torch.int32), p1, cache)[:, -1]
-                cache.advance(p1)
+                if step is not None:
+                    logits = step(tok, prompt + t)
+                else:
+                    p1 = torch.full((batch, 1), prompt + t, device=dev, dtype=torch.int32)
+                    logits = model.run_with_cache(tok[:, None].to(torch.int32), p1, cache, last_only=True)[:, -1]
+                    cache.advance(p1)
                 tok, _ = generation.sample_next_token(logits, temperature=temperature, top_k=top_k, top_p=None,
                                                       generator=gen)
             sync()
@@ -77,7 +93,7 @@ def run_inference_bench(spec, *, batch: int, prompt: int, new_tokens: int, tempe
         "prefill_tokens_per_sec": batch * prompt / t_prefill,
         "ttft_ms": 1e3 * t_first,
         "batch": batch, "prompt_tokens": prompt, "new_tokens": new_tokens, "temperature": temperature, "top_k": top_k,
-        "model": spec.model.name, "device": str(dev), "dtype": str(next(model.parameters()).dtype),
+        "cuda_graph": bool(use_graph and cuda), "model": spec.model.name, "device": str(dev), "dtype": str(next(model.parameters()).dtype),
         "data": "synthetic (random-init weights, uniform random prompt ids)",
     }
 
@@ -92,11 +108,12 @@ def main(argv: list[str] | None = None) -> int:
     ap.add_argument("--top-k", type=int, default=1)
     ap.add_argument("--repeats", type=int, default=3)
     ap.add_argument("--device", default=None)
+    ap.add_argument("--no-graph", action="store_true", help="launch every decode kernel separately")
     args = ap.parse_args(argv)
     spec = load_config(args.config)
     prompt = args.prompt if args.prompt is not None else min(512, spec.model.max_seq_len // 2)
     out = run_inference_bench(spec, batch=args.batch, prompt=prompt, new_tokens=args.new, temperature=args.temperature,
-                              top_k=args.top_k, repeats=args.repeats, device=args.device)
+                              top_k=args.top_k, repeats=args.repeats, device=args.device, use_graph=not args.no_graph)
     print(json.dumps(out))
     return 0
 

@@ -58,6 +58,8 @@ def test_generation_native_decode_matches_masked_attention(monkeypatch):
     prompts = torch.randint(0, 512, (3, 200), device="cuda", dtype=torch.int32)
     follow = torch.randint(0, 512, (3, 6), device="cuda", dtype=torch.int32)
 
+    real_cache = generation.PagedKVCache
+
     class _NoNative(generation.PagedKVCache):
         def update_and_attend(self, layer, q, k, v, positions, window):
             B, T = positions.shape
@@ -86,13 +88,13 @@ def test_generation_native_decode_matches_masked_attention(monkeypatch):
         return torch.stack(outs)
 
     model.eval()
-    fast = teacher_forced(generation.PagedKVCache)
+    fast = teacher_forced(real_cache)
     native.check_status()
     slow = teacher_forced(_NoNative)
     lp_fast, lp_slow = torch.log_softmax(fast, -1), torch.log_softmax(slow, -1)
     assert (lp_fast - lp_slow).abs().max().item() < 5e-2, (lp_fast - lp_slow).abs().max().item()
     # and the sampling loop runs end to end on the native path
-    monkeypatch.setattr(generation, "PagedKVCache", generation.PagedKVCache)
+    monkeypatch.setattr(generation, "PagedKVCache", real_cache)
     res = generation.generate_tokens(model, prompts, max_new_tokens=8, temperature=1.0, top_k=50, seed=0)
     native.check_status()
     assert len(res.generated_ids) == 3 and all(len(g) == 8 for g in res.generated_ids)
