@@ -19,7 +19,7 @@ from research_b200.ops import functional as Fn
 
 
 class PagedKVCache:
-    """``[layers, pages, page_size, kv_heads, head_dim]`` K and V pools + a page table per sequence."""
+    """``[layers, pages, kv_heads, page_size, head_dim]`` K and V pools (head-major pages) + a page table."""
 
     def __init__(self, *, layers: int, batch: int, max_len: int, kv_heads: int, head_dim: int, page_size: int,
                  dtype: torch.dtype, device: torch.device):
@@ -27,44 +27,53 @@ class PagedKVCache:
         self.pages_per_seq = (max_len + page_size - 1) // page_size
         self.max_len = self.pages_per_seq * page_size
         total_pages = batch * self.pages_per_seq
-        shape = (layers, total_pages, page_size, kv_heads, head_dim)
+        shape = (layers, total_pages, kv_heads, page_size, head_dim)
         self.k = torch.zeros(shape, dtype=dtype, device=device)
         self.v = torch.zeros(shape, dtype=dtype, device=device)
         self.page_table = torch.arange(total_pages, device=device, dtype=torch.int32).view(batch, self.pages_per_seq)
         self.lengths = torch.zeros(batch, dtype=torch.int32, device=device)
         self.batch = batch
 
-    def _flat(self, pool: torch.Tensor, layer: int) -> torch.Tensor:
-        # with the identity page table, sequence b occupies a contiguous [max_len] stretch of the pool
-        return pool[layer].view(self.batch, self.max_len, pool.shape[-2], pool.shape[-1])
+    def _pages(self, pool: torch.Tensor, layer: int) -> torch.Tensor:
+        # with the identity page table, sequence b owns pages [b * pages_per_seq, (b + 1) * pages_per_seq)
+        return pool[layer].view(self.batch, self.pages_per_seq, pool.shape[2], self.page_size, pool.shape[4])
+
+    def _rows(self, pool: torch.Tensor, layer: int, end: int) -> torch.Tensor:
+        """Dense ``[B, end, Hkv, D]`` copy of the first ``end`` rows (fallback paths only)."""
+
+        pg = self._pages(pool, layer)
+        return pg.permute(0, 1, 3, 2, 4).reshape(self.batch, self.max_len, pg.shape[2], pg.shape[4])[:, :end]
 
     def update_and_attend(self, layer: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor,
                           positions: torch.Tensor, window: int | None) -> torch.Tensor:
         """Write k, v at ``positions`` ([B,T]) and attend q over everything written so far (causal)."""
 
         B, T = positions.shape
-        kc, vc = self._flat(self.k, layer), self._flat(self.v, layer)
+        kp, vp = self._pages(self.k, layer), self._pages(self.v, layer)
+        native_ok = q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128)
+        if T == 1 and native_ok:
+            from research_b200.ops.decode import decode_attention_paged, kv_append_paged
+
+            pos = positions[:, 0]
+            kv_append_paged(k[:, 0], v[:, 0], kp, vp, pos)
+            lo = None if window is None else (pos - (window - 1)).clamp_min(0).to(torch.int32)
+            return decode_attention_paged(q[:, 0], kp, vp, (pos + 1).to(torch.int32), lo)[:, None]
         idx = positions.long()
         b_idx = torch.arange(B, device=q.device)[:, None].expand(B, T)
-        kc[b_idx, idx] = k.to(kc.dtype)
-        vc[b_idx, idx] = v.to(vc.dtype)
-        if T == 1 and q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128):
-            from research_b200.ops.decode import decode_attention
-
-            lo = None if window is None else (positions[:, 0] - (window - 1)).clamp_min(0).to(torch.int32)
-            return decode_attention(q[:, 0], kc, vc, (positions[:, 0] + 1).to(torch.int32), lo)[:, None]
-        if (T > 1 and q.is_cuda and q.dtype == torch.bfloat16 and q.shape[-1] in (64, 128)
+        kp[b_idx, idx // self.page_size, :, idx % self.page_size] = k.to(kp.dtype)
+        vp[b_idx, idx // self.page_size, :, idx % self.page_size] = v.to(vp.dtype)
+        if (T > 1 and native_ok
                 and bool((positions == torch.arange(T, device=q.device, dtype=positions.dtype)).all())):
-            # prefill from position 0: the flash kernel over the rows just written
+            # prefill from position 0: the flash kernel over the rows just computed
             from research_b200.ops import native
 
             lo = None
             if window is not None:
                 lo = (positions - (window - 1)).clamp_min(0).to(torch.int32).contiguous()
-            o, _ = native.attn_fwd(q.contiguous(), kc[:, :T], vc[:, :T], causal=True, lo=lo)
+            o, _ = native.attn_fwd(q.contiguous(), k.contiguous(), v.contiguous(), causal=True, lo=lo)
             return o.reshape(B, T, -1)
         end = int(positions.max().item()) + 1
-        keys, vals = kc[:, :end], vc[:, :end]
+        keys, vals = self._rows(self.k, layer, end), self._rows(self.v, layer, end)
         kpos = torch.arange(end, device=q.device)
         allowed = kpos[None, None, :] <= idx[:, :, None]
         if window is not None:

@@ -127,6 +127,13 @@ def main() -> int:
         kc, vc = bf((B, S, Hkv, D)), bf((B, S, Hkv, D))
         lens = torch.full((B,), S, device="cuda", dtype=torch.int32)
         ms = timed(lambda: decode_attention(q, kc, vc, lens, None), args.warmup, args.iters)
+        from research_b200.ops.decode import decode_attention_paged
+
+        kp = kc.view(B, S // 128, 128, Hkv, D).permute(0, 1, 3, 2, 4).contiguous()
+        vp = vc.view(B, S // 128, 128, Hkv, D).permute(0, 1, 3, 2, 4).contiguous()
+        ms_paged = timed(lambda: decode_attention_paged(q, kp, vp, lens, None), args.warmup, args.iters)
+        out["paged_head_major"] = {"ms": ms_paged, "gbs": 2 * kc.numel() * 2 / ms_paged / 1e6,
+                                   "frac_of_peak": 2 * kc.numel() * 2 / ms_paged / 1e6 / pk["hbm_gbs"]}
         gbs = 2 * kc.numel() * 2 / ms / 1e6
         out.update(shape=[B, S, H, Hkv, D], ms=ms, gbs=gbs, frac_of_peak=gbs / pk["hbm_gbs"])
     native.check_status()

@@ -43,7 +43,10 @@ struct DecodeParams {
   const int* lo;           // [B] or nullptr
   float* part_o;           // [B, Hq, splits, D]
   float* part_ml;          // [B, Hq, splits, 2]  (m in log2 units, l)
-  long long k_row, k_batch, v_row, v_batch;  // element strides
+  long long k_row, k_batch, v_row, v_batch;  // element strides between rows (inside a page) and sequences
+  long long k_head, v_head;                  // element stride between kv heads
+  long long k_page, v_page;                  // element stride between pages
+  int page_rows;                             // rows per page (a cache that is not paged passes all of them)
   int B, Hq, Hkv, splits;
   float scale_log2;
 };
@@ -84,8 +87,9 @@ __global__ void __launch_bounds__(kWarps * 32, (G <= 2 ? 6 : (G == 4 ? 4 : 2))) 
     m[g] = -CUDART_INF_F;
     lsum[g] = 0.f;
   }
-  const __nv_bfloat16* kb = p.k + b * p.k_batch + (long long)hkv * D + l * 8;
-  const __nv_bfloat16* vb = p.v + b * p.v_batch + (long long)hkv * D + l * 8;
+  const __nv_bfloat16* kb = p.k + b * p.k_batch + hkv * p.k_head + l * 8;
+  const __nv_bfloat16* vb = p.v + b * p.v_batch + hkv * p.v_head + l * 8;
+  const int page_rows = p.page_rows;
 
   // Software pipeline: the loads of the next UNROLL rows are in flight while the current ones are reduced.
   constexpr int UNROLL = 2;
@@ -96,8 +100,9 @@ __global__ void __launch_bounds__(kWarps * 32, (G <= 2 ? 6 : (G == 4 ? 4 : 2))) 
     for (int u = 0; u < UNROLL; ++u) {
       const int r = r0 + u * GROUPS;
       if (r < end) {
-        kd[u] = __ldg(reinterpret_cast<const uint4*>(kb + r * p.k_row));
-        vd[u] = __ldg(reinterpret_cast<const uint4*>(vb + r * p.v_row));
+        const int pg = r / page_rows, in = r - pg * page_rows;
+        kd[u] = __ldg(reinterpret_cast<const uint4*>(kb + pg * p.k_page + in * p.k_row));
+        vd[u] = __ldg(reinterpret_cast<const uint4*>(vb + pg * p.v_page + in * p.v_row));
       }
     }
   };
@@ -188,6 +193,25 @@ __global__ void decode_attn_merge_kernel(const float* __restrict__ part_o, const
   out[bh * D + d] = __float2bfloat16(ls > 0.f ? o / ls : 0.f);
 }
 
+// Cache append for one new token per sequence: row positions[b] of every kv head gets k_new / v_new.
+// One thread per 8 elements; k_new / v_new are [B, Hkv, D] views with element strides between sequences.
+__global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ k_new, const __nv_bfloat16* __restrict__ v_new,
+                                 long long kn_batch, long long vn_batch, __nv_bfloat16* __restrict__ k_cache,
+                                 __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ positions,
+                                 long long c_batch, long long c_head, long long c_page, long long c_row, int page_rows,
+                                 int B, int Hkv, int D) {
+  const int per = D / 8;
+  const int total = B * Hkv * per;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int c = i % per, h = (i / per) % Hkv, b = i / (per * Hkv);
+    const int r = positions[b];
+    const int pg = r / page_rows, in = r - pg * page_rows;
+    const long long dst = b * c_batch + h * c_head + pg * c_page + in * c_row + c * 8;
+    *reinterpret_cast<uint4*>(k_cache + dst) = *reinterpret_cast<const uint4*>(k_new + b * kn_batch + h * D + c * 8);
+    *reinterpret_cast<uint4*>(v_cache + dst) = *reinterpret_cast<const uint4*>(v_new + b * vn_batch + h * D + c * 8);
+  }
+}
+
 template <int D>
 int launch_partial(const DecodeParams& p, int G, cudaStream_t s) {
   const dim3 grid(p.splits, p.Hkv, p.B);
@@ -203,38 +227,58 @@ int launch_partial(const DecodeParams& p, int G, cudaStream_t s) {
 
 }  // namespace
 
-// Suggested number of kv splits so that the grid fills the device a few times over.
-extern "C" int b200_decode_attn_splits(int B, int Hkv, int max_rows) {
+// Number of kv splits: as many as fit in ONE wave of resident CTAs (a second, partly filled wave would leave most
+// SMs idle for the time of a whole CTA), at least 256 rows each.
+extern "C" int b200_decode_attn_splits(int B, int Hq, int Hkv, int max_rows) {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int G = Hkv > 0 ? Hq / Hkv : 1;
+  const int per_sm = G <= 2 ? 6 : (G == 4 ? 4 : 2);  // the kernels' launch bounds
   const int base = B * Hkv > 0 ? B * Hkv : 1;
-  int splits = (sms * 12 + base - 1) / base;
-  const int by_rows = (max_rows + 255) / 256;  // at least 256 rows per split
+  int splits = sms * per_sm / base;
+  const int by_rows = (max_rows + 255) / 256;
   if (splits > by_rows) splits = by_rows;
   if (splits > 64) splits = 64;
   return splits < 1 ? 1 : splits;
 }
 
-// q, out: [B,Hq,D] bf16 contiguous.  k, v: cache views [B, rows, Hkv, D] given by element strides between rows
-// and between sequences.  lengths: int32 [B] (rows valid per sequence), lo: int32 [B] or null (first visible row).
+// q, out: [B,Hq,D] bf16 contiguous.  k, v: caches addressed as base + b * batch + h * head + (r / page_rows) * page
+// + (r % page_rows) * row (element strides), which covers both a dense [B, rows, Hkv, D] cache (page_rows = rows)
+// and head-major pages [B, pages, Hkv, page_rows, D].  lengths: int32 [B] (rows valid per sequence), lo: int32 [B] or null (first visible row).
 // part_o: fp32 [B*Hq*splits*D], part_ml: fp32 [B*Hq*splits*2] scratch.  Hq/Hkv must be 1, 2, 4 or 8; D is 64 or 128.
 extern "C" int b200_decode_attn(const void* q, const void* k, const void* v, void* out, const void* lengths,
                                 const void* lo, void* part_o, void* part_ml, int B, int Hq, int Hkv, int D,
-                                long long k_row, long long k_batch, long long v_row, long long v_batch, float scale,
-                                int splits, void* stream) {
-  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || splits < 1) return -2;
-  if ((k_row % 8) || (k_batch % 8) || (v_row % 8) || (v_batch % 8)) return -1;  // 16-byte loads
+                                long long k_row, long long k_batch, long long v_row, long long v_batch,
+                                long long k_head, long long v_head, long long k_page, long long v_page, int page_rows,
+                                float scale, int splits, void* stream) {
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || splits < 1 || page_rows < 1) return -2;
+  if ((k_row % 8) || (k_batch % 8) || (v_row % 8) || (v_batch % 8) || (k_head % 8) || (v_head % 8) || (k_page % 8) ||
+      (v_page % 8))
+    return -1;  // 16-byte loads
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) return -1;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   DecodeParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (const int*)lengths,
-                 (const int*)lo, (float*)part_o, (float*)part_ml, k_row, k_batch, v_row, v_batch, B, Hq, Hkv, splits,
-                 scale * kLog2e};
+                 (const int*)lo, (float*)part_o, (float*)part_ml, k_row, k_batch, v_row, v_batch, k_head, v_head, k_page,
+                 v_page, page_rows, B, Hq, Hkv, splits, scale * kLog2e};
   int rc;
   if (D == 128) rc = launch_partial<128>(p, Hq / Hkv, s);
   else if (D == 64) rc = launch_partial<64>(p, Hq / Hkv, s);
   else return -2;
   if (rc) return rc;
   decode_attn_merge_kernel<<<B * Hq, D, 0, s>>>((const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, splits, D);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Append one token per sequence to head-major paged caches (see b200_decode_attn for the addressing).
+extern "C" int b200_kv_append(const void* k_new, const void* v_new, long long kn_batch, long long vn_batch, void* k_cache,
+                              void* v_cache, const void* positions, long long c_batch, long long c_head,
+                              long long c_page, long long c_row, int page_rows, int B, int Hkv, int D, void* stream) {
+  if (B <= 0 || Hkv <= 0 || D % 8 || page_rows < 1) return -2;
+  if ((kn_batch % 8) || (vn_batch % 8) || (c_batch % 8) || (c_head % 8) || (c_page % 8) || (c_row % 8)) return -1;
+  const int total = B * Hkv * (D / 8);
+  kv_append_kernel<<<(total + 255) / 256, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      (const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, kn_batch, vn_batch, (__nv_bfloat16*)k_cache,
+      (__nv_bfloat16*)v_cache, (const int*)positions, c_batch, c_head, c_page, c_row, page_rows, B, Hkv, D);
   return static_cast<int>(cudaGetLastError());
 }

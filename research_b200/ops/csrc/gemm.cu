@@ -53,6 +53,8 @@ struct GemmParams {
   //                      and share the K axis (variable-length contraction, e.g. per-expert weight gradients).
   const int* tile_group;
   const int* k_range;
+  // Split-K: the batch index selects a K slice of A and B, and every slice adds into the same C (z = 0).
+  int c_shared;
 };
 
 template <int BN, bool A_MN, bool B_MN, bool OUT_F32>
@@ -142,9 +144,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         int b, m0, n0, bB, zAC, kb0, kb1;
         tile_coords(t, b, m0, n0);
         if (!tile_extent(b, m0, bB, zAC, kb0, kb1)) continue;
-        const int zA = p.k_range ? 0 : zAC;
-        const int zB = p.k_range ? 0 : bB;
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        const int zA = (p.k_range || p.c_shared) ? 0 : zAC;
+        const int zB = (p.k_range || p.c_shared) ? 0 : bB;
+        const int k_off = p.c_shared ? b * k_blocks : 0;  // split-K: slice b of the full K axis
+        for (int kb = kb0 + k_off; kb < kb1 + k_off; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(&empty[s], ph ^ 1, ab, ERR_WAIT_EMPTY)) { ok = false; break; }
@@ -260,10 +263,11 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
+          const int zC = p.c_shared ? 0 : zAC;
           if (p.accumulate)
-            tma_reduce_add_3d(&tmC, buf, col0, row0, zAC);
+            tma_reduce_add_3d(&tmC, buf, col0, row0, zC);
           else
-            tma_store_3d(&tmC, buf, col0, row0, zAC);
+            tma_store_3d(&tmC, buf, col0, row0, zC);
           tma_commit_group();
         }
       }
@@ -326,7 +330,7 @@ int dispatch(bool a_mn, bool b_mn, bool out_f32, const CUtensorMap& tmA, const C
 static int gemm_impl(const void* A, const void* B, void* C, int M, int N, int K, int batch, int batch_a, int batch_b,
                      int batch_c, long long lda, long long ldb, long long ldc, long long stride_a, long long stride_b,
                      long long stride_c, int a_mn, int b_mn, int out_f32, int accumulate, int bn_hint,
-                     const int* tile_group, const int* k_range, int* status, void* stream);
+                     const int* tile_group, const int* k_range, int* status, void* stream, int c_shared = 0);
 
 extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int batch, long long lda,
                               long long ldb, long long ldc, long long stride_a, long long stride_b,
@@ -334,6 +338,17 @@ extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, int M, int 
                               int* status, void* stream) {
   return gemm_impl(A, B, C, M, N, K, batch, batch, batch, batch, lda, ldb, ldc, stride_a, stride_b, stride_c, a_mn,
                    b_mn, out_f32, accumulate, bn_hint, nullptr, nullptr, status, stream);
+}
+
+// Split-K product for skinny problems (few rows, e.g. one decode token per sequence): C[M,N] (fp32, zeroed by the
+// caller) += A[:, slice] * B[:, slice]^T for `splits` equal K slices, one CTA tile per (N tile, slice), so that a
+// weight matrix is streamed by many SMs at once.  K must be a multiple of 64 * splits.
+extern "C" int b200_gemm_bf16_splitk(const void* A, const void* B, void* C, int M, int N, int K, int splits,
+                                     long long lda, long long ldb, long long ldc, int* status, void* stream) {
+  if (splits < 1 || K % (64 * splits)) return b200host::RC_BAD_SHAPE;
+  const int kc = K / splits;
+  return gemm_impl(A, B, C, M, N, kc, splits, 1, 1, 1, lda, ldb, ldc, 0, 0, 0, 0, 0, 1, 1, 0, nullptr, nullptr, status,
+                   stream, 1);
 }
 
 // Grouped forward / data-gradient product: A [M_pad, K] and C [M_pad, N] are 2-D with every group's rows
@@ -358,22 +373,24 @@ extern "C" int b200_gemm_bf16_grouped_k(const void* A, const void* B, void* C, i
 static int gemm_impl(const void* A, const void* B, void* C, int M, int N, int K, int batch, int batch_a, int batch_b,
                      int batch_c, long long lda, long long ldb, long long ldc, long long stride_a, long long stride_b,
                      long long stride_c, int a_mn, int b_mn, int out_f32, int accumulate, int bn_hint,
-                     const int* tile_group, const int* k_range, int* status, void* stream) {
+                     const int* tile_group, const int* k_range, int* status, void* stream, int c_shared) {
   using namespace b200host;
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return RC_BAD_SHAPE;
   const int BN = (bn_hint == 128 || bn_hint == 256) ? bn_hint : (N > 128 ? 256 : 128);
   CUtensorMap tmA, tmB, tmC;
   int rc;
   const CUtensorMapDataType bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const int k_map = c_shared ? K * batch : K;  // split-K addresses slices through the K coordinate
+  if (c_shared) batch_a = batch_b = batch_c = 1;
   if (!a_mn)
-    rc = make_map_3d(&tmA, bf, A, K, M, batch_a, lda * 2, stride_a * 2, BK, BM);
+    rc = make_map_3d(&tmA, bf, A, k_map, M, batch_a, lda * 2, stride_a * 2, BK, BM);
   else
-    rc = make_map_3d(&tmA, bf, A, M, K, batch_a, lda * 2, stride_a * 2, 64, BK);
+    rc = make_map_3d(&tmA, bf, A, M, k_map, batch_a, lda * 2, stride_a * 2, 64, BK);
   if (rc) return rc;
   if (!b_mn)
-    rc = make_map_3d(&tmB, bf, B, K, N, batch_b, ldb * 2, stride_b * 2, BK, BN);
+    rc = make_map_3d(&tmB, bf, B, k_map, N, batch_b, ldb * 2, stride_b * 2, BK, BN);
   else
-    rc = make_map_3d(&tmB, bf, B, N, K, batch_b, ldb * 2, stride_b * 2, 64, BK);
+    rc = make_map_3d(&tmB, bf, B, N, k_map, batch_b, ldb * 2, stride_b * 2, 64, BK);
   if (rc) return rc;
   if (out_f32)
     rc = make_map_3d(&tmC, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, C, N, M, batch_c, ldc * 4, stride_c * 4, 32, 32);
@@ -381,7 +398,7 @@ static int gemm_impl(const void* A, const void* B, void* C, int M, int N, int K,
     rc = make_map_3d(&tmC, bf, C, N, M, batch_c, ldc * 2, stride_c * 2, 64, 32);
   if (rc) return rc;
 
-  GemmParams p{M, N, K, batch, accumulate, status, tile_group, k_range};
+  GemmParams p{M, N, K, batch, accumulate, status, tile_group, k_range, c_shared};
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * batch;
   const int grid = tiles < sm_count() ? tiles : sm_count();
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);

@@ -91,6 +91,11 @@ def linear(x: torch.Tensor, p: torch.Tensor) -> torch.Tensor:
     """``y = x @ W^T`` with ``W`` stored ``[out, in]``."""
 
     if use_native(x):
+        if not torch.is_grad_enabled() and x.numel() // x.shape[-1] <= 64:
+            # decode-sized input: stream the weight with the whole device (split-K), no autograd bookkeeping
+            w = compute_weight(p, x)
+            y = native.gemm_skinny(x.reshape(-1, x.shape[-1]), w)
+            return y.view(*x.shape[:-1], w.shape[0])
         return _LinearFn.apply(x, p)
     return F.linear(x, p.to(x.dtype))
 

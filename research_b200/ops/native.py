@@ -93,9 +93,13 @@ def _declare(lib: ctypes.CDLL) -> None:
     sig("b200_muon_apply", c_void_p, c_void_p, c_void_p, c_ll, c_float, c_float, c_void_p)
     sig("b200_scale_by_inv_norm", c_void_p, c_void_p, c_ll, c_int, c_float, c_void_p)
     sig("b200_affine_identity", c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p)
-    sig("b200_decode_attn_splits", c_int, c_int, c_int)
+    sig("b200_gemm_bf16_splitk", c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_void_p,
+        c_void_p)
+    sig("b200_decode_attn_splits", c_int, c_int, c_int, c_int)
     sig("b200_decode_attn", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
-        c_int, c_int, c_ll, c_ll, c_ll, c_ll, c_float, c_int, c_void_p)
+        c_int, c_int, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_int, c_float, c_int, c_void_p)
+    sig("b200_kv_append", c_void_p, c_void_p, c_ll, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_ll, c_ll, c_int,
+        c_int, c_int, c_int, c_void_p)
     sig("b200_attn_fwd", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
         c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_float, c_int, c_ll, c_void_p, c_void_p)
     sig("b200_attn_bwd", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -198,6 +202,39 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
 # --------------------------------------------------------------------------------------------------
 # normalisation / activation / embedding / loss / optimizer
 # --------------------------------------------------------------------------------------------------
+def splitk_factor(n: int, k: int, sms: int = 148) -> int:
+    """How many K slices a skinny ``[rows, k] x [n, k]^T`` product should be cut into so that about two CTAs per SM
+    stream the weight: a divisor of ``k / 64`` that leaves slices of at least 128."""
+
+    tiles = (n + 255) // 256
+    kblocks = k // 64
+    best = 1
+    for d in range(1, kblocks + 1):
+        if kblocks % d or k // d < 128 or tiles * d > 2 * sms:
+            continue
+        best = d
+    return best
+
+
+def gemm_skinny(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """``a [rows, K] @ b [N, K]^T`` for a handful of rows (decode): split-K so that the whole device streams ``b``.
+    Returns bf16 ``[rows, N]``."""
+
+    lib = load()
+    rows, K = a.shape
+    N = b.shape[0]
+    if K % 64 or a.stride(1) != 1 or b.stride(1) != 1:
+        return gemm(a, b, trans_b=True)
+    splits = splitk_factor(N, K)
+    if splits == 1:
+        return gemm(a, b, trans_b=True)
+    c = torch.zeros((rows, N), dtype=torch.float32, device=a.device)
+    rc = lib.b200_gemm_bf16_splitk(a.data_ptr(), b.data_ptr(), c.data_ptr(), rows, N, K, splits, a.stride(0),
+                                   b.stride(0), c.stride(0), status_word(a.device).data_ptr(), _stream())
+    _check(rc, "b200_gemm_bf16_splitk")
+    return c.to(torch.bfloat16)
+
+
 def rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor, eps: float, delta: torch.Tensor | None = None):
     """Returns ``(y, rstd, residual)``; ``residual = x + delta`` when ``delta`` is given, else ``x``."""
 

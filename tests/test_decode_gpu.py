@@ -26,6 +26,30 @@ def test_decode_attention_matches_reference(D, Hq, Hkv):
         assert torch.allclose(out.float(), ref.float(), atol=2e-2, rtol=2e-2), (out.float() - ref.float()).abs().max()
 
 
+def test_paged_decode_and_append_match_dense_cache():
+    from research_b200.ops import native
+    from research_b200.ops.decode import decode_attention_paged, decode_attention_reference, kv_append_paged
+
+    torch.manual_seed(1)
+    B, pages, Hkv, ps, D, Hq = 3, 5, 4, 128, 128, 8
+    kp = torch.randn(B, pages, Hkv, ps, D, device="cuda").bfloat16()
+    vp = torch.randn(B, pages, Hkv, ps, D, device="cuda").bfloat16()
+    pos = torch.tensor([0, 300, 639], device="cuda", dtype=torch.int32)
+    packed = torch.randn(B, (Hq + 2 * Hkv) * D, device="cuda").bfloat16()   # new k / v as views of a packed row
+    k_new = packed[:, Hq * D:(Hq + Hkv) * D].view(B, Hkv, D)
+    v_new = packed[:, (Hq + Hkv) * D:].view(B, Hkv, D)
+    kv_append_paged(k_new, v_new, kp, vp, pos)
+    dense_k = kp.permute(0, 1, 3, 2, 4).reshape(B, pages * ps, Hkv, D)
+    dense_v = vp.permute(0, 1, 3, 2, 4).reshape(B, pages * ps, Hkv, D)
+    for b in range(B):
+        assert torch.equal(dense_k[b, int(pos[b])], k_new[b]) and torch.equal(dense_v[b, int(pos[b])], v_new[b])
+    q = torch.randn(B, Hq, D, device="cuda").bfloat16()
+    out = decode_attention_paged(q, kp, vp, pos + 1, None)
+    native.check_status()
+    ref = decode_attention_reference(q, dense_k, dense_v, pos + 1, None)
+    assert torch.allclose(out.float(), ref.float(), atol=2e-2, rtol=2e-2)
+
+
 def test_decode_attention_empty_window_gives_zeros():
     from research_b200.ops.decode import decode_attention
 
@@ -63,15 +87,16 @@ def test_generation_native_decode_matches_masked_attention(monkeypatch):
     class _NoNative(generation.PagedKVCache):
         def update_and_attend(self, layer, q, k, v, positions, window):
             B, T = positions.shape
-            kc, vc = self._flat(self.k, layer), self._flat(self.v, layer)
+            kp, vp = self._pages(self.k, layer), self._pages(self.v, layer)
             idx = positions.long()
             b_idx = torch.arange(B, device=q.device)[:, None].expand(B, T)
-            kc[b_idx, idx] = k.to(kc.dtype)
-            vc[b_idx, idx] = v.to(vc.dtype)
+            kp[b_idx, idx // self.page_size, :, idx % self.page_size] = k.to(kp.dtype)
+            vp[b_idx, idx // self.page_size, :, idx % self.page_size] = v.to(vp.dtype)
             end = int(positions.max().item()) + 1
             kpos = torch.arange(end, device=q.device)
             allowed = kpos[None, None, :] <= idx[:, :, None]
-            return generation._masked_attention(q, kc[:, :end], vc[:, :end], allowed)
+            return generation._masked_attention(q, self._rows(self.k, layer, end), self._rows(self.v, layer, end),
+                                                allowed)
 
     def teacher_forced(cache_cls):
         monkeypatch.setattr(generation, "PagedKVCache", cache_cls)
