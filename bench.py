@@ -27,6 +27,8 @@ import threading
 import time
 from pathlib import Path
 
+REPO = Path(__file__).resolve().parent
+
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
@@ -123,16 +125,70 @@ def dense_1p3b_spec(n_gpus: int, manifest: Path, steps_total: int, per_gpu_batch
     return run_spec_from_mapping(raw)
 
 
+WORKLOADS = {
+    # name: (config file, description, mesh builder)
+    "dense_8b": ("dense_8b_fsdp4_tp2_adamw.toml", "dense-8B decoder (32L, d4096, 32q/8kv heads, ffn 14336, vocab 128256)"),
+    "moe_7b": ("moe_7b_ep8_dion.toml", "MoE ~7B total (16L, d2048, 64 experts ffn 1024, top-8, 1 shared expert)"),
+    "long_context": ("dense_1p3b_cp4_fsdp2_32k.toml", "dense-1.3B decoder, context parallel, seq 32768"),
+}
+
+
+def workload_spec(name: str, n_gpus: int, manifest: Path, steps_total: int, per_gpu_batch: int, seq_len: int | None,
+                  optimizer: str | None):
+    """The other named workloads, from their TOML files, re-meshed for ``n_gpus`` GPUs of one box."""
+
+    import tomllib
+
+    from research_b200.config import run_spec_from_mapping
+
+    raw = tomllib.loads((REPO / "configs" / WORKLOADS[name][0]).read_text())
+    if seq_len:
+        raw["training"]["seq_len"] = seq_len
+        raw["model"]["max_seq_len"] = seq_len
+    seq_len = raw["training"]["seq_len"]
+    if optimizer:
+        raw["optimizer"]["name"] = optimizer
+    if name == "dense_8b":
+        tp = 2 if n_gpus >= 2 else 1
+        axes, sizes, replicas = ["fsdp", "tensor"], [n_gpus // tp, tp], n_gpus // tp
+        raw["parallelism"]["tensor_parallel"] = tp > 1
+        parallelism = f"fsdp{n_gpus // tp}xtp{tp}"
+    elif name == "long_context":
+        cp = min(4, n_gpus)
+        axes, sizes, replicas = ["fsdp", "context"], [n_gpus // cp, cp], n_gpus // cp
+        raw["parallelism"]["context_parallel"] = cp > 1
+        parallelism = f"fsdp{n_gpus // cp}xcp{cp}"
+    else:
+        axes, sizes, replicas = ["fsdp"], [n_gpus], n_gpus
+        raw["parallelism"]["expert_parallel"] = n_gpus > 1
+        parallelism = f"fsdp{n_gpus}+ep{n_gpus}"
+    gb = per_gpu_batch * replicas
+    raw["mesh"] = {"axis_names": axes, "axis_sizes": sizes}
+    raw["data"]["train_manifest"] = str(manifest)
+    raw["run"]["output_dir"] = "/tmp/research_b200_bench"
+    raw["training"].update(global_batch_size=gb, target_tokens=gb * seq_len * steps_total,
+                           gradient_accumulation_steps=1)
+    raw["optimizer"]["schedule"] = {"name": "constant", "peak_lr": 3e-4, "warmup_steps": 10}
+    raw.pop("evals", None)
+    return run_spec_from_mapping(raw), gb, parallelism
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="dense_1p3b", choices=["dense_1p3b", *WORKLOADS],
+                    help="dense_1p3b is the headline config; the others are the remaining named workloads")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--per-gpu-batch", type=int, default=8)
-    ap.add_argument("--seq-len", type=int, default=4096)
-    ap.add_argument("--optimizer", default="muon", choices=["muon", "adamw", "dion"])
+    ap.add_argument("--seq-len", type=int, default=None)
+    ap.add_argument("--optimizer", default=None, choices=["muon", "adamw", "dion"])
     args = ap.parse_args()
+    headline = args.workload == "dense_1p3b"
+    if headline:
+        args.seq_len = args.seq_len or 4096
+        args.optimizer = args.optimizer or "muon"
     if args.impl == "reference":
         return reference_arm(args)
 
@@ -153,17 +209,28 @@ def main() -> int:
     torch.cuda.set_device(local_rank)
     K, W = args.steps, max(args.warmup, 3)
     steps_total = W + 2 * K + 2
-    gb = args.per_gpu_batch * world
-    tokens_needed = gb * (args.seq_len + 1) * steps_total
-    data_dir = Path(tempfile.gettempdir()) / f"research_b200_bench_data_{world}_{args.seq_len}_{steps_total}"
+    data_dir = Path(tempfile.gettempdir()) / f"research_b200_bench_data_{args.workload}_{world}_{args.seq_len}_{steps_total}"
     manifest = data_dir / "manifest.json"
+    if headline:
+        spec = dense_1p3b_spec(world, manifest, steps_total, args.per_gpu_batch, args.seq_len, args.optimizer)
+        gb, parallelism = args.per_gpu_batch * world, f"fsdp{world}"
+        model_desc = "dense-1.3B decoder (24L, d2048, 16q/8kv heads, ffn 5632, vocab 50304)"
+    else:
+        spec, gb, parallelism = workload_spec(args.workload, world, manifest, steps_total, args.per_gpu_batch,
+                                              args.seq_len, args.optimizer)
+        model_desc = WORKLOADS[args.workload][1]
+    args.seq_len = spec.training.seq_len
+    args.optimizer = spec.optimizer.name
+    tokens_needed = gb * (args.seq_len + 1) * steps_total
     if rank == 0 and not manifest.exists():
-        docs = int(tokens_needed / 1400 * 1.25) + 256
-        generate_synthetic_dataset(data_dir, seed=0, num_documents=docs, mean_length=1500, min_length=16,
-                                   max_length=16384, vocab_size=50304, eos_id=50303, val_fraction=0.02, overwrite=True)
+        mean_len = 3000 if args.workload == "dense_8b" else (6000 if args.workload == "long_context" else 1500)
+        docs = int(tokens_needed / (mean_len * 0.93) * 1.25) + 256
+        vocab = spec.model.vocab_size
+        generate_synthetic_dataset(data_dir, seed=0, num_documents=docs, mean_length=mean_len, min_length=16,
+                                   max_length=4 * args.seq_len, vocab_size=vocab, eos_id=vocab - 1, val_fraction=0.02,
+                                   overwrite=True)
     if world > 1:
         dist.barrier()
-    spec = dense_1p3b_spec(world, manifest, steps_total, args.per_gpu_batch, args.seq_len, args.optimizer)
     trainer = Trainer(spec)
     tokens_per_step = gb * args.seq_len
 
@@ -217,10 +284,12 @@ def main() -> int:
             "steps": K, "warmup": W, "ms_per_step": round(dev_ms / K, 3), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "impl": "native",
-            "config": {"model": "dense-1.3B decoder (24L, d2048, 16q/8kv heads, ffn 5632, vocab 50304)",
-                       "global_batch": gb, "seq_len": args.seq_len, "parallelism": f"fsdp{world}",
-                       "optimizer": args.optimizer, "grad_accum": 1, "doc_masks": "geometric(mean 1500)",
-                       "timing": "CUDA events, max over ranks; inputs larger than L2 (activations of 32K tokens/GPU)"},
+            "config": {"model": model_desc, "workload": args.workload,
+                       "global_batch": gb, "seq_len": args.seq_len, "parallelism": parallelism,
+                       "optimizer": args.optimizer, "grad_accum": 1,
+                       "doc_masks": "geometric document lengths" if spec.model.attention_doc_mask else "none",
+                       "timing": "CUDA events, max over ranks; inputs larger than L2 (activations of all tokens of a "
+                                 "step per GPU)"},
             "mfu": round(100.0 * fpt * value / peak, 2), "mfu_exact": round(100.0 * fpt_exact * value / peak, 2),
             "flops_per_token": fpt, "peak_flops_per_gpu": 2.25e15,
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms / K, 3),

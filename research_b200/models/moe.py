@@ -166,10 +166,24 @@ class SparseMoE(nn.Module):
         B, S, H = x.shape
         expert_ids, weights, scores = self.router(x, self.expert_bias)
         dropped = None
-        if self.moe.capacity_factor is not None:
+        plan = None
+        if Fn.use_native(x) and x.dtype == torch.bfloat16 and H % 8 == 0:
+            # device-side routing plan: ranks in token order, capacity, padded expert-major layout (no sort)
+            from research_b200.ops.grouped import RoutingPlan
+
+            capacity = None
+            if self.moe.capacity_factor is not None:
+                capacity = capacity_rows(self.moe.capacity_factor, B * S, expert_ids.shape[-1], self.num_experts)
+            plan = RoutingPlan(expert_ids.reshape(B * S, -1), self.num_experts, capacity)
+            if capacity is not None:
+                keep = plan.kept_mask.view(expert_ids.shape)
+                weights = weights * keep.to(weights.dtype)
+                dropped = (~keep).sum()
+        elif self.moe.capacity_factor is not None:
             weights, dropped = apply_capacity(expert_ids, weights, self.num_experts, self.moe.capacity_factor)
         y = dispatch_and_combine(self.experts, x.reshape(B * S, H), expert_ids.reshape(B * S, -1),
-                                 weights.reshape(B * S, -1), num_experts=self.num_experts, ex=ex).view(B, S, H)
+                                 weights.reshape(B * S, -1), num_experts=self.num_experts, ex=ex,
+                                 plan=plan).view(B, S, H)
         if self.shared_experts is not None:
             y = y + ex.reduce_scatter_sequence(self.shared_experts(ex.gather_sequence(x), ex))
         stats = router_stats(name, layer_index, expert_ids, weights, self.num_experts, dropped)
@@ -186,6 +200,12 @@ class SparseMoE(nn.Module):
         return y, tuple(aux), (stats,)
 
 
+def capacity_rows(capacity_factor: float, tokens: int, k: int, num_experts: int) -> int:
+    """Rows an expert accepts: ceil(capacity_factor * tokens * k / E)."""
+
+    return int(-(-capacity_factor * tokens * k // num_experts))
+
+
 def apply_capacity(expert_ids: torch.Tensor, weights: torch.Tensor, num_experts: int, capacity_factor: float):
     """Zero the weights of assignments beyond each expert's capacity (token order priority).
 
@@ -196,7 +216,7 @@ def apply_capacity(expert_ids: torch.Tensor, weights: torch.Tensor, num_experts:
     k = shape[-1]
     flat = expert_ids.reshape(-1).long()
     tokens = flat.numel() // k
-    capacity = int(-(-capacity_factor * tokens * k // num_experts))
+    capacity = capacity_rows(capacity_factor, tokens, k, num_experts)
     onehot = F.one_hot(flat, num_experts)
     position = (onehot.cumsum(dim=0) * onehot).sum(dim=-1) - 1     # rank of each assignment inside its expert
     keep = position < capacity

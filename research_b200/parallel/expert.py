@@ -47,11 +47,16 @@ def _local_dispatch(experts, x, expert_ids, weights, num_experts):
 
 
 def dispatch_and_combine(experts, x: torch.Tensor, expert_ids: torch.Tensor, weights: torch.Tensor, *,
-                         num_experts: int, ex) -> torch.Tensor:
-    """x: [T,H]; expert_ids, weights: [T,k] (global expert ids).  Returns sum_k w * expert(x) as [T,H]."""
+                         num_experts: int, ex, plan=None) -> torch.Tensor:
+    """x: [T,H]; expert_ids, weights: [T,k] (global expert ids).  Returns sum_k w * expert(x) as [T,H].
+    ``plan`` is the native routing plan of these assignments when the CUDA kernels are in use."""
 
     ep = ex.ep_size
     if ep == 1:
+        if plan is not None:
+            from research_b200.ops.grouped import routed_expert_ffn
+
+            return routed_expert_ffn(x, weights, plan, experts.w_gate_up, experts.w_down)
         return _local_dispatch(experts, x, expert_ids, weights, num_experts)
     if ex.ep_axis_sharing == "dedicated_ep" and not ex.extras.get("_ep_sliced"):
         # With a dedicated ``ep`` axis everything outside the routed experts is replicated over it: split the

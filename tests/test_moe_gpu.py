@@ -73,3 +73,65 @@ def test_trinity_moe_training_step_reduces_loss():
     native.check_status()
     assert all(np.isfinite(losses)), losses
     assert losses[-1] < losses[0] - 0.05, losses
+
+
+@pytest.mark.parametrize("capacity", [None, 300])
+def test_native_routing_plan_matches_sort_based_dispatch(capacity):
+    from research_b200.models.moe import apply_capacity
+    from research_b200.ops import native
+    from research_b200.ops.grouped import RoutingPlan, routed_expert_ffn
+
+    torch.manual_seed(0)
+    T, k, E, H, I = 3000, 4, 16, 256, 128
+    logits = torch.randn(T, E, device="cuda")
+    logits[:, 3] += 2.0                                   # a hot expert, so that the capacity drops something
+    w_full, ids = torch.topk(torch.softmax(logits, -1), k, dim=-1)
+    x = (torch.randn(T, H, device="cuda") * 0.5).bfloat16()
+    w1 = torch.nn.Parameter(torch.randn(E, 2 * I, H, device="cuda") * 0.05)
+    w2 = torch.nn.Parameter(torch.randn(E, H, I, device="cuda") * 0.05)
+
+    plan = RoutingPlan(ids, E, capacity)
+    # ranks and counts against the one-hot formulation
+    onehot = torch.nn.functional.one_hot(ids.reshape(-1), E)
+    pos_ref = (onehot.cumsum(0) * onehot).sum(-1) - 1
+    assert torch.equal(plan.pos.long(), pos_ref)
+    assert torch.equal(plan.counts.long(), onehot.sum(0))
+    keep = plan.kept_mask
+    if capacity is None:
+        assert bool(keep.all())
+    else:
+        assert torch.equal(keep.reshape(-1), pos_ref < capacity)
+        assert int((~keep).sum()) > 0
+    # every kept assignment owns a distinct row inside its expert's block
+    d = plan.dest[plan.dest >= 0].long()
+    assert d.unique().numel() == d.numel()
+    e_of = ids.reshape(-1)[plan.dest >= 0].long()
+    assert bool(((d >= plan.k_range[e_of, 0]) & (d < plan.k_range[e_of, 1])).all())
+
+    def run(native_path):
+        xr = x.clone().requires_grad_(True)
+        wr = (w_full * keep.to(w_full.dtype)).detach().clone().requires_grad_(True)
+        w1.main_grad = torch.zeros_like(w1)
+        w2.main_grad = torch.zeros_like(w2)
+        if native_path:
+            y = routed_expert_ffn(xr, wr, plan, w1, w2)
+        else:
+            from research_b200.models.moe import Experts
+            from research_b200.parallel.expert import _local_dispatch
+
+            experts = Experts(H, I, E)
+            experts.w_gate_up, experts.w_down = w1, w2
+            y = _local_dispatch(experts, xr, ids, wr, E)
+        g = torch.sin(torch.arange(y.numel(), device="cuda").view_as(y) * 0.01).bfloat16() * 0.1
+        y.backward(g)
+        native.check_status()
+        # a dropped assignment has no row on the native path, so its weight gets no gradient there; in the model
+        # the capacity mask multiplies the weights, which zeroes that gradient on either path
+        return (y.float(), xr.grad.float(), wr.grad.float() * keep.float(), w1.main_grad.clone(),
+                w2.main_grad.clone())
+
+    a, b = run(True), run(False)
+    names = ("y", "dx", "dw_route", "dW1", "dW2")
+    for name, u, v in zip(names, a, b):
+        tol = 0.03 * v.abs().max().item() + 1e-3
+        assert (u - v).abs().max().item() <= tol, (name, (u - v).abs().max().item(), tol)
