@@ -91,7 +91,9 @@ class Router(nn.Module):
     def forward(self, x: torch.Tensor, expert_bias: torch.Tensor):
         """x: [..., H] -> (expert_ids [...,k] int64, weights [...,k] fp32, scores [...,E] fp32)."""
 
-        logits = F.linear(x.float(), self.proj.float()) if not Fn.use_native(x) else Fn.linear(x, self.proj).float()
+        # the native GEMM needs 16-byte output rows: eight or more experts
+        native_ok = Fn.use_native(x) and self.proj.shape[0] % 8 == 0
+        logits = Fn.linear(x, self.proj).float() if native_ok else F.linear(x.float(), self.proj.float())
         if self.kind == "softmax":
             scores = torch.softmax(logits, dim=-1)
         else:

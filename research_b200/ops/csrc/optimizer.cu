@@ -10,13 +10,21 @@
 
 namespace {
 
-__global__ void muon_momentum_kernel(const float* __restrict__ g, float* __restrict__ m,
-                                     __nv_bfloat16* __restrict__ u, float* __restrict__ sumsq,
-                                     const float* __restrict__ clip, long long n, float beta, int nesterov) {
+// blockIdx.y walks a batch of equal-size matrices: matrix b starts `stride` elements after matrix b-1 in g and m
+// (they may be row slices of a fused parameter) and is written densely, `n` elements apart, into u; sumsq[b].
+__global__ void muon_momentum_kernel(const float* __restrict__ g_all, float* __restrict__ m_all,
+                                     __nv_bfloat16* __restrict__ u_all, float* __restrict__ sumsq_all,
+                                     const float* __restrict__ clip, long long n, long long stride, int batch,
+                                     float beta, int nesterov) {
   __shared__ float red[32];
   const float c = clip ? clip[0] : 1.f;
-  float acc = 0.f;
   const long long nvec = n >> 2;
+  for (int b = blockIdx.y; b < batch; b += gridDim.y) {
+  const float* g = g_all + b * stride;
+  float* m = m_all + b * stride;
+  __nv_bfloat16* u = u_all + b * n;
+  float* sumsq = sumsq_all + b;
+  float acc = 0.f;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
        i += (long long)gridDim.x * blockDim.x) {
     float4 gv = reinterpret_cast<const float4*>(g)[i];
@@ -48,11 +56,18 @@ __global__ void muon_momentum_kernel(const float* __restrict__ g, float* __restr
     for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
     if (threadIdx.x == 0) atomicAdd(sumsq, acc);
   }
+  __syncthreads();
+  }
 }
 
-__global__ void muon_apply_kernel(float* __restrict__ w, const __nv_bfloat16* __restrict__ o,
-                                  __nv_bfloat16* __restrict__ shadow, long long n, float decay, float step) {
+__global__ void muon_apply_kernel(float* __restrict__ w_all, const __nv_bfloat16* __restrict__ o_all,
+                                  __nv_bfloat16* __restrict__ shadow_all, long long n, long long stride, int batch,
+                                  float decay, float step) {
   const long long nvec = n >> 2;
+  for (int b = blockIdx.y; b < batch; b += gridDim.y) {
+  float* w = w_all + b * stride;
+  const __nv_bfloat16* o = o_all + b * n;
+  __nv_bfloat16* shadow = shadow_all ? shadow_all + b * stride : nullptr;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
        i += (long long)gridDim.x * blockDim.x) {
     float4 wv = reinterpret_cast<float4*>(w)[i];
@@ -72,6 +87,7 @@ __global__ void muon_apply_kernel(float* __restrict__ w, const __nv_bfloat16* __
       packed.y = *reinterpret_cast<uint32_t*>(&hi);
       reinterpret_cast<uint2*>(shadow)[i] = packed;
     }
+  }
   }
 }
 
@@ -147,14 +163,37 @@ extern "C" int b200_muon_momentum(const void* g, void* m, void* u, void* sumsq, 
                                   float beta, int nesterov, void* stream) {
   if (n <= 0 || (n & 3)) return -2;
   muon_momentum_kernel<<<blocks_for(n / 4, 256, 4), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      (const float*)g, (float*)m, (__nv_bfloat16*)u, (float*)sumsq, (const float*)clip, n, beta, nesterov);
+      (const float*)g, (float*)m, (__nv_bfloat16*)u, (float*)sumsq, (const float*)clip, n, n, 1, beta, nesterov);
+  return static_cast<int>(cudaGetLastError());
+}
+// `batch` matrices of `n` elements each, `stride` elements apart in g and m; u is [batch, n]; sumsq is [batch].
+extern "C" int b200_muon_momentum_batched(const void* g, void* m, void* u, void* sumsq, const void* clip, long long n,
+                                          long long stride, int batch, float beta, int nesterov, void* stream) {
+  if (n <= 0 || (n & 3) || (stride & 3) || batch < 1) return -2;
+  int bx = blocks_for(n / 4, 256, 1);
+  if (bx > 64) bx = 64;
+  const dim3 grid(bx, batch > 65535 ? 65535 : batch);
+  muon_momentum_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      (const float*)g, (float*)m, (__nv_bfloat16*)u, (float*)sumsq, (const float*)clip, n, stride, batch, beta,
+      nesterov);
   return static_cast<int>(cudaGetLastError());
 }
 extern "C" int b200_muon_apply(void* w, const void* o, void* shadow, long long n, float decay, float step,
                                void* stream) {
   if (n <= 0 || (n & 3)) return -2;
   muon_apply_kernel<<<blocks_for(n / 4, 256, 4), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      (float*)w, (const __nv_bfloat16*)o, (__nv_bfloat16*)shadow, n, decay, step);
+      (float*)w, (const __nv_bfloat16*)o, (__nv_bfloat16*)shadow, n, n, 1, decay, step);
+  return static_cast<int>(cudaGetLastError());
+}
+// w and shadow: `batch` matrices `stride` elements apart; o is [batch, n].
+extern "C" int b200_muon_apply_batched(void* w, const void* o, void* shadow, long long n, long long stride, int batch,
+                                       float decay, float step, void* stream) {
+  if (n <= 0 || (n & 3) || (stride & 3) || batch < 1) return -2;
+  int bx = blocks_for(n / 4, 256, 1);
+  if (bx > 64) bx = 64;
+  const dim3 grid(bx, batch > 65535 ? 65535 : batch);
+  muon_apply_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      (float*)w, (const __nv_bfloat16*)o, (__nv_bfloat16*)shadow, n, stride, batch, decay, step);
   return static_cast<int>(cudaGetLastError());
 }
 extern "C" int b200_scale_by_inv_norm(void* x, const void* sumsq, long long per, int batch, float eps, void* stream) {

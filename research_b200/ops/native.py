@@ -91,6 +91,9 @@ def _declare(lib: ctypes.CDLL) -> None:
         c_int, c_int, c_void_p, c_void_p, c_void_p)
     sig("b200_muon_momentum", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_float, c_int, c_void_p)
     sig("b200_muon_apply", c_void_p, c_void_p, c_void_p, c_ll, c_float, c_float, c_void_p)
+    sig("b200_muon_momentum_batched", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_int, c_float,
+        c_int, c_void_p)
+    sig("b200_muon_apply_batched", c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_int, c_float, c_float, c_void_p)
     sig("b200_scale_by_inv_norm", c_void_p, c_void_p, c_ll, c_int, c_float, c_void_p)
     sig("b200_affine_identity", c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p)
     sig("b200_gemm_bf16_splitk", c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_void_p,
@@ -474,6 +477,24 @@ def muon_momentum(g: torch.Tensor, m: torch.Tensor, u: torch.Tensor, sumsq_slot:
     lib = load()
     _check(lib.b200_muon_momentum(g.data_ptr(), m.data_ptr(), u.data_ptr(), sumsq_slot.data_ptr(), _ptr(clip),
                                   g.numel(), beta, int(nesterov), _stream()), "b200_muon_momentum")
+
+
+def muon_momentum_batched(g: torch.Tensor, m: torch.Tensor, u: torch.Tensor, sumsq: torch.Tensor,
+                          clip: torch.Tensor | None, per: int, stride: int, batch: int, beta: float,
+                          nesterov: bool) -> None:
+    """``batch`` matrices of ``per`` elements, ``stride`` elements apart from the first element of ``g`` / ``m``
+    (fp32); ``u`` is the dense bf16 ``[batch, per]`` stack; ``sumsq`` has ``batch`` fp32 slots."""
+
+    lib = load()
+    _check(lib.b200_muon_momentum_batched(g.data_ptr(), m.data_ptr(), u.data_ptr(), sumsq.data_ptr(), _ptr(clip), per,
+                                          stride, batch, beta, int(nesterov), _stream()), "b200_muon_momentum_batched")
+
+
+def muon_apply_batched(w: torch.Tensor, o: torch.Tensor, shadow: torch.Tensor | None, per: int, stride: int, batch: int,
+                       decay: float, step: float) -> None:
+    lib = load()
+    _check(lib.b200_muon_apply_batched(w.data_ptr(), o.data_ptr(), _ptr(shadow), per, stride, batch, decay, step,
+                                       _stream()), "b200_muon_apply_batched")
 
 
 def muon_apply(w: torch.Tensor, o: torch.Tensor, shadow: torch.Tensor | None, decay: float, step: float) -> None:

@@ -177,54 +177,67 @@ class Optimizer:
         return self.store.device.type == "cuda" and self.store.compute_dtype == torch.bfloat16
 
     def _muon_section_fast(self, i: int, sec: Section, entries: list[StorageEntry], lr: float) -> list[StorageEntry]:
-        """Batched Muon for plain 2-D matrices: logical matrices of equal shape are stacked so that each
-        Newton-Schulz step is three batched GEMMs; returns the entries this path does not handle."""
+        """Batched Muon: logical matrices of equal shape are stacked so that each Newton-Schulz step is three
+        batched GEMMs.  Covers plain 2-D parameters (and row slices of fused ones) and rank-3 expert stacks, whose
+        per-expert matrices are addressed with a stride; returns the entries this path does not handle."""
 
         store = self.store
         lo, _ = store.local_master_range(sec)
         leftovers: list[StorageEntry] = []
-        groups: dict[tuple[int, int], list[tuple[StorageEntry, Any, int, int]]] = {}
+        # (rows, cols) -> [(entry, meta, offset of the first matrix inside the entry, matrices, stride)]
+        groups: dict[tuple[int, int], list[tuple[StorageEntry, Any, int, int, int]]] = {}
         for e in entries:
             master = store.master_view(sec, e)
-            simple = master is not None and master.dim() == 2 and e.numel % 4 == 0 and all(
+            simple = master is not None and master.dim() in (2, 3) and e.numel % 4 == 0 and all(
                 self.routes[m.name].backend == "muon" for m in e.metas)
             if not simple:
                 leftovers.append(e)
                 continue
-            cols = e.param.shape[1]
-            for meta in e.metas:
-                a, b = meta.rows if meta.rows is not None else (0, e.param.shape[0])
-                if (b - a) % 8 or cols % 8:
-                    simple = False
-            if not simple:
+            full_rows, cols = e.param.shape[-2], e.param.shape[-1]
+            batch = e.param.shape[0] if master.dim() == 3 else 1
+            spans = [meta.rows if meta.rows is not None else (0, full_rows) for meta in e.metas]
+            if any((b - a) % 8 for a, b in spans) or cols % 8:
                 leftovers.append(e)
                 continue
-            for meta in e.metas:
-                a, b = meta.rows if meta.rows is not None else (0, e.param.shape[0])
-                groups.setdefault((b - a, cols), []).append((e, meta, a, b))
+            for meta, (a, b) in zip(e.metas, spans):
+                groups.setdefault((b - a, cols), []).append((e, meta, a * cols, batch, full_rows * cols))
         wd = float(self.spec.weight_decay)
         mom_all = self.state[i]["momentum"]
+        max_stack = 1 << 29  # elements per Newton-Schulz batch (1 GiB of bf16)
         for (rows, cols), items in groups.items():
-            n = len(items)
-            stack = native.scratch(f"muon_stack_{rows}x{cols}", n * rows * cols, torch.bfloat16, store.device)
-            stack = stack[: n * rows * cols].view(n, rows, cols)
-            sq = torch.zeros(n, dtype=torch.float32, device=store.device)
-            for k, (e, meta, a, b) in enumerate(items):
-                off = e.offset - lo + a * cols
-                cnt = rows * cols
-                g = store.grad_arena[e.offset + a * cols:e.offset + a * cols + cnt]
-                native.muon_momentum(g, mom_all[off:off + cnt], stack[k], sq[k:k + 1], self._clip, orth.MUON_MOMENTUM,
-                                     orth.MUON_NESTEROV)
-            native.scale_by_inv_norm(stack, sq, orth.MUON_NS_EPS)
-            out = orth.newton_schulz_stack_(stack)
-            step = lr * orth.rms_match_scale((rows, cols))
-            for k, (e, meta, a, b) in enumerate(items):
-                off = e.offset - lo + a * cols
-                cnt = rows * cols
-                decay = 1.0 - lr * wd if self.routes[meta.name].weight_decay else 1.0
-                shadow = store.compute_arena[e.offset + a * cols:e.offset + a * cols + cnt]
-                native.muon_apply(sec.master[off:off + cnt], out[k], shadow, decay, step)
+            per = rows * cols
+            chunk: list[tuple[StorageEntry, Any, int, int, int]] = []
+            count = 0
+            for item in items + [None]:
+                if item is not None and (not chunk or (count + item[3]) * per <= max_stack):
+                    chunk.append(item)
+                    count += item[3]
+                    continue
+                self._muon_stack(sec, chunk, count, rows, cols, lo, mom_all, lr, wd)
+                chunk, count = ([item], item[3]) if item is not None else ([], 0)
         return leftovers
+
+    def _muon_stack(self, sec: Section, items, n: int, rows: int, cols: int, lo: int, mom_all, lr: float,
+                    wd: float) -> None:
+        store = self.store
+        per = rows * cols
+        stack = native.scratch("muon_stack", n * per, torch.bfloat16, store.device)[: n * per].view(n, rows, cols)
+        sq = torch.zeros(n, dtype=torch.float32, device=store.device)
+        at = 0
+        for e, meta, first, batch, stride in items:
+            native.muon_momentum_batched(store.grad_arena[e.offset + first:], mom_all[e.offset - lo + first:],
+                                         stack[at:], sq[at:], self._clip, per, stride, batch, orth.MUON_MOMENTUM,
+                                         orth.MUON_NESTEROV)
+            at += batch
+        native.scale_by_inv_norm(stack, sq, orth.MUON_NS_EPS)
+        out = orth.newton_schulz_stack_(stack)
+        step = lr * orth.rms_match_scale((rows, cols))
+        at = 0
+        for e, meta, first, batch, stride in items:
+            decay = 1.0 - lr * wd if self.routes[meta.name].weight_decay else 1.0
+            native.muon_apply_batched(sec.master[e.offset - lo + first:], out[at:],
+                                      store.compute_arena[e.offset + first:], per, stride, batch, decay, step)
+            at += batch
 
     def _matrix_entry(self, i: int, sec: Section, e: StorageEntry, lr: float) -> None:
         store = self.store

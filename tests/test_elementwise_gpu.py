@@ -145,8 +145,10 @@ def test_adamw_sumsq_cast():
     assert torch.allclose(y.float(), p * 0.5, atol=1e-2, rtol=1e-2)
 
 
-def test_fast_muon_section_matches_reference_path():
-    """The batched tcgen05 Muon step against the per-matrix PyTorch restatement of the same update."""
+@pytest.mark.parametrize("family", ["decoder", "trinity_moe"])
+def test_fast_muon_section_matches_reference_path(family):
+    """The batched tcgen05 Muon step against the per-matrix PyTorch restatement of the same update
+    (2-D matrices, row slices of fused parameters, and rank-3 expert stacks)."""
 
     import numpy as np
 
@@ -163,6 +165,10 @@ def test_fast_muon_section_matches_reference_path():
         "data": {"train_manifest": "unused.json"},
         "training": {"seq_len": 256, "global_batch_size": 2, "target_tokens": 2 * 256 * 4, "precision": "bf16"},
     }
+    if family == "trinity_moe":
+        raw["model"].update(name="trinity", num_layers=2, trinity={
+            "initial_dense_layers": 1, "local_window": 128, "local_layers_per_global": 1, "norm_policy": "afmoe_dual",
+            "moe": {"num_experts": 4, "top_k": 2, "expert_intermediate_size": 256, "num_shared_experts": 1}})
     rng = np.random.default_rng(0)
     ids = rng.integers(0, 1024, size=(2, 257)).astype(np.int32)
     batch = Batch(input_ids=ids[:, :-1], target_ids=ids[:, 1:], loss_mask=np.ones((2, 256), dtype=bool))
