@@ -176,8 +176,16 @@ class SparseMoE(nn.Module):
             capacity = None
             if self.moe.capacity_factor is not None:
                 capacity = capacity_rows(self.moe.capacity_factor, B * S, expert_ids.shape[-1], self.num_experts)
-            plan = RoutingPlan(expert_ids.reshape(B * S, -1), self.num_experts, capacity)
-            if capacity is not None:
+            if ex.ep_size == 1:
+                plan = RoutingPlan(expert_ids.reshape(B * S, -1), self.num_experts, capacity)
+            else:
+                from research_b200.parallel import expert_fused
+
+                if ex.ep_axis_sharing != "dedicated_ep" and expert_fused.fused_available(ex, x, capacity):
+                    plan = expert_fused.ExpertParallelPlan(expert_ids.reshape(B * S, -1), self.num_experts, capacity, ex)
+            if plan is None and capacity is not None:
+                weights, dropped = apply_capacity(expert_ids, weights, self.num_experts, self.moe.capacity_factor)
+            elif capacity is not None:
                 keep = plan.kept_mask.view(expert_ids.shape)
                 weights = weights * keep.to(weights.dtype)
                 dropped = (~keep).sum()

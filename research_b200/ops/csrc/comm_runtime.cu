@@ -223,6 +223,15 @@ all_gather_pull_kernel(const PeerPtrs pp, uint4* __restrict__ dst, long long n16
   finish_and_wait_done(pp, world, rank, epoch, counter, status);
 }
 
+// Barrier over the ranks of an arena: announce epoch, wait (bounded) for everybody else's announcement.
+__global__ void peer_barrier_kernel(const PeerPtrs pp, int world, int rank, uint32_t epoch, int* status) {
+  if (threadIdx.x < world && (int)threadIdx.x != rank) {
+    __threadfence_system();
+    st_release_sys(&pp.flags[threadIdx.x]->ready[rank], epoch);
+    wait_sys(&pp.flags[rank]->ready[threadIdx.x], epoch, status, ERR_PEER_READY);
+  }
+}
+
 int grid_for_bytes(long long items, int block) {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
@@ -292,6 +301,19 @@ int b200c_vmm_free(void* ptr, unsigned long long padded) {
 }
 
 int b200c_flag_block_bytes() { return static_cast<int>(sizeof(FlagBlock)); }
+
+// All ranks call this with the same epoch on the same channel; work queued before it on every rank's stream has
+// completed (and its peer-memory writes are visible) when work queued after it starts.
+int b200c_barrier(void* const* flags, int world, int rank, unsigned epoch, int* status, void* stream) {
+  if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world) return -2;
+  PeerPtrs pp = {};
+  for (int r = 0; r < world; ++r) {
+    if (!flags[r]) return -1;
+    pp.flags[r] = static_cast<FlagBlock*>(flags[r]);
+  }
+  peer_barrier_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(pp, world, rank, epoch, status);
+  return static_cast<int>(cudaGetLastError());
+}
 
 // src[r]: rank r's copy of the slice this rank owns (n fp32, n % 4 == 0, 16-byte aligned); flags[r]: rank r's
 // flag block of this channel, as mapped here.  scratch: uint32 counter (zero) followed by >= 512 floats.

@@ -52,6 +52,10 @@ def dispatch_and_combine(experts, x: torch.Tensor, expert_ids: torch.Tensor, wei
     ``plan`` is the native routing plan of these assignments when the CUDA kernels are in use."""
 
     ep = ex.ep_size
+    if ep > 1 and plan is not None:
+        from research_b200.parallel.expert_fused import dispatch_and_combine_fused
+
+        return dispatch_and_combine_fused(experts, x, weights, plan)
     if ep == 1:
         if plan is not None:
             from research_b200.ops.grouped import routed_expert_ffn

@@ -51,6 +51,8 @@ def _comm_lib() -> ctypes.CDLL:
                                                   ctypes.POINTER(vp), ci, ci, ctypes.c_uint, vp, vp, vp]
         lib.b200c_all_gather_pull.argtypes = [ctypes.POINTER(vp), vp, ctypes.c_longlong, ctypes.POINTER(vp), ci, ci,
                                               ctypes.c_uint, ci, vp, vp, vp]
+        lib.b200c_barrier.argtypes = [ctypes.POINTER(vp), ci, ci, ctypes.c_uint, vp, vp]
+        lib.b200c_barrier.restype = ci
         for fn in (lib.b200c_vmm_alloc, lib.b200c_vmm_import, lib.b200c_vmm_free, lib.b200c_flag_block_bytes,
                    lib.b200c_reduce_scatter_pull, lib.b200c_all_gather_pull):
             fn.restype = ci
@@ -193,6 +195,14 @@ class SymmetricArena:
                                              self.next_epoch(channel), 0, self.scratch.data_ptr(),
                                              native.status_word(self.device).data_ptr(), native._stream())
         native._check(rc, "b200c_all_gather_pull")
+
+    def barrier(self, channel: int = 4) -> None:
+        """Stream-ordered barrier over the ranks of the arena (a one-block kernel with bounded waits)."""
+
+        flags = self._ptr_array(self.flag_ptrs(channel))
+        rc = self._lib.b200c_barrier(flags, self.world, self.rank, self.next_epoch(channel),
+                                     native.status_word(self.device).data_ptr(), native._stream())
+        native._check(rc, "b200c_barrier")
 
     def close(self) -> None:
         if getattr(self, "ptrs", None):

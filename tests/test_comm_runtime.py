@@ -209,6 +209,7 @@ raw = {
     "mesh": {"axis_names": axes, "axis_sizes": sizes},
     "parallelism": flags.get("parallelism", {}),
 }
+raw["model"].update(flags.get("model", {}))
 trainer = Trainer(run_spec_from_mapping(raw), build_data=False)
 rng = np.random.default_rng(0)
 losses = []
@@ -244,6 +245,12 @@ def _run_training(tmp_path, world, axes, sizes, flags, peer, port):
 @pytest.mark.parametrize("name,axes,sizes,flags", [
     ("tp2", ["tp"], [2], {"parallelism": {"mode": "ddp", "tensor_parallel": True}}),
     ("fsdp2_muon", ["fsdp"], [2], {"parallelism": {"mode": "fsdp"}, "optimizer": "muon"}),
+    ("moe_fsdp2_ep2", ["fsdp"], [2], {
+        "parallelism": {"mode": "fsdp", "expert_parallel": True},
+        "model": {"name": "trinity", "num_layers": 2, "trinity": {
+            "initial_dense_layers": 0, "local_window": 512, "local_layers_per_global": 1, "norm_policy": "afmoe_dual",
+            "moe": {"num_experts": 8, "top_k": 2, "expert_intermediate_size": 256, "num_shared_experts": 1,
+                    "capacity_factor": 1.5}}}}),
 ])
 def test_training_with_peer_memory_kernels_matches_nccl_path(tmp_path, name, axes, sizes, flags):
     if torch.cuda.device_count() < 2:
