@@ -261,3 +261,35 @@ def test_training_with_peer_memory_kernels_matches_nccl_path(tmp_path, name, axe
     for a, b in zip(fused, plain):
         assert abs(a - b) <= 2e-2 * max(1.0, abs(b)), (name, fused, plain)
     assert fused[-1] < fused[0]
+
+
+@pytest.mark.gpu
+def test_bounded_peer_wait_times_out_with_a_status_code():
+    """A barrier whose peer never announces itself gives up after its limit and reports a status code; the
+    context stays usable (nothing traps, nothing hangs)."""
+
+    import ctypes
+    import time
+
+    from research_b200.errors import KernelError
+    from research_b200.ops import native
+    from research_b200.parallel.symmetric import _comm_lib
+
+    lib = _comm_lib()
+    nbytes = lib.b200c_flag_block_bytes()
+    blocks = torch.zeros(2, nbytes, dtype=torch.uint8, device="cuda")      # flag blocks of "rank 0" and "rank 1"
+    flags = (ctypes.c_void_p * 2)(blocks[0].data_ptr(), blocks[1].data_ptr())
+    native.check_status()
+    t0 = time.perf_counter()
+    rc = lib.b200c_barrier(flags, 2, 0, 7, native.status_word().data_ptr(), native._stream())
+    assert rc == 0
+    with pytest.raises(KernelError, match="status code 21"):                # ERR_PEER_READY
+        native.check_status()
+    waited = time.perf_counter() - t0
+    assert 1.0 < waited < 10.0, waited
+    # the announcement this rank made is in the peer's block, and the device still works
+    ready = blocks[1].view(torch.int32)[:8]
+    assert int(ready[0]) == 7
+    x = torch.ones(1024, device="cuda")
+    assert float(x.sum()) == 1024.0
+    native.check_status()
