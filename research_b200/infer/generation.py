@@ -112,10 +112,16 @@ def sample_next_token(logits: torch.Tensor, *, temperature: float, top_k: int | 
         raise ContractError("generation.top_p is not supported at runtime")
     if temperature <= 0:
         raise ContractError(f"generation.temperature must be positive, got {temperature}")
+    if top_k is not None and top_k <= 0:
+        raise ContractError(f"generation.top_k must be positive, got {top_k}")
+    if logits.is_cuda and logits.dim() == 2 and logits.dtype in (torch.bfloat16, torch.float32):
+        # one kernel: threshold select, softmax mass, inverse-CDF draw from a uniform number of ``generator``
+        from research_b200.ops import native
+
+        u = torch.rand(logits.shape[0], device=logits.device, generator=generator)
+        return native.sample_topk(logits if logits.stride(1) == 1 else logits.contiguous(), u, float(temperature), top_k)
     scaled = logits.float() / float(temperature)
     if top_k is not None:
-        if top_k <= 0:
-            raise ContractError(f"generation.top_k must be positive, got {top_k}")
         k = min(int(top_k), scaled.shape[-1])
         threshold = torch.topk(scaled, k, dim=-1).values[:, -1:]
         scaled = torch.where(scaled >= threshold, scaled, torch.full_like(scaled, float("-inf")))

@@ -313,11 +313,11 @@ class ExecutionContext:
         return all_gather_dim(logits, self.tp_group, logits.dim() - 1) if self.tp_size > 1 else logits
 
     # ---- attention (local, or context parallel) ------------------------------------------------------
-    def attention(self, qkv, wq, wk, positions, *, B, S, hq, hkv, D, eps, theta, rope, lo, hi):
+    def attention(self, qkv, wq, wk, positions, *, B, S, hq, hkv, D, eps, theta, rope, lo, hi, chunks=()):
         if self.cp_size == 1:
             return Fn.attention_block(qkv, wq, wk, positions, B=B, S=S, hq=hq, hkv=hkv, D=D, eps=eps, theta=theta,
                                       rope=rope, causal=True, lo=lo, hi=hi)
         from research_b200.parallel.context import context_parallel_attention
 
         return context_parallel_attention(self, qkv, wq, wk, positions, B=B, S=S, hq=hq, hkv=hkv, D=D, eps=eps,
-                                          theta=theta, rope=rope, lo=lo)
+                                          theta=theta, rope=rope, lo=lo, chunks=chunks)

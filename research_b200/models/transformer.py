@@ -44,10 +44,10 @@ class AttentionConfig:
 class ForwardInputs:
     """Per-batch tensors shared by every layer."""
 
-    positions: torch.Tensor              # int32 [B*S], local indices
+    positions: torch.Tensor              # int32 [B*S]: global sequence position of every local row
     B: int
     S: int
-    q_offset: int = 0                    # global position of local row 0 (context parallelism)
+    chunks: tuple[tuple[int, int], ...] = ()   # context parallelism: (first global position, length) of local chunks
     lo_causal: torch.Tensor | None = None    # int32 [B,S]: document starts (or None)
     hi_causal: torch.Tensor | None = None
     lo_window: dict[int, tuple[torch.Tensor, torch.Tensor | None]] | None = None  # per window size
@@ -58,8 +58,7 @@ class ForwardInputs:
         if self.lo_window is None:
             self.lo_window = {}
         if window not in self.lo_window:
-            pos = self.positions.view(self.B, self.S)
-            idx = torch.arange(self.S, device=pos.device, dtype=torch.int32).expand(self.B, self.S) + self.q_offset
+            idx = self.positions.view(self.B, self.S)
             lo = (idx - (window - 1)).clamp_min(0)
             if self.lo_causal is not None:
                 lo = torch.maximum(lo, self.lo_causal)
@@ -120,7 +119,7 @@ class Attention(nn.Module):
         lo, hi = inp.bounds(window)
         o = ex.attention(qkv, self.q_norm, self.k_norm, inp.positions, B=B, S=S, hq=self.hq, hkv=self.hkv,
                          D=self.head_dim, eps=self.eps, theta=self.theta, rope=self.cfg.position == "rope",
-                         lo=lo, hi=hi)
+                         lo=lo, hi=hi, chunks=inp.chunks)
         if self.wgate is not None:
             o = Fn.sigmoid_gate(o.reshape(B * S, -1), Fn.linear(x2, self.wgate)).view(B, S, -1)
         return ex.row_linear(o if o.dim() == 3 else o.view(B, S, -1), self.wo)  # partial sums -> SP shard
@@ -261,8 +260,19 @@ class TransformerLM(nn.Module):
     def make_inputs(self, input_ids: torch.Tensor, token_doc_ids: torch.Tensor | None) -> ForwardInputs:
         B, S = input_ids.shape
         dev = input_ids.device
-        positions = torch.arange(S, device=dev, dtype=torch.int32).repeat(B)
-        q_offset = self.ex.cp_rank * S if self.ex.cp_size > 1 else 0
+        chunks: tuple[tuple[int, int], ...] = ()
+        if self.ex.cp_size > 1:
+            from research_b200.steps.train import context_positions
+
+            glob = context_positions(S * self.ex.cp_size, self.ex.cp_size, self.ex.cp_rank)
+            cols = torch.as_tensor(glob, device=dev, dtype=torch.long)
+            positions = cols.to(torch.int32).repeat(B)
+            # contiguous runs of global positions (one for the contiguous split, two for zig-zag)
+            breaks = [0] + [i for i in range(1, len(glob)) if glob[i] != glob[i - 1] + 1] + [len(glob)]
+            chunks = tuple((int(glob[a]), b - a) for a, b in zip(breaks[:-1], breaks[1:]))
+        else:
+            cols = None
+            positions = torch.arange(S, device=dev, dtype=torch.int32).repeat(B)
         lo = hi = None
         if token_doc_ids is not None and self.spec.attention_doc_mask:
             d = token_doc_ids.to(dev)                      # document ids of the WHOLE sequence, [B, S_full]
@@ -271,8 +281,9 @@ class TransformerLM(nn.Module):
             change[:, 1:] = d[:, 1:] != d[:, :-1]
             idx = torch.arange(full, device=dev, dtype=torch.int32).expand(B, full)
             lo = torch.cummax(torch.where(change, idx, torch.zeros_like(idx)), dim=1).values.to(torch.int32)
-            lo = lo[:, q_offset:q_offset + S].contiguous()  # this rank's rows, global kv positions
-        return ForwardInputs(positions=positions, B=B, S=S, q_offset=q_offset, lo_causal=lo, hi_causal=hi)
+            if cols is not None:
+                lo = lo.index_select(1, cols).contiguous()  # this rank's rows, global kv positions
+        return ForwardInputs(positions=positions, B=B, S=S, chunks=chunks, lo_causal=lo, hi_causal=hi)
 
     def hidden_states(self, input_ids: torch.Tensor, token_doc_ids: torch.Tensor | None = None):
         """Returns the final-normed hidden states ``[B, S(/tp), H]`` plus aux losses and router stats."""

@@ -98,6 +98,7 @@ def _declare(lib: ctypes.CDLL) -> None:
     sig("b200_affine_identity", c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p)
     sig("b200_gemm_bf16_splitk", c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_void_p,
         c_void_p)
+    sig("b200_sample_topk", c_void_p, c_ll, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p)
     sig("b200_decode_attn_splits", c_int, c_int, c_int, c_int)
     sig("b200_decode_attn", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
         c_int, c_int, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_int, c_float, c_int, c_void_p)
@@ -521,3 +522,23 @@ def affine_identity(a: torch.Tensor, alpha: float, beta: float, out: torch.Tenso
     _check(lib.b200_affine_identity(a.data_ptr(), out.data_ptr(), a.shape[-1], a.numel() // (a.shape[-1] ** 2), alpha,
                                     beta, _stream()), "b200_affine_identity")
     return out
+
+
+# --------------------------------------------------------------------------------------------------
+# sampler
+# --------------------------------------------------------------------------------------------------
+def sample_topk(logits: torch.Tensor, uniform: torch.Tensor, temperature: float, top_k: int | None):
+    """logits ``[B, V]`` (bf16 or fp32, dense rows), uniform ``[B]`` fp32 in [0, 1) -> (token int64 [B], logprob fp32 [B])."""
+
+    lib = load()
+    if logits.dtype not in (torch.bfloat16, torch.float32) or logits.stride(1) != 1:
+        raise KernelError("sample_topk needs bf16 or fp32 logits with a dense last dimension")
+    B, V = logits.shape
+    token = torch.empty(B, dtype=torch.int64, device=logits.device)
+    logprob = torch.empty(B, dtype=torch.float32, device=logits.device)
+    uniform = uniform.to(torch.float32).contiguous()
+    rc = lib.b200_sample_topk(logits.data_ptr(), logits.stride(0), int(logits.dtype == torch.bfloat16),
+                              uniform.data_ptr(), token.data_ptr(), logprob.data_ptr(), B, V, float(temperature),
+                              0 if top_k is None else int(top_k), _stream())
+    _check(rc, "b200_sample_topk")
+    return token, logprob

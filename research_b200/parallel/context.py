@@ -1,4 +1,5 @@
-"""Context-parallel attention: the sequence is split into contiguous chunks over the ``cp`` axis.
+"""Context-parallel attention: the sequence is split over the ``cp`` axis, zig-zag (rank ``r`` holds chunks ``r``
+and ``2 cp - 1 - r`` of ``2 cp``) so that causal work is balanced, or contiguously when the length does not divide.
 
 The reference shards activations on the sequence axis and lets XLA all-gather K/V around a plain global
 einsum (src/jaxtitan/models/execution.py:227-240, mesh/sharding.py:165-167).  Here every rank normalises and
@@ -59,23 +60,49 @@ class _OffsetAttentionFn(torch.autograd.Function):
 
 
 def context_parallel_attention(ex, qkv: torch.Tensor, wq, wk, positions: torch.Tensor, *, B: int, S: int, hq: int,
-                               hkv: int, D: int, eps: float, theta: float, rope: bool,
-                               lo: torch.Tensor | None) -> torch.Tensor:
-    """qkv: this rank's ``[B*S_local, (hq + 2 hkv) D]`` projection; positions: local indices ``[B*S_local]``;
-    ``lo``: per-row first visible *global* kv position or None.  Returns ``[B, S_local, hq * D]``."""
+                               hkv: int, D: int, eps: float, theta: float, rope: bool, lo: torch.Tensor | None,
+                               chunks: tuple[tuple[int, int], ...] = ()) -> torch.Tensor:
+    """qkv: this rank's ``[B*S_local, (hq + 2 hkv) D]`` projection; positions: *global* positions ``[B*S_local]``;
+    ``lo``: per-row first visible global kv position or None; ``chunks``: the ``(first global position, length)``
+    runs that make up the local rows (one run for a contiguous split, two for the zig-zag split).
+    Returns ``[B, S_local, hq * D]``."""
 
     cp, rank, group = ex.cp_size, ex.cp_rank, ex.cp_group
-    q_offset = rank * S
-    global_pos = (positions + q_offset).to(torch.int32)
-    qk = Fn.qk_norm_rope(qkv, wq, wk, global_pos, hq, hkv, D, eps, theta, rope)
+    if not chunks:
+        chunks = ((rank * S, S),)
+    qk = Fn.qk_norm_rope(qkv, wq, wk, positions.to(torch.int32), hq, hkv, D, eps, theta, rope)
     q4 = qk[:, : hq * D].reshape(B, S, hq, D)
     k4 = qk[:, hq * D:].reshape(B, S, hkv, D)
     v4 = qkv[:, (hq + hkv) * D:].reshape(B, S, hkv, D)
-    k_all = _GatherKV.apply(k4, group)[:, : (rank + 1) * S]
-    v_all = _GatherKV.apply(v4, group)[:, : (rank + 1) * S]
+    zigzag = S % 2 == 0   # the rule of steps.train.context_positions: an even local length means the zig-zag split
+    k_all = _in_sequence_order(_GatherKV.apply(k4, group), cp, S, zigzag)
+    v_all = _in_sequence_order(_GatherKV.apply(v4, group), cp, S, zigzag)
     scale = D ** -0.5
-    if Fn.use_native(qkv) and D in (64, 128) and S % 128 == 0:
-        o = _OffsetAttentionFn.apply(q4.contiguous(), k_all.contiguous(), v_all.contiguous(), lo, q_offset, scale)
-    else:
-        o = Fn.attention_reference(q4, k_all, v_all, causal=True, lo=lo, scale=scale)
+    outs = []
+    row = 0
+    for first, length in chunks:
+        end = first + length                                   # this run sees the keys of positions [0, end)
+        q_c = q4[:, row:row + length]
+        lo_c = None if lo is None else lo[:, row:row + length].contiguous()
+        k_c, v_c = k_all[:, :end], v_all[:, :end]
+        if Fn.use_native(qkv) and D in (64, 128) and length % 128 == 0 and first % 128 == 0:
+            outs.append(_OffsetAttentionFn.apply(q_c.contiguous(), k_c.contiguous(), v_c.contiguous(), lo_c, first,
+                                                 scale))
+        else:
+            outs.append(Fn.attention_reference(q_c, k_c, v_c, causal=True, lo=lo_c, scale=scale))
+        row += length
+    o = outs[0] if len(outs) == 1 else torch.cat(outs, dim=1)
     return o.reshape(B, S, hq * D)
+
+
+def _in_sequence_order(gathered: torch.Tensor, cp: int, s_local: int, zigzag: bool) -> torch.Tensor:
+    """The all-gather returns rank-major rows; with the zig-zag split rank ``r`` holds chunks ``r`` and
+    ``2 cp - 1 - r``, so the second halves come back in reverse rank order."""
+
+    if not zigzag:
+        return gathered
+    B = gathered.shape[0]
+    c = s_local // 2
+    g = gathered.reshape(B, cp, 2, c, *gathered.shape[2:])
+    first, second = g[:, :, 0], g[:, :, 1].flip(1)
+    return torch.cat([first, second], dim=1).reshape(B, 2 * cp * c, *gathered.shape[2:])

@@ -39,8 +39,27 @@ class DeviceBatch:
     local_token_count: float
 
 
-def local_batch_slices(mesh: MeshContext, batch_rows: int, seq_len: int) -> tuple[slice, slice]:
-    """Rows of the global microbatch and the sequence range this rank works on.
+def context_positions(seq_len: int, cp: int, cp_rank: int) -> np.ndarray:
+    """Global sequence positions that context-parallel rank ``cp_rank`` works on.
+
+    Zig-zag split: the sequence is cut into ``2 cp`` chunks and rank ``r`` takes chunks ``r`` and ``2 cp - 1 - r``,
+    so that under a causal mask every rank attends to the same number of (query, key) pairs.  (The reference splits
+    contiguously and leaves the balance to XLA's partitioner: mesh/sharding.py:165-167.)  Odd chunkings fall back to
+    the contiguous split."""
+
+    if cp == 1:
+        return np.arange(seq_len)
+    if seq_len % (2 * cp):
+        seq = seq_len // cp
+        return np.arange(cp_rank * seq, (cp_rank + 1) * seq)
+    c = seq_len // (2 * cp)
+    return np.concatenate([np.arange(cp_rank * c, (cp_rank + 1) * c),
+                           np.arange((2 * cp - 1 - cp_rank) * c, (2 * cp - cp_rank) * c)])
+
+
+def local_batch_slices(mesh: MeshContext, batch_rows: int, seq_len: int):
+    """Rows of the global microbatch (a slice) and the sequence positions (a slice, or an index array under
+    context parallelism) this rank works on.
 
     The batch is split over the ``data`` and ``fsdp`` axes (``data`` major), the sequence over ``cp``.
     """
@@ -49,8 +68,8 @@ def local_batch_slices(mesh: MeshContext, batch_rows: int, seq_len: int) -> tupl
     dp_rank = mesh.coord("data") * mesh.size("fsdp") + mesh.coord("fsdp")
     rows = batch_rows // dp
     cp, cp_rank = mesh.size("cp"), mesh.coord("cp")
-    seq = seq_len // cp
-    return slice(dp_rank * rows, (dp_rank + 1) * rows), slice(cp_rank * seq, (cp_rank + 1) * seq)
+    cols = slice(0, seq_len) if cp == 1 else context_positions(seq_len, cp, cp_rank)
+    return slice(dp_rank * rows, (dp_rank + 1) * rows), cols
 
 
 class BatchStager:
@@ -77,9 +96,9 @@ class BatchStager:
         return buf.to(self.device, non_blocking=True)
 
     def stage(self, batch: Batch, rows: slice, cols: slice, slot: int) -> DeviceBatch:
-        ids = np.asarray(batch.input_ids)[rows, cols]
-        tgt = np.asarray(batch.target_ids)[rows, cols]
-        msk = np.asarray(batch.loss_mask)[rows, cols]
+        ids = np.ascontiguousarray(np.asarray(batch.input_ids)[rows][:, cols])
+        tgt = np.ascontiguousarray(np.asarray(batch.target_ids)[rows][:, cols])
+        msk = np.ascontiguousarray(np.asarray(batch.loss_mask)[rows][:, cols])
         docs = None if batch.token_doc_ids is None else np.asarray(batch.token_doc_ids)[rows]
         ctx = torch.cuda.stream(self.stream) if self.cuda else _NullCtx()
         with ctx:

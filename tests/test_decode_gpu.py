@@ -123,3 +123,36 @@ def test_generation_native_decode_matches_masked_attention(monkeypatch):
     res = generation.generate_tokens(model, prompts, max_new_tokens=8, temperature=1.0, top_k=50, seed=0)
     native.check_status()
     assert len(res.generated_ids) == 3 and all(len(g) == 8 for g in res.generated_ids)
+
+
+def test_sampler_kernel_threshold_logprob_and_distribution():
+    from research_b200.ops import native
+
+    torch.manual_seed(0)
+    B, V = 4, 50304
+    logits = (torch.randn(B, V, device="cuda") * 2.0).bfloat16()
+    # argmax
+    tok, lp = native.sample_topk(logits, torch.rand(B, device="cuda"), 1.0, 1)
+    assert torch.equal(tok, logits.float().argmax(-1)) and bool((lp == 0).all())
+    # threshold with ties: kept set and log-probabilities against the PyTorch formulation
+    for T, k in ((1.0, 50), (0.7, 8), (1.3, None)):
+        scaled = logits.float() / T
+        if k is not None:
+            thr = torch.topk(scaled, k, dim=-1).values[:, -1:]
+            scaled = torch.where(scaled >= thr, scaled, torch.full_like(scaled, float("-inf")))
+        ref_logp = torch.log_softmax(scaled, -1)
+        for trial in range(8):
+            u = torch.rand(B, device="cuda")
+            tok, lp = native.sample_topk(logits, u, T, k)
+            chosen = ref_logp.gather(1, tok[:, None])[:, 0]
+            assert bool(torch.isfinite(chosen).all()), "sampled a token outside the kept set"
+            assert torch.allclose(lp, chosen, atol=2e-3, rtol=1e-3), (lp, chosen)
+    # distribution: small vocabulary, many draws of one row
+    small = torch.tensor([[2.0, 1.0, 0.0, -1.0, 3.0, 0.5, -2.0, 1.5]], device="cuda").repeat(4096, 1)
+    tok, _ = native.sample_topk(small, torch.rand(4096, device="cuda"), 1.0, 4)
+    freq = torch.bincount(tok, minlength=8).float() / 4096
+    kept = torch.tensor([2.0, 1.0, 3.0, 1.5])
+    probs = torch.zeros(8)
+    probs[[0, 1, 4, 7]] = torch.softmax(kept, 0)
+    assert float((freq.cpu() - probs).abs().max()) < 0.03, (freq, probs)
+    native.check_status()
