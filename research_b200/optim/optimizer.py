@@ -123,6 +123,8 @@ class Optimizer:
                 slow = [e for e in sec.entries if store.owns(sec, e)]
                 if sec.backend == "muon" and self._fast_muon_ok():
                     slow = self._muon_section_fast(i, sec, slow, lr)
+                elif sec.backend == "dion2" and self._fast_muon_ok():
+                    slow = [e for e in slow if not self._dion2_entry_fast(i, sec, e, lr)]
                 for e in slow:
                     self._matrix_entry(i, sec, e, lr)
         store.gather_compute_weights()
@@ -283,6 +285,53 @@ class Optimizer:
         if wd != 0.0:
             w.mul_(1.0 - lr * wd)
         w.add_(o.to(w.dtype), alpha=-scale)
+
+    def _dion2_entry_fast(self, i: int, sec: Section, e: StorageEntry, lr: float) -> bool:
+        """Dion2 for one storage entry with every logical matrix of it (all experts of a rank-3 stack) handled by
+        the same batched ops: L1 norms, one top-k, one gather, a batched Polar Express on tcgen05 GEMMs, one
+        scatter.  Same rules as ``_dion2_matrix`` (reference: src/jaxtitan/optim/dion2.py:34-125).  Returns False
+        when the entry is not eligible and must take the per-matrix path."""
+
+        store = self.store
+        master = store.master_view(sec, e)
+        if master is None or master.dim() not in (2, 3) or any(self.routes[m.name].backend != "dion2" for m in e.metas):
+            return False
+        lo, _ = store.local_master_range(sec)
+        mom = self.state[i]["momentum"][e.offset - lo:e.offset - lo + e.numel].view(e.param.shape)
+        grad = e.param.main_grad
+        wd = float(self.spec.weight_decay)
+        lead = (slice(None),) if master.dim() == 3 else ()
+        for meta in e.metas:
+            route = self.routes[meta.name]
+            sl = lead + ((slice(None),) if meta.rows is None else (slice(*meta.rows),))
+            m3 = mom[sl] if master.dim() == 3 else mom[sl].unsqueeze(0)
+            g3 = grad[sl] if master.dim() == 3 else grad[sl].unsqueeze(0)
+            w3 = master[sl] if master.dim() == 3 else master[sl].unsqueeze(0)
+            n, rows, cols = m3.shape
+            logical_axis = route.matrix_axis if route.matrix_axis is not None else 0
+            if len(meta.shape) == 3:
+                logical_axis -= 1
+            axis = (1 - logical_axis) if meta.transposed else logical_axis      # 0: rows are selected, 1: columns
+            k = max(1, math.ceil(orth.DION2_FRACTION * (rows if axis == 0 else cols)))
+            if (k % 8) or (rows % 8) or (cols % 8):
+                return False
+            m3.addcmul_(g3, self._clip)
+            norms = torch.linalg.vector_norm(m3, ord=1, dim=2 if axis == 0 else 1)             # [n, rows | cols]
+            idx = torch.topk(norms, k, dim=1).indices                                          # [n, k]
+            gidx = idx[:, :, None].expand(n, k, cols) if axis == 0 else idx[:, None, :].expand(n, rows, k)
+            selected = torch.gather(m3, 1 + axis, gidx)                                        # fp32
+            stack = selected.to(torch.bfloat16).contiguous()
+            sq = stack.float().pow(2).sum(dim=(1, 2))
+            stack = stack / (sq.sqrt().to(torch.bfloat16)[:, None, None] * 1.02 + orth.DION2_EPSILON)
+            o = orth.newton_schulz_stack_(stack.contiguous(), orth.DION2_POLAR_EXPRESS_COEFFICIENTS)
+            if wd != 0.0 and route.weight_decay:
+                w3.mul_(1.0 - lr * wd)
+            scale = lr * math.sqrt(meta.shape[-2] / meta.shape[-1])
+            w3.scatter_add_(1 + axis, gidx, o.float() * (-scale))
+            m3.scatter_(1 + axis, gidx, selected * orth.DION2_EF_DECAY)
+        if store.compute_dtype != torch.float32:
+            e.param.data.copy_(master)
+        return True
 
     def _dion2_update(self, meta, route, g, m, w, lr: float, wd: float) -> None:
         m.add_(g)

@@ -145,7 +145,7 @@ def test_adamw_sumsq_cast():
     assert torch.allclose(y.float(), p * 0.5, atol=1e-2, rtol=1e-2)
 
 
-@pytest.mark.parametrize("family", ["decoder", "trinity_moe"])
+@pytest.mark.parametrize("family", ["decoder", "trinity_moe", "trinity_moe_dion"])
 def test_fast_muon_section_matches_reference_path(family):
     """The batched tcgen05 Muon step against the per-matrix PyTorch restatement of the same update
     (2-D matrices, row slices of fused parameters, and rank-3 expert stacks)."""
@@ -165,7 +165,9 @@ def test_fast_muon_section_matches_reference_path(family):
         "data": {"train_manifest": "unused.json"},
         "training": {"seq_len": 256, "global_batch_size": 2, "target_tokens": 2 * 256 * 4, "precision": "bf16"},
     }
-    if family == "trinity_moe":
+    if family == "trinity_moe_dion":
+        raw["optimizer"]["name"] = "dion"
+    if family.startswith("trinity_moe"):
         raw["model"].update(name="trinity", num_layers=2, trinity={
             "initial_dense_layers": 1, "local_window": 128, "local_layers_per_global": 1, "norm_policy": "afmoe_dual",
             "moe": {"num_experts": 4, "top_k": 2, "expert_intermediate_size": 256, "num_shared_experts": 1}})
