@@ -42,9 +42,11 @@ class PaddedLayout:
         self.k_range = torch.stack([starts, ends], dim=1).to(torch.int32).contiguous()
 
 
-def _grouped_rows(a: torch.Tensor, w3: torch.Tensor, layout: PaddedLayout, *, b_mn: bool, out_n: int) -> torch.Tensor:
+def _grouped_rows(a: torch.Tensor, w3: torch.Tensor, layout: PaddedLayout, *, b_mn: bool, out_n: int,
+                  out: torch.Tensor | None = None) -> torch.Tensor:
     lib = native.load()
-    out = torch.empty(a.shape[0], out_n, dtype=torch.bfloat16, device=a.device)
+    if out is None:
+        out = torch.empty(a.shape[0], out_n, dtype=torch.bfloat16, device=a.device)
     E = w3.shape[0]
     K = a.shape[1]
     rc = lib.b200_gemm_bf16_grouped_rows(a.data_ptr(), w3.data_ptr(), out.data_ptr(), a.shape[0], out_n, K, E,
@@ -69,11 +71,14 @@ class _GroupedLinearFn(torch.autograd.Function):
     """y[rows of expert e] = x[rows of e] @ W[e]^T for an expert-major padded x."""
 
     @staticmethod
-    def forward(ctx, x_pad, p, layout):
+    def forward(ctx, x_pad, p, layout, out=None, dx_out=None):
+        """``out`` / ``dx_out``: optional preallocated buffers for the product and for the input gradient (the
+        expert-parallel path points them at its outbox in the symmetric arena, which saves a copy each way)."""
+
         w = Fn.compute_weight(p, x_pad)
         ctx.save_for_backward(x_pad)
-        ctx.p, ctx.layout = p, layout
-        return _grouped_rows(x_pad, w, layout, b_mn=False, out_n=w.shape[1])
+        ctx.p, ctx.layout, ctx.dx_out = p, layout, dx_out
+        return _grouped_rows(x_pad, w, layout, b_mn=False, out_n=w.shape[1], out=out)
 
     @staticmethod
     def backward(ctx, dy):
@@ -81,10 +86,10 @@ class _GroupedLinearFn(torch.autograd.Function):
         p, layout = ctx.p, ctx.layout
         w = Fn.compute_weight(p, x_pad)
         dy = dy.contiguous()
-        dx = _grouped_rows(dy, w, layout, b_mn=True, out_n=w.shape[2])
+        dx = _grouped_rows(dy, w, layout, b_mn=True, out_n=w.shape[2], out=ctx.dx_out)
         if p.requires_grad:
             _grouped_k(dy, x_pad, Fn._main_grad(p), layout)
-        return dx, None, None
+        return dx, None, None, None, None
 
 
 def grouped_expert_ffn(rows: torch.Tensor, counts: torch.Tensor, w_gate_up: torch.Tensor,

@@ -118,8 +118,10 @@ class ExpertParallelPlan:
         return (self.dest >= 0).view(self.T, self.k)
 
 
-def _push_rows(x, scale, plan: ExpertParallelPlan, ws: ExpertParallelWorkspace) -> torch.Tensor:
-    """Zero my inbox, barrier, store my rows into the owners' inboxes, barrier; returns a private copy of my inbox."""
+def _push_rows(x, scale, plan: ExpertParallelPlan, ws: ExpertParallelWorkspace, *, keep: bool) -> torch.Tensor:
+    """Zero my inbox, barrier, store my rows into the owners' inboxes, barrier.  Returns my inbox: a private copy
+    when the rows must outlive the next use of the inbox (``keep``: forward activations saved for backward), else
+    the arena view itself (gradients, which the next autograd node consumes before anything is pushed again)."""
 
     lib = _moe_lib()
     used = ws.inbox[:plan.rows_per_rank]
@@ -130,14 +132,16 @@ def _push_rows(x, scale, plan: ExpertParallelPlan, ws: ExpertParallelWorkspace) 
                              native._stream())
     native._check(rc, "b200_moe_gather")
     ws.barrier()
-    return used.clone()
+    return used.clone() if keep else used
 
 
 def _pull_rows(local_rows, w, plan: ExpertParallelPlan, ws: ExpertParallelWorkspace) -> torch.Tensor:
     """Publish my outbox, barrier, gather-and-sum my tokens' rows from the owners' outboxes, barrier."""
 
     lib = _moe_lib()
-    ws.outbox[:plan.rows_per_rank].copy_(local_rows)
+    mine = ws.outbox[:plan.rows_per_rank]
+    if local_rows.data_ptr() != mine.data_ptr():   # the grouped GEMM normally writes straight into the outbox
+        mine.copy_(local_rows)
     ws.barrier()
     H = local_rows.shape[1]
     y = torch.empty(plan.T, H, dtype=torch.bfloat16, device=local_rows.device)
@@ -152,7 +156,7 @@ class _EpDispatchFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, plan, ws):
         ctx.plan, ctx.ws = plan, ws
-        return _push_rows(x.contiguous(), None, plan, ws)
+        return _push_rows(x.contiguous(), None, plan, ws, keep=True)
 
     @staticmethod
     def backward(ctx, d_rows):
@@ -184,7 +188,7 @@ class _EpCombineFn(torch.autograd.Function):
         mine, w32 = ctx.saved_tensors
         plan, ws = ctx.plan, ctx.ws
         dy = dy.contiguous()
-        d_rows = _push_rows(dy, w32, plan, ws) if ctx.needs_input_grad[0] else None
+        d_rows = _push_rows(dy, w32, plan, ws, keep=False) if ctx.needs_input_grad[0] else None
         dw = None
         if ctx.needs_input_grad[1]:
             dw32 = (mine.view(plan.T, plan.k, -1).float() * dy.view(plan.T, 1, -1).float()).sum(-1)
@@ -208,6 +212,9 @@ def dispatch_and_combine_fused(experts, x: torch.Tensor, weights: torch.Tensor, 
         raise KernelError("expert-parallel dispatch needs a hidden size that is a multiple of 8")
     ws = workspace_for(ex, plan.rows_per_rank, x.shape[1], x.device)
     rows = _EpDispatchFn.apply(x, plan, ws)
-    h = Fn.swiglu(_GroupedLinearFn.apply(rows, experts.w_gate_up, plan.owner))
-    out = _GroupedLinearFn.apply(h, experts.w_down, plan.owner)
+    outbox = ws.outbox[:plan.rows_per_rank]
+    # the input gradient of the first product and the output of the second are what peers read: write them
+    # straight into the outbox
+    h = Fn.swiglu(_GroupedLinearFn.apply(rows, experts.w_gate_up, plan.owner, None, outbox))
+    out = _GroupedLinearFn.apply(h, experts.w_down, plan.owner, outbox, None)
     return _EpCombineFn.apply(out, weights, plan, ws)
