@@ -74,8 +74,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   // heavy (late) query tiles first: causal work grows with the tile index
   const int q_tiles = (p.S + NT * TILE_M - 1) / (NT * TILE_M);
-  const int qt = q_tiles - 1 - (int)(blockIdx.x % q_tiles);
-  const int bh = blockIdx.x / q_tiles;
+  // ... over the whole grid (all heads of the longest tile, then the next), which balances the tail
+  const int nbh = p.B * p.Hq;
+  const int qt = q_tiles - 1 - (int)(blockIdx.x / nbh);
+  const int bh = blockIdx.x % nbh;
   const int h = bh % p.Hq;
   const int b = bh / p.Hq;
   const int hkv = h / (p.Hq / p.Hkv);

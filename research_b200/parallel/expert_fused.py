@@ -191,7 +191,18 @@ class _EpCombineFn(torch.autograd.Function):
         d_rows = _push_rows(dy, w32, plan, ws, keep=False) if ctx.needs_input_grad[0] else None
         dw = None
         if ctx.needs_input_grad[1]:
-            dw32 = (mine.view(plan.T, plan.k, -1).float() * dy.view(plan.T, 1, -1).float()).sum(-1)
+            # dw[a] = <row a of my unweighted expert outputs, dy[token of a]>: one warp per assignment
+            lib = _moe_lib()
+            A = plan.T * plan.k
+            ident = plan.__dict__.get("_ident")
+            if ident is None:
+                ident = plan._ident = torch.arange(A, device=dy.device, dtype=torch.int32)
+            dw32 = torch.empty(A, dtype=torch.float32, device=dy.device)
+            one = (ctypes.c_void_p * 1)()
+            one[0] = mine.data_ptr()
+            rc = lib.b200_moe_combine_dw(one, 1, dy.data_ptr(), ident.data_ptr(), dw32.data_ptr(), A, mine.shape[1],
+                                         plan.k, 0, native._stream())
+            native._check(rc, "b200_moe_combine_dw")
             dw = dw32.view(ctx.w_shape).to(ctx.w_dtype)
         return d_rows, dw, None, None
 
