@@ -279,12 +279,20 @@ class ExecutionContext:
         if rows_local % 128 or width % 64:
             return None
         need = x.shape[0] * rows_local * width
+        if self.extras.get("tp_fusion_failed"):
+            return None
         ws = self.extras.get("tp_fusion")
         if ws is None or ws.stage.numel() < need:
+            from research_b200.parallel.symmetric import build_collectively
             from research_b200.parallel.tensor_fused import TensorParallelFusion
 
-            ws = TensorParallelFusion(self.tp_group, max_shard_elems=need, max_out_elems=need, device=x.device)
+            ws = build_collectively(
+                self.tp_group,
+                lambda: TensorParallelFusion(self.tp_group, max_shard_elems=need, max_out_elems=need, device=x.device),
+                "fused tensor-parallel workspace")
             self.extras["tp_fusion"] = ws
+            if ws is None:
+                self.extras["tp_fusion_failed"] = True
         return ws
 
     def column_linear(self, x: torch.Tensor, p: torch.Tensor) -> torch.Tensor:

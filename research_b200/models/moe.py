@@ -182,7 +182,10 @@ class SparseMoE(nn.Module):
                 from research_b200.parallel import expert_fused
 
                 if ex.ep_axis_sharing != "dedicated_ep" and expert_fused.fused_available(ex, x, capacity):
-                    plan = expert_fused.ExpertParallelPlan(expert_ids.reshape(B * S, -1), self.num_experts, capacity, ex)
+                    plan = expert_fused.ExpertParallelPlan(expert_ids.reshape(B * S, -1), self.num_experts, capacity, ex,
+                                                           H)
+                    if plan.ws is None:
+                        plan = None
             if plan is None and capacity is not None:
                 weights, dropped = apply_capacity(expert_ids, weights, self.num_experts, self.moe.capacity_factor)
             elif capacity is not None:

@@ -61,18 +61,27 @@ class ExpertParallelWorkspace:
         self.arena.barrier(BARRIER_CHANNEL)
 
 
-def workspace_for(ex, rows: int, hidden: int, device: torch.device) -> ExpertParallelWorkspace:
+def workspace_for(ex, rows: int, hidden: int, device: torch.device) -> ExpertParallelWorkspace | None:
+    """The arena workspace of the ep group, built (collectively) on first use; None when peer memory is refused."""
+
+    if ex.extras.get("ep_workspace_failed"):
+        return None
     ws = ex.extras.get("ep_workspace")
     if ws is None or ws.rows < rows or ws.hidden != hidden:
-        ws = ExpertParallelWorkspace(ex.ep_group, rows, hidden, device)
+        from research_b200.parallel.symmetric import build_collectively
+
+        ws = build_collectively(ex.ep_group, lambda: ExpertParallelWorkspace(ex.ep_group, rows, hidden, device),
+                                "expert-parallel workspace")
         ex.extras["ep_workspace"] = ws
+        if ws is None:
+            ex.extras["ep_workspace_failed"] = True
     return ws
 
 
 class ExpertParallelPlan:
     """Routing plan of one layer under expert parallelism (device tensors only, no host synchronisation)."""
 
-    def __init__(self, expert_ids: torch.Tensor, num_experts: int, capacity: int, ex):
+    def __init__(self, expert_ids: torch.Tensor, num_experts: int, capacity: int, ex, hidden: int):
         lib = _moe_lib()
         dev = expert_ids.device
         R, rank = ex.ep_size, ex.ep_rank
@@ -112,6 +121,7 @@ class ExpertParallelPlan:
                                           k_range.data_ptr(), tile_group.data_ptr(), None, st), "b200_moe_layout")
         self.owner = SimpleNamespace(tile_group=tile_group, k_range=k_range.view(el, 2))
         self.ex = ex
+        self.ws = workspace_for(ex, self.rows_per_rank, hidden, dev)   # None: peer memory refused, use NCCL
 
     @property
     def kept_mask(self) -> torch.Tensor:
@@ -221,7 +231,7 @@ def dispatch_and_combine_fused(experts, x: torch.Tensor, weights: torch.Tensor, 
     ex = plan.ex
     if x.shape[1] % 8:
         raise KernelError("expert-parallel dispatch needs a hidden size that is a multiple of 8")
-    ws = workspace_for(ex, plan.rows_per_rank, x.shape[1], x.device)
+    ws = plan.ws
     rows = _EpDispatchFn.apply(x, plan, ws)
     outbox = ws.outbox[:plan.rows_per_rank]
     # the input gradient of the first product and the output of the second are what peers read: write them

@@ -179,10 +179,13 @@ class ParamStore:
         self.arena = None
         group = self._symmetric_group()
         if group is not None:
-            from research_b200.parallel.symmetric import SymmetricArena
+            from research_b200.parallel.symmetric import SymmetricArena, build_collectively
 
             esize = torch.empty((), dtype=self.compute_dtype).element_size()
-            self.arena = SymmetricArena(group, self.total * (4 + esize) + 8192, device=dev, tag="params")
+            self.arena = build_collectively(
+                group, lambda: SymmetricArena(group, self.total * (4 + esize) + 8192, device=dev, tag="params"),
+                "symmetric parameter arena")
+        if self.arena is not None:
             self.grad_arena, self._grad_off = self.arena.carve(self.total, torch.float32)
             self.compute_arena, self._compute_off = self.arena.carve(self.total, self.compute_dtype)
         else:

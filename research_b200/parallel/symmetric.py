@@ -211,3 +211,26 @@ class SymmetricArena:
             for p in self.ptrs:
                 self._lib.b200c_vmm_free(p, self.padded)
             self.ptrs = []
+
+
+def build_collectively(group, factory, what: str):
+    """Run ``factory()`` (which allocates symmetric memory, a collective operation) on every rank of ``group`` and
+    return its result only if it succeeded everywhere; otherwise every rank gets ``None`` and the caller takes its
+    NCCL formulation.  The reason is printed once per rank, so a box whose driver refuses shareable allocations
+    still trains."""
+
+    import sys
+
+    obj, err = None, None
+    try:
+        obj = factory()
+    except Exception as exc:  # noqa: BLE001 - any failure means "do not use peer memory"
+        err = exc
+    ok = torch.tensor([0 if err is not None else 1], dtype=torch.int32,
+                      device=torch.device("cuda", torch.cuda.current_device()))
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+    if int(ok.item()) == 1:
+        return obj
+    print(f"research_b200: {what} unavailable on rank {dist.get_rank(group)}"
+          f"{'' if err is None else f' ({type(err).__name__}: {err})'}; using the NCCL path", file=sys.stderr)
+    return None
