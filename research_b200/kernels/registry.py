@@ -27,9 +27,21 @@ KERNEL_CANDIDATES = (
     {"op": "optimizer_adamw", "source": "elementwise.cu", "symbol": "b200_adamw", "engine": "SIMT"},
     {"op": "optimizer_matrix_update", "source": "gemm.cu", "symbol": "b200_gemm_bf16", "engine": "tcgen05 (Newton-Schulz)"},
     {"op": "decode_attention", "source": "decode.cu", "symbol": "b200_decode_attn", "engine": "SIMT split-KV"},
-    {"op": "gemm_allgather", "source": "comm_gemm.cu", "symbol": "b200_ag_gemm", "engine": "tcgen05 + peer loads"},
-    {"op": "gemm_reduce_scatter", "source": "comm_gemm.cu", "symbol": "b200_gemm_rs", "engine": "tcgen05 + peer reduce"},
+    {"op": "kv_cache_append", "source": "decode.cu", "symbol": "b200_kv_append", "engine": "SIMT 128-bit"},
+    {"op": "sampler", "source": "sampler.cu", "symbol": "b200_sample_topk", "engine": "SIMT radix select"},
+    {"op": "moe_dispatch_combine", "source": "moe.cu", "symbol": "b200_moe_gather", "engine": "SIMT + NVLink peer stores/loads"},
+    {"op": "moe_routing_plan", "source": "moe.cu", "symbol": "b200_moe_rank", "engine": "SIMT match_any"},
+    {"op": "optimizer_muon_elementwise", "source": "optimizer.cu", "symbol": "b200_muon_momentum_batched", "engine": "SIMT"},
+    {"op": "gemm_allgather", "source": "comm_gemm.cu", "symbol": "b200_gemm_allgather", "engine": "tcgen05 + TMA peer loads"},
+    {"op": "gemm_reduce_scatter", "source": "comm_gemm.cu", "symbol": "b200_gemm_reducescatter", "engine": "tcgen05 + TMA peer reduce-add"},
+    {"op": "grad_reduce_scatter", "source": "comm_runtime.cu", "symbol": "b200c_reduce_scatter_pull", "engine": "SIMT peer loads"},
+    {"op": "weight_all_gather", "source": "comm_runtime.cu", "symbol": "b200c_all_gather_pull", "engine": "SIMT peer loads"},
 )
+
+# ops that only some runs need (generation, multi-GPU layouts, MoE): never a reason for kernels.strict to refuse
+OPTIONAL_OPS = ("decode_attention", "kv_cache_append", "sampler", "moe_dispatch_combine", "moe_routing_plan",
+                "gemm_allgather", "gemm_reduce_scatter", "grad_reduce_scatter", "weight_all_gather",
+                "grouped_expert_gemm")
 
 
 def kernel_registry() -> list[dict[str, Any]]:
@@ -67,7 +79,6 @@ def require_kernel_plan_supported(plan: dict[str, Any], spec: RunSpec) -> None:
 
     if not spec.kernels.strict:
         return
-    missing = [op["op"] for op in plan["ops"] if not op["selected"] and op["op"] not in
-               ("decode_attention", "gemm_allgather", "gemm_reduce_scatter")]
+    missing = [op["op"] for op in plan["ops"] if not op["selected"] and op["op"] not in OPTIONAL_OPS]
     if missing:
         raise ContractError(f"kernels.strict=true but these ops would not run natively: {missing}")
