@@ -170,9 +170,12 @@ extern "C" int b200_muon_momentum(const void* g, void* m, void* u, void* sumsq, 
 extern "C" int b200_muon_momentum_batched(const void* g, void* m, void* u, void* sumsq, const void* clip, long long n,
                                           long long stride, int batch, float beta, int nesterov, void* stream) {
   if (n <= 0 || (n & 3) || (stride & 3) || batch < 1) return -2;
-  int bx = blocks_for(n / 4, 256, 1);
-  if (bx > 64) bx = 64;
-  const dim3 grid(bx, batch > 65535 ? 65535 : batch);
+  // about four waves of CTAs in total: many blocks per matrix for a single big matrix, few for a large batch
+  const int by = batch > 65535 ? 65535 : batch;
+  int bx = blocks_for(n / 4, 256, 4);
+  const int per_matrix = (blocks_for(1LL << 40, 256, 4) + by - 1) / by;
+  if (bx > per_matrix) bx = per_matrix;
+  const dim3 grid(bx < 1 ? 1 : bx, by);
   muon_momentum_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       (const float*)g, (float*)m, (__nv_bfloat16*)u, (float*)sumsq, (const float*)clip, n, stride, batch, beta,
       nesterov);
@@ -189,9 +192,12 @@ extern "C" int b200_muon_apply(void* w, const void* o, void* shadow, long long n
 extern "C" int b200_muon_apply_batched(void* w, const void* o, void* shadow, long long n, long long stride, int batch,
                                        float decay, float step, void* stream) {
   if (n <= 0 || (n & 3) || (stride & 3) || batch < 1) return -2;
-  int bx = blocks_for(n / 4, 256, 1);
-  if (bx > 64) bx = 64;
-  const dim3 grid(bx, batch > 65535 ? 65535 : batch);
+  // about four waves of CTAs in total: many blocks per matrix for a single big matrix, few for a large batch
+  const int by = batch > 65535 ? 65535 : batch;
+  int bx = blocks_for(n / 4, 256, 4);
+  const int per_matrix = (blocks_for(1LL << 40, 256, 4) + by - 1) / by;
+  if (bx > per_matrix) bx = per_matrix;
+  const dim3 grid(bx < 1 ? 1 : bx, by);
   muon_apply_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       (float*)w, (const __nv_bfloat16*)o, (__nv_bfloat16*)shadow, n, stride, batch, decay, step);
   return static_cast<int>(cudaGetLastError());
