@@ -2,6 +2,7 @@
 
 import glob
 import json
+import os
 from pathlib import Path
 
 import pytest
@@ -11,7 +12,9 @@ from research_b200.config import (load_config, resolved_config_sha256, run_spec_
 from research_b200.errors import ConfigError
 from tests.helpers import tiny_raw_config
 
-REFERENCE_CONFIGS = sorted(glob.glob("/root/reference/configs/jaxtitan/*.toml"))
+# the reference checkout, when one sits beside this repository (or where JAXTITAN_REFERENCE points)
+_REFERENCE = Path(os.environ.get("JAXTITAN_REFERENCE", Path(__file__).resolve().parents[2] / "reference"))
+REFERENCE_CONFIGS = sorted(glob.glob(str(_REFERENCE / "configs" / "jaxtitan" / "*.toml")))
 
 
 def _raw(**kw):
