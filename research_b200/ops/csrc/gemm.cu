@@ -351,6 +351,17 @@ extern "C" int b200_gemm_bf16_splitk(const void* A, const void* B, void* C, int 
                    stream, 1);
 }
 
+// Split-K for any operand layout with an fp32 output that is accumulated into (weight gradients: the contraction
+// runs over tokens and is long, the output has few tiles, and the partial sums are reduce-added anyway).
+extern "C" int b200_gemm_bf16_splitk_acc(const void* A, const void* B, void* C, int M, int N, int K, int splits,
+                                         long long lda, long long ldb, long long ldc, int a_mn, int b_mn, int* status,
+                                         void* stream) {
+  if (splits < 1 || K % (64 * splits)) return b200host::RC_BAD_SHAPE;
+  const int kc = K / splits;
+  return gemm_impl(A, B, C, M, N, kc, splits, 1, 1, 1, lda, ldb, ldc, 0, 0, 0, a_mn, b_mn, 1, 1, 0, nullptr, nullptr,
+                   status, stream, 1);
+}
+
 // Grouped forward / data-gradient product: A [M_pad, K] and C [M_pad, N] are 2-D with every group's rows
 // padded to a multiple of 128; B is [groups, ...]; tile_group[m_tile] names the group of each row tile.
 extern "C" int b200_gemm_bf16_grouped_rows(const void* A, const void* B, void* C, int M_pad, int N, int K, int groups,

@@ -83,7 +83,7 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = native.gemm(dy2, w, trans_b=False).view(ctx.x_shape)
         if p.requires_grad:
-            native.gemm(dy2, x2, trans_a=True, trans_b=False, out=_main_grad(p), accumulate=True)
+            native.gemm_wgrad(dy2, x2, _main_grad(p))
         return dx, None
 
 

@@ -96,6 +96,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     sig("b200_muon_apply_batched", c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_int, c_float, c_float, c_void_p)
     sig("b200_scale_by_inv_norm", c_void_p, c_void_p, c_ll, c_int, c_float, c_void_p)
     sig("b200_affine_identity", c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p)
+    sig("b200_gemm_bf16_splitk_acc", c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_int,
+        c_int, c_void_p, c_void_p)
     sig("b200_gemm_bf16_splitk", c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_void_p,
         c_void_p)
     sig("b200_sample_topk", c_void_p, c_ll, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p)
@@ -206,6 +208,41 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
 # --------------------------------------------------------------------------------------------------
 # normalisation / activation / embedding / loss / optimizer
 # --------------------------------------------------------------------------------------------------
+def wave_splits(m: int, n: int, k: int, sms: int = 148, max_splits: int = 8) -> int:
+    """K slices for an accumulated product with few output tiles: the smallest count (a divisor of ``k / 64``,
+    slices of at least 1024) whose ``tiles * splits`` fills whole waves of ``sms`` CTAs best."""
+
+    tiles = ((m + 127) // 128) * ((n + 255) // 256)
+    kblocks = k // 64
+    best, best_eff = 1, 0.0
+    for s in range(1, max_splits + 1):
+        if kblocks % s or k // s < 1024:
+            continue
+        work = tiles * s
+        eff = work / (-(-work // sms) * sms)
+        if eff > best_eff + 0.02:
+            best, best_eff = s, eff
+    return best
+
+
+def gemm_wgrad(dy: torch.Tensor, x: torch.Tensor, grad: torch.Tensor) -> None:
+    """``grad[M, N] (fp32) += dy[K, M]^T @ x[K, N]`` with the contraction over tokens cut into slices so that the
+    few output tiles fill whole waves of CTAs (the partial sums are reduce-added into ``grad`` either way)."""
+
+    K, M = dy.shape
+    N = x.shape[1]
+    splits = 1
+    if K % 64 == 0 and dy.stride(1) == 1 and x.stride(1) == 1 and grad.dim() == 2 and grad.stride(1) == 1:
+        splits = wave_splits(M, N, K)
+    if splits == 1:
+        gemm(dy, x, trans_a=True, trans_b=False, out=grad, accumulate=True)
+        return
+    lib = load()
+    rc = lib.b200_gemm_bf16_splitk_acc(dy.data_ptr(), x.data_ptr(), grad.data_ptr(), M, N, K, splits, dy.stride(0),
+                                       x.stride(0), grad.stride(0), 1, 1, status_word(dy.device).data_ptr(), _stream())
+    _check(rc, "b200_gemm_bf16_splitk_acc")
+
+
 def splitk_factor(n: int, k: int, sms: int = 148) -> int:
     """How many K slices a skinny ``[rows, k] x [n, k]^T`` product should be cut into so that about two CTAs per SM
     stream the weight: a divisor of ``k / 64`` that leaves slices of at least 128."""

@@ -147,7 +147,7 @@ class _ColumnLinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = fusion.gemm_scatter(dy2, w, b_mn=True, chunk_rows=s_local).view(B, s_local, K)
         if p.requires_grad:
-            native.gemm(dy2, x_full, trans_a=True, trans_b=False, out=Fn._main_grad(p), accumulate=True)
+            native.gemm_wgrad(dy2, x_full, Fn._main_grad(p))
         return dx, None, None
 
 
@@ -179,7 +179,7 @@ class _RowLinearFn(torch.autograd.Function):
             dy2 = dy2.contiguous()
         dh, dy_full = fusion.gather_gemm(dy2, w, b_mn=True, chunk_rows=s_local)
         if p.requires_grad:
-            native.gemm(dy_full, h2, trans_a=True, trans_b=False, out=Fn._main_grad(p), accumulate=True)
+            native.gemm_wgrad(dy_full, h2, Fn._main_grad(p))
         return (dh.view(B, S, K) if ctx.needs_input_grad[0] else None), None, None
 
 

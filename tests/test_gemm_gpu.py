@@ -99,3 +99,18 @@ def test_skinny_splitk_gemm_matches_reference():
         assert y.shape == (rows, n) and y.dtype == torch.bfloat16
         assert torch.allclose(y.float(), ref, atol=3e-2, rtol=3e-2), (rows, n, k, (y.float() - ref).abs().max().item())
     assert native.splitk_factor(2048, 2048) > 1
+
+
+def test_weight_gradient_split_k_accumulates_like_one_pass():
+    from research_b200.ops import native
+
+    torch.manual_seed(0)
+    for tokens, m, n in ((8192, 2048, 2048), (4096, 2048, 5632), (2048, 512, 256)):
+        dy = (torch.randn(tokens, m, device="cuda") * 0.1).bfloat16()
+        x = (torch.randn(tokens, n, device="cuda") * 0.5).bfloat16()
+        grad = torch.full((m, n), 0.25, dtype=torch.float32, device="cuda")
+        native.gemm_wgrad(dy, x, grad)
+        native.check_status()
+        ref = 0.25 + dy.float().t() @ x.float()
+        assert (grad - ref).abs().max().item() <= 2e-3 * ref.abs().max().item() + 1e-3
+    assert native.wave_splits(2048, 2048, 32768) > 1
