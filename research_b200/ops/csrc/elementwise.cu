@@ -209,17 +209,19 @@ __global__ void __launch_bounds__(kWarpsPerBlock * 32)
 qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ in, long long in_stride, __nv_bfloat16* __restrict__ out,
                        long long out_stride, const float* __restrict__ w, const int* __restrict__ positions,
                        float* __restrict__ rstd_out, long long tokens, int heads, int D, float eps, float log2_theta,
-                       int rope, int lph) {
+                       int rope, int lph, const float* __restrict__ w2, int heads_first) {
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int hpw = 32 / lph;
   const int sub = lane / lph, l = lane % lph;
   const long long total = tokens * heads;
   const bool has_cols = l * 8 < D;
-  float inv_freq[4], wv[8] = {1, 1, 1, 1, 1, 1, 1, 1};
+  // heads [0, heads_first) are scaled by w, the rest by w2 (query heads and key heads of a packed projection)
+  float inv_freq[4], wv[8] = {1, 1, 1, 1, 1, 1, 1, 1}, wv2[8] = {1, 1, 1, 1, 1, 1, 1, 1};
 #pragma unroll
   for (int i = 0; i < 4; ++i) inv_freq[i] = exp2f(-log2_theta * (2.f * (float)(l * 4 + i)) / (float)D);
   if (w && has_cols) load8f(w + l * 8, wv);
+  if (w2 && has_cols) load8f(w2 + l * 8, wv2);
   const long long groups = (total + hpw - 1) / hpw;
   for (long long gidx = (long long)blockIdx.x * kWarpsPerBlock + warp; gidx < groups;
        gidx += (long long)gridDim.x * kWarpsPerBlock) {
@@ -236,8 +238,9 @@ qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ in, long long in_stride
       ss = group_sum(ss, lph);
       const float rstd = rsqrtf(ss / (float)D + eps);
       if (l == 0 && rstd_out && idx < total) rstd_out[idx] = rstd;
+      const bool first = h < heads_first;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) f[i] = f[i] * rstd * wv[i];
+      for (int i = 0; i < 8; ++i) f[i] = f[i] * rstd * (first ? wv[i] : wv2[i]);
     }
     if (rope && active) {
       const float pos = (float)positions[t];
@@ -261,21 +264,22 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ in, long long in_stride
                        __nv_bfloat16* __restrict__ din, long long din_stride, const float* __restrict__ w,
                        const int* __restrict__ positions, const float* __restrict__ rstd_in,
                        float* __restrict__ dw, long long tokens, int heads, int D, float log2_theta, int rope,
-                       int lph) {
-  __shared__ float dw_smem[256];
+                       int lph, const float* __restrict__ w2, float* __restrict__ dw2, int heads_first) {
+  __shared__ float dw_smem[512];
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
   const int hpw = 32 / lph;
   const int sub = lane / lph, l = lane % lph;
   const long long total = tokens * heads;
   const bool has_cols = l * 8 < D;
-  if (threadIdx.x < 256) dw_smem[threadIdx.x] = 0.f;
+  for (int i = threadIdx.x; i < 512; i += blockDim.x) dw_smem[i] = 0.f;
   __syncthreads();
-  float inv_freq[4], wv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  float inv_freq[4], wv[8] = {0, 0, 0, 0, 0, 0, 0, 0}, wv2[8] = {0, 0, 0, 0, 0, 0, 0, 0};
 #pragma unroll
   for (int i = 0; i < 4; ++i) inv_freq[i] = exp2f(-log2_theta * (2.f * (float)(l * 4 + i)) / (float)D);
   if (w && has_cols) load8f(w + l * 8, wv);
-  float dw_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  if (w2 && has_cols) load8f(w2 + l * 8, wv2);
+  float dw_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}, dw_acc2[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   const long long groups = (total + hpw - 1) / hpw;
   for (long long gidx = (long long)blockIdx.x * kWarpsPerBlock + warp; gidx < groups;
        gidx += (long long)gridDim.x * kWarpsPerBlock) {
@@ -300,26 +304,33 @@ qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ in, long long in_stride
       float f[8] = {0, 0, 0, 0, 0, 0, 0, 0};
       if (active) unpack8(*reinterpret_cast<const uint4*>(in + t * in_stride + (long long)h * D + l * 8), f);
       const float rstd = idx < total ? rstd_in[idx] : 0.f;
+      const bool first = h < heads_first;
       float dot = 0.f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) dot += g[i] * wv[i] * f[i] * rstd;
+      for (int i = 0; i < 8; ++i) dot += g[i] * (first ? wv[i] : wv2[i]) * f[i] * rstd;
       dot = group_sum(dot, lph) / (float)D;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const float xhat = f[i] * rstd;
-        dw_acc[i] += g[i] * xhat;
-        g[i] = rstd * (g[i] * wv[i] - xhat * dot);
+        if (first) dw_acc[i] += g[i] * xhat; else dw_acc2[i] += g[i] * xhat;
+        g[i] = rstd * (g[i] * (first ? wv[i] : wv2[i]) - xhat * dot);
       }
     }
     if (active) *reinterpret_cast<uint4*>(din + t * din_stride + (long long)h * D + l * 8) = pack8(g);
   }
-  if (w && dw) {
+  if (w && (dw || dw2)) {
     if (has_cols) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) atomicAdd(&dw_smem[l * 8 + i], dw_acc[i]);
+      for (int i = 0; i < 8; ++i) {
+        atomicAdd(&dw_smem[l * 8 + i], dw_acc[i]);
+        atomicAdd(&dw_smem[256 + l * 8 + i], dw_acc2[i]);
+      }
     }
     __syncthreads();
-    if (threadIdx.x < D) atomicAdd(&dw[threadIdx.x], dw_smem[threadIdx.x]);
+    if (threadIdx.x < D) {
+      if (dw) atomicAdd(&dw[threadIdx.x], dw_smem[threadIdx.x]);
+      if (dw2) atomicAdd(&dw2[threadIdx.x], dw_smem[256 + threadIdx.x]);
+    }
   }
 }
 
@@ -654,7 +665,22 @@ extern "C" int b200_qknorm_rope_fwd(const void* in, long long in_stride, void* o
   const int grid = grid_for((tokens * heads + 32 / lph - 1) / (32 / lph), kWarpsPerBlock, 8);
   qknorm_rope_fwd_kernel<<<grid, kWarpsPerBlock * 32, 0, STREAM(stream)>>>(
       (const __nv_bfloat16*)in, in_stride, (__nv_bfloat16*)out, out_stride, (const float*)w, (const int*)positions,
-      (float*)rstd, tokens, heads, D, eps, log2f(theta), rope, lph);
+      (float*)rstd, tokens, heads, D, eps, log2f(theta), rope, lph, nullptr, heads);
+  return LAST_ERR();
+}
+// Query and key heads of a packed projection in one launch: the first heads_q heads use wq, the next heads_k use wk
+// (both or neither given); rstd is [tokens, heads_q + heads_k].
+extern "C" int b200_qknorm_rope_fwd_qk(const void* in, long long in_stride, void* out, long long out_stride,
+                                       const void* wq, const void* wk, const void* positions, void* rstd,
+                                       long long tokens, int heads_q, int heads_k, int D, float eps, float theta,
+                                       int rope, void* stream) {
+  if (D % 8 || D > 256 || (wq == nullptr) != (wk == nullptr)) return -2;
+  const int heads = heads_q + heads_k;
+  const int lph = lanes_per_head(D);
+  const int grid = grid_for((tokens * heads + 32 / lph - 1) / (32 / lph), kWarpsPerBlock, 8);
+  qknorm_rope_fwd_kernel<<<grid, kWarpsPerBlock * 32, 0, STREAM(stream)>>>(
+      (const __nv_bfloat16*)in, in_stride, (__nv_bfloat16*)out, out_stride, (const float*)wq, (const int*)positions,
+      (float*)rstd, tokens, heads, D, eps, log2f(theta), rope, lph, (const float*)wk, heads_q);
   return LAST_ERR();
 }
 extern "C" int b200_qknorm_rope_bwd(const void* in, long long in_stride, const void* dout, long long dout_stride,
@@ -667,7 +693,21 @@ extern "C" int b200_qknorm_rope_bwd(const void* in, long long in_stride, const v
   qknorm_rope_bwd_kernel<<<grid, kWarpsPerBlock * 32, 0, STREAM(stream)>>>(
       (const __nv_bfloat16*)in, in_stride, (const __nv_bfloat16*)dout, dout_stride, (__nv_bfloat16*)din, din_stride,
       (const float*)w, (const int*)positions, (const float*)rstd, (float*)dw, tokens, heads, D, log2f(theta), rope,
-      lph);
+      lph, nullptr, nullptr, heads);
+  return LAST_ERR();
+}
+extern "C" int b200_qknorm_rope_bwd_qk(const void* in, long long in_stride, const void* dout, long long dout_stride,
+                                       void* din, long long din_stride, const void* wq, const void* wk,
+                                       const void* positions, const void* rstd, void* dwq, void* dwk, long long tokens,
+                                       int heads_q, int heads_k, int D, float theta, int rope, void* stream) {
+  if (D % 8 || D > 256 || (wq == nullptr) != (wk == nullptr)) return -2;
+  const int heads = heads_q + heads_k;
+  const int lph = lanes_per_head(D);
+  const int grid = grid_for((tokens * heads + 32 / lph - 1) / (32 / lph), kWarpsPerBlock, 4);
+  qknorm_rope_bwd_kernel<<<grid, kWarpsPerBlock * 32, 0, STREAM(stream)>>>(
+      (const __nv_bfloat16*)in, in_stride, (const __nv_bfloat16*)dout, dout_stride, (__nv_bfloat16*)din, din_stride,
+      (const float*)wq, (const int*)positions, (const float*)rstd, (float*)dwq, tokens, heads, D, log2f(theta), rope,
+      lph, (const float*)wk, (float*)dwk, heads_q);
   return LAST_ERR();
 }
 extern "C" int b200_swiglu_fwd(const void* gu, void* h, long long rows, int I, void* stream) {

@@ -170,8 +170,8 @@ class _QkNormRopeFn(torch.autograd.Function):
     def forward(ctx, qkv, wq, wk, positions, hq, hkv, D, eps, theta, rope):
         T = qkv.shape[0]
         out = torch.empty(T, (hq + hkv) * D, dtype=qkv.dtype, device=qkv.device)
-        rq = native.qknorm_rope_fwd(qkv, out, wq, positions, hq, D, eps, theta, rope)
-        rk = native.qknorm_rope_fwd(qkv[:, hq * D:], out[:, hq * D:], wk, positions, hkv, D, eps, theta, rope)
+        rq = native.qknorm_rope_fwd_qk(qkv, out, wq, wk, positions, hq, hkv, D, eps, theta, rope)
+        rk = None
         ctx.save_for_backward(qkv, positions, rq, rk)
         ctx.params = (wq, wk)
         ctx.cfg = (hq, hkv, D, theta, rope)
@@ -184,10 +184,8 @@ class _QkNormRopeFn(torch.autograd.Function):
         hq, hkv, D, theta, rope = ctx.cfg
         dout = dout.contiguous()
         dqkv = torch.zeros_like(qkv)  # the V columns get no gradient through this op
-        native.qknorm_rope_bwd(qkv, dout, dqkv, wq, positions, rq, None if wq is None else _main_grad(wq), hq, D,
-                               theta, rope)
-        native.qknorm_rope_bwd(qkv[:, hq * D:], dout[:, hq * D:], dqkv[:, hq * D:], wk, positions, rk,
-                               None if wk is None else _main_grad(wk), hkv, D, theta, rope)
+        native.qknorm_rope_bwd_qk(qkv, dout, dqkv, wq, wk, positions, rq, None if wq is None else _main_grad(wq),
+                                  None if wk is None else _main_grad(wk), hq, hkv, D, theta, rope)
         return dqkv, None, None, None, None, None, None, None, None, None
 
 
@@ -280,8 +278,7 @@ class _AttentionBlockFn(torch.autograd.Function):
         qk = torch.empty(T, (hq + hkv) * D, dtype=qkv.dtype, device=qkv.device)
         rq = rk = None
         if wq is not None or rope:
-            rq = native.qknorm_rope_fwd(qkv, qk, wq, positions, hq, D, eps, theta, rope)
-            rk = native.qknorm_rope_fwd(qkv[:, hq * D:], qk[:, hq * D:], wk, positions, hkv, D, eps, theta, rope)
+            rq = native.qknorm_rope_fwd_qk(qkv, qk, wq, wk, positions, hq, hkv, D, eps, theta, rope)
             q4 = qk[:, : hq * D].view(B, S, hq, D)
             k4 = qk[:, hq * D:].view(B, S, hkv, D)
         else:
@@ -316,10 +313,8 @@ class _AttentionBlockFn(torch.autograd.Function):
             d_o4 = d_o4.contiguous()
         native.attn_bwd(q4, k4, v4, o, d_o4, lse, causal=causal, lo=lo, hi=hi, scale=scale, out=outs)
         if transformed:  # in place: every (token, head) vector is read and rewritten by one warp
-            native.qknorm_rope_bwd(qkv, dqkv, dqkv, wq, positions, rq, None if wq is None else _main_grad(wq), hq, D,
-                                   theta, rope)
-            native.qknorm_rope_bwd(qkv[:, hq * D:], dqkv[:, hq * D:], dqkv[:, hq * D:], wk, positions, rk,
-                                   None if wk is None else _main_grad(wk), hkv, D, theta, rope)
+            native.qknorm_rope_bwd_qk(qkv, dqkv, dqkv, wq, wk, positions, rq, None if wq is None else _main_grad(wq),
+                                      None if wk is None else _main_grad(wk), hq, hkv, D, theta, rope)
         return (dqkv,) + (None,) * 15
 
 

@@ -73,6 +73,10 @@ def _declare(lib: ctypes.CDLL) -> None:
         c_float, c_float, c_int, c_void_p)
     sig("b200_qknorm_rope_bwd", c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p,
         c_ll, c_int, c_int, c_float, c_int, c_void_p)
+    sig("b200_qknorm_rope_fwd_qk", c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int,
+        c_int, c_int, c_float, c_float, c_int, c_void_p)
+    sig("b200_qknorm_rope_bwd_qk", c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p,
+        c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_float, c_int, c_void_p)
     sig("b200_swiglu_fwd", c_void_p, c_void_p, c_ll, c_int, c_void_p)
     sig("b200_swiglu_bwd", c_void_p, c_void_p, c_void_p, c_ll, c_int, c_void_p)
     sig("b200_sigmoid_gate_fwd", c_void_p, c_void_p, c_void_p, c_ll, c_void_p)
@@ -327,6 +331,32 @@ def qknorm_rope_bwd(inp: torch.Tensor, dout: torch.Tensor, din: torch.Tensor, w:
                                   din.stride(0), _ptr(w), positions.data_ptr(), _ptr(rstd), _ptr(dw), inp.shape[0],
                                   heads, head_dim, theta, int(rope), _stream())
     _check(rc, "b200_qknorm_rope_bwd")
+
+
+def qknorm_rope_fwd_qk(inp: torch.Tensor, out: torch.Tensor, wq, wk, positions: torch.Tensor, heads_q: int,
+                       heads_k: int, head_dim: int, eps: float, theta: float, rope: bool):
+    """Query and key heads of a packed projection in one launch (``wq`` / ``wk``: both given or both None).
+    Returns ``rstd`` ``[tokens * (heads_q + heads_k)]`` (None without norm weights)."""
+
+    lib = load()
+    tokens = inp.shape[0]
+    rstd = None
+    if wq is not None:
+        rstd = torch.empty(tokens * (heads_q + heads_k), dtype=torch.float32, device=inp.device)
+    rc = lib.b200_qknorm_rope_fwd_qk(inp.data_ptr(), inp.stride(0), out.data_ptr(), out.stride(0), _ptr(wq), _ptr(wk),
+                                     positions.data_ptr(), _ptr(rstd), tokens, heads_q, heads_k, head_dim, eps, theta,
+                                     int(rope), _stream())
+    _check(rc, "b200_qknorm_rope_fwd_qk")
+    return rstd
+
+
+def qknorm_rope_bwd_qk(inp: torch.Tensor, dout: torch.Tensor, din: torch.Tensor, wq, wk, positions: torch.Tensor,
+                       rstd, dwq, dwk, heads_q: int, heads_k: int, head_dim: int, theta: float, rope: bool) -> None:
+    lib = load()
+    rc = lib.b200_qknorm_rope_bwd_qk(inp.data_ptr(), inp.stride(0), dout.data_ptr(), dout.stride(0), din.data_ptr(),
+                                     din.stride(0), _ptr(wq), _ptr(wk), positions.data_ptr(), _ptr(rstd), _ptr(dwq),
+                                     _ptr(dwk), inp.shape[0], heads_q, heads_k, head_dim, theta, int(rope), _stream())
+    _check(rc, "b200_qknorm_rope_bwd_qk")
 
 
 def swiglu_fwd(gu: torch.Tensor) -> torch.Tensor:

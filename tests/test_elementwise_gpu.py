@@ -69,6 +69,44 @@ def test_qknorm_rope(D):
     assert torch.allclose(dw, wr.grad, atol=0.15, rtol=3e-2)
 
 
+@pytest.mark.parametrize("D", [64, 128])
+def test_qknorm_rope_packed_qk_matches_two_single_launches(D):
+    """Query and key heads in one launch (separate norm weights and weight gradients) against one launch each."""
+
+    from research_b200.ops import native
+
+    T, hq, hkv, theta, eps = 70, 4, 2, 10000.0, 1e-6
+    width = (hq + 2 * hkv) * D
+    buf = _bf((T, width), 11)
+    pos = torch.arange(T, device="cuda", dtype=torch.int32) * 5
+    wq, wk = torch.rand(D, device="cuda") + 0.5, torch.rand(D, device="cuda") + 0.5
+    dout = _bf((T, (hq + hkv) * D), 12)
+    out_a = torch.zeros(T, (hq + hkv) * D, dtype=torch.bfloat16, device="cuda")
+    out_b = torch.zeros_like(out_a)
+    r = native.qknorm_rope_fwd_qk(buf, out_a, wq, wk, pos, hq, hkv, D, eps, theta, True)
+    rq = native.qknorm_rope_fwd(buf, out_b, wq, pos, hq, D, eps, theta, True)
+    rk = native.qknorm_rope_fwd(buf[:, hq * D:], out_b[:, hq * D:], wk, pos, hkv, D, eps, theta, True)
+    assert torch.equal(out_a, out_b)
+    assert torch.equal(r.view(T, hq + hkv)[:, :hq].reshape(-1), rq)
+    assert torch.equal(r.view(T, hq + hkv)[:, hq:].reshape(-1), rk)
+    din_a = torch.zeros(T, width, dtype=torch.bfloat16, device="cuda")
+    din_b = torch.zeros_like(din_a)
+    dwq_a, dwk_a = torch.zeros(D, device="cuda"), torch.zeros(D, device="cuda")
+    dwq_b, dwk_b = torch.zeros(D, device="cuda"), torch.zeros(D, device="cuda")
+    native.qknorm_rope_bwd_qk(buf, dout, din_a, wq, wk, pos, r, dwq_a, dwk_a, hq, hkv, D, theta, True)
+    native.qknorm_rope_bwd(buf, dout, din_b, wq, pos, rq, dwq_b, hq, D, theta, True)
+    native.qknorm_rope_bwd(buf[:, hq * D:], dout[:, hq * D:], din_b[:, hq * D:], wk, pos, rk, dwk_b, hkv, D, theta, True)
+    assert torch.equal(din_a, din_b)
+    assert torch.allclose(dwq_a, dwq_b, atol=1e-3, rtol=1e-4) and torch.allclose(dwk_a, dwk_b, atol=1e-3, rtol=1e-4)
+    # without norm weights (RoPE only)
+    out_c = torch.zeros_like(out_a)
+    assert native.qknorm_rope_fwd_qk(buf, out_c, None, None, pos, hq, hkv, D, eps, theta, True) is None
+    out_d = torch.zeros_like(out_a)
+    native.qknorm_rope_fwd(buf, out_d, None, pos, hq + hkv, D, eps, theta, True)
+    assert torch.equal(out_c, out_d)
+    native.check_status()
+
+
 def test_swiglu_and_gate():
     from research_b200.ops import native
 
