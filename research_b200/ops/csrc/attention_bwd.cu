@@ -501,24 +501,30 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
   }
 }
 
-// delta[b,h,s] = sum_d dO[b,s,h,d] * O[b,s,h,d]; one warp per (b,s,h)
+// delta[b,h,s] = sum_d dO[b,s,h,d] * O[b,s,h,d]; D / 8 lanes per (b,s,h), so a warp covers 32 / (D / 8) heads at once
 __global__ void attn_bwd_delta_kernel(const __nv_bfloat16* __restrict__ o, long long o_row, long long o_batch,
                                       const __nv_bfloat16* __restrict__ d_o, long long do_row, long long do_batch,
                                       float* __restrict__ delta, int B, int S, int H, int D) {
   const int lane = threadIdx.x & 31;
+  const int lph = D >> 3;            // 8 or 16 lanes per head (D = 64 or 128)
+  const int hpw = 32 / lph;
+  const int sub = lane / lph, l = lane % lph;
   const long long total = (long long)B * S * H;
-  for (long long idx = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); idx < total;
-       idx += (long long)gridDim.x * (blockDim.x >> 5)) {
-    const int h = (int)(idx % H);
-    const long long bs = idx / H;
-    const int s = (int)(bs % S);
-    const int b = (int)(bs / S);
-    const __nv_bfloat16* po = o + b * o_batch + s * o_row + (long long)h * D;
-    const __nv_bfloat16* pd = d_o + b * do_batch + s * do_row + (long long)h * D;
+  const long long groups = (total + hpw - 1) / hpw;
+  for (long long gidx = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); gidx < groups;
+       gidx += (long long)gridDim.x * (blockDim.x >> 5)) {
+    const long long idx = gidx * hpw + sub;
     float acc = 0.f;
-    for (int d = lane * 8; d < D; d += 256) {
-      const uint4 a = *reinterpret_cast<const uint4*>(po + d);
-      const uint4 c = *reinterpret_cast<const uint4*>(pd + d);
+    int h = 0, s = 0, b = 0;
+    if (idx < total) {
+      h = (int)(idx % H);
+      const long long bs = idx / H;
+      s = (int)(bs % S);
+      b = (int)(bs / S);
+      const __nv_bfloat16* po = o + b * o_batch + s * o_row + (long long)h * D + l * 8;
+      const __nv_bfloat16* pd = d_o + b * do_batch + s * do_row + (long long)h * D + l * 8;
+      const uint4 a = *reinterpret_cast<const uint4*>(po);
+      const uint4 c = *reinterpret_cast<const uint4*>(pd);
       const __nv_bfloat162* ha = reinterpret_cast<const __nv_bfloat162*>(&a);
       const __nv_bfloat162* hc = reinterpret_cast<const __nv_bfloat162*>(&c);
 #pragma unroll
@@ -527,9 +533,8 @@ __global__ void attn_bwd_delta_kernel(const __nv_bfloat16* __restrict__ o, long 
         acc += x.x * y.x + x.y * y.y;
       }
     }
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-    if (lane == 0) delta[((long long)b * H + h) * S + s] = acc;
+    for (int off = lph >> 1; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (l == 0 && idx < total) delta[((long long)b * H + h) * S + s] = acc;
   }
 }
 
@@ -574,7 +579,7 @@ extern "C" int b200_attn_bwd(const void* q, const void* k, const void* v, const 
   if (lo != nullptr && hi == nullptr) return RC_BAD_SHAPE;  // the dKV kernel masks with the kv-side bound
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   {
-    const long long rows = (long long)B * S * Hq;
+    const long long rows = ((long long)B * S * Hq + (256 / D) - 1) / (256 / D);  // warps of work
     long long blocks = (rows + 7) / 8;
     if (blocks > 148 * 16) blocks = 148 * 16;
     attn_bwd_delta_kernel<<<(int)blocks, 256, 0, s>>>((const __nv_bfloat16*)o, o_row, o_batch,
