@@ -193,7 +193,8 @@ struct RowSources {
 // y[t] = sum_j w[t,j] * pad[dest[t,j]]; one warp per token, fp32 accumulation.  H <= 8192.
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(RowSources pad, const float* __restrict__ w, const int* __restrict__ dest,
-                   __nv_bfloat16* __restrict__ y, long long T, int H, int k, long long rows_per_rank) {
+                   __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ rows_out, long long T, int H, int k,
+                   long long rows_per_rank) {
   const int lane = threadIdx.x & 31;
   const long long warp = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const long long nwarps = (long long)gridDim.x * (blockDim.x >> 5);
@@ -204,11 +205,16 @@ moe_combine_kernel(RowSources pad, const float* __restrict__ w, const int* __res
       if (c < H) {
         for (int j = 0; j < k; ++j) {
           const int d = dest[t * k + j];
-          if (d < 0) continue;
+          if (d < 0) {
+            if (rows_out) *reinterpret_cast<uint4*>(rows_out + (t * k + j) * H + c) = make_uint4(0, 0, 0, 0);
+            continue;
+          }
           const float wj = w ? w[t * k + j] : 1.f;
           const int owner = rows_per_rank > 0 ? (int)(d / rows_per_rank) : 0;
           const __nv_bfloat16* row = pad.base[owner] + (d - owner * rows_per_rank) * (long long)H;
           const uint4 v = *reinterpret_cast<const uint4*>(row + c);
+          // optionally keep the unweighted row (the gradient of the routing weights needs it later)
+          if (rows_out) *reinterpret_cast<uint4*>(rows_out + (t * k + j) * H + c) = v;
           const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
@@ -318,13 +324,14 @@ int b200_moe_gather(const void* x, const void* scale, const void* src, const voi
   return static_cast<int>(cudaGetLastError());
 }
 
-int b200_moe_combine(void* const* pad, int n_pad, const void* w, const void* dest, void* y, long long T, int H, int k,
-                     long long rows_per_rank, void* stream) {
+// rows_out (optional): bf16 [T * k, H]; row t*k+j receives the unweighted source row of assignment (t, j).
+int b200_moe_combine(void* const* pad, int n_pad, const void* w, const void* dest, void* y, void* rows_out, long long T,
+                     int H, int k, long long rows_per_rank, void* stream) {
   if (T <= 0 || H % 8 || k < 1 || n_pad < 1 || n_pad > kMaxRanks) return -2;
   RowSources rs = {};
   for (int i = 0; i < n_pad; ++i) rs.base[i] = static_cast<const __nv_bfloat16*>(pad[i]);
   moe_combine_kernel<<<grid_rows(T), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      rs, (const float*)w, (const int*)dest, (__nv_bfloat16*)y, T, H, k, rows_per_rank);
+      rs, (const float*)w, (const int*)dest, (__nv_bfloat16*)y, (__nv_bfloat16*)rows_out, T, H, k, rows_per_rank);
   return static_cast<int>(cudaGetLastError());
 }
 

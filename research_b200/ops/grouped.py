@@ -132,7 +132,7 @@ def _moe_lib():
         lib.b200_moe_layout.argtypes = [vp, ci, ci, ci, ci, vp, vp, vp, vp, vp]
         lib.b200_moe_dest.argtypes = [vp, vp, vp, ci, ci, ci, ci, ll, vp, vp, vp]
         lib.b200_moe_gather.argtypes = [vp, vp, vp, vp, pvp, ci, ll, ci, ci, ll, vp]
-        lib.b200_moe_combine.argtypes = [pvp, ci, vp, vp, vp, ll, ci, ci, ll, vp]
+        lib.b200_moe_combine.argtypes = [pvp, ci, vp, vp, vp, vp, ll, ci, ci, ll, vp]
         lib.b200_moe_combine_dw.argtypes = [pvp, ci, vp, vp, vp, ll, ci, ci, ll, vp]
         for fn in (lib.b200_moe_chunks, lib.b200_moe_rank, lib.b200_moe_layout, lib.b200_moe_dest, lib.b200_moe_gather,
                    lib.b200_moe_combine, lib.b200_moe_combine_dw):
@@ -207,7 +207,7 @@ def _combine_rows(pad, w, plan: RoutingPlan) -> torch.Tensor:
     H = pad.shape[1]
     y = torch.empty(plan.T, H, dtype=torch.bfloat16, device=pad.device)
     rc = lib.b200_moe_combine(_one_ptr(pad), 1, None if w is None else w.data_ptr(), plan.dest.data_ptr(), y.data_ptr(),
-                              plan.T, H, plan.k, 0, native._stream())
+                              None, plan.T, H, plan.k, 0, native._stream())
     native._check(rc, "b200_moe_combine")
     return y
 

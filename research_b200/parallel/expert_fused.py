@@ -145,8 +145,9 @@ def _push_rows(x, scale, plan: ExpertParallelPlan, ws: ExpertParallelWorkspace, 
     return used.clone() if keep else used
 
 
-def _pull_rows(local_rows, w, plan: ExpertParallelPlan, ws: ExpertParallelWorkspace) -> torch.Tensor:
-    """Publish my outbox, barrier, gather-and-sum my tokens' rows from the owners' outboxes, barrier."""
+def _pull_rows(local_rows, w, plan: ExpertParallelPlan, ws: ExpertParallelWorkspace, rows_out=None) -> torch.Tensor:
+    """Publish my outbox, barrier, gather-and-sum my tokens' rows from the owners' outboxes (optionally keeping the
+    unweighted rows in ``rows_out``).  The caller issues the closing barrier."""
 
     lib = _moe_lib()
     mine = ws.outbox[:plan.rows_per_rank]
@@ -156,8 +157,8 @@ def _pull_rows(local_rows, w, plan: ExpertParallelPlan, ws: ExpertParallelWorksp
     H = local_rows.shape[1]
     y = torch.empty(plan.T, H, dtype=torch.bfloat16, device=local_rows.device)
     rc = lib.b200_moe_combine(ws.ptrs(ws.outbox_off), ws.world, None if w is None else w.data_ptr(),
-                              plan.dest.data_ptr(), y.data_ptr(), plan.T, H, plan.k, plan.rows_per_rank,
-                              native._stream())
+                              plan.dest.data_ptr(), y.data_ptr(), None if rows_out is None else rows_out.data_ptr(),
+                              plan.T, H, plan.k, plan.rows_per_rank, native._stream())
     native._check(rc, "b200_moe_combine")
     return y
 
@@ -181,13 +182,9 @@ class _EpCombineFn(torch.autograd.Function):
     def forward(ctx, rows, w, plan, ws):
         lib = _moe_lib()
         w32 = w.reshape(-1).to(torch.float32).contiguous()
-        y = _pull_rows(rows.contiguous(), w32, plan, ws)
-        # keep my unweighted rows for the gradient of the routing weights
+        # keep my unweighted rows for the gradient of the routing weights: the same pass that sums them stores them
         mine = torch.empty(plan.T * plan.k, rows.shape[1], dtype=torch.bfloat16, device=rows.device)
-        # row a of `mine` = outbox row dest[a]: the combine kernel with k = 1 and unit weights over A "tokens"
-        rc = lib.b200_moe_combine(ws.ptrs(ws.outbox_off), ws.world, None, plan.dest.data_ptr(), mine.data_ptr(),
-                                  plan.T * plan.k, rows.shape[1], 1, plan.rows_per_rank, native._stream())
-        native._check(rc, "b200_moe_combine")
+        y = _pull_rows(rows.contiguous(), w32, plan, ws, rows_out=mine)
         ws.barrier()  # everybody has read my outbox
         ctx.save_for_backward(mine, w32)
         ctx.plan, ctx.ws, ctx.w_dtype, ctx.w_shape = plan, ws, w.dtype, w.shape
