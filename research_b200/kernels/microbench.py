@@ -46,7 +46,9 @@ def bf(shape, scale=1.0):
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gemm", "attn_fwd", "attn_bwd", "rmsnorm", "swiglu", "ce", "adamw", "decode"])
+    ap.add_argument("op", choices=["gemm", "attn_fwd", "attn_bwd", "rmsnorm", "swiglu", "ce", "adamw", "decode", "moe"])
+    ap.add_argument("--experts", type=int, default=64)
+    ap.add_argument("--top-k", type=int, default=8)
     ap.add_argument("--m", type=int, default=16384)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -136,6 +138,26 @@ def main() -> int:
                                    "frac_of_peak": 2 * kc.numel() * 2 / ms_paged / 1e6 / pk["hbm_gbs"]}
         gbs = 2 * kc.numel() * 2 / ms / 1e6
         out.update(shape=[B, S, H, Hkv, D], ms=ms, gbs=gbs, frac_of_peak=gbs / pk["hbm_gbs"])
+    elif args.op == "moe":
+        from research_b200.ops.grouped import RoutingPlan, _combine_rows, _gather_rows
+
+        T, k, E, H = args.rows, args.top_k, args.experts, args.hidden
+        ids = torch.topk(torch.randn(T, E, device="cuda"), k, dim=-1).indices.to(torch.int32)
+        x = bf((T, H))
+        w = torch.rand(T * k, device="cuda")
+        capacity = int(1.25 * T * k / E)
+        ms_plan = timed(lambda: RoutingPlan(ids, E, capacity), args.warmup, args.iters)
+        plan = RoutingPlan(ids, E, capacity)
+        ms_gather = timed(lambda: _gather_rows(x, None, plan), args.warmup, args.iters)
+        pad = _gather_rows(x, None, plan)
+        ms_combine = timed(lambda: _combine_rows(pad, w, plan), args.warmup, args.iters)
+        kept = int((plan.dest >= 0).sum())
+        row_bytes = H * 2
+        gather_gbs = (kept * 2 * row_bytes) / ms_gather / 1e6          # read a token row, write a padded row
+        combine_gbs = (kept * row_bytes + T * row_bytes) / ms_combine / 1e6
+        out.update(shape=[T, k, E, H], kept_rows=kept, rows_pad=plan.rows_pad, ms_plan=ms_plan, ms_gather=ms_gather,
+                   ms_combine=ms_combine, gather_gbs=gather_gbs, combine_gbs=combine_gbs,
+                   gather_frac_of_peak=gather_gbs / pk["hbm_gbs"], combine_frac_of_peak=combine_gbs / pk["hbm_gbs"])
     native.check_status()
     print(json.dumps(out))
     return 0
