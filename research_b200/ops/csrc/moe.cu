@@ -191,7 +191,8 @@ struct RowSources {
 };
 
 // y[t] = sum_j w[t,j] * pad[dest[t,j]]; one warp per token, fp32 accumulation.  H <= 8192.
-__global__ void __launch_bounds__(256)
+// full occupancy (64 warps per SM): the kernel waits on scattered 16-byte loads, more warps hide more of them
+__global__ void __launch_bounds__(256, 8)
 moe_combine_kernel(RowSources pad, const float* __restrict__ w, const int* __restrict__ dest,
                    __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ rows_out, long long T, int H, int k,
                    long long rows_per_rank) {
