@@ -46,7 +46,7 @@ def bf(shape, scale=1.0):
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gemm", "attn_fwd", "attn_bwd", "rmsnorm", "swiglu", "ce", "adamw", "decode", "moe"])
+    ap.add_argument("op", choices=["gemm", "attn_fwd", "attn_bwd", "rmsnorm", "swiglu", "ce", "adamw", "decode", "moe", "router"])
     ap.add_argument("--experts", type=int, default=64)
     ap.add_argument("--top-k", type=int, default=8)
     ap.add_argument("--m", type=int, default=16384)
@@ -158,6 +158,32 @@ def main() -> int:
         out.update(shape=[T, k, E, H], kept_rows=kept, rows_pad=plan.rows_pad, ms_plan=ms_plan, ms_gather=ms_gather,
                    ms_combine=ms_combine, gather_gbs=gather_gbs, combine_gbs=combine_gbs,
                    gather_frac_of_peak=gather_gbs / pk["hbm_gbs"], combine_frac_of_peak=combine_gbs / pk["hbm_gbs"])
+    elif args.op == "router":
+        from research_b200.ops.router import load_statistics, load_statistics_reference, route, route_reference
+
+        T, k, E = args.rows, args.top_k, args.experts
+        logits = bf((T, E), 1.5).requires_grad_(True)
+        bias = torch.zeros(E, device="cuda")
+        gw = torch.randn(T, k, device="cuda")
+
+        def fwd_bwd(fn):
+            def run():
+                logits.grad = None
+                _, w, s = fn(logits, bias, k, "sigmoid", 1.0)
+                (w * gw).sum().backward()
+            return run
+
+        ms_native = timed(fwd_bwd(route), args.warmup, args.iters)
+        ms_torch = timed(fwd_bwd(route_reference), args.warmup, args.iters)
+        with torch.no_grad():
+            ids, w, _ = route(logits, bias, k, "sigmoid", 1.0)
+            ms_fwd = timed(lambda: route(logits, bias, k, "sigmoid", 1.0), args.warmup, args.iters)
+            ms_stats = timed(lambda: load_statistics(ids, w, E), args.warmup, args.iters)
+            ms_stats_torch = timed(lambda: load_statistics_reference(ids, w, E), args.warmup, args.iters)
+        out.update(shape=[T, E, k], ms_route_fwd_bwd=ms_native, ms_route_fwd_bwd_torch=ms_torch, ms_route_fwd=ms_fwd,
+                   fwd_gbs=(T * E * 2 + T * E * 4 + T * k * 8) / ms_fwd / 1e6, ms_stats=ms_stats,
+                   ms_stats_torch=ms_stats_torch,
+                   note="fwd_bwd includes the multiply, sum and autograd glue around the kernels in both variants")
     native.check_status()
     print(json.dumps(out))
     return 0

@@ -26,18 +26,10 @@ from research_b200.ops import functional as Fn
 
 def router_stats(name: str, layer_index: int, expert_ids: torch.Tensor, weights: torch.Tensor, num_experts: int,
                  dropped: torch.Tensor | None = None) -> RouterStats:
-    ids = expert_ids.reshape(-1).long()
-    counts = torch.zeros(num_experts, dtype=torch.float32, device=ids.device).index_add_(
-        0, ids, torch.ones_like(ids, dtype=torch.float32))
-    importance = torch.zeros(num_experts, dtype=torch.float32, device=ids.device).index_add_(
-        0, ids, weights.reshape(-1).float())
-    total = counts.sum()
-    mean = total / num_experts
-    load_max, load_min = counts.max(), counts.min()
-    max_vio = (load_max - mean) / mean.clamp_min(1e-6)
-    prob = counts / total.clamp_min(1e-6)
-    entropy = -(torch.where(prob > 0, prob * torch.log(torch.where(prob > 0, prob, torch.ones_like(prob))),
-                            torch.zeros_like(prob))).sum()
+    from research_b200.ops.router import load_statistics
+
+    counts, importance, total, mean, load_min, load_max, max_vio, entropy = load_statistics(
+        expert_ids, weights, num_experts)
     return RouterStats(name=name, layer_index=layer_index, expert_counts=counts, importance=importance,
                        total_assignments=total, load_min=load_min, load_max=load_max, load_mean=mean,
                        max_vio=max_vio, load_entropy=entropy, dropped=dropped)
@@ -55,8 +47,9 @@ def sequence_balance_loss(expert_ids: torch.Tensor, scores: torch.Tensor, top_k:
     if scores.dim() != 3:
         raise ContractError(f"router scores must have shape [batch, seq, experts], got {tuple(scores.shape)}")
     B, S, E = scores.shape
-    selected = F.one_hot(expert_ids.long(), E).float().sum(dim=-2)      # [B,S,E]
-    sel_sum = selected.sum(dim=1)                                        # [B,E]
+    flat_ids = expert_ids.reshape(B, -1).long()                          # [B, S*k]
+    sel_sum = torch.zeros(B, E, dtype=torch.float32, device=scores.device).scatter_add_(
+        1, flat_ids, torch.ones_like(flat_ids, dtype=torch.float32))     # [B,E] picks per sequence and expert
     normalised = scores / scores.sum(dim=-1, keepdim=True).clamp_min(1e-20)
     p_sum = normalised.sum(dim=1)
     total_S = S
@@ -91,19 +84,12 @@ class Router(nn.Module):
     def forward(self, x: torch.Tensor, expert_bias: torch.Tensor):
         """x: [..., H] -> (expert_ids [...,k] int64, weights [...,k] fp32, scores [...,E] fp32)."""
 
+        from research_b200.ops.router import route
+
         # the native GEMM needs 16-byte output rows: eight or more experts
         native_ok = Fn.use_native(x) and self.proj.shape[0] % 8 == 0
-        logits = Fn.linear(x, self.proj).float() if native_ok else F.linear(x.float(), self.proj.float())
-        if self.kind == "softmax":
-            scores = torch.softmax(logits, dim=-1)
-        else:
-            scores = torch.sigmoid(logits)
-        _, expert_ids = torch.topk(scores + expert_bias.detach().float(), self.top_k, dim=-1)
-        top = scores.gather(-1, expert_ids)
-        if self.kind == "softmax":
-            weights = top * self.route_scale
-        else:
-            weights = top / (top.sum(dim=-1, keepdim=True) + 1e-20) * self.route_scale
+        logits = Fn.linear(x, self.proj) if native_ok else F.linear(x.float(), self.proj.float())
+        expert_ids, weights, scores = route(logits, expert_bias, self.top_k, self.kind, self.route_scale)
         return expert_ids, weights, scores
 
 

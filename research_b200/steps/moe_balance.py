@@ -30,6 +30,7 @@ class MoeBalanceState:
     momentum_factor: float
     clamp: float
     layers: list[MoeBalanceLayer]
+    kernel: Any = None        # device pointer table of the native update, built on first use
 
 
 def init_moe_balance(model, balance: MoeBalanceSpec | None) -> MoeBalanceState | None:
@@ -55,6 +56,17 @@ def apply_moe_balance_update(state: MoeBalanceState | None, router_counts: torch
         return {}
     if router_counts.shape[0] != len(state.layers):
         raise ContractError(f"router count shape must match MoE balance state, got {tuple(router_counts.shape)}")
+    from research_b200.ops import router as router_ops
+
+    biases = [layer.bias for layer in state.layers]
+    momenta = [layer.momentum for layer in state.layers]
+    if router_ops.smebu_native_ok(router_counts, biases, momenta):
+        # one launch for all layers (csrc/router.cu); the pointer table is rebuilt if a tensor moved
+        if state.kernel is None or not state.kernel.matches(biases, momenta):
+            state.kernel = router_ops.SmebuKernelState(biases, momenta)
+        bias_sq, mom_sq = router_ops.smebu_update(state.kernel, router_counts, state.load_lr, state.clamp,
+                                                  state.momentum_factor)
+        return {"smebu_bias_norm": bias_sq.sqrt(), "smebu_momentum_norm": mom_sq.sqrt()}
     bias_sq = torch.zeros((), device=router_counts.device)
     mom_sq = torch.zeros((), device=router_counts.device)
     for layer, counts in zip(state.layers, router_counts.float()):
