@@ -9,7 +9,10 @@ train state, step functions.
 
 from __future__ import annotations
 
+import atexit
 import math
+import queue
+import threading
 from dataclasses import replace
 from typing import Any
 
@@ -57,6 +60,56 @@ def compute_dtype_for(spec: RunSpec, device: torch.device) -> torch.dtype:
     return torch.bfloat16
 
 
+class BatchPrefetcher:
+    """One worker thread that assembles the microbatches of the coming optimizer steps while the GPU runs the
+    current one.  Batch assembly is host work (document packing, token-window gathers in the C++ library) that
+    releases the interpreter lock for most of its time; without the thread it sits between two steps.
+
+    Items are ``(microbatches, provenance, pipeline state after them)``; the trainer adopts the state only when
+    it consumes an item, so a checkpoint never records batches that were assembled but not trained on.
+    """
+
+    def __init__(self, pipeline, state: DataPipelineState, accumulation: int, depth: int = 2):
+        self.pipeline, self.accumulation = pipeline, accumulation
+        self.queue: queue.Queue = queue.Queue(maxsize=depth)
+        self.stop = threading.Event()
+        self.thread = threading.Thread(target=self._work, args=(state,), name="batch-prefetch", daemon=True)
+        self.thread.start()
+        atexit.register(self.close)      # never leave the worker inside native code while the interpreter exits
+
+    def _work(self, state: DataPipelineState) -> None:
+        while not self.stop.is_set():
+            try:
+                batches, prov = [], []
+                for _ in range(self.accumulation):
+                    pb: PipelineBatch = self.pipeline.next_batch(state)
+                    state = pb.state
+                    batches.append(pb.batch)
+                    prov.append(pb.provenance)
+                item = (batches, prov, state)
+            except BaseException as exc:  # handed to the consumer, which re-raises it
+                item = exc
+            while not self.stop.is_set():
+                try:
+                    self.queue.put(item, timeout=0.1)
+                    break
+                except queue.Full:
+                    continue
+            if isinstance(item, BaseException):
+                return
+
+    def get(self):
+        item = self.queue.get()
+        if isinstance(item, BaseException):
+            raise item
+        return item
+
+    def close(self) -> None:
+        self.stop.set()
+        self.thread.join(timeout=5.0)
+        atexit.unregister(self.close)
+
+
 class Trainer:
     def __init__(self, spec: RunSpec, *, mesh: MeshContext | None = None, device: torch.device | str | None = None,
                  build_data: bool = True):
@@ -83,13 +136,31 @@ class Trainer:
         self.step = 0
         self.tokens_seen = 0
         self.data = None
-        self.data_state: DataPipelineState | None = None
+        self._data_state: DataPipelineState | None = None
+        self._prefetcher: BatchPrefetcher | None = None
+        self.prefetch = True
         self.last_provenance: list[Any] = []
         if build_data:
             self.data = self.build_pipeline("train")
             self.data_state = self.data.initial_state()
 
     # ---- data --------------------------------------------------------------------------------------
+    @property
+    def data_state(self) -> DataPipelineState | None:
+        """Pipeline state after the last batch handed out (what a checkpoint records)."""
+
+        return self._data_state
+
+    @data_state.setter
+    def data_state(self, state: DataPipelineState | None) -> None:
+        self.close_prefetcher()          # batches assembled ahead belong to the old position
+        self._data_state = state
+
+    def close_prefetcher(self) -> None:
+        if self._prefetcher is not None:
+            self._prefetcher.close()
+            self._prefetcher = None
+
     def build_pipeline(self, split: str):
         d, t = self.spec.data, self.spec.training
         if d.mode != "prepared":
@@ -112,13 +183,28 @@ class Trainer:
 
         if self.data is None or self.data_state is None:
             raise ContractError("this trainer was built without a data pipeline")
+        accumulation = self.spec.training.gradient_accumulation_steps
+        if self.prefetch:
+            if self._prefetcher is None:
+                self._prefetcher = BatchPrefetcher(self.data, self._data_state, accumulation)
+            try:
+                batches, prov, state = self._prefetcher.get()
+            except StopIteration as exc:
+                self.close_prefetcher()
+                raise ContractError(f"training data exhausted before target_tokens was reached: {exc}") from exc
+            except BaseException:
+                self.close_prefetcher()
+                raise
+            self._data_state = state
+            self.last_provenance = prov
+            return batches
         batches, prov = [], []
-        for _ in range(self.spec.training.gradient_accumulation_steps):
+        for _ in range(accumulation):
             try:
                 pb: PipelineBatch = self.data.next_batch(self.data_state)
             except StopIteration as exc:
                 raise ContractError(f"training data exhausted before target_tokens was reached: {exc}") from exc
-            self.data_state = pb.state
+            self._data_state = pb.state
             batches.append(pb.batch)
             prov.append(pb.provenance)
         self.last_provenance = prov

@@ -204,3 +204,38 @@ def test_cli_exit_codes_and_json(tmp_path):
     assert json.loads(ins.stdout)["checkpoints"]["latest_step"] == 2
     kl = subprocess.run(exe + ["kernels", "list", "--json"], capture_output=True, text=True)
     assert kl.returncode == 0 and any(k["op"] == "gemm" for k in json.loads(kl.stdout)["kernels"])
+
+
+def test_batch_prefetcher_hands_out_the_same_batches_and_states(tmp_path):
+    """The worker thread runs ahead, but the trainer's data state moves only with the batches handed out, and
+    assigning a state (resume) drops what was assembled ahead."""
+    import numpy as np
+
+    from research_b200.config.loader import run_spec_from_mapping
+    from research_b200.runtime.trainer import Trainer
+    from tests.helpers import tiny_dataset, tiny_raw_config
+
+    manifest = tiny_dataset(tmp_path)
+    spec = run_spec_from_mapping(tiny_raw_config(manifest, accum=2))
+    ahead, plain = Trainer(spec, device="cpu"), Trainer(spec, device="cpu")
+    plain.prefetch = False
+    for _ in range(3):
+        a, b = ahead.next_accumulated_batch(), plain.next_accumulated_batch()
+        assert len(a) == len(b) == 2
+        for x, y in zip(a, b):
+            assert np.array_equal(np.asarray(x.input_ids), np.asarray(y.input_ids))
+        assert ahead.data.state_to_json(ahead.data_state) == plain.data.state_to_json(plain.data_state)
+        assert ahead.last_provenance == plain.last_provenance
+    # resume from the plain trainer's second position: the batches assembled ahead must not be used
+    rewind = Trainer(spec, device="cpu")
+    first = rewind.next_accumulated_batch()
+    second = rewind.next_accumulated_batch()
+    state_after_first = Trainer(spec, device="cpu")
+    state_after_first.prefetch = False
+    state_after_first.next_accumulated_batch()
+    rewind.data_state = state_after_first.data_state
+    again = rewind.next_accumulated_batch()
+    assert np.array_equal(np.asarray(again[0].input_ids), np.asarray(second[0].input_ids))
+    assert not np.array_equal(np.asarray(again[0].input_ids), np.asarray(first[0].input_ids))
+    for t in (ahead, rewind):
+        t.close_prefetcher()
