@@ -107,6 +107,10 @@ _LAYOUT = {
 }
 
 
+# axis of the logical shape that the ``expert_fsdp`` mesh axis splits (reference: mesh/sharding.py:524-538)
+EXPERT_FSDP_AXIS = {"moe_gate": 2, "moe_up": 2, "moe_down": 1}
+
+
 def layout_policy(tag: str, rank: int):
     if tag in _LAYOUT:
         return _LAYOUT[tag]
@@ -171,15 +175,16 @@ def logical_parameters(model: TransformerLM) -> tuple[ParamMeta, ...]:
             entries.append(_meta(f"{pre}.ffn_pre_norm.scale", "ffn_pre_norm", (H,), f"{pre}.ffn_pre_norm.scale"))
             if layer.is_moe:
                 moe = layer.mlp
-                E, I = moe.num_experts, moe.experts.inter
+                E, I_local = moe.num_experts, moe.experts.inter
+                I = I_local * ex.efsdp_size                        # logical (global) intermediate size
                 entries.append(_meta(f"{pre}.mlp.router.proj.kernel", "moe_router", (H, E), f"{pre}.mlp.router.proj",
                                      None, True))
                 entries.append(_meta(f"{pre}.mlp.expert_bias", "moe_expert_bias", (E,), f"{pre}.mlp.expert_bias",
                                      trainable=False))
                 entries.append(_meta(f"{pre}.mlp.experts.gate", "moe_gate", (E, H, I), f"{pre}.mlp.experts.w_gate_up",
-                                     (0, I), True))
+                                     (0, I_local), True))
                 entries.append(_meta(f"{pre}.mlp.experts.up", "moe_up", (E, H, I), f"{pre}.mlp.experts.w_gate_up",
-                                     (I, 2 * I), True))
+                                     (I_local, 2 * I_local), True))
                 entries.append(_meta(f"{pre}.mlp.experts.down", "moe_down", (E, I, H), f"{pre}.mlp.experts.w_down",
                                      None, True))
                 if moe.shared_experts is not None:
@@ -255,6 +260,7 @@ def initialize_parameters(result: ModelBuildResult, seed: int) -> None:
         local = _shard(full, meta.tp_axis, ex.tp_size, ex.tp_rank)
         if meta.tag in ROUTED_EXPERT_TAGS:
             local = _shard(local, 0, ex.ep_size, ex.ep_rank)
+            local = _shard(local, EXPERT_FSDP_AXIS[meta.tag], ex.efsdp_size, ex.efsdp_rank)
         dest.copy_(local)
 
 

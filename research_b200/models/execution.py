@@ -238,6 +238,16 @@ class ExecutionContext:
         return _rank(self.ep_group)
 
     @property
+    def efsdp_size(self) -> int:
+        """Ranks that split the routed experts' intermediate dimension (the ``expert_fsdp`` axis)."""
+
+        return _world(self.expert_fsdp_group)
+
+    @property
+    def efsdp_rank(self) -> int:
+        return _rank(self.expert_fsdp_group)
+
+    @property
     def sp(self) -> bool:
         return self.tp_size > 1 and self.sequence_parallel and self.cp_size == 1
 

@@ -134,9 +134,13 @@ class SparseMoE(nn.Module):
         if self.num_experts % ep != 0:
             raise ContractError(f"num_experts ({self.num_experts}) must be divisible by the expert axis size ({ep})")
         self.num_local = self.num_experts // ep
+        shards = ex.efsdp_size
+        if moe.expert_intermediate_size % shards != 0:
+            raise ContractError(f"expert_intermediate_size ({moe.expert_intermediate_size}) must be divisible by the "
+                                f"expert_fsdp axis size ({shards})")
         self.router = Router(spec.hidden_size, moe.num_experts, moe.top_k, moe.route_scale, moe.router)
         self.expert_bias = nn.Parameter(torch.zeros(moe.num_experts, dtype=torch.float32), requires_grad=False)
-        self.experts = Experts(spec.hidden_size, moe.expert_intermediate_size, self.num_local)
+        self.experts = Experts(spec.hidden_size, moe.expert_intermediate_size // shards, self.num_local)
         self.shared_experts = None
         if moe.num_shared_experts > 0:
             self.shared_experts = SharedSwiGLU(spec.hidden_size, moe.expert_intermediate_size * moe.num_shared_experts, ex)
@@ -180,9 +184,20 @@ class SparseMoE(nn.Module):
                 dropped = (~keep).sum()
         elif self.moe.capacity_factor is not None:
             weights, dropped = apply_capacity(expert_ids, weights, self.num_experts, self.moe.capacity_factor)
-        y = dispatch_and_combine(self.experts, x.reshape(B * S, H), expert_ids.reshape(B * S, -1),
-                                 weights.reshape(B * S, -1), num_experts=self.num_experts, ex=ex,
-                                 plan=plan).view(B, S, H)
+        x_routed, w_routed = x.reshape(B * S, H), weights.reshape(B * S, -1)
+        if ex.efsdp_size > 1:
+            # expert FSDP: every rank of the axis sees the same tokens and holds a slice of each expert's
+            # intermediate dimension; partial outputs are summed over the axis (reference: moe.py:642-643), and the
+            # gradients of the replicated inputs are summed on the way back
+            from research_b200.models.execution import copy_to_group
+
+            x_routed = copy_to_group(x_routed, ex.expert_fsdp_group)
+            w_routed = copy_to_group(w_routed, ex.expert_fsdp_group)
+        y = dispatch_and_combine(self.experts, x_routed, expert_ids.reshape(B * S, -1), w_routed,
+                                 num_experts=self.num_experts, ex=ex, plan=plan)
+        if ex.efsdp_size > 1:
+            y = all_reduce_sum(y, ex.expert_fsdp_group)
+        y = y.view(B, S, H)
         if self.shared_experts is not None:
             y = y + ex.reduce_scatter_sequence(self.shared_experts(ex.gather_sequence(x), ex))
         stats = router_stats(name, layer_index, expert_ids, weights, self.num_experts, dropped)

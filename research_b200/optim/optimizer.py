@@ -73,6 +73,8 @@ class Optimizer:
         ep_axis = self.store.ep_axis
         if ep_axis and self.mesh.size(ep_axis) > 1 and any(e.is_expert for e in sec.entries) and ep_axis not in axes:
             axes.append(ep_axis)
+        if self.mesh.size("expert_fsdp") > 1 and any(e.is_expert for e in sec.entries):
+            axes.append("expert_fsdp")   # every rank of the axis holds a distinct slice of the intermediate dimension
         return axes
 
     def _global_sumsq(self, arena: torch.Tensor | None, use_master: bool = False) -> torch.Tensor:

@@ -19,7 +19,7 @@ import torch
 import torch.distributed as dist
 
 from research_b200.errors import ContractError
-from research_b200.models.build import ROUTED_EXPERT_TAGS, ParamMeta
+from research_b200.models.build import EXPERT_FSDP_AXIS, ROUTED_EXPERT_TAGS, ParamMeta
 
 
 def _full_arena(trainer, kind: str) -> torch.Tensor:
@@ -58,6 +58,8 @@ def _logical_from_arena(trainer, meta: ParamMeta, arena: torch.Tensor) -> torch.
     t = res.logical_view(meta, storage).contiguous()
     if meta.tp_axis is not None and ex.tp_size > 1:
         t = _gather_axis(t, meta.tp_axis, ex.tp_group)
+    if meta.tag in ROUTED_EXPERT_TAGS and ex.efsdp_size > 1:
+        t = _gather_axis(t, EXPERT_FSDP_AXIS[meta.tag], ex.expert_fsdp_group)
     if meta.tag in ROUTED_EXPERT_TAGS and ex.ep_size > 1:
         t = _gather_axis(t, 0, ex.ep_group)
     return t
@@ -101,6 +103,8 @@ def _local_from_logical(trainer, meta: ParamMeta, full: np.ndarray) -> torch.Ten
         t = t.chunk(ex.tp_size, dim=meta.tp_axis)[ex.tp_rank]
     if meta.tag in ROUTED_EXPERT_TAGS and ex.ep_size > 1:
         t = t.chunk(ex.ep_size, dim=0)[ex.ep_rank]
+    if meta.tag in ROUTED_EXPERT_TAGS and ex.efsdp_size > 1:
+        t = t.chunk(ex.efsdp_size, dim=EXPERT_FSDP_AXIS[meta.tag])[ex.efsdp_rank]
     return t.transpose(-1, -2) if meta.transposed else t
 
 

@@ -36,6 +36,9 @@ CASES = [
     ("cp2", "decoder", "adamw", {"cp": 2}, {"mode": "ddp", "context_parallel": True}),
     ("ep2_moe", "trinity", "adamw", {"ep": 2}, {"mode": "ddp", "expert_parallel": True}),
     ("fsdp2_folded_ep_moe", "trinity", "adamw", {"fsdp": 2}, {"mode": "fsdp", "expert_parallel": True}),
+    # expert FSDP: routed experts split over ep (expert index) and expert_fsdp (intermediate dimension)
+    ("ep2_expert_fsdp2_moe", "trinity", "adamw", {"fsdp": 1, "ep": 2, "expert_fsdp": 2},
+     {"mode": "fsdp", "expert_parallel": True}),
 ]
 
 
@@ -46,7 +49,10 @@ def test_layout_matches_single_process(tmp_path, name, kind, optimizer, mesh, pa
     ref = _single(base)
     raw = tiny_raw_config(manifest, kind=kind, optimizer=optimizer, mesh=mesh, parallelism=parallelism,
                           steps=STEPS + 1)
-    results = run_gloo(2, train_and_collect, raw, STEPS)
+    world = 1
+    for size in mesh.values():
+        world *= size
+    results = run_gloo(world, train_and_collect, raw, STEPS)
     tol = 2e-3 if optimizer == "muon" else 2e-4
     for got in results:
         _compare(ref, got, tol)
