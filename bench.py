@@ -134,7 +134,7 @@ WORKLOADS = {
 
 
 def workload_spec(name: str, n_gpus: int, manifest: Path, steps_total: int, per_gpu_batch: int, seq_len: int | None,
-                  optimizer: str | None):
+                  optimizer: str | None, context_attention: str = "gather"):
     """The other named workloads, from their TOML files, re-meshed for ``n_gpus`` GPUs of one box."""
 
     import tomllib
@@ -157,7 +157,8 @@ def workload_spec(name: str, n_gpus: int, manifest: Path, steps_total: int, per_
         cp = min(4, n_gpus)
         axes, sizes, replicas = ["fsdp", "context"], [n_gpus // cp, cp], n_gpus // cp
         raw["parallelism"]["context_parallel"] = cp > 1
-        parallelism = f"fsdp{n_gpus // cp}xcp{cp}"
+        raw["parallelism"]["context_attention"] = context_attention
+        parallelism = f"fsdp{n_gpus // cp}xcp{cp}" + ("(ulysses)" if context_attention == "ulysses" and cp > 1 else "")
     else:
         axes, sizes, replicas = ["fsdp"], [n_gpus], n_gpus
         raw["parallelism"]["expert_parallel"] = n_gpus > 1
@@ -184,6 +185,8 @@ def main() -> int:
     ap.add_argument("--per-gpu-batch", type=int, default=8)
     ap.add_argument("--seq-len", type=int, default=None)
     ap.add_argument("--optimizer", default=None, choices=["muon", "adamw", "dion"])
+    ap.add_argument("--context-attention", default="gather", choices=["gather", "ulysses"],
+                    help="long_context only: K/V all-gather (default) or head <-> sequence all-to-all")
     args = ap.parse_args()
     headline = args.workload == "dense_1p3b"
     if headline:
@@ -217,7 +220,7 @@ def main() -> int:
         model_desc = "dense-1.3B decoder (24L, d2048, 16q/8kv heads, ffn 5632, vocab 50304)"
     else:
         spec, gb, parallelism = workload_spec(args.workload, world, manifest, steps_total, args.per_gpu_batch,
-                                              args.seq_len, args.optimizer)
+                                              args.seq_len, args.optimizer, args.context_attention)
         model_desc = WORKLOADS[args.workload][1]
     args.seq_len = spec.training.seq_len
     args.optimizer = spec.optimizer.name

@@ -213,6 +213,7 @@ PARALLELISM_FIELDS: tuple[Field, ...] = (
     ("context_parallel", _bool, False),
     ("expert_parallel", _bool, False),
     ("expert_parallel_axis", _str, "auto"),
+    ("context_attention", _str, "gather"),
 )
 ARTIFACT_FIELDS: tuple[Field, ...] = (
     ("wandb_enabled", _bool, False),

@@ -453,9 +453,11 @@ class ParallelismSpec:
     context_parallel: bool = False
     expert_parallel: bool = False
     expert_parallel_axis: str = "auto"
+    context_attention: str = "gather"    # "gather": K/V all-gather; "ulysses": head <-> sequence all-to-all
 
     def __post_init__(self) -> None:
         _one_of("parallelism.mode", self.mode, PARALLELISM_MODES)
+        _one_of("parallelism.context_attention", self.context_attention, ("gather", "ulysses"))
         _bool("parallelism.tensor_parallel", self.tensor_parallel)
         _bool("parallelism.context_parallel", self.context_parallel)
         _bool("parallelism.expert_parallel", self.expert_parallel)

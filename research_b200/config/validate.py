@@ -40,6 +40,14 @@ def validate_run_spec(spec: RunSpec) -> None:
         if "cp" not in sizes:
             raise ConfigError("parallelism.context_parallel=true requires a mesh cp axis")
         _divisible("training.seq_len", training.seq_len, "cp", cp)
+        if par.context_attention == "ulysses":
+            # heads are exchanged for sequence: every cp rank attends with heads / cp heads over the whole sequence
+            shard = tp if par.tensor_parallel else 1
+            for label, value in (("model.num_heads", model.num_heads),
+                                 ("model.n_kv_heads", model.n_kv_heads or model.num_heads)):
+                if value % (shard * cp) != 0:
+                    raise ConfigError(f"{label} ({value}) must be divisible by tp x cp ({shard * cp}) for "
+                                      "parallelism.context_attention='ulysses'")
     if tp != 1 and not par.tensor_parallel:
         raise ConfigError("mesh tp axis size greater than 1 requires parallelism.tensor_parallel=true")
     if par.tensor_parallel:

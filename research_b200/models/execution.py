@@ -209,6 +209,7 @@ class ExecutionContext:
     ep_dispatcher: str = "all_to_all"
     ep_axis_name: str | None = None
     ep_axis_sharing: str | None = None
+    cp_attention: str = "gather"            # context-parallel attention: K/V all-gather or Ulysses all-to-all
     fused: bool = True                      # use fused compute+collective kernels where available
     extras: dict[str, Any] = field(default_factory=dict)
 
@@ -335,7 +336,10 @@ class ExecutionContext:
         if self.cp_size == 1:
             return Fn.attention_block(qkv, wq, wk, positions, B=B, S=S, hq=hq, hkv=hkv, D=D, eps=eps, theta=theta,
                                       rope=rope, causal=True, lo=lo, hi=hi)
-        from research_b200.parallel.context import context_parallel_attention
+        from research_b200.parallel.context import context_parallel_attention, ulysses_attention
 
+        if self.cp_attention == "ulysses":
+            return ulysses_attention(self, qkv, wq, wk, positions, B=B, S=S, hq=hq, hkv=hkv, D=D, eps=eps,
+                                     theta=theta, rope=rope, lo=lo)
         return context_parallel_attention(self, qkv, wq, wk, positions, B=B, S=S, hq=hq, hkv=hkv, D=D, eps=eps,
                                           theta=theta, rope=rope, lo=lo, chunks=chunks)

@@ -9,6 +9,13 @@ form, so logits never materialise and only ``(r + 1) / cp`` of the keys are visi
 
 Transport: ``all_gather`` over the cp group (NCCL on GPUs, gloo on CPU).  Backward sends every rank's
 contribution to dK/dV of the chunks it attended to back to their owners with a reduce-scatter.
+
+``parallelism.context_attention = "ulysses"`` selects the other classic form (:func:`ulysses_attention`): an
+all-to-all turns the sequence split into a head split, every rank runs ordinary causal flash attention over the
+whole sequence for ``heads / cp`` heads, and a second all-to-all turns the result back.  It moves
+``(hq + 2 hkv) / cp`` head-slices per token instead of gathering all K/V, and its attention call is the plain
+single-device kernel.  (The reference ships this only as a vendored transport kernel:
+third_party/ThunderKittens/kernels/parallel/ulysses_attn/ulysses_attn.cu.)
 """
 
 from __future__ import annotations
@@ -106,3 +113,86 @@ def _in_sequence_order(gathered: torch.Tensor, cp: int, s_local: int, zigzag: bo
     g = gathered.reshape(B, cp, 2, c, *gathered.shape[2:])
     first, second = g[:, :, 0], g[:, :, 1].flip(1)
     return torch.cat([first, second], dim=1).reshape(B, 2 * cp * c, *gathered.shape[2:])
+
+
+def _order_index(cp: int, s_local: int, zigzag: bool, device) -> torch.Tensor | None:
+    """Row index that turns rank-major gathered rows into sequence order (None when they already are)."""
+
+    if not zigzag:
+        return None
+    c = s_local // 2
+    idx = torch.arange(cp * s_local, device=device).view(cp, 2, c)
+    return torch.cat([idx[:, 0], idx[:, 1].flip(0)], dim=0).reshape(-1)
+
+
+class _SeqToHeads(torch.autograd.Function):
+    """``[B, S_local, H, D]`` (all heads, my rows) -> ``[B, cp * S_local, H / cp, D]`` (my heads, all rows in
+    sequence order); the backward is the opposite exchange."""
+
+    @staticmethod
+    def forward(ctx, x, group, order):
+        cp = dist.get_world_size(group)
+        B, S, H, D = x.shape
+        ctx.group, ctx.order, ctx.cp = group, order, cp
+        send = x.view(B, S, cp, H // cp, D).permute(2, 0, 1, 3, 4).contiguous()     # [dst, B, S, h, D]
+        recv = torch.empty_like(send)                                                # [src, B, S, h, D]
+        dist.all_to_all_single(recv, send, group=group)
+        out = recv.permute(1, 0, 2, 3, 4).reshape(B, cp * S, H // cp, D)
+        return out if order is None else out.index_select(1, order)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _heads_to_seq(g, ctx.group, ctx.order, ctx.cp), None, None
+
+
+class _HeadsToSeq(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group, order):
+        cp = dist.get_world_size(group)
+        ctx.group, ctx.order, ctx.cp = group, order, cp
+        return _heads_to_seq(x, group, order, cp)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _SeqToHeads.forward(ctx, g.contiguous(), ctx.group, ctx.order), None, None
+
+
+def _heads_to_seq(x: torch.Tensor, group, order, cp: int) -> torch.Tensor:
+    """``[B, cp * S_local, h, D]`` in sequence order -> ``[B, S_local, cp * h, D]`` (my rows, all heads)."""
+
+    B, S_full, h, D = x.shape
+    S = S_full // cp
+    if order is not None:
+        x = torch.empty_like(x).index_copy_(1, order, x)         # back to rank-major rows
+    send = x.reshape(B, cp, S, h, D).permute(1, 0, 2, 3, 4).contiguous()              # [dst, B, S, h, D]
+    recv = torch.empty_like(send)                                                     # [head group, B, S, h, D]
+    dist.all_to_all_single(recv, send, group=group)
+    return recv.permute(1, 2, 0, 3, 4).reshape(B, S, cp * h, D)
+
+
+def ulysses_attention(ex, qkv: torch.Tensor, wq, wk, positions: torch.Tensor, *, B: int, S: int, hq: int, hkv: int,
+                      D: int, eps: float, theta: float, rope: bool, lo: torch.Tensor | None) -> torch.Tensor:
+    """Same contract as :func:`context_parallel_attention`; ``lo`` holds global kv positions for the local rows."""
+
+    cp, group = ex.cp_size, ex.cp_group
+    if hq % cp or hkv % cp:
+        raise ValueError(f"ulysses attention needs heads ({hq}) and kv heads ({hkv}) divisible by cp ({cp})")
+    qk = Fn.qk_norm_rope(qkv, wq, wk, positions.to(torch.int32), hq, hkv, D, eps, theta, rope)
+    q4 = qk[:, : hq * D].reshape(B, S, hq, D)
+    k4 = qk[:, hq * D:].reshape(B, S, hkv, D)
+    v4 = qkv[:, (hq + hkv) * D:].reshape(B, S, hkv, D)
+    zigzag = S % 2 == 0
+    order = _order_index(cp, S, zigzag, qkv.device)
+    q_all = _SeqToHeads.apply(q4.contiguous(), group, order)
+    k_all = _SeqToHeads.apply(k4.contiguous(), group, order)
+    v_all = _SeqToHeads.apply(v4.contiguous(), group, order)
+    lo_all = None
+    if lo is not None:
+        parts = torch.empty(cp * B, S, dtype=lo.dtype, device=lo.device)
+        dist.all_gather_into_tensor(parts, lo.contiguous(), group=group)
+        lo_all = parts.view(cp, B, S).permute(1, 0, 2).reshape(B, cp * S)
+        if order is not None:
+            lo_all = lo_all.index_select(1, order)
+        lo_all = lo_all.contiguous()
+    o = Fn.attention(q_all, k_all, v_all, causal=True, lo=lo_all, scale=D ** -0.5)
+    return _HeadsToSeq.apply(o.contiguous(), group, order).reshape(B, S, hq * D)

@@ -143,5 +143,6 @@ def execution_context_for(mesh: MeshContext, parallelism: ParallelismSpec, *, fu
         ep_dispatcher=dispatcher,
         ep_axis_name=ep.axis,
         ep_axis_sharing=ep.axis_sharing,
+        cp_attention=parallelism.context_attention,
         fused=fused,
     )

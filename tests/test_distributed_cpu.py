@@ -34,6 +34,8 @@ CASES = [
     ("tp2", "decoder", "adamw", {"tp": 2}, {"mode": "ddp", "tensor_parallel": True}),
     ("tp2_muon_duplicated", "decoder", "muon", {"tp": 2}, {"mode": "ddp", "tensor_parallel": True}),
     ("cp2", "decoder", "adamw", {"cp": 2}, {"mode": "ddp", "context_parallel": True}),
+    ("cp2_ulysses", "decoder", "adamw", {"cp": 2},
+     {"mode": "ddp", "context_parallel": True, "context_attention": "ulysses"}),
     ("ep2_moe", "trinity", "adamw", {"ep": 2}, {"mode": "ddp", "expert_parallel": True}),
     ("fsdp2_folded_ep_moe", "trinity", "adamw", {"fsdp": 2}, {"mode": "fsdp", "expert_parallel": True}),
     # expert FSDP: routed experts split over ep (expert index) and expert_fsdp (intermediate dimension)
