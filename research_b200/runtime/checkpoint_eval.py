@@ -25,7 +25,7 @@ def evaluate_checkpoint(run_dir: str | Path, selector: str) -> dict[str, Any]:
     payload = {
         "schema_version": 1, "created_at": utc_now(), "run_id": spec.run_id, "selector": selector,
         "checkpoint_step": ck.record.step, "checkpoint_path": ck.record.checkpoint_path.as_posix(),
-        "tokens_seen": ck.record.tokens_seen, "name": ev.name, "loss": result["loss"], "loss_sum": result["loss_sum"],
+        "tokens_seen": ck.record.tokens_seen, "name": ev.name, "loss": result["loss"], "bpb": result.get("bpb"), "loss_sum": result["loss_sum"],
         "token_count": int(result["token_count"]), "num_batches": result["num_batches"], "eval_sec": sec,
         "eval_tokens_per_sec": None if sec <= 0 else result["token_count"] / sec,
         "train_loss_at_checkpoint": ck.record.train_loss, "eval_loss_at_checkpoint": ck.record.eval_loss,

@@ -223,9 +223,22 @@ class Trainer:
         return self.train_on(self.next_accumulated_batch(), diagnostics=diagnostics)
 
     def evaluate(self, num_batches: int) -> dict[str, float]:
+        """Validation loss over ``num_batches`` batches; with a prepared dataset also bits per byte
+        (``loss_sum / (ln 2 * bytes of the scored target tokens)``, tokenizer-independent; reference:
+        src/research/evals.py)."""
+
+        import numpy as np
+
         pipeline = self.build_pipeline("val")
         state = pipeline.initial_state()
         loss_sum = token_count = 0.0
+        byte_count = 0
+        token_bytes = None
+        manifest = getattr(pipeline, "manifest", None)
+        if manifest is not None and getattr(manifest, "token_bytes_path", None) is not None:
+            path = manifest.manifest_path.parent / manifest.token_bytes_path
+            if path.is_file():
+                token_bytes = np.fromfile(path, dtype="<u2")
         done = 0
         self.result.model.eval()
         try:
@@ -238,14 +251,22 @@ class Trainer:
                 m = self.eval_step_fn.run(pb.batch)
                 loss_sum += m.loss_sum
                 token_count += m.token_count
+                if token_bytes is not None:
+                    targets = np.asarray(pb.batch.target_ids)
+                    mask = np.asarray(pb.batch.loss_mask) > 0
+                    byte_count += int(token_bytes[np.minimum(targets, len(token_bytes) - 1)][mask].sum())
                 done += 1
         finally:
             self.result.model.train()
             pipeline.close()
         if done == 0:
             raise ContractError("validation split has no full batch")
-        return {"loss_sum": loss_sum, "token_count": token_count, "loss": loss_sum / max(token_count, 1.0),
-                "num_batches": done}
+        out = {"loss_sum": loss_sum, "token_count": token_count, "loss": loss_sum / max(token_count, 1.0),
+               "num_batches": done}
+        if byte_count > 0:
+            out["byte_count"] = byte_count
+            out["bpb"] = loss_sum / (math.log(2.0) * byte_count)
+        return out
 
     @property
     def is_writer(self) -> bool:

@@ -195,7 +195,7 @@ def run_validation_eval(trainer: Trainer, spec: RunSpec, writer, step: int, toke
     eval_sec = time.perf_counter() - start
     row = {"schema_version": 1, "name": ev.name, "step": step, "tokens_seen": tokens_seen,
            "loss_sum": result["loss_sum"], "token_count": int(result["token_count"]), "loss": result["loss"],
-           "num_batches": result["num_batches"], "eval_sec": eval_sec,
+           "bpb": result.get("bpb"), "num_batches": result["num_batches"], "eval_sec": eval_sec,
            "eval_tokens_per_sec": None if eval_sec <= 0 else result["token_count"] / eval_sec}
     writer.append_eval_metrics(row)
     writer.append_event({"schema_version": 1, "type": "eval_completed", "run_id": spec.run_id,
@@ -347,8 +347,11 @@ def _run_initialized(spec: RunSpec, config_path: Path, writer, resume: bool, pro
         bad = _nonfinite(row)
         if bad:
             writer.append_train_metrics(row)
+            from research_b200.runtime.train_debug import find_nonfinite_leaves
+
             writer.append_event({"schema_version": 1, "type": "optimizer_nonfinite", "run_id": spec.run_id,
-                                 "created_at": utc_now(), "step": trainer.step, "fields": bad})
+                                 "created_at": utc_now(), "step": trainer.step, "fields": bad,
+                                 "leaves": find_nonfinite_leaves(trainer)})
             raise ContractError(f"non-finite training metrics at step {trainer.step}: {bad}")
         if should_log(trainer.step, trainer.tokens_seen, spec):
             writer.append_train_metrics(row)

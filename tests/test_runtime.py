@@ -48,6 +48,9 @@ def test_training_writes_the_full_artifact_set(tmp_path):
     types = [e["type"] for e in _jsonl(run_dir / "events.jsonl")]
     assert types[0] == "run_initialized" and types[-1] == "training_completed"
     assert types.count("checkpoint_saved") == 2 and "eval_completed" in types
+    eval_rows = _jsonl(run_dir / "metrics" / "eval.jsonl")
+    # bits per byte: the synthetic tokenizer gives 3 bytes per token (0 for the end-of-text id)
+    assert all(r["bpb"] is not None and 0.0 < r["bpb"] < r["loss"] for r in eval_rows)
     index = json.loads((run_dir / "checkpoints" / "index.json").read_text())
     assert index["latest_step"] == 6 and index["best_eval_step"] in (3, 6)
     ck = run_dir / "checkpoints" / "000006"
@@ -110,14 +113,19 @@ def test_data_exhaustion_and_nonfinite_abort_with_events(tmp_path, monkeypatch):
         def run(batches, diagnostics=False):
             metrics = original(batches, diagnostics=diagnostics)
             metrics.grad_norm = float("nan")
+            victim = trainer.store.entries[1]
+            victim.param.main_grad.view(-1)[:3] = float("inf")      # the event must name this leaf
             return metrics
 
         trainer.train_step_fn.run = run
 
     with pytest.raises(ContractError, match="non-finite training metrics"):
         run_training(cfg2, trainer_hook=poison)
-    types = [e["type"] for e in _jsonl(tmp_path / "runs" / "nan" / "events.jsonl")]
+    events = _jsonl(tmp_path / "runs" / "nan" / "events.jsonl")
+    types = [e["type"] for e in events]
     assert "optimizer_nonfinite" in types and types[-1] == "training_failed"
+    leaves = next(e for e in events if e["type"] == "optimizer_nonfinite")["leaves"]
+    assert [(leaf["kind"], leaf["inf"], leaf["nan"]) for leaf in leaves] == [("grad", 3, 0)]
     assert not (tmp_path / "runs" / "nan" / "checkpoints" / "000001").exists()
 
 
