@@ -145,6 +145,36 @@ class SparseMoE(nn.Module):
         if moe.num_shared_experts > 0:
             self.shared_experts = SharedSwiGLU(spec.hidden_size, moe.expert_intermediate_size * moe.num_shared_experts, ex)
 
+    def _dedicated_axis_fused(self, x: torch.Tensor, expert_ids: torch.Tensor, weights: torch.Tensor, ex):
+        """Dedicated ``ep`` axis on CUDA: tokens are replicated over the axis, so every rank routes its slice of
+        them through the peer-memory dispatch / combine kernels and the results are gathered back (the reference
+        slices the sequence inside its shard_map, components/moe.py:538-696).  The capacity applies per sender
+        slice.  Returns (y ``[T, H]``, masked weights ``[B, S, k]``, dropped count) or None when peer memory is
+        not available."""
+
+        from research_b200.models.execution import all_gather_replicated, slice_dim
+        from research_b200.parallel import expert_fused
+
+        B, S, H = x.shape
+        k = expert_ids.shape[-1]
+        ep, rank, group = ex.ep_size, ex.ep_rank, ex.ep_group
+        T = B * S
+        t_local = T // ep
+        capacity = capacity_rows(self.moe.capacity_factor, t_local, k, self.num_experts)
+        ids_local = expert_ids.reshape(T, k)[rank * t_local:(rank + 1) * t_local].contiguous()
+        plan = expert_fused.ExpertParallelPlan(ids_local, self.num_experts, capacity, ex, H)
+        if plan.ws is None:
+            return None
+        keep = plan.kept_mask
+        w_local = slice_dim(weights.reshape(T, k), group, 0) * keep.to(weights.dtype)
+        x_local = slice_dim(x.reshape(T, H), group, 0)
+        y_local = expert_fused.dispatch_and_combine_fused(self.experts, x_local, w_local, plan)
+        y = all_gather_replicated(y_local, group, 0)
+        w_all = all_gather_replicated(w_local.detach(), group, 0).view(B, S, k)      # for the load statistics
+        dropped = (~keep).sum()
+        torch.distributed.all_reduce(dropped, group=group)
+        return y, w_all, dropped
+
     def forward(self, x: torch.Tensor, ex, *, name: str, layer_index: int):
         """x: this rank's ``[B, S_local, H]`` shard of the residual stream -> (y, aux_losses, router_stats).
 
@@ -159,6 +189,7 @@ class SparseMoE(nn.Module):
         expert_ids, weights, scores = self.router(x, self.expert_bias)
         dropped = None
         plan = None
+        y_routed = None          # set when a path below has already run dispatch, experts and combine
         if Fn.use_native(x) and x.dtype == torch.bfloat16 and H % 8 == 0:
             # device-side routing plan: ranks in token order, capacity, padded expert-major layout (no sort)
             from research_b200.ops.grouped import RoutingPlan
@@ -171,12 +202,20 @@ class SparseMoE(nn.Module):
             else:
                 from research_b200.parallel import expert_fused
 
-                if ex.ep_axis_sharing != "dedicated_ep" and expert_fused.fused_available(ex, x, capacity):
+                if ex.ep_axis_sharing == "dedicated_ep":
+                    if expert_fused.fused_available(ex, x, capacity) and (B * S) % ex.ep_size == 0 \
+                            and ex.efsdp_size == 1:
+                        done = self._dedicated_axis_fused(x, expert_ids, weights, ex)
+                        if done is not None:
+                            y_routed, weights, dropped = done
+                elif expert_fused.fused_available(ex, x, capacity):
                     plan = expert_fused.ExpertParallelPlan(expert_ids.reshape(B * S, -1), self.num_experts, capacity, ex,
                                                            H)
                     if plan.ws is None:
                         plan = None
-            if plan is None and capacity is not None:
+            if y_routed is not None:
+                pass
+            elif plan is None and capacity is not None:
                 weights, dropped = apply_capacity(expert_ids, weights, self.num_experts, self.moe.capacity_factor)
             elif capacity is not None:
                 keep = plan.kept_mask.view(expert_ids.shape)
@@ -184,19 +223,22 @@ class SparseMoE(nn.Module):
                 dropped = (~keep).sum()
         elif self.moe.capacity_factor is not None:
             weights, dropped = apply_capacity(expert_ids, weights, self.num_experts, self.moe.capacity_factor)
-        x_routed, w_routed = x.reshape(B * S, H), weights.reshape(B * S, -1)
-        if ex.efsdp_size > 1:
-            # expert FSDP: every rank of the axis sees the same tokens and holds a slice of each expert's
-            # intermediate dimension; partial outputs are summed over the axis (reference: moe.py:642-643), and the
-            # gradients of the replicated inputs are summed on the way back
-            from research_b200.models.execution import copy_to_group
+        if y_routed is not None:
+            y = y_routed
+        else:
+            x_routed, w_routed = x.reshape(B * S, H), weights.reshape(B * S, -1)
+            if ex.efsdp_size > 1:
+                # expert FSDP: every rank of the axis sees the same tokens and holds a slice of each expert's
+                # intermediate dimension; partial outputs are summed over the axis (reference: moe.py:642-643), and
+                # the gradients of the replicated inputs are summed on the way back
+                from research_b200.models.execution import copy_to_group
 
-            x_routed = copy_to_group(x_routed, ex.expert_fsdp_group)
-            w_routed = copy_to_group(w_routed, ex.expert_fsdp_group)
-        y = dispatch_and_combine(self.experts, x_routed, expert_ids.reshape(B * S, -1), w_routed,
-                                 num_experts=self.num_experts, ex=ex, plan=plan)
-        if ex.efsdp_size > 1:
-            y = all_reduce_sum(y, ex.expert_fsdp_group)
+                x_routed = copy_to_group(x_routed, ex.expert_fsdp_group)
+                w_routed = copy_to_group(w_routed, ex.expert_fsdp_group)
+            y = dispatch_and_combine(self.experts, x_routed, expert_ids.reshape(B * S, -1), w_routed,
+                                     num_experts=self.num_experts, ex=ex, plan=plan)
+            if ex.efsdp_size > 1:
+                y = all_reduce_sum(y, ex.expert_fsdp_group)
         y = y.view(B, S, H)
         if self.shared_experts is not None:
             y = y + ex.reduce_scatter_sequence(self.shared_experts(ex.gather_sequence(x), ex))

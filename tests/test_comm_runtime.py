@@ -251,6 +251,13 @@ def _run_training(tmp_path, world, axes, sizes, flags, peer, port):
             "initial_dense_layers": 0, "local_window": 512, "local_layers_per_global": 1, "norm_policy": "afmoe_dual",
             "moe": {"num_experts": 8, "top_k": 2, "expert_intermediate_size": 256, "num_shared_experts": 1,
                     "capacity_factor": 1.5}}}}),
+    # a dedicated ep axis: tokens are replicated over it, every rank dispatches its slice of them
+    ("moe_ep2_dedicated", ["ep"], [2], {
+        "parallelism": {"mode": "ddp", "expert_parallel": True},
+        "model": {"name": "trinity", "num_layers": 2, "trinity": {
+            "initial_dense_layers": 0, "local_window": 512, "local_layers_per_global": 1, "norm_policy": "afmoe_dual",
+            "moe": {"num_experts": 8, "top_k": 2, "expert_intermediate_size": 256, "num_shared_experts": 1,
+                    "capacity_factor": 2.0}}}}),
 ])
 def test_training_with_peer_memory_kernels_matches_nccl_path(tmp_path, name, axes, sizes, flags):
     if torch.cuda.device_count() < 2:
