@@ -16,6 +16,7 @@ import ctypes
 import os
 import tempfile
 import uuid
+import weakref
 
 import torch
 import torch.distributed as dist
@@ -90,6 +91,20 @@ def exchange_descriptors(group, fd: int, *, tag: str, timeout_ms: int = _EXCHANG
     return out
 
 
+_GUARD_BYTES = 256
+_MAX_GUARDS = 32
+_CANARY = 0x5AFEB200
+_ARENAS: "weakref.WeakSet[SymmetricArena]" = weakref.WeakSet()
+
+
+def check_all_canaries() -> None:
+    """Check the guard words of every live arena of this process (tests, and every step when
+    ``RESEARCH_B200_DEBUG=1``)."""
+
+    for arena in list(_ARENAS):
+        arena.check_canaries()
+
+
 class SymmetricArena:
     """``nbytes`` of payload per rank plus flag blocks, mapped on every rank of ``group``."""
 
@@ -105,7 +120,7 @@ class SymmetricArena:
         lib = _comm_lib()
         self._lib = lib
         self.flag_bytes = lib.b200c_flag_block_bytes()
-        self.payload = (int(nbytes) + _ALIGN - 1) // _ALIGN * _ALIGN
+        self.payload = (int(nbytes) + _GUARD_BYTES * _MAX_GUARDS + _ALIGN - 1) // _ALIGN * _ALIGN
         want = self.payload + CHANNELS * self.flag_bytes
         ptr, fd, padded = ctypes.c_void_p(), ctypes.c_int(-1), ctypes.c_ulonglong(0)
         with torch.cuda.device(self.device):
@@ -136,6 +151,8 @@ class SymmetricArena:
         self.bytes.zero_()
         self._epochs = [0] * CHANNELS
         self._cursor = 0
+        self._guards: list[tuple[int, int]] = []      # (byte offset of the guard, offset of the buffer before it)
+        _ARENAS.add(self)
         self.scratch = torch.zeros(1024, dtype=torch.float32, device=self.device)
         torch.cuda.synchronize(self.device)
         dist.barrier(group=group)  # nobody signals into an arena that is still being zeroed
@@ -146,10 +163,27 @@ class SymmetricArena:
 
         size = numel * torch.empty((), dtype=dtype).element_size()
         off = self._cursor
-        if off + size > self.payload:
+        guard = (off + size + 255) // 256 * 256
+        if guard + _GUARD_BYTES > self.payload:
             raise ContractError(f"symmetric arena exhausted: {off} + {size} > {self.payload}")
-        self._cursor = (off + size + 255) // 256 * 256
+        # a guard block of canary words follows every buffer: a kernel (local or on a peer) that writes past the end
+        # of a buffer changes it, and check_canaries() names the buffer
+        self.bytes[guard:guard + _GUARD_BYTES].view(torch.int32).fill_(_CANARY)
+        self._guards.append((guard, off))
+        self._cursor = guard + _GUARD_BYTES
         return self.bytes[off:off + size].view(dtype), off
+
+    def check_canaries(self) -> None:
+        """Raise when a guard block behind one of the carved buffers no longer holds its canary words."""
+
+        if not self._guards:
+            return
+        words = torch.stack([self.bytes[g:g + _GUARD_BYTES].view(torch.int32) for g, _ in self._guards])
+        bad = (words != _CANARY).any(dim=1).cpu().tolist()                      # one device-to-host read
+        broken = [off for (_, off), hit in zip(self._guards, bad) if hit]
+        if broken:
+            raise KernelError(f"symmetric arena of rank {self.rank}: the guard words behind the buffers at byte "
+                              f"offsets {broken} were overwritten (a write ran past the end of a buffer)")
 
     def peer_ptr(self, rank: int, offset: int) -> int:
         return self.ptrs[rank] + offset
@@ -211,6 +245,8 @@ class SymmetricArena:
             for p in self.ptrs:
                 self._lib.b200c_vmm_free(p, self.padded)
             self.ptrs = []
+            self._guards = []          # the memory is gone: nothing left to check
+            _ARENAS.discard(self)
 
 
 def build_collectively(group, factory, what: str):

@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import atexit
 import math
+import os
 import queue
 import threading
 from dataclasses import replace
@@ -139,6 +140,7 @@ class Trainer:
         self._data_state: DataPipelineState | None = None
         self._prefetcher: BatchPrefetcher | None = None
         self.prefetch = True
+        self.debug_checks = self.device.type == "cuda" and os.environ.get("RESEARCH_B200_DEBUG", "0") == "1"
         self.last_provenance: list[Any] = []
         if build_data:
             self.data = self.build_pipeline("train")
@@ -213,6 +215,13 @@ class Trainer:
     # ---- steps -------------------------------------------------------------------------------------
     def train_on(self, batches: list[Batch], *, diagnostics: bool = False) -> StepMetrics:
         metrics = self.train_step_fn.run(batches, diagnostics=diagnostics)
+        if self.debug_checks:
+            # guard words behind every peer-memory buffer, and the kernels' status word (bounded waits that gave up)
+            from research_b200.ops import native
+            from research_b200.parallel.symmetric import check_all_canaries
+
+            check_all_canaries()
+            native.check_status()
         self.step += 1
         self.tokens_seen += sum(int(b.input_ids.shape[0] * b.input_ids.shape[1]) for b in batches)
         return metrics

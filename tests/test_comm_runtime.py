@@ -76,6 +76,7 @@ for it in range(3):
     native.check_status()
     want = torch.arange(1, world + 1, device="cuda").repeat_interleave(n).to(torch.bfloat16) + it
     assert torch.equal(weights, want)
+arena.check_canaries()                      # nothing wrote past the end of a buffer, here or from a peer
 torch.cuda.synchronize()
 dist.barrier()
 arena.close()
@@ -166,6 +167,7 @@ for it in range(3):
     assert torch.allclose(xr.grad.float(), xf.grad, atol=3e-2, rtol=5e-2), (xr.grad.float() - xf.grad).abs().max().item()
     for mg, rg in ((p1.main_grad, w1f.grad), (p2.main_grad, w2f.grad)):
         assert (mg - rg).abs().max().item() <= 0.03 * rg.abs().max().item() + 1e-3
+fusion.arena.check_canaries()               # the TMA reduce-adds of the peers stayed inside the output buffer
 torch.cuda.synchronize()
 dist.barrier()
 dist.destroy_process_group()
@@ -229,7 +231,9 @@ dist.destroy_process_group()
 def _run_training(tmp_path, world, axes, sizes, flags, peer, port):
     script = tmp_path / "train_ranks.py"
     script.write_text(_TRAIN_SCRIPT)
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", RESEARCH_B200_PEER_COLLECTIVES="1" if peer else "0")
+    # RESEARCH_B200_DEBUG=1: after every step the trainer checks the guard words behind all peer-memory buffers
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", RESEARCH_B200_PEER_COLLECTIVES="1" if peer else "0",
+               RESEARCH_B200_DEBUG="1")
     import json
 
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
