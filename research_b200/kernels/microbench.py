@@ -133,9 +133,12 @@ def main() -> int:
 
         kp = kc.view(B, S // 128, 128, Hkv, D).permute(0, 1, 3, 2, 4).contiguous()
         vp = vc.view(B, S // 128, 128, Hkv, D).permute(0, 1, 3, 2, 4).contiguous()
-        ms_paged = timed(lambda: decode_attention_paged(q, kp, vp, lens, None), args.warmup, args.iters)
-        out["paged_head_major"] = {"ms": ms_paged, "gbs": 2 * kc.numel() * 2 / ms_paged / 1e6,
-                                   "frac_of_peak": 2 * kc.numel() * 2 / ms_paged / 1e6 / pk["hbm_gbs"]}
+        nbytes = 2 * kc.numel() * 2
+        for name in ("stream", "registers"):
+            ms_paged = timed(lambda: decode_attention_paged(q, kp, vp, lens, None, kernel=name), args.warmup,
+                             args.iters)
+            out[f"paged_head_major_{name}"] = {"ms": ms_paged, "gbs": nbytes / ms_paged / 1e6,
+                                               "frac_of_peak": nbytes / ms_paged / 1e6 / pk["hbm_gbs"]}
         gbs = 2 * kc.numel() * 2 / ms / 1e6
         out.update(shape=[B, S, H, Hkv, D], ms=ms, gbs=gbs, frac_of_peak=gbs / pk["hbm_gbs"])
     elif args.op == "moe":

@@ -15,6 +15,8 @@
 #include <math_constants.h>
 #include <stdint.h>
 
+#include "b200.cuh"
+
 namespace {
 
 constexpr int kWarps = 4;
@@ -225,6 +227,220 @@ int launch_partial(const DecodeParams& p, int G, cudaStream_t s) {
   return static_cast<int>(cudaGetLastError());
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Head-major pages: the rows of one (page, kv head) are contiguous, so a tile of kTile rows of K (or V) is one
+// contiguous block.  This variant streams such tiles into shared memory with bulk asynchronous copies
+// (cp.async.bulk, completion on an mbarrier) through a ring of kStages slots, so that kStages tiles per CTA are in
+// flight while the warps reduce the tile that has landed: the loads no longer wait for the arithmetic of the
+// same thread, which is what held the register-resident kernel above at about half of the copy bandwidth.
+// The arithmetic, the split-KV scheme and the merge are the same.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kTile = 32;     // cache rows per tile
+constexpr int kStages = 4;
+constexpr int ERR_DECODE_TILE = 31;  // status code: a tile never landed
+
+struct PagedParams {
+  const __nv_bfloat16* q;
+  const __nv_bfloat16* k;
+  const __nv_bfloat16* v;
+  const int* lengths;
+  const int* lo;
+  float* part_o;
+  float* part_ml;
+  long long batch, head, page;  // element strides of the caches (K and V share them)
+  int page_rows;
+  int B, Hq, Hkv, splits;
+  float scale_log2;
+  int* status;
+};
+
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(b200::smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(b200::smem_u32(bar))
+               : "memory");
+}
+
+template <int D, int G>
+__global__ void __launch_bounds__(kWarps * 32) decode_attn_paged_kernel(const PagedParams p) {
+  constexpr int LPR = D / 8;
+  constexpr int RPW = 32 / LPR;
+  constexpr int GROUPS = kWarps * RPW;
+  constexpr int ROWS_PER_GROUP = kTile / GROUPS;
+  constexpr uint32_t TILE_BYTES = kTile * D * 2;
+  static_assert(kTile % GROUPS == 0, "a tile is a whole number of rows per lane group");
+  extern __shared__ __align__(128) unsigned char smem[];
+  __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(smem);                           // [kStages][kTile * D]
+  __nv_bfloat16* vs = reinterpret_cast<__nv_bfloat16*>(smem + kStages * TILE_BYTES);
+  float* s_acc = reinterpret_cast<float*>(smem + 2 * kStages * TILE_BYTES);             // [GROUPS][G][D]
+  float* s_ml = s_acc + GROUPS * G * D;                                                 // [GROUPS][G][2]
+  __shared__ uint64_t full[kStages];
+  __shared__ int abort_flag;
+
+  const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane / LPR, l = lane % LPR;
+  const int grp = warp * RPW + sub;
+  const uint32_t gmask = LPR == 32 ? 0xffffffffu : (((1u << LPR) - 1u) << (sub * LPR));
+
+  const int len = p.lengths[b];
+  const int first = p.lo ? max(p.lo[b], 0) : 0;
+  const int tile_lo = first / kTile;
+  const int tile_hi = len > first ? (len + kTile - 1) / kTile : tile_lo;
+  const int per = (tile_hi - tile_lo + p.splits - 1) / p.splits;
+  const int t_begin = tile_lo + split * per;
+  const int n_tiles = max(min(t_begin + per, tile_hi) - t_begin, 0);
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) b200::mbar_init(&full[s], 1);
+    b200::mbar_fence_init();
+  }
+  __syncthreads();
+  const b200::AbortCtx ab{&abort_flag, p.status};
+  const __nv_bfloat16* kb = p.k + b * p.batch + hkv * p.head;
+  const __nv_bfloat16* vb = p.v + b * p.batch + hkv * p.head;
+  auto issue = [&](int i) {  // thread 0 only
+    const int s = i % kStages;
+    const int r0 = (t_begin + i) * kTile;
+    const int pg = r0 / p.page_rows, in = r0 - pg * p.page_rows;
+    const long long off = pg * p.page + (long long)in * D;
+    b200::mbar_expect_tx(&full[s], 2 * TILE_BYTES);
+    bulk_load(ks + s * (kTile * D), kb + off, TILE_BYTES, &full[s]);
+    bulk_load(vs + s * (kTile * D), vb + off, TILE_BYTES, &full[s]);
+  };
+  int issued = 0;
+  if (threadIdx.x == 0)
+    for (; issued < min(kStages, n_tiles); ++issued) issue(issued);
+
+  float q[G][8], acc[G][8], m[G], lsum[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const __nv_bfloat16* qp = p.q + ((long long)b * p.Hq + hkv * G + g) * D + l * 8;
+    unpack8(*reinterpret_cast<const uint4*>(qp), q[g]);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      q[g][i] *= p.scale_log2;
+      acc[g][i] = 0.f;
+    }
+    m[g] = -CUDART_INF_F;
+    lsum[g] = 0.f;
+  }
+
+  int done = 0;
+  for (; done < n_tiles; ++done) {
+    const int s = done % kStages;
+    // the verdict is made uniform over the CTA, so that either everybody reduces this tile or everybody leaves
+    const bool landed = b200::mbar_wait(&full[s], (done / kStages) & 1, ab, ERR_DECODE_TILE);
+    if (!__syncthreads_and(landed)) break;
+    const int r0 = (t_begin + done) * kTile;
+    const __nv_bfloat16* kt = ks + s * (kTile * D) + l * 8;
+    const __nv_bfloat16* vt = vs + s * (kTile * D) + l * 8;
+#pragma unroll
+    for (int u = 0; u < ROWS_PER_GROUP; ++u) {
+      const int j = grp + u * GROUPS;
+      const int r = r0 + j;
+      if (r >= first && r < len) {  // uniform inside a lane group
+        float kf[8], vf[8];
+        unpack8(*reinterpret_cast<const uint4*>(kt + j * D), kf);
+        unpack8(*reinterpret_cast<const uint4*>(vt + j * D), vf);
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          float sc = 0.f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) sc = fmaf(q[g][i], kf[i], sc);
+#pragma unroll
+          for (int off = LPR >> 1; off > 0; off >>= 1) sc += __shfl_xor_sync(gmask, sc, off, LPR);
+          const float m_new = fmaxf(m[g], sc);
+          const float alpha = ex2f(m[g] - m_new);
+          const float pr = ex2f(sc - m_new);
+          m[g] = m_new;
+          lsum[g] = lsum[g] * alpha + pr;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(acc[g][i], alpha, pr * vf[i]);
+        }
+      }
+    }
+    __syncthreads();  // every warp is done with slot s
+    if (threadIdx.x == 0 && issued < n_tiles && !abort_flag) issue(issued++);
+  }
+  if (done < n_tiles) {
+    // a wait gave up: the copies already issued still target this CTA's shared memory, so thread 0 waits for them
+    // (bounded again) before anybody leaves
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      for (int i = done; i < issued; ++i) {
+        const uint64_t t0 = b200::globaltimer_ns();
+        while (!b200::mbar_try_wait(&full[i % kStages], (i / kStages) & 1) &&
+               b200::globaltimer_ns() - t0 < b200::kWaitLimitNs) {
+        }
+      }
+    }
+    __syncthreads();
+    return;
+  }
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s_acc[(grp * G + g) * D + l * 8 + i] = acc[g][i];
+    if (l == 0) {
+      s_ml[(grp * G + g) * 2] = m[g];
+      s_ml[(grp * G + g) * 2 + 1] = lsum[g];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += kWarps * 32) {
+    const int g = idx / D, d = idx % D;
+    float mm = -CUDART_INF_F;
+#pragma unroll
+    for (int j = 0; j < GROUPS; ++j) mm = fmaxf(mm, s_ml[(j * G + g) * 2]);
+    float o = 0.f, ls = 0.f;
+    if (mm > -CUDART_INF_F) {
+#pragma unroll
+      for (int j = 0; j < GROUPS; ++j) {
+        const float w = ex2f(s_ml[(j * G + g) * 2] - mm);
+        o = fmaf(s_acc[(j * G + g) * D + d], w, o);
+        ls = fmaf(s_ml[(j * G + g) * 2 + 1], w, ls);
+      }
+    }
+    const long long slot = ((long long)b * p.Hq + hkv * G + g) * p.splits + split;
+    p.part_o[slot * D + d] = o;
+    if (d == 0) {
+      p.part_ml[slot * 2] = mm;
+      p.part_ml[slot * 2 + 1] = ls;
+    }
+  }
+}
+
+template <int D, int G>
+constexpr int paged_smem_bytes() {
+  return 2 * kStages * kTile * D * 2 + (kWarps * (32 / (D / 8))) * G * (D + 2) * 4;
+}
+
+template <int D, int G>
+int launch_paged_one(const PagedParams& p, cudaStream_t s) {
+  constexpr int bytes = paged_smem_bytes<D, G>();
+  static bool configured = false;  // per instantiation; the attribute is per function and sticky
+  if (!configured) {
+    if (cudaFuncSetAttribute(decode_attn_paged_kernel<D, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) !=
+        cudaSuccess)
+      return -3;
+    configured = true;
+  }
+  decode_attn_paged_kernel<D, G><<<dim3(p.splits, p.Hkv, p.B), kWarps * 32, bytes, s>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
+template <int D>
+int launch_paged(const PagedParams& p, int G, cudaStream_t s) {
+  switch (G) {
+    case 1: return launch_paged_one<D, 1>(p, s);
+    case 2: return launch_paged_one<D, 2>(p, s);
+    case 4: return launch_paged_one<D, 4>(p, s);
+    case 8: return launch_paged_one<D, 8>(p, s);
+    default: return -2;
+  }
+}
+
 }  // namespace
 
 // Number of kv splits: as many as fit in ONE wave of resident CTAs (a second, partly filled wave would leave most
@@ -280,5 +496,46 @@ extern "C" int b200_kv_append(const void* k_new, const void* v_new, long long kn
   kv_append_kernel<<<(total + 255) / 256, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       (const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, kn_batch, vn_batch, (__nv_bfloat16*)k_cache,
       (__nv_bfloat16*)v_cache, (const int*)positions, c_batch, c_head, c_page, c_row, page_rows, B, Hkv, D);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// Splits for the tile-streaming kernel: one wave of resident CTAs (shared memory allows three per SM for GQA groups
+// up to two, two otherwise), at least 256 rows each.
+extern "C" int b200_decode_attn_paged_splits(int B, int Hq, int Hkv, int max_rows) {
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int G = Hkv > 0 ? Hq / Hkv : 1;
+  const int per_sm = G <= 2 ? 3 : 2;
+  const int base = B * Hkv > 0 ? B * Hkv : 1;
+  int splits = sms * per_sm / base;
+  const int by_rows = (max_rows + 255) / 256;
+  if (splits > by_rows) splits = by_rows;
+  if (splits > 64) splits = 64;
+  return splits < 1 ? 1 : splits;
+}
+
+// Decode attention over head-major pages [.., pages, Hkv, page_rows, D] whose rows are contiguous inside a
+// (page, head) block: element strides `batch`, `head`, `page` (shared by K and V), page_rows a multiple of 32.
+// Every page that holds a row below lengths[b] must be allocated in full (tiles of 32 rows are copied whole).
+// Scratch and result as for b200_decode_attn; `status` is the device status word that bounded waits report to.
+extern "C" int b200_decode_attn_paged(const void* q, const void* k, const void* v, void* out, const void* lengths,
+                                      const void* lo, void* part_o, void* part_ml, int B, int Hq, int Hkv, int D,
+                                      long long batch, long long head, long long page, int page_rows, float scale,
+                                      int splits, void* status, void* stream) {
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || splits < 1 || page_rows < kTile || page_rows % kTile || !status)
+    return -2;
+  if ((batch % 8) || (head % 8) || (page % 8)) return -1;  // 16-byte aligned bulk copies
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) return -1;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  PagedParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (const int*)lengths,
+                (const int*)lo, (float*)part_o, (float*)part_ml, batch, head, page, page_rows, B, Hq, Hkv, splits,
+                scale * kLog2e, (int*)status};
+  int rc;
+  if (D == 128) rc = launch_paged<128>(p, Hq / Hkv, s);
+  else if (D == 64) rc = launch_paged<64>(p, Hq / Hkv, s);
+  else return -2;
+  if (rc) return rc;
+  decode_attn_merge_kernel<<<B * Hq, D, 0, s>>>((const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, splits, D);
   return static_cast<int>(cudaGetLastError());
 }

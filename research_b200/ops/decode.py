@@ -7,6 +7,8 @@ once; see ``csrc/decode.cu``.  The reference attends over the whole padded cache
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from research_b200.errors import KernelError
@@ -33,21 +35,38 @@ def decode_attention_reference(q: torch.Tensor, k_cache: torch.Tensor, v_cache: 
     return torch.einsum("bhk,bkhd->bhd", p, vf).to(q.dtype).reshape(B, Hq * D)
 
 
-def _launch(q, k_base, v_base, lengths, lo, *, B, Hq, Hkv, D, rows, strides, page_rows, scale):
+def _launch(q, k_base, v_base, lengths, lo, *, B, Hq, Hkv, D, rows, strides, page_rows, scale, kernel="auto"):
+    """``kernel``: "stream" (tiles through shared memory with bulk asynchronous copies; needs rows that are
+    contiguous inside a page and pages of a multiple of 32 rows), "registers" (16-byte loads into registers, any
+    strides) or "auto" (stream where the layout allows it)."""
+
     lib = native.load()
     q = q.contiguous()
     lengths = lengths.to(torch.int32).contiguous()
     lo = None if lo is None else lo.to(torch.int32).contiguous()
-    splits = lib.b200_decode_attn_splits(B, Hq, Hkv, rows)
+    k_row, k_batch, k_head, k_page = strides
+    can_stream = k_row == D and page_rows % 32 == 0 and k_batch % 8 == 0 and k_head % 8 == 0 and k_page % 8 == 0
+    if kernel == "stream" and not can_stream:
+        raise KernelError("the streaming decode kernel needs head-major pages of a multiple of 32 rows")
+    stream = can_stream and kernel != "registers" and os.environ.get("RESEARCH_B200_DECODE_STREAM", "1") != "0"
+    splits = (lib.b200_decode_attn_paged_splits if stream else lib.b200_decode_attn_splits)(B, Hq, Hkv, rows)
     part_o = native.scratch("decode_part_o", B * Hq * splits * D, torch.float32, q.device)
     part_ml = native.scratch("decode_part_ml", B * Hq * splits * 2, torch.float32, q.device)
     out = torch.empty((B, Hq, D), dtype=torch.bfloat16, device=q.device)
-    k_row, k_batch, k_head, k_page = strides
-    rc = lib.b200_decode_attn(q.data_ptr(), k_base.data_ptr(), v_base.data_ptr(), out.data_ptr(), lengths.data_ptr(),
-                              None if lo is None else lo.data_ptr(), part_o.data_ptr(), part_ml.data_ptr(), B, Hq, Hkv,
-                              D, k_row, k_batch, k_row, k_batch, k_head, k_head, k_page, k_page, page_rows,
-                              float(D ** -0.5 if scale is None else scale), splits, native._stream())
-    native._check(rc, "b200_decode_attn")
+    lo_ptr = None if lo is None else lo.data_ptr()
+    sm_scale = float(D ** -0.5 if scale is None else scale)
+    if stream:
+        rc = lib.b200_decode_attn_paged(q.data_ptr(), k_base.data_ptr(), v_base.data_ptr(), out.data_ptr(),
+                                        lengths.data_ptr(), lo_ptr, part_o.data_ptr(), part_ml.data_ptr(), B, Hq, Hkv,
+                                        D, k_batch, k_head, k_page, page_rows, sm_scale, splits,
+                                        native.status_word(q.device).data_ptr(), native._stream())
+        native._check(rc, "b200_decode_attn_paged")
+    else:
+        rc = lib.b200_decode_attn(q.data_ptr(), k_base.data_ptr(), v_base.data_ptr(), out.data_ptr(),
+                                  lengths.data_ptr(), lo_ptr, part_o.data_ptr(), part_ml.data_ptr(), B, Hq, Hkv, D,
+                                  k_row, k_batch, k_row, k_batch, k_head, k_head, k_page, k_page, page_rows, sm_scale,
+                                  splits, native._stream())
+        native._check(rc, "b200_decode_attn")
     native.LAUNCHES += 1  # _check counts one launch; the merge kernel is the second
     return out.view(B, Hq * D)
 
@@ -79,7 +98,8 @@ def decode_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
 
 
 def decode_attention_paged(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, lengths: torch.Tensor,
-                           lo: torch.Tensor | None = None, scale: float | None = None) -> torch.Tensor:
+                           lo: torch.Tensor | None = None, scale: float | None = None,
+                           kernel: str = "auto") -> torch.Tensor:
     """Head-major paged caches ``[B, pages, Hkv, page_rows, D]`` (contiguous): every (page, head) is one dense
     ``page_rows x D`` block, so a CTA streams contiguous memory.  Returns ``[B, Hq*D]`` bf16."""
 
@@ -89,7 +109,8 @@ def decode_attention_paged(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
         raise KernelError("paged caches must be contiguous bf16 [B, pages, Hkv, page_rows, D]")
     _check_q(q, Hkv)
     return _launch(q, k_pool, v_pool, lengths, lo, B=B, Hq=Hq, Hkv=Hkv, D=D, rows=pages * page_rows,
-                   strides=(D, k_pool.stride(0), k_pool.stride(2), k_pool.stride(1)), page_rows=page_rows, scale=scale)
+                   strides=(D, k_pool.stride(0), k_pool.stride(2), k_pool.stride(1)), page_rows=page_rows, scale=scale,
+                   kernel=kernel)
 
 
 def kv_append_paged(k_new: torch.Tensor, v_new: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,

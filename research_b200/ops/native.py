@@ -108,6 +108,9 @@ def _declare(lib: ctypes.CDLL) -> None:
     sig("b200_decode_attn_splits", c_int, c_int, c_int, c_int)
     sig("b200_decode_attn", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
         c_int, c_int, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_int, c_float, c_int, c_void_p)
+    sig("b200_decode_attn_paged", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+        c_int, c_int, c_int, c_ll, c_ll, c_ll, c_int, c_float, c_int, c_void_p, c_void_p)
+    sig("b200_decode_attn_paged_splits", c_int, c_int, c_int, c_int)
     sig("b200_kv_append", c_void_p, c_void_p, c_ll, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_ll, c_ll, c_int,
         c_int, c_int, c_int, c_void_p)
     sig("b200_attn_fwd", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,

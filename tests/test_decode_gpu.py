@@ -50,6 +50,33 @@ def test_paged_decode_and_append_match_dense_cache():
     assert torch.allclose(out.float(), ref.float(), atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("D,Hq,Hkv,page_rows", [(128, 16, 8, 128), (128, 8, 8, 64), (64, 16, 4, 128), (128, 16, 2, 32)])
+def test_streaming_paged_decode_matches_reference_and_register_kernel(D, Hq, Hkv, page_rows):
+    """The tile-streaming kernel (bulk copies into shared memory) against the fp32 restatement and the
+    register-resident kernel, with ragged lengths, a lower bound that does not sit on a tile edge, an empty
+    window and a sequence that ends on the first row of a page."""
+    from research_b200.ops import native
+    from research_b200.ops.decode import decode_attention_paged, decode_attention_reference
+
+    torch.manual_seed(D + Hq + page_rows)
+    B, pages = 5, 1024 // page_rows
+    q = (torch.randn(B, Hq, D, device="cuda") * 0.7).bfloat16()
+    kp = (torch.randn(B, pages, Hkv, page_rows, D, device="cuda") * 0.7).bfloat16()
+    vp = torch.randn(B, pages, Hkv, page_rows, D, device="cuda").bfloat16()
+    lengths = torch.tensor([1024, 517, 1, page_rows + 1, 300], device="cuda", dtype=torch.int32)
+    lo = torch.tensor([0, 45, 0, 3, 300], device="cuda", dtype=torch.int32)       # the last window is empty
+    dense_k = kp.permute(0, 1, 3, 2, 4).reshape(B, pages * page_rows, Hkv, D)
+    dense_v = vp.permute(0, 1, 3, 2, 4).reshape(B, pages * page_rows, Hkv, D)
+    for bounds in (None, lo):
+        want = decode_attention_reference(q, dense_k, dense_v, lengths, bounds).float()
+        got = decode_attention_paged(q, kp, vp, lengths, bounds, kernel="stream").float()
+        regs = decode_attention_paged(q, kp, vp, lengths, bounds, kernel="registers").float()
+        native.check_status()
+        torch.testing.assert_close(got, want, atol=2e-2, rtol=2e-2)
+        torch.testing.assert_close(got, regs, atol=1e-2, rtol=1e-2)
+    assert torch.count_nonzero(got[4]) == 0
+
+
 def test_decode_attention_empty_window_gives_zeros():
     from research_b200.ops.decode import decode_attention
 
