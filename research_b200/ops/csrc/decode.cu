@@ -235,8 +235,12 @@ int launch_partial(const DecodeParams& p, int G, cudaStream_t s) {
 // same thread, which is what held the register-resident kernel above at about half of the copy bandwidth.
 // The arithmetic, the split-KV scheme and the merge are the same.
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int kTile = 32;     // cache rows per tile
-constexpr int kStages = 4;
+// Measured on B200 (32 x 2304 and 64 x 4096 cached rows, 16 / 8 heads of 128): tiles of 64 rows, 3 slots and 8 warps
+// (two CTAs per SM) reach 0.72 / 0.83 of the copy bandwidth; 32-row tiles with 4 warps 0.54 / 0.61, 128-row tiles
+// with 16 warps 0.65 / 0.76.
+constexpr int kTile = 64;     // cache rows per tile
+constexpr int kStages = 3;
+constexpr int kPagedWarps = 8;
 constexpr int ERR_DECODE_TILE = 31;  // status code: a tile never landed
 
 struct PagedParams {
@@ -260,20 +264,20 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
                : "memory");
 }
 
-template <int D, int G>
-__global__ void __launch_bounds__(kWarps * 32) decode_attn_paged_kernel(const PagedParams p) {
+template <int D, int G, int TILE, int STAGES, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) decode_attn_paged_kernel(const PagedParams p) {
   constexpr int LPR = D / 8;
   constexpr int RPW = 32 / LPR;
-  constexpr int GROUPS = kWarps * RPW;
-  constexpr int ROWS_PER_GROUP = kTile / GROUPS;
-  constexpr uint32_t TILE_BYTES = kTile * D * 2;
-  static_assert(kTile % GROUPS == 0, "a tile is a whole number of rows per lane group");
+  constexpr int GROUPS = WARPS * RPW;
+  constexpr int ROWS_PER_GROUP = TILE / GROUPS;
+  constexpr uint32_t TILE_BYTES = TILE * D * 2;
+  static_assert(TILE % GROUPS == 0, "a tile is a whole number of rows per lane group");
   extern __shared__ __align__(128) unsigned char smem[];
-  __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(smem);                           // [kStages][kTile * D]
-  __nv_bfloat16* vs = reinterpret_cast<__nv_bfloat16*>(smem + kStages * TILE_BYTES);
-  float* s_acc = reinterpret_cast<float*>(smem + 2 * kStages * TILE_BYTES);             // [GROUPS][G][D]
+  __nv_bfloat16* ks = reinterpret_cast<__nv_bfloat16*>(smem);                           // [STAGES][TILE * D]
+  __nv_bfloat16* vs = reinterpret_cast<__nv_bfloat16*>(smem + STAGES * TILE_BYTES);
+  float* s_acc = reinterpret_cast<float*>(smem + 2 * STAGES * TILE_BYTES);             // [GROUPS][G][D]
   float* s_ml = s_acc + GROUPS * G * D;                                                 // [GROUPS][G][2]
-  __shared__ uint64_t full[kStages];
+  __shared__ uint64_t full[STAGES];
   __shared__ int abort_flag;
 
   const int split = blockIdx.x, hkv = blockIdx.y, b = blockIdx.z;
@@ -284,15 +288,15 @@ __global__ void __launch_bounds__(kWarps * 32) decode_attn_paged_kernel(const Pa
 
   const int len = p.lengths[b];
   const int first = p.lo ? max(p.lo[b], 0) : 0;
-  const int tile_lo = first / kTile;
-  const int tile_hi = len > first ? (len + kTile - 1) / kTile : tile_lo;
+  const int tile_lo = first / TILE;
+  const int tile_hi = len > first ? (len + TILE - 1) / TILE : tile_lo;
   const int per = (tile_hi - tile_lo + p.splits - 1) / p.splits;
   const int t_begin = tile_lo + split * per;
   const int n_tiles = max(min(t_begin + per, tile_hi) - t_begin, 0);
 
   if (threadIdx.x == 0) {
     abort_flag = 0;
-    for (int s = 0; s < kStages; ++s) b200::mbar_init(&full[s], 1);
+    for (int s = 0; s < STAGES; ++s) b200::mbar_init(&full[s], 1);
     b200::mbar_fence_init();
   }
   __syncthreads();
@@ -300,17 +304,17 @@ __global__ void __launch_bounds__(kWarps * 32) decode_attn_paged_kernel(const Pa
   const __nv_bfloat16* kb = p.k + b * p.batch + hkv * p.head;
   const __nv_bfloat16* vb = p.v + b * p.batch + hkv * p.head;
   auto issue = [&](int i) {  // thread 0 only
-    const int s = i % kStages;
-    const int r0 = (t_begin + i) * kTile;
+    const int s = i % STAGES;
+    const int r0 = (t_begin + i) * TILE;
     const int pg = r0 / p.page_rows, in = r0 - pg * p.page_rows;
     const long long off = pg * p.page + (long long)in * D;
     b200::mbar_expect_tx(&full[s], 2 * TILE_BYTES);
-    bulk_load(ks + s * (kTile * D), kb + off, TILE_BYTES, &full[s]);
-    bulk_load(vs + s * (kTile * D), vb + off, TILE_BYTES, &full[s]);
+    bulk_load(ks + s * (TILE * D), kb + off, TILE_BYTES, &full[s]);
+    bulk_load(vs + s * (TILE * D), vb + off, TILE_BYTES, &full[s]);
   };
   int issued = 0;
   if (threadIdx.x == 0)
-    for (; issued < min(kStages, n_tiles); ++issued) issue(issued);
+    for (; issued < min(STAGES, n_tiles); ++issued) issue(issued);
 
   float q[G][8], acc[G][8], m[G], lsum[G];
 #pragma unroll
@@ -328,36 +332,70 @@ __global__ void __launch_bounds__(kWarps * 32) decode_attn_paged_kernel(const Pa
 
   int done = 0;
   for (; done < n_tiles; ++done) {
-    const int s = done % kStages;
+    const int s = done % STAGES;
     // the verdict is made uniform over the CTA, so that either everybody reduces this tile or everybody leaves
-    const bool landed = b200::mbar_wait(&full[s], (done / kStages) & 1, ab, ERR_DECODE_TILE);
+    const bool landed = b200::mbar_wait(&full[s], (done / STAGES) & 1, ab, ERR_DECODE_TILE);
     if (!__syncthreads_and(landed)) break;
-    const int r0 = (t_begin + done) * kTile;
-    const __nv_bfloat16* kt = ks + s * (kTile * D) + l * 8;
-    const __nv_bfloat16* vt = vs + s * (kTile * D) + l * 8;
+    const int r0 = (t_begin + done) * TILE;
+    const __nv_bfloat16* kt = ks + s * (TILE * D) + l * 8;
+    const __nv_bfloat16* vt = vs + s * (TILE * D) + l * 8;
+    // Blocked online softmax: the scores of all rows of this lane group (and all heads of the GQA group) first, as
+    // independent dot products and shuffle trees, then one running-maximum update and one rescale per tile.
+    float sc[ROWS_PER_GROUP][G];
+    bool valid[ROWS_PER_GROUP];
 #pragma unroll
     for (int u = 0; u < ROWS_PER_GROUP; ++u) {
       const int j = grp + u * GROUPS;
       const int r = r0 + j;
-      if (r >= first && r < len) {  // uniform inside a lane group
-        float kf[8], vf[8];
-        unpack8(*reinterpret_cast<const uint4*>(kt + j * D), kf);
-        unpack8(*reinterpret_cast<const uint4*>(vt + j * D), vf);
+      valid[u] = r >= first && r < len;  // uniform inside a lane group
+      float kf[8];
+      unpack8(*reinterpret_cast<const uint4*>(kt + j * D), kf);
 #pragma unroll
-        for (int g = 0; g < G; ++g) {
-          float sc = 0.f;
+      for (int g = 0; g < G; ++g) {
+        float a = 0.f;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) sc = fmaf(q[g][i], kf[i], sc);
+        for (int i = 0; i < 8; ++i) a = fmaf(q[g][i], kf[i], a);
+        sc[u][g] = a;
+      }
+    }
 #pragma unroll
-          for (int off = LPR >> 1; off > 0; off >>= 1) sc += __shfl_xor_sync(gmask, sc, off, LPR);
-          const float m_new = fmaxf(m[g], sc);
-          const float alpha = ex2f(m[g] - m_new);
-          const float pr = ex2f(sc - m_new);
-          m[g] = m_new;
-          lsum[g] = lsum[g] * alpha + pr;
+    for (int off = LPR >> 1; off > 0; off >>= 1) {
 #pragma unroll
-          for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(acc[g][i], alpha, pr * vf[i]);
-        }
+      for (int u = 0; u < ROWS_PER_GROUP; ++u)
+#pragma unroll
+        for (int g = 0; g < G; ++g) sc[u][g] += __shfl_xor_sync(gmask, sc[u][g], off, LPR);
+    }
+    float pr[ROWS_PER_GROUP][G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float m_new = m[g];
+#pragma unroll
+      for (int u = 0; u < ROWS_PER_GROUP; ++u) {
+        sc[u][g] = valid[u] ? sc[u][g] : -CUDART_INF_F;  // rows outside the window (their bytes may be anything)
+        m_new = fmaxf(m_new, sc[u][g]);
+      }
+      const float m_use = m_new == -CUDART_INF_F ? 0.f : m_new;  // nothing visible yet: keep the state at zero
+      const float alpha = ex2f(m[g] - m_use);
+      float psum = 0.f;
+#pragma unroll
+      for (int u = 0; u < ROWS_PER_GROUP; ++u) {
+        pr[u][g] = ex2f(sc[u][g] - m_use);
+        psum += pr[u][g];
+      }
+      m[g] = m_new;
+      lsum[g] = lsum[g] * alpha + psum;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[g][i] *= alpha;
+    }
+#pragma unroll
+    for (int u = 0; u < ROWS_PER_GROUP; ++u) {
+      if (valid[u]) {
+        float vf[8];
+        unpack8(*reinterpret_cast<const uint4*>(vt + (grp + u * GROUPS) * D), vf);
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(pr[u][g], vf[i], acc[g][i]);
       }
     }
     __syncthreads();  // every warp is done with slot s
@@ -370,7 +408,7 @@ __global__ void __launch_bounds__(kWarps * 32) decode_attn_paged_kernel(const Pa
     if (threadIdx.x == 0) {
       for (int i = done; i < issued; ++i) {
         const uint64_t t0 = b200::globaltimer_ns();
-        while (!b200::mbar_try_wait(&full[i % kStages], (i / kStages) & 1) &&
+        while (!b200::mbar_try_wait(&full[i % STAGES], (i / STAGES) & 1) &&
                b200::globaltimer_ns() - t0 < b200::kWaitLimitNs) {
         }
       }
@@ -388,7 +426,7 @@ __global__ void __launch_bounds__(kWarps * 32) decode_attn_paged_kernel(const Pa
     }
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < G * D; idx += kWarps * 32) {
+  for (int idx = threadIdx.x; idx < G * D; idx += WARPS * 32) {
     const int g = idx / D, d = idx % D;
     float mm = -CUDART_INF_F;
 #pragma unroll
@@ -411,23 +449,28 @@ __global__ void __launch_bounds__(kWarps * 32) decode_attn_paged_kernel(const Pa
   }
 }
 
-template <int D, int G>
+template <int D, int G, int TILE, int STAGES, int WARPS>
 constexpr int paged_smem_bytes() {
-  return 2 * kStages * kTile * D * 2 + (kWarps * (32 / (D / 8))) * G * (D + 2) * 4;
+  return 2 * STAGES * TILE * D * 2 + (WARPS * (32 / (D / 8))) * G * (D + 2) * 4;
+}
+
+template <int D, int G, int TILE, int STAGES, int WARPS>
+int launch_paged_cfg(const PagedParams& p, cudaStream_t s) {
+  constexpr int bytes = paged_smem_bytes<D, G, TILE, STAGES, WARPS>();
+  static bool configured = false;  // per instantiation; the attribute is per function and sticky
+  if (!configured) {
+    if (cudaFuncSetAttribute(decode_attn_paged_kernel<D, G, TILE, STAGES, WARPS>,
+                             cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
+      return -3;
+    configured = true;
+  }
+  decode_attn_paged_kernel<D, G, TILE, STAGES, WARPS><<<dim3(p.splits, p.Hkv, p.B), WARPS * 32, bytes, s>>>(p);
+  return static_cast<int>(cudaGetLastError());
 }
 
 template <int D, int G>
 int launch_paged_one(const PagedParams& p, cudaStream_t s) {
-  constexpr int bytes = paged_smem_bytes<D, G>();
-  static bool configured = false;  // per instantiation; the attribute is per function and sticky
-  if (!configured) {
-    if (cudaFuncSetAttribute(decode_attn_paged_kernel<D, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) !=
-        cudaSuccess)
-      return -3;
-    configured = true;
-  }
-  decode_attn_paged_kernel<D, G><<<dim3(p.splits, p.Hkv, p.B), kWarps * 32, bytes, s>>>(p);
-  return static_cast<int>(cudaGetLastError());
+  return launch_paged_cfg<D, G, kTile, kStages, kPagedWarps>(p, s);
 }
 
 template <int D>
@@ -499,14 +542,14 @@ extern "C" int b200_kv_append(const void* k_new, const void* v_new, long long kn
   return static_cast<int>(cudaGetLastError());
 }
 
-// Splits for the tile-streaming kernel: one wave of resident CTAs (shared memory allows three per SM for GQA groups
-// up to two, two otherwise), at least 256 rows each.
+// Splits for the tile-streaming kernel: one wave of resident CTAs (shared memory allows two per SM for GQA groups
+// up to two, one otherwise), at least 256 rows each.
 extern "C" int b200_decode_attn_paged_splits(int B, int Hq, int Hkv, int max_rows) {
   int dev = 0, sms = 148;
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const int G = Hkv > 0 ? Hq / Hkv : 1;
-  const int per_sm = G <= 2 ? 3 : 2;
+  const int per_sm = G <= 2 ? 2 : 1;  // by the shared memory of the tile ring and the merge scratch
   const int base = B * Hkv > 0 ? B * Hkv : 1;
   int splits = sms * per_sm / base;
   const int by_rows = (max_rows + 255) / 256;
@@ -516,15 +559,16 @@ extern "C" int b200_decode_attn_paged_splits(int B, int Hq, int Hkv, int max_row
 }
 
 // Decode attention over head-major pages [.., pages, Hkv, page_rows, D] whose rows are contiguous inside a
-// (page, head) block: element strides `batch`, `head`, `page` (shared by K and V), page_rows a multiple of 32.
-// Every page that holds a row below lengths[b] must be allocated in full (tiles of 32 rows are copied whole).
+// (page, head) block: element strides `batch`, `head`, `page` (shared by K and V), page_rows a multiple of 64.
+// Every page that holds a row below lengths[b] must be allocated in full (tiles of 64 rows are copied whole).
 // Scratch and result as for b200_decode_attn; `status` is the device status word that bounded waits report to.
 extern "C" int b200_decode_attn_paged(const void* q, const void* k, const void* v, void* out, const void* lengths,
                                       const void* lo, void* part_o, void* part_ml, int B, int Hq, int Hkv, int D,
                                       long long batch, long long head, long long page, int page_rows, float scale,
                                       int splits, void* status, void* stream) {
-  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || splits < 1 || page_rows < kTile || page_rows % kTile || !status)
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || splits < 1 || !status)
     return -2;
+  if (page_rows < kTile || page_rows % kTile) return -2;  // a tile never straddles two pages
   if ((batch % 8) || (head % 8) || (page % 8)) return -1;  // 16-byte aligned bulk copies
   if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v)) & 15) return -1;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);

@@ -37,7 +37,7 @@ def decode_attention_reference(q: torch.Tensor, k_cache: torch.Tensor, v_cache: 
 
 def _launch(q, k_base, v_base, lengths, lo, *, B, Hq, Hkv, D, rows, strides, page_rows, scale, kernel="auto"):
     """``kernel``: "stream" (tiles through shared memory with bulk asynchronous copies; needs rows that are
-    contiguous inside a page and pages of a multiple of 32 rows), "registers" (16-byte loads into registers, any
+    contiguous inside a page and pages of a multiple of 64 rows), "registers" (16-byte loads into registers, any
     strides) or "auto" (stream where the layout allows it)."""
 
     lib = native.load()
@@ -45,9 +45,9 @@ def _launch(q, k_base, v_base, lengths, lo, *, B, Hq, Hkv, D, rows, strides, pag
     lengths = lengths.to(torch.int32).contiguous()
     lo = None if lo is None else lo.to(torch.int32).contiguous()
     k_row, k_batch, k_head, k_page = strides
-    can_stream = k_row == D and page_rows % 32 == 0 and k_batch % 8 == 0 and k_head % 8 == 0 and k_page % 8 == 0
+    can_stream = k_row == D and page_rows % 64 == 0 and k_batch % 8 == 0 and k_head % 8 == 0 and k_page % 8 == 0
     if kernel == "stream" and not can_stream:
-        raise KernelError("the streaming decode kernel needs head-major pages of a multiple of 32 rows")
+        raise KernelError("the streaming decode kernel needs head-major pages of a multiple of 64 rows")
     stream = can_stream and kernel != "registers" and os.environ.get("RESEARCH_B200_DECODE_STREAM", "1") != "0"
     splits = (lib.b200_decode_attn_paged_splits if stream else lib.b200_decode_attn_splits)(B, Hq, Hkv, rows)
     part_o = native.scratch("decode_part_o", B * Hq * splits * D, torch.float32, q.device)
