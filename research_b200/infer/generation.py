@@ -59,11 +59,23 @@ class PagedKVCache:
             lo = None if window is None else (pos - (window - 1)).clamp_min(0).to(torch.int32)
             return decode_attention_paged(q[:, 0], kp, vp, (pos + 1).to(torch.int32), lo)[:, None]
         idx = positions.long()
-        b_idx = torch.arange(B, device=q.device)[:, None].expand(B, T)
-        kp[b_idx, idx // self.page_size, :, idx % self.page_size] = k.to(kp.dtype)
-        vp[b_idx, idx // self.page_size, :, idx % self.page_size] = v.to(vp.dtype)
-        if (T > 1 and native_ok
-                and bool((positions == torch.arange(T, device=q.device, dtype=positions.dtype)).all())):
+        from_zero = T > 1 and bool((positions == torch.arange(T, device=q.device, dtype=positions.dtype)).all())
+        if from_zero:
+            # a prompt written from row 0: whole pages are strided block copies, no index arithmetic per element
+            ps = self.page_size
+            full = T // ps
+            if full:
+                kp[:, :full].copy_(k[:, :full * ps].reshape(B, full, ps, *k.shape[2:]).permute(0, 1, 3, 2, 4))
+                vp[:, :full].copy_(v[:, :full * ps].reshape(B, full, ps, *v.shape[2:]).permute(0, 1, 3, 2, 4))
+            rest = T - full * ps
+            if rest:
+                kp[:, full, :, :rest].copy_(k[:, full * ps:].permute(0, 2, 1, 3))
+                vp[:, full, :, :rest].copy_(v[:, full * ps:].permute(0, 2, 1, 3))
+        else:
+            b_idx = torch.arange(B, device=q.device)[:, None].expand(B, T)
+            kp[b_idx, idx // self.page_size, :, idx % self.page_size] = k.to(kp.dtype)
+            vp[b_idx, idx // self.page_size, :, idx % self.page_size] = v.to(vp.dtype)
+        if from_zero and native_ok:
             # prefill from position 0: the flash kernel over the rows just computed
             from research_b200.ops import native
 
