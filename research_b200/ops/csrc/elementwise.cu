@@ -95,6 +95,70 @@ rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __r
   }
 }
 
+// The same for a handful of rows (a decode step): one block per row, so that a row's loads are issued by 256 threads at
+// once instead of one warp walking it.
+__global__ void __launch_bounds__(256)
+rmsnorm_fwd_row_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ delta,
+                       const float* __restrict__ w, __nv_bfloat16* __restrict__ res_out, __nv_bfloat16* __restrict__ y,
+                       float* __restrict__ rstd_out, int H, float eps) {
+  __shared__ float part[8];
+  const long long row = blockIdx.x;
+  const int nvec = H >> 3;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
+  const uint4* dr = delta ? reinterpret_cast<const uint4*>(delta + row * H) : nullptr;
+  uint4* rr = res_out ? reinterpret_cast<uint4*>(res_out + row * H) : nullptr;
+  float ss = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += 256) {
+    float f[8];
+    unpack8(xr[v], f);
+    if (dr) {
+      float g[8];
+      unpack8(dr[v], g);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) f[i] += g[i];
+      uint4 s = pack8(f);
+      rr[v] = s;
+      unpack8(s, f);  // normalise exactly what was stored
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ss += f[i] * f[i];
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float total = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) total += part[i];
+  const float rstd = rsqrtf(total / (float)H + eps);
+  if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+  const uint4* src = dr ? reinterpret_cast<const uint4*>(res_out + row * H) : xr;
+  uint4* yr = reinterpret_cast<uint4*>(y + row * H);
+  for (int v = threadIdx.x; v < nvec; v += 256) {  // a thread re-reads only what it wrote itself
+    float f[8], wv[8];
+    unpack8(src[v], f);
+    load8f(w + v * 8, wv);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = f[i] * rstd * wv[i];
+    yr[v] = pack8(f);
+  }
+}
+
+// Tail of a split-K GEMM for a handful of rows: the slices were reduce-added into an fp32 workspace that was zero
+// before; this reads the sums, writes them as bf16 and puts the zeros back, so the workspace needs no separate
+// fill before its next use.  n % 4 == 0.
+__global__ void __launch_bounds__(256)
+splitk_finish_kernel(float* __restrict__ ws, __nv_bfloat16* __restrict__ out, long long n4) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
+    const float4 v = reinterpret_cast<const float4*>(ws)[i];
+    reinterpret_cast<float4*>(ws)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 packed;
+    packed.x = *reinterpret_cast<uint32_t*>(&lo);
+    packed.y = *reinterpret_cast<uint32_t*>(&hi);
+    reinterpret_cast<uint2*>(out)[i] = packed;
+  }
+}
+
 // RMSNorm backward.  dx = rstd * (dy*w - xhat * mean(dy*w*xhat)) (+ dres if given); dw += sum_rows dy*xhat
 // NV > 0: H == NV * 256 and every lane keeps its dw partial sums in registers over all of its rows;
 // NV == 0: any H % 8 == 0, partial sums go through shared-memory atomics.  Either way a block folds its
@@ -637,6 +701,12 @@ inline int grid_for(long long work_items, int block, int per_sm = 8) {
 extern "C" int b200_rmsnorm_fwd(const void* x, const void* delta, const void* w, void* res_out, void* y, void* rstd,
                                 int rows, int H, float eps, void* stream) {
   if (H % 8) return -2;
+  if (rows > 0 && rows <= 512) {
+    rmsnorm_fwd_row_kernel<<<rows, 256, 0, STREAM(stream)>>>(
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)delta, (const float*)w, (__nv_bfloat16*)res_out,
+        (__nv_bfloat16*)y, (float*)rstd, H, eps);
+    return LAST_ERR();
+  }
   const int grid = grid_for((long long)rows, kWarpsPerBlock, 8);
   rmsnorm_fwd_kernel<<<grid, kWarpsPerBlock * 32, 0, STREAM(stream)>>>(
       (const __nv_bfloat16*)x, (const __nv_bfloat16*)delta, (const float*)w, (__nv_bfloat16*)res_out,
@@ -800,5 +870,15 @@ extern "C" int b200_sumsq(const void* x, int is_bf16, long long n, void* scratch
 extern "C" int b200_cast_f32_bf16(const void* x, void* y, long long n, float scale, void* stream) {
   if (n <= 0) return 0;
   cast_f32_bf16_kernel<<<grid_for(n, 256, 8), 256, 0, STREAM(stream)>>>((const float*)x, (__nv_bfloat16*)y, n, scale);
+  return LAST_ERR();
+}
+
+// ws: fp32 [n] holding split-K sums (zeroed again on return), out: bf16 [n]; n % 4 == 0, both 16-byte aligned.
+extern "C" int b200_splitk_finish(void* ws, void* out, long long n, void* stream) {
+  if (n <= 0 || n % 4) return -2;
+  const long long n4 = n / 4;
+  long long blocks = (n4 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  splitk_finish_kernel<<<(int)blocks, 256, 0, STREAM(stream)>>>((float*)ws, (__nv_bfloat16*)out, n4);
   return LAST_ERR();
 }

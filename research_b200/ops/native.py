@@ -111,6 +111,7 @@ def _declare(lib: ctypes.CDLL) -> None:
     sig("b200_decode_attn_paged", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
         c_int, c_int, c_int, c_ll, c_ll, c_ll, c_int, c_float, c_int, c_void_p, c_void_p)
     sig("b200_decode_attn_paged_splits", c_int, c_int, c_int, c_int)
+    sig("b200_splitk_finish", c_void_p, c_void_p, c_ll, c_void_p)
     sig("b200_kv_append", c_void_p, c_void_p, c_ll, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_ll, c_ll, c_int,
         c_int, c_int, c_int, c_void_p)
     sig("b200_attn_fwd", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
@@ -276,11 +277,41 @@ def gemm_skinny(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     splits = splitk_factor(N, K)
     if splits == 1:
         return gemm(a, b, trans_b=True)
-    c = torch.zeros((rows, N), dtype=torch.float32, device=a.device)
-    rc = lib.b200_gemm_bf16_splitk(a.data_ptr(), b.data_ptr(), c.data_ptr(), rows, N, K, splits, a.stride(0),
-                                   b.stride(0), c.stride(0), status_word(a.device).data_ptr(), _stream())
-    _check(rc, "b200_gemm_bf16_splitk")
-    return c.to(torch.bfloat16)
+    if N % 4:
+        c = torch.zeros((rows, N), dtype=torch.float32, device=a.device)
+        rc = lib.b200_gemm_bf16_splitk(a.data_ptr(), b.data_ptr(), c.data_ptr(), rows, N, K, splits, a.stride(0),
+                                       b.stride(0), c.stride(0), status_word(a.device).data_ptr(), _stream())
+        _check(rc, "b200_gemm_bf16_splitk")
+        return c.to(torch.bfloat16)
+    # the slices add into a persistent fp32 workspace that is zero between calls: the finishing kernel converts the
+    # sums to bf16 and clears what it read, so a decode step runs no fill and no cast kernel per linear
+    ws = _splitk_workspace(rows * N, a.device)
+    out = torch.empty((rows, N), dtype=torch.bfloat16, device=a.device)
+    try:
+        rc = lib.b200_gemm_bf16_splitk(a.data_ptr(), b.data_ptr(), ws.data_ptr(), rows, N, K, splits, a.stride(0),
+                                       b.stride(0), N, status_word(a.device).data_ptr(), _stream())
+        _check(rc, "b200_gemm_bf16_splitk")
+        _check(lib.b200_splitk_finish(ws.data_ptr(), out.data_ptr(), rows * N, _stream()), "b200_splitk_finish")
+    except Exception:
+        _splitk_ws.pop(_device_index(a.device), None)      # its contents are unknown now: start from a fresh one
+        raise
+    return out
+
+
+_splitk_ws: dict[int, torch.Tensor] = {}
+
+
+def _device_index(device: torch.device) -> int:
+    return device.index if device.index is not None else torch.cuda.current_device()
+
+
+def _splitk_workspace(numel: int, device: torch.device) -> torch.Tensor:
+    key = _device_index(device)
+    ws = _splitk_ws.get(key)
+    if ws is None or ws.numel() < numel:
+        ws = torch.zeros(max(numel, 1 << 20), dtype=torch.float32, device=device)
+        _splitk_ws[key] = ws
+    return ws
 
 
 def rmsnorm_fwd(x: torch.Tensor, w: torch.Tensor, eps: float, delta: torch.Tensor | None = None):

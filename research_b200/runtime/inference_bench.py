@@ -81,6 +81,7 @@ def run_inference_bench(spec, *, batch: int, prompt: int, new_tokens: int, tempe
     for _ in range(warmup):
         one_run()
     runs = [one_run() for _ in range(repeats)]
+    all_prefill = [1e3 * r[0] for r in runs]
     runs.sort(key=lambda r: r[2])
     t_prefill, t_first, t_decode = runs[len(runs) // 2]
     steps = max(new_tokens - 1, 1)
@@ -90,6 +91,7 @@ def run_inference_bench(spec, *, batch: int, prompt: int, new_tokens: int, tempe
         "unit": "tokens/s",
         "decode_ms_per_step": 1e3 * t_decode / steps,
         "prefill_ms": 1e3 * t_prefill,
+        "prefill_ms_all_runs": all_prefill,
         "prefill_tokens_per_sec": batch * prompt / t_prefill,
         "ttft_ms": 1e3 * t_first,
         "batch": batch, "prompt_tokens": prompt, "new_tokens": new_tokens, "temperature": temperature, "top_k": top_k,

@@ -14,10 +14,11 @@ def _bf(shape, seed, scale=1.0):
 
 
 @pytest.mark.parametrize("H", [128, 2048, 4096, 1000])
-def test_rmsnorm_fwd_bwd(H):
+@pytest.mark.parametrize("rows", [77, 1500])   # one block per row below 512 rows, one warp per row above
+def test_rmsnorm_fwd_bwd(H, rows):
     from research_b200.ops import native
 
-    rows, eps = 77, 1e-6
+    eps = 1e-6
     x, delta, dy = _bf((rows, H), 1), _bf((rows, H), 2), _bf((rows, H), 3)
     w = torch.rand(H, device="cuda") + 0.5
     y, rstd, res = native.rmsnorm_fwd(x, w, eps, delta)

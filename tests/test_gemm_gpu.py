@@ -90,7 +90,9 @@ def test_skinny_splitk_gemm_matches_reference():
     from research_b200.ops import native
 
     torch.manual_seed(0)
-    for rows, n, k in ((32, 2048, 2048), (32, 2048, 5632), (7, 11264, 2048), (64, 4096, 2048), (3, 512, 256)):
+    # the shapes share one fp32 workspace that every call must leave zeroed: large after small and back again
+    for rows, n, k in ((32, 2048, 2048), (32, 2048, 5632), (7, 11264, 2048), (64, 4096, 2048), (3, 512, 256),
+                       (64, 11264, 2048), (32, 2048, 2048)):
         a = (torch.randn(rows, k, device="cuda") * 0.5).bfloat16()
         b = (torch.randn(n, k, device="cuda") * 0.05).bfloat16()
         y = native.gemm_skinny(a, b)
