@@ -544,12 +544,8 @@ int launch_bwd(const CUtensorMap& x1, const CUtensorMap& x2, const CUtensorMap& 
   using L = BwdSmem<D>;
   auto* kern = attn_bwd_kernel<D, DKV>;
   constexpr int smem_bytes = L::TOTAL;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
+  static bool configured[b200host::kMaxDevices] = {};   // per kernel instantiation and device
+  if (int rc = b200host::ensure_dynamic_smem(kern, smem_bytes, configured)) return rc;
   const int tiles = ((DKV ? p.Skv : p.S) + TILE - 1) / TILE;
   const int grid = tiles * (DKV ? p.Hkv : p.Hq) * p.B;
   kern<<<grid, NUM_THREADS, smem_bytes, stream>>>(x1, x2, y1, y2, o1, o2, p);

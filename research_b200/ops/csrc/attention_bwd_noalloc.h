@@ -14,7 +14,9 @@
 //   * B * Hq * S must not exceed B200_ATTN_NOALLOC_MAX_ROWS; larger problems are rejected with
 //     B200_ATTN_NOALLOC_TOO_LARGE (and a line on stderr) before anything is launched.
 //   * The first call on each device looks up the array's device address (cudaGetSymbolAddress with that device
-//     current) and caches it.  Make that first call outside of any stream capture.
+//     current) and caches it.  Make that first call outside of any stream capture, and do not let two threads
+//     make the first call for the same device at the same time (the cache slot is written without a lock; both
+//     would write the same value, but nothing orders the writes).
 //   * All calls on one device share the one array.  The array keeps whatever the last call left in it; every
 //     call overwrites the part it uses before reading it, so nothing has to be cleared - but two calls
 //     that overlap in time on the same GPU (different streams, different threads) race on it.  Serialise them.

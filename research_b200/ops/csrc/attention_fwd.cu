@@ -360,12 +360,8 @@ int launch_fwd(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap
   using L = FwdSmem<D>;
   auto* kern = attn_fwd_kernel<D>;
   constexpr int smem_bytes = L::TOTAL + 1024;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
+  static bool configured[b200host::kMaxDevices] = {};   // per kernel instantiation and device
+  if (int rc = b200host::ensure_dynamic_smem(kern, smem_bytes, configured)) return rc;
   const int q_tiles = (p.S + NT * TILE_M - 1) / (NT * TILE_M);
   const int grid = q_tiles * p.Hq * p.B;
   kern<<<grid, NUM_THREADS, smem_bytes, stream>>>(tmQ, tmK, tmV, tmO, p);

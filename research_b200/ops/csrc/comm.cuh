@@ -15,7 +15,15 @@ enum CommError : int {
 };
 
 constexpr int kMaxPeers = 8;
-constexpr uint64_t kPeerWaitLimitNs = 2000000000ull;  // 2 s
+constexpr uint64_t kPeerWaitLimitNs = 2000000000ull;  // 2 s: the limit when the host configured none
+
+// The status buffer that every kernel gets is four int32 words: [0] the first error code (0 = none), [1] unused,
+// [2] the limit of a cross-GPU wait in milliseconds as configured by the host (0 = the 2 s default), [3] unused.
+// The limit is read only on the slow path, after the first probes of a flag failed.
+__device__ __forceinline__ uint64_t peer_wait_limit_ns(const int* status) {
+  const int ms = reinterpret_cast<const volatile int*>(status)[2];
+  return ms > 0 ? (uint64_t)ms * 1000000ull : kPeerWaitLimitNs;
+}
 
 // Layout of one rank's flag block (uint32 words) inside its symmetric arena.
 //   ready[src]  written by rank src: "my buffer holds epoch e"
@@ -58,13 +66,14 @@ __device__ __forceinline__ bool reached(uint32_t seen, uint32_t want) { return (
 __device__ __forceinline__ bool wait_sys(const uint32_t* flag, uint32_t want, int* status, int code) {
   if (reached(ld_acquire_sys(flag), want)) return true;
   const uint64_t t0 = timer_ns();
+  const uint64_t limit = peer_wait_limit_ns(status);
   while (true) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i) {
       if (reached(ld_acquire_sys(flag), want)) return true;
       __nanosleep(200);
     }
-    if (timer_ns() - t0 > kPeerWaitLimitNs) {
+    if (timer_ns() - t0 > limit) {
       atomicCAS(status, 0, code);
       return false;
     }
@@ -75,13 +84,14 @@ __device__ __forceinline__ bool wait_sys(const uint32_t* flag, uint32_t want, in
 __device__ __forceinline__ bool wait_gpu(const uint32_t* flag, uint32_t want, int* status, int code) {
   if (reached(ld_acquire_gpu(flag), want)) return true;
   const uint64_t t0 = timer_ns();
+  const uint64_t limit = peer_wait_limit_ns(status);
   while (true) {
 #pragma unroll 1
     for (int i = 0; i < 64; ++i) {
       if (reached(ld_acquire_gpu(flag), want)) return true;
       __nanosleep(100);
     }
-    if (timer_ns() - t0 > kPeerWaitLimitNs) {
+    if (timer_ns() - t0 > limit) {
       atomicCAS(status, 0, code);
       return false;
     }

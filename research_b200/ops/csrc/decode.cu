@@ -457,13 +457,9 @@ constexpr int paged_smem_bytes() {
 template <int D, int G, int TILE, int STAGES, int WARPS>
 int launch_paged_cfg(const PagedParams& p, cudaStream_t s) {
   constexpr int bytes = paged_smem_bytes<D, G, TILE, STAGES, WARPS>();
-  static bool configured = false;  // per instantiation; the attribute is per function and sticky
-  if (!configured) {
-    if (cudaFuncSetAttribute(decode_attn_paged_kernel<D, G, TILE, STAGES, WARPS>,
-                             cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
-      return -3;
-    configured = true;
-  }
+  static bool configured[b200host::kMaxDevices] = {};  // per instantiation and device; the attribute is sticky
+  if (b200host::ensure_dynamic_smem(decode_attn_paged_kernel<D, G, TILE, STAGES, WARPS>, bytes, configured) != 0)
+    return -3;
   decode_attn_paged_kernel<D, G, TILE, STAGES, WARPS><<<dim3(p.splits, p.Hkv, p.B), WARPS * 32, bytes, s>>>(p);
   return static_cast<int>(cudaGetLastError());
 }

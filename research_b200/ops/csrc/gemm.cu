@@ -294,13 +294,9 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tm
            cudaStream_t stream) {
   using L = SmemLayout<BN>;
   auto* kern = gemm_bf16_kernel<BN, A_MN, B_MN, OUT_F32>;
-  static bool configured = false;
   constexpr int smem_bytes = L::TOTAL + 1024;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-    if (e != cudaSuccess) return static_cast<int>(e);
-    configured = true;
-  }
+  static bool configured[b200host::kMaxDevices] = {};   // per kernel instantiation and device
+  if (int rc = b200host::ensure_dynamic_smem(kern, smem_bytes, configured)) return rc;
   kern<<<grid, NUM_THREADS, smem_bytes, stream>>>(tmA, tmB, tmC, p);
   return static_cast<int>(cudaGetLastError());
 }

@@ -46,6 +46,23 @@ inline int sm_count() {
   return n[dev];
 }
 
+// The opt-in to more than 48 KB of dynamic shared memory is an attribute of (function, device).  `done` is the
+// caller's per-kernel table (one static table per template instantiation), indexed by the current device, so a
+// process that drives several GPUs configures the kernel on each of them.  Devices beyond the table are
+// configured on every launch.
+constexpr int kMaxDevices = 64;
+template <typename Kern>
+inline int ensure_dynamic_smem(Kern* kern, int bytes, bool (&done)[kMaxDevices]) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return static_cast<int>(cudaGetLastError());
+  const bool tracked = dev >= 0 && dev < kMaxDevices;
+  if (tracked && done[dev]) return 0;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) return static_cast<int>(e);
+  if (tracked) done[dev] = true;
+  return 0;
+}
+
 // Rank-3 row-major tensor [d2][d1][d0] (d0 innermost) with byte strides s1 (between d1 rows) and
 // s2 (between d2 slabs); box {b0, b1, 1}; 128-byte swizzle; zero fill out of bounds.
 inline int make_map_3d(CUtensorMap* out, CUtensorMapDataType dt, const void* base, uint64_t d0, uint64_t d1,

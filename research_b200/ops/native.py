@@ -11,6 +11,7 @@ for tests and for the end of a step, not for the hot path).
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from pathlib import Path
 
@@ -129,25 +130,55 @@ def _ptr(t: torch.Tensor | None) -> int | None:
     return None if t is None else t.data_ptr()
 
 
+def peer_wait_limit_ms() -> int:
+    """Limit of one cross-GPU wait inside a kernel, in milliseconds (``RESEARCH_B200_PEER_WAIT_MS``, default 30 s).
+
+    It has to sit well above the skew between ranks that the host can cause (a trace export on one rank, a slow
+    data read, a garbage-collection pause): a wait that gives up makes its kernel skip the dependent work."""
+
+    return max(1, int(os.environ.get("RESEARCH_B200_PEER_WAIT_MS", "30000")))
+
+
 def status_word(device: torch.device | int | None = None) -> torch.Tensor:
+    """Four int32 words per device that every kernel with a bounded wait gets: [0] first error code (0 = none),
+    [2] the cross-GPU wait limit in milliseconds (read by the kernels), [1] and [3] unused."""
+
     dev = torch.cuda.current_device() if device is None else torch.device(device).index
     if dev is None:
         dev = torch.cuda.current_device()
     buf = _status.get(dev)
     if buf is None:
-        buf = torch.zeros(4, dtype=torch.int32, device=f"cuda:{dev}")
+        buf = torch.tensor([0, 0, peer_wait_limit_ms(), 0], dtype=torch.int32, device=f"cuda:{dev}")
         _status[dev] = buf
     return buf
+
+
+def set_peer_wait_limit_ms(ms: int, device: torch.device | int | None = None) -> None:
+    """Change the cross-GPU wait limit of the kernels launched after this call on ``device``."""
+
+    status_word(device)[2:3].fill_(max(1, int(ms)))
+
+
+def status_code_tensor(device: torch.device | int | None = None) -> torch.Tensor:
+    """The error-code word as a 1-element device tensor (no synchronisation): callers fold it into a device vector
+    that goes to the host anyway."""
+
+    return status_word(device)[0:1]
+
+
+def raise_for_status_code(code: int, device: torch.device | int | None = None) -> None:
+    """Raise :class:`KernelError` for a non-zero status code that the caller already holds on the host, and clear
+    the device word so that the next check starts clean."""
+
+    if int(code) != 0:
+        status_word(device)[0:1].zero_()
+        raise KernelError(f"device-side bounded wait ran out (status code {int(code)})")
 
 
 def check_status(device: torch.device | int | None = None) -> None:
     """Synchronise and raise if a kernel's bounded wait ran out since the last check."""
 
-    buf = status_word(device)
-    code = int(buf[0].item())
-    if code != 0:
-        buf.zero_()
-        raise KernelError(f"device-side bounded wait ran out (status code {code})")
+    raise_for_status_code(int(status_word(device)[0].item()), device)
 
 
 def scratch(name: str, numel: int, dtype: torch.dtype, device: torch.device) -> torch.Tensor:

@@ -64,6 +64,11 @@ class OptimizerBuildResult:
 
         return {a.name: ("muon" if a.backend == "dist_muon" else a.backend) for a in self.route_assignments}
 
+    def weight_decay_by_name(self) -> dict[str, bool]:
+        """Whether decoupled weight decay applies, per logical parameter (reference mask: optim/build.py:506-518)."""
+
+        return {a.name: a.weight_decay for a in self.route_assignments}
+
 
 def _fallback_reason(spec: OptimizerSpec, item: ParamMeta, backend: str, explicit: bool) -> str | None:
     if spec.name not in ("muon", "dion") or backend != "adamw":

@@ -160,7 +160,7 @@ class Optimizer:
         st = self.state[i]
         g = store.grad_arena[lo:hi]
         p = sec.master
-        wd = float(self.spec.weight_decay)
+        wd = float(self.spec.weight_decay) if sec.decay else 0.0      # the route's weight_decay flag
         step = self.count + 1
         separate = store.compute_dtype != torch.float32
         if p.is_cuda:

@@ -50,6 +50,7 @@ class StorageEntry:
     offset: int = 0                 # element offset inside the arenas
     numel: int = 0
     owner: int = 0                  # owning rank along shard_axis (matrix sections)
+    decay: bool = True              # AdamW entries: decoupled weight decay applies (the route's ``weight_decay`` flag)
 
     @property
     def is_expert(self) -> bool:
@@ -66,6 +67,7 @@ class Section:
     start: int = 0
     length: int = 0                 # padded so that it splits evenly over the shard axis
     owner_block: int = 0            # matrix sections: elements per owner block
+    decay: bool = True              # AdamW sections: whether weight decay applies to every element of the section
 
     def local_range(self, shard_rank: int, shard_size: int) -> tuple[int, int]:
         if self.shard_axis is None or shard_size == 1:
@@ -76,7 +78,7 @@ class Section:
 
 class ParamStore:
     def __init__(self, result: ModelBuildResult, mesh: MeshContext, *, mode: str, compute_dtype: torch.dtype,
-                 backend_of: dict[str, str], ep_axis: str | None = None):
+                 backend_of: dict[str, str], ep_axis: str | None = None, decay_of: dict[str, bool] | None = None):
         self.result = result
         self.mesh = mesh
         self.mode = mode
@@ -109,8 +111,11 @@ class ParamStore:
             shard_axis = None
             if mode in ("zero2", "fsdp") and mesh.size("fsdp") > 1 and not (is_expert and ep_axis == "fsdp"):
                 shard_axis = "fsdp"
+            decays = {bool((decay_of or {}).get(m.name, True)) for m in metas}
+            if backend == "adamw" and len(decays) != 1:
+                raise ContractError(f"logical parameters fused in {name} disagree on weight decay")
             self.entries.append(StorageEntry(name, param, metas, backend, tuple(axes), shard_axis,
-                                             numel=param.numel()))
+                                             numel=param.numel(), decay=decays.pop() if backend == "adamw" else True))
         self._layout()
         self._materialise()
 
@@ -120,11 +125,13 @@ class ParamStore:
         order = {"adamw": 0, "muon": 1, "dion2": 2, "frozen": 3}
         tp_sharded = lambda e: any(m.tp_axis is not None for m in e.metas)  # noqa: E731
         for e in sorted(self.entries, key=lambda e: (order[e.backend], e.reduce_axes, str(e.shard_axis),
-                                                     e.is_expert, tp_sharded(e))):
+                                                     e.is_expert, tp_sharded(e), not e.decay)):
             # expert and tensor-parallel-sharded parameters are disjoint across their axis, the rest is replicated:
-            # they must not share a section because norms are summed per section
-            key = (e.backend, e.reduce_axes, e.shard_axis, e.is_expert, tp_sharded(e))
-            sections.setdefault(key, Section(key, e.backend, e.reduce_axes, e.shard_axis)).entries.append(e)
+            # they must not share a section because norms are summed per section; AdamW parameters with and without
+            # weight decay get sections of their own because the kernel takes one decay per launch
+            key = (e.backend, e.reduce_axes, e.shard_axis, e.is_expert, tp_sharded(e), e.decay)
+            sections.setdefault(key, Section(key, e.backend, e.reduce_axes, e.shard_axis,
+                                             decay=e.decay)).entries.append(e)
         cursor = 0
         self.sections: list[Section] = []
         for sec in sections.values():
@@ -271,7 +278,7 @@ class ParamStore:
                     out = buf[r * per:(r + 1) * per]
                     if self.arena is not None:
                         # one kernel: pull the peers' copies of the local slice over NVLink and sum in rank order
-                        self.arena.reduce_scatter(self._grad_off + 4 * sec.start, per, channel=0)
+                        self.arena.reduce_scatter(self._grad_off + 4 * (sec.start + r * per), per, channel=0)
                     elif buf.is_cuda:
                         dist.reduce_scatter_tensor(out, buf, group=group)
                     else:

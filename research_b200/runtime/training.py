@@ -35,7 +35,7 @@ from research_b200.runtime.diagnostics import (ARTIFACT_WRITER, EXECUTION_MODE, 
 from research_b200.runtime.profiling import ProfilingManager
 from research_b200.runtime.resume import (build_resume_compat, checkpoint_metadata, validate_resume_compat,
                                           validate_resume_metadata)
-from research_b200.runtime.state_io import collect_state_tensors, load_state_tensors
+from research_b200.runtime.state_io import iter_state_tensors, load_state_tensors
 from research_b200.runtime.trainer import Trainer
 from research_b200.services.artifacts import build_artifact_writer, initialize_run, utc_now
 from research_b200.services.checkpoints import LocalCheckpointService
@@ -215,7 +215,8 @@ def _host_state(trainer: Trainer, spec: RunSpec, wall_start_ns: int) -> tuple[di
 def save_checkpoint(trainer: Trainer, spec: RunSpec, service: LocalCheckpointService, writer, index, row, eval_row,
                     reason: str, wall_start_ns: int, compat, progress: ProgressFn):
     start = time.perf_counter()
-    tensors = collect_state_tensors(trainer)      # collective: every rank participates
+    # collective: every rank takes part, the arrays are assembled on the writer only, one parameter at a time
+    tensors = iter_state_tensors(trainer, writer_only=True)
     dataset, host = _host_state(trainer, spec, wall_start_ns)
     metadata = checkpoint_metadata(spec, row, reason=reason, eval_row=eval_row, compat=compat)
     path = service.save(trainer.step, tensors, dataset, host, metadata)

@@ -1,5 +1,6 @@
-"""Checkpoint service: composite checkpoints in an Orbax-compatible directory layout, written and read without
-Orbax (neither orbax nor tensorstore can be installed offline).
+"""Checkpoint service: composite checkpoints in an Orbax-like directory layout, written and read without Orbax
+(neither orbax nor tensorstore can be installed offline).  The layout is write-compatible by construction only: it
+has not been cross-loaded by Orbax, and checkpoints that Orbax itself wrote (OCDBT + zstd by default) are not read.
 
 Layout (what the reference's ``CheckpointManager`` produces, src/jaxtitan/services/checkpoints.py:54-176;
 tests/jaxtitan/test_checkpoints.py:53)::
@@ -16,21 +17,22 @@ tests/jaxtitan/test_checkpoints.py:53)::
         metadata/metadata               JSON item
 
 Leaf key paths follow the reference's ``TrainState`` (step, tokens_seen, model.<nnx path>, opt_state..., rng...,
-moe_balance...) with model kernels in the reference's ``[in, out]`` orientation.  The reader also accepts the
-OCDBT form for inspection when every value is stored raw, but what it is tested on is its own output.
+moe_balance...) with model kernels in the reference's ``[in, out]`` orientation.  The reader reads this writer's
+output.
 Retention: keep the newest ``max_to_keep`` plus protected steps (latest / best), as the reference's
-``_ProtectedLatestPolicy`` (checkpoints.py:183-199).  Saves are synchronous and committed by renaming a temporary
-directory.
+``_ProtectedLatestPolicy`` (checkpoints.py:183-199).  Saves are synchronous: everything is written and fsynced
+in a temporary directory, an existing directory of the same step is moved aside only then, and the rename commits.
 """
 
 from __future__ import annotations
 
 import json
+import os
 import shutil
 import time
 from dataclasses import dataclass
 from pathlib import Path
-from typing import Any, Mapping
+from typing import Any, Iterable, Mapping
 
 import numpy as np
 
@@ -106,6 +108,37 @@ def read_array(leaf_dir: Path) -> np.ndarray:
     return np.fromfile(path, dtype=dtype).reshape(shape)
 
 
+def _fsync_dir(path: Path) -> None:
+    try:
+        fd = os.open(path, os.O_RDONLY)
+    except OSError:
+        return
+    try:
+        os.fsync(fd)
+    except OSError:
+        pass
+    finally:
+        os.close(fd)
+
+
+def _fsync_tree(root: Path) -> None:
+    """Flush every file and directory under ``root`` so that the rename that follows commits complete data."""
+
+    for dirpath, _, files in os.walk(root):
+        for name in files:
+            try:
+                fd = os.open(os.path.join(dirpath, name), os.O_RDONLY)
+            except OSError:
+                continue
+            try:
+                os.fsync(fd)
+            except OSError:
+                pass
+            finally:
+                os.close(fd)
+        _fsync_dir(Path(dirpath))
+
+
 class LocalCheckpointService:
     ITEMS = ("train", "dataset", "host", "metadata")
 
@@ -122,24 +155,31 @@ class LocalCheckpointService:
             self.checkpoints_dir.mkdir(parents=True, exist_ok=True)
 
     # ---- save ----------------------------------------------------------------------------------------
-    def save(self, step: int, tensors: Mapping[str, np.ndarray], dataset_state: Mapping[str, Any],
-             host_state: Mapping[str, Any], metadata: Mapping[str, Any]) -> Path:
+    def save(self, step: int, tensors: "Mapping[str, np.ndarray] | Iterable[tuple[str, np.ndarray | None]]",
+             dataset_state: Mapping[str, Any], host_state: Mapping[str, Any], metadata: Mapping[str, Any]) -> Path:
+        """``tensors``: a mapping, or an iterable of ``(leaf name, array)`` pairs that is consumed leaf by leaf (so
+        that a producer which gathers one parameter at a time never holds the whole state).  Ranks that do not write
+        still drain the iterable, because producing it may be a collective operation."""
+
         if step < 0:
             raise ContractError(f"checkpoint step must be non-negative, got {step}")
         if host_state.get("dataset") != dict(dataset_state):
             raise ContractError("host_state.dataset must match dataset_state when saving a checkpoint")
         final = self.checkpoints_dir / step_dir_name(step)
+        pairs = tensors.items() if hasattr(tensors, "items") else tensors
         if not self.is_writer:
+            for _ in pairs:
+                pass
             return final
         tmp = self.checkpoints_dir / f"{step_dir_name(step)}.orbax-checkpoint-tmp-{int(time.time() * 1e6)}"
-        if final.exists():
-            shutil.rmtree(final)
         try:
             train = tmp / "train"
             train.mkdir(parents=True)
             tree_meta = {}
-            for name, value in tensors.items():
+            names = []
+            for name, value in pairs:
                 arr = np.asarray(value)
+                names.append(name)
                 write_array(train / name, arr)
                 tree_meta[name] = {"key_metadata": [{"key": part, "key_type": 2} for part in name.split(".")],
                                    "value_metadata": {"value_type": "jax.Array", "skip_deserialize": False,
@@ -147,7 +187,7 @@ class LocalCheckpointService:
             (train / "_METADATA").write_text(json.dumps({"tree_metadata": tree_meta, "use_zarr3": False,
                                                          "store_array_data_equal_to_fill_value": True}, sort_keys=True))
             (train / "_sharding").write_text(json.dumps({name: {"sharding_type": "SingleDeviceSharding"}
-                                                         for name in tensors}, sort_keys=True))
+                                                         for name in names}, sort_keys=True))
             for item, payload in (("dataset", dataset_state), ("host", host_state), ("metadata", metadata)):
                 (tmp / item).mkdir()
                 (tmp / item / "metadata").write_text(canonical_json(payload))
@@ -158,7 +198,15 @@ class LocalCheckpointService:
                                   "metadata": "orbax.checkpoint._src.handlers.json_checkpoint_handler.JsonCheckpointHandler"},
                 "init_timestamp_nsecs": time.time_ns(), "commit_timestamp_nsecs": time.time_ns(),
                 "writer": "research_b200"}, sort_keys=True))
+            _fsync_tree(tmp)
+            old = None
+            if final.exists():           # same step saved again: the old copy goes only once the new one is complete
+                old = self.checkpoints_dir / f"{step_dir_name(step)}.replaced-{int(time.time() * 1e6)}"
+                final.replace(old)
             tmp.replace(final)
+            _fsync_dir(self.checkpoints_dir)
+            if old is not None:
+                shutil.rmtree(old, ignore_errors=True)
         except Exception:
             shutil.rmtree(tmp, ignore_errors=True)
             raise

@@ -182,6 +182,10 @@ class TrainStep:
         grad_scale = 1.0 / global_count
         dp_world = mesh.size("data") * mesh.size("fsdp") * mesh.size("cp")
         self.store.zero_grads()
+        if self.device.type == "cuda":
+            from research_b200.parallel.symmetric import align_ranks
+
+            align_ranks()      # absorbs host skew between ranks before the first peer-memory kernel of the step
         staged = self.stager.stage(batches[0], rows, cols, 0)
         ce_sums, z_sums, aux_vals = [], [], []
         all_stats = []
@@ -216,9 +220,21 @@ class TrainStep:
         router_payload = self._router_metrics(all_stats) if all_stats and all_stats[0] else {}
         router_keys = sorted(k for k, v in router_payload.items() if torch.is_tensor(v) and v.dim() == 0)
         extras += [router_payload[k].reshape(1).float() for k in router_keys]
+        # the kernels' status word (a bounded wait that gave up) rides along: max over all ranks, checked every step
+        status = None
+        if self.device.type == "cuda":
+            from research_b200.ops import native
+
+            status = native.status_code_tensor(self.device).float()
+            if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+                status = status.clone()
+                dist.all_reduce(status, op=dist.ReduceOp.MAX)
+            extras.append(status)
         flat = torch.cat([packed] + extras)
         host = flat.detach().cpu().tolist()
         self.d2h_bytes[0] += flat.numel() * 4
+        if status is not None:
+            native.raise_for_status_code(int(host.pop()), self.device)
         ce_host, z_host = host[:mb], host[mb:2 * mb]
         pos = 2 * mb
         aux_host = None

@@ -52,30 +52,52 @@ sys.path.insert(0, sys.argv[1])
 from research_b200.ops import native
 from research_b200.parallel.symmetric import SymmetricArena
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+want_mc = sys.argv[2] == "nvls"
 torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
 dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
 n = 1 << 20
-arena = SymmetricArena(dist.group.WORLD, world * n * 4 + world * n * 2 + 4096)
+arena = SymmetricArena(dist.group.WORLD, world * n * 4 + world * n * 2 + 4096, multicast=want_mc)
+if want_mc:
+    assert arena.mc_ptr != 0, "the arena was not bound to a multicast object"
 grads, g_off = arena.carve(world * n, torch.float32)
 weights, w_off = arena.carve(world * n, torch.bfloat16)
+modes = [False, True] if want_mc else [False]          # plain peer loads, then multimem through the switch
 for it in range(3):
+  for nvls in modes:
     torch.manual_seed(100 * it + rank)
     grads.copy_(torch.randn(world * n, device="cuda"))
     ref = grads.clone()
     dist.all_reduce(ref)
     ref = ref[rank * n:(rank + 1) * n] * 0.5
     sumsq = torch.zeros(1, device="cuda")
-    arena.reduce_scatter(g_off, n, scale=0.5, sumsq=sumsq)
+    arena.reduce_scatter(g_off + 4 * rank * n, n, scale=0.5, sumsq=sumsq, nvls=nvls)
     native.check_status()
     got = grads[rank * n:(rank + 1) * n]
-    assert torch.allclose(got, ref, atol=1e-5, rtol=1e-5), (got - ref).abs().max().item()
+    assert torch.allclose(got, ref, atol=1e-5, rtol=1e-5), (nvls, (got - ref).abs().max().item())
     assert abs(sumsq.item() - ref.double().pow(2).sum().item()) <= 1e-3 * ref.double().pow(2).sum().item()
     weights.zero_()
     weights[rank * n:(rank + 1) * n] = (rank + 1 + it)
-    arena.all_gather(w_off, n * 2)
+    arena.all_gather(w_off, n * 2, nvls=nvls)
     native.check_status()
     want = torch.arange(1, world + 1, device="cuda").repeat_interleave(n).to(torch.bfloat16) + it
-    assert torch.equal(weights, want)
+    assert torch.equal(weights, want), nvls
+# slices of different sizes per rank (rank 0 owns nothing), a capped grid, a side stream: the shape of the
+# bucketed reduction that overlaps the backward pass
+side = torch.cuda.Stream()
+for nvls in modes:
+    torch.manual_seed(7 + rank)
+    grads.copy_(torch.randn(world * n, device="cuda"))
+    ref = grads.clone()
+    dist.all_reduce(ref)
+    sizes = [4096 * r for r in range(world)]
+    starts = [sum(sizes[:r]) for r in range(world)]
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        arena.reduce_scatter(g_off + 4 * starts[rank], sizes[rank], nvls=nvls, max_ctas=16, channel=6)
+    torch.cuda.current_stream().wait_stream(side)
+    native.check_status()
+    a, b = starts[rank], starts[rank] + sizes[rank]
+    assert torch.allclose(grads[a:b], ref[a:b], atol=1e-5, rtol=1e-5), nvls
 arena.check_canaries()                      # nothing wrote past the end of a buffer, here or from a peer
 torch.cuda.synchronize()
 dist.barrier()
@@ -86,15 +108,21 @@ print("RANK_OK", rank)
 
 
 @pytest.mark.gpu
-def test_symmetric_arena_collectives_on_all_visible_gpus(tmp_path):
+@pytest.mark.parametrize("transport", ["peer", "nvls"])
+def test_symmetric_arena_collectives_on_all_visible_gpus(tmp_path, transport):
+    """``peer``: plain loads from the peers' arenas.  ``nvls``: the arena is bound to an NVLink multicast object
+    and the same collectives also run as ``multimem.ld_reduce`` / ``multimem.st``.  Every rank runs to the end and
+    closes the arena (unbinding it) before it exits."""
+
     world = min(torch.cuda.device_count(), 4)
     if world < 2:
         pytest.skip("needs at least two GPUs")
     script = tmp_path / "arena_ranks.py"
     script.write_text(_GPU_SCRIPT)
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    port = "29731" if transport == "peer" else "29732"
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
-           "--master-addr", "127.0.0.1", "--master-port", "29731", str(script), str(ROOT)]
+           "--master-addr", "127.0.0.1", "--master-port", port, str(script), str(ROOT), transport]
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     assert proc.stdout.count("RANK_OK") == world
@@ -291,11 +319,15 @@ def test_bounded_peer_wait_times_out_with_a_status_code():
     blocks = torch.zeros(2, nbytes, dtype=torch.uint8, device="cuda")      # flag blocks of "rank 0" and "rank 1"
     flags = (ctypes.c_void_p * 2)(blocks[0].data_ptr(), blocks[1].data_ptr())
     native.check_status()
+    native.set_peer_wait_limit_ms(1500)                                     # training default: 30 s
     t0 = time.perf_counter()
-    rc = lib.b200c_barrier(flags, 2, 0, 7, native.status_word().data_ptr(), native._stream())
-    assert rc == 0
-    with pytest.raises(KernelError, match="status code 21"):                # ERR_PEER_READY
-        native.check_status()
+    try:
+        rc = lib.b200c_barrier(flags, 2, 0, 7, native.status_word().data_ptr(), native._stream())
+        assert rc == 0
+        with pytest.raises(KernelError, match="status code 21"):            # ERR_PEER_READY
+            native.check_status()
+    finally:
+        native.set_peer_wait_limit_ms(native.peer_wait_limit_ms())
     waited = time.perf_counter() - t0
     assert 1.0 < waited < 10.0, waited
     # the announcement this rank made is in the peer's block, and the device still works

@@ -4,7 +4,9 @@ Some hosts that load the kernel library may not allocate device memory (their me
 do not own, or they run where cudaMalloc is forbidden).  ``b200_attn_bwd_noalloc`` serves them by keeping the
 backward pass's ``delta`` scratch in a fixed array inside the library.  This test checks, on two calls in a
 row (the array is shared and keeps the previous call's contents), that it produces what the ordinary entry
-point produces, and that oversize problems are refused.  The file name makes pytest collect it last.
+point produces and what an fp32 restatement of attention gives through autograd, that the call leaves the amount
+of device memory in use unchanged (the property it exists for), and that oversize problems are refused.  The
+file name makes pytest collect it last.
 """
 
 import ctypes
@@ -31,12 +33,27 @@ def _symbol():
     return fn
 
 
-def _call(fn, q, k, v, o, d_o, lse, causal):
+def _fp32_oracle(q, k, v, d_o, causal):
+    """Gradients of a plain fp32 attention (GQA by repeating K/V heads) through autograd."""
+
+    B, S, Hq, D = q.shape
+    g = Hq // k.shape[2]
+    qf, kf, vf = (t.float().detach().requires_grad_(True) for t in (q, k, v))
+    s = torch.einsum("bqhd,bkhd->bhqk", qf, kf.repeat_interleave(g, dim=2)) * D ** -0.5
+    if causal:
+        idx = torch.arange(S, device=q.device)
+        s = s.masked_fill(idx[None, None, :, None] < idx[None, None, None, :], float("-inf"))
+    o = torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, dim=-1), vf.repeat_interleave(g, dim=2))
+    o.backward(d_o.float())
+    return qf.grad, kf.grad, vf.grad
+
+
+def _call(fn, q, k, v, o, d_o, lse, causal, outs=None):
     from research_b200.ops import native
 
     B, S, Hq, D = q.shape
     Hkv = k.shape[2]
-    dq, dk, dv = torch.zeros_like(q), torch.zeros_like(k), torch.zeros_like(v)
+    dq, dk, dv = outs if outs is not None else (torch.zeros_like(q), torch.zeros_like(k), torch.zeros_like(v))
     rc = fn(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), d_o.data_ptr(), lse.data_ptr(), dq.data_ptr(),
             dk.data_ptr(), dv.data_ptr(), None, None, B, S, Hq, Hkv, D, q.stride(1), q.stride(0), k.stride(1),
             k.stride(0), v.stride(1), v.stride(0), o.stride(1), o.stride(0), d_o.stride(1), d_o.stride(0),
@@ -55,13 +72,27 @@ def test_noalloc_matches_regular_entry_point_twice():
         d_o = _bf((B, S, Hq, D), seed + 30, 0.5)
         o, lse = native.attn_fwd(q, k, v, causal=True)
         ref = native.attn_bwd(q, k, v, o, d_o, lse, causal=True)
-        rc, dq, dk, dv = _call(fn, q, k, v, o, d_o, lse, True)
+        oracle = _fp32_oracle(q, k, v, d_o, True)
+        outs = (torch.zeros_like(q), torch.zeros_like(k), torch.zeros_like(v))
+        if call == 0:
+            # the first call on a device may load kernel images and looks up the scratch array's address:
+            # run it once before memory is measured
+            assert _call(fn, q, k, v, o, d_o, lse, True)[0] == 0
+        torch.cuda.synchronize()
+        free_before, torch_before = torch.cuda.mem_get_info()[0], torch.cuda.memory_reserved()
+        rc, dq, dk, dv = _call(fn, q, k, v, o, d_o, lse, True, outs)
+        torch.cuda.synchronize()
+        free_after, torch_after = torch.cuda.mem_get_info()[0], torch.cuda.memory_reserved()
         assert rc == 0, (call, rc)
+        assert free_after == free_before and torch_after == torch_before, (free_before, free_after)
         native.check_status()
-        for name, got, want in zip(("dq", "dk", "dv"), (dq, dk, dv), ref):
+        for name, got, want, exact in zip(("dq", "dk", "dv"), (dq, dk, dv), ref, oracle):
             err = (got.float() - want.float()).abs().max().item()
             scale = want.float().abs().max().item()
             assert err <= 2e-2 * scale + 2e-2, (call, name, err, scale)
+            err = (got.float() - exact).abs().max().item()
+            scale = exact.abs().max().item()
+            assert err <= 2e-2 * scale + 2e-2, (call, name, "fp32 oracle", err, scale)
 
 
 def test_noalloc_rejects_oversize_problem():
