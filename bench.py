@@ -12,6 +12,11 @@ over K optimizer steps whose host batches were prepared beforehand; ``e2e`` time
 the pinned host->device copy of every step's tokens and the device->host read of the step's loss.
 
 ``--impl reference`` runs the unmodified reference from ``baseline/_ref`` when it can be imported there.
+``--impl library`` runs the same model, data, optimizer and mesh of THIS package on stock PyTorch operators only
+(cuBLAS matmuls, ``scaled_dot_product_attention``, plain tensor ops in the optimizer, NCCL collectives; none of this
+package's kernels): the stand-in for an "NCCL + cuBLAS build" on the same box.  The native line carries that
+comparison measured in the same process under ``vs_library`` (``--no-library`` skips it), and at one GPU a
+``decode`` record (batch 32, prompt 2048, 256 new tokens, temperature 1.0, top-k 50; ``--no-decode`` skips it).
 """
 
 from __future__ import annotations
@@ -181,7 +186,9 @@ def main() -> int:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--impl", default="native", choices=["native", "reference", "library"])
+    ap.add_argument("--no-library", action="store_true", help="native arm: skip the in-process library comparison")
+    ap.add_argument("--no-decode", action="store_true", help="native arm: skip the generation record (1 GPU only)")
     ap.add_argument("--per-gpu-batch", type=int, default=8)
     ap.add_argument("--seq-len", type=int, default=None)
     ap.add_argument("--optimizer", default=None, choices=["muon", "adamw", "dion"])
@@ -194,6 +201,11 @@ def main() -> int:
         args.optimizer = args.optimizer or "muon"
     if args.impl == "reference":
         return reference_arm(args)
+    if args.impl == "library":
+        os.environ["RESEARCH_B200_LIBRARY"] = "1"
+        os.environ["RESEARCH_B200_PEER_COLLECTIVES"] = "0"
+
+    import gc
 
     import numpy as np
     import torch
@@ -234,7 +246,6 @@ def main() -> int:
                                    overwrite=True)
     if world > 1:
         dist.barrier()
-    trainer = Trainer(spec)
     tokens_per_step = gb * args.seq_len
 
     def sync():
@@ -242,40 +253,84 @@ def main() -> int:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(W):
-        trainer.train_step()
-    native.check_status()
-    # ---- device-timed region: batches prepared on the host beforehand ------------------------------
-    prepared = [trainer.next_accumulated_batch() for _ in range(K)]
-    sampler = ClockSampler(local_rank)
-    sync()
-    sampler.start()
-    launches0 = native.LAUNCHES
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    last = None
-    for batches in prepared:
-        last = trainer.train_on(batches)
-    end.record()
-    sync()
-    launches = native.LAUNCHES - launches0
-    dev_ms = start.elapsed_time(end)
-    # ---- end-to-end region through the public API ---------------------------------------------------
-    h2d0, d2h0 = trainer.train_step_fn.h2d_bytes[0], trainer.train_step_fn.d2h_bytes[0]
-    sync()
-    t0 = time.perf_counter()
-    for _ in range(K):
-        last = trainer.train_step()
-    sync()
-    e2e_s = time.perf_counter() - t0
-    clocks = sampler.stop()
-    native.check_status()
-    h2d = (trainer.train_step_fn.h2d_bytes[0] - h2d0) / K
-    d2h = (trainer.train_step_fn.d2h_bytes[0] - d2h0) / K
-    times = torch.tensor([dev_ms, e2e_s * 1e3], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    dev_ms, e2e_ms = times.tolist()
+    def measure(label: str) -> dict:
+        """Build a trainer, warm up, then the device-timed region and the end-to-end region of one arm."""
+
+        trainer = Trainer(spec)
+        for _ in range(W):
+            trainer.train_step()
+        native.check_status()
+        # ---- device-timed region: batches prepared on the host beforehand --------------------------
+        prepared = [trainer.next_accumulated_batch() for _ in range(K)]
+        sampler = ClockSampler(local_rank)
+        sync()
+        sampler.start()
+        launches0 = native.LAUNCHES
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        last = None
+        for batches in prepared:
+            last = trainer.train_on(batches)
+        end.record()
+        sync()
+        launches = native.LAUNCHES - launches0
+        dev_ms = start.elapsed_time(end)
+        # ---- end-to-end region through the public API -----------------------------------------------
+        h2d0, d2h0 = trainer.train_step_fn.h2d_bytes[0], trainer.train_step_fn.d2h_bytes[0]
+        sync()
+        t0 = time.perf_counter()
+        for _ in range(K):
+            last = trainer.train_step()
+        sync()
+        e2e_s = time.perf_counter() - t0
+        clocks = sampler.stop()
+        native.check_status()
+        h2d = (trainer.train_step_fn.h2d_bytes[0] - h2d0) / K
+        d2h = (trainer.train_step_fn.d2h_bytes[0] - d2h0) / K
+        times = torch.tensor([dev_ms, e2e_s * 1e3], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(times, op=dist.ReduceOp.MAX)
+        dev_ms, e2e_ms = times.tolist()
+        out = {"label": label, "dev_ms": dev_ms, "e2e_ms": e2e_ms, "h2d": h2d, "d2h": d2h, "launches": launches,
+               "clocks": clocks, "loss": None if last is None else round(last.loss, 4),
+               "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 2)}
+        trainer.close()
+        del trainer, prepared
+        gc.collect()
+        torch.cuda.empty_cache()
+        torch.cuda.reset_peak_memory_stats()
+        return out
+
+    from research_b200.ops import functional as Fn
+
+    arm = measure(args.impl)
+    library = None
+    if args.impl == "native" and not args.no_library:
+        # the same spec on stock PyTorch operators and NCCL, in this process, right after the native arm
+        Fn.set_library_mode(True)
+        os.environ["RESEARCH_B200_PEER_COLLECTIVES"] = "0"
+        try:
+            library = measure("library")
+        except Exception as exc:  # noqa: BLE001 - the comparison must never take the headline down with it
+            library = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+        finally:
+            Fn.set_library_mode(False)
+            os.environ.pop("RESEARCH_B200_PEER_COLLECTIVES", None)
+    decode = None
+    if args.impl == "native" and world == 1 and headline and not args.no_decode:
+        from research_b200.runtime.inference_bench import run_inference_bench
+
+        try:
+            rec = run_inference_bench(spec, batch=32, prompt=2048, new_tokens=256, temperature=1.0, top_k=50,
+                                      warmup=1, repeats=3)
+            decode = {k: (round(v, 3) if isinstance(v, float) else v) for k, v in rec.items()
+                      if k in ("metric", "value", "unit", "decode_ms_per_step", "prefill_ms", "prefill_tokens_per_sec",
+                               "ttft_ms", "batch", "prompt_tokens", "new_tokens", "temperature", "top_k", "cuda_graph")}
+            decode["timing"] = "wall clock between synchronizes, median of 3 runs after 1 warm-up run"
+        except Exception as exc:  # noqa: BLE001
+            decode = {"error": f"{type(exc).__name__}: {exc}"[:300]}
+    dev_ms, e2e_ms, h2d, d2h, launches, clocks = (arm["dev_ms"], arm["e2e_ms"], arm["h2d"], arm["d2h"],
+                                                  arm["launches"], arm["clocks"])
     value = tokens_per_step * K / (dev_ms * 1e-3)
     e2e_value = tokens_per_step * K / (e2e_ms * 1e-3)
     fpt = estimate_flops_per_token(spec.model, args.seq_len)
@@ -286,7 +341,7 @@ def main() -> int:
             "metric": "train_tokens_per_sec", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world,
             "steps": K, "warmup": W, "ms_per_step": round(dev_ms / K, 3), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "impl": "native",
+            "impl": args.impl,
             "config": {"model": model_desc, "workload": args.workload,
                        "global_batch": gb, "seq_len": args.seq_len, "parallelism": parallelism,
                        "optimizer": args.optimizer, "grad_accum": 1,
@@ -298,10 +353,25 @@ def main() -> int:
             "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms / K, 3),
                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)},
             "gpu_launches": int(launches), "clocks": clocks,
-            "final_loss": None if last is None else round(last.loss, 4),
+            "final_loss": arm["loss"], "peak_mem_gb": arm["peak_mem_gb"],
             "baseline_note": "the reference publishes no B200 number and no number for this config; nearest published: "
                              "dense 1.666B FSDP2xTP2 Muon 8,136 tok/s on 4xH100",
         }
+        if library is not None:
+            if "error" in library:
+                out["vs_library"] = library
+            else:
+                lib_value = tokens_per_step * K / (library["dev_ms"] * 1e-3)
+                lib_e2e = tokens_per_step * K / (library["e2e_ms"] * 1e-3)
+                out["vs_library"] = {
+                    "what": "same spec on stock PyTorch operators (cuBLAS, scaled_dot_product_attention, tensor-op "
+                            "optimizer) and NCCL, same process, same timing; not the reference",
+                    "value": round(lib_value, 1), "ms_per_step": round(library["dev_ms"] / K, 3),
+                    "ratio": round(value / lib_value, 3), "e2e_value": round(lib_e2e, 1),
+                    "e2e_ratio": round(e2e_value / lib_e2e, 3), "gpu_launches": int(library["launches"]),
+                    "clocks": library["clocks"], "final_loss": library["loss"], "peak_mem_gb": library["peak_mem_gb"]}
+        if decode is not None:
+            out["decode"] = decode
         print(json.dumps(out))
     if world > 1:
         dist.barrier()

@@ -252,6 +252,9 @@ class TransformerLM(nn.Module):
         self.lm_head = None if spec.tied_embeddings else nn.Parameter(
             torch.empty(self.vocab_local, H, dtype=torch.float32))
         self.compute_dtype = torch.float32
+        # called with a layer index once every kernel of that layer's backward pass has been issued (the parameter
+        # store starts that layer's gradient reduction from it); set per forward pass by the training step
+        self.layer_backward_hook = None
 
     # ---- helpers ---------------------------------------------------------------------------------
     def head_weight(self) -> torch.Tensor:
@@ -296,7 +299,11 @@ class TransformerLM(nn.Module):
         aux_all: list[AuxLoss] = []
         stats_all: list[RouterStats] = []
         remat = self.spec.remat == "block" and torch.is_grad_enabled()
-        for layer in self.layers:
+        hook = self.layer_backward_hook if torch.is_grad_enabled() else None
+        for index, layer in enumerate(self.layers):
+            if hook is not None and x.requires_grad:
+                # the gradient of a layer's input is the last thing its backward pass produces
+                x.register_hook(lambda grad, index=index, hook=hook: hook(index))
             if remat:
                 x, delta, aux, stats = checkpoint(layer, x, delta, inp, ex, use_reentrant=False)
             else:

@@ -13,6 +13,7 @@ exist on the GPU path.  On the reference path ordinary autograd populates ``.gra
 from __future__ import annotations
 
 import math
+import os
 from contextlib import contextmanager
 
 import torch
@@ -20,7 +21,29 @@ import torch.nn.functional as F
 
 from research_b200.ops import native
 
-_FORCE_REFERENCE = False
+# RESEARCH_B200_LIBRARY=1 runs the whole stack on stock PyTorch operators (cuBLAS matmuls, the library's
+# scaled_dot_product_attention, plain tensor ops in the optimizer, NCCL collectives): the comparison arm of the
+# benchmark.  None of this package's kernels runs in that mode.
+_LIBRARY = os.environ.get("RESEARCH_B200_LIBRARY", "0") == "1"
+_FORCE_REFERENCE = _LIBRARY
+
+
+def library_mode() -> bool:
+    return _LIBRARY
+
+
+def set_library_mode(enabled: bool) -> None:
+    """Switch library mode for objects built after this call (the benchmark's comparison arm)."""
+
+    global _LIBRARY, _FORCE_REFERENCE
+    _LIBRARY = bool(enabled)
+    _FORCE_REFERENCE = bool(enabled)
+
+
+def native_enabled() -> bool:
+    """False while the plain PyTorch implementations are forced (library mode, ``reference_mode``)."""
+
+    return not _FORCE_REFERENCE
 
 
 @contextmanager
@@ -266,7 +289,28 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, causal: bool
         if lo is not None and hi is None:
             hi = native.kv_visibility_upper_bound(lo)
         return _AttentionFn.apply(q, k, v, lo, hi, causal, scale)
+    if _LIBRARY and q.is_cuda:
+        return attention_library(q, k, v, causal=causal, lo=lo, scale=scale)
     return attention_reference(q, k, v, causal=causal, lo=lo, scale=scale)
+
+
+def attention_library(q, k, v, *, causal: bool, lo: torch.Tensor | None, scale: float) -> torch.Tensor:
+    """The same attention through ``torch.nn.functional.scaled_dot_product_attention`` (grouped-query form): causal
+    flag when there is no document mask, else a boolean ``[B, 1, S, Sk]`` mask built from the per-row bounds."""
+
+    B, S, Hq, D = q.shape
+    Sk = k.shape[1]
+    qt, kt, vt = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+    if lo is None:
+        o = F.scaled_dot_product_attention(qt, kt, vt, is_causal=causal and S == Sk, scale=scale, enable_gqa=True)
+        return o.transpose(1, 2)
+    qi = torch.arange(S, device=q.device) + (Sk - S)
+    ki = torch.arange(Sk, device=q.device)
+    allowed = ki[None, None, None, :] >= lo.long()[:, None, :, None]
+    if causal:
+        allowed = allowed & (qi[None, None, :, None] >= ki[None, None, None, :])
+    o = F.scaled_dot_product_attention(qt, kt, vt, attn_mask=allowed, scale=scale, enable_gqa=True)
+    return o.transpose(1, 2)
 
 
 class _AttentionBlockFn(torch.autograd.Function):

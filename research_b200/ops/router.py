@@ -36,8 +36,14 @@ def _lib():
     return lib
 
 
+def _native_enabled() -> bool:
+    from research_b200.ops import functional as Fn
+
+    return Fn.native_enabled()
+
+
 def native_route_ok(logits: torch.Tensor, num_experts: int, top_k: int) -> bool:
-    return (logits.is_cuda and native.available() and logits.dtype in (torch.bfloat16, torch.float32)
+    return (logits.is_cuda and native.available() and _native_enabled() and logits.dtype in (torch.bfloat16, torch.float32)
             and num_experts <= MAX_EXPERTS and top_k <= MAX_TOP_K)
 
 
@@ -127,7 +133,8 @@ def load_statistics_reference(expert_ids: torch.Tensor, weights: torch.Tensor, n
 def load_statistics(expert_ids: torch.Tensor, weights: torch.Tensor, num_experts: int):
     """(counts [E], importance [E], total, mean, min, max, max violation, entropy), all fp32 device tensors."""
 
-    if not (expert_ids.is_cuda and native.available() and num_experts <= MAX_EXPERTS and expert_ids.numel() > 0):
+    if not (expert_ids.is_cuda and native.available() and _native_enabled() and num_experts <= MAX_EXPERTS
+            and expert_ids.numel() > 0):
         return load_statistics_reference(expert_ids, weights, num_experts)
     lib = _lib()
     ids = expert_ids.reshape(-1).to(torch.int32).contiguous()
@@ -161,7 +168,7 @@ class SmebuKernelState:
 
 
 def smebu_native_ok(counts: torch.Tensor, biases, momenta) -> bool:
-    return (counts.is_cuda and native.available()
+    return (counts.is_cuda and native.available() and _native_enabled()
             and all(t.is_cuda and t.dtype == torch.float32 and t.is_contiguous() for t in (*biases, *momenta)))
 
 

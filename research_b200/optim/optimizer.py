@@ -23,6 +23,7 @@ import torch.distributed as dist
 
 from research_b200.errors import ContractError
 from research_b200.models.build import ROUTED_EXPERT_TAGS
+from research_b200.ops import functional as Fn
 from research_b200.ops import native
 from research_b200.optim import orthogonalize as orth
 from research_b200.optim.build import ADAMW_B1, ADAMW_B2, ADAMW_EPS, OptimizerBuildResult
@@ -32,7 +33,7 @@ from research_b200.parallel.sharding import ParamStore, Section, StorageEntry
 def _sumsq(x: torch.Tensor, out: torch.Tensor, index: int) -> None:
     if x.numel() == 0:
         return
-    if x.is_cuda and x.dtype in (torch.float32, torch.bfloat16) and x.is_contiguous():
+    if x.is_cuda and x.dtype in (torch.float32, torch.bfloat16) and x.is_contiguous() and Fn.native_enabled():
         native.sumsq(x.reshape(-1), out[index:index + 1], accumulate=True)
     else:
         out[index] += x.float().pow(2).sum()
@@ -163,7 +164,7 @@ class Optimizer:
         wd = float(self.spec.weight_decay) if sec.decay else 0.0      # the route's weight_decay flag
         step = self.count + 1
         separate = store.compute_dtype != torch.float32
-        if p.is_cuda:
+        if p.is_cuda and Fn.native_enabled():
             shadow = store.compute_arena[lo:hi] if separate else None
             native.adamw(p, st["mu"], st["nu"], g, shadow, self._clip, lr, ADAMW_B1, ADAMW_B2, ADAMW_EPS, wd, step)
             return
@@ -178,7 +179,8 @@ class Optimizer:
 
     # ---- matrix optimizers -------------------------------------------------------------------------
     def _fast_muon_ok(self) -> bool:
-        return self.store.device.type == "cuda" and self.store.compute_dtype == torch.bfloat16
+        return (self.store.device.type == "cuda" and self.store.compute_dtype == torch.bfloat16 and
+                Fn.native_enabled())
 
     def _muon_section_fast(self, i: int, sec: Section, entries: list[StorageEntry], lr: float) -> list[StorageEntry]:
         """Batched Muon: logical matrices of equal shape are stacked so that each Newton-Schulz step is three

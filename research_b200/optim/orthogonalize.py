@@ -33,7 +33,10 @@ DION2_POLAR_EXPRESS_COEFFICIENTS = (
 
 
 def _native_ok(x: torch.Tensor) -> bool:
-    return x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and x.shape[-2] % 8 == 0
+    from research_b200.ops import functional as Fn
+
+    return (x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and x.shape[-2] % 8 == 0 and
+            Fn.native_enabled())
 
 
 def _iterate(x: torch.Tensor, coefficients) -> torch.Tensor:

@@ -17,9 +17,9 @@ Sections group parameters that share an optimizer backend and the same set of gr
 
 from __future__ import annotations
 
-import os
-
 import math
+import os
+import re
 from dataclasses import dataclass, field
 from typing import Any
 
@@ -31,6 +31,15 @@ from research_b200.models.build import NORM_TAGS, ROUTED_EXPERT_TAGS, ModelBuild
 from research_b200.parallel.mesh import MeshContext
 
 ALIGN = 256  # elements; keeps every parameter 512-byte (bf16) / 1 KiB (fp32) aligned inside the arenas
+BUCKET_CHANNEL = 6          # flag channel of the bucketed gradient reduction that overlaps the backward pass
+_LAYER_RE = re.compile(r"(?:^|\.)layers\.(\d+)\.")
+
+
+def layer_of(name: str) -> int:
+    """Index of the transformer block a parameter belongs to, or -1 (embedding, final norm, lm_head)."""
+
+    m = _LAYER_RE.search(name)
+    return int(m.group(1)) if m else -1
 
 
 def _ceil_to(n: int, m: int) -> int:
@@ -68,6 +77,10 @@ class Section:
     length: int = 0                 # padded so that it splits evenly over the shard axis
     owner_block: int = 0            # matrix sections: elements per owner block
     decay: bool = True              # AdamW sections: whether weight decay applies to every element of the section
+    # matrix sections split over owners: layer -> element range of that layer's matrices inside THIS rank's owner
+    # block (entries of a block are laid out in backward order, so every layer is one contiguous range)
+    bucket_ranges: dict = field(default_factory=dict)
+    bucket_layers: tuple = ()       # all layers that have matrices in this section, in backward order (every rank)
 
     def local_range(self, shard_rank: int, shard_size: int) -> tuple[int, int]:
         if self.shard_axis is None or shard_size == 1:
@@ -148,11 +161,19 @@ class ParamStore:
                     e.owner = owner
                 sizes = [sum(_ceil_to(e.numel, ALIGN) for e in b) for b in blocks]
                 sec.owner_block = _ceil_to(max(sizes) if sizes else 0, ALIGN)
+                me = self.mesh.coord(sec.shard_axis)
                 for owner, b in enumerate(blocks):
                     off = sec.start + owner * sec.owner_block
-                    for e in b:
+                    # backward order inside a block: the gradients of a layer become final together, and the
+                    # reduction of that contiguous range can start while earlier layers are still in backward
+                    for e in sorted(b, key=lambda e: (-layer_of(e.name), e.name)):
                         e.offset = off
+                        if owner == me:
+                            lo_hi = sec.bucket_ranges.get(layer_of(e.name))
+                            end = off + _ceil_to(e.numel, ALIGN)
+                            sec.bucket_ranges[layer_of(e.name)] = (off, end) if lo_hi is None else (lo_hi[0], end)
                         off += _ceil_to(e.numel, ALIGN)
+                sec.bucket_layers = tuple(sorted({layer_of(e.name) for e in sec.entries}, reverse=True))
                 sec.length = sec.owner_block * n_shard
             else:
                 off = sec.start
@@ -198,6 +219,12 @@ class ParamStore:
         else:
             self.compute_arena = torch.zeros(self.total, dtype=self.compute_dtype, device=dev)
             self.grad_arena = torch.zeros(self.total, dtype=torch.float32, device=dev)
+        # bucketed reduction on a side stream (see begin_backward_overlap)
+        self._overlap = (self.arena is not None and os.environ.get("RESEARCH_B200_OVERLAP_REDUCE", "1") != "0")
+        self._comm_stream = torch.cuda.Stream(dev, priority=-1) if self._overlap else None
+        self._bucket_ctas = int(os.environ.get("RESEARCH_B200_REDUCE_CTAS", "48"))
+        self._pending: list[tuple[Section, int]] = []
+        self._armed = False
         separate_master = self.compute_dtype != torch.float32
         for sec in self.sections:
             lo, hi = self.local_master_range(sec)
@@ -261,11 +288,58 @@ class ParamStore:
                 e.param.main_grad.add_(g.to(torch.float32))
                 e.param.grad = None
 
+    # ---- bucketed reduction that overlaps the backward pass ----------------------------------------------
+    def _bucketed(self, sec: Section) -> bool:
+        return (self._overlap and sec.backend in ("muon", "dion2") and sec.shard_axis is not None and
+                sec.shard_axis in sec.reduce_axes and self.mesh.size(sec.shard_axis) > 1 and bool(sec.bucket_layers))
+
+    def begin_backward_overlap(self) -> None:
+        """Arm the per-layer reduction for the backward pass that follows (the last microbatch of a step).
+
+        Matrix sections that are split over owners keep each layer's matrices contiguous inside an owner's block.
+        When the model reports that the backward pass of layer ``i`` has been issued (``on_layer_backward``), the
+        reduce-scatter of that layer's ranges is launched on a high-priority side stream behind an event of the
+        compute stream, with a capped grid, so that it runs over NVLink while earlier layers are still in backward.
+        ``reduce_gradients`` launches what is left and joins the streams."""
+
+        self._pending = [(sec, layer) for sec in self.sections if self._bucketed(sec) for layer in sec.bucket_layers]
+        self._pending.sort(key=lambda item: -item[1])           # backward order, the same on every rank
+        self._armed = bool(self._pending)
+
+    def on_layer_backward(self, layer: int) -> None:
+        """Autograd hook of the model: every kernel of layer ``layer``'s backward pass is on the compute stream."""
+
+        if not self._armed:
+            return
+        ready = [item for item in self._pending if item[1] >= layer]
+        if ready:
+            self._launch_buckets(ready)
+            self._pending = [item for item in self._pending if item[1] < layer]
+
+    def _launch_buckets(self, items: list[tuple[Section, int]]) -> None:
+        comm = self._comm_stream
+        comm.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(comm):
+            for sec, layer in items:
+                a, b = sec.bucket_ranges.get(layer, (sec.start, sec.start))       # this rank may own nothing here
+                self.arena.reduce_scatter(self._grad_off + 4 * a, b - a, channel=BUCKET_CHANNEL,
+                                          max_ctas=self._bucket_ctas)
+                for axis in sec.reduce_axes:
+                    group = self.mesh.group(axis)
+                    if axis != sec.shard_axis and group is not None and b > a:
+                        dist.all_reduce(self.grad_arena[a:b], group=group)
+
     def reduce_gradients(self) -> None:
         """Sum gradients over every replica axis; sharded sections end with only the local range valid."""
 
+        bucketed = set()
+        if self._armed:
+            if self._pending:
+                self._launch_buckets(self._pending)
+                self._pending = []
+            bucketed = {id(sec) for sec in self.sections if self._bucketed(sec)}
         for sec in self.sections:
-            if sec.backend == "frozen" or sec.length == 0:
+            if sec.backend == "frozen" or sec.length == 0 or id(sec) in bucketed:
                 continue
             buf = self.grad_arena[sec.start:sec.start + sec.length]
             for axis in sec.reduce_axes:
@@ -285,6 +359,9 @@ class ParamStore:
                         dist.all_reduce(buf, group=group)
                 else:
                     dist.all_reduce(buf, group=group)
+        if self._armed:
+            torch.cuda.current_stream(self.device).wait_stream(self._comm_stream)
+            self._armed = False
 
     def gather_compute_weights(self) -> None:
         """After the optimizer step: every rank gets the updated compute weights of sharded sections."""

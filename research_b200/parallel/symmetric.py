@@ -161,6 +161,16 @@ def align_ranks() -> None:
         arena.barrier(channel=ALIGN_CHANNEL)
 
 
+def close_all_arenas() -> None:
+    """Close every live arena of this process in creation order (collective over each arena's group)."""
+
+    for ref in list(_ARENA_ORDER):
+        arena = ref()
+        if arena is not None:
+            arena.close()
+    _ARENA_ORDER.clear()
+
+
 def check_all_canaries() -> None:
     """Check the guard words of every live arena of this process (tests, and every step when
     ``RESEARCH_B200_DEBUG=1``)."""

@@ -278,6 +278,17 @@ class Trainer:
             out["bpb"] = loss_sum / (math.log(2.0) * byte_count)
         return out
 
+    def close(self) -> None:
+        """Stop the prefetch thread and give back the symmetric device memory of this trainer (collective when the
+        parameter store uses peer memory: every rank calls it)."""
+
+        self.close_prefetcher()
+        from research_b200.parallel import symmetric
+
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+            symmetric.close_all_arenas()
+
     @property
     def is_writer(self) -> bool:
         return self.mesh.rank == 0

@@ -139,7 +139,7 @@ class TrainStep:
         self.d2h_bytes = [0]
         self.stager = BatchStager(self.device, self.h2d_bytes)
         self.z_weight = float(spec.training.loss.z_loss_weight)
-        self.native = self.device.type == "cuda" and store.compute_dtype == torch.bfloat16
+        self.native = (self.device.type == "cuda" and store.compute_dtype == torch.bfloat16 and Fn.native_enabled())
         self.loss_axes = [a for a in ("data", "fsdp", "cp") if mesh.size(a) > 1]
         if result.execution.sp:
             self.loss_axes.append("tp")
@@ -194,6 +194,10 @@ class TrainStep:
             current = staged
             if k + 1 < len(batches):
                 staged = self.stager.stage(batches[k + 1], rows, cols, (k + 1) % 2)
+            last = k + 1 == len(batches)
+            if last and self.native:
+                self.store.begin_backward_overlap()
+            self.model.layer_backward_hook = self.store.on_layer_backward if (last and self.native) else None
             ce, z, aux, stats = self._microbatch(current, grad_scale, global_counts[k], dp_world)
             ce_sums.append(ce)
             z_sums.append(z)

@@ -102,3 +102,31 @@ def test_adamw_step_matches_torch(tmp_path):
         opt.step()
     for p, r in zip(params, ref):
         assert torch.allclose(p, r, atol=1e-6, rtol=1e-5)
+
+
+def test_adamw_route_rule_without_weight_decay_is_not_decayed(tmp_path):
+    """A route rule with ``weight_decay = false`` on an AdamW-routed tag masks the decay for those parameters only
+    (reference: src/jaxtitan/optim/build.py:506-518)."""
+
+    from tests.helpers import tiny_dataset
+    from research_b200.runtime.trainer import Trainer
+
+    manifest = tiny_dataset(tmp_path)
+    raw = tiny_raw_config(manifest, clip=None)
+    raw["optimizer"]["schedule"] = {"peak_lr": 1e-2}
+    raw["optimizer"]["weight_decay"] = 0.5
+    import dataclasses
+
+    spec = run_spec_from_mapping(raw)
+    rule = ParamRouteRule("final_norm", "adamw", weight_decay=False)
+    spec = dataclasses.replace(spec, optimizer=dataclasses.replace(spec.optimizer, route_rules=(rule,)))
+    trainer = Trainer(spec, device="cpu")
+    by_decay = {sec.decay for sec in trainer.store.sections if sec.backend == "adamw"}
+    assert by_decay == {True, False}
+    before = {e.name: e.param.detach().clone() for e in trainer.store.entries}
+    trainer.store.zero_grads()                       # zero gradients: only the decay moves a parameter
+    trainer.optimizer.step()
+    for e in trainer.store.entries:
+        moved = not torch.equal(e.param.detach(), before[e.name])
+        is_norm = all(m.tag == "final_norm" for m in e.metas)
+        assert moved != is_norm, (e.name, moved)

@@ -1,0 +1,125 @@
+"""Train state <-> checkpoint leaves: leaf names, the 64-bit token counter, saving under one layout and restoring
+under another, replacing a step directory."""
+
+import json
+
+import numpy as np
+import pytest
+import torch
+
+from research_b200.config import run_spec_from_mapping
+from research_b200.runtime.state_io import (collect_state_tensors, iter_state_tensors, load_state_tensors,
+                                            optimizer_leaf_names)
+from research_b200.runtime.trainer import Trainer
+from research_b200.services.checkpoints import LocalCheckpointService
+from tests.helpers import run_gloo, tiny_dataset, tiny_raw_config
+
+
+def _trainer(tmp_path, **kw):
+    manifest = tmp_path / "ds" / "manifest.json"
+    if not manifest.exists():
+        manifest = tiny_dataset(tmp_path)
+    return Trainer(run_spec_from_mapping(tiny_raw_config(manifest, **kw)), device="cpu")
+
+
+def test_optimizer_leaves_follow_the_optax_chain_tree(tmp_path):
+    """clip -> index 0 (no arrays); Muon with decay -> 1; AdamW fallback -> 2, whose own chain keeps mu / nu under
+    element 0 (reference chain: src/jaxtitan/optim/build.py:176-202, 560-656)."""
+
+    trainer = _trainer(tmp_path, optimizer="muon")
+    names = optimizer_leaf_names(trainer)
+    assert names[("momentum", "layers.0.attn.q.kernel")] == "opt_state.1.inner_state.momentum.layers.0.attn.q.kernel"
+    assert names[("mu", "embed.embedding")] == "opt_state.2.inner_state.0.mu.embed.embedding"
+    assert names[("nu", "norm.scale")] == "opt_state.2.inner_state.0.nu.norm.scale"
+    trainer = _trainer(tmp_path, optimizer="adamw", clip=None)
+    names = optimizer_leaf_names(trainer)
+    assert names[("mu", "layers.0.attn.q.kernel")] == "opt_state.0.inner_state.0.mu.layers.0.attn.q.kernel"
+    leaves = collect_state_tensors(trainer)
+    assert set(names.values()) <= set(leaves)
+
+
+def test_token_counter_beyond_32_bits_round_trips(tmp_path):
+    trainer = _trainer(tmp_path)
+    trainer.train_step()
+    trainer.tokens_seen = (3 << 32) + 12345             # about 13e9 tokens: the uint32 leaf alone would wrap
+    leaves = collect_state_tensors(trainer)
+    assert leaves["tokens_seen"].dtype == np.uint32 and int(leaves["tokens_seen"]) == 12345
+    assert int(leaves["tokens_seen_hi"]) == 3
+    other = _trainer(tmp_path)
+    load_state_tensors(other, leaves)
+    assert other.tokens_seen == (3 << 32) + 12345 and other.step == 1
+    for name, value in collect_state_tensors(other).items():
+        assert np.array_equal(value, leaves[name]), name
+    # a checkpoint written before the high word existed still loads
+    del leaves["tokens_seen_hi"]
+    load_state_tensors(other, leaves)
+    assert other.tokens_seen == 12345
+
+
+def test_legacy_optimizer_leaf_names_still_load(tmp_path):
+    trainer = _trainer(tmp_path, optimizer="muon")
+    trainer.train_step()
+    leaves = collect_state_tensors(trainer)
+    legacy = {}
+    for name, value in leaves.items():
+        if ".inner_state.momentum." in name:
+            name = "opt_state.matrix.momentum." + name.split(".inner_state.momentum.", 1)[1]
+        elif ".inner_state.0.mu." in name:
+            name = "opt_state.adamw.mu." + name.split(".inner_state.0.mu.", 1)[1]
+        elif ".inner_state.0.nu." in name:
+            name = "opt_state.adamw.nu." + name.split(".inner_state.0.nu.", 1)[1]
+        legacy[name] = value
+    other = _trainer(tmp_path, optimizer="muon")
+    load_state_tensors(other, legacy)
+    for name, value in collect_state_tensors(other).items():
+        assert np.array_equal(value, leaves[name]), name
+
+
+def _save_sharded(rank, world, raw, out_dir):
+    trainer = Trainer(run_spec_from_mapping(raw), device="cpu")
+    for _ in range(2):
+        trainer.train_step()
+    svc = LocalCheckpointService(out_dir, is_writer=rank == 0)
+    pairs = list(iter_state_tensors(trainer, writer_only=True))
+    if rank != 0:
+        assert all(value is None for _, value in pairs)          # only the writer assembles arrays
+    svc.save(trainer.step, iter_state_tensors(trainer, writer_only=True), {"a": 1}, {"dataset": {"a": 1}}, {"m": 1})
+    return {k: torch.from_numpy(np.array(v)) for k, v in collect_state_tensors(trainer).items()}
+
+
+@pytest.mark.parametrize("optimizer,mesh,parallelism", [
+    ("adamw", {"fsdp": 2}, {"mode": "zero2"}),
+    ("muon", {"fsdp": 2}, {"mode": "fsdp"}),
+])
+def test_sharded_save_assembles_on_the_writer_and_restores_on_one_process(tmp_path, optimizer, mesh, parallelism):
+    manifest = tiny_dataset(tmp_path)
+    raw = tiny_raw_config(manifest, optimizer=optimizer, mesh=mesh, parallelism=parallelism, steps=4)
+    results = run_gloo(2, _save_sharded, raw, str(tmp_path / "run"))
+    restored = LocalCheckpointService(tmp_path / "run").restore_latest()
+    assert restored.step == 2
+    for name, want in results[0].items():
+        assert np.array_equal(restored.tensors[name].reshape(-1), want.numpy().reshape(-1)), name
+    # the same leaves load into an unsharded trainer and come back bit for bit
+    single = Trainer(run_spec_from_mapping(tiny_raw_config(manifest, optimizer=optimizer, steps=4)), device="cpu")
+    load_state_tensors(single, restored.tensors)
+    for name, value in collect_state_tensors(single).items():
+        assert np.array_equal(value.reshape(-1), restored.tensors[name].reshape(-1)), name
+
+
+def test_saving_a_step_twice_replaces_it_only_when_the_new_copy_is_complete(tmp_path):
+    svc = LocalCheckpointService(tmp_path)
+    svc.save(3, {"x": np.arange(4, dtype=np.float32)}, {"a": 1}, {"dataset": {"a": 1}}, {"v": 1})
+
+    def failing():
+        yield "x", np.arange(4, dtype=np.float32) + 1
+        raise RuntimeError("producer died")
+
+    with pytest.raises(RuntimeError):
+        svc.save(3, failing(), {"a": 1}, {"dataset": {"a": 1}}, {"v": 2})
+    kept = svc.restore(3)
+    assert kept.metadata == {"v": 1} and np.array_equal(kept.tensors["x"], np.arange(4, dtype=np.float32))
+    svc.save(3, {"x": np.arange(4, dtype=np.float32) + 2}, {"a": 1}, {"dataset": {"a": 1}}, {"v": 3})
+    assert svc.restore(3).metadata == {"v": 3}
+    leftovers = [p.name for p in (tmp_path / "checkpoints").iterdir() if p.name != "000003"]
+    assert leftovers == [], leftovers
+    assert json.loads((tmp_path / "checkpoints" / "000003" / "_CHECKPOINT_METADATA").read_text())["writer"]
