@@ -233,6 +233,10 @@ def training_progress_printer():
             tail = "" if ev is None else f" eval_loss={_fmt_metric(ev)}"
             print(f"checkpoint step {payload['step']}: {payload['checkpoint_path']} reason={payload['reason']} "
                   f"sec={_fmt_metric(payload['checkpoint_sec'])}{tail}")
+        elif event == "failed":
+            row = payload.get("row", {})
+            groups = ", ".join(payload.get("optimizer_nonfinite_groups") or [])
+            print(f"failed at step {row.get('step')}: non-finite optimizer groups: {groups}")
         elif event == "completed":
             s = payload["summary"]
             tail = "" if s.final_eval_loss is None else f" final_eval={_fmt_metric(s.final_eval_loss)}"

@@ -63,6 +63,9 @@ class Optimizer:
         self._clip = torch.ones(1, dtype=torch.float32, device=dev)
         self.tp_group = store.result.execution.tp_group
         self.tp_size = store.result.execution.tp_size
+        from research_b200.optim.diagnostics import group_templates
+
+        self.group_templates, self.group_index = group_templates(build.route_assignments, store.result.metadata)
 
     # ---- norms -----------------------------------------------------------------------------------
     def _sum_axes(self, sec: Section) -> list[str]:
@@ -150,6 +153,9 @@ class Optimizer:
                     buf[idx] = part
             out["update_norm"] = buf.sum().sqrt().clone()
             del upd
+            from research_b200.optim.diagnostics import group_square_sums
+
+            out["group_squares"] = group_square_sums(self, before, _sumsq)      # [groups, 3], still on the device
         return out
 
     # ---- AdamW -------------------------------------------------------------------------------------

@@ -32,6 +32,56 @@ def _read_jsonl(path: Path) -> list[dict[str, Any]]:
     return rows
 
 
+def _num(value: Any) -> float:
+    return float(value) if isinstance(value, (int, float)) and not isinstance(value, bool) else 0.0
+
+
+def router_health(final: dict[str, Any], recent: list[dict[str, Any]]) -> dict[str, Any] | None:
+    """Router roll-up from the newest row that carries per-layer statistics: the summary figures plus the layer with
+    the worst load imbalance (reference: src/jaxtitan/runtime/inspect.py:197-222)."""
+
+    last = next((r for r in reversed(recent) if r.get("moe_router_layers")), recent[-1] if recent else {})
+    layers = final.get("final_moe_router_layers") or last.get("moe_router_layers")
+    if not isinstance(layers, list) or not layers:
+        return None
+    worst = max(layers, key=lambda item: _num(item.get("load_cv")))
+    pick = lambda key: final.get(f"final_{key}", last.get(key))  # noqa: E731
+    return {
+        "layer_count": len(layers), "dead_experts_count": pick("router_dead_experts_count"),
+        "mean_load_cv": pick("router_mean_load_cv"), "mean_importance_cv": pick("router_mean_importance_cv"),
+        "mean_importance_entropy": pick("router_mean_importance_entropy"),
+        "worst_layer": {k: worst.get(k) for k in ("layer_index", "load_cv", "load_entropy", "experts_active",
+                                                  "importance_cv", "importance_entropy")},
+    }
+
+
+def optimizer_health(final: dict[str, Any], recent: list[dict[str, Any]]) -> dict[str, Any] | None:
+    """Optimizer roll-up from the newest row with group norms: counts, update/parameter ratios and the group whose
+    update is largest relative to its parameters (reference: src/jaxtitan/runtime/inspect.py:225-266)."""
+
+    last = next((r for r in reversed(recent) if r.get("optimizer_groups")), recent[-1] if recent else {})
+    groups = final.get("final_optimizer_groups") or last.get("optimizer_groups")
+    if not isinstance(groups, list) or not groups:
+        return None
+    worst = max(groups, key=lambda item: _num(item.get("update_param_ratio")))
+
+    def pick(key: str):
+        value = final.get(f"final_optimizer_{key}")
+        return last.get(f"optimizer_{key}") if value is None else value
+
+    return {
+        "group_count": len(groups), "update_param_ratio_max_group": worst.get("group"),
+        "update_param_ratio_max": pick("update_param_ratio_max"),
+        "update_param_ratio_mean": pick("update_param_ratio_mean"),
+        "groups_with_zero_grad": pick("groups_with_zero_grad"),
+        "groups_with_zero_update": pick("groups_with_zero_update"),
+        "nonfinite_groups": pick("nonfinite_groups"),
+        "route_backend_counts": pick("route_backend_counts"),
+        "worst_update_ratio_group": {k: worst.get(k) for k in ("group", "tag", "backend", "update_param_ratio",
+                                                               "grad_param_ratio")},
+    }
+
+
 def inspect_run(run_dir: str | Path) -> dict[str, Any]:
     run_dir = Path(run_dir)
     if not run_dir.is_dir():
@@ -76,6 +126,8 @@ def inspect_run(run_dir: str | Path) -> dict[str, Any]:
                    "last": events[-1] if events else None,
                    "failures": [e for e in events if str(e.get("type", "")).endswith("_failed")]},
         "router": router,
+        "router_health": router_health(summary or {}, train[-8:]),
+        "optimizer_health": optimizer_health(summary or {}, train[-8:]),
         "optimizer": None if runtime is None else runtime.get("optimizer", {}) and {
             "name": runtime["optimizer"].get("name"),
             "backend_parameter_counts": runtime["optimizer"].get("backend_parameter_counts")},

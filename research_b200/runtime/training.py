@@ -92,6 +92,17 @@ class RunSummary:
     final_router_max_vio: float | None = None
     final_router_mean_load_cv: float | None = None
     final_router_dead_experts_count: float | None = None
+    final_router_mean_importance_cv: float | None = None
+    final_router_mean_importance_entropy: float | None = None
+    final_optimizer_groups: list[dict[str, Any]] | None = None
+    final_optimizer_grad_norm_max_group: str | None = None
+    final_optimizer_update_norm_max_group: str | None = None
+    final_optimizer_update_param_ratio_max: float | None = None
+    final_optimizer_update_param_ratio_mean: float | None = None
+    final_optimizer_groups_with_zero_grad: int | None = None
+    final_optimizer_groups_with_zero_update: int | None = None
+    final_optimizer_nonfinite_group_count: int | None = None
+    final_optimizer_nonfinite_groups: list[str] | None = None
     final_optimizer_route_backend_counts: dict[str, int] | None = None
 
 
@@ -144,10 +155,11 @@ def metrics_row(trainer: Trainer, metrics: StepMetrics, spec: RunSpec) -> dict[s
                     "examples": t.global_batch_size * t.gradient_accumulation_steps,
                     "target_tokens": t.global_batch_size * t.seq_len * t.gradient_accumulation_steps,
                     "document_aware": False, "documents_touched": None, "document_min": None, "document_max": None})
-    if metrics.router_layers:
-        row["moe_router_layers"] = [
-            {"layer_index": int(l["layer_index"]), "expert_counts": [float(v) for v in l["counts"].tolist()],
-             "importance": [float(v) for v in l["importance"].tolist()]} for l in metrics.router_layers]
+    from research_b200.optim.diagnostics import health_fields, router_layers_payload
+
+    row["moe_router_layers"] = router_layers_payload(metrics.router_layers) if metrics.router_layers else None
+    row["optimizer_groups"] = metrics.optimizer_groups or None
+    row.update(health_fields(metrics.optimizer_groups))
     t = spec.training
     data_axis = trainer.mesh.size("data") * trainer.mesh.size("fsdp")
     row.update({
@@ -354,6 +366,18 @@ def _run_initialized(spec: RunSpec, config_path: Path, writer, resume: bool, pro
                                  "created_at": utc_now(), "step": trainer.step, "fields": bad,
                                  "leaves": find_nonfinite_leaves(trainer)})
             raise ContractError(f"non-finite training metrics at step {trainer.step}: {bad}")
+        bad_groups = row.get("optimizer_nonfinite_groups") or []
+        if bad_groups:
+            from research_b200.runtime.train_debug import find_nonfinite_leaves
+
+            writer.append_train_metrics(row)
+            writer.append_event({"schema_version": 1, "type": "optimizer_nonfinite", "run_id": spec.run_id,
+                                 "created_at": utc_now(), "step": trainer.step, "tokens_seen": trainer.tokens_seen,
+                                 "optimizer_nonfinite_group_count": len(bad_groups),
+                                 "optimizer_nonfinite_groups": list(bad_groups),
+                                 "leaves": find_nonfinite_leaves(trainer)})
+            progress("failed", {"row": row, "optimizer_nonfinite_groups": list(bad_groups)})
+            raise ContractError(f"optimizer state became non-finite at step {trainer.step}: {', '.join(bad_groups)}")
         if should_log(trainer.step, trainer.tokens_seen, spec):
             writer.append_train_metrics(row)
             last_logged_step = trainer.step
@@ -385,6 +409,10 @@ def _run_initialized(spec: RunSpec, config_path: Path, writer, resume: bool, pro
     profiler.finish()
     service.close()
     diag = training_diagnostics_summary(rows)
+    from research_b200.optim.diagnostics import HEALTH_KEYS
+
+    # group norms exist on the steps that computed diagnostics (the logged ones): report the newest of them
+    last_groups_row = next((r for r in reversed(rows) if r.get("optimizer_groups")), {})
     latest, best = index.latest_record, index.best_record
     t = spec.training
     data_axis = trainer.mesh.size("data") * trainer.mesh.size("fsdp")
@@ -418,6 +446,10 @@ def _run_initialized(spec: RunSpec, config_path: Path, writer, resume: bool, pro
         final_router_max_vio=last_row.get("router_max_vio"),
         final_router_mean_load_cv=last_row.get("router_mean_load_cv"),
         final_router_dead_experts_count=last_row.get("router_dead_experts_count"),
+        final_router_mean_importance_cv=last_row.get("router_mean_importance_cv"),
+        final_router_mean_importance_entropy=last_row.get("router_mean_importance_entropy"),
+        final_optimizer_groups=last_groups_row.get("optimizer_groups"),
+        **{f"final_{k}": last_groups_row.get(k) for k in HEALTH_KEYS if k != "optimizer_route_backend_counts"},
         final_optimizer_route_backend_counts=backend_counts, **diag,
     )
 

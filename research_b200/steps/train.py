@@ -219,8 +219,11 @@ class TrainStep:
             if group is not None:
                 dist.all_reduce(packed, group=group)
         extras = [opt["grad_norm"].reshape(1).float(), opt["clip_scale"].reshape(1).float()]
+        n_groups = 0
         if diagnostics:
             extras += [opt["param_norm"].reshape(1).float(), opt["update_norm"].reshape(1).float()]
+            n_groups = len(self.optimizer.group_templates)
+            extras.append(opt["group_squares"].reshape(-1).float())
         router_payload = self._router_metrics(all_stats) if all_stats and all_stats[0] else {}
         router_keys = sorted(k for k, v in router_payload.items() if torch.is_tensor(v) and v.dim() == 0)
         extras += [router_payload[k].reshape(1).float() for k in router_keys]
@@ -249,9 +252,12 @@ class TrainStep:
         grad_norm, clip_scale = host[pos], host[pos + 1]
         pos += 2
         param_norm = update_norm = None
+        group_squares = None
         if diagnostics:
             param_norm, update_norm = host[pos], host[pos + 1]
             pos += 2
+            group_squares = host[pos:pos + 3 * n_groups]
+            pos += 3 * n_groups
         router_host = {k: host[pos + i] for i, k in enumerate(router_keys)}
         metrics = StepMetrics(
             loss_sum=float(sum(ce_host)), token_count=float(sum(global_counts)), lr=opt["lr"], grad_norm=grad_norm,
@@ -265,7 +271,10 @@ class TrainStep:
         metrics.router = router_host
         metrics.router_layers = router_payload.get("layers", [])
         metrics.smebu = {k: v for k, v in router_host.items() if k.startswith("smebu_")}
-        metrics.optimizer_groups = []
+        if group_squares is not None:
+            from research_b200.optim.diagnostics import groups_payload
+
+            metrics.optimizer_groups = groups_payload(self.optimizer.group_templates, group_squares)
         metrics.router["clip_scale"] = clip_scale
         return metrics
 
