@@ -14,6 +14,7 @@ of a checkpoint save and read checkpoints themselves on resume.
 from __future__ import annotations
 
 import math
+import os
 import time
 from dataclasses import asdict, dataclass
 from pathlib import Path
@@ -271,13 +272,28 @@ def run_training(config_path: str | Path, *, resume: bool = False, progress: Pro
     writer.append_event({"schema_version": 1, "type": "training_started", "run_id": spec.run_id,
                          "created_at": utc_now(), "resume": resume, "config_path": config_path.as_posix(),
                          "world_size": world})
+    monitor = None
+    if world > 1:
+        from research_b200.runtime.watchdog import RankMonitor
+
+        # every rank posts heartbeats to the process group's store; a rank that leaves marks itself failed there
+        monitor = RankMonitor(torch.distributed.distributed_c10d._get_default_store(), rank, world,
+                              directory=run_dir / "diagnostics" / "heartbeats", writer=writer, run_id=spec.run_id,
+                              timeout_s=float(os.environ.get("RESEARCH_B200_RANK_TIMEOUT_S", "300")),
+                              poll_s=float(os.environ.get("RESEARCH_B200_RANK_POLL_S", "2"))).start()
     try:
-        summary = _run_initialized(spec, config_path, writer, resume, progress, trainer_hook)
+        summary = _run_initialized(spec, config_path, writer, resume, progress, trainer_hook, monitor)
     except Exception as exc:
+        if monitor is not None:
+            monitor.mark_failed(-1, f"{type(exc).__name__}: {exc}")
+            monitor.stop()
         writer.append_event({"schema_version": 1, "type": "training_failed", "run_id": spec.run_id,
                              "created_at": utc_now(), "error_type": type(exc).__name__, "error_message": str(exc)})
         writer.close()
         raise
+    if monitor is not None:
+        monitor.mark_done(summary.steps)
+        monitor.stop()
     writer.write_summary(normalize(asdict(summary)))
     writer.append_event({"schema_version": 1, "type": "training_completed", "run_id": spec.run_id,
                          "created_at": utc_now(), "steps": summary.steps, "tokens_seen": summary.tokens_seen,
@@ -288,7 +304,7 @@ def run_training(config_path: str | Path, *, resume: bool = False, progress: Pro
 
 
 def _run_initialized(spec: RunSpec, config_path: Path, writer, resume: bool, progress: ProgressFn,
-                     trainer_hook) -> RunSummary:
+                     trainer_hook, monitor=None) -> RunSummary:
     wall_start = time.perf_counter()
     wall_start_ns = time.time_ns()
     trainer = Trainer(spec)
@@ -349,8 +365,12 @@ def _run_initialized(spec: RunSpec, config_path: Path, writer, resume: bool, pro
                 progress("compile_start", {"phase": "train"})
                 first = False
             diagnostics = should_log(next_step, trainer.tokens_seen + _step_tokens(spec), spec)
+            if monitor is not None:
+                monitor.check()          # a peer that left between steps is seen here, before the next launch
             with timer.phase("train_step"), profiler.annotate("train_step"):
                 metrics = trainer.train_on(batches, diagnostics=diagnostics)
+            if monitor is not None:
+                monitor.beat(trainer.step)
         timings = timer.reset()
         row = metrics_row(trainer, metrics, spec)
         row = enrich_train_metrics(row, timings=timings, runtime=runtime,
