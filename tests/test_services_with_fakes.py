@@ -1,0 +1,353 @@
+"""Host services that talk to something outside the process, tested against fakes: Hugging Face streaming with a
+fake iterable dataset, the W&B mirror with a fake ``wandb`` module, the profiler window with a fake
+``torch.profiler.profile``, and the profile analyzer on hand-made runs and traces.  (The reference tests the same
+parts the same way: tests/jaxtitan/test_data_pipeline.py:123-182, test_runtime_training.py:300-595,
+test_profile_analysis.py.)"""
+
+import json
+import sys
+import types
+
+import numpy as np
+import pytest
+
+from research_b200.config import run_spec_from_mapping
+from research_b200.config.specs import DataSpec, HFStreamingSpec
+from research_b200.errors import ContractError
+from tests.helpers import tiny_dataset, tiny_raw_config, write_toml
+
+
+# ---- Hugging Face streaming ------------------------------------------------------------------------
+class FakeTokenizer:
+    eot_id = 255
+
+    def encode(self, text):
+        return [ord(c) % 200 for c in text]
+
+
+class FakeIterableDataset:
+    """Rows of text with the ``state_dict`` / ``load_state_dict`` pair of a streaming ``datasets`` dataset."""
+
+    def __init__(self, rows):
+        self.rows, self.position = rows, 0
+
+    def __iter__(self):
+        while self.position < len(self.rows):
+            row = self.rows[self.position]
+            self.position += 1
+            yield row
+
+    def state_dict(self):
+        return {"position": self.position}
+
+    def load_state_dict(self, state):
+        self.position = int(state["position"])
+
+
+def _streaming(rows, seq_len=8, batch=2, loads=None):
+    from research_b200.data.streaming import HFStreamingTextPipeline
+
+    spec = DataSpec(mode="hf_streaming", tokenizer_id="fake", hf_streaming=HFStreamingSpec(
+        dataset="corp/us", split="train", revision="abc123"))
+
+    def loader(s):
+        if loads is not None:
+            loads.append((s.dataset, s.split, s.revision))
+        return FakeIterableDataset(rows)
+
+    return HFStreamingTextPipeline(spec, seq_len=seq_len, batch_size=batch, dataset_loader=loader,
+                                   tokenizer=FakeTokenizer())
+
+
+ROWS = [{"text": "the quick brown fox"}, {"text": ""}, {"other": 1}, {"text": "jumps over the lazy dog"},
+        {"text": "pack my box with five dozen liquor jugs"}, {"text": "sphinx of black quartz judge my vow"}]
+
+
+def test_streaming_packs_documents_with_eot_and_skips_empty_rows():
+    loads = []
+    pipe = _streaming(ROWS, loads=loads)
+    first = pipe.next_batch(pipe.initial_state())
+    assert loads == [("corp/us", "train", "abc123")]                        # the pinned revision reaches the loader
+    ids = np.concatenate([first.batch.input_ids[0], first.batch.target_ids[0][-1:]])
+    want = [ord(c) % 200 for c in "the quick brown fox"] + [255]
+    assert ids.tolist() == want[:9]                                          # one row = seq_len + 1 tokens, shifted
+    assert first.batch.loss_mask.all() and first.batch.input_ids.shape == (2, 8)
+    assert first.state.stream_state["documents_consumed"] == 1 and first.state.next_record_index == 2
+    assert len(first.state.stream_state["pending_tokens"]) == len(want) - 18
+    assert first.provenance.token_start == 0 and first.provenance.token_end == 16
+    second = pipe.next_batch(first.state)
+    assert second.state.stream_state["documents_consumed"] == 4              # the empty and the text-less rows count
+    assert pipe.describe()["backend"] == "hf_streaming" and pipe.describe()["revision"] == "abc123"
+
+
+def test_streaming_resumes_with_the_very_next_token():
+    pipe = _streaming(ROWS)
+    state = pipe.initial_state()
+    straight = []
+    for _ in range(4):
+        pb = pipe.next_batch(state)
+        state = pb.state
+        straight.append(pb.batch.input_ids.copy())
+    pipe2 = _streaming(ROWS)
+    state = pipe2.initial_state()
+    for _ in range(2):
+        state = pipe2.next_batch(state).state
+    saved = json.loads(json.dumps(pipe2.state_to_json(state)))              # what a checkpoint stores
+    resumed = _streaming(ROWS)                                               # a new process, a new dataset object
+    state = resumed.state_from_json(saved)
+    for want in straight[2:]:
+        pb = resumed.next_batch(state)
+        state = pb.state
+        assert np.array_equal(pb.batch.input_ids, want)
+
+
+def test_streaming_rejects_foreign_state_and_ends_cleanly():
+    pipe = _streaming(ROWS[:1], seq_len=64)
+    with pytest.raises(StopIteration, match="ended before one full batch"):
+        pipe.next_batch(pipe.initial_state())
+    other = _streaming(ROWS, seq_len=4)
+    saved = other.state_to_json(other.next_batch(other.initial_state()).state)
+    with pytest.raises(ContractError, match="does not match this pipeline"):
+        _streaming(ROWS, seq_len=8).state_from_json(saved)
+
+
+# ---- W&B mirror --------------------------------------------------------------------------------------
+class FakeWandb(types.ModuleType):
+    def __init__(self, fail_on=None):
+        super().__init__("wandb")
+        self.calls, self.fail_on = [], fail_on
+        self.run = types.SimpleNamespace(summary={})
+
+    def _call(self, what, **kw):
+        self.calls.append((what, kw))
+        if self.fail_on == what:
+            raise RuntimeError(f"fake wandb {what} failure")
+
+    def init(self, **kw):
+        self._call("init", **kw)
+        return self.run
+
+    def log(self, payload, step=None):
+        self._call("log", payload=payload, step=step)
+
+    def finish(self):
+        self._call("finish")
+
+
+def _wandb_config(tmp_path, run_id):
+    manifest = tmp_path / "ds" / "manifest.json"
+    if not manifest.exists():
+        manifest = tiny_dataset(tmp_path)
+    raw = tiny_raw_config(manifest, steps=3, run_id=run_id, output_dir=(tmp_path / "runs").as_posix(), evals=True)
+    raw["artifacts"] = {"wandb_enabled": True, "wandb_project": "proj", "wandb_mode": "offline",
+                        "wandb_tags": ["a", "b"]}
+    return write_toml(raw, tmp_path / f"{run_id}.toml")
+
+
+def test_wandb_mirror_logs_namespaced_metrics_after_the_local_files(tmp_path, monkeypatch):
+    from research_b200.runtime.training import run_training
+    from research_b200.services.wandb import namespaced_metrics
+
+    fake = FakeWandb()
+    monkeypatch.setitem(sys.modules, "wandb", fake)
+    summary = run_training(_wandb_config(tmp_path, "wb"))
+    names = [c[0] for c in fake.calls]
+    assert names[0] == "init" and names[-1] == "finish" and names.count("log") >= 4
+    init = fake.calls[0][1]
+    assert init["project"] == "proj" and init["mode"] == "offline" and init["resume"] == "allow"
+    assert init["id"].startswith("wb-") and len(init["id"]) == len("wb-") + 16 and init["tags"] == ["a", "b"]
+    train_logs = [c[1] for c in fake.calls if c[0] == "log" and "train/loss" in c[1]["payload"]]
+    assert [c["step"] for c in train_logs] == [1, 2, 3]
+    assert {"optimizer/grad_norm", "optimizer/lr", "perf/train_tokens_per_sec", "data/token_start"} <= \
+        set(train_logs[-1]["payload"])
+    assert any("eval/loss" in c[1]["payload"] for c in fake.calls if c[0] == "log")
+    assert fake.run.summary["steps"] == summary.steps == 3
+    meta = json.loads((tmp_path / "runs" / "wb" / "diagnostics" / "wandb.json").read_text())
+    assert meta["enabled"] and meta["run_id"] == init["id"] and meta["project"] == "proj"
+    ns = namespaced_metrics({"loss": 1.0, "router_max_vio": 0.1, "mfu": 0.4, "flag": True, "name": "x"})
+    assert ns == {"train/loss": 1.0, "router/router_max_vio": 0.1, "perf/mfu": 0.4}
+
+
+def test_wandb_failure_is_an_event_and_aborts_with_local_files_intact(tmp_path, monkeypatch):
+    from research_b200.runtime.training import run_training
+
+    monkeypatch.setitem(sys.modules, "wandb", FakeWandb(fail_on="log"))
+    with pytest.raises(ContractError, match="wandb log_train failed"):
+        run_training(_wandb_config(tmp_path, "wbfail"))
+    run_dir = tmp_path / "runs" / "wbfail"
+    events = [json.loads(line) for line in (run_dir / "events.jsonl").read_text().splitlines()]
+    failed = next(e for e in events if e["type"] == "wandb_failed")
+    assert failed["operation"] == "log_train" and failed["error_type"] == "RuntimeError"
+    assert events[-1]["type"] == "training_failed"
+    assert len((run_dir / "metrics" / "train.jsonl").read_text().splitlines()) == 1     # local row written first
+
+
+def test_wandb_enabled_without_the_package_is_a_contract_error(tmp_path, monkeypatch):
+    from research_b200.runtime.training import run_training
+
+    monkeypatch.setitem(sys.modules, "wandb", None)                        # import wandb -> ImportError
+    with pytest.raises(ContractError, match="wandb package is not importable"):
+        run_training(_wandb_config(tmp_path, "wbmissing"))
+
+
+# ---- profiler window ---------------------------------------------------------------------------------
+class FakeProfile:
+    instances = []
+
+    def __init__(self, activities=None, fail_export=False):
+        self.entered = self.exited = False
+        self.exported = None
+        FakeProfile.instances.append(self)
+
+    def __enter__(self):
+        self.entered = True
+        return self
+
+    def __exit__(self, *exc):
+        self.exited = True
+        return False
+
+    def export_chrome_trace(self, path):
+        if FakeProfile.fail_export:
+            raise OSError("disk full")
+        self.exported = path
+        with open(path, "w") as f:
+            json.dump({"traceEvents": []}, f)
+
+    fail_export = False
+
+
+class Sink:
+    def __init__(self):
+        self.events, self.profiling = [], None
+
+    def append_event(self, e):
+        self.events.append(e)
+
+    def write_profiling_diagnostics(self, payload):
+        self.profiling = payload
+
+
+def _profiling_spec(tmp_path, **prof):
+    raw = tiny_raw_config(tmp_path / "m.json")
+    raw["profiling"] = dict(enabled=True, trace_start_step=2, trace_steps=2, **prof)
+    return run_spec_from_mapping(raw)
+
+
+def test_profiler_traces_exactly_the_configured_window(tmp_path, monkeypatch):
+    import torch
+
+    from research_b200.runtime.profiling import ProfilingManager
+
+    FakeProfile.instances, FakeProfile.fail_export = [], False
+    monkeypatch.setattr(torch.profiler, "profile", FakeProfile)
+    (tmp_path / "profiles").mkdir()
+    sink = Sink()
+    mgr = ProfilingManager(_profiling_spec(tmp_path), tmp_path, sink)
+    running = []
+    for step in range(1, 6):
+        with mgr.step(step):
+            with mgr.annotate("train_step"):
+                running.append(bool(FakeProfile.instances and FakeProfile.instances[-1].entered
+                                    and not FakeProfile.instances[-1].exited))
+    mgr.finish()
+    assert running == [False, True, True, False, False]                     # steps 2 and 3 only
+    assert len(FakeProfile.instances) == 1
+    assert [e["type"] for e in sink.events] == ["profiling_trace_started", "profiling_trace_completed"]
+    assert sink.events[0]["step"] == 2 and sink.events[1]["step"] == 3
+    assert sink.profiling["status"] == "completed" and sink.profiling["trace_path"] == "profiles/trace_steps_2_3.json"
+    assert (tmp_path / sink.profiling["trace_path"]).is_file()
+    with pytest.raises(ContractError, match="is not after resumed step 2"):
+        mgr.check_resume(2)
+    mgr.check_resume(1)
+
+
+def test_profiler_failure_and_disabled_modes(tmp_path, monkeypatch):
+    import torch
+
+    from research_b200.runtime.profiling import ProfilingManager
+
+    FakeProfile.instances, FakeProfile.fail_export = [], True
+    monkeypatch.setattr(torch.profiler, "profile", FakeProfile)
+    (tmp_path / "profiles").mkdir()
+    sink = Sink()
+    mgr = ProfilingManager(_profiling_spec(tmp_path), tmp_path, sink)
+    for step in range(1, 5):
+        with mgr.step(step):
+            pass
+    assert [e["type"] for e in sink.events] == ["profiling_trace_started", "profiling_trace_failed"]
+    assert sink.events[-1]["error_type"] == "OSError" and sink.profiling["status"] == "failed"
+    FakeProfile.instances, FakeProfile.fail_export = [], False
+    # a rank that is not the writer never starts a trace; a disabled section reports "disabled"
+    quiet = ProfilingManager(_profiling_spec(tmp_path), tmp_path, Sink(), enabled=False)
+    for step in range(1, 5):
+        with quiet.step(step):
+            pass
+    assert FakeProfile.instances == []
+    off = ProfilingManager(run_spec_from_mapping(tiny_raw_config(tmp_path / "m.json")), tmp_path, Sink())
+    assert off.payload()["status"] == "disabled" and not off.active
+
+
+# ---- profile analysis ----------------------------------------------------------------------------------
+def _fake_run(root, name, *, step_sec, tps, trace_end=None, exclude=None, trace=None, optimizer="adamw"):
+    run = root / name
+    (run / "metrics").mkdir(parents=True)
+    (run / "diagnostics").mkdir()
+    rows = [{"step": i + 1, "train_step_sec": s, "step_sec": s + 0.01, "train_tokens_per_sec": t, "loss": 3.0 - 0.1 * i}
+            for i, (s, t) in enumerate(zip(step_sec, tps))]
+    (run / "metrics" / "train.jsonl").write_text("\n".join(json.dumps(r) for r in rows))
+    events = [{"type": "checkpoint_saved", "step": s} for s in (exclude or [])]
+    (run / "events.jsonl").write_text("\n".join(json.dumps(e) for e in events))
+    (run / "diagnostics" / "runtime.json").write_text(json.dumps({
+        "runtime": {"device_kind": "NVIDIA B200"}, "mesh": {"device_count": 8}, "optimizer": {"name": optimizer},
+        "parallelism": {"mode": "fsdp"}}))
+    if trace_end is not None:
+        (run / "diagnostics" / "profiling.json").write_text(json.dumps({"enabled": True, "trace_end_step": trace_end}))
+    if trace is not None:
+        (run / "profiles").mkdir()
+        (run / "profiles" / "trace.json").write_text(json.dumps({"traceEvents": trace}))
+    return run
+
+
+def test_profile_analysis_steady_window_medians_pairs_and_kernel_categories(tmp_path):
+    from research_b200.runtime.profile_analysis import analyze_profile_root, categorize_kernel, summarize_trace
+
+    trace = [
+        {"ph": "X", "cat": "kernel", "name": "gemm_bf16_kernel<256>", "dur": 700.0},
+        {"ph": "X", "cat": "kernel", "name": "attn_fwd_kernel<128>", "dur": 200.0},
+        {"ph": "X", "cat": "kernel", "name": "ncclDevKernel_AllGather_RING_LL", "dur": 60.0},
+        {"ph": "X", "cat": "kernel", "name": "ncclDevKernel_ReduceScatter_Sum_f32", "dur": 40.0},
+        {"ph": "X", "cat": "cpu_op", "name": "aten::mm", "dur": 999.0},             # host op: ignored
+        {"ph": "M", "name": "process_name"},
+    ]
+    _fake_run(tmp_path, "dense_tp_adamw", step_sec=[9.0, 0.5, 0.4, 0.41, 0.39, 5.0, 0.40],
+              tps=[1, 100, 110, 108, 112, 10, 111], trace_end=3, exclude=[6], trace=trace)
+    _fake_run(tmp_path, "dense_tp_muon", step_sec=[9.0, 0.6, 0.6, 0.62, 0.58, 0.60, 0.61],
+              tps=[1, 80, 82, 81, 83, 82, 80], optimizer="muon")
+    out = analyze_profile_root(tmp_path, warmup_steps=2)
+    assert out["run_count"] == 2 and out["hardware"] == {"8xNVIDIA B200": ["dense_tp_adamw", "dense_tp_muon"]}
+    adamw, muon = out["runs"]
+    # steady window: after max(warmup + 1, trace_end + 1) = step 4, without the checkpoint step 6
+    assert adamw["steady"]["start_step"] == 4 and adamw["steady"]["rows"] == 3 and adamw["steady"]["excluded_steps"] == [6]
+    assert adamw["steady"]["medians"]["train_step_sec"] == pytest.approx(0.40)
+    assert muon["steady"]["start_step"] == 3 and muon["steady"]["medians"]["train_step_sec"] == pytest.approx(0.60)
+    (pair,) = out["comparisons"]
+    assert pair["kind"] == "optimizer" and pair["candidate"] == "dense_tp_muon" and pair["baseline"] == "dense_tp_adamw"
+    assert pair["train_step_delta"] == pytest.approx(0.5)
+    t = adamw["traces"][0]
+    assert t["total_gpu_time_us"] == 1000.0 and t["gpu_time_share"]["gemm"] == pytest.approx(0.7)
+    assert t["collective_counts"] == {"AllGather": 1, "ReduceScatter": 1} and t["kernel_counts"]["nccl"] == 2
+    assert t["top_kernels"][0]["name"].startswith("gemm_bf16_kernel")
+    assert categorize_kernel("b200c_reduce_scatter_pull") == "other" and categorize_kernel("adamw_kernel") == "optimizer"
+    assert summarize_trace(tmp_path / "dense_tp_adamw" / "profiles" / "trace.json")["trace"] == "trace.json"
+
+
+def test_profile_analysis_rejects_bad_roots(tmp_path):
+    from research_b200.runtime.profile_analysis import analyze_profile_root
+
+    with pytest.raises(ContractError, match="not a directory"):
+        analyze_profile_root(tmp_path / "nope")
+    with pytest.raises(ContractError, match="no metrics/train.jsonl"):
+        analyze_profile_root(tmp_path)
+    with pytest.raises(ContractError, match="non-negative"):
+        analyze_profile_root(tmp_path, warmup_steps=-1)
