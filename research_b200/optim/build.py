@@ -58,6 +58,7 @@ class OptimizerBuildResult:
     adamw_fallback_schedule: Callable[[int], float] | None
     route_assignments: tuple[RouteAssignment, ...]
     description: str
+    muon_execution_plans: tuple = ()          # one MuonLeafPlan per tensor-parallel-sharded Muon matrix
 
     def backend_by_name(self) -> dict[str, str]:
         """Storage-level backend per logical parameter: adamw | muon | dion2 (dist_muon is a muon mode)."""
@@ -154,7 +155,18 @@ def build_optimizer(spec: OptimizerSpec, metadata: tuple[ParamMeta, ...], *, tp_
     assignments = route_assignments(spec, tuple(metadata), tp_size=tp_size)
     schedule = build_lr_schedule(spec.schedule)
     fallback = None if spec.adamw_fallback_schedule is None else build_lr_schedule(spec.adamw_fallback_schedule)
-    return OptimizerBuildResult(spec, schedule, fallback, assignments, describe_optimizer(spec))
+    from research_b200.optim.distributed_ns import build_muon_execution_plans
+
+    plans = build_muon_execution_plans(assignments, tuple(metadata), tp_size=tp_size, requested_mode=spec.muon_tp_mode)
+    return OptimizerBuildResult(spec, schedule, fallback, assignments, describe_optimizer(spec), plans)
+
+
+def _muon_plan_summary(result: OptimizerBuildResult) -> dict[str, Any] | None:
+    if not result.muon_execution_plans:
+        return None
+    from research_b200.optim.distributed_ns import summarize_plans
+
+    return summarize_plans(result.muon_execution_plans)
 
 
 def optimizer_policy_summary(result: OptimizerBuildResult) -> dict[str, Any]:
@@ -173,6 +185,7 @@ def optimizer_policy_summary(result: OptimizerBuildResult) -> dict[str, Any]:
         "muon": muon_policy_constants() if spec.name == "muon" else None,
         "dion2": dion2_policy_constants() if spec.name == "dion" else None,
         "muon_tp_mode": spec.muon_tp_mode,
+        "muon_tp_execution": _muon_plan_summary(result),
         "backend_parameter_counts": dict(sorted(by_backend.items())),
         "groups": [{"tag": t, "backend": b, "parameters": n} for (t, b), n in sorted(groups.items())],
         "routes": [

@@ -63,6 +63,8 @@ class Optimizer:
         self._clip = torch.ones(1, dtype=torch.float32, device=dev)
         self.tp_group = store.result.execution.tp_group
         self.tp_size = store.result.execution.tp_size
+        self.muon_plans = {p.name: p for p in getattr(build, "muon_execution_plans", ())}
+        self._gram_reducer = None
         from research_b200.optim.diagnostics import group_templates
 
         self.group_templates, self.group_index = group_templates(build.route_assignments, store.result.metadata)
@@ -127,6 +129,8 @@ class Optimizer:
                 self._adamw(i, sec, adamw_lr)
             elif sec.backend in ("muon", "dion2"):
                 slow = [e for e in sec.entries if store.owns(sec, e)]
+                if sec.backend == "muon" and self.tp_size > 1 and self.muon_plans:
+                    slow = self._dist_muon_bucketed(i, sec, slow, lr)
                 if sec.backend == "muon" and self._fast_muon_ok():
                     slow = self._muon_section_fast(i, sec, slow, lr)
                 elif sec.backend == "dion2" and self._fast_muon_ok():
@@ -251,6 +255,78 @@ class Optimizer:
                                       store.compute_arena[e.offset + first:], per, stride, batch, decay, step)
             at += batch
 
+    # ---- distributed Muon over the tensor-parallel group ---------------------------------------------
+    def _reducer(self):
+        """Transport of the packed Gram reductions: a symmetric arena of the tensor-parallel group on CUDA (one
+        peer-memory kernel per reduction), ``torch.distributed`` otherwise."""
+
+        if self._gram_reducer is None:
+            import os
+
+            from research_b200.optim import distributed_ns as dns
+
+            reducer = None
+            use_arena = (self.store.device.type == "cuda" and Fn.native_enabled() and self.tp_size <= 8 and
+                         os.environ.get("RESEARCH_B200_PEER_COLLECTIVES", "1") != "0")
+            if use_arena:
+                from research_b200.parallel.symmetric import build_collectively
+
+                # bf16 payload limit of a bucket, held as fp32, plus one norm slot per leaf
+                capacity = dns.GRAM_BUCKET_MAX_BYTES // 2 + 4096
+                largest = max((p.gram_dimension ** 2 for p in self.muon_plans.values()), default=0)
+                capacity = max(capacity, largest + 4096)
+                reducer = build_collectively(self.tp_group,
+                                             lambda: dns.ArenaReducer(self.tp_group, capacity, self.store.device),
+                                             "symmetric arena for distributed Muon")
+            self._gram_reducer = reducer or dns.TorchReducer(self.tp_group)
+        return self._gram_reducer
+
+    def _dist_muon_bucketed(self, i: int, sec: Section, entries: list[StorageEntry], lr: float) -> list[StorageEntry]:
+        """Muon for the tensor-parallel-sharded matrices of a section whose plan is a distributed execution: momentum
+        update per leaf, then one bucketed Newton-Schulz per Gram bucket (one packed reduction per step for all
+        leaves of the bucket), then the parameter update.  Returns the entries that take another path."""
+
+        from research_b200.optim.distributed_ns import bucketed_distributed_zeropower
+
+        store = self.store
+        lo, _ = store.local_master_range(sec)
+        wd = float(self.spec.weight_decay)
+        leftovers: list[StorageEntry] = []
+        buckets: dict[int, list[tuple]] = {}
+        touched: list[StorageEntry] = []
+        for e in entries:
+            plans = [self.muon_plans.get(m.name) for m in e.metas]
+            master = store.master_view(sec, e)
+            if (master is None or master.dim() != 2 or
+                    any(p is None or p.execution == "duplicated" for p in plans)):
+                leftovers.append(e)
+                continue
+            mom = self.state[i]["momentum"][e.offset - lo:e.offset - lo + e.numel].view(e.param.shape)
+            grad = e.param.main_grad
+            touched.append(e)
+            for meta, plan in zip(e.metas, plans):
+                route = self.routes[meta.name]
+                sl = slice(None) if meta.rows is None else slice(*meta.rows)
+                g = grad[sl] * self._clip
+                m = mom[sl]
+                m.mul_(orth.MUON_MOMENTUM).add_(g, alpha=1.0 - orth.MUON_MOMENTUM)
+                u = (1.0 - orth.MUON_MOMENTUM) * g + orth.MUON_MOMENTUM * m if orth.MUON_NESTEROV else m
+                axis = (len(meta.shape) - 1 - route.matrix_axis) if meta.transposed else route.matrix_axis
+                buckets.setdefault(plan.bucket_id, []).append((meta, route, plan, u.to(torch.bfloat16), master[sl], axis))
+        dtype = torch.bfloat16 if orth.MUON_NS_PRECISION == "bfloat16" else torch.float32
+        for bucket_id in sorted(buckets):
+            items = buckets[bucket_id]
+            outs = bucketed_distributed_zeropower([it[3] for it in items], [it[2] for it in items],
+                                                  [it[5] for it in items], self.tp_group, self._reducer(), dtype)
+            for (meta, route, plan, _, w, _), o in zip(items, outs):
+                if wd != 0.0 and route.weight_decay:
+                    w.mul_(1.0 - lr * wd)
+                w.add_(o.to(w.dtype), alpha=-lr * orth.rms_match_scale(meta.shape))
+        if store.compute_dtype != torch.float32:
+            for e in touched:
+                e.param.data.copy_(store.master_view(sec, e))
+        return leftovers
+
     def _matrix_entry(self, i: int, sec: Section, e: StorageEntry, lr: float) -> None:
         store = self.store
         master = store.master_view(sec, e)
@@ -283,8 +359,12 @@ class Optimizer:
         logical_shape = meta.shape
         if route.backend == "dist_muon" and self.tp_size > 1:
             storage_axis = (len(meta.shape) - 1 - route.matrix_axis) if meta.transposed else route.matrix_axis
-            if self.spec.muon_tp_mode == "distributed":
-                o = _sharded_newton_schulz(u.to(torch.bfloat16), storage_axis, self.tp_group)
+            plan = self.muon_plans.get(meta.name)
+            if plan is not None and plan.execution != "duplicated":
+                from research_b200.optim.distributed_ns import bucketed_distributed_zeropower
+
+                o = bucketed_distributed_zeropower([u.to(torch.bfloat16)], [plan], [storage_axis], self.tp_group,
+                                                   self._reducer())[0]
             else:
                 full = _all_gather_axis(u.to(torch.bfloat16).contiguous(), storage_axis, self.tp_group)
                 o_full = orth.zeropower_via_newton_schulz(full)
@@ -382,25 +462,3 @@ def _all_gather_axis(x: torch.Tensor, axis: int, group) -> torch.Tensor:
     out = torch.empty((n * xt.shape[0],) + tuple(xt.shape[1:]), dtype=x.dtype, device=x.device)
     dist.all_gather_into_tensor(out, xt, group=group)
     return out.movedim(0, axis).contiguous()
-
-
-def _sharded_newton_schulz(x: torch.Tensor, shard_axis: int, group) -> torch.Tensor:
-    """Newton-Schulz on a matrix split along ``shard_axis`` over ``group``: the Gram matrix contracts over the
-    split axis, so it is the sum of the shards' Grams (one all-reduce per step); the norm is global."""
-
-    sq = x.float().pow(2).sum().reshape(1)
-    dist.all_reduce(sq, group=group)
-    x = x / torch.clamp(sq.sqrt(), min=orth.MUON_NS_EPS).to(x.dtype)
-    a, b, c = orth.MUON_NS_COEFFICIENTS
-    for _ in range(orth.MUON_NS_STEPS):
-        if shard_axis == x.dim() - 1:      # columns split: left Gram X X^T
-            gram = (x @ x.transpose(-1, -2)).float()
-            dist.all_reduce(gram, group=group)
-            gram = gram.to(x.dtype)
-            x = a * x + (b * gram + c * (gram @ gram)) @ x
-        else:                              # rows split: right Gram X^T X
-            gram = (x.transpose(-1, -2) @ x).float()
-            dist.all_reduce(gram, group=group)
-            gram = gram.to(x.dtype)
-            x = a * x + x @ (b * gram + c * (gram @ gram))
-    return x

@@ -10,6 +10,8 @@ ROOT = Path(__file__).resolve().parent.parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+# tests fail fast: a peer that never arrives is given up on after 3 s (training default: 30 s); child ranks inherit it
+os.environ.setdefault("RESEARCH_B200_PEER_WAIT_MS", "3000")
 
 
 def pytest_configure(config):
