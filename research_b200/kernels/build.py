@@ -126,6 +126,33 @@ def build_all(*, force: bool = False, verbose: bool = False, ptxas_info: bool = 
     return BuildResult(KERNEL_LIB, host_lib, True, tuple(p.name for p in cu), digest)
 
 
+def ensure_current() -> BuildResult | None:
+    """Rebuild the libraries when they are missing or were built from other sources than the ones on disk.
+
+    Called when the kernel library is loaded: a stale shared object whose exported functions no longer match the
+    Python bindings fails in confusing ways, so the sha256 of the sources is checked every time (a few milliseconds)
+    and a mismatch triggers the in-tree build.  Several ranks starting at once serialise on a lock file; the
+    first one builds, the others find the digest up to date.  Without nvcc an existing library is used as it is
+    (with a warning on stderr)."""
+
+    import fcntl
+    import sys
+
+    LIB_DIR.mkdir(parents=True, exist_ok=True)
+    with open(LIB_DIR / ".build.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            return build_all()
+        except ContractError as exc:
+            if KERNEL_LIB.exists() and "nvcc not found" in str(exc):
+                print("research_b200: nvcc not found, using the existing kernel library without checking that it "
+                      "matches the sources", file=sys.stderr)
+                return None
+            raise
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
 def build_host_only() -> Path | None:
     """Build just the host C++ library (used when only ``libb200host.so`` is missing)."""
 

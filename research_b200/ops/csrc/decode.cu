@@ -16,6 +16,7 @@
 #include <stdint.h>
 
 #include "b200.cuh"
+#include "host_util.cuh"
 
 namespace {
 

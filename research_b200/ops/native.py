@@ -39,17 +39,16 @@ def available() -> bool:
 
 
 def load() -> ctypes.CDLL:
-    """Load the kernel library, building it first when the shared object is missing."""
+    """Load the kernel library, building it first when the shared object is missing or stale."""
 
     global _lib
     if _lib is not None:
         return _lib
     with _lock:
         if _lib is None:
-            if not _LIB_PATH.exists():
-                from research_b200.kernels.build import build_all
+            from research_b200.kernels.build import ensure_current
 
-                build_all()
+            ensure_current()          # builds when missing, rebuilds when the sources changed since the last build
             if not _LIB_PATH.exists():
                 raise KernelError(f"native kernel library is missing: {_LIB_PATH}")
             lib = ctypes.CDLL(str(_LIB_PATH))
