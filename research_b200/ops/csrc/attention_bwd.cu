@@ -25,6 +25,12 @@
 // `hi` (int32 [B,Skv], non-decreasing) is the kv-side view: the last query position that can see kv k;
 // the dKV kernel masks with it alone, so it must be given whenever `lo` is.
 //
+// Context parallelism (`ring.enabled`, see ring.cuh): K and V are the staging buffers in sequence order.  The dQ
+// kernel carries the transfer CTAs that fill them and waits on a block's flag before it streams the block; the
+// dKV kernel, which runs after it, finds everything staged and ADDS its dK / dV tiles into the accumulation
+// buffer of the rank that owns those kv rows with TMA reduce-adds (bf16), own rows included, so that the
+// contributions of all ranks and of both local query chunks meet in one buffer per owner.
+//
 // Oracle: autograd of softmax(QK^T * scale) V in fp32 (reference attention:
 // models/components/attention.py:269-278).  The reference's only hand-written backward is Hopper wgmma
 // (third_party/ThunderKittens/kernels/attention/mha_h100/mha_h100.cu:254-483).
@@ -32,6 +38,7 @@
 
 #include "b200.cuh"
 #include "host_util.cuh"
+#include "ring.cuh"
 
 using namespace b200;
 
@@ -64,6 +71,13 @@ struct BwdParams {
   const float* lse;    // [B,Hq,S]
   const float* delta;  // [B,Hq,S]
   int* status;
+  b200ring::RingArgs ring;
+};
+
+// dK / dV accumulation buffers of every rank of the context group ([B, local rows, Hkv, D] bf16), as tensor maps.
+struct OwnerMaps {
+  CUtensorMap dk[b200comm::kMaxPeers];
+  CUtensorMap dv[b200comm::kMaxPeers];
 };
 
 template <int D, bool DKV>
@@ -71,7 +85,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant__ CUtensorMap tmX2,
                 const __grid_constant__ CUtensorMap tmY1, const __grid_constant__ CUtensorMap tmY2,
                 const __grid_constant__ CUtensorMap tmOut1, const __grid_constant__ CUtensorMap tmOut2,
-                const BwdParams p) {
+                const __grid_constant__ OwnerMaps owners, const BwdParams p) {
   using L = BwdSmem<D>;
   constexpr int NBOX = D / 64;
   // The swizzled tiles need 1024-byte alignment and the budget has no room for a round-up, so the
@@ -108,10 +122,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
   int b, h_res, r0;            // batch, head of the resident tile, first row of the resident tile
   int blk_begin, blk_count;    // streamed block range (per query head for DKV)
   int n_total;                 // streamed blocks in total
+  // context parallelism: the first CTAs of the dQ launch stage K/V instead of computing
+  const int n_xfer = (!DKV && p.ring.enabled) ? p.ring.n_transfer : 0;
+  const bool is_xfer = (int)blockIdx.x < n_xfer;
   {
+    const int cta = is_xfer ? 0 : (int)blockIdx.x - n_xfer;
     const int nbh = p.B * (DKV ? p.Hkv : p.Hq);
-    const int t_idx = (int)(blockIdx.x / nbh);
-    const int bh = (int)(blockIdx.x % nbh);
+    const int t_idx = cta / nbh;
+    const int bh = cta % nbh;
     if (!DKV) {
       const int qt = tiles - 1 - t_idx;
       h_res = bh % p.Hq;
@@ -137,6 +155,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
       blk_count = max(end - blk_begin, 0);
       n_total = blk_count * G;
     }
+    if (is_xfer) blk_count = n_total = 0;
   }
   const int hkv = DKV ? h_res : h_res / G;
 
@@ -174,7 +193,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
   uint8_t* sX2 = sX1 + L::TILE_BYTES;
   uint8_t* sBuf = smem + L::BUF_OFF;
 
-  if (warp == 0) {
+  if (is_xfer) {
+    // ---------------------------------------------------------------- K/V transfer (context parallelism)
+    b200ring::transfer_cta(p.ring, smem, reinterpret_cast<uint64_t*>(smem + b200ring::kSmemBytes), ab);
+  } else if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0 && n_total > 0) {
       tma_prefetch_desc(&tmX1);
@@ -191,6 +213,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
         const int g = DKV ? n / blk_count : 0;
         const int blk = blk_begin + (DKV ? n % blk_count : n);
         const int hy = DKV ? hkv * G + g : hkv;
+        if (!DKV && p.ring.enabled && !b200ring::wait_block(p.ring, b, blk, p.status)) {
+          *ab.flag = 1;   // the kv block never arrived: the other roles of this CTA stop waiting too
+          ok = false;
+          break;
+        }
         for (int which = 0; which < 2; ++which) {
           const uint32_t item = 2 * n + which;
           const int slot = item % RING;
@@ -452,7 +479,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
     //      64-column box `half` of the D columns (for D = 64 only half 0 has columns).  The softmax scale
     //      that dS left out is applied here (dQ and dK; dV has none).
     if (n_total > 0 && ok) ok = mbar_wait_warp(acc_done, 0, ab, ERR_WAIT_O_READY);
-    if ((n_total == 0 || ok) && half < NBOX) {
+    // with per-owner accumulation a tile that no local query sees adds nothing; transfer CTAs compute nothing
+    const bool skip_empty = is_xfer || (DKV && p.ring.enabled && n_total == 0);
+    if ((n_total == 0 || ok) && half < NBOX && !skip_empty) {
       tc_fence_after();
       const int slab_row = r0 + quad * 32;
       uint8_t* slab = sBuf + half * 16384 + quad * 32 * 128;
@@ -482,13 +511,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0 && slab_row < (DKV ? p.Skv : p.S)) {
-          tma_store_4d(which == 0 ? &tmOut1 : &tmOut2, slab, half * 64, h_res, slab_row, b);
+          if (DKV && p.ring.enabled) {
+            // kv rows of the sequence -> the rank that owns them and the row in its buffer
+            const int seg = slab_row / p.ring.seg_rows;
+            const int owner = p.ring.seg_owner[seg];
+            const int local = p.ring.seg_first_row[seg] + slab_row % p.ring.seg_rows;
+            tma_reduce_add_4d(which == 0 ? &owners.dk[owner] : &owners.dv[owner], slab, half * 64, h_res, local, b);
+          } else {
+            tma_store_4d(which == 0 ? &tmOut1 : &tmOut2, slab, half * 64, h_res, slab_row, b);
+          }
           tma_commit_group();
           tma_wait_group_read<0>();
         }
         __syncwarp();
       }
-      if (lane == 0) tma_wait_group<0>();
+      if (lane == 0) {
+        tma_wait_group<0>();
+        if (DKV && p.ring.enabled) __threadfence_system();   // the adds have landed at their owners
+      }
     }
   }
 
@@ -540,15 +580,16 @@ __global__ void attn_bwd_delta_kernel(const __nv_bfloat16* __restrict__ o, long 
 
 template <int D, bool DKV>
 int launch_bwd(const CUtensorMap& x1, const CUtensorMap& x2, const CUtensorMap& y1, const CUtensorMap& y2,
-               const CUtensorMap& o1, const CUtensorMap& o2, const BwdParams& p, cudaStream_t stream) {
+               const CUtensorMap& o1, const CUtensorMap& o2, const OwnerMaps& owners, const BwdParams& p,
+               cudaStream_t stream) {
   using L = BwdSmem<D>;
   auto* kern = attn_bwd_kernel<D, DKV>;
   constexpr int smem_bytes = L::TOTAL;
   static bool configured[b200host::kMaxDevices] = {};   // per kernel instantiation and device
   if (int rc = b200host::ensure_dynamic_smem(kern, smem_bytes, configured)) return rc;
   const int tiles = ((DKV ? p.Skv : p.S) + TILE - 1) / TILE;
-  const int grid = tiles * (DKV ? p.Hkv : p.Hq) * p.B;
-  kern<<<grid, NUM_THREADS, smem_bytes, stream>>>(x1, x2, y1, y2, o1, o2, p);
+  const int grid = tiles * (DKV ? p.Hkv : p.Hq) * p.B + ((!DKV && p.ring.enabled) ? p.ring.n_transfer : 0);
+  kern<<<grid, NUM_THREADS, smem_bytes, stream>>>(x1, x2, y1, y2, o1, o2, owners, p);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -558,14 +599,13 @@ int launch_bwd(const CUtensorMap& x1, const CUtensorMap& x2, const CUtensorMap& 
 // strides between tokens (`*_row`) and batches (`*_batch`), outputs included (so dq/dk/dv may be column
 // ranges of one packed gradient buffer).  dq/dk/dv are written (not accumulated).
 // delta: [B,Hq,S] fp32 scratch that this call fills.  lo / hi: int32 [B,S] or null.
-extern "C" int b200_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
-                             const void* lse, void* delta, void* dq, void* dk, void* dv, const void* lo,
-                             const void* hi, int B, int S, int Hq, int Hkv, int D, long long q_row, long long q_batch,
-                             long long k_row, long long k_batch, long long v_row, long long v_batch, long long o_row,
-                             long long o_batch, long long do_row, long long do_batch, long long dq_row,
-                             long long dq_batch, long long dk_row, long long dk_batch, long long dv_row,
-                             long long dv_batch, float scale, int causal, long long skv_and_qoff, int* status,
-                             void* stream) {
+static int attn_bwd_impl(const void* q, const void* k, const void* v, const void* o, const void* d_o, const void* lse,
+                         void* delta, void* dq, void* dk, void* dv, const void* lo, const void* hi, int B, int S,
+                         int Hq, int Hkv, int D, long long q_row, long long q_batch, long long k_row,
+                         long long k_batch, long long v_row, long long v_batch, long long o_row, long long o_batch,
+                         long long do_row, long long do_batch, long long dq_row, long long dq_batch, long long dk_row,
+                         long long dk_batch, long long dv_row, long long dv_batch, float scale, int causal,
+                         long long skv_and_qoff, const b200ring::RingHostArgs* ring, int* status, void* stream) {
   using namespace b200host;
   const int Skv = (skv_and_qoff & 0xffffffffLL) ? (int)(skv_and_qoff & 0xffffffffLL) : S;
   const int q_off = (int)(skv_and_qoff >> 32);
@@ -574,6 +614,30 @@ extern "C" int b200_attn_bwd(const void* q, const void* k, const void* v, const 
   if (D != 128 && D != 64) return RC_BAD_SHAPE;
   if (lo != nullptr && hi == nullptr) return RC_BAD_SHAPE;  // the dKV kernel masks with the kv-side bound
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const CUtensorMapDataType bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const uint64_t hs = (uint64_t)D * 2;
+  CUtensorMap tQ, tK, tV, tdO, tdQ, tdK, tdV;
+  static const OwnerMaps no_owners = {};
+  OwnerMaps owner_maps = {};
+  int rc;
+  BwdParams p{B, S, Skv, q_off, Hq, Hkv, causal, scale, (const int*)lo, (const int*)hi, (const float*)lse, (const float*)delta, status};
+  if (ring) {
+    // K and V are the staging buffers: dense [B, seq_len, Hkv, D]; dK / dV go to the owners' accumulation buffers
+    if (k_row != (long long)Hkv * D || v_row != k_row || k_batch != (long long)ring->seq_len * k_row ||
+        v_batch != k_batch || Skv > ring->seq_len || Skv % 128)
+      return RC_BAD_SHAPE;
+    if ((rc = b200ring::fill_ring_args(p.ring, *ring, const_cast<void*>(k), const_cast<void*>(v), B, Hkv, D))) return rc;
+    const uint64_t row_b = (uint64_t)Hkv * D * 2, batch_b = (uint64_t)ring->local_rows * row_b;
+    for (int r = 0; r < ring->world; ++r) {
+      if (!ring->peer_dk[r] || !ring->peer_dv[r]) return RC_BAD_ALIGNMENT;
+      if ((rc = make_map_4d(&owner_maps.dk[r], bf, ring->peer_dk[r], D, Hkv, ring->local_rows, B, hs, row_b, batch_b, 64,
+                            1, 32)))
+        return rc;
+      if ((rc = make_map_4d(&owner_maps.dv[r], bf, ring->peer_dv[r], D, Hkv, ring->local_rows, B, hs, row_b, batch_b, 64,
+                            1, 32)))
+        return rc;
+    }
+  }
   {
     const long long rows = ((long long)B * S * Hq + (256 / D) - 1) / (256 / D);  // warps of work
     long long blocks = (rows + 7) / 8;
@@ -582,24 +646,53 @@ extern "C" int b200_attn_bwd(const void* q, const void* k, const void* v, const 
                                                       (const __nv_bfloat16*)d_o, do_row, do_batch, (float*)delta, B, S,
                                                       Hq, D);
   }
-  const CUtensorMapDataType bf = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  const uint64_t hs = (uint64_t)D * 2;
-  CUtensorMap tQ, tK, tV, tdO, tdQ, tdK, tdV;
-  int rc;
   if ((rc = make_map_4d(&tQ, bf, q, D, Hq, S, B, hs, q_row * 2, q_batch * 2, 64, 1, 128))) return rc;
   if ((rc = make_map_4d(&tK, bf, k, D, Hkv, Skv, B, hs, k_row * 2, k_batch * 2, 64, 1, 128))) return rc;
   if ((rc = make_map_4d(&tV, bf, v, D, Hkv, Skv, B, hs, v_row * 2, v_batch * 2, 64, 1, 128))) return rc;
   if ((rc = make_map_4d(&tdO, bf, d_o, D, Hq, S, B, hs, do_row * 2, do_batch * 2, 64, 1, 128))) return rc;
   if ((rc = make_map_4d(&tdQ, bf, dq, D, Hq, S, B, hs, dq_row * 2, dq_batch * 2, 64, 1, 32))) return rc;
-  if ((rc = make_map_4d(&tdK, bf, dk, D, Hkv, Skv, B, hs, dk_row * 2, dk_batch * 2, 64, 1, 32))) return rc;
-  if ((rc = make_map_4d(&tdV, bf, dv, D, Hkv, Skv, B, hs, dv_row * 2, dv_batch * 2, 64, 1, 32))) return rc;
-  BwdParams p{B, S, Skv, q_off, Hq, Hkv, causal, scale, (const int*)lo, (const int*)hi, (const float*)lse, (const float*)delta, status};
-  if (D == 128) {
-    if ((rc = launch_bwd<128, false>(tQ, tdO, tK, tV, tdQ, tdQ, p, s))) return rc;
-    return launch_bwd<128, true>(tK, tV, tQ, tdO, tdK, tdV, p, s);
+  if (!ring) {
+    if ((rc = make_map_4d(&tdK, bf, dk, D, Hkv, Skv, B, hs, dk_row * 2, dk_batch * 2, 64, 1, 32))) return rc;
+    if ((rc = make_map_4d(&tdV, bf, dv, D, Hkv, Skv, B, hs, dv_row * 2, dv_batch * 2, 64, 1, 32))) return rc;
+  } else {
+    tdK = tdQ;   // never stored through: the dKV kernel adds into the owners' buffers
+    tdV = tdQ;
   }
-  if ((rc = launch_bwd<64, false>(tQ, tdO, tK, tV, tdQ, tdQ, p, s))) return rc;
-  return launch_bwd<64, true>(tK, tV, tQ, tdO, tdK, tdV, p, s);
+  const OwnerMaps& om = ring ? owner_maps : no_owners;
+  if (D == 128) {
+    if ((rc = launch_bwd<128, false>(tQ, tdO, tK, tV, tdQ, tdQ, om, p, s))) return rc;
+    return launch_bwd<128, true>(tK, tV, tQ, tdO, tdK, tdV, om, p, s);
+  }
+  if ((rc = launch_bwd<64, false>(tQ, tdO, tK, tV, tdQ, tdQ, om, p, s))) return rc;
+  return launch_bwd<64, true>(tK, tV, tQ, tdO, tdK, tdV, om, p, s);
+}
+
+extern "C" int b200_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                             const void* lse, void* delta, void* dq, void* dk, void* dv, const void* lo,
+                             const void* hi, int B, int S, int Hq, int Hkv, int D, long long q_row, long long q_batch,
+                             long long k_row, long long k_batch, long long v_row, long long v_batch, long long o_row,
+                             long long o_batch, long long do_row, long long do_batch, long long dq_row,
+                             long long dq_batch, long long dk_row, long long dk_batch, long long dv_row,
+                             long long dv_batch, float scale, int causal, long long skv_and_qoff, int* status,
+                             void* stream) {
+  return attn_bwd_impl(q, k, v, o, d_o, lse, delta, dq, dk, dv, lo, hi, B, S, Hq, Hkv, D, q_row, q_batch, k_row,
+                       k_batch, v_row, v_batch, o_row, o_batch, do_row, do_batch, dq_row, dq_batch, dk_row, dk_batch,
+                       dv_row, dv_batch, scale, causal, skv_and_qoff, nullptr, status, stream);
+}
+
+// The same for context parallelism (ring.cuh): k, v are this rank's staging buffers [B, seq_len, Hkv, D]; the dQ
+// launch stages the blocks listed in `ring` while it runs; dK and dV are ADDED into the accumulation buffers of
+// the ranks that own the kv rows (`ring->peer_dk / peer_dv`, zeroed by their owners before the launch).
+extern "C" int b200_attn_bwd_ring(const void* q, const void* k, const void* v, const void* o, const void* d_o,
+                                  const void* lse, void* delta, void* dq, const void* lo, const void* hi, int B, int S,
+                                  int Hq, int Hkv, int D, long long q_row, long long q_batch, long long k_row,
+                                  long long k_batch, long long o_row, long long o_batch, long long do_row,
+                                  long long do_batch, long long dq_row, long long dq_batch, float scale, int causal,
+                                  long long skv_and_qoff, const void* ring, int* status, void* stream) {
+  if (!ring) return b200host::RC_BAD_SHAPE;
+  return attn_bwd_impl(q, k, v, o, d_o, lse, delta, dq, nullptr, nullptr, lo, hi, B, S, Hq, Hkv, D, q_row, q_batch,
+                       k_row, k_batch, k_row, k_batch, o_row, o_batch, do_row, do_batch, dq_row, dq_batch, 0, 0, 0, 0,
+                       scale, causal, skv_and_qoff, static_cast<const b200ring::RingHostArgs*>(ring), status, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------

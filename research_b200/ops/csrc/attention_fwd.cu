@@ -13,12 +13,17 @@
 // windows, and whole kv blocks left of lo[first row] or right of the last row are skipped.
 // GQA: query head h reads kv head h / (Hq / Hkv).  Writes O [B,S,Hq,D] and LSE [B,Hq,S] (natural log).
 //
+// Context parallelism (`ring.enabled`): K and V are the staging buffers of ring.cuh; the first `n_transfer` CTAs
+// pull the rows from their owners while the others attend, and the TMA producer waits on a block's flag before it
+// loads the block.
+//
 // Oracle: the reference's attention is softmax(QK^T / sqrt(D)) V with fp32 logits and probabilities
 // cast to the compute dtype (models/components/attention.py:269-278); masks from
 // models/components/masks.py:9-48.  Its vendored Blackwell comparator (other head dims, no backward, no
 // document mask) is third_party/ThunderKittens/kernels/attention/bf16_b300_mha_causal/bf16_b300_mha_causal.cu.
 #include "b200.cuh"
 #include "host_util.cuh"
+#include "ring.cuh"
 
 using namespace b200;
 
@@ -49,6 +54,7 @@ struct FwdParams {
   const int* lo;     // [B, S] or nullptr
   float* lse;        // [B, Hq, S]
   int* status;
+  b200ring::RingArgs ring;
 };
 
 template <int D>
@@ -72,12 +78,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
+  // context parallelism: the first CTAs of the grid stage K/V instead of attending
+  const int n_xfer = p.ring.enabled ? p.ring.n_transfer : 0;
+  const bool is_xfer = (int)blockIdx.x < n_xfer;
+  const int cta = is_xfer ? 0 : (int)blockIdx.x - n_xfer;
   // heavy (late) query tiles first: causal work grows with the tile index
   const int q_tiles = (p.S + NT * TILE_M - 1) / (NT * TILE_M);
   // ... over the whole grid (all heads of the longest tile, then the next), which balances the tail
   const int nbh = p.B * p.Hq;
-  const int qt = q_tiles - 1 - (int)(blockIdx.x / nbh);
-  const int bh = blockIdx.x % nbh;
+  const int qt = q_tiles - 1 - (cta / nbh);
+  const int bh = cta % nbh;
   const int h = bh % p.Hq;
   const int b = bh / p.Hq;
   const int hkv = h / (p.Hq / p.Hkv);
@@ -88,7 +98,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   if (p.lo) kv_begin = p.lo[(long long)b * p.S + q0] / BLOCK_N;
   int kv_end = (p.Skv + BLOCK_N - 1) / BLOCK_N;
   if (p.causal) kv_end = min(kv_end, (p.q_off + min(q0 + NT * TILE_M, p.S) - 1) / BLOCK_N + 1);
-  const int n_blocks = max(kv_end - kv_begin, 0);
+  const int n_blocks = is_xfer ? 0 : max(kv_end - kv_begin, 0);
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -115,7 +125,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const uint32_t tmem_S = tmem_base;              // NT * 128 columns
   const uint32_t tmem_O = tmem_base + NT * 128;   // NT * D columns
 
-  if (warp == 0) {
+  if (is_xfer) {
+    // ---------------------------------------------------------------- K/V transfer (context parallelism)
+    b200ring::transfer_cta(p.ring, smem, reinterpret_cast<uint64_t*>(smem + b200ring::kSmemBytes), ab);
+  } else if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0 && n_blocks > 0) {
       tma_prefetch_desc(&tmQ);
@@ -132,6 +145,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const int slot = item % KV_SLOTS;
         const uint32_t ph = (item / KV_SLOTS) & 1;
         if (!mbar_wait(&kv_empty[slot], ph ^ 1, ab, ERR_WAIT_EMPTY)) { ok = false; return; }
+        if (p.ring.enabled && !b200ring::wait_block(p.ring, b, kv_begin + j, p.status)) {
+          *ab.flag = 1;   // the block never arrived: the other roles of this CTA stop waiting too
+          ok = false;
+          return;
+        }
         mbar_expect_tx(&kv_full[slot], L::TILE_D_BYTES);
         for (int bx = 0; bx < NBOX; ++bx)
           tma_load_4d(smem + L::KV_OFF + slot * L::TILE_D_BYTES + bx * 16384, tm, &kv_full[slot], bx * 64, hkv,
@@ -363,7 +381,7 @@ int launch_fwd(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap
   static bool configured[b200host::kMaxDevices] = {};   // per kernel instantiation and device
   if (int rc = b200host::ensure_dynamic_smem(kern, smem_bytes, configured)) return rc;
   const int q_tiles = (p.S + NT * TILE_M - 1) / (NT * TILE_M);
-  const int grid = q_tiles * p.Hq * p.B;
+  const int grid = q_tiles * p.Hq * p.B + (p.ring.enabled ? p.ring.n_transfer : 0);
   kern<<<grid, NUM_THREADS, smem_bytes, stream>>>(tmQ, tmK, tmV, tmO, p);
   return static_cast<int>(cudaGetLastError());
 }
@@ -374,11 +392,11 @@ int launch_fwd(const CUtensorMap& tmQ, const CUtensorMap& tmK, const CUtensorMap
 // apart); k, v: [B,Skv,Hkv,D] likewise; o: [B,S,Hq,D]; lse: [B,Hq,S] fp32; lo: [B,S] int32 or null.
 // skv_and_qoff packs the kv length and the global position of query row 0 for context-parallel callers
 // (0 = same length as the queries, offset 0): low 32 bits Skv, high 32 bits q_off (a multiple of 128).
-extern "C" int b200_attn_fwd(const void* q, const void* k, const void* v, void* o, void* lse, const void* lo, int B,
-                             int S, int Hq, int Hkv, int D, long long q_row, long long q_batch, long long k_row,
-                             long long k_batch, long long v_row, long long v_batch, long long o_row,
-                             long long o_batch, float scale, int causal, long long skv_and_qoff, int* status,
-                             void* stream) {
+static int attn_fwd_impl(const void* q, const void* k, const void* v, void* o, void* lse, const void* lo, int B, int S,
+                         int Hq, int Hkv, int D, long long q_row, long long q_batch, long long k_row,
+                         long long k_batch, long long v_row, long long v_batch, long long o_row, long long o_batch,
+                         float scale, int causal, long long skv_and_qoff, const b200ring::RingHostArgs* ring,
+                         int* status, void* stream) {
   using namespace b200host;
   const int Skv = (skv_and_qoff & 0xffffffffLL) ? (int)(skv_and_qoff & 0xffffffffLL) : S;
   const int q_off = (int)(skv_and_qoff >> 32);
@@ -393,7 +411,36 @@ extern "C" int b200_attn_fwd(const void* q, const void* k, const void* v, void* 
   if ((rc = make_map_4d(&tmV, bf, v, D, Hkv, Skv, B, (uint64_t)D * 2, v_row * 2, v_batch * 2, 64, 1, 128))) return rc;
   if ((rc = make_map_4d(&tmO, bf, o, D, Hq, S, B, (uint64_t)D * 2, o_row * 2, o_batch * 2, 64, 1, 32))) return rc;
   FwdParams p{B, S, Skv, q_off, Hq, Hkv, causal, scale * 1.4426950408889634f, (const int*)lo, (float*)lse, status};
+  if (ring) {
+    // K and V are the staging buffers: dense [B, seq_len, Hkv, D], filled by this launch's transfer CTAs
+    if (k_row != (long long)Hkv * D || v_row != k_row || k_batch != (long long)ring->seq_len * k_row ||
+        v_batch != k_batch || Skv > ring->seq_len)
+      return RC_BAD_SHAPE;
+    if ((rc = b200ring::fill_ring_args(p.ring, *ring, const_cast<void*>(k), const_cast<void*>(v), B, Hkv, D))) return rc;
+  }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (D == 128) return launch_fwd<128>(tmQ, tmK, tmV, tmO, p, s);
   return launch_fwd<64>(tmQ, tmK, tmV, tmO, p, s);
+}
+
+extern "C" int b200_attn_fwd(const void* q, const void* k, const void* v, void* o, void* lse, const void* lo, int B,
+                             int S, int Hq, int Hkv, int D, long long q_row, long long q_batch, long long k_row,
+                             long long k_batch, long long v_row, long long v_batch, long long o_row,
+                             long long o_batch, float scale, int causal, long long skv_and_qoff, int* status,
+                             void* stream) {
+  return attn_fwd_impl(q, k, v, o, lse, lo, B, S, Hq, Hkv, D, q_row, q_batch, k_row, k_batch, v_row, v_batch, o_row,
+                       o_batch, scale, causal, skv_and_qoff, nullptr, status, stream);
+}
+
+// The same with the K/V exchange of context parallelism inside the launch (ring.cuh): k, v are this rank's
+// staging buffers [B, seq_len, Hkv, D]; `ring` says which blocks to pull from which rank's buffer.
+extern "C" int b200_attn_fwd_ring(const void* q, const void* k, const void* v, void* o, void* lse, const void* lo,
+                                  int B, int S, int Hq, int Hkv, int D, long long q_row, long long q_batch,
+                                  long long k_row, long long k_batch, long long v_row, long long v_batch,
+                                  long long o_row, long long o_batch, float scale, int causal,
+                                  long long skv_and_qoff, const void* ring, int* status, void* stream) {
+  if (!ring) return b200host::RC_BAD_SHAPE;
+  return attn_fwd_impl(q, k, v, o, lse, lo, B, S, Hq, Hkv, D, q_row, q_batch, k_row, k_batch, v_row, v_batch, o_row,
+                       o_batch, scale, causal, skv_and_qoff, static_cast<const b200ring::RingHostArgs*>(ring), status,
+                       stream);
 }

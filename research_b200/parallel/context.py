@@ -7,8 +7,11 @@ rotates its own q/k chunk (positions are global), K and V chunks are exchanged o
 queries attend to the keys of their own and all earlier chunks with the flash-attention kernel's query-offset
 form, so logits never materialise and only ``(r + 1) / cp`` of the keys are visited by rank ``r``.
 
-Transport: ``all_gather`` over the cp group (NCCL on GPUs, gloo on CPU).  Backward sends every rank's
-contribution to dK/dV of the chunks it attended to back to their owners with a reduce-scatter.
+Transport on GPUs: the exchange happens inside the attention kernels (:mod:`research_b200.parallel.ring_attention`:
+transfer CTAs of the attention launch pull K/V blocks over NVLink while the other CTAs attend; dK/dV tiles are
+reduce-added into their owners' buffers from the backward kernel).  Fallback, CPU path and test oracle:
+``all_gather`` over the cp group (NCCL on GPUs, gloo on CPU) followed by the kernel, with a reduce-scatter of
+dK/dV in backward.
 
 ``parallelism.context_attention = "ulysses"`` selects the other classic form (:func:`ulysses_attention`): an
 all-to-all turns the sequence split into a head split, every rank runs ordinary causal flash attention over the
@@ -82,6 +85,14 @@ def context_parallel_attention(ex, qkv: torch.Tensor, wq, wk, positions: torch.T
     k4 = qk[:, hq * D:].reshape(B, S, hkv, D)
     v4 = qkv[:, (hq + hkv) * D:].reshape(B, S, hkv, D)
     zigzag = S % 2 == 0   # the rule of steps.train.context_positions: an even local length means the zig-zag split
+    zigzag = zigzag and len(chunks) == 2
+    from research_b200.parallel import ring_attention as ring
+
+    if Fn.use_native(qkv) and ring.ring_available(ex, q4, S, hkv, D, chunks):
+        ws = ring.workspace_for(group, B, S, hkv, D, zigzag, q4.device)
+        if ws is not None:
+            # the K/V exchange happens inside the attention launches (no all-gather, no reduce-scatter)
+            return ring.ring_attention(q4, k4, v4, lo, ws, chunks, D ** -0.5).reshape(B, S, hq * D)
     k_all = _in_sequence_order(_GatherKV.apply(k4, group), cp, S, zigzag)
     v_all = _in_sequence_order(_GatherKV.apply(v4, group), cp, S, zigzag)
     scale = D ** -0.5
