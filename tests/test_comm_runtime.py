@@ -233,7 +233,8 @@ raw = {
     "run": {"id": "fused-parity"},
     "model": {"name": "decoder", "variant": "t", "vocab_size": 1024, "hidden_size": 256, "intermediate_size": 512,
               "num_layers": 2, "num_heads": 4, "n_kv_heads": 2, "max_seq_len": 512, "init": "normal_0.02"},
-    "optimizer": {"name": flags.get("optimizer", "adamw"), "grad_clip_norm": 1.0, "schedule": {"peak_lr": 1e-3}},
+    "optimizer": {"name": flags.get("optimizer", "adamw"), "grad_clip_norm": 1.0, "schedule": {"peak_lr": 1e-3},
+                  "muon_tp_mode": flags.get("muon_tp_mode", "duplicated")},
     "data": {"train_manifest": "unused.json"},
     "training": {"seq_len": 512, "global_batch_size": 4, "target_tokens": 4 * 512 * 8, "precision": "bf16"},
     "mesh": {"axis_names": axes, "axis_sizes": sizes},
@@ -249,28 +250,40 @@ for step in range(4):
     m = trainer.train_on([batch])
     losses.append(float(m.loss))
 native.check_status()
+# the whole logical parameter tree after four steps (a collective gather: every rank takes part)
+from research_b200.runtime.state_io import collect_state_tensors
+state = collect_state_tensors(trainer)
 if rank == 0:
     print("LOSSES", json.dumps(losses))
+    np.savez(sys.argv[5], **{k: v for k, v in state.items() if k.startswith("model.")})
 dist.barrier()
+trainer.close()
 dist.destroy_process_group()
 """
 
 
-def _run_training(tmp_path, world, axes, sizes, flags, peer, port):
-    script = tmp_path / "train_ranks.py"
-    script.write_text(_TRAIN_SCRIPT)
-    # RESEARCH_B200_DEBUG=1: after every step the trainer checks the guard words behind all peer-memory buffers
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", RESEARCH_B200_PEER_COLLECTIVES="1" if peer else "0",
-               RESEARCH_B200_DEBUG="1")
+def _run_training(tmp_path, world, axes, sizes, flags, peer, port, extra_env=None):
+    """Returns ``(losses of four steps, logical parameters after them)`` of a ``world``-rank run."""
+
     import json
 
+    import numpy as np
+
+    script = tmp_path / "train_ranks.py"
+    script.write_text(_TRAIN_SCRIPT)
+    out = tmp_path / f"params_{port}.npz"
+    # RESEARCH_B200_DEBUG=1: after every step the trainer checks the guard words behind all peer-memory buffers
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", RESEARCH_B200_PEER_COLLECTIVES="1" if peer else "0",
+               RESEARCH_B200_DEBUG="1", **(extra_env or {}))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(port), str(script), str(ROOT), json.dumps(axes),
-           json.dumps(sizes), json.dumps(flags)]
+           json.dumps(sizes), json.dumps(flags), str(out)]
     proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
     line = [l for l in proc.stdout.splitlines() if l.startswith("LOSSES")][-1]
-    return json.loads(line.split(" ", 1)[1])
+    with np.load(out) as data:
+        params = {k: data[k] for k in data.files}
+    return json.loads(line.split(" ", 1)[1]), params
 
 
 @pytest.mark.gpu
@@ -290,16 +303,40 @@ def _run_training(tmp_path, world, axes, sizes, flags, peer, port):
             "initial_dense_layers": 0, "local_window": 512, "local_layers_per_global": 1, "norm_policy": "afmoe_dual",
             "moe": {"num_experts": 8, "top_k": 2, "expert_intermediate_size": 256, "num_shared_experts": 1,
                     "capacity_factor": 2.0}}}}),
+    # Newton-Schulz on tensor-parallel shards: packed Gram reductions through the symmetric arena against NCCL
+    ("tp2_muon_distributed", ["tp"], [2], {"parallelism": {"mode": "ddp", "tensor_parallel": True},
+                                           "optimizer": "muon", "muon_tp_mode": "distributed"}),
+    # context parallelism: K/V exchange inside the attention kernels against all-gather + reduce-scatter
+    ("cp2_ring", ["cp"], [2], {"parallelism": {"mode": "ddp", "context_parallel": True},
+                               "model": {"attention_doc_mask": False}}),
+    # the same FSDP run with the arena bound to an NVLink multicast object (multimem reduce-scatter / all-gather)
+    ("fsdp2_muon_nvls", ["fsdp"], [2], {"parallelism": {"mode": "fsdp"}, "optimizer": "muon",
+                                        "env": {"RESEARCH_B200_NVLS": "1"}}),
 ])
 def test_training_with_peer_memory_kernels_matches_nccl_path(tmp_path, name, axes, sizes, flags):
+    """Four optimizer steps through the peer-memory kernels and through NCCL: the losses agree and so does every
+    logical parameter afterwards (a gradient that is wrong but small would move the parameters apart)."""
+
     if torch.cuda.device_count() < 2:
         pytest.skip("needs at least two GPUs")
-    fused = _run_training(tmp_path, 2, axes, sizes, flags, True, 29741)
-    plain = _run_training(tmp_path, 2, axes, sizes, flags, False, 29743)
+    extra = flags.get("env")
+    fused, p_fused = _run_training(tmp_path, 2, axes, sizes, flags, True, 29741, extra)
+    plain, p_plain = _run_training(tmp_path, 2, axes, sizes, flags, False, 29743)
     assert len(fused) == len(plain) == 4
     for a, b in zip(fused, plain):
         assert abs(a - b) <= 2e-2 * max(1.0, abs(b)), (name, fused, plain)
     assert fused[-1] < fused[0]
+    assert set(p_fused) == set(p_plain) and p_fused
+    import numpy as np
+
+    for key, want in p_plain.items():
+        got = p_fused[key]
+        # Four steps at lr 1e-3 move a weight by up to 4e-3.  Adam-style updates turn a rounding-level difference of
+        # a tiny gradient into a full-size step for that one element, so single elements may differ by a step or
+        # two; a wrong gradient moves whole tensors, which the mean difference catches.
+        diff = np.abs(got.astype(np.float64) - want.astype(np.float64))
+        assert diff.mean() <= 2e-4, (name, key, "mean", float(diff.mean()))
+        assert diff.max() <= 8e-3, (name, key, "max", float(diff.max()))
 
 
 @pytest.mark.gpu
