@@ -20,6 +20,9 @@ class Batch:
     loss_mask: Any
     doc_ids: Any | None = None        # first document id of each row
     token_doc_ids: Any | None = None  # document id of every input token (document-aware pipelines)
+    # Number of unmasked target tokens of the WHOLE batch.  Set by pipelines that materialise only the rows of this
+    # rank (the other rows are zero-filled); consumers that need the global count must use it when it is present.
+    mask_count: float | None = None
 
     @property
     def shape(self) -> tuple[int, ...]:

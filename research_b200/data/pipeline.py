@@ -226,6 +226,20 @@ class _PreparedPipelineBase:
         self.num_records = 0
         self.source_summary = ""
         self.sampler_summary = ""
+        # rows of every batch whose tokens this process needs (None: all).  The sampling state always advances
+        # over the whole batch, so the order stays the same on every rank; only the token reads are skipped.
+        self.local_rows: range | None = None
+
+    def set_local_rows(self, rows: range | None) -> None:
+        """Materialise only ``rows`` of each batch (a rank of a data-parallel job needs only its own rows); the
+        other rows come back zero-filled and ``Batch.mask_count`` carries the whole batch's unmasked-token count."""
+
+        if rows is not None and (rows.start < 0 or rows.stop > self.batch_size or rows.step != 1):
+            raise ContractError(f"local rows {rows} are not inside a batch of {self.batch_size}")
+        self.local_rows = rows
+
+    def _is_local(self, row: int) -> bool:
+        return self.local_rows is None or row in self.local_rows
 
     # -- state plumbing ----------------------------------------------------------------------------
     def _make_state(self, backend_state: Mapping[str, Any], next_record_index: int, epoch: int) -> DataPipelineState:
@@ -345,9 +359,10 @@ class PreparedTokenWindowPipeline(_PreparedPipelineBase):
     def initial_state(self) -> DataPipelineState:
         return self._make_state({"next_index": 0}, 0, 0)
 
-    def _record(self, key: int) -> tuple[np.ndarray, int, int | None]:
+    def _record(self, key: int, materialise: bool = True) -> tuple[np.ndarray, int, int | None]:
         start = self.split_start + key * self.seq_len
-        tokens = self.reader.read(start, start + self.seq_len + 1)
+        tokens = self.reader.read(start, start + self.seq_len + 1) if materialise else \
+            np.zeros(self.seq_len + 1, dtype=np.int32)
         doc_id = None
         if self.document_offsets is not None:
             doc_id = int(np.searchsorted(self.document_offsets, start, side="right")) - 1
@@ -361,14 +376,15 @@ class PreparedTokenWindowPipeline(_PreparedPipelineBase):
         keys = range(first, first + self.batch_size)
         if self._perm is not None:
             keys = [int(self._perm[k]) for k in keys]
-        rows = [self._record(int(k)) for k in keys]
+        rows = [self._record(int(k), self._is_local(i)) for i, k in enumerate(keys)]
         tokens = np.stack([r[0] for r in rows]).astype(np.int32)
         starts = tuple(r[1] for r in rows)
         doc_ids = None
         if self.document_offsets is not None:
             doc_ids = np.asarray([r[2] for r in rows], dtype=np.int32)
         batch = Batch(input_ids=tokens[:, :-1].copy(), target_ids=tokens[:, 1:].copy(),
-                      loss_mask=np.ones((self.batch_size, self.seq_len), dtype=np.bool_), doc_ids=doc_ids)
+                      loss_mask=np.ones((self.batch_size, self.seq_len), dtype=np.bool_), doc_ids=doc_ids,
+                      mask_count=None if self.local_rows is None else float(self.batch_size * self.seq_len))
         nxt = first + self.batch_size
         return PipelineBatch(
             batch=batch,
@@ -459,7 +475,10 @@ class PreparedTokenDocumentBufferPipeline(_PreparedPipelineBase):
             start, end = self.document_spans[doc]
             backend["active"].append({"doc_id": int(doc), "cursor": int(start), "end": int(end)})
 
-    def _next_record(self, backend: dict[str, Any], rng: np.random.Generator):
+    def _next_record(self, backend: dict[str, Any], rng: np.random.Generator, materialise: bool = True):
+        """One packed row.  ``materialise=False`` advances the sampler exactly as usual but reads no tokens: the row
+        comes back zero-filled, with the number of unmasked targets it would have had."""
+
         need = self.seq_len + 1
         pieces: list[np.ndarray] = []
         piece_docs: list[tuple[int, int]] = []  # (doc_id, count)
@@ -475,7 +494,8 @@ class PreparedTokenDocumentBufferPipeline(_PreparedPipelineBase):
             entry = active[idx]
             cursor, end, doc_id = int(entry["cursor"]), int(entry["end"]), int(entry["doc_id"])
             take = min(need - got, end - cursor)
-            pieces.append(self.reader.read(cursor, cursor + take))
+            if materialise:
+                pieces.append(self.reader.read(cursor, cursor + take))
             piece_docs.append((doc_id, take))
             if first_offset is None:
                 first_offset = cursor
@@ -486,11 +506,16 @@ class PreparedTokenDocumentBufferPipeline(_PreparedPipelineBase):
                 del active[idx]
             else:
                 active[idx] = {"doc_id": doc_id, "cursor": cursor, "end": end}
+        docs = np.asarray([d for d, _ in piece_docs], dtype=np.int64)
+        # a target is masked where the document changes: once per pair of neighbouring pieces of different documents
+        unmasked = self.seq_len - int(np.count_nonzero(docs[1:] != docs[:-1]))
+        if not materialise:
+            return (np.zeros(need, dtype=np.int32), np.zeros(self.seq_len, dtype=np.bool_),
+                    np.zeros(need, dtype=np.int64), int(piece_docs[0][0]), int(first_offset), int(max_offset), unmasked)
         tokens = np.concatenate(pieces).astype(np.int32)
-        token_docs = np.repeat(np.asarray([d for d, _ in piece_docs], dtype=np.int64),
-                               np.asarray([c for _, c in piece_docs], dtype=np.int64))
+        token_docs = np.repeat(docs, np.asarray([c for _, c in piece_docs], dtype=np.int64))
         loss_mask = token_docs[:-1] == token_docs[1:]
-        return tokens, loss_mask, token_docs, int(piece_docs[0][0]), int(first_offset), int(max_offset)
+        return tokens, loss_mask, token_docs, int(piece_docs[0][0]), int(first_offset), int(max_offset), unmasked
 
     def next_batch(self, state: DataPipelineState) -> PipelineBatch:
         self._validate_state(state)
@@ -498,9 +523,9 @@ class PreparedTokenDocumentBufferPipeline(_PreparedPipelineBase):
         rng = np.random.default_rng()
         rng.bit_generator.state = backend["rng_state"]
         rows = []
-        for _ in range(self.batch_size):
+        for row in range(self.batch_size):
             try:
-                rows.append(self._next_record(backend, rng))
+                rows.append(self._next_record(backend, rng, self._is_local(row)))
             except StopIteration as exc:
                 raise StopIteration(
                     f"not enough document-buffer tokens left in {self.split} split for one full batch"
@@ -510,7 +535,8 @@ class PreparedTokenDocumentBufferPipeline(_PreparedPipelineBase):
         doc_ids = np.asarray([r[3] for r in rows], dtype=np.int32)
         batch = Batch(input_ids=tokens[:, :-1].copy(), target_ids=tokens[:, 1:].copy(),
                       loss_mask=np.stack([r[1] for r in rows]).astype(np.bool_), doc_ids=doc_ids,
-                      token_doc_ids=np.stack([r[2][:-1] for r in rows]).astype(np.int32))
+                      token_doc_ids=np.stack([r[2][:-1] for r in rows]).astype(np.int32),
+                      mask_count=None if self.local_rows is None else float(sum(r[6] for r in rows)))
         nxt = state.next_record_index + self.batch_size
         starts = tuple(r[4] for r in rows)
         return PipelineBatch(

@@ -175,11 +175,18 @@ class Trainer:
         if manifest is None:
             raise ContractError("a prepared manifest is required for this split")
         order = d.order if split == "train" else "sequential"
-        return build_prepared_token_pipeline(
+        pipeline = build_prepared_token_pipeline(
             manifest, tokenizer_id=d.tokenizer_id, split=split, seq_len=t.seq_len, batch_size=t.global_batch_size,
             order=order, shuffle_seed=d.shuffle_seed if split == "train" else None,
             document_buffer_size=d.document_buffer_size if split == "train" else None,
             document_refill_size=d.document_refill_size if split == "train" else None)
+        if split == "train" and self.mesh.world_size > 1 and hasattr(pipeline, "set_local_rows"):
+            # every rank walks the same sampling sequence but reads only the tokens of its own rows
+            from research_b200.steps.train import local_batch_slices
+
+            rows, _ = local_batch_slices(self.mesh, t.global_batch_size, t.seq_len)
+            pipeline.set_local_rows(range(rows.start, rows.stop))
+        return pipeline
 
     def next_accumulated_batch(self) -> list[Batch]:
         """The microbatches of one optimizer step (reference: runtime/training.py:744-757)."""

@@ -177,7 +177,9 @@ class TrainStep:
         mesh = self.mesh
         B, S = batches[0].input_ids.shape
         rows, cols = local_batch_slices(mesh, B, S)
-        global_counts = [float(np.asarray(b.loss_mask).sum()) for b in batches]
+        # a pipeline that materialises only this rank's rows says how many targets the whole batch leaves unmasked
+        global_counts = [float(np.asarray(b.loss_mask).sum()) if getattr(b, "mask_count", None) is None
+                         else float(b.mask_count) for b in batches]
         global_count = max(sum(global_counts), 1.0)
         grad_scale = 1.0 / global_count
         dp_world = mesh.size("data") * mesh.size("fsdp") * mesh.size("cp")

@@ -187,3 +187,37 @@ def test_native_window_gather_matches_numpy(tmp_path):
     for r, s in enumerate(starts):
         want = read_token_range(manifest, int(s), int(s) + 33).astype(np.int32)
         assert np.array_equal(inp[r], want[:-1]) and np.array_equal(tgt[r], want[1:])
+
+
+@pytest.mark.parametrize("order", ["sequential", "shuffle", "document_buffer"])
+def test_local_rows_keep_the_order_and_read_only_their_tokens(tmp_path, order):
+    """A rank of a data-parallel job materialises only its rows: those rows, the pipeline state after every batch
+    and the batch's unmasked-token count are the same as when every row is read."""
+
+    manifest = tiny_dataset(tmp_path, documents=400)
+    kw = dict(tokenizer_id=None, split="train", seq_len=32, batch_size=8, order=order,
+              shuffle_seed=None if order == "sequential" else 3,
+              document_buffer_size=8 if order == "document_buffer" else None,
+              document_refill_size=8 if order == "document_buffer" else None)
+    full = build_prepared_token_pipeline(manifest, **kw)
+    part = build_prepared_token_pipeline(manifest, **kw)
+    part.set_local_rows(range(2, 4))
+    reads = []
+    original = part.reader.read
+    part.reader.read = lambda a, b: (reads.append(b - a), original(a, b))[1]
+    s_full, s_part = full.initial_state(), part.initial_state()
+    for _ in range(5):
+        a, b = full.next_batch(s_full), part.next_batch(s_part)
+        s_full, s_part = a.state, b.state
+        assert full.state_to_json(s_full) == part.state_to_json(s_part)
+        assert a.provenance == b.provenance
+        for name in ("input_ids", "target_ids", "loss_mask"):
+            assert np.array_equal(getattr(a.batch, name)[2:4], getattr(b.batch, name)[2:4]), name
+        assert not b.batch.input_ids[:2].any() and not b.batch.input_ids[4:].any()
+        assert b.batch.mask_count == float(np.asarray(a.batch.loss_mask).sum())
+        assert a.batch.mask_count is None
+        if a.batch.token_doc_ids is not None:
+            assert np.array_equal(a.batch.token_doc_ids[2:4], b.batch.token_doc_ids[2:4])
+    assert sum(reads) == 5 * 2 * 33                       # two rows of seq_len + 1 tokens per batch, nothing else
+    with pytest.raises(ContractError, match="not inside a batch"):
+        part.set_local_rows(range(6, 10))
