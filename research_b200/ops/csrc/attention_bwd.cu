@@ -195,7 +195,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
 
   if (is_xfer) {
     // ---------------------------------------------------------------- K/V transfer (context parallelism)
-    b200ring::transfer_cta(p.ring, smem, reinterpret_cast<uint64_t*>(smem + b200ring::kSmemBytes), ab);
+    // buffers and barriers of the copy pipelines sit in front of this kernel's statistics and barriers
+    b200ring::transfer_cta<b200ring::pipes_for_window(L::STAT_OFF)>(p.ring, smem, ab);
   } else if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0 && n_total > 0) {

@@ -127,7 +127,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   if (is_xfer) {
     // ---------------------------------------------------------------- K/V transfer (context parallelism)
-    b200ring::transfer_cta(p.ring, smem, reinterpret_cast<uint64_t*>(smem + b200ring::kSmemBytes), ab);
+    // buffers and barriers of the copy pipelines sit in front of this kernel's own barriers (L::BAR_OFF)
+    b200ring::transfer_cta<b200ring::pipes_for_window(L::BAR_OFF)>(p.ring, smem, ab);
   } else if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0 && n_blocks > 0) {

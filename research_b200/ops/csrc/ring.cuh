@@ -26,11 +26,19 @@ namespace b200ring {
 using namespace b200;
 using namespace b200comm;
 
-constexpr int kPipes = 4;            // copy pipelines per transfer CTA, one elected thread each
+constexpr int kMaxPipes = 4;         // copy pipelines per transfer CTA at most, one elected thread each
 constexpr int kBufs = 3;             // shared-memory buffers per pipeline
 constexpr int kLag = 1;              // a chunk is stored kLag iterations after its load was issued
 constexpr int kChunkBytes = 16384;   // bytes per bulk copy
-constexpr int kSmemBytes = kPipes * kBufs * kChunkBytes;   // 192 KB, the front of the kernel's dynamic window
+constexpr int kPipeBytes = kBufs * kChunkBytes;
+
+// Pipelines that fit into the first `window_bytes` of a kernel's dynamic shared memory (the part in front of the
+// kernel's own barriers), leaving room for the pipelines' mbarriers behind the buffers.  The attention kernels
+// size their window by head dimension, so head dimension 64 gets fewer pipelines than 128.
+constexpr int pipes_for_window(int window_bytes) {
+  const int fit = (window_bytes - kMaxPipes * kBufs * 8) / kPipeBytes;
+  return fit > kMaxPipes ? kMaxPipes : fit;
+}
 constexpr int kMaxSegments = 16;     // 2 * kMaxPeers sequence segments (zig-zag split)
 
 struct RingArgs {
@@ -65,9 +73,13 @@ __device__ __forceinline__ bool wait_block(const RingArgs& r, int batch, int blo
   return true;
 }
 
-// Body of a transfer CTA.  `smem`: kSmemBytes of 128-byte aligned shared memory; `bars`: kPipes * kBufs mbarriers
-// that nothing else uses.  Called by every thread of the CTA.
-__device__ __forceinline__ void transfer_cta(const RingArgs& r, uint8_t* smem, uint64_t* bars, const AbortCtx& ab) {
+// Body of a transfer CTA.  `smem`: PIPES * kPipeBytes of 128-byte aligned shared memory followed by PIPES * kBufs
+// mbarriers, all of it unused by anything else in this CTA.  Called by every thread of the CTA.
+template <int PIPES>
+__device__ __forceinline__ void transfer_cta(const RingArgs& r, uint8_t* smem, const AbortCtx& ab) {
+  static_assert(PIPES >= 1 && PIPES <= kMaxPipes, "the shared-memory window holds no copy pipeline");
+  constexpr int kPipes = PIPES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + PIPES * kPipeBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (blockIdx.x == 0 && (int)threadIdx.x < r.world && (int)threadIdx.x != r.rank) {
     __threadfence_system();

@@ -85,7 +85,6 @@ def context_parallel_attention(ex, qkv: torch.Tensor, wq, wk, positions: torch.T
     k4 = qk[:, hq * D:].reshape(B, S, hkv, D)
     v4 = qkv[:, (hq + hkv) * D:].reshape(B, S, hkv, D)
     zigzag = S % 2 == 0   # the rule of steps.train.context_positions: an even local length means the zig-zag split
-    zigzag = zigzag and len(chunks) == 2
     from research_b200.parallel import ring_attention as ring
 
     if Fn.use_native(qkv) and ring.ring_available(ex, q4, S, hkv, D, chunks):

@@ -79,7 +79,7 @@ def benchmark_component(component: str, *, warmup: int = 3, iters: int = 10, art
     elif component == "muon":
         from research_b200.runtime.muon_bench import benchmark_muon
 
-        report = benchmark_muon(warmup=warmup, iters=iters)
+        report = benchmark_muon(warmup=warmup, iters=iters, artifact_dir=artifact_dir)
     else:
         raise ContractError(f"unknown benchmark component {component!r}")
     if artifact_dir:

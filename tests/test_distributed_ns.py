@@ -109,3 +109,34 @@ def test_training_with_distributed_muon_matches_one_process(tmp_path, tp_mode):
             assert err <= 4e-3 * (1.0 + want.abs().max().item()), (name, err)
     for name, t in results[0]["model"].items():
         assert torch.equal(t, results[1]["model"][name]), name
+
+
+def _selector_worker(rank, world):
+    from research_b200.runtime.muon_bench import benchmark_muon
+
+    return benchmark_muon(warmup=1, iters=2, cases="leaves")
+
+
+def test_selector_checks_every_candidate_and_picks_one():
+    from research_b200.runtime import muon_bench as mb
+
+    assert mb.eligible_executions((1024, 256), 1, 4) == ("duplicated", "distributed_large_gram", "distributed_exchange")
+    assert mb.eligible_executions((1024, 4096), 1, 4) == ("duplicated", "distributed_direct")
+    assert mb.eligible_executions((4096, 1024), 0, 4) == ("duplicated", "distributed_direct")
+    assert mb.eligible_executions((1024, 1024), 0, 4) == ("duplicated", "distributed_large_gram", "distributed_exchange")
+    assert len(mb.calibration_bucket_cases()) == 14 and len(mb.PRODUCTION_BUCKETS) == 7
+    assert mb.UPDATE_ATOL == pytest.approx(1.2e-2) and mb.PARAM_ATOL == pytest.approx(2.5e-2)
+    reports = run_gloo(2, _selector_worker)
+    report = reports[0]
+    assert report["tp_size"] == 2 and len(report["cases"]) == 7 and report["all_selected_pass"]
+    for case in report["cases"]:
+        by = {c["execution"]: c for c in case["candidates"]}
+        assert by["duplicated"]["max_update_abs_error"] == 0.0 and by["duplicated"]["correctness_gate"]
+        for name, c in by.items():
+            assert c["finite"] and c["momentum_exact"] and c["deterministic"], (case["case"], name, c)
+            assert c["replica_max_abs_error"] == 0.0 and c["correctness_gate"], (case["case"], name, c)
+            assert c["timing_ms"]["min"] <= c["timing_ms"]["median"] <= c["timing_ms"]["max"]
+        assert case["selected"] in by
+    kv = next(c for c in report["cases"] if c["case"] == "attention_kv")
+    assert {c["execution"] for c in kv["candidates"]} == {"duplicated", "distributed_large_gram", "distributed_exchange"}
+    assert reports[1]["selection"] == report["selection"]              # every rank reaches the same verdict
