@@ -214,6 +214,7 @@ PARALLELISM_FIELDS: tuple[Field, ...] = (
     ("expert_parallel", _bool, False),
     ("expert_parallel_axis", _str, "auto"),
     ("context_attention", _str, "gather"),
+    ("fsdp_resident", _bool, True),
 )
 ARTIFACT_FIELDS: tuple[Field, ...] = (
     ("wandb_enabled", _bool, False),

@@ -454,9 +454,15 @@ class ParallelismSpec:
     expert_parallel: bool = False
     expert_parallel_axis: str = "auto"
     context_attention: str = "gather"    # "gather": K/V all-gather; "ulysses": head <-> sequence all-to-all
+    # false: with mode="fsdp" the compute copy of the weights is kept only where it is owned and every layer's
+    # weights are fetched from their owners right before the layer runs (ZeRO-3); true keeps them on every rank
+    fsdp_resident: bool = True
 
     def __post_init__(self) -> None:
         _one_of("parallelism.mode", self.mode, PARALLELISM_MODES)
+        _bool("parallelism.fsdp_resident", self.fsdp_resident)
+        if not self.fsdp_resident and self.mode != "fsdp":
+            raise ContractError("parallelism.fsdp_resident=false requires parallelism.mode='fsdp'")
         _one_of("parallelism.context_attention", self.context_attention, ("gather", "ulysses"))
         _bool("parallelism.tensor_parallel", self.tensor_parallel)
         _bool("parallelism.context_parallel", self.context_parallel)

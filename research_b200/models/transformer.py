@@ -255,6 +255,8 @@ class TransformerLM(nn.Module):
         # called with a layer index once every kernel of that layer's backward pass has been issued (the parameter
         # store starts that layer's gradient reduction from it); set per forward pass by the training step
         self.layer_backward_hook = None
+        # called with a layer index right before that layer runs forward (weights sharded at rest are fetched by it)
+        self.layer_prepare = None
 
     # ---- helpers ---------------------------------------------------------------------------------
     def head_weight(self) -> torch.Tensor:
@@ -304,12 +306,17 @@ class TransformerLM(nn.Module):
             if hook is not None and x.requires_grad:
                 # the gradient of a layer's input is the last thing its backward pass produces
                 x.register_hook(lambda grad, index=index, hook=hook: hook(index))
+            if self.layer_prepare is not None:
+                self.layer_prepare(index)
             if remat:
                 x, delta, aux, stats = checkpoint(layer, x, delta, inp, ex, use_reentrant=False)
             else:
                 x, delta, aux, stats = layer(x, delta, inp, ex)
             aux_all.extend(aux)
             stats_all.extend(stats)
+        if hook is not None and x.requires_grad:
+            # fires before the last layer's backward pass starts ("every layer from len(layers) up is done")
+            x.register_hook(lambda grad, n=len(self.layers), hook=hook: hook(n))
         h, _ = self.norm.add_forward(x, delta)
         return h, tuple(aux_all), tuple(stats_all)
 
@@ -343,6 +350,8 @@ class TransformerLM(nn.Module):
         x = Fn.embedding(token_ids, self.embed, self.embed_scale, self.compute_dtype)
         delta = None
         for li, layer in enumerate(self.layers):
+            if self.layer_prepare is not None:
+                self.layer_prepare(li)
             def attend(attn: Attention, h, li=li):
                 q, k, v, x2 = attn.project_qkv(h, positions)
                 window = attn.cfg.local_window if attn.cfg.mask == "sliding_window" else None

@@ -347,6 +347,28 @@ all_gather_nvls_kernel(const PeerPtrs pp, const uint4* __restrict__ own, uint4* 
   finish_and_wait_done(pp, world, rank, epoch, counter, status);
 }
 
+// Plain copies of up to a few dozen byte ranges in one launch (sources may be peers' arenas).  No flags: the caller
+// orders the launch after whatever wrote the sources (a barrier over the ranks, stream order locally).
+struct CopyPiece {
+  const void* src;
+  void* dst;
+  long long bytes;
+};
+__global__ void __launch_bounds__(256) copy_pieces_kernel(const CopyPiece* __restrict__ pieces) {
+  const CopyPiece pc = pieces[blockIdx.y];
+  const long long n16 = pc.bytes >> 4;
+  const uint4* s = reinterpret_cast<const uint4*>(pc.src);
+  uint4* d = reinterpret_cast<uint4*>(pc.dst);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (long long)gridDim.x * blockDim.x)
+    d[i] = s[i];
+  if (blockIdx.x == 0) {   // the last bytes of a range whose length is not a multiple of 16
+    const long long tail = pc.bytes & 15;
+    if ((long long)threadIdx.x < tail)
+      reinterpret_cast<uint8_t*>(pc.dst)[(n16 << 4) + threadIdx.x] =
+          reinterpret_cast<const uint8_t*>(pc.src)[(n16 << 4) + threadIdx.x];
+  }
+}
+
 // Barrier over the ranks of an arena: announce epoch, wait (bounded) for everybody else's announcement.
 __global__ void peer_barrier_kernel(const PeerPtrs pp, int world, int rank, uint32_t epoch, int* status) {
   if (threadIdx.x < world && (int)threadIdx.x != rank) {
@@ -510,6 +532,15 @@ int b200c_all_gather_nvls(const void* own, void* mc_dst, long long bytes_per_ran
   all_gather_nvls_kernel<<<grid, 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       pp, static_cast<const uint4*>(own), static_cast<uint4*>(mc_dst), n16, static_cast<uint32_t*>(scratch), world,
       rank, epoch, status);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// table: device array of n_pieces {src, dst, bytes} records (16-byte aligned addresses).  Used to bring the weight
+// shards of one layer from their owners' arenas into the local layer buffer.
+int b200c_copy_pieces(const void* table, int n_pieces, int ctas_per_piece, void* stream) {
+  if (!table || n_pieces <= 0 || n_pieces > 65535 || ctas_per_piece <= 0) return -2;
+  copy_pieces_kernel<<<dim3(ctas_per_piece, n_pieces), 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      static_cast<const CopyPiece*>(table));
   return static_cast<int>(cudaGetLastError());
 }
 

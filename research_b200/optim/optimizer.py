@@ -175,7 +175,7 @@ class Optimizer:
         step = self.count + 1
         separate = store.compute_dtype != torch.float32
         if p.is_cuda and Fn.native_enabled():
-            shadow = store.compute_arena[lo:hi] if separate else None
+            shadow = store.shadow(lo, hi) if separate else None
             native.adamw(p, st["mu"], st["nu"], g, shadow, self._clip, lr, ADAMW_B1, ADAMW_B2, ADAMW_EPS, wd, step)
             return
         gs = g * self._clip
@@ -185,7 +185,7 @@ class Optimizer:
         vhat = st["nu"] / (1 - ADAMW_B2 ** step)
         p.sub_(lr * (mhat / (vhat.sqrt() + ADAMW_EPS) + wd * p))
         if separate:
-            store.compute_arena[lo:hi].copy_(p)
+            store.shadow(lo, hi).copy_(p)
 
     # ---- matrix optimizers -------------------------------------------------------------------------
     def _fast_muon_ok(self) -> bool:
@@ -252,7 +252,7 @@ class Optimizer:
         for e, meta, first, batch, stride in items:
             decay = 1.0 - lr * wd if self.routes[meta.name].weight_decay else 1.0
             native.muon_apply_batched(sec.master[e.offset - lo + first:], out[at:],
-                                      store.compute_arena[e.offset + first:], per, stride, batch, decay, step)
+                                      store.shadow(e.offset + first), per, stride, batch, decay, step)
             at += batch
 
     # ---- distributed Muon over the tensor-parallel group ---------------------------------------------
@@ -324,7 +324,7 @@ class Optimizer:
                 w.add_(o.to(w.dtype), alpha=-lr * orth.rms_match_scale(meta.shape))
         if store.compute_dtype != torch.float32:
             for e in touched:
-                e.param.data.copy_(store.master_view(sec, e))
+                store.write_entry_shadow(e, store.master_view(sec, e))
         return leftovers
 
     def _matrix_entry(self, i: int, sec: Section, e: StorageEntry, lr: float) -> None:
@@ -350,7 +350,7 @@ class Optimizer:
             else:
                 self._muon_update(meta, route, g, m, w, lr, decay)
         if store.compute_dtype != torch.float32:
-            e.param.data.copy_(master)
+            store.write_entry_shadow(e, master)
 
     def _muon_update(self, meta, route, g, m, w, lr: float, wd: float) -> None:
         m.mul_(orth.MUON_MOMENTUM).add_(g, alpha=1.0 - orth.MUON_MOMENTUM)
@@ -420,7 +420,7 @@ class Optimizer:
             w3.scatter_add_(1 + axis, gidx, o.float() * (-scale))
             m3.scatter_(1 + axis, gidx, selected * orth.DION2_EF_DECAY)
         if store.compute_dtype != torch.float32:
-            e.param.data.copy_(master)
+            store.write_entry_shadow(e, master)
         return True
 
     def _dion2_update(self, meta, route, g, m, w, lr: float, wd: float) -> None:

@@ -13,6 +13,13 @@ The reference expresses placement as per-leaf ``NamedSharding`` s that XLA turns
   all-gathered back into the arena.
 
 Sections group parameters that share an optimizer backend and the same set of gradient-reduction groups.
+
+``parallelism.fsdp_resident = false`` (ZeRO-3): the compute copy of a sharded section is kept only where it is owned
+(each rank its element range or its owner block, 1/N of the section).  The weights of one transformer layer are
+brought from their owners into one of two layer buffers right before the layer runs, forward and backward, over
+NVLink peer loads on a side stream while the previous layer computes (NCCL / gloo collectives off CUDA); embeddings,
+the final norm and the lm_head are gathered once per step.  The reference shards every tagged parameter along its
+``fsdp_axis`` and lets XLA gather it at use (src/jaxtitan/mesh/sharding.py:445-501).
 """
 
 from __future__ import annotations
@@ -81,6 +88,7 @@ class Section:
     # block (entries of a block are laid out in backward order, so every layer is one contiguous range)
     bucket_ranges: dict = field(default_factory=dict)
     bucket_layers: tuple = ()       # all layers that have matrices in this section, in backward order (every rank)
+    rest_start: int = 0             # weights sharded at rest: where this rank's part of the section starts
 
     def local_range(self, shard_rank: int, shard_size: int) -> tuple[int, int]:
         if self.shard_axis is None or shard_size == 1:
@@ -91,13 +99,15 @@ class Section:
 
 class ParamStore:
     def __init__(self, result: ModelBuildResult, mesh: MeshContext, *, mode: str, compute_dtype: torch.dtype,
-                 backend_of: dict[str, str], ep_axis: str | None = None, decay_of: dict[str, bool] | None = None):
+                 backend_of: dict[str, str], ep_axis: str | None = None, decay_of: dict[str, bool] | None = None,
+                 resident: bool = True):
         self.result = result
         self.mesh = mesh
         self.mode = mode
         self.compute_dtype = compute_dtype
         self.device = next(result.model.parameters()).device
         self.ep_axis = ep_axis
+        self.resident = bool(resident)
         by_storage: dict[str, list[ParamMeta]] = {}
         for meta in result.metadata:
             by_storage.setdefault(meta.storage, []).append(meta)
@@ -130,7 +140,12 @@ class ParamStore:
             self.entries.append(StorageEntry(name, param, metas, backend, tuple(axes), shard_axis,
                                              numel=param.numel(), decay=decays.pop() if backend == "adamw" else True))
         self._layout()
-        self._materialise()
+        if not self.resident and not any(self._sharded(sec) for sec in self.sections):
+            self.resident = True            # nothing is split over a shard axis: there is nothing to keep away
+        if self.resident:
+            self._materialise()
+        else:
+            self._materialise_sharded()
 
     # ---- layout ----------------------------------------------------------------------------------
     def _layout(self) -> None:
@@ -246,6 +261,259 @@ class ParamStore:
                 lo, hi = self.local_master_range(sec)
                 sec.master = self.compute_arena[lo:hi]
         self.result.model.compute_dtype = self.compute_dtype
+
+    # ---- compute copy: where the optimizer writes it -----------------------------------------------------
+    def _sharded(self, sec: Section) -> bool:
+        return sec.shard_axis is not None and self.mesh.size(sec.shard_axis) > 1 and sec.backend != "frozen"
+
+    def _section_at(self, offset: int) -> Section:
+        for sec in self.sections:
+            if sec.start <= offset < sec.start + max(sec.length, 1):
+                return sec
+        raise ContractError(f"arena offset {offset} is outside every section")
+
+    def shadow(self, a: int, b: int | None = None) -> torch.Tensor:
+        """Compute-dtype storage of the arena elements ``[a, b)`` (``b`` omitted: up to the end of what this rank
+        holds of that section).  With resident weights that is a slice of the compute arena; with weights sharded
+        at rest the range must lie inside what this rank owns."""
+
+        if self.resident:
+            return self.compute_arena[a:] if b is None else self.compute_arena[a:b]
+        sec = self._section_at(a)
+        lo, hi = self.local_master_range(sec) if self._sharded(sec) else (sec.start, sec.start + sec.length)
+        end = hi if b is None else b
+        if a < lo or end > hi:
+            raise ContractError(f"arena range [{a}, {end}) is not held by this rank (it holds [{lo}, {hi}))")
+        base = sec.rest_start - lo
+        return self.rest[base + a:base + end]
+
+    def write_entry_shadow(self, e: StorageEntry, master: torch.Tensor) -> None:
+        """Refresh the compute copy of a whole storage entry from its fp32 master (owner of the entry only)."""
+
+        if self.resident:
+            e.param.data.copy_(master)
+        else:
+            self.shadow(e.offset, e.offset + e.numel).copy_(master.reshape(-1))
+
+    def load_shadow(self, e: StorageEntry, flat: torch.Tensor) -> None:
+        """Checkpoint restore: ``flat`` holds the whole entry; keep what this rank stores of it."""
+
+        if self.resident:
+            self.compute_arena[e.offset:e.offset + e.numel].copy_(flat)
+            return
+        sec = self.section_of(e)
+        lo, hi = self.local_master_range(sec) if self._sharded(sec) else (sec.start, sec.start + sec.length)
+        a, b = max(e.offset, lo), min(e.offset + e.numel, hi)
+        if b > a:
+            self.shadow(a, b).copy_(flat[a - e.offset:b - e.offset])
+
+    # ---- weights sharded at rest (ZeRO-3) -------------------------------------------------------------------
+    def _materialise_sharded(self) -> None:
+        dev = self.device
+        dtype = self.compute_dtype
+        esize = torch.empty((), dtype=dtype).element_size()
+        # what every rank keeps: its 1/N of sharded sections, all of the others
+        cursor = 0
+        for sec in self.sections:
+            n = self.mesh.size(sec.shard_axis) if self._sharded(sec) else 1
+            sec.rest_start = cursor
+            cursor += _ceil_to(sec.length // n, ALIGN)
+        rest_total = cursor
+        self.arena = None
+        group = self._symmetric_group()
+        if group is not None:
+            from research_b200.parallel.symmetric import SymmetricArena, build_collectively
+
+            self.arena = build_collectively(
+                group, lambda: SymmetricArena(group, self.total * 4 + rest_total * esize + 8192, device=dev,
+                                              tag="params"), "symmetric parameter arena")
+        if self.arena is not None:
+            self.grad_arena, self._grad_off = self.arena.carve(self.total, torch.float32)
+            self.rest, self._rest_off = self.arena.carve(rest_total, dtype)
+        else:
+            self.grad_arena = torch.zeros(self.total, dtype=torch.float32, device=dev)
+            self.rest = torch.zeros(rest_total, dtype=dtype, device=dev)
+        self.compute_arena = None
+        # gathered entries: per layer into a layer buffer, the rest (embedding, final norm, lm_head) once per step
+        gathered = [e for e in self.entries if self._sharded(self.section_of(e))]
+        self._layers = sorted({layer_of(e.name) for e in gathered if layer_of(e.name) >= 0})
+        self._layer_entries = {l: sorted((e for e in gathered if layer_of(e.name) == l), key=lambda e: e.offset)
+                               for l in self._layers}
+        self._extra_entries = sorted((e for e in gathered if layer_of(e.name) < 0), key=lambda e: e.offset)
+        self._dst_off: dict[str, int] = {}
+        slot_size = 0
+        for l, entries in self._layer_entries.items():
+            off = 0
+            for e in entries:
+                self._dst_off[e.name] = off
+                off += _ceil_to(e.numel, ALIGN)
+            slot_size = max(slot_size, off)
+        off = 0
+        for e in self._extra_entries:
+            self._dst_off[e.name] = off
+            off += _ceil_to(e.numel, ALIGN)
+        native_path = dev.type == "cuda" and dtype == torch.bfloat16
+        # plain autograd keeps references to the weights it saw in forward, so off the native path every layer keeps
+        # a buffer of its own for the whole step; the native kernels read the parameter at launch time and two
+        # buffers (the layer in use, the layer being fetched) are enough
+        self._n_slots = 2 if native_path else max(len(self._layers), 1)
+        self._slots = [torch.zeros(max(slot_size, 1), dtype=dtype, device=dev) for _ in range(self._n_slots)]
+        self._extras = torch.zeros(max(off, 1), dtype=dtype, device=dev)
+        self._slot_layer: list[int | None] = [None] * self._n_slots
+        self._gather_stream = torch.cuda.Stream(dev) if dev.type == "cuda" else None
+        self._slot_ready = [None] * self._n_slots          # event: the gather into the slot has finished
+        self._slot_free = [None] * self._n_slots           # event: the compute that read the slot has been issued
+        self._tables: dict[tuple, tuple[torch.Tensor, int]] = {}
+        self._overlap = (self.arena is not None and os.environ.get("RESEARCH_B200_OVERLAP_REDUCE", "1") != "0")
+        self._comm_stream = torch.cuda.Stream(dev, priority=-1) if self._overlap else None
+        self._bucket_ctas = int(os.environ.get("RESEARCH_B200_REDUCE_CTAS", "48"))
+        self._pending = []
+        self._armed = False
+        separate_master = dtype != torch.float32
+        for sec in self.sections:
+            lo, hi = self.local_master_range(sec)
+            sec.master = torch.zeros(hi - lo, dtype=torch.float32, device=dev) if separate_master else None
+        for e in self.entries:
+            sec = self.section_of(e)
+            fp32 = e.param.data.detach().to(torch.float32).reshape(-1)
+            lo, hi = self.local_master_range(sec) if self._sharded(sec) else (sec.start, sec.start + sec.length)
+            a, b = max(e.offset, lo), min(e.offset + e.numel, hi)
+            if b > a:
+                self.shadow(a, b).copy_(fp32[a - e.offset:b - e.offset])
+                if separate_master:
+                    mlo, _ = self.local_master_range(sec)
+                    ma, mb = max(e.offset, mlo), min(e.offset + e.numel, self.local_master_range(sec)[1])
+                    if mb > ma:
+                        sec.master[ma - mlo:mb - mlo].copy_(fp32[ma - e.offset:mb - e.offset])
+            if self._sharded(sec):
+                # a view of the buffer the values will be fetched into: the shape is right from the start, the
+                # contents only while the layer is acquired (or, outside the layers, after the per-step gather)
+                layer = layer_of(e.name)
+                buf = self._extras if layer < 0 else self._slots[self._slot_for(layer)]
+                off = self._dst_off[e.name]
+                e.param.data = buf[off:off + e.numel].view(e.param.shape)
+            else:
+                e.param.data = self.shadow(e.offset, e.offset + e.numel).view(e.param.shape)
+            e.param.main_grad = self.grad_arena[e.offset:e.offset + e.numel].view(e.param.shape)
+        if not separate_master:
+            for sec in self.sections:
+                lo, hi = self.local_master_range(sec)
+                sec.master = self.shadow(lo, hi)
+        self.result.model.compute_dtype = dtype
+        self.refresh_resident_extras()
+
+    def _pieces(self, entries: list[StorageEntry]) -> list[tuple[int, int, int, int]]:
+        """``(owning rank, offset in the owner's rest buffer, offset in the destination buffer, elements)`` for every
+        stretch of ``entries`` that one rank holds."""
+
+        out = []
+        for e in entries:
+            sec = self.section_of(e)
+            n = self.mesh.size(sec.shard_axis)
+            per = sec.length // n
+            for r in range(n):
+                lo = sec.start + r * per
+                a, b = max(e.offset, lo), min(e.offset + e.numel, lo + per)
+                if b > a:
+                    out.append((r, sec.rest_start + a - lo, self._dst_off[e.name] + a - e.offset, b - a))
+        return out
+
+    def _gather(self, entries: list[StorageEntry], dst: torch.Tensor, key: tuple) -> None:
+        """Fill ``dst`` with the compute copy of ``entries`` from the ranks that hold them."""
+
+        if not entries:
+            return
+        pieces = self._pieces(entries)
+        sec = self.section_of(entries[0])
+        me = self.mesh.coord(sec.shard_axis)
+        esize = dst.element_size()
+        if self.arena is not None:
+            from research_b200.parallel.symmetric import copy_pieces
+
+            if key not in self._tables:
+                rows = [(self.arena.peer_ptr(r, self._rest_off) + src * esize, dst.data_ptr() + off * esize, n * esize)
+                        for r, src, off, n in pieces]
+                self._tables[key] = (torch.tensor(rows, dtype=torch.int64, device=self.device), len(rows))
+            table, n = self._tables[key]
+            copy_pieces(table, n)
+            return
+        # collectives: every rank contributes what it holds, zeros elsewhere (adding zeros is exact)
+        dst.zero_()
+        for r, src, off, n in pieces:
+            if r == me:
+                dst[off:off + n].copy_(self.rest[src:src + n])
+        group = self.mesh.group(sec.shard_axis)
+        if group is not None:
+            dist.all_reduce(dst, group=group)
+
+    def refresh_resident_extras(self) -> None:
+        """Once per step, after the optimizer: every rank gets the parameters that are used outside the transformer
+        layers (embedding, final norm, lm_head); the layer buffers are stale from here on."""
+
+        if self.resident:
+            return
+        if self.arena is not None:
+            self.arena.barrier()            # every rank's rest buffer holds the updated weights
+        self._gather(self._extra_entries, self._extras, ("extras",))
+        for e in self._extra_entries:
+            off = self._dst_off[e.name]
+            e.param.data = self._extras[off:off + e.numel].view(e.param.shape)
+        self._slot_layer = [None] * self._n_slots
+
+    def _fetch(self, layer: int, slot: int) -> None:
+        dev_cuda = self._gather_stream is not None
+        if dev_cuda:
+            if self._slot_free[slot] is not None:
+                self._gather_stream.wait_event(self._slot_free[slot])      # the slot's previous reader is done
+            self._gather_stream.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(self._gather_stream):
+                self._gather(self._layer_entries[layer], self._slots[slot], ("layer", layer, slot))
+                ev = torch.cuda.Event()
+                ev.record(self._gather_stream)
+            self._slot_ready[slot] = ev
+        else:
+            self._gather(self._layer_entries[layer], self._slots[slot], ("layer", layer, slot))
+        self._slot_layer[slot] = layer
+
+    def _slot_for(self, layer: int) -> int:
+        return self._layers.index(layer) % self._n_slots
+
+    def acquire_layer(self, layer: int, direction: int = 1) -> None:
+        """Make the weights of ``layer`` usable (its parameters point into a layer buffer that holds them) and start
+        fetching the next layer in ``direction`` (+1 forward, -1 backward).  No-op with resident weights."""
+
+        if self.resident or layer not in self._layer_entries:
+            return
+        slot = self._slot_for(layer)
+        if self._slot_layer[slot] != layer:
+            self._fetch(layer, slot)
+        if self._slot_ready[slot] is not None:
+            torch.cuda.current_stream(self.device).wait_event(self._slot_ready[slot])
+        buf = self._slots[slot]
+        for e in self._layer_entries[layer]:
+            off = self._dst_off[e.name]
+            e.param.data = buf[off:off + e.numel].view(e.param.shape)
+        nxt = layer + direction
+        if nxt in self._layer_entries:
+            nslot = self._slot_for(nxt)
+            if nslot != slot and self._slot_layer[nslot] != nxt:
+                if self._gather_stream is not None and self._slot_layer[nslot] is not None:
+                    # the kernels that read the other slot (the previous layer) are all on the stream by now
+                    ev = torch.cuda.Event()
+                    ev.record(torch.cuda.current_stream(self.device))
+                    self._slot_free[nslot] = ev
+                self._fetch(nxt, nslot)
+
+    def memory_report(self) -> dict[str, Any]:
+        """Bytes of the compute copy this rank holds, by kind (for the resident / sharded comparison)."""
+
+        esize = torch.empty((), dtype=self.compute_dtype).element_size()
+        if self.resident:
+            return {"mode": "resident", "compute_bytes": self.total * esize, "layer_buffer_bytes": 0,
+                    "extras_bytes": 0}
+        return {"mode": "sharded", "compute_bytes": self.rest.numel() * esize,
+                "layer_buffer_bytes": sum(s.numel() for s in self._slots) * esize,
+                "extras_bytes": self._extras.numel() * esize, "layer_buffers": self._n_slots}
 
     # ---- queries ---------------------------------------------------------------------------------
     def section_of(self, e: StorageEntry) -> Section:
@@ -366,6 +634,9 @@ class ParamStore:
     def gather_compute_weights(self) -> None:
         """After the optimizer step: every rank gets the updated compute weights of sharded sections."""
 
+        if not self.resident:
+            self.refresh_resident_extras()
+            return
         for sec in self.sections:
             if sec.shard_axis is None or sec.backend == "frozen":
                 continue
@@ -384,6 +655,7 @@ class ParamStore:
     def describe(self) -> dict[str, Any]:
         return {
             "mode": self.mode,
+            "weights_resident": self.resident,
             "compute_dtype": str(self.compute_dtype).replace("torch.", ""),
             "arena_elements": self.total,
             "sections": [

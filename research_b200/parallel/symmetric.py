@@ -55,6 +55,8 @@ def _comm_lib() -> ctypes.CDLL:
                                                   ci, ci, ctypes.c_uint, ci, vp, vp, vp]
         lib.b200c_all_gather_nvls.argtypes = [vp, vp, ctypes.c_longlong, ctypes.POINTER(vp), ci, ci, ctypes.c_uint,
                                               vp, vp, vp]
+        lib.b200c_copy_pieces.argtypes = [vp, ci, ci, vp]
+        lib.b200c_copy_pieces.restype = ci
         lib.b200c_mc_supported.argtypes = []
         lib.b200c_mc_granularity.argtypes = [ci, ull]
         lib.b200c_mc_granularity.restype = ull
@@ -130,6 +132,14 @@ def broadcast_descriptor(group, fd: int | None, *, tag: str, timeout_ms: int = _
     if got < 0:
         raise ContractError(f"rank {rank} could not fetch the multicast descriptor: errno {-got}")
     return got
+
+
+def copy_pieces(table: torch.Tensor, n_pieces: int, ctas_per_piece: int = 8) -> None:
+    """One launch that copies ``n_pieces`` byte ranges described by ``table`` (int64 ``[n, 3]``: source address,
+    destination address, byte count; sources may be peers' arenas) on the current stream."""
+
+    rc = _comm_lib().b200c_copy_pieces(table.data_ptr(), int(n_pieces), int(ctas_per_piece), native._stream())
+    native._check(rc, "b200c_copy_pieces")
 
 
 def nvls_requested() -> bool:

@@ -236,11 +236,13 @@ def load_state_tensors(trainer, tensors: dict[str, np.ndarray]) -> None:
                 res.storage_view(meta, storage).copy_(_local_from_logical(trainer, meta, need(leaf)).to(dev))
             flat = storage.reshape(-1)
             if kind == "master":
-                store.compute_arena[entry.offset:entry.offset + entry.numel].copy_(flat)
-                if b > a and sec.master is not None and sec.master.data_ptr() != store.compute_arena[lo:hi].data_ptr():
+                store.load_shadow(entry, flat)
+                if b > a and sec.master is not None and store.compute_dtype != torch.float32:
                     sec.master[a - lo:b - lo].copy_(flat[a - entry.offset:b - entry.offset])
             elif b > a and kind in opt.state[i]:
                 opt.state[i][kind][a - lo:b - lo].copy_(flat[a - entry.offset:b - entry.offset])
+    if not store.resident:
+        store.refresh_resident_extras()          # weights sharded at rest: the per-step gathers start from the new values
     if trainer.moe_balance is not None:
         for i, layer in enumerate(trainer.moe_balance.layers):
             layer.momentum.copy_(torch.from_numpy(np.asarray(need(f"moe_balance.layers.{i}.momentum"))).to(dev))

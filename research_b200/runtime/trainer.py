@@ -128,7 +128,10 @@ class Trainer:
         ep = resolve_expert_parallel_axis(spec.parallelism, self.mesh.sizes)
         self.store = ParamStore(self.result, self.mesh, mode=spec.parallelism.mode, compute_dtype=self.compute_dtype,
                                 backend_of=self.optimizer_build.backend_by_name(), ep_axis=ep.axis,
-                                decay_of=self.optimizer_build.weight_decay_by_name())
+                                decay_of=self.optimizer_build.weight_decay_by_name(),
+                                resident=spec.parallelism.fsdp_resident)
+        if not self.store.resident:
+            self.result.model.layer_prepare = self.store.acquire_layer
         self.optimizer = Optimizer(self.optimizer_build, self.store)
         moe = spec.model.trinity.moe if spec.model.trinity is not None else None
         self.moe_balance = init_moe_balance(self.result.model, None if moe is None else moe.balance)

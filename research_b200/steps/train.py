@@ -168,6 +168,23 @@ class TrainStep:
         objective.backward()
         return ce_sum.detach(), z_sum.detach(), (None if aux_total is None else aux_total.detach()), stats
 
+    def _backward_hook(self, last_microbatch: bool):
+        """What the model calls when the backward pass of layer ``i`` has been issued: start the reduction of that
+        layer's gradients (last microbatch, native path) and, with weights sharded at rest, fetch layer ``i - 1``."""
+
+        store = self.store
+        reduce = last_microbatch and self.native
+        if store.resident and not reduce:
+            return None
+
+        def hook(layer: int) -> None:
+            if reduce:
+                store.on_layer_backward(layer)
+            if not store.resident and layer >= 1:
+                store.acquire_layer(layer - 1, -1)
+
+        return hook
+
     def _head_weight(self):
         return self.model.head_weight()
 
@@ -199,7 +216,7 @@ class TrainStep:
             last = k + 1 == len(batches)
             if last and self.native:
                 self.store.begin_backward_overlap()
-            self.model.layer_backward_hook = self.store.on_layer_backward if (last and self.native) else None
+            self.model.layer_backward_hook = self._backward_hook(last)
             ce, z, aux, stats = self._microbatch(current, grad_scale, global_counts[k], dp_world)
             ce_sums.append(ce)
             z_sums.append(z)

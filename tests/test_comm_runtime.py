@@ -309,6 +309,9 @@ def _run_training(tmp_path, world, axes, sizes, flags, peer, port, extra_env=Non
     # context parallelism: K/V exchange inside the attention kernels against all-gather + reduce-scatter
     ("cp2_ring", ["cp"], [2], {"parallelism": {"mode": "ddp", "context_parallel": True},
                                "model": {"attention_doc_mask": False}}),
+    # weights sharded at rest: every layer's weights are fetched from their owners' arenas before the layer runs
+    ("fsdp2_muon_sharded_params", ["fsdp"], [2], {"parallelism": {"mode": "fsdp", "fsdp_resident": False},
+                                                  "optimizer": "muon"}),
     # the same FSDP run with the arena bound to an NVLink multicast object (multimem reduce-scatter / all-gather)
     ("fsdp2_muon_nvls", ["fsdp"], [2], {"parallelism": {"mode": "fsdp"}, "optimizer": "muon",
                                         "env": {"RESEARCH_B200_NVLS": "1"}}),

@@ -28,6 +28,8 @@ def _compare(ref, got, tol=2e-4):
 
 
 CASES = [
+    ("fsdp2_sharded_params", "decoder", "adamw", {"fsdp": 2}, {"mode": "fsdp", "fsdp_resident": False}),
+    ("fsdp2_sharded_params_muon", "decoder", "muon", {"fsdp": 2}, {"mode": "fsdp", "fsdp_resident": False}),
     ("ddp2", "decoder", "adamw", {"data": 2}, {"mode": "ddp"}),
     ("zero2", "decoder", "adamw", {"fsdp": 2}, {"mode": "zero2"}),
     ("fsdp2_muon", "decoder", "muon", {"fsdp": 2}, {"mode": "fsdp"}),

@@ -90,6 +90,7 @@ def _save_sharded(rank, world, raw, out_dir):
 @pytest.mark.parametrize("optimizer,mesh,parallelism", [
     ("adamw", {"fsdp": 2}, {"mode": "zero2"}),
     ("muon", {"fsdp": 2}, {"mode": "fsdp"}),
+    ("muon", {"fsdp": 2}, {"mode": "fsdp", "fsdp_resident": False}),       # weights sharded at rest
 ])
 def test_sharded_save_assembles_on_the_writer_and_restores_on_one_process(tmp_path, optimizer, mesh, parallelism):
     manifest = tiny_dataset(tmp_path)
@@ -123,3 +124,31 @@ def test_saving_a_step_twice_replaces_it_only_when_the_new_copy_is_complete(tmp_
     leftovers = [p.name for p in (tmp_path / "checkpoints").iterdir() if p.name != "000003"]
     assert leftovers == [], leftovers
     assert json.loads((tmp_path / "checkpoints" / "000003" / "_CHECKPOINT_METADATA").read_text())["writer"]
+
+
+def _reload_sharded(rank, world, raw, ckpt_dir):
+    """Restore into a job whose weights are sharded at rest and take one more step."""
+
+    trainer = Trainer(run_spec_from_mapping(raw), device="cpu")
+    restored = LocalCheckpointService(ckpt_dir, is_writer=False).restore_latest()
+    load_state_tensors(trainer, restored.tensors)
+    state = {k: torch.from_numpy(np.array(v)) for k, v in collect_state_tensors(trainer).items()}
+    trainer.data_state = trainer.data.state_from_json(restored.dataset_state) if restored.dataset_state.get("backend") \
+        else trainer.data_state
+    loss = trainer.train_step().loss_sum
+    return {"state": state, "loss": loss, "memory": trainer.store.memory_report()}
+
+
+def test_restore_into_weights_sharded_at_rest(tmp_path):
+    manifest = tiny_dataset(tmp_path)
+    resident = tiny_raw_config(manifest, optimizer="muon", mesh={"fsdp": 2}, parallelism={"mode": "fsdp"}, steps=4)
+    saved = run_gloo(2, _save_sharded, resident, str(tmp_path / "run"))
+    sharded = tiny_raw_config(manifest, optimizer="muon", mesh={"fsdp": 2},
+                              parallelism={"mode": "fsdp", "fsdp_resident": False}, steps=4)
+    a = run_gloo(2, _reload_sharded, sharded, str(tmp_path / "run"))
+    b = run_gloo(2, _reload_sharded, resident, str(tmp_path / "run"))
+    for name, want in saved[0].items():
+        assert np.array_equal(a[0]["state"][name].numpy().reshape(-1), want.numpy().reshape(-1)), name
+    assert a[0]["loss"] == pytest.approx(b[0]["loss"], rel=1e-5)           # the step after the restore agrees
+    assert a[0]["memory"]["mode"] == "sharded" and b[0]["memory"]["mode"] == "resident"
+    assert a[0]["memory"]["compute_bytes"] < b[0]["memory"]["compute_bytes"]
