@@ -251,58 +251,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       tc_fence_after();
       const bool need_mask = (p.causal && kv0 + BLOCK_N - 1 > q_pos) || (kv0 < lo_row) || (kv0 + BLOCK_N > p.Skv);
       const int hi = p.causal ? min(q_pos, p.Skv - 1) : p.Skv - 1;
-      // pass 1: block maximum of the scaled, masked scores
-      float bm = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(tS + c * 32, r);
-        tmem_ld_wait();
-        if (need_mask) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int col = kv0 + c * 32 + i;
-            const float v = (col > hi || col < lo_row) ? -INFINITY : __uint_as_float(r[i]);
-            bm = fmaxf(bm, v);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) bm = fmaxf(bm, __uint_as_float(r[i]));
-        }
-      }
-      bm *= p.scale_log2;  // scale > 0, so the maximum commutes with it
-      const bool need = bm > m_ref + kRescaleThreshold;
-      if (__any_sync(0xffffffffu, need)) {
-        const float m_new = need ? bm : m_ref;
-        const float alpha = ex2_approx(m_ref - m_new);
-        if (j > 0) {
-          if (!mbar_wait_warp(&pv_done[t], (j - 1) & 1, ab, ERR_WAIT_O_READY)) { ok = false; break; }
-          tc_fence_after();
-#pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(tO + c * 32, r);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32b_x32(tO + c * 32, r);
-          }
-          tmem_st_wait();
-        }
-        l_sum *= alpha;
-        m_ref = m_new;
-      }
-      if (j > 0) {  // the previous P of this tile has been consumed
-        if (!mbar_wait_warp(&pv_done[t], (j - 1) & 1, ab, ERR_WAIT_O_READY)) { ok = false; break; }
-      }
-      // pass 2: probabilities, row sum, P to shared memory (bf16, 128-byte swizzle, K-major for the PV MMA)
       float sum = 0.f;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32b_x32(tS + c * 32, r);
-        tmem_ld_wait();
+      // exponentials of 32 scores relative to m_ref, their sum, and P (bf16, 128-byte swizzle, K-major for the PV
+      // MMA) into shared memory; returns the largest exponent argument seen (how far the row maximum moved)
+      auto emit_chunk = [&](const uint32_t (&r)[32], int c) -> float {
         float e[32];
+        float top = -INFINITY;
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           float v = __uint_as_float(r[i]) * p.scale_log2 - m_ref;
@@ -310,6 +264,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
             const int col = kv0 + c * 32 + i;
             if (col > hi || col < lo_row) v = -INFINITY;
           }
+          top = fmaxf(top, v);
           e[i] = ex2_approx(v);
           sum += e[i];
         }
@@ -322,6 +277,80 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           v.w = pack_bf16x2(e[8 * i + 6], e[8 * i + 7]);
           const int chunk = c * 4 + i;  // 16-byte chunk index along kv (16 per row)
           *reinterpret_cast<uint4*>(sP + (chunk >> 3) * 16384 + sw128_offset(row, chunk & 7)) = v;
+        }
+        return top;
+      };
+      // Fast path (every block but the first, unless a row maximum jumps): ONE pass over the scores with the
+      // reference maximum of the previous blocks.  The lazy-rescale rule tolerates a maximum that is up to 2^8
+      // above the reference, so the pass is kept when no row of the warp moved further; the loads of one chunk
+      // are in flight while the previous chunk is worked on.
+      bool done = false;
+      if (j > 0) {
+        if (!mbar_wait_warp(&pv_done[t], (j - 1) & 1, ab, ERR_WAIT_O_READY)) { ok = false; break; }   // P(j-1) consumed
+        uint32_t ra[32], rb[32];
+        tmem_ld_32x32b_x32(tS, ra);
+        tmem_ld_32x32b_x32(tS + 32, rb);
+        tmem_ld_wait();
+        float top = emit_chunk(ra, 0);
+        tmem_ld_32x32b_x32(tS + 64, ra);
+        top = fmaxf(top, emit_chunk(rb, 1));
+        tmem_ld_wait();
+        tmem_ld_32x32b_x32(tS + 96, rb);
+        top = fmaxf(top, emit_chunk(ra, 2));
+        tmem_ld_wait();
+        top = fmaxf(top, emit_chunk(rb, 3));
+        done = !__any_sync(0xffffffffu, top > kRescaleThreshold);
+        if (!done) sum = 0.f;   // a row maximum moved too far: redo the block with a new reference
+      }
+      if (!done) {
+        // pass 1: block maximum of the scaled, masked scores
+        float bm = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tS + c * 32, r);
+          tmem_ld_wait();
+          if (need_mask) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int col = kv0 + c * 32 + i;
+              const float v = (col > hi || col < lo_row) ? -INFINITY : __uint_as_float(r[i]);
+              bm = fmaxf(bm, v);
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) bm = fmaxf(bm, __uint_as_float(r[i]));
+          }
+        }
+        bm *= p.scale_log2;  // scale > 0, so the maximum commutes with it
+        const bool need = bm > m_ref + kRescaleThreshold;
+        if (__any_sync(0xffffffffu, need)) {
+          const float m_new = need ? bm : m_ref;
+          const float alpha = ex2_approx(m_ref - m_new);
+          if (j > 0) {
+            // pv_done(j-1) was waited for above: O holds the sum over the blocks before this one
+            tc_fence_after();
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t r[32];
+              tmem_ld_32x32b_x32(tO + c * 32, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+              tmem_st_32x32b_x32(tO + c * 32, r);
+            }
+            tmem_st_wait();
+          }
+          l_sum *= alpha;
+          m_ref = m_new;
+        }
+        // pass 2: probabilities, row sum, P to shared memory
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32b_x32(tS + c * 32, r);
+          tmem_ld_wait();
+          emit_chunk(r, c);
         }
       }
       l_sum += sum;
