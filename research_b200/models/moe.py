@@ -145,7 +145,18 @@ class SparseMoE(nn.Module):
         if moe.num_shared_experts > 0:
             self.shared_experts = SharedSwiGLU(spec.hidden_size, moe.expert_intermediate_size * moe.num_shared_experts, ex)
 
-    def _dedicated_axis_fused(self, x: torch.Tensor, expert_ids: torch.Tensor, weights: torch.Tensor, ex):
+    @staticmethod
+    def _layer_slot(ex, layer_index: int) -> int:
+        """Index of this MoE layer among the MoE layers seen so far (stable over steps): selects the layer's own
+        forward inbox in the expert-parallel workspace."""
+
+        slots = ex.extras.setdefault("moe_layer_slots", {})
+        if layer_index not in slots:
+            slots[layer_index] = len(slots)
+        return slots[layer_index]
+
+    def _dedicated_axis_fused(self, x: torch.Tensor, expert_ids: torch.Tensor, weights: torch.Tensor, ex,
+                              layer_index: int = 0):
         """Dedicated ``ep`` axis on CUDA: tokens are replicated over the axis, so every rank routes its slice of
         them through the peer-memory dispatch / combine kernels and the results are gathered back (the reference
         slices the sequence inside its shard_map, components/moe.py:538-696).  The capacity applies per sender
@@ -162,7 +173,8 @@ class SparseMoE(nn.Module):
         t_local = T // ep
         capacity = capacity_rows(self.moe.capacity_factor, t_local, k, self.num_experts)
         ids_local = expert_ids.reshape(T, k)[rank * t_local:(rank + 1) * t_local].contiguous()
-        plan = expert_fused.ExpertParallelPlan(ids_local, self.num_experts, capacity, ex, H)
+        plan = expert_fused.ExpertParallelPlan(ids_local, self.num_experts, capacity, ex, H,
+                                               layer_slot=self._layer_slot(ex, layer_index))
         if plan.ws is None:
             return None
         keep = plan.kept_mask
@@ -205,12 +217,12 @@ class SparseMoE(nn.Module):
                 if ex.ep_axis_sharing == "dedicated_ep":
                     if expert_fused.fused_available(ex, x, capacity) and (B * S) % ex.ep_size == 0 \
                             and ex.efsdp_size == 1:
-                        done = self._dedicated_axis_fused(x, expert_ids, weights, ex)
+                        done = self._dedicated_axis_fused(x, expert_ids, weights, ex, layer_index)
                         if done is not None:
                             y_routed, weights, dropped = done
                 elif expert_fused.fused_available(ex, x, capacity):
                     plan = expert_fused.ExpertParallelPlan(expert_ids.reshape(B * S, -1), self.num_experts, capacity, ex,
-                                                           H)
+                                                           H, layer_slot=self._layer_slot(ex, layer_index))
                     if plan.ws is None:
                         plan = None
             if y_routed is not None:

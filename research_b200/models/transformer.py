@@ -248,6 +248,8 @@ class TransformerLM(nn.Module):
         else:
             raise ContractError(f"unsupported model.name {spec.name!r}")
         self.layers = nn.ModuleList(layers)
+        # how many layers route tokens to experts: sizes the per-layer inboxes of the expert-parallel workspace
+        ex.extras["moe_layer_count"] = sum(1 for layer in layers if getattr(layer, "is_moe", False))
         self.norm = RMSNorm(H, spec.norm_epsilon)
         self.lm_head = None if spec.tied_embeddings else nn.Parameter(
             torch.empty(self.vocab_local, H, dtype=torch.float32))

@@ -119,6 +119,20 @@ __global__ void __launch_bounds__(256) moe_layout_kernel(const int* __restrict__
   }
 }
 
+// Zero the padding rows behind the real rows of every expert block (rows [starts[e] + counts[e], next multiple of
+// 128)): the grouped GEMMs contract over whole padded blocks, so these rows must not hold stale data, while the
+// real rows are about to be written by the senders.  One CTA per expert.
+__global__ void __launch_bounds__(256) moe_zero_pad_kernel(__nv_bfloat16* __restrict__ buf, const int* __restrict__ starts,
+                                                           const int* __restrict__ counts, int H) {
+  const int e = blockIdx.x;
+  const int first = starts[e] + counts[e];
+  const int last = (first + 127) / 128 * 128;
+  const long long n16 = (long long)(last - first) * H / 8;          // 16-byte units (H % 8 == 0)
+  uint4* p = reinterpret_cast<uint4*>(buf + (long long)first * H);
+  const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+  for (long long i = threadIdx.x; i < n16; i += blockDim.x) p[i] = z;
+}
+
 // dest[a] = starts[e] + pos[a] (+ row_base of the rank that owns e) for kept assignments, else -1; src[dest] = a.
 // With expert parallelism experts_per_rank > 0: `starts` then holds, per global expert, the first row *for this
 // sender* inside the owner's buffer, and dest encodes owner * rows_per_rank + row.
@@ -300,6 +314,14 @@ int b200_moe_layout(const void* counts, int E, int capacity, int pad, int tiles,
   moe_layout_kernel<<<1, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>((const int*)counts, E, capacity, pad, tiles,
                                                                           (int*)starts, (int*)k_range,
                                                                           (int*)tile_group, (int*)kept);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// buf: [rows, H] bf16 expert-major buffer; starts / counts: int32 [E] first row and real row count of every block.
+int b200_moe_zero_pad(void* buf, const void* starts, const void* counts, int E, int H, void* stream) {
+  if (E <= 0 || E > kMaxExperts || H % 8) return -2;
+  moe_zero_pad_kernel<<<E, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>((__nv_bfloat16*)buf, (const int*)starts,
+                                                                            (const int*)counts, H);
   return static_cast<int>(cudaGetLastError());
 }
 

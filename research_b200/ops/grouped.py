@@ -131,6 +131,8 @@ def _moe_lib():
         lib.b200_moe_rank.argtypes = [vp, ci, ci, vp, vp, vp, vp]
         lib.b200_moe_layout.argtypes = [vp, ci, ci, ci, ci, vp, vp, vp, vp, vp]
         lib.b200_moe_dest.argtypes = [vp, vp, vp, ci, ci, ci, ci, ll, vp, vp, vp]
+        lib.b200_moe_zero_pad.argtypes = [vp, vp, vp, ci, ci, vp]
+        lib.b200_moe_zero_pad.restype = ci
         lib.b200_moe_gather.argtypes = [vp, vp, vp, vp, pvp, ci, ll, ci, ci, ll, vp]
         lib.b200_moe_combine.argtypes = [pvp, ci, vp, vp, vp, vp, ll, ci, ci, ll, vp]
         lib.b200_moe_combine_dw.argtypes = [pvp, ci, vp, vp, vp, ll, ci, ci, ll, vp]

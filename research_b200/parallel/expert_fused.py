@@ -13,6 +13,9 @@ Per MoE layer, with the routed experts split over the ``ep`` ranks of one node:
 
 Backward mirrors it (push of weighted output gradients, pull of input gradients).  Stream-ordered peer barriers
 (bounded waits) separate the phases.  The path needs a capacity factor, which bounds the owner's buffer.
+Every MoE layer has an inbox of its own for the forward rows (they are what the backward pass of the grouped GEMMs
+reads, so nothing is copied out of the arena), a shared inbox takes the gradient rows, and only the padding rows
+behind each expert's block are zeroed before a push.
 The NCCL formulation in :mod:`research_b200.parallel.expert` is the fallback and the test oracle.
 
 Reference: src/jaxtitan/models/components/moe.py:538-696 (ragged all-to-all dispatcher), 606-662 (metadata and
@@ -36,20 +39,39 @@ from research_b200.parallel.symmetric import SymmetricArena
 BARRIER_CHANNEL = 5
 
 
-class ExpertParallelWorkspace:
-    """Two row buffers per rank in a symmetric arena: one that peers write (dispatch, backward of combine) and one
-    that peers read (combine, backward of dispatch)."""
+FORWARD_SLOT_BUDGET_BYTES = 48 << 30     # per-layer forward inboxes are used while they fit in this much memory
 
-    def __init__(self, group, rows: int, hidden: int, device: torch.device):
+
+class ExpertParallelWorkspace:
+    """Row buffers per rank in a symmetric arena: inboxes that peers write (one per MoE layer for the forward rows
+    when that fits the budget, one shared for gradient rows) and an outbox that peers read (combine, backward of
+    dispatch)."""
+
+    def __init__(self, group, rows: int, hidden: int, device: torch.device, layers: int = 0):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.rows, self.hidden = rows, hidden
-        self.arena = SymmetricArena(group, 2 * rows * hidden * 2 + 8192, device=device, tag="ep")
-        self.inbox, self.inbox_off = self.arena.carve(rows * hidden, torch.bfloat16)
+        per = rows * hidden * 2
+        self.forward_slots = layers if 0 < layers and layers * per <= FORWARD_SLOT_BUDGET_BYTES else 0
+        n_in = 1 + self.forward_slots
+        self.arena = SymmetricArena(group, (n_in + 1) * (per + 512) + 8192, device=device, tag="ep")
+        self.inboxes, self.inbox_offs = [], []
+        for _ in range(n_in):
+            t, off = self.arena.carve(rows * hidden, torch.bfloat16)
+            self.inboxes.append(t.view(rows, hidden))
+            self.inbox_offs.append(off)
+        self.inbox, self.inbox_off = self.inboxes[0], self.inbox_offs[0]      # the shared (gradient) inbox
         self.outbox, self.outbox_off = self.arena.carve(rows * hidden, torch.bfloat16)
-        self.inbox = self.inbox.view(rows, hidden)
         self.outbox = self.outbox.view(rows, hidden)
+
+    def inbox_for(self, layer_slot: int | None) -> tuple[torch.Tensor, int, bool]:
+        """``(buffer, arena offset, private)`` of the inbox for a forward push of MoE layer ``layer_slot`` (private:
+        nothing else is pushed into it during the step) or, with None, of the shared gradient inbox."""
+
+        if layer_slot is not None and layer_slot < self.forward_slots:
+            return self.inboxes[1 + layer_slot], self.inbox_offs[1 + layer_slot], True
+        return self.inbox, self.inbox_off, False
 
     def ptrs(self, offset: int):
         arr = (ctypes.c_void_p * self.world)()
@@ -70,7 +92,9 @@ def workspace_for(ex, rows: int, hidden: int, device: torch.device) -> ExpertPar
     if ws is None or ws.rows < rows or ws.hidden != hidden:
         from research_b200.parallel.symmetric import build_collectively
 
-        ws = build_collectively(ex.ep_group, lambda: ExpertParallelWorkspace(ex.ep_group, rows, hidden, device),
+        layers = int(ex.extras.get("moe_layer_count", 0))
+        ws = build_collectively(ex.ep_group,
+                                lambda: ExpertParallelWorkspace(ex.ep_group, rows, hidden, device, layers),
                                 "expert-parallel workspace")
         ex.extras["ep_workspace"] = ws
         if ws is None:
@@ -81,8 +105,10 @@ def workspace_for(ex, rows: int, hidden: int, device: torch.device) -> ExpertPar
 class ExpertParallelPlan:
     """Routing plan of one layer under expert parallelism (device tensors only, no host synchronisation)."""
 
-    def __init__(self, expert_ids: torch.Tensor, num_experts: int, capacity: int, ex, hidden: int):
+    def __init__(self, expert_ids: torch.Tensor, num_experts: int, capacity: int, ex, hidden: int,
+                 layer_slot: int | None = None):
         lib = _moe_lib()
+        self.layer_slot = layer_slot          # index of the MoE layer among the model's MoE layers (or None)
         dev = expert_ids.device
         R, rank = ex.ep_size, ex.ep_rank
         E = num_experts
@@ -120,6 +146,7 @@ class ExpertParallelPlan:
         native._check(lib.b200_moe_layout(mine.data_ptr(), el, 0, TILE, tiles, starts_local.data_ptr(),
                                           k_range.data_ptr(), tile_group.data_ptr(), None, st), "b200_moe_layout")
         self.owner = SimpleNamespace(tile_group=tile_group, k_range=k_range.view(el, 2))
+        self.local_starts, self.local_counts, self.local_experts = starts_local, mine, el
         self.ex = ex
         self.ws = workspace_for(ex, self.rows_per_rank, hidden, dev)   # None: peer memory refused, use NCCL
 
@@ -128,21 +155,29 @@ class ExpertParallelPlan:
         return (self.dest >= 0).view(self.T, self.k)
 
 
-def _push_rows(x, scale, plan: ExpertParallelPlan, ws: ExpertParallelWorkspace, *, keep: bool) -> torch.Tensor:
-    """Zero my inbox, barrier, store my rows into the owners' inboxes, barrier.  Returns my inbox: a private copy
-    when the rows must outlive the next use of the inbox (``keep``: forward activations saved for backward), else
-    the arena view itself (gradients, which the next autograd node consumes before anything is pushed again)."""
+def _push_rows(x, scale, plan: ExpertParallelPlan, ws: ExpertParallelWorkspace, *, forward: bool) -> torch.Tensor:
+    """Store my rows into the owners' inboxes and return my inbox (an arena view, no copy).
+
+    ``forward``: the rows are activations that the backward pass reads again.  They go into the inbox of this MoE
+    layer, which nothing else writes during the step, so no barrier has to protect a previous reader.  Without a
+    per-layer inbox (or for gradient rows) the shared inbox is used: a barrier first makes sure every owner has
+    finished reading what the previous push left there, and forward rows are copied out afterwards.  Only the
+    padding rows behind each expert's block are zeroed: the real rows are overwritten by the senders."""
 
     lib = _moe_lib()
-    used = ws.inbox[:plan.rows_per_rank]
-    used.zero_()
-    ws.barrier()
+    inbox, offset, private = ws.inbox_for(plan.layer_slot if forward else None)
+    used = inbox[:plan.rows_per_rank]
+    rc = lib.b200_moe_zero_pad(used.data_ptr(), plan.local_starts.data_ptr(), plan.local_counts.data_ptr(),
+                               plan.local_experts, x.shape[1], native._stream())
+    native._check(rc, "b200_moe_zero_pad")
+    if not private:
+        ws.barrier()
     rc = lib.b200_moe_gather(x.data_ptr(), None if scale is None else scale.data_ptr(), None, plan.dest.data_ptr(),
-                             ws.ptrs(ws.inbox_off), ws.world, plan.T * plan.k, x.shape[1], plan.k, plan.rows_per_rank,
+                             ws.ptrs(offset), ws.world, plan.T * plan.k, x.shape[1], plan.k, plan.rows_per_rank,
                              native._stream())
     native._check(rc, "b200_moe_gather")
     ws.barrier()
-    return used.clone() if keep else used
+    return used.clone() if (forward and not private) else used
 
 
 def _pull_rows(local_rows, w, plan: ExpertParallelPlan, ws: ExpertParallelWorkspace, rows_out=None) -> torch.Tensor:
@@ -167,7 +202,7 @@ class _EpDispatchFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, plan, ws):
         ctx.plan, ctx.ws = plan, ws
-        return _push_rows(x.contiguous(), None, plan, ws, keep=True)
+        return _push_rows(x.contiguous(), None, plan, ws, forward=True)
 
     @staticmethod
     def backward(ctx, d_rows):
@@ -195,7 +230,7 @@ class _EpCombineFn(torch.autograd.Function):
         mine, w32 = ctx.saved_tensors
         plan, ws = ctx.plan, ctx.ws
         dy = dy.contiguous()
-        d_rows = _push_rows(dy, w32, plan, ws, keep=False) if ctx.needs_input_grad[0] else None
+        d_rows = _push_rows(dy, w32, plan, ws, forward=False) if ctx.needs_input_grad[0] else None
         dw = None
         if ctx.needs_input_grad[1]:
             # dw[a] = <row a of my unweighted expert outputs, dy[token of a]>: one warp per assignment
