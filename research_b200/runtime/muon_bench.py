@@ -299,6 +299,9 @@ def benchmark_muon(*, warmup: int = 2, iters: int = 5, artifact_dir: str | Path 
 
     from research_b200.ops import functional as Fn
 
+    from research_b200.parallel.mesh import init_distributed
+
+    init_distributed()            # under torchrun: the ranks of this launch form the tensor-parallel group
     device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
     started_group = False
     if not dist.is_initialized():
