@@ -215,6 +215,7 @@ PARALLELISM_FIELDS: tuple[Field, ...] = (
     ("expert_parallel_axis", _str, "auto"),
     ("context_attention", _str, "gather"),
     ("fsdp_resident", _bool, True),
+    ("vocab_parallel_head", _bool, False),
 )
 ARTIFACT_FIELDS: tuple[Field, ...] = (
     ("wandb_enabled", _bool, False),

@@ -457,10 +457,17 @@ class ParallelismSpec:
     # false: with mode="fsdp" the compute copy of the weights is kept only where it is owned and every layer's
     # weights are fetched from their owners right before the layer runs (ZeRO-3); true keeps them on every rank
     fsdp_resident: bool = True
+    # true: under tensor parallelism the lm_head is split over the vocabulary (each rank scores its slice of the
+    # vocabulary for all tokens; max / sum-exp / target logit are reduced over the group) instead of being kept
+    # whole on every rank with the tokens split
+    vocab_parallel_head: bool = False
 
     def __post_init__(self) -> None:
         _one_of("parallelism.mode", self.mode, PARALLELISM_MODES)
         _bool("parallelism.fsdp_resident", self.fsdp_resident)
+        _bool("parallelism.vocab_parallel_head", self.vocab_parallel_head)
+        if self.vocab_parallel_head and not self.tensor_parallel:
+            raise ContractError("parallelism.vocab_parallel_head=true requires parallelism.tensor_parallel=true")
         if not self.fsdp_resident and self.mode != "fsdp":
             raise ContractError("parallelism.fsdp_resident=false requires parallelism.mode='fsdp'")
         _one_of("parallelism.context_attention", self.context_attention, ("gather", "ulysses"))

@@ -199,7 +199,12 @@ def logical_parameters(model: TransformerLM) -> tuple[ParamMeta, ...]:
             raise ContractError(f"unrecognized layer type {type(layer).__name__}")
     entries.append(_meta("norm.scale", "final_norm", (H,), "norm.scale"))
     if model.lm_head is not None:
-        entries.append(_meta("lm_head.kernel", "lm_head", (H, V), "lm_head", None, True))
+        head = _meta("lm_head.kernel", "lm_head", (H, V), "lm_head", None, True)
+        if model.vocab_parallel:      # split over the vocabulary (logical axis 1) across the tensor-parallel group
+            import dataclasses
+
+            head = dataclasses.replace(head, tp_axis=1)
+        entries.append(head)
     return tuple(entries)
 
 

@@ -211,6 +211,7 @@ class ExecutionContext:
     ep_axis_sharing: str | None = None
     cp_attention: str = "gather"            # context-parallel attention: K/V all-gather or Ulysses all-to-all
     fused: bool = True                      # use fused compute+collective kernels where available
+    vocab_parallel: bool = False            # lm_head split over the vocabulary across the tensor-parallel group
     extras: dict[str, Any] = field(default_factory=dict)
 
     # ---- sizes -----------------------------------------------------------------------------------

@@ -223,8 +223,14 @@ class TransformerLM(nn.Module):
         self.spec = spec
         self.ex = ex
         H, V = spec.hidden_size, spec.vocab_size
-        # the lm_head stays whole on every tensor-parallel rank: each rank scores its own sequence shard
-        self.vocab_local = V
+        # default: the lm_head stays whole on every tensor-parallel rank and each rank scores its own sequence shard;
+        # with ``vocab_parallel`` each rank holds V / tp rows of it and scores them for all tokens
+        self.vocab_parallel = bool(ex.vocab_parallel and ex.tp_size > 1 and not spec.tied_embeddings)
+        if ex.vocab_parallel and ex.tp_size > 1 and spec.tied_embeddings:
+            raise ContractError("parallelism.vocab_parallel_head needs untied embeddings (model.tied_embeddings=false)")
+        if self.vocab_parallel and V % ex.tp_size:
+            raise ContractError(f"vocab_size {V} is not divisible by the tensor-parallel size {ex.tp_size}")
+        self.vocab_local = V // ex.tp_size if self.vocab_parallel else V
         self.embed = nn.Parameter(torch.empty(V, H, dtype=torch.float32))
         self.embed_scale = 1.0
         layers: list[nn.Module] = []
@@ -325,8 +331,17 @@ class TransformerLM(nn.Module):
     def forward(self, input_ids: torch.Tensor, token_doc_ids: torch.Tensor | None = None) -> ModelOutput:
         h, aux, stats = self.hidden_states(input_ids, token_doc_ids)
         h = self.ex.gather_sequence(h)
-        logits = Fn.linear(h, self.head_weight())
+        logits = self.full_logits(Fn.linear(h, self.head_weight()))
         return ModelOutput(logits=logits, aux_losses=aux, router_stats=stats)
+
+    def full_logits(self, logits: torch.Tensor) -> torch.Tensor:
+        """Logits over the whole vocabulary: with a vocabulary-parallel lm_head the ranks' slices are concatenated."""
+
+        if not self.vocab_parallel:
+            return logits
+        from research_b200.models.execution import all_gather_dim
+
+        return all_gather_dim(logits, self.ex.tp_group, logits.dim() - 1)
 
     # ---- inference with a dense functional KV cache --------------------------------------------
     def _infer_block(self, layer, x, delta, positions, attend):
@@ -363,4 +378,4 @@ class TransformerLM(nn.Module):
         h, _ = self.norm.add_forward(x, delta)
         if last_only:
             h = h[:, -1:].contiguous()
-        return Fn.linear(h, self.head_weight())
+        return self.full_logits(Fn.linear(h, self.head_weight()))

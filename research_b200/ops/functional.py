@@ -523,6 +523,83 @@ def lm_head_cross_entropy(x: torch.Tensor, p: torch.Tensor, targets: torch.Tenso
     return ((lse - tl) * mf).sum(), (lse.pow(2) * mf).sum()
 
 
+class _VocabParallelCeFn(torch.autograd.Function):
+    """Cross-entropy over a vocabulary that is split across ``group``: this rank holds rows ``[rank * Vl, (rank + 1)
+    * Vl)`` of the lm_head and scores them for all tokens; the row maximum, the sum of exponentials and the target
+    logit are reduced over the group (one MAX and one SUM reduction per token chunk).  Like :class:`_LmHeadCeFn` the
+    forward also produces the gradients of ``grad_scale * (ce + z_weight * z)``: ``dx`` holds this rank's partial
+    input gradient (the caller's gather of the activations sums the partials in its backward) and the weight
+    gradient goes to ``main_grad`` (native path) or is returned (reference path)."""
+
+    @staticmethod
+    def forward(ctx, x, p, targets, mask, grad_scale, z_weight, group, chunk_tokens, native_path):
+        import torch.distributed as dist
+
+        w = compute_weight(p, x) if native_path else p.to(x.dtype)
+        T, H = x.shape
+        Vl = w.shape[0]
+        first = dist.get_rank(group) * Vl
+        need_grad = bool(ctx.needs_input_grad[0] or ctx.needs_input_grad[1])
+        dx = torch.zeros_like(x) if need_grad else None
+        dw = None if native_path or not need_grad else torch.zeros(w.shape, dtype=torch.float32, device=x.device)
+        ce_sum = torch.zeros((), dtype=torch.float32, device=x.device)
+        z_sum = torch.zeros((), dtype=torch.float32, device=x.device)
+        for t0 in range(0, T, chunk_tokens):
+            t1 = min(t0 + chunk_tokens, T)
+            xc = x[t0:t1]
+            if native_path:
+                logits = native.gemm(xc, w, trans_b=True, out_dtype=torch.float32)
+            else:
+                logits = (xc @ w.t()).float()
+            m = logits.max(dim=1).values
+            dist.all_reduce(m, op=dist.ReduceOp.MAX, group=group)
+            local = targets[t0:t1].long() - first
+            mine = (local >= 0) & (local < Vl)
+            picked = logits.gather(1, local.clamp(0, Vl - 1)[:, None])[:, 0] * mine
+            packed = torch.stack([torch.exp(logits - m[:, None]).sum(dim=1), picked])
+            dist.all_reduce(packed, group=group)
+            lse = m + packed[0].log()
+            mf = mask[t0:t1].float()
+            ce_sum += ((lse - packed[1]) * mf).sum()
+            z_sum += (lse.pow(2) * mf).sum()
+            if need_grad:
+                # d/dlogits of grad_scale * (ce + zw * lse^2) = grad_scale * mask * ((1 + 2 zw lse) softmax - onehot)
+                probs = torch.exp(logits - lse[:, None])
+                g = probs * ((1.0 + 2.0 * z_weight * lse) * mf * grad_scale)[:, None]
+                rows = torch.nonzero(mine, as_tuple=True)[0]
+                g[rows, local[rows]] -= (mf * grad_scale)[rows]
+                g = g.to(x.dtype)
+                if native_path:
+                    native.gemm(g, w, trans_b=False, out=dx[t0:t1])
+                    if p.requires_grad:
+                        native.gemm(g, xc, trans_a=True, trans_b=False, out=_main_grad(p), accumulate=True)
+                else:
+                    dx[t0:t1] = g @ w
+                    dw += (g.t() @ xc).float()
+        ctx.save_for_backward(dx, dw)
+        ctx.mark_non_differentiable(z_sum)
+        return ce_sum, z_sum
+
+    @staticmethod
+    def backward(ctx, g_loss, g_z):
+        dx, dw = ctx.saved_tensors
+        return dx, (None if dw is None else dw.to(dx.dtype)), None, None, None, None, None, None, None
+
+
+def vocab_parallel_cross_entropy(x: torch.Tensor, p: torch.Tensor, targets: torch.Tensor, mask: torch.Tensor, group, *,
+                                 grad_scale: float, z_weight: float = 0.0, chunk_tokens: int = 4096):
+    """Masked CE (and z-loss sum) with the lm_head ``p`` (``[V / n, H]``: this rank's rows) split over ``group``.
+
+    ``x``: the activations of ALL tokens (the same on every rank of the group).  Returns ``(ce_sum, z_sum)``, the
+    same on every rank; the gradient of ``grad_scale * (ce_sum + z_weight * z_sum)`` is formed inside the forward
+    pass as in :func:`lm_head_cross_entropy`, so callers backpropagate through ``ce_sum`` with factor 1.
+    Reference: src/jaxtitan/models/execution.py:209-219, src/jaxtitan/steps/eval.py:40-51."""
+
+    x2 = x.reshape(-1, x.shape[-1]).contiguous()
+    return _VocabParallelCeFn.apply(x2, p, targets.reshape(-1), mask.reshape(-1), grad_scale, z_weight, group,
+                                    chunk_tokens, use_native(x2))
+
+
 def objective_from_sums(ce_sum: torch.Tensor, z_sum: torch.Tensor, *, grad_scale: float, z_weight: float,
                         native_path: bool) -> torch.Tensor:
     """The scalar to call ``backward()`` on so that both paths give ``d[grad_scale*(ce + zw*z)]``."""

@@ -145,4 +145,5 @@ def execution_context_for(mesh: MeshContext, parallelism: ParallelismSpec, *, fu
         ep_axis_sharing=ep.axis_sharing,
         cp_attention=parallelism.context_attention,
         fused=fused,
+        vocab_parallel=bool(parallelism.vocab_parallel_head and parallelism.tensor_parallel),
     )

@@ -27,7 +27,7 @@ class EvalStep:
         self.device = store.device
         self.stager = BatchStager(self.device, [0])
         self.loss_axes = [a for a in ("data", "fsdp", "cp") if mesh.size(a) > 1]
-        if result.execution.sp:
+        if result.execution.sp and not result.model.vocab_parallel:
             self.loss_axes.append("tp")
 
     @torch.no_grad()
@@ -39,10 +39,15 @@ class EvalStep:
         h, _, _ = self.model.hidden_states(db.input_ids, db.token_doc_ids)
         targets, mask = db.target_ids, db.loss_mask
         ex = self.result.execution
-        if ex.sp:
-            targets = targets.chunk(ex.tp_size, dim=1)[ex.tp_rank].contiguous()
-            mask = mask.chunk(ex.tp_size, dim=1)[ex.tp_rank].contiguous()
-        ce_sum, _ = Fn.lm_head_cross_entropy(h, self.model.head_weight(), targets, mask, grad_scale=1.0, z_weight=0.0)
+        if self.model.vocab_parallel:
+            ce_sum, _ = Fn.vocab_parallel_cross_entropy(ex.gather_sequence(h), self.model.head_weight(), targets, mask,
+                                                        ex.tp_group, grad_scale=1.0, z_weight=0.0)
+        else:
+            if ex.sp:
+                targets = targets.chunk(ex.tp_size, dim=1)[ex.tp_rank].contiguous()
+                mask = mask.chunk(ex.tp_size, dim=1)[ex.tp_rank].contiguous()
+            ce_sum, _ = Fn.lm_head_cross_entropy(h, self.model.head_weight(), targets, mask, grad_scale=1.0,
+                                                 z_weight=0.0)
         total = ce_sum.detach().float().reshape(1)
         for axis in self.loss_axes:
             group = self.mesh.group(axis)

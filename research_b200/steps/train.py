@@ -141,22 +141,30 @@ class TrainStep:
         self.z_weight = float(spec.training.loss.z_loss_weight)
         self.native = (self.device.type == "cuda" and store.compute_dtype == torch.bfloat16 and Fn.native_enabled())
         self.loss_axes = [a for a in ("data", "fsdp", "cp") if mesh.size(a) > 1]
-        if result.execution.sp:
-            self.loss_axes.append("tp")
+        if result.execution.sp and not result.model.vocab_parallel:
+            self.loss_axes.append("tp")       # token-parallel loss: every tensor-parallel rank scored other tokens
 
     # ------------------------------------------------------------------------------------------------
     def _microbatch(self, db: DeviceBatch, grad_scale: float, global_mb_tokens: float, dp_world: int):
         model, ex = self.model, self.result.execution
         h, aux_losses, stats = model.hidden_states(db.input_ids, db.token_doc_ids)
         targets, mask = db.target_ids, db.loss_mask
-        if ex.sp:  # the final hidden states are sequence-sharded over tp: shard targets the same way
-            n, r = ex.tp_size, ex.tp_rank
-            targets = targets.chunk(n, dim=1)[r].contiguous()
-            mask = mask.chunk(n, dim=1)[r].contiguous()
         head = self._head_weight()
-        ce_sum, z_sum = Fn.lm_head_cross_entropy(h, head, targets, mask, grad_scale=grad_scale,
-                                                 z_weight=self.z_weight)
-        native_path = Fn.use_native(h)
+        if model.vocab_parallel:
+            # every tensor-parallel rank scores its slice of the vocabulary for all tokens; the loss sums come out
+            # the same on every rank of the group and the gradient is formed inside the op on both paths
+            h = ex.gather_sequence(h)
+            ce_sum, z_sum = Fn.vocab_parallel_cross_entropy(h, head, targets, mask, ex.tp_group,
+                                                            grad_scale=grad_scale, z_weight=self.z_weight)
+            native_path = True
+        else:
+            if ex.sp:  # the final hidden states are sequence-sharded over tp: shard targets the same way
+                n, r = ex.tp_size, ex.tp_rank
+                targets = targets.chunk(n, dim=1)[r].contiguous()
+                mask = mask.chunk(n, dim=1)[r].contiguous()
+            ce_sum, z_sum = Fn.lm_head_cross_entropy(h, head, targets, mask, grad_scale=grad_scale,
+                                                     z_weight=self.z_weight)
+            native_path = Fn.use_native(h)
         objective = Fn.objective_from_sums(ce_sum, z_sum, grad_scale=grad_scale, z_weight=self.z_weight,
                                            native_path=native_path)
         aux_total = None
@@ -265,7 +273,9 @@ class TrainStep:
         pos = 2 * mb
         aux_host = None
         if has_aux:
-            n_aux_ranks = dp_world * (mesh.size("tp") if self.result.execution.sp else 1)
+            n_aux_ranks = 1
+            for axis in self.loss_axes:          # the ranks whose values the packed reduction added up
+                n_aux_ranks *= mesh.size(axis)
             aux_host = [v / n_aux_ranks for v in host[pos:pos + mb]]
             pos += mb
         grad_norm, clip_scale = host[pos], host[pos + 1]

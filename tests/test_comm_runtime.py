@@ -309,6 +309,9 @@ def _run_training(tmp_path, world, axes, sizes, flags, peer, port, extra_env=Non
     # context parallelism: K/V exchange inside the attention kernels against all-gather + reduce-scatter
     ("cp2_ring", ["cp"], [2], {"parallelism": {"mode": "ddp", "context_parallel": True},
                                "model": {"attention_doc_mask": False}}),
+    # lm_head split over the vocabulary: max / sum-exp / target-logit reductions over the tensor-parallel group
+    ("tp2_vocab_parallel_head", ["tp"], [2], {"parallelism": {"mode": "ddp", "tensor_parallel": True,
+                                                              "vocab_parallel_head": True}}),
     # weights sharded at rest: every layer's weights are fetched from their owners' arenas before the layer runs
     ("fsdp2_muon_sharded_params", ["fsdp"], [2], {"parallelism": {"mode": "fsdp", "fsdp_resident": False},
                                                   "optimizer": "muon"}),

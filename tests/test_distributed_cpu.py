@@ -34,6 +34,8 @@ CASES = [
     ("zero2", "decoder", "adamw", {"fsdp": 2}, {"mode": "zero2"}),
     ("fsdp2_muon", "decoder", "muon", {"fsdp": 2}, {"mode": "fsdp"}),
     ("tp2", "decoder", "adamw", {"tp": 2}, {"mode": "ddp", "tensor_parallel": True}),
+    ("tp2_vocab_parallel_head", "decoder", "adamw", {"tp": 2},
+     {"mode": "ddp", "tensor_parallel": True, "vocab_parallel_head": True}),
     ("tp2_muon_duplicated", "decoder", "muon", {"tp": 2}, {"mode": "ddp", "tensor_parallel": True}),
     ("cp2", "decoder", "adamw", {"cp": 2}, {"mode": "ddp", "context_parallel": True}),
     ("cp2_ulysses", "decoder", "adamw", {"cp": 2},
