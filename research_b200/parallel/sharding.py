@@ -129,8 +129,15 @@ class ParamStore:
                 if mesh.size(axis) > 1 and not (is_expert and axis == ep_axis):
                     axes.append(axis)
             replicated_over_tp = all(m.tp_axis is None for m in metas) and not is_expert
-            if tp_active and replicated_over_tp and result.execution.sp:
-                axes.append("tp")  # sequence-parallel regions see only a slice of the tokens
+            head_local = any(m.tag in ("attention_q_norm", "attention_k_norm") for m in metas)
+            if tp_active and replicated_over_tp and (result.execution.sp or head_local):
+                # sequence-parallel regions see only a slice of the tokens; the per-head q/k norm scales see only
+                # this rank's heads whether or not the sequence is split
+                axes.append("tp")
+            if tp_active and is_expert and result.execution.sp and "tp" not in axes:
+                # routed experts are not split over tp: every tensor-parallel rank routes its own slice of the tokens
+                # through the same expert weights, so their gradients are partial sums over that axis
+                axes.append("tp")
             shard_axis = None
             if mode in ("zero2", "fsdp") and mesh.size("fsdp") > 1 and not (is_expert and ep_axis == "fsdp"):
                 shard_axis = "fsdp"

@@ -34,6 +34,16 @@ CASES = [
     ("zero2", "decoder", "adamw", {"fsdp": 2}, {"mode": "zero2"}),
     ("fsdp2_muon", "decoder", "muon", {"fsdp": 2}, {"mode": "fsdp"}),
     ("tp2", "decoder", "adamw", {"tp": 2}, {"mode": "ddp", "tensor_parallel": True}),
+    # compositions on four ranks
+    ("hsdp_data2_fsdp2", "decoder", "adamw", {"data": 2, "fsdp": 2}, {"mode": "fsdp"}),
+    ("hsdp_data2_fsdp2_muon", "decoder", "muon", {"data": 2, "fsdp": 2}, {"mode": "fsdp"}),
+    ("fsdp2_tp2", "decoder", "adamw", {"fsdp": 2, "tp": 2}, {"mode": "fsdp", "tensor_parallel": True}),
+    ("cp2_tp2", "decoder", "adamw", {"cp": 2, "tp": 2},
+     {"mode": "ddp", "context_parallel": True, "tensor_parallel": True}),
+    ("tp2_ep2_moe", "trinity", "adamw", {"tp": 2, "ep": 2},
+     {"mode": "ddp", "tensor_parallel": True, "expert_parallel": True}),
+    ("fsdp2_sharded_params_tp2", "decoder", "adamw", {"fsdp": 2, "tp": 2},
+     {"mode": "fsdp", "tensor_parallel": True, "fsdp_resident": False}),
     ("tp2_vocab_parallel_head", "decoder", "adamw", {"tp": 2},
      {"mode": "ddp", "tensor_parallel": True, "vocab_parallel_head": True}),
     ("tp2_muon_duplicated", "decoder", "muon", {"tp": 2}, {"mode": "ddp", "tensor_parallel": True}),
@@ -62,6 +72,8 @@ def test_layout_matches_single_process(tmp_path, name, kind, optimizer, mesh, pa
     tol = 2e-3 if optimizer == "muon" else 2e-4
     for got in results:
         _compare(ref, got, tol)
-    # every rank ends with the same logical parameters
+    # every rank ends with the same logical parameters, all of them finite
     for name_, t in results[0]["model"].items():
-        assert torch.equal(t, results[1]["model"][name_]), name_
+        assert torch.isfinite(t).all(), name_
+        for other in results[1:]:
+            assert torch.equal(t, other["model"][name_]), name_
