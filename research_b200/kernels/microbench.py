@@ -46,7 +46,7 @@ def bf(shape, scale=1.0):
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("op", choices=["gemm", "attn_fwd", "attn_bwd", "rmsnorm", "swiglu", "ce", "adamw", "decode", "moe", "router"])
+    ap.add_argument("op", choices=["gemm", "attn_fwd", "attn_bwd", "rmsnorm", "rmsnorm_bwd", "dion2", "swiglu", "ce", "adamw", "decode", "moe", "router"])
     ap.add_argument("--experts", type=int, default=64)
     ap.add_argument("--top-k", type=int, default=8)
     ap.add_argument("--m", type=int, default=16384)
@@ -99,6 +99,37 @@ def main() -> int:
         ms = timed(lambda: native.rmsnorm_fwd(x, w, 1e-6), args.warmup, args.iters)
         gbs = 2 * x.numel() * 2 / ms / 1e6
         out.update(shape=[args.rows, args.hidden], ms=ms, gbs=gbs, frac_of_peak=gbs / pk["hbm_gbs"])
+    elif args.op == "rmsnorm_bwd":
+        x, dy, w = bf((args.rows, args.hidden)), bf((args.rows, args.hidden)), torch.ones(args.hidden, device="cuda")
+        rstd = torch.rsqrt(x.float().pow(2).mean(-1) + 1e-6)
+        dw = torch.zeros(args.hidden, device="cuda")
+        ms = timed(lambda: native.rmsnorm_bwd(x, w, rstd, dy, dw), args.warmup, args.iters)
+        gbs = 3 * x.numel() * 2 / ms / 1e6                       # x and dy read, dx written
+        out.update(shape=[args.rows, args.hidden], ms=ms, gbs=gbs, frac_of_peak=gbs / pk["hbm_gbs"])
+    elif args.op == "dion2":
+        # one Dion2 update of a stack of expert matrices without the orthogonaliser: accumulate + select + gather,
+        # then apply; algorithmic bytes: m, g read and m written (12 B), w read and written + bf16 copy (10 B)
+        n, rows, cols = args.experts // 8 or 1, args.hidden, args.k
+        g, m, w = (torch.randn(n, rows, cols, device="cuda") for _ in range(3))
+        sh = torch.empty(n, rows, cols, device="cuda", dtype=torch.bfloat16)
+        res = {}
+        for axis in (0, 1):
+            k = (rows if axis == 0 else cols) // 4
+            o = bf((n, k, cols) if axis == 0 else (n, rows, k))
+            state = {}
+
+            def first():
+                state["sel"] = native.dion2_select_stack(g, m, None, n, rows, cols, rows * cols, axis, k, 1e-8)
+
+            def second():
+                native.dion2_apply(w, m, o, state["sel"][2], sh, n, rows, cols, k, rows * cols, axis, 0.999, 1e-3, 0.95)
+
+            ms1 = timed(first, args.warmup, args.iters)
+            ms2 = timed(second, args.warmup, args.iters)
+            b1, b2 = 12 * g.numel() + 4.5 * g.numel() / 4, 10 * g.numel() + 10 * g.numel() / 4
+            res[f"axis{axis}"] = {"select_ms": ms1, "select_frac": b1 / ms1 / 1e6 / pk["hbm_gbs"],
+                                  "apply_ms": ms2, "apply_frac": b2 / ms2 / 1e6 / pk["hbm_gbs"]}
+        out.update(shape=[n, rows, cols], **res)
     elif args.op == "swiglu":
         gu = bf((args.rows, 2 * args.hidden))
         ms = timed(lambda: native.swiglu_fwd(gu), args.warmup, args.iters)
@@ -112,7 +143,7 @@ def main() -> int:
         ms = timed(lambda: native.ce_fwd_bwd(logits, tgt, mask, 1.0 / rows, 0.0), args.warmup, args.iters)
         gbs = 2 * logits.numel() * 2 / ms / 1e6
         out.update(shape=[rows, args.vocab], ms=ms, gbs=gbs, frac_of_peak=gbs / pk["hbm_gbs"],
-                   note="algorithmic bytes = one read + one write of the logits; the kernel reads the row three times")
+                   note="algorithmic bytes = one read + one write of the logits")
     elif args.op == "adamw":
         n = args.rows * args.hidden
         p, m, v = (torch.zeros(n, device="cuda") for _ in range(3))

@@ -25,6 +25,7 @@ import torch
 import torch.distributed as dist
 
 from research_b200.ops import functional as Fn
+from research_b200.ops import native
 
 EP_DISPATCHERS = ("all_to_all", "rdep_static", "psum")
 
@@ -287,6 +288,8 @@ class ExecutionContext:
         if not (self.fused and self.sp and x.is_cuda and x.dtype == torch.bfloat16 and Fn.use_native(x)):
             return None
         if os.environ.get("RESEARCH_B200_PEER_COLLECTIVES", "1") == "0" or self.tp_size > 8:
+            return None
+        if native.deterministic():      # the scatter epilogue reduce-adds into the owner in arrival order
             return None
         if rows_local % 128 or width % 64:
             return None

@@ -11,6 +11,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "b200.cuh"
+#include "host_util.cuh"
+
 namespace {
 
 constexpr int kWarpsPerBlock = 8;
@@ -333,6 +336,74 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
     const float v = dw_smem[i];
     if (v != 0.f) atomicAdd(&dw[i], v);
   }
+}
+
+// RMSNorm backward for wide rows (H = 8 * blockDim.x, H % 256 == 0): a thread owns 8 columns of every row, so a row
+// of x and dy is read once into registers, the dw partial sums are 8 registers, and R rows are in flight per
+// iteration (one block-wide reduction of R dot products through shared memory, double buffered by iteration parity).
+template <int R, int MAXT, int MINB>
+__global__ void __launch_bounds__(MAXT, MINB)
+rmsnorm_bwd_cols_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
+                        const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dy,
+                        const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
+                        float* __restrict__ dw, int rows, int H) {
+  __shared__ float red[2][R][32];
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5, nwarps = blockDim.x >> 5;
+  const int nvec = H >> 3;
+  const float inv_h = 1.f / (float)H;
+  float wv[8], acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  load8f(w + t * 8, wv);
+  int parity = 0;
+  for (long long r0 = (long long)blockIdx.x * R; r0 < rows; r0 += (long long)gridDim.x * R, parity ^= 1) {
+    uint4 xr[R], gr[R], rr[R];
+    float rs[R], dot[R];
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int j = 0; j < R; ++j) {
+      const long long row = r0 + j;
+      const bool valid = row < rows;
+      xr[j] = valid ? reinterpret_cast<const uint4*>(x)[row * nvec + t] : zero;
+      gr[j] = valid ? reinterpret_cast<const uint4*>(dy)[row * nvec + t] : zero;
+      rr[j] = (valid && dres) ? reinterpret_cast<const uint4*>(dres)[row * nvec + t] : zero;
+      rs[j] = valid ? rstd_in[row] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < R; ++j) {
+      float f[8], g[8];
+      unpack8(xr[j], f);
+      unpack8(gr[j], g);
+      float d = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) d += g[i] * wv[i] * f[i];
+      d = warp_sum(d * rs[j]);
+      if (lane == 0) red[parity][j][warp] = d;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < R; ++j) {
+      float d = lane < nwarps ? red[parity][j][lane] : 0.f;
+      dot[j] = warp_sum(d) * inv_h;
+    }
+#pragma unroll
+    for (int j = 0; j < R; ++j) {
+      const long long row = r0 + j;
+      if (row >= rows) break;
+      float f[8], g[8], r[8], o[8];
+      unpack8(xr[j], f);
+      unpack8(gr[j], g);
+      unpack8(rr[j], r);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float xhat = f[i] * rs[j];
+        o[i] = rs[j] * (g[i] * wv[i] - xhat * dot[j]) + r[i];
+        acc[i] += g[i] * xhat;
+      }
+      reinterpret_cast<uint4*>(dx)[row * nvec + t] = pack8(o);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    if (acc[i] != 0.f) atomicAdd(&dw[t * 8 + i], acc[i]);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -695,6 +766,118 @@ ce_fwd_bwd_kernel(__nv_bfloat16* __restrict__ logits, long long ld, const int* _
   }
 }
 
+// The same op with the row staged in shared memory: one bulk copy in, three passes over shared memory, one bulk
+// copy out, so the logits cross the memory system once in each direction and two or three rows per SM overlap
+// their phases.  V % 8 == 0 and 2 V bytes of dynamic shared memory; 16-byte aligned rows.
+constexpr int kCeThreads = 512;
+constexpr uint32_t kCeChunkBytes = 32768;
+__global__ void __launch_bounds__(kCeThreads)
+ce_fwd_bwd_staged_kernel(__nv_bfloat16* __restrict__ logits, long long ld, const int* __restrict__ targets,
+                         const uint8_t* __restrict__ mask, float* __restrict__ loss_row, float* __restrict__ z_row,
+                         float* __restrict__ lse_row, int V, float grad_scale, float z_weight, int write_grad,
+                         int* __restrict__ status) {
+  extern __shared__ __align__(128) unsigned char ce_row_smem[];
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ float red[2][32];
+  __shared__ int abort_flag;
+  const long long row = blockIdx.x;
+  __nv_bfloat16* grow = logits + row * ld;
+  uint4* srow = reinterpret_cast<uint4*>(ce_row_smem);
+  const int nvec = V >> 3;
+  const uint32_t bytes = (uint32_t)V * 2u;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (mask[row] == 0) {
+    if (write_grad) {
+      const uint4 z = make_uint4(0, 0, 0, 0);
+      for (int v = threadIdx.x; v < nvec; v += kCeThreads) reinterpret_cast<uint4*>(grow)[v] = z;
+    }
+    if (threadIdx.x == 0) { loss_row[row] = 0.f; z_row[row] = 0.f; if (lse_row) lse_row[row] = 0.f; }
+    return;
+  }
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    b200::mbar_init(&bar, 1);
+    b200::mbar_fence_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    b200::mbar_expect_tx(&bar, bytes);
+    for (uint32_t off = 0; off < bytes; off += kCeChunkBytes)
+      b200::bulk_g2s(ce_row_smem + off, reinterpret_cast<const unsigned char*>(grow) + off,
+                     min(kCeChunkBytes, bytes - off), &bar);
+  }
+  const b200::AbortCtx ab{&abort_flag, status};
+  const bool ok = b200::mbar_wait(&bar, 0, ab, b200::ERR_WAIT_FULL);
+  if (!__syncthreads_and(ok)) {
+    // the limit ran out (recorded in the status word): give the copies still in flight one more bounded wait so
+    // that they do not land in shared memory of a CTA that has left, then leave without writing anything
+    if (threadIdx.x == 0) {
+      const uint64_t t0 = b200::globaltimer_ns();
+      while (!b200::mbar_try_wait(&bar, 0) && b200::globaltimer_ns() - t0 < b200::kWaitLimitNs) {}
+    }
+    __syncthreads();
+    return;
+  }
+  const int tgt = targets[row];
+  const float tl = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(ce_row_smem)[tgt]);
+  // pass 1: the maximum, on packed pairs (no conversion to fp32: bf16 compares exactly)
+  __nv_bfloat162 m2v = __float2bfloat162_rn(-INFINITY);
+  for (int v = threadIdx.x; v < nvec; v += kCeThreads) {
+    const uint4 q = srow[v];
+    m2v = __hmax2(m2v, *reinterpret_cast<const __nv_bfloat162*>(&q.x));
+    m2v = __hmax2(m2v, *reinterpret_cast<const __nv_bfloat162*>(&q.y));
+    m2v = __hmax2(m2v, *reinterpret_cast<const __nv_bfloat162*>(&q.z));
+    m2v = __hmax2(m2v, *reinterpret_cast<const __nv_bfloat162*>(&q.w));
+  }
+  float m = fmaxf(__low2float(m2v), __high2float(m2v));
+  m = warp_max(m);
+  if (lane == 0) red[0][warp] = m;
+  __syncthreads();
+  m = warp_max(red[0][lane & (kCeThreads / 32 - 1)]);
+  constexpr float kLog2e = 1.4426950408889634f;
+  const float m2 = m * kLog2e;
+  float s = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += kCeThreads) {
+    float f[8];
+    unpack8(srow[v], f);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) s += b200::ex2_approx(fmaf(f[k], kLog2e, -m2));
+  }
+  s = warp_sum(s);
+  if (lane == 0) red[1][warp] = s;
+  __syncthreads();
+  s = warp_sum(lane < kCeThreads / 32 ? red[1][lane] : 0.f);
+  const float lse = m + logf(s);
+  if (threadIdx.x == 0) {
+    loss_row[row] = lse - tl;
+    z_row[row] = lse * lse;
+    if (lse_row) lse_row[row] = lse;
+  }
+  if (!write_grad) return;
+  const float coef = grad_scale * (1.f + 2.f * z_weight * lse) / s;
+  for (int v = threadIdx.x; v < nvec; v += kCeThreads) {
+    float f[8];
+    unpack8(srow[v], f);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) f[k] = coef * b200::ex2_approx(fmaf(f[k], kLog2e, -m2));
+    const int off = tgt - v * 8;
+    if (off >= 0 && off < 8) {
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        if (k == off) f[k] -= grad_scale;
+    }
+    srow[v] = pack8(f);
+  }
+  b200::fence_proxy_async_smem();      // the generic-proxy writes above are read by the bulk store below
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (uint32_t off = 0; off < bytes; off += kCeChunkBytes)
+      b200::bulk_s2g(reinterpret_cast<unsigned char*>(grow) + off, ce_row_smem + off, min(kCeChunkBytes, bytes - off));
+    b200::tma_commit_group();
+    b200::tma_wait_group_read<0>();    // shared memory stays valid until the store has read it
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
 // Flat-arena AdamW: p, m, v fp32 [n]; g bf16 or fp32 [n]; writes the bf16 shadow of p.
 //   g' = g * gscale[0] (clip factor, device scalar; nullptr = 1)
@@ -723,6 +906,50 @@ __global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float
     pi -= lr * (mhat / (sqrtf(vhat) + eps) + wd * pi);
     p[i] = pi;
     if (shadow) shadow[i] = __float2bfloat16(pi);
+  }
+}
+
+// Four elements per thread with 16-byte accesses (n % 4 == 0, 16-byte aligned arenas).
+template <typename GT>
+__global__ void __launch_bounds__(256)
+adamw_vec4_kernel(float4* __restrict__ p, float4* __restrict__ m, float4* __restrict__ v, const GT* __restrict__ g,
+                  __nv_bfloat16* __restrict__ shadow, const float* __restrict__ gscale, long long nvec, float lr,
+                  float b1, float b2, float eps, float wd, float bc1, float bc2) {
+  const float gs = gscale ? gscale[0] : 1.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    float gi[4];
+    if constexpr (sizeof(GT) == 2) {
+      const uint2 raw = reinterpret_cast<const uint2*>(g)[i];
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+      gi[0] = a.x; gi[1] = a.y; gi[2] = b.x; gi[3] = b.y;
+    } else {
+      const float4 raw = reinterpret_cast<const float4*>(g)[i];
+      gi[0] = raw.x; gi[1] = raw.y; gi[2] = raw.z; gi[3] = raw.w;
+    }
+    const float4 m4 = m[i], v4 = v[i], p4 = p[i];
+    float mi[4] = {m4.x, m4.y, m4.z, m4.w}, vi[4] = {v4.x, v4.y, v4.z, v4.w}, pi[4] = {p4.x, p4.y, p4.z, p4.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float gk = gi[k] * gs;
+      mi[k] = b1 * mi[k] + (1.f - b1) * gk;
+      vi[k] = b2 * vi[k] + (1.f - b2) * gk * gk;
+      const float mhat = mi[k] / bc1;
+      const float vhat = vi[k] / bc2;
+      pi[k] -= lr * (mhat / (sqrtf(vhat) + eps) + wd * pi[k]);
+    }
+    m[i] = make_float4(mi[0], mi[1], mi[2], mi[3]);
+    v[i] = make_float4(vi[0], vi[1], vi[2], vi[3]);
+    p[i] = make_float4(pi[0], pi[1], pi[2], pi[3]);
+    if (shadow) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(pi[0], pi[1]);
+      __nv_bfloat162 hi = __floats2bfloat162_rn(pi[2], pi[3]);
+      uint2 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&lo);
+      pk.y = *reinterpret_cast<uint32_t*>(&hi);
+      reinterpret_cast<uint2*>(shadow)[i] = pk;
+    }
   }
 }
 
@@ -816,6 +1043,19 @@ extern "C" int b200_rmsnorm_fwd(const void* x, const void* delta, const void* w,
 extern "C" int b200_rmsnorm_bwd(const void* x, const void* w, const void* rstd, const void* dy, const void* dres,
                                 void* dx, void* dw, int rows, int H, void* stream) {
   if (H % 8 || H * 4 > 48 * 1024) return -2;
+  if (H >= 2048 && H % 256 == 0 && H <= 8192) {
+    const int threads = H / 8;
+#define RMS_BWD_COLS(R, MAXT, PER_SM)                                                                      \
+  rmsnorm_bwd_cols_kernel<R, MAXT, PER_SM><<<grid_for(((long long)rows + R - 1) / R, 1, PER_SM), threads, 0,        \
+                                     STREAM(stream)>>>(                                                      \
+      (const __nv_bfloat16*)x, (const float*)w, (const float*)rstd, (const __nv_bfloat16*)dy,              \
+      (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, (float*)dw, rows, H)
+    if (threads <= 256) RMS_BWD_COLS(2, 256, 2);
+    else if (threads <= 512) RMS_BWD_COLS(2, 512, 1);
+    else RMS_BWD_COLS(1, 1024, 1);
+#undef RMS_BWD_COLS
+    return LAST_ERR();
+  }
   const int grid = grid_for((long long)rows, kWarpsPerBlock, 2);
 #define RMS_BWD(NV)                                                                                     \
   rmsnorm_bwd_kernel<NV><<<grid, kWarpsPerBlock * 32, H * sizeof(float), STREAM(stream)>>>(              \
@@ -932,9 +1172,18 @@ extern "C" int b200_embedding_bwd(const void* ids, const void* dout, void* dtabl
 }
 extern "C" int b200_ce_fwd_bwd(void* logits, long long ld, const void* targets, const void* mask, void* loss_row,
                                void* z_row, void* lse_row, int rows, int V, float grad_scale, float z_weight,
-                               int write_grad, void* stream) {
+                               int write_grad, void* status, void* stream) {
   if (rows <= 0) return 0;
   if (ld % 8) return -1;  // rows must stay 16-byte aligned for the vector path
+  const size_t row_bytes = (size_t)V * 2;
+  if (V % 8 == 0 && row_bytes <= 200 * 1024 && (reinterpret_cast<uintptr_t>(logits) & 15u) == 0 && status) {
+    static bool configured[b200host::kMaxDevices] = {};
+    if (int rc = b200host::ensure_dynamic_smem(ce_fwd_bwd_staged_kernel, 200 * 1024, configured)) return rc;
+    ce_fwd_bwd_staged_kernel<<<rows, kCeThreads, row_bytes, STREAM(stream)>>>(
+        (__nv_bfloat16*)logits, ld, (const int*)targets, (const uint8_t*)mask, (float*)loss_row, (float*)z_row,
+        (float*)lse_row, V, grad_scale, z_weight, write_grad, (int*)status);
+    return LAST_ERR();
+  }
   ce_fwd_bwd_kernel<<<rows, 512, 0, STREAM(stream)>>>((__nv_bfloat16*)logits, ld, (const int*)targets,
                                                       (const uint8_t*)mask, (float*)loss_row, (float*)z_row,
                                                       (float*)lse_row, V, grad_scale, z_weight, write_grad);
@@ -944,6 +1193,20 @@ extern "C" int b200_adamw(void* p, void* m, void* v, const void* g, int g_is_bf1
                           long long n, float lr, float b1, float b2, float eps, float wd, float bc1, float bc2,
                           void* stream) {
   if (n <= 0) return 0;
+  auto misaligned = [](const void* q, uintptr_t a) { return (reinterpret_cast<uintptr_t>(q) & (a - 1)) != 0; };
+  if (n % 4 == 0 && !misaligned(p, 16) && !misaligned(m, 16) && !misaligned(v, 16) &&
+      !misaligned(g, g_is_bf16 ? 8 : 16) && !misaligned(shadow, 8)) {
+    const int vgrid = grid_for(n / 4, 256, 8);
+    if (g_is_bf16)
+      adamw_vec4_kernel<__nv_bfloat16><<<vgrid, 256, 0, STREAM(stream)>>>(
+          (float4*)p, (float4*)m, (float4*)v, (const __nv_bfloat16*)g, (__nv_bfloat16*)shadow, (const float*)gscale,
+          n / 4, lr, b1, b2, eps, wd, bc1, bc2);
+    else
+      adamw_vec4_kernel<float><<<vgrid, 256, 0, STREAM(stream)>>>((float4*)p, (float4*)m, (float4*)v, (const float*)g,
+                                                                 (__nv_bfloat16*)shadow, (const float*)gscale, n / 4,
+                                                                 lr, b1, b2, eps, wd, bc1, bc2);
+    return LAST_ERR();
+  }
   const int grid = grid_for(n, 256, 8);
   if (g_is_bf16)
     adamw_kernel<__nv_bfloat16><<<grid, 256, 0, STREAM(stream)>>>((float*)p, (float*)m, (float*)v,

@@ -63,6 +63,14 @@ def use_native(t: torch.Tensor) -> bool:
     return t.is_cuda and t.dtype == torch.bfloat16 and not _FORCE_REFERENCE
 
 
+def _ordered_sums_only() -> bool:
+    """True in the deterministic debugging mode: kernels that add partial sums in arrival order (fp32 atomics for
+    the gradients of norm scales and of the embedding table) give way to the PyTorch forms, whose reductions have a
+    fixed order."""
+
+    return native.deterministic()
+
+
 def compute_weight(p: torch.Tensor, like: torch.Tensor) -> torch.Tensor:
     """The tensor a kernel multiplies with: the bf16 shadow on the native path, a cast view otherwise."""
 
@@ -158,7 +166,7 @@ def _rmsnorm_ref(x, w, eps):
 
 
 def rmsnorm(x: torch.Tensor, p: torch.Tensor, eps: float) -> torch.Tensor:
-    if use_native(x):
+    if use_native(x) and not (_ordered_sums_only() and p.requires_grad and torch.is_grad_enabled()):
         return _RmsNormFn.apply(x, None, p, eps)[0]
     return _rmsnorm_ref(x, p, eps)
 
@@ -166,7 +174,7 @@ def rmsnorm(x: torch.Tensor, p: torch.Tensor, eps: float) -> torch.Tensor:
 def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor, p: torch.Tensor, eps: float):
     """``res = x + delta; y = rmsnorm(res)``; returns ``(y, res)`` from one pass over the data."""
 
-    if use_native(x):
+    if use_native(x) and not (_ordered_sums_only() and p.requires_grad and torch.is_grad_enabled()):
         return _RmsNormFn.apply(x, delta, p, eps)
     res = x + delta
     return _rmsnorm_ref(res, p, eps), res
@@ -206,7 +214,8 @@ class _QkNormRopeFn(torch.autograd.Function):
         wq, wk = ctx.params
         hq, hkv, D, theta, rope = ctx.cfg
         dout = dout.contiguous()
-        dqkv = torch.zeros_like(qkv)  # the V columns get no gradient through this op
+        dqkv = torch.empty_like(qkv)
+        dqkv[:, (hq + hkv) * D:].zero_()  # the V columns get no gradient through this op; the kernel writes the rest
         native.qknorm_rope_bwd_qk(qkv, dout, dqkv, wq, wk, positions, rq, None if wq is None else _main_grad(wq),
                                   None if wk is None else _main_grad(wk), hq, hkv, D, theta, rope)
         return dqkv, None, None, None, None, None, None, None, None, None
@@ -219,7 +228,7 @@ def qk_norm_rope(qkv: torch.Tensor, wq, wk, positions: torch.Tensor, hq: int, hk
     qkv: ``[T, (hq + 2 hkv) * D]``; positions: int32 ``[T]``.  Returns ``[T, (hq + hkv) * D]``.
     """
 
-    if use_native(qkv):
+    if use_native(qkv) and not (_ordered_sums_only() and wq is not None and torch.is_grad_enabled()):
         return _QkNormRopeFn.apply(qkv, wq, wk, positions, hq, hkv, D, eps, theta, rope)
     T = qkv.shape[0]
     q = qkv[:, : hq * D].reshape(T, hq, D)
@@ -373,7 +382,8 @@ def attention_block(qkv: torch.Tensor, wq, wk, positions: torch.Tensor, *, B: in
 
     if scale is None:
         scale = D ** -0.5
-    if use_native(qkv) and D in (64, 128):
+    if use_native(qkv) and D in (64, 128) and not (_ordered_sums_only() and wq is not None
+                                                   and torch.is_grad_enabled()):
         if lo is not None and hi is None:
             hi = native.kv_visibility_upper_bound(lo)
         return _AttentionBlockFn.apply(qkv, wq, wk, positions, lo, hi, B, S, hq, hkv, D, eps, theta, rope, causal,
@@ -451,7 +461,8 @@ class _EmbeddingFn(torch.autograd.Function):
 
 
 def embedding(ids: torch.Tensor, p: torch.Tensor, scale: float = 1.0, dtype: torch.dtype = torch.float32) -> torch.Tensor:
-    if p.is_cuda and dtype == torch.bfloat16 and not _FORCE_REFERENCE and p.shape[1] % 8 == 0:
+    if (p.is_cuda and dtype == torch.bfloat16 and not _FORCE_REFERENCE and p.shape[1] % 8 == 0
+            and not (_ordered_sums_only() and p.requires_grad and torch.is_grad_enabled())):
         like = torch.empty(0, dtype=dtype, device=p.device)
         return _EmbeddingFn.apply(ids, p, scale, like)
     out = F.embedding(ids.long(), p).to(dtype)

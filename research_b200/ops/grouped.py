@@ -136,6 +136,11 @@ def _moe_lib():
         lib.b200_moe_gather.argtypes = [vp, vp, vp, vp, pvp, ci, ll, ci, ci, ll, vp]
         lib.b200_moe_combine.argtypes = [pvp, ci, vp, vp, vp, vp, ll, ci, ci, ll, vp]
         lib.b200_moe_combine_dw.argtypes = [pvp, ci, vp, vp, vp, ll, ci, ci, ll, vp]
+        lib.b200_moe_post_sources.argtypes = [vp, ll, ci, ll, ci, ci, _ct.c_uint, pvp, vp]
+        lib.b200_moe_post_sources.restype = ci
+        lib.b200_moe_dispatch_gemm.argtypes = [pvp, ci, vp, vp, vp, vp, ci, ci, ci, ci, ll, ll, vp, ci, ci, ci, vp, vp,
+                                               _ct.c_uint, vp, vp]
+        lib.b200_moe_dispatch_gemm.restype = ci
         for fn in (lib.b200_moe_chunks, lib.b200_moe_rank, lib.b200_moe_layout, lib.b200_moe_dest, lib.b200_moe_gather,
                    lib.b200_moe_combine, lib.b200_moe_combine_dw):
             fn.restype = ci

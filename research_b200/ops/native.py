@@ -27,6 +27,19 @@ _scratch: dict[tuple[int, str], torch.Tensor] = {}
 
 LAUNCHES = 0
 
+# Debugging switch (``RESEARCH_B200_DETERMINISTIC=1``): every sum whose order depends on which CTA or GPU arrives first
+# takes a fixed-order form instead, so that a whole training step is bit-for-bit repeatable (slower).
+_DETERMINISTIC = os.environ.get("RESEARCH_B200_DETERMINISTIC", "0") == "1"
+
+
+def deterministic() -> bool:
+    return _DETERMINISTIC
+
+
+def set_deterministic(enabled: bool) -> None:
+    global _DETERMINISTIC
+    _DETERMINISTIC = bool(enabled)
+
 c_void_p, c_int, c_ll, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
 
 
@@ -84,7 +97,7 @@ def _declare(lib: ctypes.CDLL) -> None:
     sig("b200_embedding_fwd", c_void_p, c_void_p, c_void_p, c_ll, c_int, c_float, c_void_p)
     sig("b200_embedding_bwd", c_void_p, c_void_p, c_void_p, c_ll, c_int, c_float, c_void_p)
     sig("b200_ce_fwd_bwd", c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
-        c_float, c_int, c_void_p)
+        c_float, c_int, c_void_p, c_void_p)
     sig("b200_adamw", c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_ll, c_float, c_float, c_float,
         c_float, c_float, c_float, c_float, c_void_p)
     sig("b200_sumsq", c_void_p, c_int, c_ll, c_void_p, c_void_p, c_int, c_void_p)
@@ -100,6 +113,13 @@ def _declare(lib: ctypes.CDLL) -> None:
     sig("b200_muon_apply_batched", c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_int, c_float, c_float, c_void_p)
     sig("b200_scale_by_inv_norm", c_void_p, c_void_p, c_ll, c_int, c_float, c_void_p)
     sig("b200_affine_identity", c_void_p, c_void_p, c_int, c_int, c_float, c_float, c_void_p)
+    sig("b200_dion2_accumulate", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_int,
+        c_int, c_void_p)
+    sig("b200_dion2_select", c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p)
+    sig("b200_dion2_gather", c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_int, c_float,
+        c_void_p)
+    sig("b200_dion2_apply", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_int,
+        c_float, c_float, c_float, c_void_p)
     sig("b200_gemm_bf16_splitk_acc", c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_int,
         c_int, c_void_p, c_void_p)
     sig("b200_gemm_bf16_splitk", c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_void_p,
@@ -270,7 +290,8 @@ def gemm_wgrad(dy: torch.Tensor, x: torch.Tensor, grad: torch.Tensor) -> None:
     K, M = dy.shape
     N = x.shape[1]
     splits = 1
-    if K % 64 == 0 and dy.stride(1) == 1 and x.stride(1) == 1 and grad.dim() == 2 and grad.stride(1) == 1:
+    if (K % 64 == 0 and dy.stride(1) == 1 and x.stride(1) == 1 and grad.dim() == 2 and grad.stride(1) == 1
+            and not _DETERMINISTIC):         # slices are reduce-added in arrival order
         splits = wave_splits(M, N, K)
     if splits == 1:
         gemm(dy, x, trans_a=True, trans_b=False, out=grad, accumulate=True)
@@ -485,7 +506,8 @@ def ce_fwd_bwd(logits: torch.Tensor, targets: torch.Tensor, mask: torch.Tensor, 
     z = torch.empty(rows, dtype=torch.float32, device=logits.device)
     lse = torch.empty(rows, dtype=torch.float32, device=logits.device)
     rc = lib.b200_ce_fwd_bwd(logits.data_ptr(), logits.stride(0), targets.data_ptr(), mask.data_ptr(), loss.data_ptr(),
-                             z.data_ptr(), lse.data_ptr(), rows, V, grad_scale, z_weight, int(write_grad), _stream())
+                             z.data_ptr(), lse.data_ptr(), rows, V, grad_scale, z_weight, int(write_grad),
+                             status_word(logits.device).data_ptr(), _stream())
     _check(rc, "b200_ce_fwd_bwd")
     return loss, z, lse
 
@@ -644,6 +666,53 @@ def scale_by_inv_norm(x: torch.Tensor, sumsq_vec: torch.Tensor, eps: float) -> N
     batch = x.shape[0]
     _check(lib.b200_scale_by_inv_norm(x.data_ptr(), sumsq_vec.data_ptr(), x.numel() // batch, batch, eps, _stream()),
            "b200_scale_by_inv_norm")
+
+
+def dion2_supported(n: int, rows: int, cols: int, stride: int, axis: int) -> bool:
+    """Size rules of the Dion2 kernels: 16-byte rows, at most 12288 slices on the selected axis."""
+
+    return cols % 4 == 0 and stride % 4 == 0 and 0 < n <= 65535 and (rows if axis == 0 else cols) <= 12288
+
+
+def dion2_select_stack(g: torch.Tensor, m: torch.Tensor, clip: torch.Tensor | None, n: int, rows: int, cols: int,
+                       stride: int, axis: int, k: int, eps: float):
+    """First half of a Dion2 update of ``n`` fp32 matrices ``[rows, cols]`` that start ``stride`` elements apart at
+    ``g`` / ``m`` (tensors whose first element is the first matrix's first element): ``m += clip * g``, the ``k``
+    row (``axis`` 0) or column (``axis`` 1) slices of largest L1 norm, and the normalised bf16 stack of them
+    (``[n, k, cols]`` or ``[n, rows, k]``, slices in order of decreasing norm, ties by index).  Returns
+    ``(stack, idx [n, k] int32, inv [n, dim] int32)`` where ``inv`` maps a slice to its place in the stack or -1."""
+
+    lib = load()
+    dev = m.device
+    dim = rows if axis == 0 else cols
+    splits = 1
+    if axis == 1:
+        strips = n * ((cols + 127) // 128)
+        splits = max(1, min(16, -(-592 // strips), rows // 64 or 1))
+    norms = torch.empty((2, splits, n, dim), dtype=torch.float32, device=dev)
+    idx = torch.empty((n, k), dtype=torch.int32, device=dev)
+    inv = torch.empty((n, dim), dtype=torch.int32, device=dev)
+    sq_sel = torch.empty((n, k), dtype=torch.float32, device=dev)
+    stack = torch.empty((n, k, cols) if axis == 0 else (n, rows, k), dtype=torch.bfloat16, device=dev)
+    st = _stream()
+    _check(lib.b200_dion2_accumulate(g.data_ptr(), m.data_ptr(), _ptr(clip), norms[0].data_ptr(), norms[1].data_ptr(),
+                                     n, rows, cols, stride, axis, splits, st), "b200_dion2_accumulate")
+    _check(lib.b200_dion2_select(norms[0].data_ptr(), norms[1].data_ptr(), splits, n, dim, k, idx.data_ptr(),
+                                 inv.data_ptr(), sq_sel.data_ptr(), st), "b200_dion2_select")
+    _check(lib.b200_dion2_gather(m.data_ptr(), idx.data_ptr(), sq_sel.data_ptr(), stack.data_ptr(), n, rows, cols, k,
+                                 stride, axis, eps, st), "b200_dion2_gather")
+    return stack, idx, inv
+
+
+def dion2_apply(w: torch.Tensor, m: torch.Tensor, o: torch.Tensor, inv: torch.Tensor, shadow: torch.Tensor | None,
+                n: int, rows: int, cols: int, k: int, stride: int, axis: int, decay: float, step: float,
+                ef: float) -> None:
+    """Second half: ``w <- w * decay - step * o`` on the selected slices (``decay`` everywhere), ``m <- ef * m`` on the
+    selected slices, and the bf16 compute copy of all of ``w`` into ``shadow`` (same element offsets as ``w``)."""
+
+    lib = load()
+    _check(lib.b200_dion2_apply(w.data_ptr(), m.data_ptr(), o.data_ptr(), inv.data_ptr(), _ptr(shadow), n, rows, cols,
+                                k, stride, axis, decay, step, ef, _stream()), "b200_dion2_apply")
 
 
 def affine_identity(a: torch.Tensor, alpha: float, beta: float, out: torch.Tensor | None = None) -> torch.Tensor:

@@ -134,7 +134,7 @@ def load_statistics(expert_ids: torch.Tensor, weights: torch.Tensor, num_experts
     """(counts [E], importance [E], total, mean, min, max, max violation, entropy), all fp32 device tensors."""
 
     if not (expert_ids.is_cuda and native.available() and _native_enabled() and num_experts <= MAX_EXPERTS
-            and expert_ids.numel() > 0):
+            and expert_ids.numel() > 0 and not native.deterministic()):   # importance: fp32 atomics
         return load_statistics_reference(expert_ids, weights, num_experts)
     lib = _lib()
     ids = expert_ids.reshape(-1).to(torch.int32).contiguous()

@@ -186,11 +186,18 @@ class ArenaReducer(TorchReducer):
 
     def buffer(self, numel: int, device: torch.device) -> torch.Tensor:
         if numel > self.capacity:
-            raise ContractError(f"Gram bucket of {numel} values exceeds the arena slot of {self.capacity}")
+            # a single Gram larger than a slot (a bucket never holds more than one such matrix): the library
+            # all-reduce takes it, in its own buffer
+            self._oversize = super().buffer(numel, device)
+            return self._oversize
         self.turn ^= 1
         return self.slots[self.turn][0][:numel]
 
     def all_reduce(self, packed: torch.Tensor) -> torch.Tensor:
+        oversize = getattr(self, "_oversize", None)
+        if oversize is not None and packed.data_ptr() == oversize.data_ptr():
+            self._oversize = None
+            return super().all_reduce(packed)
         n = packed.numel()
         pad = (-n) % 4
         tensor, offset = self.slots[self.turn]

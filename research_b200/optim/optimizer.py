@@ -245,6 +245,8 @@ class Optimizer:
                                          stack[at:], sq[at:], self._clip, per, stride, batch, orth.MUON_MOMENTUM,
                                          orth.MUON_NESTEROV)
             at += batch
+        if native.deterministic():        # the kernel adds per-CTA partial sums in arrival order
+            sq = stack.float().pow(2).sum(dim=(1, 2))
         native.scale_by_inv_norm(stack, sq, orth.MUON_NS_EPS)
         out = orth.newton_schulz_stack_(stack)
         step = lr * orth.rms_match_scale((rows, cols))
@@ -391,6 +393,11 @@ class Optimizer:
         grad = e.param.main_grad
         wd = float(self.spec.weight_decay)
         lead = (slice(None),) if master.dim() == 3 else ()
+        # the apply kernel writes the bf16 compute copy of the slices it updates when that copy has the master's layout
+        shadow = None
+        if store.compute_dtype == torch.bfloat16:
+            shadow = (e.param.data if store.resident else store.shadow(e.offset, e.offset + e.numel)).view(master.shape)
+        all_kernels = True
         for meta in e.metas:
             route = self.routes[meta.name]
             sl = lead + ((slice(None),) if meta.rows is None else (slice(*meta.rows),))
@@ -405,6 +412,25 @@ class Optimizer:
             k = max(1, math.ceil(orth.DION2_FRACTION * (rows if axis == 0 else cols)))
             if (k % 8) or (rows % 8) or (cols % 8):
                 return False
+            decay = 1.0 - lr * wd if (wd != 0.0 and route.weight_decay) else 1.0
+            scale = lr * math.sqrt(meta.shape[-2] / meta.shape[-1])
+            stride = m3.stride(0) if n > 1 else rows * cols
+            kernels = (Fn.native_enabled() and m3.is_cuda and m3.dtype == torch.float32 and g3.dtype == torch.float32
+                       and m3.stride(1) == cols and g3.stride(1) == cols and (n == 1 or g3.stride(0) == stride)
+                       and native.dion2_supported(n, rows, cols, stride, axis)
+                       and all(t.data_ptr() % 16 == 0 for t in (m3, g3, w3)))
+            if kernels:
+                clip = self._clip if isinstance(self._clip, torch.Tensor) else None
+                stack, _, inv = native.dion2_select_stack(g3, m3, clip, n, rows, cols, stride, axis, k,
+                                                          orth.DION2_EPSILON)
+                o = orth.newton_schulz_stack_(stack, orth.DION2_POLAR_EXPRESS_COEFFICIENTS)
+                sh3 = None
+                if shadow is not None:
+                    sh3 = shadow[sl] if master.dim() == 3 else shadow[sl].unsqueeze(0)
+                native.dion2_apply(w3, m3, o, inv, sh3, n, rows, cols, k, stride, axis, decay, scale,
+                                   orth.DION2_EF_DECAY)
+                continue
+            all_kernels = False
             m3.addcmul_(g3, self._clip)
             norms = torch.linalg.vector_norm(m3, ord=1, dim=2 if axis == 0 else 1)             # [n, rows | cols]
             idx = torch.topk(norms, k, dim=1).indices                                          # [n, k]
@@ -414,11 +440,12 @@ class Optimizer:
             sq = stack.float().pow(2).sum(dim=(1, 2))
             stack = stack / (sq.sqrt().to(torch.bfloat16)[:, None, None] * 1.02 + orth.DION2_EPSILON)
             o = orth.newton_schulz_stack_(stack.contiguous(), orth.DION2_POLAR_EXPRESS_COEFFICIENTS)
-            if wd != 0.0 and route.weight_decay:
-                w3.mul_(1.0 - lr * wd)
-            scale = lr * math.sqrt(meta.shape[-2] / meta.shape[-1])
+            if decay != 1.0:
+                w3.mul_(decay)
             w3.scatter_add_(1 + axis, gidx, o.float() * (-scale))
             m3.scatter_(1 + axis, gidx, selected * orth.DION2_EF_DECAY)
+        if all_kernels and shadow is not None:
+            return True
         if store.compute_dtype != torch.float32:
             store.write_entry_shadow(e, master)
         return True

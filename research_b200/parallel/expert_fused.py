@@ -16,6 +16,11 @@ Backward mirrors it (push of weighted output gradients, pull of input gradients)
 Every MoE layer has an inbox of its own for the forward rows (they are what the backward pass of the grouped GEMMs
 reads, so nothing is copied out of the arena), a shared inbox takes the gradient rows, and only the padding rows
 behind each expert's block are zeroed before a push.
+
+With a per-layer inbox the forward dispatch and the first expert GEMM are one kernel (``ops/csrc/moe_comm_gemm.cu``):
+the senders only post 8 bytes per row (which token of which rank the row is), the owner's kernel pulls the rows
+from the senders' token buffers with its transfer CTAs and its tensor-core CTAs start on every 128-row tile as soon
+as that tile has landed.  ``RESEARCH_B200_MOE_FUSED=0`` keeps the push + barrier + GEMM sequence.
 The NCCL formulation in :mod:`research_b200.parallel.expert` is the fallback and the test oracle.
 
 Reference: src/jaxtitan/models/components/moe.py:538-696 (ragged all-to-all dispatcher), 606-662 (metadata and
@@ -47,15 +52,16 @@ class ExpertParallelWorkspace:
     when that fits the budget, one shared for gradient rows) and an outbox that peers read (combine, backward of
     dispatch)."""
 
-    def __init__(self, group, rows: int, hidden: int, device: torch.device, layers: int = 0):
+    def __init__(self, group, rows: int, hidden: int, device: torch.device, layers: int = 0, tokens: int = 0):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
-        self.rows, self.hidden = rows, hidden
+        self.rows, self.hidden, self.tokens = rows, hidden, tokens
         per = rows * hidden * 2
         self.forward_slots = layers if 0 < layers and layers * per <= FORWARD_SLOT_BUDGET_BYTES else 0
         n_in = 1 + self.forward_slots
-        self.arena = SymmetricArena(group, (n_in + 1) * (per + 512) + 8192, device=device, tag="ep")
+        fused_bytes = (tokens * hidden * 2 + rows * 8 + 1024) if (tokens and self.forward_slots) else 0
+        self.arena = SymmetricArena(group, (n_in + 1) * (per + 512) + fused_bytes + 8192, device=device, tag="ep")
         self.inboxes, self.inbox_offs = [], []
         for _ in range(n_in):
             t, off = self.arena.carve(rows * hidden, torch.bfloat16)
@@ -64,6 +70,17 @@ class ExpertParallelWorkspace:
         self.inbox, self.inbox_off = self.inboxes[0], self.inbox_offs[0]      # the shared (gradient) inbox
         self.outbox, self.outbox_off = self.arena.carve(rows * hidden, torch.bfloat16)
         self.outbox = self.outbox.view(rows, hidden)
+        # fused dispatch + GEMM: my tokens where peers can read them, the source list that peers write, and the
+        # local per-tile flags (epochs only grow, so the arrays are shared by all layers and never cleared)
+        self.xbox = None
+        if fused_bytes:
+            self.xbox, self.xbox_off = self.arena.carve(tokens * hidden, torch.bfloat16)
+            self.xbox = self.xbox.view(tokens, hidden)
+            self.sources, self.sources_off = self.arena.carve(rows, torch.int64)
+            self.sources.zero_()
+            self.row_flags = torch.zeros(rows // TILE, dtype=torch.int32, device=device)
+            self.tile_parts = torch.zeros(rows // TILE, dtype=torch.int32, device=device)
+            self.dispatch_epoch = 0
 
     def inbox_for(self, layer_slot: int | None) -> tuple[torch.Tensor, int, bool]:
         """``(buffer, arena offset, private)`` of the inbox for a forward push of MoE layer ``layer_slot`` (private:
@@ -83,18 +100,21 @@ class ExpertParallelWorkspace:
         self.arena.barrier(BARRIER_CHANNEL)
 
 
-def workspace_for(ex, rows: int, hidden: int, device: torch.device) -> ExpertParallelWorkspace | None:
+def workspace_for(ex, rows: int, hidden: int, device: torch.device, tokens: int = 0) -> ExpertParallelWorkspace | None:
     """The arena workspace of the ep group, built (collectively) on first use; None when peer memory is refused."""
 
     if ex.extras.get("ep_workspace_failed"):
         return None
     ws = ex.extras.get("ep_workspace")
-    if ws is None or ws.rows < rows or ws.hidden != hidden:
+    if ws is None or ws.rows < rows or ws.hidden != hidden or ws.tokens < tokens:
         from research_b200.parallel.symmetric import build_collectively
 
         layers = int(ex.extras.get("moe_layer_count", 0))
+        if ws is not None:
+            rows, tokens = max(rows, ws.rows), max(tokens, ws.tokens)
+            ws.arena.close()
         ws = build_collectively(ex.ep_group,
-                                lambda: ExpertParallelWorkspace(ex.ep_group, rows, hidden, device, layers),
+                                lambda: ExpertParallelWorkspace(ex.ep_group, rows, hidden, device, layers, tokens),
                                 "expert-parallel workspace")
         ex.extras["ep_workspace"] = ws
         if ws is None:
@@ -148,7 +168,8 @@ class ExpertParallelPlan:
         self.owner = SimpleNamespace(tile_group=tile_group, k_range=k_range.view(el, 2))
         self.local_starts, self.local_counts, self.local_experts = starts_local, mine, el
         self.ex = ex
-        self.ws = workspace_for(ex, self.rows_per_rank, hidden, dev)   # None: peer memory refused, use NCCL
+        # None: peer memory refused, use NCCL
+        self.ws = workspace_for(ex, self.rows_per_rank, hidden, dev, self.T if fused_gemm_requested() else 0)
 
     @property
     def kept_mask(self) -> torch.Tensor:
@@ -249,6 +270,65 @@ class _EpCombineFn(torch.autograd.Function):
         return d_rows, dw, None, None
 
 
+def fused_gemm_requested() -> bool:
+    import os
+
+    return os.environ.get("RESEARCH_B200_MOE_FUSED", "1") != "0" and not native.deterministic()
+
+
+class _EpDispatchLinearFn(torch.autograd.Function):
+    """Forward dispatch and the gate|up product of the routed experts as one kernel: ``x`` [T, H] local tokens ->
+    [rows, N] for my experts' rows.  The pulled rows stay in this layer's inbox for the weight gradient."""
+
+    @staticmethod
+    def forward(ctx, x, p, plan, ws):
+        import os
+
+        lib = _moe_lib()
+        w = Fn.compute_weight(p, x)                                   # [local experts, N, K]
+        inbox, _, private = ws.inbox_for(plan.layer_slot)
+        if not private or ws.xbox is None:
+            raise KernelError("the fused dispatch needs a per-layer inbox and a token buffer in the arena")
+        rows, (T, H) = plan.rows_per_rank, x.shape
+        used = inbox[:rows]
+        ws.xbox[:T].copy_(x)
+        ws.dispatch_epoch += 1
+        epoch = ws.dispatch_epoch & 0x7FFFFFFF
+        st = native._stream()
+        rc = lib.b200_moe_post_sources(plan.dest.data_ptr(), plan.T * plan.k, plan.k, rows, ws.world, ws.rank, epoch,
+                                       ws.ptrs(ws.sources_off), st)
+        native._check(rc, "b200_moe_post_sources")
+        ws.barrier()                                                  # token buffers and source lists are in place
+        out = torch.empty(rows, w.shape[1], dtype=torch.bfloat16, device=x.device)
+        rc = lib.b200_moe_dispatch_gemm(ws.ptrs(ws.xbox_off), ws.tokens, ws.sources.data_ptr(), used.data_ptr(),
+                                        w.data_ptr(), out.data_ptr(), rows, w.shape[1], H, w.shape[0], w.stride(1),
+                                        w.stride(0), plan.owner.tile_group.data_ptr(), ws.world, ws.rank,
+                                        int(os.environ.get("RESEARCH_B200_MOE_XFER_CTAS", "16")),
+                                        ws.row_flags.data_ptr(), ws.tile_parts.data_ptr(), epoch,
+                                        native.status_word(x.device).data_ptr(), st)
+        native._check(rc, "b200_moe_dispatch_gemm")
+        ws.barrier()                                                  # peers have finished reading my tokens
+        ctx.save_for_backward(used)
+        ctx.p, ctx.plan, ctx.ws = p, plan, ws
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        from research_b200.ops.grouped import _grouped_k, _grouped_rows
+
+        (rows_in,) = ctx.saved_tensors
+        p, plan, ws = ctx.p, ctx.plan, ctx.ws
+        w = Fn.compute_weight(p, rows_in)
+        dy = dy.contiguous()
+        # the input gradient of my rows goes straight into the outbox, from where their senders pull it
+        d_rows = _grouped_rows(dy, w, plan.owner, b_mn=True, out_n=w.shape[2], out=ws.outbox[:plan.rows_per_rank])
+        if p.requires_grad:
+            _grouped_k(dy, rows_in, Fn._main_grad(p), plan.owner)
+        dx = _pull_rows(d_rows, None, plan, ws)
+        ws.barrier()  # everybody has read my outbox
+        return dx, None, None, None
+
+
 def fused_available(ex, x: torch.Tensor, capacity) -> bool:
     import os
 
@@ -264,8 +344,14 @@ def dispatch_and_combine_fused(experts, x: torch.Tensor, weights: torch.Tensor, 
     if x.shape[1] % 8:
         raise KernelError("expert-parallel dispatch needs a hidden size that is a multiple of 8")
     ws = plan.ws
-    rows = _EpDispatchFn.apply(x, plan, ws)
     outbox = ws.outbox[:plan.rows_per_rank]
+    if (fused_gemm_requested() and ws.xbox is not None and ws.inbox_for(plan.layer_slot)[2] and x.shape[1] % 64 == 0
+            and x.shape[0] <= ws.tokens and experts.w_gate_up.shape[1] % 64 == 0):
+        # dispatch and the gate|up product in one kernel: the GEMM starts on row tiles as they arrive
+        h = Fn.swiglu(_EpDispatchLinearFn.apply(x.contiguous(), experts.w_gate_up, plan, ws))
+        out = _GroupedLinearFn.apply(h, experts.w_down, plan.owner, outbox, None)
+        return _EpCombineFn.apply(out, weights, plan, ws)
+    rows = _EpDispatchFn.apply(x, plan, ws)
     # the input gradient of the first product and the output of the second are what peers read: write them
     # straight into the outbox
     h = Fn.swiglu(_GroupedLinearFn.apply(rows, experts.w_gate_up, plan.owner, None, outbox))

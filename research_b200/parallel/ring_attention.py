@@ -168,6 +168,8 @@ def ring_available(ex, q: torch.Tensor, s_local: int, hkv: int, D: int, chunks) 
 
     if os.environ.get("RESEARCH_B200_PEER_COLLECTIVES", "1") == "0" or os.environ.get("RESEARCH_B200_RING", "1") == "0":
         return False
+    if native.deterministic():          # dK / dV partial sums are reduce-added into their owner in arrival order
+        return False
     if not (q.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128) and 2 <= ex.cp_size <= MAX_PEERS):
         return False
     if (128 * hkv * D * 2) % 16384:

@@ -24,6 +24,7 @@ from research_b200.config.specs import RunSpec
 from research_b200.contracts import Batch, StepMetrics
 from research_b200.models.build import ModelBuildResult
 from research_b200.ops import functional as Fn
+from research_b200.ops import native
 from research_b200.optim.optimizer import Optimizer
 from research_b200.parallel.mesh import MeshContext
 from research_b200.parallel.sharding import ParamStore
@@ -230,7 +231,7 @@ class TrainStep:
             z_sums.append(z)
             aux_vals.append(aux)
             all_stats.append(stats)
-        if not self.native:
+        if not self.native or native.deterministic():   # deterministic mode sends a few operators through autograd
             self.store.collect_autograd_grads()
         self.store.reduce_gradients()
         opt = self.optimizer.step(diagnostics=diagnostics)
@@ -257,8 +258,6 @@ class TrainStep:
         # the kernels' status word (a bounded wait that gave up) rides along: max over all ranks, checked every step
         status = None
         if self.device.type == "cuda":
-            from research_b200.ops import native
-
             status = native.status_code_tensor(self.device).float()
             if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
                 status = status.clone()

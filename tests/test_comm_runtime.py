@@ -218,6 +218,91 @@ def test_fused_tensor_parallel_gemms_match_collective_formulation(tmp_path):
     assert proc.stdout.count("RANK_OK") == world
 
 
+_EP_SCRIPT = r"""
+import os, sys, torch, torch.distributed as dist
+from types import SimpleNamespace
+sys.path.insert(0, sys.argv[1])
+from research_b200.ops import functional as Fn
+from research_b200.ops import native
+from research_b200.ops.grouped import _GroupedLinearFn
+from research_b200.parallel import expert_fused as ef
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+dist.init_process_group("nccl", device_id=torch.device("cuda", torch.cuda.current_device()))
+E, k, T = 4 * world, 2, 1536
+ex = SimpleNamespace(ep_size=world, ep_rank=rank, ep_group=dist.group.WORLD, ep_dispatcher="all_to_all",
+                     extras={"moe_layer_count": 1})
+for it, (H, N) in enumerate([(256, 256), (2176, 128), (4096, 64)]):     # 512-byte rows, 17 chunks of 256 bytes, 2 of 4 KB
+    torch.manual_seed(100 * it + rank)
+    El = E // world
+    x = (torch.randn(T, H, device="cuda") * 0.5).bfloat16()
+    ids = torch.topk(torch.randn(T, E, device="cuda"), k, dim=-1).indices.to(torch.int32)
+    if it == 1:
+        ids[:, 0] = 0                                # a hot expert: the capacity drops assignments, others stay empty
+        ids[:, 1] = 1 + (ids[:, 1] % 2)
+    capacity = int(1.25 * T * k / E)
+    w_a = torch.nn.Parameter((torch.randn(El, N, H, device="cuda") * 0.05).bfloat16())
+    w_b = torch.nn.Parameter(w_a.detach().clone())
+    w_a.main_grad = torch.zeros(El, N, H, device="cuda"); w_b.main_grad = torch.zeros(El, N, H, device="cuda")
+    plan = ef.ExpertParallelPlan(ids, E, capacity, ex, H, layer_slot=0)
+    ws = plan.ws
+    assert ws is not None and ws.xbox is not None and ws.inbox_for(0)[2]
+    rows = plan.rows_per_rank
+    live = (plan.owner.tile_group >= 0).repeat_interleave(128)                # rows of tiles that hold an expert
+    g = (torch.randn(rows, N, device="cuda") * 0.1).bfloat16()
+    # push + barrier + grouped GEMM
+    xa = x.clone().requires_grad_(True)
+    rows_a = ef._EpDispatchFn.apply(xa, plan, ws)
+    kept_a = rows_a.detach().clone()
+    ya = _GroupedLinearFn.apply(rows_a, w_a, plan.owner, None, ws.outbox[:rows])
+    (ya.float() * g.float())[live].sum().backward()
+    native.check_status()
+    ya = ya.detach().clone()
+    # one kernel: the owner pulls the rows and multiplies tiles as they land
+    ws.inbox_for(0)[0].fill_(7.0)                                             # nothing of the first pass may survive
+    dist.barrier()
+    xb = x.clone().requires_grad_(True)
+    yb = ef._EpDispatchLinearFn.apply(xb, w_b, plan, ws)
+    (yb.float() * g.float())[live].sum().backward()
+    native.check_status()
+    kept_b = ws.inbox_for(0)[0][:rows]
+    assert torch.equal(kept_a[live], kept_b[live]), "dispatched rows differ"
+    assert torch.allclose(ya[live].float(), yb[live].float(), atol=1e-2, rtol=1e-2), (ya[live].float() - yb[live].float()).abs().max().item()
+    ref = torch.zeros(rows, N, device="cuda")
+    tg = plan.owner.tile_group.repeat_interleave(128)
+    for e in range(El):
+        sel = tg == e
+        ref[sel] = kept_a[sel].float() @ w_a[e].float().t()
+    assert torch.allclose(yb[live].float(), ref[live], atol=3e-2, rtol=3e-2), (yb[live].float() - ref[live]).abs().max().item()
+    assert torch.allclose(xa.grad.float(), xb.grad.float(), atol=1e-2, rtol=1e-2)
+    assert (w_a.main_grad - w_b.main_grad).abs().max().item() <= 1e-2 * w_a.main_grad.abs().max().item() + 1e-4
+    ws.arena.check_canaries()
+    dist.barrier()
+torch.cuda.synchronize()
+dist.barrier()
+dist.destroy_process_group()
+print("RANK_OK", rank)
+"""
+
+
+@pytest.mark.gpu
+def test_fused_expert_dispatch_gemm_matches_push_then_grouped_gemm(tmp_path):
+    """Dispatched rows (bit for bit), expert outputs, input gradients and weight gradients of the kernel that pulls
+    rows and multiplies tiles as they land, against the push + barrier + grouped GEMM sequence and an fp32 product."""
+
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    script = tmp_path / "ep_ranks.py"
+    script.write_text(_EP_SCRIPT)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", RESEARCH_B200_PEER_WAIT_MS="3000")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", "29735", str(script), str(ROOT)]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-3000:]
+    assert proc.stdout.count("RANK_OK") == world
+
+
 _TRAIN_SCRIPT = r"""
 import json, os, sys, numpy as np, torch, torch.distributed as dist
 sys.path.insert(0, sys.argv[1])

@@ -144,8 +144,16 @@ def test_embedding_and_ce():
     ref = torch.zeros(V, H, device="cuda").index_add_(0, ids.long(), out.float())
     assert torch.allclose(dtable, ref, atol=1e-3, rtol=1e-3)
 
-    V2 = 50304
-    logits = _bf((T, V2), 12, 2.0)
+
+@pytest.mark.parametrize("V2,ld", [(50304, 50304), (1000, 1000), (32768, 32776), (1004, 1008), (128256, 128256)])
+def test_cross_entropy_rows_staged_in_shared_memory_and_the_three_pass_form(V2, ld):
+    """Rows of at most 200 KB with V % 8 == 0 take the kernel that stages the row in shared memory (one bulk copy in,
+    one out); the others the three-pass kernel.  Both against the fp32 autograd oracle, padded row stride included."""
+
+    from research_b200.ops import native
+
+    T = 24
+    logits = _bf((T, ld), 12, 2.0)[:, :V2]
     tgt = torch.randint(0, V2, (T,), device="cuda", dtype=torch.int32)
     mask = (torch.rand(T, device="cuda") > 0.2).to(torch.uint8)
     zw, gs = 1e-4, 1.0 / float(mask.sum().item())
@@ -158,14 +166,19 @@ def test_embedding_and_ce():
     assert torch.allclose(loss, ce.detach(), atol=2e-3, rtol=1e-3)
     assert torch.allclose(z, (lse.pow(2) * mask).detach(), atol=1e-2, rtol=1e-3)
     assert torch.allclose(logits.float(), lf.grad, atol=2e-4, rtol=5e-2)
+    assert torch.allclose(lse_k, (lse * mask).detach(), atol=2e-3, rtol=1e-3)
+    assert not logits[mask == 0].any()
+    native.check_status()
 
 
-def test_adamw_sumsq_cast():
+@pytest.mark.parametrize("n,gdtype", [(100_003, torch.bfloat16), (100_000, torch.bfloat16), (65_536, torch.float32)])
+def test_adamw_sumsq_cast(n, gdtype):
+    """n % 4 == 0 takes the 16-byte-access kernel, the odd size the scalar one."""
+
     from research_b200.ops import native
 
-    n = 100_003
     p = torch.randn(n, device="cuda")
-    g = torch.randn(n, device="cuda").to(torch.bfloat16)
+    g = torch.randn(n, device="cuda").to(gdtype)
     m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
     shadow = torch.empty(n, dtype=torch.bfloat16, device="cuda")
     pr = p.clone().requires_grad_(True)
