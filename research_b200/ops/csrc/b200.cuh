@@ -304,6 +304,19 @@ __device__ __forceinline__ float ex2_approx(float x) {
   return y;
 }
 
+// 2^x on the FMA and integer pipes (no special-function unit): round-to-nearest split x = n + f with the 1.5 * 2^23
+// trick, a cubic for 2^f on [-0.5, 0.5] (minimax, relative error 7.5e-5: invisible after rounding to bf16) and n added
+// to the exponent field.  x is clamped at -125 (the result is then about 2e-38, never a NaN); x < 127.
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fmaxf(x, -125.f);
+  const float t = x + 12582912.f;
+  const float f = x - (t - 12582912.f);
+  float p = fmaf(f, 0.0551716685f, 0.2426111251f);
+  p = fmaf(p, f, 0.6932609677f);
+  p = fmaf(p, f, 0.9999280572f);
+  return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
+
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);

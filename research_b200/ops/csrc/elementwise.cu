@@ -338,72 +338,98 @@ rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
   }
 }
 
-// RMSNorm backward for wide rows (H = 8 * blockDim.x, H % 256 == 0): a thread owns 8 columns of every row, so a row
-// of x and dy is read once into registers, the dw partial sums are 8 registers, and R rows are in flight per
-// iteration (one block-wide reduction of R dot products through shared memory, double buffered by iteration parity).
-template <int R, int MAXT, int MINB>
-__global__ void __launch_bounds__(MAXT, MINB)
+// RMSNorm backward for wide rows (H = 8 * VEC * THREADS): a block walks rows, a thread owns 8 * VEC columns of every
+// row, so the row of x and dy is read once into registers, the dw partial sums are 8 * VEC registers, and the loads
+// of the block's next row are issued before the current row is reduced (one block-wide reduction of the dot product
+// through shared memory per row, double buffered by parity), which keeps loads in flight all the time.
+template <int VEC, int THREADS, int MINB>
+__global__ void __launch_bounds__(THREADS, MINB)
 rmsnorm_bwd_cols_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ w,
                         const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dy,
                         const __nv_bfloat16* __restrict__ dres, __nv_bfloat16* __restrict__ dx,
                         float* __restrict__ dw, int rows, int H) {
-  __shared__ float red[2][R][32];
-  const int t = threadIdx.x, lane = t & 31, warp = t >> 5, nwarps = blockDim.x >> 5;
-  const int nvec = H >> 3;
+  __shared__ float red[2][32];
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  constexpr int kWarps = THREADS / 32;
+  const long long nvec = H >> 3;
   const float inv_h = 1.f / (float)H;
-  float wv[8], acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  load8f(w + t * 8, wv);
+  float wv[VEC][8], acc[VEC][8];
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) {
+    load8f(w + (t + v * THREADS) * 8, wv[v]);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[v][i] = 0.f;
+  }
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  uint4 xc[VEC], gc[VEC], rc[VEC];
+  float rs = 0.f;
+  long long row = blockIdx.x;
+  if (row < rows) {
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      xc[v] = reinterpret_cast<const uint4*>(x)[row * nvec + t + v * THREADS];
+      gc[v] = reinterpret_cast<const uint4*>(dy)[row * nvec + t + v * THREADS];
+      rc[v] = dres ? reinterpret_cast<const uint4*>(dres)[row * nvec + t + v * THREADS] : zero;
+    }
+    rs = rstd_in[row];
+  }
   int parity = 0;
-  for (long long r0 = (long long)blockIdx.x * R; r0 < rows; r0 += (long long)gridDim.x * R, parity ^= 1) {
-    uint4 xr[R], gr[R], rr[R];
-    float rs[R], dot[R];
-    const uint4 zero = make_uint4(0, 0, 0, 0);
+  for (; row < rows; row += gridDim.x, parity ^= 1) {
+    uint4 xn[VEC], gn[VEC], rn[VEC];
+    float rsn = 0.f;
+    const long long next = row + gridDim.x;
+    if (next < rows) {  // in flight while this row is reduced and written
 #pragma unroll
-    for (int j = 0; j < R; ++j) {
-      const long long row = r0 + j;
-      const bool valid = row < rows;
-      xr[j] = valid ? reinterpret_cast<const uint4*>(x)[row * nvec + t] : zero;
-      gr[j] = valid ? reinterpret_cast<const uint4*>(dy)[row * nvec + t] : zero;
-      rr[j] = (valid && dres) ? reinterpret_cast<const uint4*>(dres)[row * nvec + t] : zero;
-      rs[j] = valid ? rstd_in[row] : 0.f;
+      for (int v = 0; v < VEC; ++v) {
+        xn[v] = reinterpret_cast<const uint4*>(x)[next * nvec + t + v * THREADS];
+        gn[v] = reinterpret_cast<const uint4*>(dy)[next * nvec + t + v * THREADS];
+        rn[v] = dres ? reinterpret_cast<const uint4*>(dres)[next * nvec + t + v * THREADS] : zero;
+      }
+      rsn = rstd_in[next];
+    } else {
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) xn[v] = gn[v] = rn[v] = zero;
     }
+    float d = 0.f;
 #pragma unroll
-    for (int j = 0; j < R; ++j) {
+    for (int v = 0; v < VEC; ++v) {
       float f[8], g[8];
-      unpack8(xr[j], f);
-      unpack8(gr[j], g);
-      float d = 0.f;
+      unpack8(xc[v], f);
+      unpack8(gc[v], g);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) d += g[i] * wv[i] * f[i];
-      d = warp_sum(d * rs[j]);
-      if (lane == 0) red[parity][j][warp] = d;
+      for (int i = 0; i < 8; ++i) d += g[i] * wv[v][i] * f[i];
     }
+    d = warp_sum(d * rs);
+    if (lane == 0) red[parity][warp] = d;
     __syncthreads();
+    const float dot = warp_sum(lane < kWarps ? red[parity][lane] : 0.f) * inv_h;
 #pragma unroll
-    for (int j = 0; j < R; ++j) {
-      float d = lane < nwarps ? red[parity][j][lane] : 0.f;
-      dot[j] = warp_sum(d) * inv_h;
-    }
-#pragma unroll
-    for (int j = 0; j < R; ++j) {
-      const long long row = r0 + j;
-      if (row >= rows) break;
+    for (int v = 0; v < VEC; ++v) {
       float f[8], g[8], r[8], o[8];
-      unpack8(xr[j], f);
-      unpack8(gr[j], g);
-      unpack8(rr[j], r);
+      unpack8(xc[v], f);
+      unpack8(gc[v], g);
+      unpack8(rc[v], r);
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const float xhat = f[i] * rs[j];
-        o[i] = rs[j] * (g[i] * wv[i] - xhat * dot[j]) + r[i];
-        acc[i] += g[i] * xhat;
+        const float xhat = f[i] * rs;
+        o[i] = rs * (g[i] * wv[v][i] - xhat * dot) + r[i];
+        acc[v][i] += g[i] * xhat;
       }
-      reinterpret_cast<uint4*>(dx)[row * nvec + t] = pack8(o);
+      reinterpret_cast<uint4*>(dx)[row * nvec + t + v * THREADS] = pack8(o);
     }
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      xc[v] = xn[v];
+      gc[v] = gn[v];
+      rc[v] = rn[v];
+    }
+    rs = rsn;
   }
 #pragma unroll
-  for (int i = 0; i < 8; ++i)
-    if (acc[i] != 0.f) atomicAdd(&dw[t * 8 + i], acc[i]);
+  for (int v = 0; v < VEC; ++v)
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (acc[v][i] != 0.f) atomicAdd(&dw[(t + v * THREADS) * 8 + i], acc[v][i]);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1043,16 +1069,13 @@ extern "C" int b200_rmsnorm_fwd(const void* x, const void* delta, const void* w,
 extern "C" int b200_rmsnorm_bwd(const void* x, const void* w, const void* rstd, const void* dy, const void* dres,
                                 void* dx, void* dw, int rows, int H, void* stream) {
   if (H % 8 || H * 4 > 48 * 1024) return -2;
-  if (H >= 2048 && H % 256 == 0 && H <= 8192) {
-    const int threads = H / 8;
-#define RMS_BWD_COLS(R, MAXT, PER_SM)                                                                      \
-  rmsnorm_bwd_cols_kernel<R, MAXT, PER_SM><<<grid_for(((long long)rows + R - 1) / R, 1, PER_SM), threads, 0,        \
-                                     STREAM(stream)>>>(                                                      \
-      (const __nv_bfloat16*)x, (const float*)w, (const float*)rstd, (const __nv_bfloat16*)dy,              \
+  if (H == 4096 || H == 8192) {   // narrower rows: the warp-per-row kernel below measured faster
+#define RMS_BWD_COLS(VEC, THREADS, MINB)                                                                        \
+  rmsnorm_bwd_cols_kernel<VEC, THREADS, MINB><<<grid_for((long long)rows, 1, MINB), THREADS, 0, STREAM(stream)>>>( \
+      (const __nv_bfloat16*)x, (const float*)w, (const float*)rstd, (const __nv_bfloat16*)dy,                   \
       (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, (float*)dw, rows, H)
-    if (threads <= 256) RMS_BWD_COLS(2, 256, 2);
-    else if (threads <= 512) RMS_BWD_COLS(2, 512, 1);
-    else RMS_BWD_COLS(1, 1024, 1);
+    if (H == 4096) RMS_BWD_COLS(2, 256, 2);
+    else RMS_BWD_COLS(2, 512, 1);
 #undef RMS_BWD_COLS
     return LAST_ERR();
   }

@@ -42,8 +42,11 @@ constexpr int XFER_LAG = XFER_BUFS - 2;
 constexpr int XFER_CHUNK = 4096;
 constexpr int XFER_RING_BYTES = XFER_PIPES * XFER_BUFS * XFER_CHUNK;
 constexpr int XFER_ZERO_OFF = XFER_RING_BYTES;              // one chunk of zeros behind the rings
-constexpr int XFER_BYTES = XFER_RING_BYTES + XFER_CHUNK;
 constexpr int ROWS_PER_PIPE = BM / XFER_PIPES;
+constexpr int XFER_ENT_OFF = XFER_ZERO_OFF + XFER_CHUNK;    // the source entries of each pipe's rows of the tile
+constexpr int XFER_BYTES = XFER_ENT_OFF + 2 * XFER_PIPES * ROWS_PER_PIPE * 8;   // two tiles' entries per pipe
+constexpr int XFER_PUBLISH_DELAY = 2;                       // stores issued after a tile's last one before it is published
+static_assert(ROWS_PER_PIPE == 32, "one source entry per lane of the transfer warp");
 
 template <int BN>
 struct SmemLayout {
@@ -138,18 +141,25 @@ moe_dispatch_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 
   if (is_xfer) {
     // ------------------------------------------------------------------ transfer CTA
-    if (lane == 0 && warp < XFER_PIPES) {
+    if (warp < XFER_PIPES) {
+      // One pipe per warp.  The whole warp fetches the 32 source entries of its rows of a tile with one coalesced
+      // load into shared memory (a dependent global load per row on the issuing thread would cost more than the
+      // copy itself); lane 0 runs the ring of bulk copies.  The ring streams across tiles: the stores of a tile's
+      // last rows are issued while the next tile's loads are already in flight, and the tile is published a few
+      // stores later, once `cp.async.bulk.wait_group` says its stores have completed.
       uint8_t* ring = smem + warp * XFER_BUFS * XFER_CHUNK;
       const uint8_t* zeros = smem + XFER_ZERO_OFF;
+      unsigned long long* ent_base =
+          reinterpret_cast<unsigned long long*>(smem + XFER_ENT_OFF) + warp * 2 * ROWS_PER_PIPE;
       uint64_t* bar = xbar + warp * XFER_BUFS;
       const int chunks_per_row = p.K * 2 / p.chunk_bytes;
-      const int items = ROWS_PER_PIPE * chunks_per_row;    // per tile and pipe
+      const int items = ROWS_PER_PIPE * chunks_per_row;    // per tile and pipe (at least 32 > XFER_LAG)
       const long long row_bytes = (long long)p.K * 2;
       uint32_t phase = 0;                                   // bit b: parity of the next completion of ring buffer b
       bool ok = true;
-      // where does row `r` of the inbox come from?  nullptr: a padding row
-      auto source_of = [&](int r) -> const uint8_t* {
-        const unsigned long long e = p.sources[r];
+      // where does row `i` of a tile's 32 rows of this pipe come from?  nullptr: a padding row
+      auto source_of = [&](const unsigned long long* ent, int i) -> const uint8_t* {
+        const unsigned long long e = ent[i];
         if ((uint32_t)(e >> 32) != p.epoch) return nullptr;
         const int src = (int)((e >> 24) & 0xffu), tok = (int)(e & 0xffffffu);
         if (src >= p.world || tok >= p.tokens) {            // not a row that exists: record it, store zeros
@@ -158,40 +168,22 @@ moe_dispatch_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         }
         return reinterpret_cast<const uint8_t*>(p.x[src]) + (long long)tok * row_bytes;
       };
-      for (int t = (int)blockIdx.x; t < tiles_m && ok; t += p.n_xfer) {
-        if (p.tile_group[t] < 0) continue;
-        const int row0 = t * BM + warp * ROWS_PER_PIPE;
-        for (int i = 0; i < items + XFER_LAG && ok; ++i) {
-          if (i < items) {
-            const int r = row0 + i / chunks_per_row, c = i % chunks_per_row;
-            const int buf = i % XFER_BUFS;
-            // the store that last read this ring buffer has finished reading it
-            if (i >= XFER_BUFS) tma_wait_group_read<XFER_BUFS - XFER_LAG - 1>();
-            const uint8_t* src = source_of(r);
-            if (src) {
-              mbar_expect_tx(&bar[buf], (uint32_t)p.chunk_bytes);
-              bulk_g2s(ring + buf * XFER_CHUNK, src + (long long)c * p.chunk_bytes, (uint32_t)p.chunk_bytes,
-                       &bar[buf]);
-            }
-          }
-          const int j = i - XFER_LAG;
-          if (j >= 0) {
-            const int r = row0 + j / chunks_per_row, c = j % chunks_per_row;
-            const int buf = j % XFER_BUFS;
-            uint8_t* dst = reinterpret_cast<uint8_t*>(p.inbox) + (long long)r * row_bytes + (long long)c * p.chunk_bytes;
-            if (source_of(r)) {
-              if (!mbar_wait(&bar[buf], (phase >> buf) & 1u, ab, ERR_WAIT_FULL)) { ok = false; break; }
-              phase ^= 1u << buf;
-              bulk_s2g(dst, ring + buf * XFER_CHUNK, (uint32_t)p.chunk_bytes);
-            } else {
-              bulk_s2g(dst, zeros, (uint32_t)p.chunk_bytes);
-            }
-            tma_commit_group();
-          }
+      // lane 0 only: store item j of tile `t` (entries `ent`) from its ring buffer (or from the zeros)
+      auto store_item = [&](int t, const unsigned long long* ent, int j, long long g) -> bool {
+        const int r = t * BM + warp * ROWS_PER_PIPE + j / chunks_per_row, c = j % chunks_per_row;
+        const int buf = (int)(g % XFER_BUFS);
+        uint8_t* dst = reinterpret_cast<uint8_t*>(p.inbox) + (long long)r * row_bytes + (long long)c * p.chunk_bytes;
+        if (source_of(ent, j / chunks_per_row)) {
+          if (!mbar_wait(&bar[buf], (phase >> buf) & 1u, ab, ERR_WAIT_FULL)) return false;
+          phase ^= 1u << buf;
+          bulk_s2g(dst, ring + buf * XFER_CHUNK, (uint32_t)p.chunk_bytes);
+        } else {
+          bulk_s2g(dst, zeros, (uint32_t)p.chunk_bytes);
         }
-        // this pipe's quarter of the tile is in memory; the pipe that completes the tile publishes it
-        tma_wait_group<0>();
-        if (!ok) break;
+        tma_commit_group();
+        return true;
+      };
+      auto publish = [&](int t) {
         fence_proxy_async_all();
         __threadfence();
         if (atomicAdd(&p.tile_parts[t], 1u) == (uint32_t)XFER_PIPES - 1u) {
@@ -199,12 +191,59 @@ moe_dispatch_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           __threadfence();
           st_release_gpu(&p.row_flags[t], p.epoch);
         }
+      };
+      long long g = 0;          // items issued so far by this pipe (ring position), all tiles
+      int prev = -1;            // the tile whose last XFER_LAG stores are still to be issued, then to be published
+      int k = 0;                // tiles handled by this pipe
+      for (int t = (int)blockIdx.x; t < tiles_m && ok; t += p.n_xfer) {
+        if (p.tile_group[t] < 0) continue;
+        unsigned long long* ent = ent_base + (k & 1) * ROWS_PER_PIPE;
+        const unsigned long long* ent_prev = ent_base + ((k & 1) ^ 1) * ROWS_PER_PIPE;
+        __syncwarp();           // lane 0 is past the tile before the previous one, whose entries are overwritten now
+        ent[lane] = p.sources[t * BM + warp * ROWS_PER_PIPE + lane];
+        __syncwarp();
+        if (lane == 0) {
+          for (int i = 0; i < items && ok; ++i, ++g) {
+            const int buf = (int)(g % XFER_BUFS);
+            // the store that last read this ring buffer has finished reading it
+            if (g >= XFER_BUFS) tma_wait_group_read<XFER_BUFS - XFER_LAG - 1>();
+            const uint8_t* src = source_of(ent, i / chunks_per_row);
+            if (src) {
+              mbar_expect_tx(&bar[buf], (uint32_t)p.chunk_bytes);
+              bulk_g2s(ring + buf * XFER_CHUNK, src + (long long)(i % chunks_per_row) * p.chunk_bytes,
+                       (uint32_t)p.chunk_bytes, &bar[buf]);
+            }
+            // the store that lags XFER_LAG items behind: of this tile, or still of the previous one
+            if (i >= XFER_LAG) {
+              ok = store_item(t, ent, i - XFER_LAG, g - XFER_LAG);
+            } else if (prev >= 0) {
+              ok = store_item(prev, ent_prev, items - XFER_LAG + i, g - XFER_LAG);
+            }
+            if (ok && prev >= 0 && i == XFER_LAG - 1 + XFER_PUBLISH_DELAY) {
+              tma_wait_group<XFER_PUBLISH_DELAY>();       // everything but the latest stores, so all of `prev`
+              publish(prev);
+              prev = -1;
+            }
+          }
+          if (ok) prev = t;
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        ++k;
       }
-      tma_wait_group<0>();
-      if (!ok) {
-        // give the loads still in flight time to land before shared memory is released
-        const uint64_t t0 = globaltimer_ns();
-        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+      if (lane == 0) {
+        if (ok && prev >= 0) {
+          // the last tile: its remaining stores, then everything is complete
+          const unsigned long long* ent_last = ent_base + ((k - 1) & 1) * ROWS_PER_PIPE;
+          for (int i = 0; i < XFER_LAG && ok; ++i, ++g) ok = store_item(prev, ent_last, items - XFER_LAG + i, g - XFER_LAG);
+          tma_wait_group<0>();
+          if (ok) publish(prev);
+        }
+        tma_wait_group<0>();
+        if (!ok) {
+          // give the loads still in flight time to land before shared memory is released
+          const uint64_t t0 = globaltimer_ns();
+          while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+        }
       }
     }
   } else if (warp == 0) {

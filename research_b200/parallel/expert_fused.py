@@ -308,7 +308,9 @@ class _EpDispatchLinearFn(torch.autograd.Function):
                                         native.status_word(x.device).data_ptr(), st)
         native._check(rc, "b200_moe_dispatch_gemm")
         ws.barrier()                                                  # peers have finished reading my tokens
-        ctx.save_for_backward(used)
+        # kept as a plain attribute: every buffer of the arena is a view of one byte tensor, so a later copy into the
+        # token buffer would trip the version check of a saved tensor although this layer's inbox is untouched
+        ctx.rows_in = used
         ctx.p, ctx.plan, ctx.ws = p, plan, ws
         return out
 
@@ -316,8 +318,7 @@ class _EpDispatchLinearFn(torch.autograd.Function):
     def backward(ctx, dy):
         from research_b200.ops.grouped import _grouped_k, _grouped_rows
 
-        (rows_in,) = ctx.saved_tensors
-        p, plan, ws = ctx.p, ctx.plan, ctx.ws
+        rows_in, p, plan, ws = ctx.rows_in, ctx.p, ctx.plan, ctx.ws
         w = Fn.compute_weight(p, rows_in)
         dy = dy.contiguous()
         # the input gradient of my rows goes straight into the outbox, from where their senders pull it

@@ -426,7 +426,10 @@ def test_training_with_peer_memory_kernels_matches_nccl_path(tmp_path, name, axe
         # a tiny gradient into a full-size step for that one element, so single elements may differ by a step or
         # two; a wrong gradient moves whole tensors, which the mean difference catches.
         diff = np.abs(got.astype(np.float64) - want.astype(np.float64))
-        assert diff.mean() <= 2e-4, (name, key, "mean", float(diff.mean()))
+        # routed models: a token whose k-th and (k+1)-th router scores are a rounding apart may go to another expert
+        # on one of the two paths from the second step on, which moves more elements by a step than rounding alone
+        mean_limit = 6e-4 if name.startswith("moe") else 2e-4
+        assert diff.mean() <= mean_limit, (name, key, "mean", float(diff.mean()))
         assert diff.max() <= 8e-3, (name, key, "max", float(diff.max()))
 
 
