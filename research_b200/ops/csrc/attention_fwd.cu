@@ -287,18 +287,17 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       bool done = false;
       if (j > 0) {
         if (!mbar_wait_warp(&pv_done[t], (j - 1) & 1, ab, ERR_WAIT_O_READY)) { ok = false; break; }   // P(j-1) consumed
-        uint32_t ra[32], rb[32];
+        // all 128 scores of the row at once: the latency of the tensor-memory loads is paid once per block
+        uint32_t ra[32], rb[32], rc[32], rd[32];
         tmem_ld_32x32b_x32(tS, ra);
         tmem_ld_32x32b_x32(tS + 32, rb);
+        tmem_ld_32x32b_x32(tS + 64, rc);
+        tmem_ld_32x32b_x32(tS + 96, rd);
         tmem_ld_wait();
         float top = emit_chunk(ra, 0);
-        tmem_ld_32x32b_x32(tS + 64, ra);
         top = fmaxf(top, emit_chunk(rb, 1));
-        tmem_ld_wait();
-        tmem_ld_32x32b_x32(tS + 96, rb);
-        top = fmaxf(top, emit_chunk(ra, 2));
-        tmem_ld_wait();
-        top = fmaxf(top, emit_chunk(rb, 3));
+        top = fmaxf(top, emit_chunk(rc, 2));
+        top = fmaxf(top, emit_chunk(rd, 3));
         done = !__any_sync(0xffffffffu, top > kRescaleThreshold);
         if (!done) sum = 0.f;   // a row maximum moved too far: redo the block with a new reference
       }

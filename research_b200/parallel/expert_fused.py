@@ -303,7 +303,7 @@ class _EpDispatchLinearFn(torch.autograd.Function):
         rc = lib.b200_moe_dispatch_gemm(ws.ptrs(ws.xbox_off), ws.tokens, ws.sources.data_ptr(), used.data_ptr(),
                                         w.data_ptr(), out.data_ptr(), rows, w.shape[1], H, w.shape[0], w.stride(1),
                                         w.stride(0), plan.owner.tile_group.data_ptr(), ws.world, ws.rank,
-                                        int(os.environ.get("RESEARCH_B200_MOE_XFER_CTAS", "16")),
+                                        int(os.environ.get("RESEARCH_B200_MOE_XFER_CTAS", "32")),
                                         ws.row_flags.data_ptr(), ws.tile_parts.data_ptr(), epoch,
                                         native.status_word(x.device).data_ptr(), st)
         native._check(rc, "b200_moe_dispatch_gemm")
