@@ -241,32 +241,34 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmX1, const __grid_constant_
       constexpr uint32_t idesc_a = make_idesc_bf16(TILE, D, false, true);      // K-major A * Y (MN-major)
       auto ybuf = [&](int item) -> const uint8_t* { return smem + L::RING_OFF + (item % RING) * L::TILE_BYTES; };
       auto ring_wait = [&](int item) { return mbar_wait(&full[item % RING], (item / RING) & 1, ab, ERR_WAIT_FULL); };
+      // One descriptor per operand, built when the product is issued; the slice of an MMA instruction is that
+      // descriptor plus a compile-time constant in its address field (units of 16 bytes), so nothing but an add
+      // sits between two of the 64-clock instructions that this one thread issues.
       auto issue_t = [&](uint32_t d_tmem, const uint8_t* x, const uint8_t* y) {
-        const uint32_t a_base = smem_u32(x), b_base = smem_u32(y);
+        const uint64_t a0 = make_smem_desc_sw128(smem_u32(x), 16, 1024), b0 = make_smem_desc_sw128(smem_u32(y), 16, 1024);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          tc_mma_ss(d_tmem, make_smem_desc_sw128(a_base + off, 16, 1024), make_smem_desc_sw128(b_base + off, 16, 1024),
-                    idesc_t, kk != 0 ? 1u : 0u);
+          const uint64_t off = (uint64_t)(((kk >> 2) * 16384 + (kk & 3) * 32) >> 4);
+          tc_mma_ss(d_tmem, a0 + off, b0 + off, idesc_t, kk != 0 ? 1u : 0u);
         }
       };
       // A = P^T in shared memory
       auto issue_acc_ss = [&](uint32_t d_tmem, const uint8_t* y, bool accumulate) {
-        const uint32_t a_base = smem_u32(sBuf), b_base = smem_u32(y);
+        const uint64_t a0 = make_smem_desc_sw128(smem_u32(sBuf), 16, 1024);
+        const uint64_t b0 = make_smem_desc_sw128(smem_u32(y), 16384, 1024);
 #pragma unroll
         for (int kk = 0; kk < TILE / 16; ++kk) {
-          const uint32_t a_off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          tc_mma_ss(d_tmem, make_smem_desc_sw128(a_base + a_off, 16, 1024),
-                    make_smem_desc_sw128(b_base + kk * 2048, 16384, 1024), idesc_a, (accumulate || kk != 0) ? 1u : 0u);
+          const uint64_t a_off = (uint64_t)(((kk >> 2) * 16384 + (kk & 3) * 32) >> 4);
+          tc_mma_ss(d_tmem, a0 + a_off, b0 + (uint64_t)((kk * 2048) >> 4), idesc_a, (accumulate || kk != 0) ? 1u : 0u);
         }
       };
       // A = packed dS in tensor memory: 16 K-elements are 8 columns; the two 64-element halves sit 64 columns apart
       auto issue_acc_ts = [&](uint32_t d_tmem, const uint8_t* y, bool accumulate) {
-        const uint32_t b_base = smem_u32(y);
+        const uint64_t b0 = make_smem_desc_sw128(smem_u32(y), 16384, 1024);
 #pragma unroll
         for (int kk = 0; kk < TILE / 16; ++kk) {
-          tc_mma_ts(d_tmem, tm_DS + (kk >> 2) * 64 + (kk & 3) * 8, make_smem_desc_sw128(b_base + kk * 2048, 16384, 1024),
-                    idesc_a, (accumulate || kk != 0) ? 1u : 0u);
+          tc_mma_ts(d_tmem, tm_DS + (kk >> 2) * 64 + (kk & 3) * 8, b0 + (uint64_t)((kk * 2048) >> 4), idesc_a,
+                    (accumulate || kk != 0) ? 1u : 0u);
         }
       };
       bool ok = mbar_wait(x_full, 0, ab, ERR_WAIT_FULL);

@@ -174,26 +174,39 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       constexpr uint32_t idesc_pv = make_idesc_bf16(TILE_M, D, false, true);
       bool ok = mbar_wait(q_full, 0, ab, ERR_WAIT_FULL);
       uint32_t item = 0;
+      // Shared-memory descriptors are built once per operand; the slice of one MMA instruction is that descriptor
+      // plus a compile-time constant in its address field (units of 16 bytes).  A tile product is D / 16 (or
+      // BLOCK_N / 16) instructions of 64 clocks each and one thread issues them all, so next to nothing may sit
+      // between two of them.
+      uint64_t dq[NT], dp[NT], dk[KV_SLOTS], dv[KV_SLOTS];
+#pragma unroll
+      for (int t = 0; t < NT; ++t) {
+        dq[t] = make_smem_desc_sw128(smem_u32(smem + L::Q_OFF + t * L::TILE_D_BYTES), 16, 1024);
+        dp[t] = make_smem_desc_sw128(smem_u32(smem + L::P_OFF + t * L::P_BYTES), 16, 1024);
+      }
+#pragma unroll
+      for (int sl = 0; sl < KV_SLOTS; ++sl) {
+        const uint32_t kv_base = smem_u32(smem + L::KV_OFF + sl * L::TILE_D_BYTES);
+        dk[sl] = make_smem_desc_sw128(kv_base, 16, 1024);
+        dv[sl] = make_smem_desc_sw128(kv_base, 16384, 1024);
+      }
+      static_assert(KV_SLOTS == 3 && NT == 2, "slot and tile selects below are written out");
       auto issue_qk = [&](int t, int slot) {
-        const uint32_t a_base = smem_u32(smem + L::Q_OFF + t * L::TILE_D_BYTES);
-        const uint32_t b_base = smem_u32(smem + L::KV_OFF + slot * L::TILE_D_BYTES);
+        const uint64_t a0 = t == 0 ? dq[0] : dq[1], b0 = slot == 0 ? dk[0] : (slot == 1 ? dk[1] : dk[2]);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          tc_mma_ss(tmem_S + t * 128, make_smem_desc_sw128(a_base + off, 16, 1024),
-                    make_smem_desc_sw128(b_base + off, 16, 1024), idesc_qk, kk != 0 ? 1u : 0u);
+          const uint64_t off = (uint64_t)(((kk >> 2) * 16384 + (kk & 3) * 32) >> 4);
+          tc_mma_ss(tmem_S + t * 128, a0 + off, b0 + off, idesc_qk, kk != 0 ? 1u : 0u);
         }
         tc_commit(&s_full[t]);
       };
       auto issue_pv = [&](int t, int slot, bool accumulate) {
-        const uint32_t a_base = smem_u32(smem + L::P_OFF + t * L::P_BYTES);
-        const uint32_t b_base = smem_u32(smem + L::KV_OFF + slot * L::TILE_D_BYTES);
+        const uint64_t a0 = t == 0 ? dp[0] : dp[1], b0 = slot == 0 ? dv[0] : (slot == 1 ? dv[1] : dv[2]);
 #pragma unroll
         for (int kk = 0; kk < BLOCK_N / 16; ++kk) {
-          const uint32_t a_off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          tc_mma_ss(tmem_O + t * D, make_smem_desc_sw128(a_base + a_off, 16, 1024),
-                    make_smem_desc_sw128(b_base + kk * 2048, 16384, 1024), idesc_pv,
-                    (accumulate || kk != 0) ? 1u : 0u);
+          const uint64_t a_off = (uint64_t)(((kk >> 2) * 16384 + (kk & 3) * 32) >> 4);
+          const uint64_t b_off = (uint64_t)((kk * 2048) >> 4);
+          tc_mma_ss(tmem_O + t * D, a0 + a_off, b0 + b_off, idesc_pv, (accumulate || kk != 0) ? 1u : 0u);
         }
         tc_commit(&pv_done[t]);
       };
