@@ -54,10 +54,16 @@ class PagedKVCache:
         if T == 1 and native_ok:
             from research_b200.ops.decode import decode_attention_paged, kv_append_paged
 
-            pos = positions[:, 0]
+            # the positions of a step are the same for every layer: the contiguous copy and the lengths are made by
+            # the first layer and reused by the others (two launches per step instead of two per layer)
+            step = getattr(self, "_step_positions", None)
+            if layer == 0 or step is None or step[0] is not positions:
+                pos = positions[:, 0].to(torch.int32).contiguous()
+                step = self._step_positions = (positions, pos, pos + 1)
+            _, pos, lengths = step
             kv_append_paged(k[:, 0], v[:, 0], kp, vp, pos)
             lo = None if window is None else (pos - (window - 1)).clamp_min(0).to(torch.int32)
-            return decode_attention_paged(q[:, 0], kp, vp, (pos + 1).to(torch.int32), lo)[:, None]
+            return decode_attention_paged(q[:, 0], kp, vp, lengths, lo)[:, None]
         idx = positions.long()
         from_zero = T > 1 and bool((positions == torch.arange(T, device=q.device, dtype=positions.dtype)).all())
         if from_zero:

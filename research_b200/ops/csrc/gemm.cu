@@ -55,6 +55,14 @@ struct GemmParams {
   const int* k_range;
   // Split-K: the batch index selects a K slice of A and B, and every slice adds into the same C (z = 0).
   int c_shared;
+  // Split-K with the finishing pass inside the kernel (fp32 C is a workspace that is zero between launches): the CTA
+  // that adds the last slice of an output tile converts the tile's sums to bf16 into fin_out and clears the
+  // workspace behind it.  fin_count: one zeroed counter per output tile, left zero.
+  const float* fin_ws_ptr;
+  __nv_bfloat16* fin_out;
+  long long fin_ld_ws, fin_ld_out;
+  unsigned int* fin_count;
+  int fin_splits;
 };
 
 template <int BN, bool A_MN, bool B_MN, bool OUT_F32>
@@ -71,6 +79,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile unsigned int* fin_prev = reinterpret_cast<volatile unsigned int*>(tmem_slot + 2);
   const AbortCtx ab{abort_flag, p.status};
 
   const int warp = threadIdx.x >> 5;
@@ -275,6 +284,38 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
+      if (OUT_F32 && p.fin_out) {
+        // split-K with the finishing pass fused: when this CTA's adds of the tile are in memory, count the slice;
+        // the CTA that counts the last one converts the tile and clears the workspace
+        float* ws = reinterpret_cast<float*>(const_cast<void*>(static_cast<const void*>(p.fin_ws_ptr)));
+        if (lane == 0) {
+          tma_wait_group<0>();
+          fence_proxy_async_all();
+          __threadfence();
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps
+        const int tile_id = (m0 / BM) * ((p.N + BN - 1) / BN) + n0 / BN;
+        if (warp == 2 && lane == 0) *fin_prev = atomicAdd(&p.fin_count[tile_id], 1u);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*fin_prev == (unsigned int)p.fin_splits - 1u) {
+          __threadfence();
+          const int tid = (int)threadIdx.x - 64;          // 0..127 among the epilogue threads
+          const int rows = min(BM, p.M - m0);
+          const int vec_per_row = min(BN, p.N - n0) >> 2;
+          for (int i = tid; i < rows * vec_per_row; i += EPI_WARPS * 32) {
+            const int r = i / vec_per_row, c = (i - r * vec_per_row) << 2;
+            float4* src = reinterpret_cast<float4*>(ws + (long long)(m0 + r) * p.fin_ld_ws + n0 + c);
+            const float4 v = __ldcg(src);
+            uint2 o;
+            o.x = pack_bf16x2(v.x, v.y);
+            o.y = pack_bf16x2(v.z, v.w);
+            *reinterpret_cast<uint2*>(p.fin_out + (long long)(m0 + r) * p.fin_ld_out + n0 + c) = o;
+            __stcg(src, make_float4(0.f, 0.f, 0.f, 0.f));
+          }
+          if (tid == 0) p.fin_count[tile_id] = 0u;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");   // fin_prev may be rewritten for the next tile
+      }
     }
     if (lane == 0) tma_wait_group<0>();
   }
@@ -326,7 +367,8 @@ int dispatch(bool a_mn, bool b_mn, bool out_f32, const CUtensorMap& tmA, const C
 static int gemm_impl(const void* A, const void* B, void* C, int M, int N, int K, int batch, int batch_a, int batch_b,
                      int batch_c, long long lda, long long ldb, long long ldc, long long stride_a, long long stride_b,
                      long long stride_c, int a_mn, int b_mn, int out_f32, int accumulate, int bn_hint,
-                     const int* tile_group, const int* k_range, int* status, void* stream, int c_shared = 0);
+                     const int* tile_group, const int* k_range, int* status, void* stream, int c_shared = 0,
+                     void* fin_out = nullptr, long long fin_ld_out = 0, void* fin_count = nullptr);
 
 extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int batch, long long lda,
                               long long ldb, long long ldc, long long stride_a, long long stride_b,
@@ -345,6 +387,18 @@ extern "C" int b200_gemm_bf16_splitk(const void* A, const void* B, void* C, int 
   const int kc = K / splits;
   return gemm_impl(A, B, C, M, N, kc, splits, 1, 1, 1, lda, ldb, ldc, 0, 0, 0, 0, 0, 1, 1, 0, nullptr, nullptr, status,
                    stream, 1);
+}
+
+// The same with the finishing pass inside the kernel: `ws` is an fp32 [M, N] workspace (row stride ldws) that is zero
+// on entry and zero again on exit, `out` receives the bf16 result (row stride ldo), `counters` holds one zeroed
+// uint32 per 128 x BN output tile (left zero).  N, ldws and ldo must be multiples of 4.
+extern "C" int b200_gemm_bf16_splitk_fused(const void* A, const void* B, void* ws, void* out, void* counters, int M,
+                                           int N, int K, int splits, long long lda, long long ldb, long long ldws,
+                                           long long ldo, int* status, void* stream) {
+  if (splits < 1 || K % (64 * splits) || !out || !counters) return b200host::RC_BAD_SHAPE;
+  const int kc = K / splits;
+  return gemm_impl(A, B, ws, M, N, kc, splits, 1, 1, 1, lda, ldb, ldws, 0, 0, 0, 0, 0, 1, 1, 0, nullptr, nullptr,
+                   status, stream, 1, out, ldo, counters);
 }
 
 // Split-K for any operand layout with an fp32 output that is accumulated into (weight gradients: the contraction
@@ -380,7 +434,8 @@ extern "C" int b200_gemm_bf16_grouped_k(const void* A, const void* B, void* C, i
 static int gemm_impl(const void* A, const void* B, void* C, int M, int N, int K, int batch, int batch_a, int batch_b,
                      int batch_c, long long lda, long long ldb, long long ldc, long long stride_a, long long stride_b,
                      long long stride_c, int a_mn, int b_mn, int out_f32, int accumulate, int bn_hint,
-                     const int* tile_group, const int* k_range, int* status, void* stream, int c_shared) {
+                     const int* tile_group, const int* k_range, int* status, void* stream, int c_shared, void* fin_out,
+                     long long fin_ld_out, void* fin_count) {
   using namespace b200host;
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return RC_BAD_SHAPE;
   const int BN = (bn_hint == 128 || bn_hint == 256) ? bn_hint : (N > 128 ? 256 : 128);
@@ -406,6 +461,15 @@ static int gemm_impl(const void* A, const void* B, void* C, int M, int N, int K,
   if (rc) return rc;
 
   GemmParams p{M, N, K, batch, accumulate, status, tile_group, k_range, c_shared};
+  p.fin_ws_ptr = fin_out ? static_cast<const float*>(C) : nullptr;
+  p.fin_out = static_cast<__nv_bfloat16*>(fin_out);
+  p.fin_ld_ws = ldc;
+  p.fin_ld_out = fin_ld_out;
+  p.fin_count = static_cast<unsigned int*>(fin_count);
+  p.fin_splits = batch;
+  if (fin_out && (!c_shared || !out_f32 || !accumulate || !fin_count || (N & 3) || (ldc & 3) || (fin_ld_out & 3) ||
+                  (reinterpret_cast<uintptr_t>(C) & 15) || (reinterpret_cast<uintptr_t>(fin_out) & 7)))
+    return RC_BAD_SHAPE;
   const int tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * batch;
   const int grid = tiles < sm_count() ? tiles : sm_count();
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);

@@ -124,6 +124,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         c_int, c_void_p, c_void_p)
     sig("b200_gemm_bf16_splitk", c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_void_p,
         c_void_p)
+    sig("b200_gemm_bf16_splitk_fused", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll,
+        c_ll, c_ll, c_ll, c_void_p, c_void_p)
     sig("b200_sample_topk", c_void_p, c_ll, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p)
     sig("b200_decode_attn_splits", c_int, c_int, c_int, c_int)
     sig("b200_decode_attn", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
@@ -336,22 +338,43 @@ def gemm_skinny(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
                                        b.stride(0), c.stride(0), status_word(a.device).data_ptr(), _stream())
         _check(rc, "b200_gemm_bf16_splitk")
         return c.to(torch.bfloat16)
-    # the slices add into a persistent fp32 workspace that is zero between calls: the finishing kernel converts the
-    # sums to bf16 and clears what it read, so a decode step runs no fill and no cast kernel per linear
+    # the slices add into a persistent fp32 workspace that is zero between calls; the CTA that adds the last slice of
+    # an output tile converts the tile to bf16 and clears the workspace behind it, so a decode step runs no fill, no
+    # cast and no finishing kernel per linear
     ws = _splitk_workspace(rows * N, a.device)
     out = torch.empty((rows, N), dtype=torch.bfloat16, device=a.device)
     try:
+        if rows <= 128 and os.environ.get("RESEARCH_B200_SPLITK_FUSED", "1") != "0":
+            counters = _splitk_counters(a.device)
+            rc = lib.b200_gemm_bf16_splitk_fused(a.data_ptr(), b.data_ptr(), ws.data_ptr(), out.data_ptr(),
+                                                 counters.data_ptr(), rows, N, K, splits, a.stride(0), b.stride(0), N,
+                                                 N, status_word(a.device).data_ptr(), _stream())
+            _check(rc, "b200_gemm_bf16_splitk_fused")
+            return out
         rc = lib.b200_gemm_bf16_splitk(a.data_ptr(), b.data_ptr(), ws.data_ptr(), rows, N, K, splits, a.stride(0),
                                        b.stride(0), N, status_word(a.device).data_ptr(), _stream())
         _check(rc, "b200_gemm_bf16_splitk")
         _check(lib.b200_splitk_finish(ws.data_ptr(), out.data_ptr(), rows * N, _stream()), "b200_splitk_finish")
     except Exception:
         _splitk_ws.pop(_device_index(a.device), None)      # its contents are unknown now: start from a fresh one
+        _splitk_cnt.pop(_device_index(a.device), None)
         raise
     return out
 
 
 _splitk_ws: dict[int, torch.Tensor] = {}
+_splitk_cnt: dict[int, torch.Tensor] = {}
+
+
+def _splitk_counters(device: torch.device) -> torch.Tensor:
+    """One uint32 per output tile of a fused split-K product (N up to 2^20 columns); zero between launches."""
+
+    key = _device_index(device)
+    cnt = _splitk_cnt.get(key)
+    if cnt is None:
+        cnt = torch.zeros(8192, dtype=torch.int32, device=device)
+        _splitk_cnt[key] = cnt
+    return cnt
 
 
 def _device_index(device: torch.device) -> int:
