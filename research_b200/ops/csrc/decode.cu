@@ -257,6 +257,7 @@ struct PagedParams {
   int B, Hq, Hkv, splits;
   float scale_log2;
   int* status;
+  long long q_batch;            // elements between the query rows of two sequences (heads are D apart)
 };
 
 __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -320,7 +321,7 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attn_paged_kernel(const Pag
   float q[G][8], acc[G][8], m[G], lsum[G];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
-    const __nv_bfloat16* qp = p.q + ((long long)b * p.Hq + hkv * G + g) * D + l * 8;
+    const __nv_bfloat16* qp = p.q + (long long)b * p.q_batch + (long long)(hkv * G + g) * D + l * 8;
     unpack8(*reinterpret_cast<const uint4*>(qp), q[g]);
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
@@ -562,8 +563,8 @@ extern "C" int b200_decode_attn_paged_splits(int B, int Hq, int Hkv, int max_row
 extern "C" int b200_decode_attn_paged(const void* q, const void* k, const void* v, void* out, const void* lengths,
                                       const void* lo, void* part_o, void* part_ml, int B, int Hq, int Hkv, int D,
                                       long long batch, long long head, long long page, int page_rows, float scale,
-                                      int splits, void* status, void* stream) {
-  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || splits < 1 || !status)
+                                      int splits, long long q_batch, void* status, void* stream) {
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || Hq % Hkv || splits < 1 || !status || q_batch < (long long)Hq * D || (q_batch % 8))
     return -2;
   if (page_rows < kTile || page_rows % kTile) return -2;  // a tile never straddles two pages
   if ((batch % 8) || (head % 8) || (page % 8)) return -1;  // 16-byte aligned bulk copies
@@ -571,7 +572,7 @@ extern "C" int b200_decode_attn_paged(const void* q, const void* k, const void* 
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   PagedParams p{(const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (const int*)lengths,
                 (const int*)lo, (float*)part_o, (float*)part_ml, batch, head, page, page_rows, B, Hq, Hkv, splits,
-                scale * kLog2e, (int*)status};
+                scale * kLog2e, (int*)status, q_batch};
   int rc;
   if (D == 128) rc = launch_paged<128>(p, Hq / Hkv, s);
   else if (D == 64) rc = launch_paged<64>(p, Hq / Hkv, s);

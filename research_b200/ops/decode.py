@@ -41,7 +41,10 @@ def _launch(q, k_base, v_base, lengths, lo, *, B, Hq, Hkv, D, rows, strides, pag
     strides) or "auto" (stream where the layout allows it)."""
 
     lib = native.load()
-    q = q.contiguous()
+    # the streaming kernel takes the queries where the projection left them (rows of a packed q|k buffer)
+    strided_q = q.dim() == 3 and q.stride(2) == 1 and q.stride(1) == D and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
+    if not strided_q:
+        q = q.contiguous()
     lengths = lengths.to(torch.int32).contiguous()
     lo = None if lo is None else lo.to(torch.int32).contiguous()
     k_row, k_batch, k_head, k_page = strides
@@ -58,10 +61,11 @@ def _launch(q, k_base, v_base, lengths, lo, *, B, Hq, Hkv, D, rows, strides, pag
     if stream:
         rc = lib.b200_decode_attn_paged(q.data_ptr(), k_base.data_ptr(), v_base.data_ptr(), out.data_ptr(),
                                         lengths.data_ptr(), lo_ptr, part_o.data_ptr(), part_ml.data_ptr(), B, Hq, Hkv,
-                                        D, k_batch, k_head, k_page, page_rows, sm_scale, splits,
+                                        D, k_batch, k_head, k_page, page_rows, sm_scale, splits, q.stride(0),
                                         native.status_word(q.device).data_ptr(), native._stream())
         native._check(rc, "b200_decode_attn_paged")
     else:
+        q = q.contiguous()
         rc = lib.b200_decode_attn(q.data_ptr(), k_base.data_ptr(), v_base.data_ptr(), out.data_ptr(),
                                   lengths.data_ptr(), lo_ptr, part_o.data_ptr(), part_ml.data_ptr(), B, Hq, Hkv, D,
                                   k_row, k_batch, k_row, k_batch, k_head, k_head, k_page, k_page, page_rows, sm_scale,

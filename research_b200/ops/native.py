@@ -131,7 +131,7 @@ def _declare(lib: ctypes.CDLL) -> None:
     sig("b200_decode_attn", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
         c_int, c_int, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_ll, c_int, c_float, c_int, c_void_p)
     sig("b200_decode_attn_paged", c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
-        c_int, c_int, c_int, c_ll, c_ll, c_ll, c_int, c_float, c_int, c_void_p, c_void_p)
+        c_int, c_int, c_int, c_ll, c_ll, c_ll, c_int, c_float, c_int, c_ll, c_void_p, c_void_p)
     sig("b200_decode_attn_paged_splits", c_int, c_int, c_int, c_int)
     sig("b200_splitk_finish", c_void_p, c_void_p, c_ll, c_void_p)
     sig("b200_kv_append", c_void_p, c_void_p, c_ll, c_ll, c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_ll, c_ll, c_int,
@@ -320,9 +320,11 @@ def splitk_factor(n: int, k: int, sms: int = 148) -> int:
     return best
 
 
-def gemm_skinny(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+def gemm_skinny(a: torch.Tensor, b: torch.Tensor, fused_finish: bool | None = None) -> torch.Tensor:
     """``a [rows, K] @ b [N, K]^T`` for a handful of rows (decode): split-K so that the whole device streams ``b``.
-    Returns bf16 ``[rows, N]``."""
+    Returns bf16 ``[rows, N]``.  ``fused_finish``: let the CTA that adds the last slice of a tile convert it inside the
+    product (default: ``RESEARCH_B200_SPLITK_FUSED``, off: inside a CUDA graph the separate 3 us finishing kernel
+    measured cheaper than the counters, fences and barriers that the fused form adds to every CTA)."""
 
     lib = load()
     rows, K = a.shape
@@ -338,13 +340,14 @@ def gemm_skinny(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
                                        b.stride(0), c.stride(0), status_word(a.device).data_ptr(), _stream())
         _check(rc, "b200_gemm_bf16_splitk")
         return c.to(torch.bfloat16)
-    # the slices add into a persistent fp32 workspace that is zero between calls; the CTA that adds the last slice of
-    # an output tile converts the tile to bf16 and clears the workspace behind it, so a decode step runs no fill, no
-    # cast and no finishing kernel per linear
+    # the slices add into a persistent fp32 workspace that is zero between calls; a finishing pass (a small kernel,
+    # or the CTA that adds the last slice of a tile) converts the sums to bf16 and clears the workspace behind it,
+    # so a decode step runs no fill and no cast per linear
     ws = _splitk_workspace(rows * N, a.device)
     out = torch.empty((rows, N), dtype=torch.bfloat16, device=a.device)
     try:
-        if rows <= 128 and os.environ.get("RESEARCH_B200_SPLITK_FUSED", "1") != "0":
+        if rows <= 128 and (fused_finish if fused_finish is not None
+                            else os.environ.get("RESEARCH_B200_SPLITK_FUSED", "0") == "1"):
             counters = _splitk_counters(a.device)
             rc = lib.b200_gemm_bf16_splitk_fused(a.data_ptr(), b.data_ptr(), ws.data_ptr(), out.data_ptr(),
                                                  counters.data_ptr(), rows, N, K, splits, a.stride(0), b.stride(0), N,

@@ -74,6 +74,12 @@ def test_streaming_paged_decode_matches_reference_and_register_kernel(D, Hq, Hkv
         native.check_status()
         torch.testing.assert_close(got, want, atol=2e-2, rtol=2e-2)
         torch.testing.assert_close(got, regs, atol=1e-2, rtol=1e-2)
+        # queries left where the projection wrote them: rows of a packed q|k buffer, read without a copy
+        packed = torch.zeros(B, (Hq + Hkv) * D, device="cuda", dtype=torch.bfloat16)
+        packed[:, : Hq * D] = q.reshape(B, Hq * D)
+        strided = packed[:, : Hq * D].view(B, Hq, D)
+        assert not strided.is_contiguous()
+        assert torch.equal(decode_attention_paged(strided, kp, vp, lengths, bounds, kernel="stream").float(), got)
     assert torch.count_nonzero(got[4]) == 0
 
 

@@ -95,11 +95,12 @@ def test_skinny_splitk_gemm_matches_reference():
                        (64, 11264, 2048), (32, 2048, 2048)):
         a = (torch.randn(rows, k, device="cuda") * 0.5).bfloat16()
         b = (torch.randn(n, k, device="cuda") * 0.05).bfloat16()
-        y = native.gemm_skinny(a, b)
-        native.check_status()
         ref = a.float() @ b.float().t()
-        assert y.shape == (rows, n) and y.dtype == torch.bfloat16
-        assert torch.allclose(y.float(), ref, atol=3e-2, rtol=3e-2), (rows, n, k, (y.float() - ref).abs().max().item())
+        for fused in (False, True):       # finishing pass as its own kernel / inside the product
+            y = native.gemm_skinny(a, b, fused_finish=fused)
+            native.check_status()
+            assert y.shape == (rows, n) and y.dtype == torch.bfloat16
+            assert torch.allclose(y.float(), ref, atol=3e-2, rtol=3e-2), (rows, n, k, fused, (y.float() - ref).abs().max().item())
     assert native.splitk_factor(2048, 2048) > 1
 
 
