@@ -242,7 +242,7 @@ class ParamStore:
             self.compute_arena = torch.zeros(self.total, dtype=self.compute_dtype, device=dev)
             self.grad_arena = torch.zeros(self.total, dtype=torch.float32, device=dev)
         # bucketed reduction on a side stream (see begin_backward_overlap)
-        self._overlap = (self.arena is not None and os.environ.get("RESEARCH_B200_OVERLAP_REDUCE", "1") != "0")
+        self._overlap = (self.arena is not None and os.environ.get("RESEARCH_B200_OVERLAP_REDUCE", "0") == "1")
         self._comm_stream = torch.cuda.Stream(dev, priority=-1) if self._overlap else None
         self._bucket_ctas = int(os.environ.get("RESEARCH_B200_REDUCE_CTAS", "48"))
         self._pending: list[tuple[Section, int]] = []
@@ -371,7 +371,7 @@ class ParamStore:
         self._slot_ready = [None] * self._n_slots          # event: the gather into the slot has finished
         self._slot_free = [None] * self._n_slots           # event: the compute that read the slot has been issued
         self._tables: dict[tuple, tuple[torch.Tensor, int]] = {}
-        self._overlap = (self.arena is not None and os.environ.get("RESEARCH_B200_OVERLAP_REDUCE", "1") != "0")
+        self._overlap = (self.arena is not None and os.environ.get("RESEARCH_B200_OVERLAP_REDUCE", "0") == "1")
         self._comm_stream = torch.cuda.Stream(dev, priority=-1) if self._overlap else None
         self._bucket_ctas = int(os.environ.get("RESEARCH_B200_REDUCE_CTAS", "48"))
         self._pending = []

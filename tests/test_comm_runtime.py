@@ -375,6 +375,9 @@ def _run_training(tmp_path, world, axes, sizes, flags, peer, port, extra_env=Non
 @pytest.mark.parametrize("name,axes,sizes,flags", [
     ("tp2", ["tp"], [2], {"parallelism": {"mode": "ddp", "tensor_parallel": True}}),
     ("fsdp2_muon", ["fsdp"], [2], {"parallelism": {"mode": "fsdp"}, "optimizer": "muon"}),
+    # the opt-in form: every layer's gradients are reduced on a side stream while earlier layers are in backward
+    ("fsdp2_muon_overlapped_reduce", ["fsdp"], [2], {"parallelism": {"mode": "fsdp"}, "optimizer": "muon",
+                                                     "env": {"RESEARCH_B200_OVERLAP_REDUCE": "1"}}),
     ("moe_fsdp2_ep2", ["fsdp"], [2], {
         "parallelism": {"mode": "fsdp", "expert_parallel": True},
         "model": {"name": "trinity", "num_layers": 2, "trinity": {
