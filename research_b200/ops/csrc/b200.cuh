@@ -67,6 +67,11 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// Programmatic dependent launch (see host_util.cuh: launch_kernel).  Both are no-ops for a kernel that was launched
+// the ordinary way.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // One probe of a barrier phase.  The hint lets the hardware keep the thread suspended (not issuing) for up to that
 // many nanoseconds while the phase is incomplete; it resumes as soon as the phase completes.  Without it a waiting
 // warp polls back to back and takes issue slots from the warps of its scheduler that have work.

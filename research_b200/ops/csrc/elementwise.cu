@@ -159,6 +159,8 @@ rmsnorm_fwd_row_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
                        const float* __restrict__ w, __nv_bfloat16* __restrict__ res_out, __nv_bfloat16* __restrict__ y,
                        float* __restrict__ rstd_out, int H, float eps) {
   __shared__ float part[8];
+  b200::pdl_launch_dependents();   // no-ops unless launched as a dependent (decode steps)
+  b200::pdl_wait();
   const long long row = blockIdx.x;
   const int nvec = H >> 3;
   const uint4* xr = reinterpret_cast<const uint4*>(x + row * H);
@@ -205,6 +207,8 @@ rmsnorm_fwd_row_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16*
 // fill before its next use.  n % 4 == 0.
 __global__ void __launch_bounds__(256)
 splitk_finish_kernel(float* __restrict__ ws, __nv_bfloat16* __restrict__ out, long long n4) {
+  b200::pdl_launch_dependents();
+  b200::pdl_wait();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (long long)gridDim.x * blockDim.x) {
     const float4 v = reinterpret_cast<const float4*>(ws)[i];
     reinterpret_cast<float4*>(ws)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -600,6 +604,8 @@ __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfl
                                   int I) {
   const unsigned nvec = (unsigned)I >> 3;
   const unsigned total = (unsigned)rows * nvec;
+  b200::pdl_launch_dependents();
+  b200::pdl_wait();
   for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
     const unsigned r = i / nvec;
     const unsigned v = i - r * nvec;
@@ -1043,10 +1049,11 @@ extern "C" int b200_rmsnorm_fwd(const void* x, const void* delta, const void* w,
                                 int rows, int H, float eps, void* stream) {
   if (H % 8) return -2;
   if (rows > 0 && rows <= 512) {
-    rmsnorm_fwd_row_kernel<<<rows, 256, 0, STREAM(stream)>>>(
+    // few rows = a decode step: launched as a dependent so that it is resident when its predecessor ends
+    return static_cast<int>(b200host::launch_kernel(
+        rmsnorm_fwd_row_kernel, dim3(rows), dim3(256), 0, STREAM(stream), b200host::pdl_enabled() != 0,
         (const __nv_bfloat16*)x, (const __nv_bfloat16*)delta, (const float*)w, (__nv_bfloat16*)res_out,
-        (__nv_bfloat16*)y, (float*)rstd, H, eps);
-    return LAST_ERR();
+        (__nv_bfloat16*)y, (float*)rstd, H, eps));
   }
   const int grid = grid_for((long long)rows, kWarpsPerBlock, 8);
 #define RMS_FWD(NV)                                                                                         \
@@ -1155,9 +1162,9 @@ extern "C" int b200_qknorm_rope_bwd_qk(const void* in, long long in_stride, cons
 }
 extern "C" int b200_swiglu_fwd(const void* gu, void* h, long long rows, int I, void* stream) {
   if (I % 8 || rows * (I / 8) >= (1LL << 32)) return -2;
-  swiglu_fwd_kernel<<<grid_for(rows * (I / 8), 256), 256, 0, STREAM(stream)>>>((const __nv_bfloat16*)gu,
-                                                                                (__nv_bfloat16*)h, rows, I);
-  return LAST_ERR();
+  return static_cast<int>(b200host::launch_kernel(swiglu_fwd_kernel, dim3(grid_for(rows * (I / 8), 256)), dim3(256), 0,
+                                                  STREAM(stream), rows <= 512 && b200host::pdl_enabled() != 0,
+                                                  (const __nv_bfloat16*)gu, (__nv_bfloat16*)h, rows, I));
 }
 extern "C" int b200_swiglu_bwd(const void* gu, const void* dh, void* dgu, long long rows, int I, void* stream) {
   if (I % 8 || rows * (I / 8) >= (1LL << 32)) return -2;
@@ -1265,6 +1272,6 @@ extern "C" int b200_splitk_finish(void* ws, void* out, long long n, void* stream
   const long long n4 = n / 4;
   long long blocks = (n4 + 255) / 256;
   if (blocks > 148 * 8) blocks = 148 * 8;
-  splitk_finish_kernel<<<(int)blocks, 256, 0, STREAM(stream)>>>((float*)ws, (__nv_bfloat16*)out, n4);
-  return LAST_ERR();
+  return static_cast<int>(b200host::launch_kernel(splitk_finish_kernel, dim3((int)blocks), dim3(256), 0, STREAM(stream),
+                                                  b200host::pdl_enabled() != 0, (float*)ws, (__nv_bfloat16*)out, n4));
 }

@@ -63,6 +63,9 @@ struct GemmParams {
   long long fin_ld_ws, fin_ld_out;
   unsigned int* fin_count;
   int fin_splits;
+  // Programmatic dependent launch (skinny split-K products of a decode step): the weight tiles of the first stages
+  // are requested before the wait for the predecessor, only the activation tiles and the output come after it.
+  int pdl;
 };
 
 template <int BN, bool A_MN, bool B_MN, bool OUT_F32>
@@ -72,6 +75,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   using L = SmemLayout<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  if (p.pdl) pdl_launch_dependents();   // the successor may take its place on the SMs; it waits for this grid itself
 
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + L::BAR_OFF);
   uint64_t* empty = full + STAGES;
@@ -149,6 +154,33 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       tma_prefetch_desc(&tmB);
       uint32_t it = 0;
       bool ok = true;
+      auto load_b = [&](uint8_t* sB, uint64_t* bar, int kb, int n0, int zB) {
+        if (!B_MN) {
+          tma_load_3d(sB, &tmB, bar, kb * BK, n0, zB);
+        } else {
+#pragma unroll
+          for (int j = 0; j < BN / 64; ++j) tma_load_3d(sB + j * 8192, &tmB, bar, n0 + j * 64, kb * BK, zB);
+        }
+      };
+      // Dependent launch: B (the weights) does not depend on the predecessor, so the B tiles of the first tile's
+      // first stages are on their way before this CTA waits for it; A follows after the wait.
+      uint32_t b_ahead = 0;
+      if (p.pdl) {
+        if ((int)blockIdx.x < total_tiles) {
+          int b, m0, n0, bB, zAC, kb0, kb1;
+          tile_coords(blockIdx.x, b, m0, n0);
+          if (tile_extent(b, m0, bB, zAC, kb0, kb1)) {
+            const int zB = (p.k_range || p.c_shared) ? 0 : bB;
+            const int k_off = p.c_shared ? b * k_blocks : 0;
+            for (int kb = kb0 + k_off; kb < kb1 + k_off && b_ahead < (uint32_t)STAGES; ++kb, ++b_ahead) {
+              uint8_t* sB = smem + b_ahead * L::STAGE_BYTES + A_TILE_BYTES;
+              mbar_expect_tx(&full[b_ahead], L::STAGE_BYTES);
+              load_b(sB, &full[b_ahead], kb, n0, zB);
+            }
+          }
+        }
+        pdl_wait();
+      }
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
         int b, m0, n0, bB, zAC, kb0, kb1;
         tile_coords(t, b, m0, n0);
@@ -159,22 +191,18 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         for (int kb = kb0 + k_off; kb < kb1 + k_off; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
-          if (!mbar_wait(&empty[s], ph ^ 1, ab, ERR_WAIT_EMPTY)) { ok = false; break; }
+          const bool b_requested = it < b_ahead;   // expect_tx and the B tile of this stage went out before the wait
+          if (!b_requested && !mbar_wait(&empty[s], ph ^ 1, ab, ERR_WAIT_EMPTY)) { ok = false; break; }
           uint8_t* sA = smem + s * L::STAGE_BYTES;
           uint8_t* sB = sA + A_TILE_BYTES;
-          mbar_expect_tx(&full[s], L::STAGE_BYTES);
+          if (!b_requested) mbar_expect_tx(&full[s], L::STAGE_BYTES);
           if (!A_MN) {
             tma_load_3d(sA, &tmA, &full[s], kb * BK, m0, zA);
           } else {
 #pragma unroll
             for (int j = 0; j < BM / 64; ++j) tma_load_3d(sA + j * 8192, &tmA, &full[s], m0 + j * 64, kb * BK, zA);
           }
-          if (!B_MN) {
-            tma_load_3d(sB, &tmB, &full[s], kb * BK, n0, zB);
-          } else {
-#pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_3d(sB + j * 8192, &tmB, &full[s], n0 + j * 64, kb * BK, zB);
-          }
+          if (!b_requested) load_b(sB, &full[s], kb, n0, zB);
         }
       }
       if (!ok) {
@@ -226,6 +254,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t tile_iter = 0;
     uint32_t box_iter = 0;
     bool ok = true;
+    if (p.pdl) pdl_wait();   // C (and the workspace behind it) belongs to the predecessor until it has completed
     for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
       int b, m0, n0, bB, zAC, kb0, kb1;
       tile_coords(t, b, m0, n0);
@@ -338,6 +367,8 @@ int launch(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tm
   constexpr int smem_bytes = L::TOTAL + 1024;
   static bool configured[b200host::kMaxDevices] = {};   // per kernel instantiation and device
   if (int rc = b200host::ensure_dynamic_smem(kern, smem_bytes, configured)) return rc;
+  if (p.pdl) return static_cast<int>(b200host::launch_kernel(kern, dim3(grid), dim3(NUM_THREADS), smem_bytes, stream, true,
+                                                             tmA, tmB, tmC, p));
   kern<<<grid, NUM_THREADS, smem_bytes, stream>>>(tmA, tmB, tmC, p);
   return static_cast<int>(cudaGetLastError());
 }
@@ -368,7 +399,7 @@ static int gemm_impl(const void* A, const void* B, void* C, int M, int N, int K,
                      int batch_c, long long lda, long long ldb, long long ldc, long long stride_a, long long stride_b,
                      long long stride_c, int a_mn, int b_mn, int out_f32, int accumulate, int bn_hint,
                      const int* tile_group, const int* k_range, int* status, void* stream, int c_shared = 0,
-                     void* fin_out = nullptr, long long fin_ld_out = 0, void* fin_count = nullptr);
+                     void* fin_out = nullptr, long long fin_ld_out = 0, void* fin_count = nullptr, int pdl = 0);
 
 extern "C" int b200_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int batch, long long lda,
                               long long ldb, long long ldc, long long stride_a, long long stride_b,
@@ -386,7 +417,7 @@ extern "C" int b200_gemm_bf16_splitk(const void* A, const void* B, void* C, int 
   if (splits < 1 || K % (64 * splits)) return b200host::RC_BAD_SHAPE;
   const int kc = K / splits;
   return gemm_impl(A, B, C, M, N, kc, splits, 1, 1, 1, lda, ldb, ldc, 0, 0, 0, 0, 0, 1, 1, 0, nullptr, nullptr, status,
-                   stream, 1);
+                   stream, 1, nullptr, 0, nullptr, b200host::pdl_enabled());
 }
 
 // The same with the finishing pass inside the kernel: `ws` is an fp32 [M, N] workspace (row stride ldws) that is zero
@@ -398,7 +429,7 @@ extern "C" int b200_gemm_bf16_splitk_fused(const void* A, const void* B, void* w
   if (splits < 1 || K % (64 * splits) || !out || !counters) return b200host::RC_BAD_SHAPE;
   const int kc = K / splits;
   return gemm_impl(A, B, ws, M, N, kc, splits, 1, 1, 1, lda, ldb, ldws, 0, 0, 0, 0, 0, 1, 1, 0, nullptr, nullptr,
-                   status, stream, 1, out, ldo, counters);
+                   status, stream, 1, out, ldo, counters, b200host::pdl_enabled());
 }
 
 // Split-K for any operand layout with an fp32 output that is accumulated into (weight gradients: the contraction
@@ -435,7 +466,7 @@ static int gemm_impl(const void* A, const void* B, void* C, int M, int N, int K,
                      int batch_c, long long lda, long long ldb, long long ldc, long long stride_a, long long stride_b,
                      long long stride_c, int a_mn, int b_mn, int out_f32, int accumulate, int bn_hint,
                      const int* tile_group, const int* k_range, int* status, void* stream, int c_shared, void* fin_out,
-                     long long fin_ld_out, void* fin_count) {
+                     long long fin_ld_out, void* fin_count, int pdl) {
   using namespace b200host;
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return RC_BAD_SHAPE;
   const int BN = (bn_hint == 128 || bn_hint == 256) ? bn_hint : (N > 128 ? 256 : 128);
@@ -467,6 +498,7 @@ static int gemm_impl(const void* A, const void* B, void* C, int M, int N, int K,
   p.fin_ld_out = fin_ld_out;
   p.fin_count = static_cast<unsigned int*>(fin_count);
   p.fin_splits = batch;
+  p.pdl = pdl;
   if (fin_out && (!c_shared || !out_f32 || !accumulate || !fin_count || (N & 3) || (ldc & 3) || (fin_ld_out & 3) ||
                   (reinterpret_cast<uintptr_t>(C) & 15) || (reinterpret_cast<uintptr_t>(fin_out) & 7)))
     return RC_BAD_SHAPE;

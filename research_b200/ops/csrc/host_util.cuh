@@ -1,6 +1,7 @@
 // Host-side helpers shared by the launchers: tensor-map encoding through the driver entry point
 // (no link-time dependency on libcuda), device attribute cache, error plumbing.
 #pragma once
+#include <stdlib.h>
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -61,6 +62,36 @@ inline int ensure_dynamic_smem(Kern* kern, int bytes, bool (&done)[kMaxDevices])
   if (e != cudaSuccess) return static_cast<int>(e);
   if (tracked) done[dev] = true;
   return 0;
+}
+
+// RESEARCH_B200_PDL=0 turns programmatic dependent launch off for the kernels of a decode step that use it.
+inline int pdl_enabled() {
+  static const int on = [] {
+    const char* v = getenv("RESEARCH_B200_PDL");
+    return (v && v[0] == '0') ? 0 : 1;
+  }();
+  return on;
+}
+
+// Launch with programmatic dependent launch when `pdl` is set: the kernel may become resident while its predecessor
+// in the stream is still running, and everything it reads or writes that the predecessor also touches must come
+// after its `griddepcontrol.wait` (b200.cuh: pdl_wait), which returns when the predecessor has completed.  A
+// predecessor lets this happen early by executing `griddepcontrol.launch_dependents` (pdl_launch_dependents) in
+// every CTA; without it the dependent launch begins when the predecessor's last CTA has exited.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 bool pdl, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 
 // Rank-3 row-major tensor [d2][d1][d0] (d0 innermost) with byte strides s1 (between d1 rows) and
