@@ -189,6 +189,9 @@ def main() -> int:
     ap.add_argument("--impl", default="native", choices=["native", "reference", "library"])
     ap.add_argument("--no-library", action="store_true", help="native arm: skip the in-process library comparison")
     ap.add_argument("--no-decode", action="store_true", help="native arm: skip the generation record (1 GPU only)")
+    ap.add_argument("--kernel-table", default=None, metavar="FILE",
+                    help="after the timed regions, run one more step under the torch profiler and write rank 0's "
+                         "kernel-time table to FILE")
     ap.add_argument("--per-gpu-batch", type=int, default=8)
     ap.add_argument("--seq-len", type=int, default=None)
     ap.add_argument("--optimizer", default=None, choices=["muon", "adamw", "dion"])
@@ -291,6 +294,17 @@ def main() -> int:
         if world > 1:
             dist.all_reduce(times, op=dist.ReduceOp.MAX)
         dev_ms, e2e_ms = times.tolist()
+        if args.kernel_table and label == "native":
+            # one more step under the torch profiler (outside every timed region): kernel time by name, rank 0
+            from torch.profiler import ProfilerActivity, profile
+
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                trainer.train_step()
+                torch.cuda.synchronize()
+            if rank == 0:
+                Path(args.kernel_table).write_text(
+                    prof.key_averages().table(sort_by="cuda_time_total", row_limit=80, max_name_column_width=100))
+            sync()
         out = {"label": label, "dev_ms": dev_ms, "e2e_ms": e2e_ms, "h2d": h2d, "d2h": d2h, "launches": launches,
                "clocks": clocks, "loss": None if last is None else round(last.loss, 4),
                "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 2)}
