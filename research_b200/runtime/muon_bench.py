@@ -10,7 +10,8 @@ give the same bits when run twice, leave all replicas equal, and keep the update
 and the fastest one that passed is the selection.  The process group the command runs in plays the tensor-parallel
 group (one rank: every execution degenerates to the local iteration, which still exercises the code).
 
-``jaxtitan profile bench muon`` prints the report and, with ``--out``, writes ``manifest.json`` with one entry per case.
+``jaxtitan profile bench muon`` prints the report and, with ``--artifact-dir``, writes ``manifest.json`` with one entry
+per case (``runtime/validation_matrix.py: analyze_muon_bench`` gates it).
 """
 
 from __future__ import annotations
