@@ -32,7 +32,7 @@ PARALLELISM_MODES = ("ddp", "fsdp", "zero2")
 EXPERT_PARALLEL_AXES = ("auto", "data", "ep", "fsdp")
 PRECISION_NAMES = ("bf16", "fp32", "mixed_bf16")
 
-# BASELINE-style axis spellings accepted in [mesh].axis_names and mapped to the reference spelling
+# Long axis spellings (tensor, context, expert) accepted in [mesh].axis_names and mapped to the reference spelling
 AXIS_ALIASES = {"tensor": "tp", "context": "cp", "expert": "ep"}
 SUPPORTED_AXES = ("data", "fsdp", "tp", "cp", "ep", "expert_fsdp")
 
