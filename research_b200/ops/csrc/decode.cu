@@ -182,6 +182,8 @@ __global__ void decode_attn_merge_kernel(const float* __restrict__ part_o, const
                                          __nv_bfloat16* __restrict__ out, int splits, int D) {
   const long long bh = blockIdx.x;
   const int d = threadIdx.x;
+  b200::pdl_launch_dependents();
+  b200::pdl_wait();
   if (d >= D) return;
   float mm = -CUDART_INF_F;
   for (int s = 0; s < splits; ++s) mm = fmaxf(mm, part_ml[(bh * splits + s) * 2]);
@@ -205,6 +207,8 @@ __global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ k_new, const 
                                  int B, int Hkv, int D) {
   const int per = D / 8;
   const int total = B * Hkv * per;
+  b200::pdl_launch_dependents();
+  b200::pdl_wait();
   for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
     const int c = i % per, h = (i / per) % Hkv, b = i / (per * Hkv);
     const int r = positions[b];
@@ -288,6 +292,10 @@ __global__ void __launch_bounds__(WARPS * 32) decode_attn_paged_kernel(const Pag
   const int grp = warp * RPW + sub;
   const uint32_t gmask = LPR == 32 ? 0xffffffffu : (((1u << LPR) - 1u) << (sub * LPR));
 
+  // launched as a programmatic dependent inside a decode step: resident early, everything in global memory (the
+  // row just appended included) is read after the predecessor has completed
+  b200::pdl_launch_dependents();
+  b200::pdl_wait();
   const int len = p.lengths[b];
   const int first = p.lo ? max(p.lo[b], 0) : 0;
   const int tile_lo = first / TILE;
@@ -462,8 +470,9 @@ int launch_paged_cfg(const PagedParams& p, cudaStream_t s) {
   static bool configured[b200host::kMaxDevices] = {};  // per instantiation and device; the attribute is sticky
   if (b200host::ensure_dynamic_smem(decode_attn_paged_kernel<D, G, TILE, STAGES, WARPS>, bytes, configured) != 0)
     return -3;
-  decode_attn_paged_kernel<D, G, TILE, STAGES, WARPS><<<dim3(p.splits, p.Hkv, p.B), WARPS * 32, bytes, s>>>(p);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(b200host::launch_kernel(decode_attn_paged_kernel<D, G, TILE, STAGES, WARPS>,
+                                                  dim3(p.splits, p.Hkv, p.B), dim3(WARPS * 32), bytes, s,
+                                                  b200host::pdl_enabled() != 0, p));
 }
 
 template <int D, int G>
@@ -523,8 +532,9 @@ extern "C" int b200_decode_attn(const void* q, const void* k, const void* v, voi
   else if (D == 64) rc = launch_partial<64>(p, Hq / Hkv, s);
   else return -2;
   if (rc) return rc;
-  decode_attn_merge_kernel<<<B * Hq, D, 0, s>>>((const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, splits, D);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(b200host::launch_kernel(decode_attn_merge_kernel, dim3(B * Hq), dim3(D), 0, s,
+                                                  b200host::pdl_enabled() != 0, (const float*)part_o,
+                                                  (const float*)part_ml, (__nv_bfloat16*)out, splits, D));
 }
 
 // Append one token per sequence to head-major paged caches (see b200_decode_attn for the addressing).
@@ -534,10 +544,11 @@ extern "C" int b200_kv_append(const void* k_new, const void* v_new, long long kn
   if (B <= 0 || Hkv <= 0 || D % 8 || page_rows < 1) return -2;
   if ((kn_batch % 8) || (vn_batch % 8) || (c_batch % 8) || (c_head % 8) || (c_page % 8) || (c_row % 8)) return -1;
   const int total = B * Hkv * (D / 8);
-  kv_append_kernel<<<(total + 255) / 256, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      (const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, kn_batch, vn_batch, (__nv_bfloat16*)k_cache,
-      (__nv_bfloat16*)v_cache, (const int*)positions, c_batch, c_head, c_page, c_row, page_rows, B, Hkv, D);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(b200host::launch_kernel(
+      kv_append_kernel, dim3((total + 255) / 256), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream),
+      b200host::pdl_enabled() != 0, (const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, kn_batch, vn_batch,
+      (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, (const int*)positions, c_batch, c_head, c_page, c_row, page_rows,
+      B, Hkv, D));
 }
 
 // Splits for the tile-streaming kernel: one wave of resident CTAs (shared memory allows two per SM for GQA groups
@@ -578,6 +589,7 @@ extern "C" int b200_decode_attn_paged(const void* q, const void* k, const void* 
   else if (D == 64) rc = launch_paged<64>(p, Hq / Hkv, s);
   else return -2;
   if (rc) return rc;
-  decode_attn_merge_kernel<<<B * Hq, D, 0, s>>>((const float*)part_o, (const float*)part_ml, (__nv_bfloat16*)out, splits, D);
-  return static_cast<int>(cudaGetLastError());
+  return static_cast<int>(b200host::launch_kernel(decode_attn_merge_kernel, dim3(B * Hq), dim3(D), 0, s,
+                                                  b200host::pdl_enabled() != 0, (const float*)part_o,
+                                                  (const float*)part_ml, (__nv_bfloat16*)out, splits, D));
 }

@@ -473,8 +473,11 @@ qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ in, long long in_stride
   float inv_freq[4], wv[8] = {1, 1, 1, 1, 1, 1, 1, 1}, wv2[8] = {1, 1, 1, 1, 1, 1, 1, 1};
 #pragma unroll
   for (int i = 0; i < 4; ++i) inv_freq[i] = exp2f(-log2_theta * (2.f * (float)(l * 4 + i)) / (float)D);
+  // the norm scales are weights (no predecessor writes them): they are read before the wait for the predecessor
   if (w && has_cols) load8f(w + l * 8, wv);
   if (w2 && has_cols) load8f(w2 + l * 8, wv2);
+  b200::pdl_launch_dependents();   // no-ops unless launched as a dependent (decode steps)
+  b200::pdl_wait();
   const long long groups = (total + hpw - 1) / hpw;
   for (long long gidx = (long long)blockIdx.x * kWarpsPerBlock + warp; gidx < groups;
        gidx += (long long)gridDim.x * kWarpsPerBlock) {
@@ -1113,10 +1116,10 @@ extern "C" int b200_qknorm_rope_fwd(const void* in, long long in_stride, void* o
   if (D % 8 || D > 256) return -2;
   const int lph = lanes_per_head(D);
   const int grid = grid_for((tokens * heads + 32 / lph - 1) / (32 / lph), kWarpsPerBlock, 8);
-  qknorm_rope_fwd_kernel<<<grid, kWarpsPerBlock * 32, 0, STREAM(stream)>>>(
+  return static_cast<int>(b200host::launch_kernel(qknorm_rope_fwd_kernel, dim3(grid), dim3(kWarpsPerBlock * 32), 0,
+                                                  STREAM(stream), tokens <= 512 && b200host::pdl_enabled() != 0,
       (const __nv_bfloat16*)in, in_stride, (__nv_bfloat16*)out, out_stride, (const float*)w, (const int*)positions,
-      (float*)rstd, tokens, heads, D, eps, log2f(theta), rope, lph, nullptr, heads);
-  return LAST_ERR();
+      (float*)rstd, tokens, heads, D, eps, log2f(theta), rope, lph, nullptr, heads));
 }
 // Query and key heads of a packed projection in one launch: the first heads_q heads use wq, the next heads_k use wk
 // (both or neither given); rstd is [tokens, heads_q + heads_k].
@@ -1128,10 +1131,10 @@ extern "C" int b200_qknorm_rope_fwd_qk(const void* in, long long in_stride, void
   const int heads = heads_q + heads_k;
   const int lph = lanes_per_head(D);
   const int grid = grid_for((tokens * heads + 32 / lph - 1) / (32 / lph), kWarpsPerBlock, 8);
-  qknorm_rope_fwd_kernel<<<grid, kWarpsPerBlock * 32, 0, STREAM(stream)>>>(
+  return static_cast<int>(b200host::launch_kernel(qknorm_rope_fwd_kernel, dim3(grid), dim3(kWarpsPerBlock * 32), 0,
+                                                  STREAM(stream), tokens <= 512 && b200host::pdl_enabled() != 0,
       (const __nv_bfloat16*)in, in_stride, (__nv_bfloat16*)out, out_stride, (const float*)wq, (const int*)positions,
-      (float*)rstd, tokens, heads, D, eps, log2f(theta), rope, lph, (const float*)wk, heads_q);
-  return LAST_ERR();
+      (float*)rstd, tokens, heads, D, eps, log2f(theta), rope, lph, (const float*)wk, heads_q));
 }
 extern "C" int b200_qknorm_rope_bwd(const void* in, long long in_stride, const void* dout, long long dout_stride,
                                     void* din, long long din_stride, const void* w, const void* positions,
