@@ -183,7 +183,7 @@ def case_command(case: MatrixCase, config_path: Path, port: int) -> list[str]:
 
 
 def run_matrix(name: str, out_root: str | Path, *, gpus: int, manifest: str | Path, dry_run: bool = False,
-               timeout_s: float = 1800.0, runner=subprocess.run) -> dict[str, Any]:
+               timeout_s: float = 1800.0, runner=subprocess.run, only: tuple[str, ...] = ()) -> dict[str, Any]:
     """Run (or, with ``dry_run``, only plan) every case of matrix ``name`` that fits ``gpus`` GPUs; returns and writes
     ``matrix.json`` (cases, commands, exit codes) and bundles the run directories as ``<name>.tgz``."""
 
@@ -194,6 +194,8 @@ def run_matrix(name: str, out_root: str | Path, *, gpus: int, manifest: str | Pa
     runs_dir.mkdir(parents=True, exist_ok=True)
     records = []
     for i, case in enumerate(MATRICES[name]):
+        if only and not any(part in case.run_id for part in only):
+            continue
         record: dict[str, Any] = {"case": asdict(case), "gpus": case.gpus}
         if case.gpus > gpus:
             record.update(status="skipped", reason=f"needs {case.gpus} GPUs, {gpus} given")
@@ -391,6 +393,8 @@ def main(argv: list[str] | None = None) -> int:
     p.add_argument("--out", default="runs/validation")
     p.add_argument("--manifest", required=True, help="prepared-token manifest (jaxtitan data prepare | synth)")
     p.add_argument("--dry-run", action="store_true", help="write the configs and the plan, launch nothing")
+    p.add_argument("--only", action="append", default=[], metavar="TEXT",
+                   help="run only the cases whose id contains TEXT (repeatable)")
     p = sub.add_parser("analyze", help="gate a capture directory or bundle, optionally against a baseline")
     p.add_argument("candidate")
     p.add_argument("--baseline")
@@ -403,7 +407,8 @@ def main(argv: list[str] | None = None) -> int:
     args = ap.parse_args(argv)
     try:
         if args.command == "run":
-            payload = run_matrix(args.matrix, args.out, gpus=args.gpus, manifest=args.manifest, dry_run=args.dry_run)
+            payload = run_matrix(args.matrix, args.out, gpus=args.gpus, manifest=args.manifest, dry_run=args.dry_run,
+                                 only=tuple(args.only))
             for rec in payload["cases"]:
                 print(f"{rec['case']['run_id']:<58} {rec['status']}")
             return 0 if all(r["status"] in ("ok", "planned", "skipped") for r in payload["cases"]) else 1

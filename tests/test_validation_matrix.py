@@ -69,6 +69,10 @@ def test_dry_run_plans_one_launch_per_case_and_skips_what_does_not_fit(tmp_path)
     nccl = next(c for c in plan["cases"] if c["case"]["run_id"].endswith("dense_fsdp4_muon_nccl"))
     assert nccl["env"] == {"RESEARCH_B200_PEER_COLLECTIVES": "0"}
     assert json.loads((tmp_path / "correctness17" / "matrix.json").read_text())["matrix"] == "correctness17"
+    subset = vm.run_matrix("correctness17", tmp_path / "sub", gpus=4, manifest=tmp_path / "m.json", dry_run=True,
+                           only=("moe_ep4", "cp4_muon_fused"))
+    assert sorted(c["case"]["run_id"].split("17_")[1] for c in subset["cases"]) == [
+        "dense_cp4_muon_fused", "moe_ep4_adamw_fused", "moe_ep4_adamw_nccl", "moe_ep4_dion_fused"]
     small = vm.run_matrix("correctness17", tmp_path / "two", gpus=2, manifest=tmp_path / "m.json", dry_run=True)
     assert all(c["status"] == "skipped" for c in small["cases"])
     with pytest.raises(ContractError, match="unknown validation matrix"):
