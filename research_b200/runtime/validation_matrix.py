@@ -165,7 +165,8 @@ def derive_config(case: MatrixCase, manifest: str | Path, output_dir: str | Path
     raw["run"] = {**raw.get("run", {}), "id": case.run_id, "output_dir": str(output_dir)}
     raw["data"]["train_manifest"] = str(manifest)
     raw["training"].update(seq_len=seq, global_batch_size=gb, gradient_accumulation_steps=1,
-                           target_tokens=gb * seq * case.steps)
+                           target_tokens=gb * seq * case.steps, log_every_steps=1)   # every step is a row: the gates
+    #                                                                                  and the steady medians read them
     raw.pop("evals", None)
     if case.profile_steps:
         raw["profiling"] = {"enabled": True, "trace_start_step": case.profile_steps[0],
@@ -279,16 +280,23 @@ def gate_run(run_dir: Path) -> dict[str, Any]:
     elif len(losses) >= 4 and not min(losses[len(losses) // 2:]) < losses[0]:
         problems.append(f"loss did not fall: first {losses[0]:.4f}, best of the second half "
                         f"{min(losses[len(losses) // 2:]):.4f}")
+    # Non-finite optimizer groups fail the run.  Groups without a gradient or an update (a router bias that the
+    # balance policy moves instead of the optimizer, an expert that no token reached) and dead experts are reported
+    # next to the verdict, as the reference's roll-ups report them, but do not fail it.
+    notes: list[str] = []
     opt = optimizer_health(summary, train[-8:])
     if opt:
-        for key in ("nonfinite_groups", "groups_with_zero_grad", "groups_with_zero_update"):
+        if opt.get("nonfinite_groups"):
+            problems.append(f"optimizer health: nonfinite_groups = {opt['nonfinite_groups']}")
+        for key in ("groups_with_zero_grad", "groups_with_zero_update"):
             if opt.get(key):
-                problems.append(f"optimizer health: {key} = {opt[key]}")
+                notes.append(f"{key} = {opt[key]}")
     rtr = router_health(summary, train[-8:])
     if rtr and rtr.get("dead_experts_count"):
-        problems.append(f"router health: {rtr['dead_experts_count']} dead experts")
+        notes.append(f"dead experts = {rtr['dead_experts_count']}")
     return {"run_id": run_dir.name, "rows": len(train), "first_loss": losses[0] if losses else None,
-            "final_loss": losses[-1] if losses else None, "problems": problems, "gate": not problems}
+            "final_loss": losses[-1] if losses else None, "problems": problems, "notes": notes,
+            "gate": not problems}
 
 
 PAIRS = (("fused", "nccl", "transport", 1.10), ("distributed", "duplicated", "muon_tp_mode", 1.25))
@@ -337,7 +345,8 @@ def format_matrix_analysis(payload: Mapping[str, Any]) -> str:
         first = "-" if r["first_loss"] is None else f"{r['first_loss']:.4f}"
         final = "-" if r["final_loss"] is None else f"{r['final_loss']:.4f}"
         lines.append(f"{r['run_id']:<58} {r['rows']:>4}  {first:<8}  {final:<8}  {ms(r['train_step_sec']):>7}  "
-                     f"{'ok' if r['gate'] else 'FAIL: ' + '; '.join(r['problems'])}")
+                     f"{'ok' if r['gate'] else 'FAIL: ' + '; '.join(r['problems'])}"
+                     f"{'  (' + '; '.join(r['notes']) + ')' if r.get('notes') else ''}")
     for p in payload["pairs"]:
         lines.append(f"pair {p['kind']}: {p['candidate']} / {p['reference']} = {p['step_time_ratio']:.3f} "
                      f"(envelope {p['envelope']:.2f}) {'ok' if p['gate'] else 'FAIL'}")

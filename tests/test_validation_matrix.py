@@ -141,6 +141,19 @@ def test_a_run_that_breaks_a_gate_is_named_with_its_problem(tmp_path, kwargs, ne
     assert "FAIL" in vm.format_matrix_analysis(payload)
 
 
+def test_groups_without_gradient_are_noted_not_failed(tmp_path):
+    groups = [{"group": "router_bias:adamw", "finite": True, "update_param_ratio": 0.0}]
+    run = _write_run(tmp_path / "c", "moe_fused", step_sec=0.1, groups=groups)
+    rows = [json.loads(line) for line in (run / "metrics" / "train.jsonl").read_text().splitlines()]
+    rows[-1].update(optimizer_groups_with_zero_grad=1, optimizer_groups_with_zero_update=1)
+    (run / "metrics" / "train.jsonl").write_text("".join(json.dumps(r) + "\n" for r in rows))
+    payload = vm.analyze_matrix(tmp_path / "c", work_dir=tmp_path / "w")
+    only = payload["runs"][0]
+    assert only["gate"] and payload["overall_gate"]
+    assert only["notes"] == ["groups_with_zero_grad = 1", "groups_with_zero_update = 1"]
+    assert "(groups_with_zero_grad = 1; groups_with_zero_update = 1)" in vm.format_matrix_analysis(payload)
+
+
 def test_slow_fused_path_breaks_the_pair_envelope(tmp_path):
     _write_run(tmp_path / "c", "x_fused", step_sec=0.130)
     _write_run(tmp_path / "c", "x_nccl", step_sec=0.100)
