@@ -224,8 +224,13 @@ def run_matrix(name: str, out_root: str | Path, *, gpus: int, manifest: str | Pa
     payload = {"schema_version": SCHEMA_VERSION, "matrix": name, "gpus": gpus, "cases": records}
     (runs_dir / "matrix.json").write_text(json.dumps(payload, indent=2, sort_keys=True, default=str))
     if not dry_run:
+        # the bundle carries what the analyzers read (metrics, events, diagnostics, summaries, traces, configs); the
+        # checkpoints stay in the run directories: gigabytes of weights would turn bundling into the longest step
+        def without_checkpoints(info: tarfile.TarInfo) -> tarfile.TarInfo | None:
+            return None if "/checkpoints/" in f"/{info.name}/" and not info.name.endswith("/checkpoints") else info
+
         with tarfile.open(out_root / f"{name}.tgz", "w:gz") as archive:
-            archive.add(runs_dir, arcname=name)
+            archive.add(runs_dir, arcname=name, filter=without_checkpoints)
     return payload
 
 

@@ -88,6 +88,12 @@ def test_run_matrix_records_exit_codes_and_bundles_the_runs(tmp_path):
 
     def runner(cmd, **kwargs):
         calls.append((cmd, kwargs["env"].get("RESEARCH_B200_PEER_COLLECTIVES")))
+        if len(calls) == 1:                                        # what a run leaves behind: metrics and a checkpoint
+            run = tmp_path / "correctness17" / "some_run"
+            (run / "checkpoints" / "000017" / "train").mkdir(parents=True)
+            (run / "checkpoints" / "000017" / "train" / "leaf").write_bytes(b"x" * 4096)
+            (run / "metrics").mkdir()
+            (run / "metrics" / "train.jsonl").write_text("{}\n")
         return Proc(1 if len(calls) == 2 else 0)
 
     out = vm.run_matrix("correctness17", tmp_path, gpus=4, manifest=tmp_path / "m.json", runner=runner)
@@ -95,7 +101,9 @@ def test_run_matrix_records_exit_codes_and_bundles_the_runs(tmp_path):
     assert [c["status"] for c in out["cases"]].count("failed") == 1 and out["cases"][1]["stderr_tail"] == "boom"
     assert calls[1][1] == "0"                                     # the NCCL case ran with the switch in its environment
     with tarfile.open(tmp_path / "correctness17.tgz") as archive:
-        assert "correctness17/matrix.json" in archive.getnames()
+        names = archive.getnames()
+    assert "correctness17/matrix.json" in names and "correctness17/some_run/metrics/train.jsonl" in names
+    assert not any("000017" in n for n in names)                  # checkpoints stay out of the bundle
 
 
 def test_analyzer_gates_runs_pairs_and_baseline(tmp_path):
