@@ -285,17 +285,12 @@ def _dispatch(args: argparse.Namespace) -> int:
             manifest = initialize_run(args.path)
             print(f"initialized run {manifest.run_id} at {manifest.run_dir}")
         elif args.run_command == "preflight":
-            from research_b200.runtime.preflight import run_preflight
+            from research_b200.runtime.preflight import (format_preflight_report, preflight_report_to_json,
+                                                         run_preflight)
 
             report = run_preflight(args.path)
             if _is_rank0():
-                if args.json:
-                    _print_json(report)
-                else:
-                    fs = report["first_step"]
-                    print(f"preflight ok: run {report['run_id']} | devices {report['devices']['count']} x "
-                          f"{report['devices']['kind']} | first-step loss {_fmt_metric(fs['loss'])} | "
-                          f"tps {_fmt_tps(fs['train_tokens_per_sec'])} | mfu {_fmt_percent(fs['mfu'])}")
+                print(preflight_report_to_json(report) if args.json else format_preflight_report(report))
         elif args.run_command == "train":
             from research_b200.runtime.training import run_training
 

@@ -69,9 +69,13 @@ def kernel_plan(spec: RunSpec, *, device: torch.device | None = None) -> dict[st
                     "selected": bool(active and item["built"]),
                     "fallback": None if (active and item["built"]) else "pytorch",
                     "fallback_reason": reason if not active else (None if item["built"] else "symbol not built")})
+    selected = [op["op"] for op in ops if op["selected"]]
+    unavailable = [op["op"] for op in ops if not op["built"]]
+    fallback = [op["op"] for op in ops if not op["selected"] and op["built"]]
     return {"schema_version": 1, "arch": "sm_100a", "enabled": True, "strict": spec.kernels.strict,
             "compile": spec.kernels.compile, "library": str(native.lib_path()), "library_present": native.available(),
-            "active": active, "ops": ops}
+            "active": active, "device_kind": device.type, "active_count": len(selected),
+            "fallback_count": len(fallback), "disabled_count": 0, "unavailable_count": len(unavailable), "ops": ops}
 
 
 def require_kernel_plan_supported(plan: dict[str, Any], spec: RunSpec) -> None:

@@ -260,6 +260,10 @@ class Trainer:
             if path.is_file():
                 token_bytes = np.fromfile(path, dtype="<u2")
         done = 0
+        token_start = token_end = None
+        examples = target_tokens = 0
+        doc_ids: list[int] = []
+        document_aware = True
         self.result.model.eval()
         try:
             for _ in range(num_batches):
@@ -268,6 +272,20 @@ class Trainer:
                 except StopIteration:
                     break
                 state = pb.state
+                prov = getattr(pb, "provenance", None)
+                if prov is not None:
+                    token_start = prov.token_start if token_start is None else token_start
+                    token_end = prov.token_end
+                    examples += prov.examples
+                    target_tokens += prov.target_tokens
+                    if prov.row_doc_ids is None:
+                        document_aware = False
+                    else:
+                        doc_ids.extend(prov.row_doc_ids)
+                else:
+                    document_aware = False
+                    examples += int(pb.batch.input_ids.shape[0])
+                    target_tokens += int(pb.batch.input_ids.shape[0] * pb.batch.input_ids.shape[1])
                 m = self.eval_step_fn.run(pb.batch)
                 loss_sum += m.loss_sum
                 token_count += m.token_count
@@ -282,7 +300,11 @@ class Trainer:
         if done == 0:
             raise ContractError("validation split has no full batch")
         out = {"loss_sum": loss_sum, "token_count": token_count, "loss": loss_sum / max(token_count, 1.0),
-               "num_batches": done}
+               "num_batches": done, "token_start": token_start, "token_end": token_end, "examples": examples,
+               "target_tokens": target_tokens, "document_aware": document_aware,
+               "documents_touched": len(set(doc_ids)) if document_aware else None,
+               "document_min": min(doc_ids) if document_aware and doc_ids else None,
+               "document_max": max(doc_ids) if document_aware and doc_ids else None}
         if byte_count > 0:
             out["byte_count"] = byte_count
             out["bpb"] = loss_sum / (math.log(2.0) * byte_count)

@@ -30,9 +30,10 @@ from research_b200.data.pipeline import data_pipeline_state_to_dict
 from research_b200.errors import ContractError, JaxtitanError
 from research_b200.optim.build import optimizer_policy_summary
 from research_b200.runtime.checkpoint_index import load_checkpoint_index, record_checkpoint
-from research_b200.runtime.diagnostics import (ARTIFACT_WRITER, EXECUTION_MODE, METRICS_SCOPE, PhaseTimer,
+from research_b200.runtime.diagnostics import (ARTIFACT_WRITER, METRICS_SCOPE, PhaseTimer,
                                                build_runtime_diagnostics, device_kind, device_telemetry,
-                                               enrich_train_metrics, training_diagnostics_summary)
+                                               enrich_eval_metrics, enrich_train_metrics, runtime_execution_mode,
+                                               training_diagnostics_summary)
 from research_b200.runtime.profiling import ProfilingManager
 from research_b200.runtime.resume import (build_resume_compat, checkpoint_metadata, validate_resume_compat,
                                           validate_resume_metadata)
@@ -206,10 +207,12 @@ def run_validation_eval(trainer: Trainer, spec: RunSpec, writer, step: int, toke
                              "error_type": type(exc).__name__, "error_message": str(exc)})
         raise
     eval_sec = time.perf_counter() - start
-    row = {"schema_version": 1, "name": ev.name, "step": step, "tokens_seen": tokens_seen,
+    row = {"schema_version": 1, "name": ev.name, "eval_name": ev.name, "step": step, "tokens_seen": tokens_seen,
            "loss_sum": result["loss_sum"], "token_count": int(result["token_count"]), "loss": result["loss"],
-           "bpb": result.get("bpb"), "num_batches": result["num_batches"], "eval_sec": eval_sec,
-           "eval_tokens_per_sec": None if eval_sec <= 0 else result["token_count"] / eval_sec}
+           "bpb": result.get("bpb"), "num_batches": result["num_batches"]}
+    row.update({k: result.get(k) for k in ("token_start", "token_end", "examples", "target_tokens", "document_aware",
+                                           "documents_touched", "document_min", "document_max")})
+    row = enrich_eval_metrics(row, eval_sec=eval_sec)
     writer.append_eval_metrics(row)
     writer.append_event({"schema_version": 1, "type": "eval_completed", "run_id": spec.run_id,
                          "created_at": utc_now(), "step": step, "name": ev.name, "loss": row["loss"]})
@@ -267,7 +270,7 @@ def run_training(config_path: str | Path, *, resume: bool = False, progress: Pro
         initialize_run(config_path)
     if world > 1:
         torch.distributed.barrier()
-    writer = build_artifact_writer(spec, run_dir, is_writer=rank == 0)
+    writer = build_artifact_writer(spec, run_dir, is_writer=rank == 0, resume=resume)
     progress("start", {"spec": spec, "config_path": str(config_path), "resume": resume})
     writer.append_event({"schema_version": 1, "type": "training_started", "run_id": spec.run_id,
                          "created_at": utc_now(), "resume": resume, "config_path": config_path.as_posix(),
@@ -428,7 +431,7 @@ def _run_initialized(spec: RunSpec, config_path: Path, writer, resume: bool, pro
                                 compat, progress)
     profiler.finish()
     service.close()
-    diag = training_diagnostics_summary(rows)
+    diag = training_diagnostics_summary(rows)       # wall time and device fields are set on the summary below
     from research_b200.optim.diagnostics import HEALTH_KEYS
 
     # group norms exist on the steps that computed diagnostics (the logged ones): report the newest of them
@@ -451,7 +454,7 @@ def _run_initialized(spec: RunSpec, config_path: Path, writer, resume: bool, pro
         best_checkpoint_path=None if best is None else best.checkpoint_path.as_posix(),
         total_wall_sec=time.perf_counter() - wall_start, device_kind=device_kind(trainer.device),
         device_count=trainer.mesh.world_size, runtime_diagnostics_path="diagnostics/runtime.json",
-        execution_mode=EXECUTION_MODE, metrics_scope=METRICS_SCOPE, artifact_writer=ARTIFACT_WRITER,
+        execution_mode=runtime_execution_mode(spec), metrics_scope=METRICS_SCOPE, artifact_writer=ARTIFACT_WRITER,
         model_remat=spec.model.remat, data_axis_size=data_axis, global_batch_size=t.global_batch_size,
         per_device_batch_size=t.global_batch_size // data_axis,
         gradient_accumulation_steps=t.gradient_accumulation_steps,

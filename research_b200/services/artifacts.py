@@ -144,13 +144,15 @@ def initialize_run(config_path: str | Path) -> RunManifest:
     return manifest
 
 
-def build_artifact_writer(spec: RunSpec, run_dir: str | Path, *, is_writer: bool = True) -> LocalArtifactWriter:
-    """Local writer, mirrored to W&B when ``[artifacts].wandb_enabled`` (reference: services/wandb.py:242-273)."""
+def build_artifact_writer(spec: RunSpec, run_dir: str | Path, *, is_writer: bool = True,
+                          resume: bool = False) -> LocalArtifactWriter:
+    """Local writer, mirrored to W&B when ``[artifacts].wandb_enabled`` (reference: services/wandb.py:242-273).
+    With ``resume`` the mirror continues the W&B run named in ``diagnostics/wandb.json``."""
 
     if not is_writer:
         return NullArtifactWriter(run_dir)
     if spec.artifacts.wandb_enabled:
         from research_b200.services.wandb import WandbMirroredWriter
 
-        return WandbMirroredWriter(spec, run_dir)
+        return WandbMirroredWriter(spec, run_dir, resume=resume)
     return LocalArtifactWriter(run_dir)

@@ -1,0 +1,204 @@
+"""Runtime diagnostics payload, telemetry through a fake NVML, metric enrichment and the preflight report."""
+
+import json
+import types
+from pathlib import Path
+
+import pytest
+import torch
+
+from research_b200.config import run_spec_from_mapping
+from research_b200.runtime import diagnostics as D
+from tests.helpers import tiny_dataset, tiny_raw_config, write_toml
+
+
+class FakeNvml:
+    """Three boards; the second one cannot report power, the third one cannot report utilisation."""
+
+    NVML_TEMPERATURE_GPU = 0
+
+    def __init__(self, fail_init=False):
+        self.fail_init = fail_init
+        self.handles = []
+
+    def nvmlInit(self):
+        if self.fail_init:
+            raise RuntimeError("no driver")
+
+    def nvmlDeviceGetHandleByIndex(self, i):
+        self.handles.append(i)
+        return i
+
+    def nvmlDeviceGetMemoryInfo(self, h):
+        return types.SimpleNamespace(used=(h + 1) * 10, total=100)
+
+    def nvmlDeviceGetUtilizationRates(self, h):
+        if h == 2:
+            raise RuntimeError("not supported")
+        return types.SimpleNamespace(gpu=50.0 + 20 * h, memory=10.0 * (h + 1))
+
+    def nvmlDeviceGetPowerUsage(self, h):
+        if h == 1:
+            raise RuntimeError("not supported")
+        return 400_000 + 100_000 * h
+
+    def nvmlDeviceGetTemperature(self, h, kind):
+        return 40 + 5 * h
+
+
+def _spec(**kw):
+    return run_spec_from_mapping(tiny_raw_config(Path("m.json"), **kw))
+
+
+def test_nvml_sampling_sums_memory_and_power_averages_utilisation_and_takes_the_hottest_board():
+    nvml = FakeNvml()
+    out = D.sample_nvml([0, 1, 2], provider=nvml)
+    assert nvml.handles == [0, 1, 2]
+    assert out["gpu_memory_used_bytes"] == 60 and out["gpu_memory_total_bytes"] == 300
+    assert out["gpu_utilization_pct"] == pytest.approx(60.0) and out["gpu_memory_utilization_pct"] == pytest.approx(15.0)
+    assert out["gpu_power_w"] == pytest.approx(400.0 + 600.0) and out["gpu_temperature_c"] == 50.0
+
+
+def test_nvml_sampling_degrades_to_nulls():
+    empty = {k: None for k in D.TELEMETRY_KEYS[3:]}
+    assert D.sample_nvml([0], provider=None) == empty
+    assert D.sample_nvml([], provider=FakeNvml()) == empty
+    assert D.sample_nvml([0], provider=FakeNvml(fail_init=True)) == empty
+    cpu = D.sample_device_telemetry(torch.device("cpu"))
+    assert set(cpu) == set(D.TELEMETRY_KEYS) and all(v is None for v in cpu.values())
+    seen = D.sample_device_telemetry(torch.device("cpu"), nvml_provider=FakeNvml())
+    assert seen["gpu_power_w"] == pytest.approx(400.0) and seen["device_memory_used_bytes"] is None
+
+
+def test_execution_mode_names_the_state_mode_and_the_activation_axes():
+    assert D.runtime_execution_mode(_spec()) == "replicated_data_parallel"
+    tp = _spec(mesh={"fsdp": 2, "tp": 2}, parallelism={"mode": "fsdp", "tensor_parallel": True})
+    assert D.runtime_execution_mode(tp) == "fsdp+tp"
+    cp = _spec(mesh={"data": 1, "cp": 2}, parallelism={"mode": "ddp", "context_parallel": True})
+    assert D.runtime_execution_mode(cp) == "replicated_data_parallel+cp"
+    ep = _spec(kind="trinity", mesh={"fsdp": 1, "ep": 2, "tp": 2},
+               parallelism={"mode": "zero2", "expert_parallel": True, "tensor_parallel": True})
+    assert D.runtime_execution_mode(ep) == "zero2+ep+tp"
+
+
+def test_phase_timer_accumulates_and_resets():
+    t = D.PhaseTimer()
+    with t.phase("a"):
+        pass
+    with t.phase("a"):
+        pass
+    t.add("b", 1.5)
+    t.add("b", 0.5)
+    assert t.get("b") == 2.0 and t.get("a") >= 0.0 and t.get("missing") == 0.0 and set(t.to_dict()) == {"a", "b"}
+    assert t.total_sec() >= 0.0
+    out = t.reset()
+    assert out["b"] == 2.0 and t.to_dict() == {}
+    with pytest.raises(ValueError):
+        with t.phase("boom"):
+            raise ValueError("x")
+    assert "boom" in t.to_dict()                       # the time of a failed phase is still recorded
+
+
+RUNTIME = {"performance": {"flops_per_token": 1000, "flops_per_token_exact": 800, "peak_flops_per_device": 1e6,
+                           "peak_flops_total": 2e6, "device_kind": "B200", "device_count": 2},
+           "parallelism": {"mode": "fsdp", "execution_mode": "fsdp+tp"},
+           "device_telemetry": {"gpu_power_w": 900.0}}
+
+
+def test_train_row_enrichment_rates_and_mfu():
+    row = {"step": 3, "target_tokens": 400, "examples": 4, "loss": 2.0}
+    out = D.enrich_train_metrics(row, timings={"data": 0.5, "train_step": 1.5, "metrics_sync": 0.5,
+                                               "train_loop_step": 4.0}, runtime=RUNTIME)
+    assert out["train_step_sec"] == 2.0 and out["step_sec"] == 4.0 and out["data_sec"] == 0.5
+    assert out["train_tokens_per_sec"] == 200.0 and out["tokens_per_sec"] == 100.0 and out["examples_per_sec"] == 1.0
+    assert out["flops_per_step"] == 400_000 and out["flops_per_sec"] == 200_000.0
+    assert out["mfu"] == pytest.approx(10.0) and out["mfu_exact"] == pytest.approx(8.0)
+    assert out["execution_mode"] == "fsdp+tp" and out["parallelism_mode"] == "fsdp"
+    assert out["gpu_power_w"] == 900.0 and out["gpu_temperature_c"] is None and out["loss"] == 2.0
+    # the reference's *_sec names are taken as well; a fresh telemetry sample wins over the one in the payload
+    same = D.enrich_train_metrics(row, timings={"data_sec": 0.5, "train_dispatch_sec": 1.5, "metrics_sync_sec": 0.5,
+                                                "step_sec": 4.0}, runtime=RUNTIME,
+                                  telemetry={"gpu_power_w": 500.0})
+    assert same["train_tokens_per_sec"] == 200.0 and same["step_sec"] == 4.0 and same["gpu_power_w"] == 500.0
+    idle = D.enrich_train_metrics(row, timings={}, runtime=RUNTIME)
+    assert idle["train_tokens_per_sec"] is None and idle["mfu"] is None and idle["flops_per_sec"] is None
+    no_peak = dict(RUNTIME, performance=dict(RUNTIME["performance"], peak_flops_total=None))
+    assert D.enrich_train_metrics(row, timings={"train_step": 1.0}, runtime=no_peak)["mfu"] is None
+
+
+def test_eval_row_enrichment_and_run_summary():
+    ev = D.enrich_eval_metrics({"loss": 1.0, "target_tokens": 300, "examples": 6}, eval_sec=2.0)
+    assert ev["eval_tokens_per_sec"] == 150.0 and ev["eval_examples_per_sec"] == 3.0 and ev["eval_sec"] == 2.0
+    assert D.enrich_eval_metrics({"target_tokens": 1, "examples": 1}, eval_sec=0.0)["eval_tokens_per_sec"] is None
+    rows = [{"train_tokens_per_sec": 10.0, "mfu": 1.0, "batch_het": None},
+            {"train_tokens_per_sec": 30.0, "mfu": None, "batch_het": 0.5},
+            {"train_tokens_per_sec": 50.0, "mfu": 3.0, "batch_het": True}]
+    s = D.training_diagnostics_summary(rows, total_wall_sec=9.0, runtime=RUNTIME)
+    assert s["avg_train_tokens_per_sec"] == 30.0 and s["steady_train_tokens_per_sec"] == 40.0
+    assert s["final_train_tokens_per_sec"] == 50.0 and s["avg_mfu"] == 2.0 and s["final_mfu"] == 3.0
+    assert s["avg_batch_het"] == 0.5 and s["final_batch_het"] is None           # a boolean is not a number
+    assert s["total_wall_sec"] == 9.0 and s["device_kind"] == "B200" and s["execution_mode"] == "fsdp+tp"
+    assert s["runtime_diagnostics_path"] == "diagnostics/runtime.json"
+    one = D.training_diagnostics_summary(rows[:1])
+    assert one["steady_train_tokens_per_sec"] is None and "total_wall_sec" not in one
+    none = D.training_diagnostics_summary([])
+    assert none["avg_train_tokens_per_sec"] is None and none["final_mfu"] is None
+
+
+def test_batch_and_compile_contract_arithmetic():
+    spec = _spec(batch=8, seq_len=16, accum=3)
+    b = D.batch_summary(spec, 4)
+    assert b == {"global_batch_size": 8, "micro_global_batch_size": 8, "effective_global_batch_size": 24,
+                 "gradient_accumulation_steps": 3, "per_device_batch_size": 2, "micro_tokens_per_step": 128,
+                 "effective_tokens_per_step": 384, "global_tokens_per_step": 384, "per_device_tokens_per_step": 96}
+    mesh = types.SimpleNamespace(size=lambda a: {"data": 2, "fsdp": 2}.get(a, 1))
+    c = D.compile_contract_summary(spec, mesh)
+    assert c["train"]["expected_batch_shape"] == [3, 8, 16] and c["eval"]["expected_batch_shape"] == [8, 16]
+    assert c["train"]["donate_state"] is True and c["eval"]["donate_state"] is False
+    assert c["train"]["input_shardings"]["input_ids"] == {"rows": ["data", "fsdp"], "sequence": []}
+    assert D.moe_balance_payload(spec) == {"name": "none"}
+    moe = D.moe_balance_payload(_spec(kind="trinity"))
+    assert moe["name"] == "smebu" and set(moe) == {"name", "load_lr", "momentum", "clamp", "sequence_aux_loss_weight"}
+
+
+def test_runtime_payload_and_preflight_report_of_a_tiny_run(tmp_path):
+    from research_b200.runtime.preflight import format_preflight_report, preflight_report_to_json, run_preflight
+
+    manifest = tiny_dataset(tmp_path)
+    raw = tiny_raw_config(manifest, kind="trinity", run_id="pf", output_dir=(tmp_path / "runs").as_posix(), evals=True,
+                          accum=2, batch=4)
+    report = run_preflight(write_toml(raw, tmp_path / "pf.toml"))
+    assert not (tmp_path / "runs" / "pf").exists()                      # a preflight writes nothing
+    assert report["status"] == "ok" and report["training"]["compile"] == "passed"
+    tr = report["training"]
+    assert tr["batch_tokens"] == 4 * 32 * 2 and tr["estimated_steps"] == 4 and tr["per_device_batch_size"] == 4
+    assert tr["first_step_loss"] == pytest.approx(report["first_step"]["loss"])
+    assert tr["first_step_moe_aux_loss"] is not None and tr["first_step_router_max_vio"] is not None
+    fb = report["data"]["first_batch"]
+    assert fb["target_tokens"] == 256 and fb["examples"] == 8 and fb["document_aware"] and fb["documents_touched"] >= 1
+    assert report["data"]["train_split_tokens"] == report["data"]["train_split_end"] - report["data"]["train_split_start"]
+    ev = report["eval"]
+    assert ev["num_batches"] == 2 and ev["split"] == "val" and ev["target_tokens"] == 2 * 4 * 32 and ev["loss"] > 0
+    diag = report["diagnostics"]
+    for key in ("python", "packages", "runtime", "mesh", "model", "optimizer", "performance", "compile", "parallelism",
+                "profiling", "kernels", "sharding", "data_pipeline", "device_telemetry"):
+        assert key in diag, key
+    assert diag["model"]["moe_balance"]["name"] == "smebu" and diag["model"]["parameter_leaves"] > 0
+    assert diag["mesh"]["effective_tokens_per_step"] == 256 and diag["mesh"]["global_mesh_size"] == 1
+    par = diag["parallelism"]
+    assert par["execution_mode"] == "replicated_data_parallel" and par["tensor_parallel_policy"]["lm_head"] == "replicated"
+    assert par["expert_parallel_policy"]["num_experts"] == 4 and par["expert_parallel_policy"]["enabled"] is False
+    assert par["batch"]["per_device_batch_size"] == 4 and par["host_artifacts"]["writer"] == "single_host"
+    kern = report["kernels"]
+    assert kern["active_count"] == 0 and kern["fallback_count"] + kern["unavailable_count"] == len(kern["ops"])
+    obs = report["observed_sharding"]
+    assert obs["first_train_batch"]["input_ids"]["shape"] == [4, 32] and obs["train_state"]["mode"] == "ddp"
+    text = format_preflight_report(report)
+    for head in ("preflight: ok", "run: pf", "devices:", "mesh:", "parallelism:", "train data:", "model: trinity",
+                 "optimizer: adamw", "training: estimated_steps=4", "first step: loss=", "compile contract:",
+                 "profiling:", "kernels:", "eval: name=validation"):
+        assert head in text, head
+    assert json.loads(preflight_report_to_json(report))["run_id"] == "pf"
+    no_eval = tiny_raw_config(manifest, run_id="pf2", output_dir=(tmp_path / "runs").as_posix())
+    second = run_preflight(write_toml(no_eval, tmp_path / "pf2.toml"))
+    assert second["eval"] is None and "eval: skipped" in format_preflight_report(second)

@@ -120,8 +120,12 @@ class FakeWandb(types.ModuleType):
 
     def _call(self, what, **kw):
         self.calls.append((what, kw))
-        if self.fail_on == what:
+        hit = self.fail_on(what, kw) if callable(self.fail_on) else self.fail_on == what
+        if hit:
             raise RuntimeError(f"fake wandb {what} failure")
+
+    def Table(self, columns, data):
+        return {"columns": columns, "data": data}
 
     def init(self, **kw):
         self._call("init", **kw)
@@ -164,16 +168,59 @@ def test_wandb_mirror_logs_namespaced_metrics_after_the_local_files(tmp_path, mo
     assert fake.run.summary["steps"] == summary.steps == 3
     meta = json.loads((tmp_path / "runs" / "wb" / "diagnostics" / "wandb.json").read_text())
     assert meta["enabled"] and meta["run_id"] == init["id"] and meta["project"] == "proj"
-    ns = namespaced_metrics({"loss": 1.0, "router_max_vio": 0.1, "mfu": 0.4, "flag": True, "name": "x"})
-    assert ns == {"train/loss": 1.0, "router/router_max_vio": 0.1, "perf/mfu": 0.4}
+    assert meta["wandb_run_id"] == init["id"] and meta["resume"] == "allow" and meta["tags"] == ["a", "b"]
+    ns = namespaced_metrics({"loss": 1.0, "router_max_vio": 0.1, "mfu": 0.4, "flag": True, "name": "x", "step": 3,
+                             "bad": float("nan"), "worse": float("inf"), "optimizer_groups": [1], "gpu_power_w": 700.0,
+                             "tokens_seen": 10, "smebu_bias_norm": 0.5, "optimizer_update_norm_max": 2.0})
+    assert ns == {"train/loss": 1.0, "router/router_max_vio": 0.1, "perf/mfu": 0.4, "train/flag": True,
+                  "perf/gpu_power_w": 700.0, "data/tokens_seen": 10, "router/smebu_bias_norm": 0.5,
+                  "optimizer/optimizer_update_norm_max": 2.0}
+    assert namespaced_metrics({"loss": 2.0, "eval_sec": 1.0}, "eval") == {"eval/loss": 2.0, "eval/eval_sec": 1.0}
+    # lifecycle events become markers, the runtime diagnostics and the summary land in the W&B summary
+    markers = [k for c in fake.calls if c[0] == "log" for k in c[1]["payload"] if k.startswith("event/") and
+               k.count("/") == 1]
+    assert markers[0] == "event/training_started" and markers[-1] == "event/training_completed"
+    assert "event/checkpoint_saved" in markers
+    assert fake.run.summary["diagnostics/device_count"] == 1 and fake.run.summary["diagnostics/flops_per_token"] > 0
+    assert fake.run.summary["final/final_loss"] == pytest.approx(summary.final_loss)
+    tables = [c[1]["payload"] for c in fake.calls if c[0] == "log" and "final/optimizer_groups" in c[1]["payload"]]
+    assert len(tables) == 1 and "group" in " ".join(tables[0]["final/optimizer_groups"]["columns"])
+
+
+def test_wandb_resume_continues_the_recorded_run_and_needs_its_metadata(tmp_path, monkeypatch):
+    from research_b200.runtime.training import run_training
+
+    fake = FakeWandb()
+    monkeypatch.setitem(sys.modules, "wandb", fake)
+    config = _wandb_config(tmp_path, "wbres")
+    run_training(config)
+    first_id = fake.calls[0][1]["id"]
+    raw = config.read_text().replace(f"target_tokens = {32 * 4 * 3}", f"target_tokens = {32 * 4 * 5}")
+    assert raw != config.read_text()
+    config.write_text(raw)
+    again = FakeWandb()
+    monkeypatch.setitem(sys.modules, "wandb", again)
+    summary = run_training(config, resume=True)
+    init = again.calls[0][1]
+    assert summary.steps == 5 and init["resume"] == "must" and init["id"] == first_id
+    (tmp_path / "runs" / "wbres" / "diagnostics" / "wandb.json").unlink()
+    monkeypatch.setitem(sys.modules, "wandb", FakeWandb())
+    with pytest.raises(ContractError, match="diagnostics/wandb.json is missing"):
+        run_training(config, resume=True)
+    events = [json.loads(line) for line in (tmp_path / "runs" / "wbres" / "events.jsonl").read_text().splitlines()]
+    assert events[-1]["type"] == "wandb_failed" and events[-1]["operation"] == "init"
 
 
 def test_wandb_failure_is_an_event_and_aborts_with_local_files_intact(tmp_path, monkeypatch):
     from research_b200.runtime.training import run_training
 
-    monkeypatch.setitem(sys.modules, "wandb", FakeWandb(fail_on="log"))
+    fake = FakeWandb(fail_on=lambda what, kw: what == "log" and "train/loss" in kw["payload"])
+    monkeypatch.setitem(sys.modules, "wandb", fake)
     with pytest.raises(ContractError, match="wandb log_train failed"):
         run_training(_wandb_config(tmp_path, "wbfail"))
+    after = [c for c in fake.calls[[c[0] == "log" and "train/loss" in c[1]["payload"] for c in fake.calls].index(True) + 1:]
+             if c[0] == "log"]
+    assert after == []                                                      # the mirror is off after its first failure
     run_dir = tmp_path / "runs" / "wbfail"
     events = [json.loads(line) for line in (run_dir / "events.jsonl").read_text().splitlines()]
     failed = next(e for e in events if e["type"] == "wandb_failed")
