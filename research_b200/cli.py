@@ -298,17 +298,10 @@ def _dispatch(args: argparse.Namespace) -> int:
                 _prepare_fresh_train_run(args.path, args.overwrite)
             run_training(args.path, resume=args.resume, progress=training_progress_printer())
         elif args.run_command == "inspect":
-            from research_b200.runtime.inspect import inspect_run
+            from research_b200.runtime.inspect import format_run_inspection, inspect_run, run_inspection_to_json
 
             report = inspect_run(args.run_dir)
-            if args.json:
-                _print_json(report)
-            else:
-                prog = report["progress"] or {}
-                print(f"run {report['run_id']}: status={report['status']} step={prog.get('step')} "
-                      f"tokens={_fmt_int(prog.get('tokens_seen'))} loss={_fmt_metric(prog.get('loss'))} "
-                      f"checkpoints={len(report['checkpoints']['records'])} "
-                      f"latest={report['checkpoints']['latest_step']} best={report['checkpoints']['best_eval_step']}")
+            print(run_inspection_to_json(report) if args.json else format_run_inspection(report))
     elif args.command == "eval":
         from research_b200.runtime.checkpoint_eval import evaluate_checkpoint
 

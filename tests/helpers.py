@@ -97,14 +97,22 @@ def write_toml(raw: dict, path: Path) -> Path:
     return path
 
 
+GLOO_COLLECTIVE_TIMEOUT_S = 180
+GLOO_RUN_DEADLINE_S = 420
+
+
 def _worker(rank: int, world: int, port: int, fn, args, out_dir: str):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), LOCAL_WORLD_SIZE=str(world),
                       MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.set_num_threads(1)
     try:
+        import datetime
+
         import torch.distributed as dist
 
-        dist.init_process_group("gloo", rank=rank, world_size=world)
+        # a short collective timeout: a rank that waits for a peer that never comes fails in minutes, not in half an hour
+        dist.init_process_group("gloo", rank=rank, world_size=world,
+                                timeout=datetime.timedelta(seconds=GLOO_COLLECTIVE_TIMEOUT_S))
         result = fn(rank, world, *args)
         torch.save(result, os.path.join(out_dir, f"rank{rank}.pt"))
         dist.barrier()
@@ -115,8 +123,8 @@ def _worker(rank: int, world: int, port: int, fn, args, out_dir: str):
         raise
 
 
-def run_gloo(world: int, fn, *args):
-    """Run ``fn(rank, world, *args)`` in ``world`` CPU processes over gloo; returns the per-rank results."""
+def _run_gloo_once(world: int, fn, args):
+    import time
 
     import torch.multiprocessing as mp
 
@@ -126,18 +134,39 @@ def run_gloo(world: int, fn, *args):
     procs = [ctx.Process(target=_worker, args=(r, world, port, fn, args, out_dir)) for r in range(world)]
     for p in procs:
         p.start()
+    deadline = time.monotonic() + GLOO_RUN_DEADLINE_S
     for p in procs:
-        p.join(timeout=600)
+        p.join(timeout=max(deadline - time.monotonic(), 0.0))
+    stuck = [r for r, p in enumerate(procs) if p.is_alive()]
+    for r in stuck:
+        procs[r].terminate()                      # our own children, by handle
+        procs[r].join(timeout=10)
     errors = []
     for r, p in enumerate(procs):
         err = Path(out_dir) / f"rank{r}.err"
         if err.exists():
             errors.append(f"rank {r}:\n{err.read_text()}")
+        elif r in stuck:
+            errors.append(f"rank {r} was still running after {GLOO_RUN_DEADLINE_S} s")
         elif p.exitcode != 0:
             errors.append(f"rank {r} exited with code {p.exitcode}")
     if errors:
+        return None, errors, bool(stuck) or all("Timed out" in e or "timed out" in e for e in errors)
+    return [torch.load(os.path.join(out_dir, f"rank{r}.pt"), weights_only=False) for r in range(world)], [], False
+
+
+def run_gloo(world: int, fn, *args):
+    """Run ``fn(rank, world, *args)`` in ``world`` CPU processes over gloo; returns the per-rank results.
+
+    A run in which the ranks only timed out on one another (no rank raised anything else) is tried once more: on a
+    loaded host the gloo rendezvous of a fresh group occasionally loses a connection."""
+
+    results, errors, only_timeouts = _run_gloo_once(world, fn, args)
+    if errors and only_timeouts:
+        results, errors, _ = _run_gloo_once(world, fn, args)
+    if errors:
         raise AssertionError("\n".join(errors))
-    return [torch.load(os.path.join(out_dir, f"rank{r}.pt"), weights_only=False) for r in range(world)]
+    return results
 
 
 def train_and_collect(rank: int, world: int, raw: dict, steps: int):

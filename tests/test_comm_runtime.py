@@ -26,8 +26,8 @@ def _broker_worker(rank: int, world: int, tmp: str) -> None:
     fds = exchange_descriptors(dist.group.WORLD, fd, tag="test")
     assert len(fds) == world
     for r, got in enumerate(fds):
-        os.lseek(got, 0, os.SEEK_SET)
-        assert os.read(got, 64).decode() == f"hello from rank {r}"
+        # a passed descriptor shares its file offset with every process that holds it: read at an explicit position
+        assert os.pread(got, 64, 0).decode() == f"hello from rank {r}"
         if r != rank:
             os.close(got)
     os.close(fd)

@@ -202,3 +202,54 @@ def test_runtime_payload_and_preflight_report_of_a_tiny_run(tmp_path):
     no_eval = tiny_raw_config(manifest, run_id="pf2", output_dir=(tmp_path / "runs").as_posix())
     second = run_preflight(write_toml(no_eval, tmp_path / "pf2.toml"))
     assert second["eval"] is None and "eval: skipped" in format_preflight_report(second)
+
+
+def test_run_inspection_sections_formatter_and_missing_checkpoint(tmp_path):
+    import shutil
+
+    from research_b200.errors import ContractError
+    from research_b200.runtime.inspect import (format_run_inspection, inspect_run, profiling_summary,
+                                               run_inspection_to_json, wandb_summary)
+    from research_b200.runtime.training import run_training
+
+    manifest = tiny_dataset(tmp_path)
+    raw = tiny_raw_config(manifest, kind="trinity", run_id="ins", output_dir=(tmp_path / "runs").as_posix(), evals=True,
+                          steps=4, checkpoint_every=2)
+    run_training(write_toml(raw, tmp_path / "ins.toml"))
+    run_dir = tmp_path / "runs" / "ins"
+    report = inspect_run(run_dir)
+    assert report["status"] == "completed" and report["final"]["step"] == 4 and report["final"]["eval_loss"] > 0
+    assert [c["step"] for c in report["checkpoints"]] == [2, 4] and all(c["exists"] for c in report["checkpoints"])
+    assert report["latest_checkpoint"]["step"] == 4 and report["best_checkpoint"]["eval_loss"] is not None
+    assert report["checkpoint_index"]["latest_step"] == 4
+    diag = report["diagnostics"]
+    assert diag["path"] == "diagnostics/runtime.json" and diag["backend"] == "cpu" and diag["device_count"] == 1
+    assert diag["parallelism"]["batch"]["global_batch_size"] == 4 and diag["data_pipeline"]["order"] == "document_buffer"
+    assert report["kernels"]["active_count"] == 0 and report["kernels"]["unavailable"] is not None
+    assert report["wandb"] is None and report["profiling"]["enabled"] is False
+    assert len(report["recent_train_metrics"]) == 4 and len(report["recent_eval_metrics"]) >= 2
+    assert report["router_health"]["layer_count"] == 1 and report["optimizer_health"]["group_count"] > 0
+    text = format_run_inspection(report)
+    for head in ("run: ins", "status: completed", "final: step=4", "validation: loss=", "runtime: backend=cpu",
+                 "parallelism: mode=replicated_data_parallel", "data pipeline: backend=blackwell_native", "kernels:",
+                 "router health: layers=1", "optimizer health: groups=", "latest checkpoint: step=4",
+                 "best checkpoint: step=", "checkpoints:", "  step=2 "):
+        assert head in text, head
+    assert "wandb:" not in text and "profiling:" not in text
+    assert json.loads(run_inspection_to_json(report))["run_id"] == "ins"
+    # sections that come from optional files
+    wb = wandb_summary({"enabled": True, "wandb_run_id": "ins-abc", "project": "p", "url": None}, None)
+    assert wb["wandb_run_id"] == "ins-abc" and wb["entity"] is None
+    assert wandb_summary(None, {"wandb": {"project": "q"}})["project"] == "q" and wandb_summary(None, {}) is None
+    prof = profiling_summary({"enabled": True, "status": "completed", "trace_files": ["profiles/a.trace.json.gz"],
+                              "traced_step_range": {"start": 3, "end": 4}}, None)
+    assert prof["perfetto_trace_available"] and prof["trace_step_range"] == {"start": 3, "end": 4}
+    configured = profiling_summary(None, {"profiling": {"enabled": True, "trace_start_step": 3, "trace_steps": 2}})
+    assert configured["status"] == "configured" and configured["trace_step_range"] is None
+    # a run that never finished still inspects; a retained checkpoint that vanished is an error
+    (run_dir / "summaries" / "final.json").unlink()
+    partial = inspect_run(run_dir)
+    assert partial["final"] is None and "progress: step=4" in format_run_inspection(partial)
+    shutil.rmtree(run_dir / report["latest_checkpoint"]["checkpoint_path"])
+    with pytest.raises(ContractError, match="retained path does not exist"):
+        inspect_run(run_dir)

@@ -209,7 +209,11 @@ def test_cli_exit_codes_and_json(tmp_path):
                                        "1,x", "--max-new-tokens", "2"], capture_output=True, text=True)
     assert bad_prompt.returncode == 2 and "invalid token id" in bad_prompt.stderr
     ins = subprocess.run(exe + ["run", "inspect", str(run_dir), "--json"], capture_output=True, text=True)
-    assert json.loads(ins.stdout)["checkpoints"]["latest_step"] == 2
+    inspected = json.loads(ins.stdout)
+    assert inspected["checkpoint_index"]["latest_step"] == 2 and inspected["latest_checkpoint"]["exists"]
+    assert [c["step"] for c in inspected["checkpoints"]] == [2] and inspected["final"]["step"] == 2
+    text = subprocess.run(exe + ["run", "inspect", str(run_dir)], capture_output=True, text=True).stdout
+    assert "status: completed" in text and "latest checkpoint: step=2" in text and "kernels: enabled=True" in text
     kl = subprocess.run(exe + ["kernels", "list", "--json"], capture_output=True, text=True)
     assert kl.returncode == 0 and any(k["op"] == "gemm" for k in json.loads(kl.stdout)["kernels"])
 

@@ -59,25 +59,50 @@ def _streaming(rows, seq_len=8, batch=2, loads=None):
                                    tokenizer=FakeTokenizer())
 
 
-ROWS = [{"text": "the quick brown fox"}, {"text": ""}, {"other": 1}, {"text": "jumps over the lazy dog"},
+ROWS = [{"text": "the quick brown fox"}, {"text": ""}, {"text": "jumps over the lazy dog", "other": 1},
         {"text": "pack my box with five dozen liquor jugs"}, {"text": "sphinx of black quartz judge my vow"}]
 
 
-def test_streaming_packs_documents_with_eot_and_skips_empty_rows():
+def _stream_tokens(rows, eot=255):
+    out = []
+    for row in rows:
+        out.extend([ord(c) % 200 for c in row["text"]] + [eot])
+    return out
+
+
+def test_streaming_records_overlap_by_one_token_so_every_token_is_a_target_once():
     loads = []
     pipe = _streaming(ROWS, loads=loads)
     first = pipe.next_batch(pipe.initial_state())
     assert loads == [("corp/us", "train", "abc123")]                        # the pinned revision reaches the loader
-    ids = np.concatenate([first.batch.input_ids[0], first.batch.target_ids[0][-1:]])
-    want = [ord(c) % 200 for c in "the quick brown fox"] + [255]
-    assert ids.tolist() == want[:9]                                          # one row = seq_len + 1 tokens, shifted
+    stream = _stream_tokens(ROWS)
+    assert first.batch.input_ids.tolist() == [stream[0:8], stream[8:16]]
+    assert first.batch.target_ids.tolist() == [stream[1:9], stream[9:17]]
     assert first.batch.loss_mask.all() and first.batch.input_ids.shape == (2, 8)
-    assert first.state.stream_state["documents_consumed"] == 1 and first.state.next_record_index == 2
-    assert len(first.state.stream_state["pending_tokens"]) == len(want) - 18
+    st = first.state.stream_state
+    assert st["pending_tokens"] == [stream[16]] and st["tokens_emitted"] == 16 and first.state.next_record_index == 2
+    assert st["rows_seen"] == 1 and st["docs_seen"] == 1 and st["current_doc_active"] and st["hf_state"] == {"position": 0}
+    assert st["current_doc_token_offset"] == 17                              # of the 20 tokens of the first document
     assert first.provenance.token_start == 0 and first.provenance.token_end == 16
+    assert first.provenance.row_start_offsets == (0, 8) and first.provenance.row_doc_ids is None
     second = pipe.next_batch(first.state)
-    assert second.state.stream_state["documents_consumed"] == 4              # the empty and the text-less rows count
-    assert pipe.describe()["backend"] == "hf_streaming" and pipe.describe()["revision"] == "abc123"
+    assert second.batch.input_ids.tolist() == [stream[16:24], stream[24:32]]
+    assert second.state.stream_state["rows_seen"] == 3                       # an empty text is a document of one EOT
+    assert second.state.stream_state["docs_seen"] == 3
+    d = pipe.describe()
+    assert d["backend"] == "hf_streaming" and d["revision"] == "abc123" and d["exact_resume"] and d["num_records"] is None
+    assert d["tokens_emitted"] == 32 and d["rows_seen"] == 3 and d["source"]["dataset"] == "corp/us"
+    assert json.loads(d["source_summary"])["revision"] == "abc123" and d["document_aware"] is False
+
+
+def test_streaming_never_holds_more_than_one_record_of_pending_tokens():
+    long_rows = [{"text": "x" * 1000}, {"text": "y" * 1000}]
+    pipe = _streaming(long_rows, seq_len=8, batch=2)
+    state = pipe.initial_state()
+    for _ in range(20):
+        pb = pipe.next_batch(state)
+        state = pb.state
+        assert len(state.stream_state["pending_tokens"]) == 1
 
 
 def test_streaming_resumes_with_the_very_next_token():
@@ -88,27 +113,54 @@ def test_streaming_resumes_with_the_very_next_token():
         pb = pipe.next_batch(state)
         state = pb.state
         straight.append(pb.batch.input_ids.copy())
-    pipe2 = _streaming(ROWS)
-    state = pipe2.initial_state()
-    for _ in range(2):
-        state = pipe2.next_batch(state).state
-    saved = json.loads(json.dumps(pipe2.state_to_json(state)))              # what a checkpoint stores
-    resumed = _streaming(ROWS)                                               # a new process, a new dataset object
-    state = resumed.state_from_json(saved)
-    for want in straight[2:]:
-        pb = resumed.next_batch(state)
-        state = pb.state
-        assert np.array_equal(pb.batch.input_ids, want)
+    for stop in (1, 2, 3):                                                   # mid-document and at a document's end
+        pipe2 = _streaming(ROWS)
+        state = pipe2.initial_state()
+        for _ in range(stop):
+            state = pipe2.next_batch(state).state
+        saved = json.loads(json.dumps(pipe2.state_to_json(state)))          # what a checkpoint stores
+        resumed = _streaming(ROWS)                                           # a new process, a new dataset object
+        state = resumed.state_from_json(saved)
+        for want in straight[stop:]:
+            pb = resumed.next_batch(state)
+            state = pb.state
+            assert np.array_equal(pb.batch.input_ids, want)
+    # going back to an older state of the same pipeline object restores it as well
+    again = pipe.next_batch(pipe.state_from_json(saved))
+    assert np.array_equal(again.batch.input_ids, straight[3])
 
 
-def test_streaming_rejects_foreign_state_and_ends_cleanly():
+def test_streaming_rejects_foreign_state_bad_rows_and_ends_cleanly():
+    from research_b200.data.streaming import build_hf_streaming_pipeline, hf_streaming_compat_payload
+
     pipe = _streaming(ROWS[:1], seq_len=64)
     with pytest.raises(StopIteration, match="ended before one full batch"):
         pipe.next_batch(pipe.initial_state())
     other = _streaming(ROWS, seq_len=4)
     saved = other.state_to_json(other.next_batch(other.initial_state()).state)
-    with pytest.raises(ContractError, match="does not match this pipeline"):
+    with pytest.raises(ContractError, match="state seq_len mismatch"):
         _streaming(ROWS, seq_len=8).state_from_json(saved)
+    with pytest.raises(ContractError, match="token_offset must match"):
+        other.state_from_json({**saved, "token_offset": 3})
+    with pytest.raises(ContractError, match="only epoch=0"):
+        other.state_from_json({**saved, "epoch": 1})
+    with pytest.raises(ContractError, match="hf_state must be a JSON object"):
+        other.state_from_json({**saved, "stream_state": {**saved["stream_state"], "hf_state": None}})
+    broken = other.state_from_json({**saved, "stream_state": {**saved["stream_state"], "current_doc_token_offset": 999}})
+    with pytest.raises(ContractError, match="outside current document tokens"):
+        other.next_batch(broken)
+    for rows, match in (([{"other": 1}], "missing text column"), ([{"text": 5}], "must contain strings"),
+                        (["plain"], "rows must be mappings")):
+        bad = _streaming(rows)
+        with pytest.raises(ContractError, match=match):
+            bad.next_batch(bad.initial_state())
+    spec = DataSpec(mode="hf_streaming", tokenizer_id="fake", hf_streaming=HFStreamingSpec(
+        dataset="corp/us", split="train", revision="abc123"))
+    built = build_hf_streaming_pipeline(spec, seq_len=8, batch_size=2, tokenizer=FakeTokenizer(),
+                                        dataset_loader=lambda s: FakeIterableDataset(ROWS))
+    assert built.next_batch(built.initial_state()).batch.input_ids.shape == (2, 8)
+    compat = hf_streaming_compat_payload(spec.hf_streaming, tokenizer_id="fake", seq_len=8, batch_size=2)
+    assert compat["exact_resume"] and compat["source"]["revision"] == "abc123" and compat["order"] == "sequential"
 
 
 # ---- W&B mirror --------------------------------------------------------------------------------------
