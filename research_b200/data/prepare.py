@@ -208,6 +208,43 @@ def load_tokenizer(name: str):
 
 
 # ---- sources ---------------------------------------------------------------------------------------------
+def resolve_source_files(paths: Iterable[str], base: Path) -> tuple[Path, ...]:
+    """``source.paths`` entries as files: ``~`` expanded, relative to the config's folder, shell patterns expanded in
+    sorted order (reference: src/jaxtitan/data/prepare.py:679-697)."""
+
+    import glob
+    import os
+
+    files: list[Path] = []
+    for raw_path in paths:
+        expanded = os.path.expanduser(raw_path)
+        if not os.path.isabs(expanded):
+            expanded = os.path.join(str(base), expanded)
+        matches = sorted(glob.glob(expanded)) if glob.has_magic(expanded) else [expanded]
+        if not matches:
+            raise ContractError(f"source.paths entry did not match any files: {raw_path!r}")
+        for match in matches:
+            path = Path(match)
+            if not path.exists():
+                raise ContractError(f"source path does not exist: {raw_path!r}")
+            if path.is_dir():
+                raise ContractError(f"source path must be a file, got directory: {path}")
+            files.append(path)
+    return tuple(files)
+
+
+def source_manifest(source: PrepareSourceConfig, base: Path) -> dict[str, Any]:
+    """The ``source`` section of a prepared manifest: what was read, and for local files how many and how large."""
+
+    if source.type == "hf":
+        return {"type": source.type, "dataset": source.dataset, "name": source.name, "data_dir": source.data_dir,
+                "split": source.split, "text_column": source.text_column, "streaming": source.streaming}
+    files = resolve_source_files(source.paths, base)
+    return {"type": source.type, "paths": list(source.paths),
+            "text_column": None if source.type == "text" else source.text_column,
+            "resolved_file_count": len(files), "resolved_total_bytes": sum(f.stat().st_size for f in files)}
+
+
 def iter_texts(source: PrepareSourceConfig, base: Path) -> Iterator[str]:
     if source.type == "hf":
         try:
@@ -221,10 +258,7 @@ def iter_texts(source: PrepareSourceConfig, base: Path) -> Iterator[str]:
             if isinstance(text, str) and text:
                 yield text
         return
-    for rel in source.paths:
-        path = Path(rel) if Path(rel).is_absolute() else base / rel
-        if not path.is_file():
-            raise ContractError(f"source path does not exist: {path}")
+    for path in resolve_source_files(source.paths, base):
         if source.type == "text":
             with path.open("r", encoding="utf-8") as handle:
                 for line in handle:
@@ -277,12 +311,8 @@ def _batches(items: Iterable[str], size: int) -> Iterator[list[str]]:
 
 
 def tokenized_documents(cfg: PrepareConfig, base: Path) -> Iterator[list[int]]:
-    workers = cfg.tokenization.workers
+    workers = resolve_workers(cfg.tokenization.workers)
     texts = iter_texts(cfg.source, base)
-    if workers == "auto":
-        import os
-
-        workers = max(1, min(8, (os.cpu_count() or 2) - 1))
     if workers == 1:
         tok = load_tokenizer(cfg.tokenizer.name)
         for text in texts:
@@ -348,7 +378,18 @@ class ShardWriter:
         return self.shards
 
 
+def resolve_workers(workers) -> int:
+    if workers == "auto":
+        import os
+
+        return max(1, min(8, (os.cpu_count() or 2) - 1))
+    return int(workers)
+
+
 def prepare_dataset(config_path: str | Path, *, overwrite: bool = False) -> dict[str, Any]:
+    import time
+
+    started = time.perf_counter()
     config_path = Path(config_path)
     cfg = load_prepare_config(config_path)
     out_dir = cfg.output.path if cfg.output.path.is_absolute() else Path.cwd() / cfg.output.path
@@ -361,7 +402,9 @@ def prepare_dataset(config_path: str | Path, *, overwrite: bool = False) -> dict
     writer = ShardWriter(out_dir, cfg.output.shard_tokens)
     offsets = [0]
     budget = cfg.output.max_tokens
+    docs_seen = 0
     for doc in tokenized_documents(cfg, config_path.parent):
+        docs_seen += 1
         ids = list(doc) + ([tok.eot_id] if cfg.tokenizer.append_eot else [])
         if not ids:
             continue
@@ -385,15 +428,24 @@ def prepare_dataset(config_path: str | Path, *, overwrite: bool = False) -> dict
     (out_dir / "document_offsets.u64").write_bytes(off.tobytes())
     tb = tok.token_byte_lengths().astype("<u2")
     (out_dir / "token_bytes.bin").write_bytes(tb.tobytes())
+    elapsed = time.perf_counter() - started
+    from research_b200.services.artifacts import utc_now
+
     manifest = {
-        "schema_version": 1, "kind": "training_tokens", "dtype": "uint32",
+        "schema_version": 1, "created_at": utc_now(), "kind": "training_tokens", "dtype": "uint32",
         "tokenizer": {"name": cfg.tokenizer.name, "vocab_size": int(tok.vocab_size), "eot_id": int(tok.eot_id),
-                      "append_eot": cfg.tokenizer.append_eot},
-        "source": {"type": cfg.source.type, "dataset": cfg.source.dataset, "split": cfg.source.split,
-                   "paths": list(cfg.source.paths), "text_column": cfg.source.text_column},
-        "num_tokens": total, "shards": shards,
+                      "eot_token": int(tok.eot_id), "append_eot": cfg.tokenizer.append_eot},
+        "source": source_manifest(cfg.source, config_path.parent),
+        "val_fraction": float(cfg.output.val_fraction), "max_tokens": cfg.output.max_tokens,
+        "shard_tokens": cfg.output.shard_tokens,
+        "num_tokens": total, "num_docs": len(offsets) - 1, "source_docs_seen": docs_seen,
+        "elapsed_sec": elapsed, "tokens_per_sec": total / elapsed if elapsed > 0 else None,
+        "tokenization": {"workers": resolve_workers(cfg.tokenization.workers),
+                         "batch_docs": cfg.tokenization.batch_docs, "queue_batches": cfg.tokenization.queue_batches},
+        "shards": shards,
         "splits": {"train": {"start": 0, "end": val_start, "tokens": val_start},
                    "val": {"start": val_start, "end": total, "tokens": total - val_start}},
+        "train_tokens": val_start, "val_tokens": total - val_start,
         "documents": {"count": len(offsets) - 1},
         "files": {"token_bytes": {"path": "token_bytes.bin", "dtype": "uint16", "bytes": int(tb.nbytes),
                                   "sha256": sha256(tb.tobytes()).hexdigest()},

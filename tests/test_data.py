@@ -221,3 +221,68 @@ def test_local_rows_keep_the_order_and_read_only_their_tokens(tmp_path, order):
     assert sum(reads) == 5 * 2 * 33                       # two rows of seq_len + 1 tokens per batch, nothing else
     with pytest.raises(ContractError, match="not inside a batch"):
         part.set_local_rows(range(6, 10))
+
+
+def test_prepare_records_its_source_and_settings_and_expands_patterns(tmp_path):
+    import json
+
+    from research_b200.data.inspect import data_config_snippet, format_inspection, inspect_dataset, record_count
+    from research_b200.data.prepare import prepare_dataset, resolve_source_files
+
+    (tmp_path / "part-b.jsonl").write_text("\n".join(json.dumps({"body": f"second file row {i}"}) for i in range(60)))
+    (tmp_path / "part-a.jsonl").write_text("\n".join(json.dumps({"body": f"first file row {i}", "n": i})
+                                                     for i in range(60)) + "\n" + json.dumps({"n": 1}) + "\n")
+    cfg = tmp_path / "prep.toml"
+    cfg.write_text('[source]\ntype = "jsonl"\npaths = ["part-*.jsonl"]\ntext_column = "body"\n'
+                   '[tokenizer]\nname = "byte-level"\n'
+                   '[output]\npath = "%s"\nmax_tokens = 100000\nval_fraction = 0.1\nshard_tokens = 1000\n'
+                   '[tokenization]\nworkers = 1\nbatch_docs = 16\n' % (tmp_path / "out").as_posix())
+    files = resolve_source_files(["part-*.jsonl"], tmp_path)
+    assert [f.name for f in files] == ["part-a.jsonl", "part-b.jsonl"]          # sorted expansion
+    with pytest.raises(ContractError, match="did not match any files"):
+        resolve_source_files(["nothing-*.jsonl"], tmp_path)
+    with pytest.raises(ContractError, match="does not exist"):
+        resolve_source_files(["missing.jsonl"], tmp_path)
+    with pytest.raises(ContractError, match="must be a file, got directory"):
+        resolve_source_files([str(tmp_path)], tmp_path)
+    prepare_dataset(cfg)
+    raw = json.loads((tmp_path / "out" / "manifest.json").read_text())
+    assert raw["source"] == {"type": "jsonl", "paths": ["part-*.jsonl"], "text_column": "body",
+                             "resolved_file_count": 2,
+                             "resolved_total_bytes": sum(f.stat().st_size for f in files)}
+    assert raw["num_docs"] == raw["documents"]["count"] == 120 and raw["source_docs_seen"] == 120
+    assert raw["tokenizer"]["eot_token"] == 256 and raw["tokenizer"]["append_eot"] is True
+    assert raw["val_fraction"] == 0.1 and raw["max_tokens"] == 100000 and raw["shard_tokens"] == 1000
+    assert raw["tokenization"] == {"workers": 1, "batch_docs": 16, "queue_batches": 8}
+    assert raw["train_tokens"] + raw["val_tokens"] == raw["num_tokens"] and raw["elapsed_sec"] >= 0
+    assert raw["created_at"].endswith("Z") and raw["tokens_per_sec"] > 0
+    first = np.fromfile(tmp_path / "out" / "tokens-00000.bin", dtype="<u4")
+    assert bytes(first[:16].astype(np.uint8)).decode() == "first file row 0"      # part-a comes first
+    # inspection of that dataset
+    report = inspect_dataset(tmp_path / "out" / "manifest.json", tokenizer_id="byte-level", verify_checksums=True,
+                             seq_len=64)
+    assert report["tokens"] == {"total": raw["num_tokens"], "train": raw["train_tokens"], "val": raw["val_tokens"]}
+    assert report["source"]["resolved_file_count"] == 2 and report["tokenizer"]["name"] == "byte-level"
+    assert report["documents"]["count"] == 120 and report["documents"]["offsets_path"] == "document_offsets.u64"
+    assert report["documents"]["lengths"]["min"] == len("first file row 0") + 1
+    assert report["shards"]["count"] == len(raw["shards"]) and report["shards"]["checksums_present"]
+    assert report["shards"]["bytes"] == 4 * raw["num_tokens"] and len(report["shards"]["files"]) == report["shards"]["count"]
+    assert report["records"] == {"seq_len": 64, "train": (raw["train_tokens"] - 1) // 64,
+                                 "val": (raw["val_tokens"] - 1) // 64,
+                                 "train_document_buffer_rows": raw["train_tokens"] // 65}
+    assert record_count(1, 8) == 0 and record_count(9, 8) == 1 and record_count(17, 8) == 2
+    text = format_inspection(report)
+    for head in ("source: type=jsonl files=2", "tokenizer: byte-level append_eot=True eot=256", "tokens: total=",
+                 "documents: count=120", "shards: count=", "document lengths: min=", "records: seq_len=64",
+                 "training config:", 'order = "document_buffer"'):
+        assert head in text, head
+    assert inspect_dataset(tmp_path / "out" / "manifest.json")["records"] is None
+    with pytest.raises(ContractError, match="--seq-len must be positive"):
+        inspect_dataset(tmp_path / "out" / "manifest.json", seq_len=0)
+    with pytest.raises(ContractError, match="does not match config tokenizer"):
+        inspect_dataset(tmp_path / "out" / "manifest.json", tokenizer_id="gpt2")
+    # the pasted block is a loadable [data] section
+    import tomllib
+
+    block = tomllib.loads(data_config_snippet(validate_dataset_manifest(tmp_path / "out" / "manifest.json")))["data"]
+    assert block["order"] == "document_buffer" and block["tokenizer_id"] == "byte-level" and block["mode"] == "prepared"
