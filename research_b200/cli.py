@@ -310,8 +310,9 @@ def _dispatch(args: argparse.Namespace) -> int:
             if args.json:
                 _print_json(payload)
             else:
-                print(f"checkpoint {payload['checkpoint_step']}: loss={_fmt_metric(payload['loss'])} "
-                      f"tokens={_fmt_int(payload['token_count'])} batches={payload['num_batches']}")
+                from research_b200.runtime.checkpoint_eval import format_checkpoint_eval
+
+                print(format_checkpoint_eval(payload))
     elif args.command == "sample":
         from research_b200.runtime.sampling import sample_checkpoint
 
@@ -321,7 +322,9 @@ def _dispatch(args: argparse.Namespace) -> int:
             if args.json:
                 _print_json(row)
             else:
-                print(f"checkpoint {row['checkpoint_step']}: generated {row['generated_ids']}")
+                from research_b200.runtime.sampling import format_checkpoint_sample
+
+                print(format_checkpoint_sample(row))
     else:
         build_parser().print_help()
     return 0

@@ -26,6 +26,14 @@ class InferenceCheckpoint:
     spec: RunSpec
     record: CheckpointRecord
     path: Path
+    runtime_fingerprint: str | None = None
+
+    def describe(self, selector: str | None = None) -> dict:
+        """The ``checkpoint`` section of eval and sample artifacts."""
+
+        out = {"step": self.record.step, "path": self.record.checkpoint_path.as_posix(),
+               "tokens_seen": self.record.tokens_seen, "runtime_fingerprint": self.runtime_fingerprint}
+        return out if selector is None else {"selector": selector, **out}
 
     @property
     def model(self):
@@ -82,4 +90,4 @@ def restore_inference_checkpoint(run_dir: str | Path, selector: str) -> Inferenc
     restored = service.restore(record.step)
     load_state_tensors(trainer, restored.tensors)
     validate_resume_compat(restored, spec, state_step=trainer.step, state_tokens=trainer.tokens_seen, compat=compat)
-    return InferenceCheckpoint(trainer, spec, record, restored.path)
+    return InferenceCheckpoint(trainer, spec, record, restored.path, compat.runtime_fingerprint)

@@ -253,3 +253,54 @@ def test_run_inspection_sections_formatter_and_missing_checkpoint(tmp_path):
     shutil.rmtree(run_dir / report["latest_checkpoint"]["checkpoint_path"])
     with pytest.raises(ContractError, match="retained path does not exist"):
         inspect_run(run_dir)
+
+
+def test_checkpoint_eval_and_sample_payloads(tmp_path):
+    from research_b200.errors import ContractError
+    from research_b200.runtime.checkpoint_eval import (checkpoint_eval_to_json, evaluate_checkpoint,
+                                                       format_checkpoint_eval)
+    from research_b200.runtime.sampling import (checkpoint_sample_to_json, format_checkpoint_sample, parse_prompt_ids,
+                                                sample_checkpoint)
+    from research_b200.runtime.training import run_training
+
+    manifest = tiny_dataset(tmp_path)
+    raw = tiny_raw_config(manifest, run_id="ce", output_dir=(tmp_path / "runs").as_posix(), evals=True, steps=2,
+                          checkpoint_every=2)
+    summary = run_training(write_toml(raw, tmp_path / "ce.toml"))
+    run_dir = tmp_path / "runs" / "ce"
+    payload = evaluate_checkpoint(run_dir, "latest")
+    assert payload["status"] == "completed" and payload["checkpoint"]["step"] == 2
+    assert payload["checkpoint"]["path"] == payload["checkpoint_path"] and len(payload["checkpoint"]["runtime_fingerprint"]) == 64
+    row = payload["eval"]
+    assert row["eval_name"] == "validation" and row["num_batches"] == 2 and row["target_tokens"] == 2 * 4 * 32
+    assert row["loss"] == pytest.approx(summary.final_eval_loss, rel=1e-6) and row["eval_tokens_per_sec"] > 0
+    assert row["token_start"] is not None and row["document_aware"] in (True, False)
+    assert payload["data"]["manifest_path"] == manifest.as_posix() and len(payload["data"]["manifest_sha256"]) == 64
+    stored = json.loads((run_dir / payload["artifact_path"]).read_text())
+    assert stored["eval"]["loss"] == row["loss"] and stored["checkpoint"] == payload["checkpoint"]
+    assert format_checkpoint_eval(payload).startswith("evaluated checkpoint step=2 path=checkpoints/")
+    assert json.loads(checkpoint_eval_to_json(payload))["run_id"] == "ce"
+    with pytest.raises(ContractError, match="needs checkpoint and eval objects"):
+        format_checkpoint_eval({"checkpoint": 1})
+
+    sample = sample_checkpoint(run_dir, "2", prompt_ids=[5, 6, 7], max_new_tokens=3, top_k=1)
+    assert sample["checkpoint"]["selector"] == "2" and sample["checkpoint"]["step"] == 2
+    assert sample["model"] == {"name": "decoder", "variant": "tiny", "vocab_size": 256, "max_seq_len": 64}
+    assert sample["sampling"] == {"max_new_tokens": 3, "temperature": 1.0, "top_k": 1, "top_p": None}
+    assert sample["prompt_ids"] == [5, 6, 7] and len(sample["generated_ids"]) == 3 and len(sample["full_ids"]) == 6
+    assert "sampled checkpoint step=2" in format_checkpoint_sample(sample)
+    assert json.loads(checkpoint_sample_to_json(sample))["status"] == "completed"
+    lines = (run_dir / sample["artifact_path"]).read_text().splitlines()
+    assert len(lines) == 1 and json.loads(lines[0])["generated_ids"] == sample["generated_ids"]
+    with pytest.raises(ContractError, match="exceeds vocab size"):
+        sample_checkpoint(run_dir, "latest", prompt_ids="1", max_new_tokens=1, top_k=1000)
+    with pytest.raises(ContractError, match="outside the vocabulary"):
+        sample_checkpoint(run_dir, "latest", prompt_ids="1,999", max_new_tokens=1)
+    assert parse_prompt_ids(" 1, 2 ,3") == [1, 2, 3] and parse_prompt_ids((4, 5)) == [4, 5]
+    for bad, match in (("", "non-empty"), ("1,,2", "invalid token id"), ("1,-2", "invalid token id"),
+                       ("0x10", "invalid token id"), ([], "at least one"), ([1, True], "must be integers"),
+                       ([1, 2.0], "must be integers"), ([-1], "non-negative")):
+        with pytest.raises(ContractError, match=match):
+            parse_prompt_ids(bad)
+    with pytest.raises(ContractError, match="outside the vocabulary"):
+        parse_prompt_ids([300], 256)
