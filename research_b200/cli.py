@@ -398,10 +398,11 @@ def _kernels(args: argparse.Namespace) -> int:
 
 def _profile(args: argparse.Namespace) -> int:
     if args.profile_command == "analyze":
-        from research_b200.runtime.profile_analysis import analyze_profile_root
+        from research_b200.runtime.profile_analysis import (analyze_profile_root, format_profile_analysis,
+                                                            profile_analysis_to_json)
 
         report = analyze_profile_root(args.root, warmup_steps=args.warmup_steps)
-        _print_json(report) if args.json else print(json.dumps(report, indent=1))
+        print(profile_analysis_to_json(report) if args.json else format_profile_analysis(report))
     else:
         from research_b200.runtime.profile_bench import benchmark_component
 

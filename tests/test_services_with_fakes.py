@@ -450,3 +450,76 @@ def test_profile_analysis_rejects_bad_roots(tmp_path):
         analyze_profile_root(tmp_path)
     with pytest.raises(ContractError, match="non-negative"):
         analyze_profile_root(tmp_path, warmup_steps=-1)
+
+
+def _structured_run(root, name, *, optimizer, parallelism, step=0.5, status="completed", nonfinite=0, hidden=64):
+    import gzip
+
+    run = _fake_run(root, name, step_sec=[9.0, step, step, step, step], tps=[1, 100, 100, 100, 100], optimizer=optimizer)
+    (run / "config").mkdir()
+    (run / "summaries").mkdir()
+    (run / "config" / "resolved.json").write_text(json.dumps({
+        "model": {"name": "decoder", "hidden_size": hidden, "variant": name, "remat": "none"},
+        "optimizer": {"name": optimizer}, "parallelism": parallelism}))
+    (run / "summaries" / "final.json").write_text(json.dumps({
+        "run_id": name, "status": status, "final_optimizer_nonfinite_group_count": nonfinite}))
+    (run / "profiles").mkdir()
+    with gzip.open(run / "profiles" / "step.trace.json.gz", "wt") as handle:
+        json.dump({"traceEvents": [{"ph": "X", "cat": "kernel", "name": "gemm_bf16_kernel", "dur": 30.0},
+                                   {"ph": "X", "cat": "gpu_memcpy", "name": "Memcpy DtoD", "dur": 10.0},
+                                   {"ph": "X", "cat": "kernel", "name": "broken", "dur": "x"}]}, handle)
+    return run
+
+
+def test_profile_analysis_pairs_by_structure_and_reports_the_tracing_tax(tmp_path):
+    from research_b200.runtime.profile_analysis import (analyze_profile_root, format_profile_analysis, layout_name,
+                                                        model_signature, profile_analysis_to_json, relative_delta)
+
+    _structured_run(tmp_path, "a-plain", optimizer="adamw", parallelism={"mode": "ddp"}, step=0.4)
+    _structured_run(tmp_path, "b-tensor", optimizer="adamw", parallelism={"mode": "ddp", "tensor_parallel": True}, step=0.5)
+    _structured_run(tmp_path, "c-tensor-ns", optimizer="muon", parallelism={"mode": "ddp", "tensor_parallel": True}, step=0.6)
+    _structured_run(tmp_path, "d-sharded", optimizer="adamw", parallelism={"mode": "fsdp", "tensor_parallel": True}, step=0.55)
+    _structured_run(tmp_path, "e-other-net", optimizer="muon", parallelism={"mode": "ddp", "tensor_parallel": True},
+                    hidden=128)
+    traced = tmp_path / "a-plain" / "diagnostics" / "profiling.json"
+    traced.write_text(json.dumps({"enabled": True, "trace_start_step": 2, "trace_end_step": 3}))
+    rows = [json.loads(l) for l in (tmp_path / "a-plain" / "metrics" / "train.jsonl").read_text().splitlines()]
+    rows[1]["train_step_sec"] = rows[2]["train_step_sec"] = 0.6                      # the traced steps run slower
+    (tmp_path / "a-plain" / "metrics" / "train.jsonl").write_text("\n".join(json.dumps(r) for r in rows))
+    out = analyze_profile_root(tmp_path, warmup_steps=1)
+    pairs = {(p["kind"], p["candidate"], p["baseline"]): p for p in out["comparisons"]}
+    assert set(pairs) == {("layout", "b-tensor", "a-plain"), ("layout", "d-sharded", "b-tensor"),
+                          ("optimizer", "c-tensor-ns", "b-tensor")}           # the other network pairs with nothing
+    assert pairs[("optimizer", "c-tensor-ns", "b-tensor")]["train_step_delta"] == pytest.approx(0.2)
+    assert pairs[("layout", "b-tensor", "a-plain")]["train_step_delta"] == pytest.approx(0.25)
+    plain = out["runs"][0]
+    assert plain["layout"] == "ddp" and out["runs"][3]["layout"] == "fsdp+tp" and plain["status"] == "completed"
+    assert plain["trace_window"]["row_count"] == 2 and plain["steady"]["start_step"] == 4
+    assert plain["trace_window"]["tax"]["train_step_sec"] == pytest.approx(0.5)
+    assert out["runs"][1]["trace_window"]["tax"] is None and plain["hlo"] is None
+    trace = plain["trace"]
+    assert trace["trace"] == "step.trace.json.gz" and trace["event_count"] == 2       # the malformed event is skipped
+    assert trace["gpu_time_us"] == {"gemm": 30.0, "memcpy": 10.0} and trace["max_kernel_us"]["gemm"] == 30.0
+    text = format_profile_analysis(out)
+    assert "profile analysis: runs=5" in text and "paired deltas:" in text and "traced steps 2-3: train +50.0%" in text
+    assert "optimizer c-tensor-ns vs b-tensor: train=+20.0%" in text and "gpu time: gemm=75% memcpy=25%" in text
+    assert json.loads(profile_analysis_to_json(out))["run_count"] == 5
+    assert model_signature({"a": 1, "variant": "x", "remat": "full"}) == '{"a":1}' and model_signature(None) == "unknown"
+    assert layout_name({"parallelism": {"mode": "zero2", "tensor_parallel": True, "expert_parallel": True}}) == "zero2+tp+ep"
+    assert layout_name({}) == "ddp"
+    assert relative_delta(3.0, 2.0) == pytest.approx(0.5) and relative_delta(1.0, 0) is None and relative_delta(None, 1.0) is None
+
+
+def test_profile_analysis_refuses_unfinished_or_nonfinite_runs(tmp_path):
+    from research_b200.runtime.profile_analysis import analyze_profile_root
+
+    _structured_run(tmp_path / "one", "failed-run", optimizer="adamw", parallelism={"mode": "ddp"}, status="failed")
+    with pytest.raises(ContractError, match="is not completed: status='failed'"):
+        analyze_profile_root(tmp_path / "one")
+    _structured_run(tmp_path / "two", "nan-run", optimizer="adamw", parallelism={"mode": "ddp"}, nonfinite=2)
+    with pytest.raises(ContractError, match="contains nonfinite optimizer groups"):
+        analyze_profile_root(tmp_path / "two")
+    run = _structured_run(tmp_path / "three", "bad-trace", optimizer="adamw", parallelism={"mode": "ddp"})
+    (run / "profiles" / "broken.json").write_text("{not json")
+    with pytest.raises(ContractError, match="failed to read trace"):
+        analyze_profile_root(tmp_path / "three")
