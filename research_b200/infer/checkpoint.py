@@ -84,7 +84,7 @@ def restore_inference_checkpoint(run_dir: str | Path, selector: str) -> Inferenc
     service = LocalCheckpointService(run_dir, is_writer=False)
     trainer = Trainer(spec)
     spec = trainer.spec
-    compat = build_resume_compat(spec, optimizer_policy=optimizer_policy_summary(trainer.optimizer_build),
+    compat = build_resume_compat(spec, optimizer_policy=optimizer_policy_summary(trainer.optimizer_build, trainer.result.metadata),
                                  data_pipeline=trainer.data.describe())
     validate_resume_metadata(service.restore_metadata(record.step), spec, compat=compat)
     restored = service.restore(record.step)

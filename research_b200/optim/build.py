@@ -169,30 +169,108 @@ def _muon_plan_summary(result: OptimizerBuildResult) -> dict[str, Any] | None:
     return summarize_plans(result.muon_execution_plans)
 
 
-def optimizer_policy_summary(result: OptimizerBuildResult) -> dict[str, Any]:
-    """Stable payload for ``diagnostics/runtime.json`` and the resume fingerprint."""
+def schedule_payload(spec) -> dict[str, Any] | None:
+    if spec is None:
+        return None
+    return {"name": spec.name, "peak_lr": spec.peak_lr, "warmup_steps": spec.warmup_steps,
+            "total_steps": spec.total_steps, "min_lr_ratio": spec.min_lr_ratio, "stable_steps": spec.stable_steps}
+
+
+def distributed_policy_payload(name: str) -> dict[str, str]:
+    """How each optimizer family lives with sharded state here (reference: optim/build.py:470-487, whose Muon turns
+    into Dion2 under FSDP; here whole matrices go to owner ranks instead)."""
+
+    if name == "adamw":
+        return {"optimizer_state": "elementwise_shard_safe", "gradient_update": "elementwise_shard_safe",
+                "zero2_fsdp": "supported"}
+    if name == "muon":
+        return {"optimizer_state": "whole_matrices_on_owner_ranks_or_tp_sharded_dist_muon",
+                "gradient_update": "muon_on_the_owner_rank_dist_muon_for_tp",
+                "zero2_fsdp": "owner_distributed_muon"}
+    if name == "dion":
+        return {"optimizer_state": "whole_matrices_on_owner_ranks", "gradient_update": "dion2_on_the_owner_rank",
+                "zero2_fsdp": "owner_distributed_dion2"}
+    return {"optimizer_state": "unknown", "gradient_update": "unknown", "zero2_fsdp": "unsupported"}
+
+
+def route_distributed_policy(backend: str, *, muon_tp_mode: str) -> str:
+    if backend == "adamw":
+        return "elementwise_shard_safe"
+    if backend in ("muon", "dion2"):
+        return "complete_matrix_or_per_expert_complete_matrix"
+    if backend == "dist_muon":
+        return "duplicated_full_logical_matrix" if muon_tp_mode == "duplicated" else "sharded_gram_collectives"
+    return "unknown"
+
+
+def dist_muon_policy_payload(spec: OptimizerSpec) -> dict[str, Any]:
+    """What the tensor-parallel Muon mode promises (reference: optim/build.py:332-359)."""
+
+    common = {"requested_mode": spec.muon_tp_mode,
+              "newton_schulz_precision": muon_policy_constants().get("newton_schulz_precision"),
+              "replicated_model_axis_reduction": "mean", "auto_selected_for": "tp_sharded_muon_matrix_routes"}
+    if spec.muon_tp_mode == "duplicated":
+        return {**common, "distributed_policy": "duplicated_full_logical_matrix", "exact": True,
+                "approximation": "none", "execution": "duplicated",
+                "performance": "single_bf16_logical_matrix_gather",
+                "numerical_contract": "accepted_bfloat16_reference"}
+    return {**common, "distributed_policy": "sharded_gram_collectives", "exact": False,
+            "approximation": "floating_point_reduction_order", "execution": "distributed",
+            "performance": "one_norm_plus_five_gram_reductions_with_optional_exchange",
+            "numerical_contract": "deterministic_close_not_bitwise"}
+
+
+def optimizer_policy_summary(result: OptimizerBuildResult, metadata: tuple[ParamMeta, ...] | None = None) -> dict[str, Any]:
+    """Stable payload for ``diagnostics/runtime.json`` and the resume fingerprint
+    (sections of the reference's payload: optim/build.py:231-329)."""
 
     by_backend: dict[str, int] = {}
+    fallbacks: dict[str, int] = {}
     groups: dict[tuple[str, str], int] = {}
     for a in result.route_assignments:
         by_backend[a.backend] = by_backend.get(a.backend, 0) + 1
         groups[(a.tag, a.backend)] = groups.get((a.tag, a.backend), 0) + 1
+        if a.fallback_reason is not None:
+            fallbacks[a.fallback_reason] = fallbacks.get(a.fallback_reason, 0) + 1
     spec = result.spec
+    shapes = {} if metadata is None else {m.path: list(m.shape) for m in metadata}
+    plan_summary = _muon_plan_summary(result)
+    dist_muon = dist_muon_policy_payload(spec)
+    if plan_summary is not None:
+        dist_muon["leaf_execution_plans"] = plan_summary["leaves"]
     return {
         "name": spec.name,
+        "requested_name": spec.name,
         "description": result.description,
-        "adamw": {"b1": ADAMW_B1, "b2": ADAMW_B2, "eps": ADAMW_EPS},
-        "muon": muon_policy_constants() if spec.name == "muon" else None,
-        "dion2": dion2_policy_constants() if spec.name == "dion" else None,
+        "schedule": schedule_payload(spec.schedule),
+        "adamw_fallback_schedule": schedule_payload(spec.adamw_fallback_schedule),
+        "supported_runtime_backends": sorted(SUPPORTED_RUNTIME_BACKENDS),
+        "internal_runtime_backends": ["dion2", "dist_muon"],
+        "distributed_policy": distributed_policy_payload(spec.name),
+        "adamw": {"b1": ADAMW_B1, "b2": ADAMW_B2, "eps": ADAMW_EPS, "distributed_policy": "elementwise_shard_safe"},
+        "muon": None if spec.name != "muon" else {
+            **muon_policy_constants(), "tp_mode": spec.muon_tp_mode,
+            "distributed_policy": "owner_distributed_complete_matrices",
+            "rank3_expert_policy": "per_expert_full_matrix",
+            "hidden_matrix_tags": sorted(MUON_MATRIX_TAGS), "routed_expert_matrix_tags": sorted(ROUTED_EXPERT_TAGS),
+            "fallback_tags": ["embedding", "lm_head", *sorted(NORM_TAGS)]},
+        "dion2": None if spec.name != "dion" else {**dion2_policy_constants(),
+                                                    "distributed_policy": "owner_distributed_complete_matrices"},
+        "dist_muon": dist_muon,
+        "auto_routing": {"muon_sharded_matrix_backend": "muon", "muon_tp_sharded_matrix_backend": "dist_muon",
+                         "active": any(a.auto_resolved for a in result.route_assignments)},
         "muon_tp_mode": spec.muon_tp_mode,
-        "muon_tp_execution": _muon_plan_summary(result),
+        "muon_tp_execution": plan_summary,
         "backend_parameter_counts": dict(sorted(by_backend.items())),
+        "route_counts": dict(sorted(by_backend.items())),
+        "fallback_counts": dict(sorted(fallbacks.items())),
         "groups": [{"tag": t, "backend": b, "parameters": n} for (t, b), n in sorted(groups.items())],
         "routes": [
             {"path": a.name, "tag": a.tag, "backend": a.backend, "weight_decay": a.weight_decay,
              "requested_backend": a.requested_backend, "auto_resolved": a.auto_resolved,
              "resolution_reason": a.resolution_reason, "fallback_reason": a.fallback_reason,
-             "matrix_axis": a.matrix_axis}
+             "matrix_axis": a.matrix_axis, "logical_shape": shapes.get(a.path),
+             "distributed_policy": route_distributed_policy(a.backend, muon_tp_mode=spec.muon_tp_mode)}
             for a in result.route_assignments
         ],
     }

@@ -50,7 +50,7 @@ def run_preflight(config_path: str | Path) -> dict[str, Any]:
     spec = trainer.spec
     mesh = trainer.mesh
     t = spec.training
-    policy = optimizer_policy_summary(trainer.optimizer_build)
+    policy = optimizer_policy_summary(trainer.optimizer_build, trainer.result.metadata)
     pipeline = trainer.data.describe()
     runtime = build_runtime_diagnostics(spec, trainer, optimizer_policy=policy, data_pipeline=pipeline)
     require_kernel_plan_supported(runtime["kernels"], spec)

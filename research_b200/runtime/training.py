@@ -315,7 +315,7 @@ def _run_initialized(spec: RunSpec, config_path: Path, writer, resume: bool, pro
     if trainer_hook is not None:
         trainer_hook(trainer)
     run_dir = spec.dirs.run_dir
-    policy = optimizer_policy_summary(trainer.optimizer_build)
+    policy = optimizer_policy_summary(trainer.optimizer_build, trainer.result.metadata)
     pipeline_description = trainer.data.describe()
     compat = build_resume_compat(spec, optimizer_policy=policy, data_pipeline=pipeline_description)
     runtime = build_runtime_diagnostics(spec, trainer, optimizer_policy=policy, data_pipeline=pipeline_description)

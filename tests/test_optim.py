@@ -81,6 +81,53 @@ def test_routing_by_tag():
         build_optimizer(OptimizerSpec(name="soap", schedule=ScheduleSpec(peak_lr=1e-3)), res.metadata)
 
 
+def test_policy_summary_sections():
+    from research_b200.optim.build import (describe_optimizer, dist_muon_policy_payload, distributed_policy_payload,
+                                           route_distributed_policy, schedule_payload)
+
+    raw = tiny_raw_config(Path("m.json"), kind="trinity", optimizer="muon")
+    raw["optimizer"]["schedule"] = {"peak_lr": 2e-3, "name": "wsd", "warmup_steps": 2, "total_steps": 40,
+                                    "stable_steps": 30, "min_lr_ratio": 0.1}
+    raw["optimizer"]["adamw_fallback_schedule"] = {"peak_lr": 1e-3, "warmup_steps": 1}
+    spec = run_spec_from_mapping(raw)
+    res = build_model(spec.model, seed=0)
+    built = build_optimizer(spec.optimizer, res.metadata, tp_size=2)
+    s = optimizer_policy_summary(built, res.metadata)
+    assert s["name"] == s["requested_name"] == "muon" and s["supported_runtime_backends"] == ["adamw", "dion", "muon"]
+    assert s["schedule"] == {"name": "wsd", "peak_lr": 2e-3, "warmup_steps": 2, "total_steps": 40,
+                             "min_lr_ratio": 0.1, "stable_steps": 30}
+    assert s["adamw_fallback_schedule"]["peak_lr"] == 1e-3 and s["adamw_fallback_schedule"]["name"] == "constant"
+    assert s["route_counts"] == s["backend_parameter_counts"] and sum(s["route_counts"].values()) == len(res.metadata)
+    assert set(s["route_counts"]) == {"adamw", "dist_muon", "muon"}              # experts stay whole: plain muon
+    assert s["fallback_counts"]["norm"] > 0 and s["fallback_counts"]["embedding"] == 1
+    assert s["auto_routing"]["active"] is True and s["auto_routing"]["muon_tp_sharded_matrix_backend"] == "dist_muon"
+    assert s["distributed_policy"]["zero2_fsdp"] == "owner_distributed_muon"
+    assert s["muon"]["tp_mode"] == spec.optimizer.muon_tp_mode and "attention_q" in s["muon"]["hidden_matrix_tags"]
+    assert "moe_gate" in s["muon"]["routed_expert_matrix_tags"] and s["dion2"] is None
+    route = next(r for r in s["routes"] if r["path"] == "layers.0.attn.q.kernel")
+    assert route["backend"] == "dist_muon" and route["logical_shape"] == [64, 64] and route["auto_resolved"]
+    assert route["distributed_policy"] in ("duplicated_full_logical_matrix", "sharded_gram_collectives")
+    plans = s["dist_muon"]["leaf_execution_plans"]
+    assert len(plans) == s["route_counts"]["dist_muon"] and {"path", "execution", "bucket_id"} <= set(plans[0])
+    assert optimizer_policy_summary(built)["routes"][0]["logical_shape"] is None      # shapes need the metadata
+    # the fixed payloads
+    dup = dist_muon_policy_payload(OptimizerSpec(name="muon", schedule=ScheduleSpec(peak_lr=1e-3), muon_tp_mode="duplicated"))
+    dis = dist_muon_policy_payload(OptimizerSpec(name="muon", schedule=ScheduleSpec(peak_lr=1e-3), muon_tp_mode="distributed"))
+    assert dup["exact"] is True and dup["execution"] == "duplicated" and dis["exact"] is False
+    assert dis["distributed_policy"] == "sharded_gram_collectives"
+    assert distributed_policy_payload("adamw")["zero2_fsdp"] == "supported"
+    assert distributed_policy_payload("soap")["zero2_fsdp"] == "unsupported"
+    assert route_distributed_policy("adamw", muon_tp_mode="distributed") == "elementwise_shard_safe"
+    assert route_distributed_policy("dist_muon", muon_tp_mode="duplicated") == "duplicated_full_logical_matrix"
+    assert route_distributed_policy("other", muon_tp_mode="duplicated") == "unknown" and schedule_payload(None) is None
+    text = describe_optimizer(spec.optimizer)
+    assert "schedule=wsd" in text and "stable_steps=30" in text and "adamw_fallback_schedule=constant:peak_lr=0.001" in text
+    adamw = build_optimizer(OptimizerSpec(name="adamw", schedule=ScheduleSpec(peak_lr=1e-3)), res.metadata)
+    plain = optimizer_policy_summary(adamw, res.metadata)
+    assert plain["muon"] is None and plain["fallback_counts"] == {} and plain["auto_routing"]["active"] is False
+    assert plain["muon_tp_execution"] is None and "leaf_execution_plans" not in plain["dist_muon"]
+
+
 def test_adamw_step_matches_torch(tmp_path):
     from tests.helpers import tiny_dataset
     from research_b200.runtime.trainer import Trainer
