@@ -106,6 +106,37 @@ class RunSummary:
     final_optimizer_nonfinite_group_count: int | None = None
     final_optimizer_nonfinite_groups: list[str] | None = None
     final_optimizer_route_backend_counts: dict[str, int] | None = None
+    final_moe_router_layers: list[dict[str, Any]] | None = None
+    global_device_count: int | None = None
+    process_index: int | None = None
+    single_process: bool | None = None
+    data_pipeline_version: str | None = None
+    data_pipeline_worker_count: int | None = None
+    data_pipeline_worker_buffer_size: int | None = None
+    data_pipeline_prefetch: bool | None = None
+    data_pipeline_state_schema_version: int | None = None
+    data_document_count: int | None = None
+    data_document_offsets_path: str | None = None
+    data_document_offsets_sha256: str | None = None
+    data_document_buffer_size: int | None = None
+    data_document_refill_size: int | None = None
+
+
+COMPLETED_EVENT_FIELDS = (
+    "target_tokens", "total_wall_sec", "final_train_tokens_per_sec", "avg_train_tokens_per_sec",
+    "steady_train_tokens_per_sec", "final_mfu", "avg_mfu", "final_batch_het", "avg_batch_het", "execution_mode",
+    "metrics_scope", "artifact_writer", "model_remat", "data_axis_size", "gradient_accumulation_steps",
+    "effective_global_batch_size", "effective_tokens_per_step", "per_device_batch_size", "selected_device_count",
+    "data_pipeline_backend", "data_pipeline_order", "data_pipeline_shuffle_seed", "data_pipeline_worker_count",
+    "data_pipeline_worker_buffer_size", "data_pipeline_prefetch", "data_document_buffer_size",
+    "data_document_refill_size", "moe_balance_policy", "z_loss_weight", "final_moe_router_layers",
+    "final_router_max_vio", "final_router_mean_load_cv", "final_router_dead_experts_count",
+    "final_router_mean_importance_cv", "final_router_mean_importance_entropy", "final_optimizer_groups",
+    "final_optimizer_grad_norm_max_group", "final_optimizer_update_norm_max_group",
+    "final_optimizer_update_param_ratio_max", "final_optimizer_update_param_ratio_mean",
+    "final_optimizer_groups_with_zero_grad", "final_optimizer_groups_with_zero_update",
+    "final_optimizer_nonfinite_group_count", "final_optimizer_nonfinite_groups",
+    "final_optimizer_route_backend_counts")
 
 
 def _noop_progress(event: str, payload: dict[str, Any]) -> None:
@@ -272,9 +303,22 @@ def run_training(config_path: str | Path, *, resume: bool = False, progress: Pro
         torch.distributed.barrier()
     writer = build_artifact_writer(spec, run_dir, is_writer=rank == 0, resume=resume)
     progress("start", {"spec": spec, "config_path": str(config_path), "resume": resume})
+    moe = spec.model.trinity.moe if spec.model.trinity is not None else None
     writer.append_event({"schema_version": 1, "type": "training_started", "run_id": spec.run_id,
                          "created_at": utc_now(), "resume": resume, "config_path": config_path.as_posix(),
-                         "world_size": world})
+                         "world_size": world, "execution_mode": runtime_execution_mode(spec),
+                         "parallelism_mode": spec.parallelism.mode, "metrics_scope": METRICS_SCOPE,
+                         "artifact_writer": ARTIFACT_WRITER, "model_remat": spec.model.remat,
+                         "gradient_accumulation_steps": spec.training.gradient_accumulation_steps,
+                         "data_pipeline_backend": "blackwell_native" if spec.data.mode == "prepared" else "hf_streaming",
+                         "data_pipeline_order": spec.data.order, "data_pipeline_shuffle_seed": spec.data.shuffle_seed,
+                         "data_pipeline_worker_count": spec.data.worker_count,
+                         "data_pipeline_worker_buffer_size": spec.data.worker_buffer_size,
+                         "data_pipeline_prefetch": spec.data.prefetch,
+                         "data_document_buffer_size": spec.data.document_buffer_size,
+                         "data_document_refill_size": spec.data.document_refill_size,
+                         "moe_balance_policy": None if moe is None else moe.balance.name,
+                         "z_loss_weight": spec.training.loss.z_loss_weight})
     monitor = None
     if world > 1:
         from research_b200.runtime.watchdog import RankMonitor
@@ -291,16 +335,20 @@ def run_training(config_path: str | Path, *, resume: bool = False, progress: Pro
             monitor.mark_failed(-1, f"{type(exc).__name__}: {exc}")
             monitor.stop()
         writer.append_event({"schema_version": 1, "type": "training_failed", "run_id": spec.run_id,
-                             "created_at": utc_now(), "error_type": type(exc).__name__, "error_message": str(exc)})
+                             "created_at": utc_now(), "error_type": type(exc).__name__, "error_message": str(exc),
+                             "error": str(exc)})
         writer.close()
         raise
     if monitor is not None:
         monitor.mark_done(summary.steps)
         monitor.stop()
     writer.write_summary(normalize(asdict(summary)))
+    completed = normalize(asdict(summary))
     writer.append_event({"schema_version": 1, "type": "training_completed", "run_id": spec.run_id,
                          "created_at": utc_now(), "steps": summary.steps, "tokens_seen": summary.tokens_seen,
-                         "final_loss": summary.final_loss})
+                         "final_loss": summary.final_loss,
+                         # the run-level figures of the summary, so that the event stream alone tells how a run ended
+                         **{k: completed[k] for k in COMPLETED_EVENT_FIELDS}})
     writer.close()
     progress("completed", {"summary": summary})
     return summary
@@ -462,8 +510,8 @@ def _run_initialized(spec: RunSpec, config_path: Path, writer, resume: bool, pro
         micro_tokens_per_step=t.global_batch_size * t.seq_len,
         effective_tokens_per_step=t.global_batch_size * t.seq_len * t.gradient_accumulation_steps,
         selected_device_count=trainer.mesh.world_size, process_count=trainer.mesh.world_size,
-        data_pipeline_backend="blackwell_native", data_pipeline_order=spec.data.order,
-        data_pipeline_shuffle_seed=spec.data.shuffle_seed,
+        data_pipeline_backend=pipeline_description.get("backend", "blackwell_native"),
+        data_pipeline_order=spec.data.order, data_pipeline_shuffle_seed=spec.data.shuffle_seed,
         data_document_aware=bool(last_row.get("document_aware")),
         moe_balance_policy=None if moe is None else moe.balance.name, z_loss_weight=t.loss.z_loss_weight,
         final_router_max_vio=last_row.get("router_max_vio"),
@@ -473,7 +521,21 @@ def _run_initialized(spec: RunSpec, config_path: Path, writer, resume: bool, pro
         final_router_mean_importance_entropy=last_row.get("router_mean_importance_entropy"),
         final_optimizer_groups=last_groups_row.get("optimizer_groups"),
         **{f"final_{k}": last_groups_row.get(k) for k in HEALTH_KEYS if k != "optimizer_route_backend_counts"},
-        final_optimizer_route_backend_counts=backend_counts, **diag,
+        final_optimizer_route_backend_counts=backend_counts,
+        final_moe_router_layers=next((r["moe_router_layers"] for r in reversed(rows) if r.get("moe_router_layers")),
+                                     None),
+        global_device_count=trainer.mesh.world_size, process_index=trainer.mesh.rank,
+        single_process=trainer.mesh.world_size == 1,
+        data_pipeline_version=pipeline_description.get("backend_version"),
+        data_pipeline_worker_count=pipeline_description.get("worker_count"),
+        data_pipeline_worker_buffer_size=pipeline_description.get("worker_buffer_size"),
+        data_pipeline_prefetch=pipeline_description.get("prefetch"),
+        data_pipeline_state_schema_version=pipeline_description.get("state_schema_version"),
+        data_document_count=pipeline_description.get("document_count"),
+        data_document_offsets_path=pipeline_description.get("document_offsets_path"),
+        data_document_offsets_sha256=pipeline_description.get("document_offsets_sha256"),
+        data_document_buffer_size=pipeline_description.get("document_buffer_size"),
+        data_document_refill_size=pipeline_description.get("document_refill_size"), **diag,
     )
 
 

@@ -304,3 +304,37 @@ def test_checkpoint_eval_and_sample_payloads(tmp_path):
             parse_prompt_ids(bad)
     with pytest.raises(ContractError, match="outside the vocabulary"):
         parse_prompt_ids([300], 256)
+
+
+def test_lifecycle_events_and_summary_carry_the_run_level_fields(tmp_path):
+    from research_b200.runtime.training import COMPLETED_EVENT_FIELDS, run_training
+
+    manifest = tiny_dataset(tmp_path)
+    raw = tiny_raw_config(manifest, kind="trinity", run_id="ev", output_dir=(tmp_path / "runs").as_posix(), steps=3)
+    summary = run_training(write_toml(raw, tmp_path / "ev.toml"))
+    run_dir = tmp_path / "runs" / "ev"
+    events = [json.loads(line) for line in (run_dir / "events.jsonl").read_text().splitlines()]
+    started = next(e for e in events if e["type"] == "training_started")
+    assert started["execution_mode"] == "replicated_data_parallel" and started["parallelism_mode"] == "ddp"
+    assert started["data_pipeline_backend"] == "blackwell_native" and started["data_pipeline_order"] == "document_buffer"
+    assert started["data_document_buffer_size"] == 8 and started["moe_balance_policy"] == "smebu"
+    assert started["gradient_accumulation_steps"] == 1 and started["z_loss_weight"] == 0.0 and started["resume"] is False
+    done = events[-1]
+    assert done["type"] == "training_completed" and set(COMPLETED_EVENT_FIELDS) <= set(done)
+    assert done["steps"] == 3 and done["final_loss"] == pytest.approx(summary.final_loss)
+    assert done["final_moe_router_layers"][0]["layer_index"] == 1 and done["final_optimizer_groups"]
+    final = json.loads((run_dir / "summaries" / "final.json").read_text())
+    assert final["single_process"] is True and final["process_index"] == 0 and final["global_device_count"] == 1
+    assert final["data_document_count"] == 300 and final["data_document_offsets_path"] == "document_offsets.u64"
+    assert final["data_pipeline_state_schema_version"] == 2 and final["data_pipeline_version"].startswith("research_b200-")
+    assert final["data_pipeline_worker_count"] == 0 and final["data_pipeline_prefetch"] is False
+    assert final["data_document_buffer_size"] == 8 and final["data_document_refill_size"] == 8
+    assert final["final_moe_router_layers"] == done["final_moe_router_layers"]
+    assert final["execution_mode"] == "replicated_data_parallel"
+    # a failing run says why in the same two keys the mirror and the inspector read
+    bad = tiny_raw_config(manifest, run_id="evbad", output_dir=(tmp_path / "runs").as_posix(), steps=3)
+    bad["training"]["target_tokens"] = 10 ** 9                                   # more than the data holds
+    with pytest.raises(Exception):
+        run_training(write_toml(bad, tmp_path / "evbad.toml"))
+    failed = [json.loads(l) for l in (tmp_path / "runs" / "evbad" / "events.jsonl").read_text().splitlines()][-1]
+    assert failed["type"] == "training_failed" and failed["error"] == failed["error_message"] and failed["error_type"]
