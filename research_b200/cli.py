@@ -404,11 +404,12 @@ def _profile(args: argparse.Namespace) -> int:
         report = analyze_profile_root(args.root, warmup_steps=args.warmup_steps)
         print(profile_analysis_to_json(report) if args.json else format_profile_analysis(report))
     else:
-        from research_b200.runtime.profile_bench import benchmark_component
+        from research_b200.runtime.profile_bench import benchmark_component, benchmark_to_json, format_benchmark
 
         report = benchmark_component(args.component, warmup=args.warmup, iters=args.iters,
                                      artifact_dir=args.artifact_dir, trace=args.trace)
-        _print_json(report) if args.json else print(json.dumps(report, indent=1))
+        if _is_rank0():
+            print(benchmark_to_json(report) if args.json else format_benchmark(report))
     return 0
 
 

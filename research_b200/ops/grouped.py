@@ -113,7 +113,12 @@ def grouped_expert_ffn(rows: torch.Tensor, counts: torch.Tensor, w_gate_up: torc
             continue
         h = Fn.swiglu(F.linear(seg, w_gate_up[e].to(seg.dtype)))
         pieces.append(F.linear(h, w_down[e].to(seg.dtype)))
-    return torch.cat(pieces, dim=0) if pieces else out
+    if pieces:
+        return torch.cat(pieces, dim=0)
+    # No row reached these experts.  The result must still be a function of ``rows``: under expert parallelism the
+    # exchanges before and after this call run in the backward pass of every rank or of none, and a result cut off
+    # from its input would take them out of this rank's backward while its peers wait in theirs.
+    return out + rows * 0
 
 
 # --------------------------------------------------------------------------------------------------

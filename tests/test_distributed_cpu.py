@@ -77,3 +77,52 @@ def test_layout_matches_single_process(tmp_path, name, kind, optimizer, mesh, pa
         assert torch.isfinite(t).all(), name_
         for other in results[1:]:
             assert torch.equal(t, other["model"][name_]), name_
+
+
+def _idle_rank_worker(rank, world, routing):
+    """One MoE layer, experts over all ranks, routing forced; returns the output and the input gradient."""
+
+    import torch
+
+    from research_b200.config.specs import MeshSpec, ModelSpec, MoeBalanceSpec, ParallelismSpec, TrinityMoeSpec, TrinitySpec
+    from research_b200.models.moe import SparseMoE
+    from research_b200.parallel.mesh import build_mesh_context, execution_context_for
+    from research_b200.runtime.profile_bench import FixedRouter, routing_ids
+
+    device = torch.device("cpu")
+    axes = {"data": 1} if world == 1 else {"data": 1, "ep": world}
+    mesh = build_mesh_context(MeshSpec(axis_names=tuple(axes), axis_sizes=tuple(axes.values())), device=device)
+    ex = execution_context_for(mesh, ParallelismSpec(mode="ddp", expert_parallel=world > 1))
+    experts, top_k, tokens, hidden, inter = 4, 2, 16, 32, 48
+    moe = TrinityMoeSpec(num_experts=experts, top_k=top_k, expert_intermediate_size=inter, capacity_factor=None,
+                         balance=MoeBalanceSpec())
+    spec = ModelSpec(name="trinity", variant="t", vocab_size=64, hidden_size=hidden, intermediate_size=inter,
+                     num_layers=2, num_heads=2, max_seq_len=tokens,
+                     trinity=TrinitySpec(initial_dense_layers=1, local_window=8, local_layers_per_global=1, moe=moe))
+    layer = SparseMoE(spec, moe, ex)
+    local = experts // world
+    gen = torch.Generator().manual_seed(7)
+    w_gate_up = torch.randn(experts, 2 * inter, hidden, generator=gen) * 0.1
+    w_down = torch.randn(experts, hidden, inter, generator=gen) * 0.1
+    with torch.no_grad():
+        layer.experts.w_gate_up.copy_(w_gate_up[rank * local:(rank + 1) * local])
+        layer.experts.w_down.copy_(w_down[rank * local:(rank + 1) * local])
+    layer.router = FixedRouter(routing_ids(routing, tokens, top_k, experts, device), experts)
+    x = torch.randn(1, tokens, hidden, generator=gen).requires_grad_(True)
+    y, _, _ = layer(x, ex, name="l", layer_index=0)
+    (y.square().sum()).backward()
+    grads = layer.experts.w_gate_up.grad
+    return {"y": y.detach(), "dx": x.grad.clone(), "dw_norm": None if grads is None else float(grads.norm())}
+
+
+@pytest.mark.parametrize("routing", ["skewed", "balanced"])
+def test_expert_parallel_backward_completes_when_a_rank_receives_no_token(routing):
+    """With every token routed to the experts of rank 0, rank 1 computes nothing, yet it must run the same exchanges
+    in its backward pass as rank 0 does: the run finishes and matches the single-process layer."""
+
+    (ref,) = run_gloo(1, _idle_rank_worker, routing)
+    got = run_gloo(2, _idle_rank_worker, routing)
+    for r in got:
+        assert torch.allclose(r["y"], ref["y"], atol=1e-5) and torch.allclose(r["dx"], ref["dx"], atol=1e-5)
+    if routing == "skewed":
+        assert got[0]["dw_norm"] > 0 and not got[1]["dw_norm"]          # the idle rank's experts get no gradient
