@@ -37,6 +37,22 @@ PARAM_ENVELOPE = 1.25e-3
 UPDATE_ATOL = UPDATE_ENVELOPE * BENCH_LR / CALIBRATION_LR
 PARAM_ATOL = PARAM_ENVELOPE * BENCH_LR / CALIBRATION_LR
 WEIGHT_DECAY = 0.01
+STABILITY_LIMIT = 0.05             # median absolute deviation over the median of a candidate's timings
+SELECTION_MIN_SPEEDUP = 1.05       # what a distributed execution must gain over the duplicated one to be selected
+SELECTION_TIE_FRACTION = 0.03
+
+
+def benchmark_contract() -> dict[str, Any]:
+    """The numerical and measurement policy of the selector, as data (reference: muon_bench.py:854-874)."""
+
+    return {"correctness_steps": 5, "benchmark_learning_rate": BENCH_LR,
+            "reference_calibration_learning_rate": CALIBRATION_LR, "reference_update_atol": UPDATE_ENVELOPE,
+            "reference_parameter_atol": PARAM_ENVELOPE, "tolerance_scaling": "linear_with_learning_rate",
+            "update_atol": UPDATE_ATOL, "parameter_atol": PARAM_ATOL, "candidate_order": "rotating",
+            "timing_reducer": "median", "tail_percentile": 95,
+            "stability_metric": "median_abs_deviation_over_median", "stability_limit": STABILITY_LIMIT,
+            "selection_min_speedup": SELECTION_MIN_SPEEDUP, "selection_tie_fraction": SELECTION_TIE_FRACTION,
+            "timing_is_production_acceptance_gate": False}
 
 
 @dataclass(frozen=True)
@@ -276,9 +292,19 @@ def benchmark_case(leaf: Leaf, count: int, name: str, kind: str, group, device, 
     for c in candidates:
         rows_out.append({"execution": c.execution, **checks[c.execution], "timing_ms": timing_summary(c.timings),
                          "collectives": collective_operand_model(leaf.shape, c.execution, world)})
+    for r in rows_out:
+        t = r["timing_ms"]
+        r["stability"] = t["median_abs_deviation"] / t["median"] if t["median"] > 0 else None
+        r["stable"] = r["stability"] is not None and r["stability"] <= STABILITY_LIMIT
     passing = [r for r in rows_out if r["correctness_gate"]]
     best = min(passing, key=lambda r: r["timing_ms"]["median"]) if passing else None
     duplicated = next(r for r in rows_out if r["execution"] == "duplicated")
+    reason = None if best is None else "fastest_passing_candidate"
+    if best is not None and best is not duplicated and duplicated["correctness_gate"]:
+        # a distributed execution replaces the exact duplicated one only for a clear gain
+        gain = duplicated["timing_ms"]["median"] / max(best["timing_ms"]["median"], 1e-9)
+        if gain < SELECTION_MIN_SPEEDUP:
+            best, reason = duplicated, "gain_below_selection_min_speedup"
     return {
         "case": name, "kind": kind, "role": leaf.role, "logical_shape": list(leaf.shape),
         "tp_partition_dim": leaf.tp_partition_dim, "leaf_count": count,
@@ -287,6 +313,7 @@ def benchmark_case(leaf: Leaf, count: int, name: str, kind: str, group, device, 
                             "tp_size": world, "leaf_count": count,
                             "aggregate_matrix_elements": math.prod(leaf.shape) * count},
         "candidates": rows_out, "selected": None if best is None else best["execution"],
+        "selection_reason": reason,
         "speedup_vs_duplicated": None if best is None else
         duplicated["timing_ms"]["median"] / max(best["timing_ms"]["median"], 1e-9),
     }
@@ -340,7 +367,7 @@ def benchmark_muon(*, warmup: int = 2, iters: int = 5, artifact_dir: str | Path 
         "transport": type(reducer).__name__, "benchmark_learning_rate": BENCH_LR,
         "envelope": {"update_atol": UPDATE_ATOL, "parameter_atol": PARAM_ATOL,
                      "calibration": {"lr": CALIBRATION_LR, "update": UPDATE_ENVELOPE, "parameter": PARAM_ENVELOPE}},
-        "gram_bucket_max_bytes": dns.GRAM_BUCKET_MAX_BYTES, "cases": rows,
+        "gram_bucket_max_bytes": dns.GRAM_BUCKET_MAX_BYTES, "contract": benchmark_contract(), "cases": rows,
         "selection": {r["case"]: r.get("selected") for r in rows if "skipped" not in r},
         "all_selected_pass": all(r.get("selected") is not None for r in rows if "skipped" not in r),
     }

@@ -202,8 +202,8 @@ def benchmark_component(component: str, *, warmup: int = 3, iters: int = 10, art
         muon = benchmark_muon(warmup=warmup, iters=iters, artifact_dir=artifact_dir)
         report = {**envelope, **muon, "device_count": muon.get("tp_size"), "correctness_is_checked": True,
                   "known_correctness_constraint": "duplicated_five_step_calibrated_envelope",
-                  "measurement_contract": {"timer": "cuda_events" if device.type == "cuda" else "perf_counter",
-                                           "reducer": "median", "selection": "fastest_candidate_inside_the_envelope"}}
+                  "measurement_contract": {**muon["contract"], "reducer": "median",
+                                           "timer": "host_clock_around_a_synchronised_step_max_over_ranks"}}
     if artifact_dir:
         out = Path(artifact_dir)
         out.mkdir(parents=True, exist_ok=True)

@@ -136,7 +136,16 @@ def test_selector_checks_every_candidate_and_picks_one():
             assert c["finite"] and c["momentum_exact"] and c["deterministic"], (case["case"], name, c)
             assert c["replica_max_abs_error"] == 0.0 and c["correctness_gate"], (case["case"], name, c)
             assert c["timing_ms"]["min"] <= c["timing_ms"]["median"] <= c["timing_ms"]["max"]
-        assert case["selected"] in by
+        assert case["selected"] in by and case["selection_reason"] in ("fastest_passing_candidate",
+                                                                        "gain_below_selection_min_speedup")
+        chosen, dup = by[case["selected"]], by["duplicated"]
+        if case["selected"] != "duplicated":                                # a distributed pick needs a clear gain
+            assert dup["timing_ms"]["median"] / chosen["timing_ms"]["median"] >= mb.SELECTION_MIN_SPEEDUP
+        assert all(c["stability"] >= 0 and isinstance(c["stable"], bool) for c in by.values())
     kv = next(c for c in report["cases"] if c["case"] == "attention_kv")
     assert {c["execution"] for c in kv["candidates"]} == {"duplicated", "distributed_large_gram", "distributed_exchange"}
     assert reports[1]["selection"] == report["selection"]              # every rank reaches the same verdict
+    contract = report["contract"]
+    assert contract == mb.benchmark_contract() and contract["selection_min_speedup"] == 1.05
+    assert contract["update_atol"] == mb.UPDATE_ATOL and contract["stability_limit"] == 0.05
+    assert contract["timing_is_production_acceptance_gate"] is False and contract["correctness_steps"] == 5
