@@ -177,3 +177,64 @@ def test_adamw_route_rule_without_weight_decay_is_not_decayed(tmp_path):
         moved = not torch.equal(e.param.detach(), before[e.name])
         is_norm = all(m.tag == "final_norm" for m in e.metas)
         assert moved != is_norm, (e.name, moved)
+
+
+def _newton_schulz_restated(x):
+    """The quintic iteration spelled out (bf16, left Gram of the wide orientation)."""
+
+    x = x.to(torch.bfloat16)
+    x = x / torch.clamp(torch.linalg.matrix_norm(x.float()).to(torch.bfloat16), min=1e-7)
+    wide = x.shape[0] <= x.shape[1]
+    if not wide:
+        x = x.t()
+    a, b, c = 3.4445, -4.7750, 2.0315
+    for _ in range(5):
+        gram = x @ x.t()
+        x = a * x + (b * gram + c * (gram @ gram)) @ x
+    return (x if wide else x.t()).float()
+
+
+@pytest.mark.parametrize("kind", ["decoder", "trinity"])
+def test_muon_step_matches_the_update_rule(tmp_path, kind):
+    """``m <- 0.95 m + 0.05 g``; Nesterov input ``0.05 g + 0.95 m``; five Newton-Schulz steps in bf16; step
+    ``lr * 0.2 * sqrt(max(rows, cols))``; decoupled decay ``lr * wd * p`` (reference: src/jaxtitan/optim/muon.py:97-127)."""
+
+    from tests.helpers import tiny_dataset
+    from research_b200.runtime.trainer import Trainer
+
+    manifest = tiny_dataset(tmp_path)
+    raw = tiny_raw_config(manifest, kind=kind, optimizer="muon", clip=None)
+    raw["optimizer"]["schedule"] = {"peak_lr": 2e-2}
+    raw["optimizer"]["weight_decay"] = 0.1
+    trainer = Trainer(run_spec_from_mapping(raw), device="cpu")
+    lr, wd = 2e-2, 0.1
+    entries = [e for e in trainer.store.entries if e.backend == "muon"]
+    assert entries and any(e.param.dim() == 3 for e in entries) == (kind == "trinity")
+    torch.manual_seed(0)
+    momentum = {e.name: torch.zeros_like(e.param) for e in entries}
+    expected = {e.name: e.param.detach().clone() for e in entries}
+    for _ in range(2):
+        trainer.store.zero_grads()
+        grads = {}
+        for e in trainer.store.entries:
+            g = torch.randn_like(e.param) * 0.1
+            e.param.main_grad.copy_(g)
+            grads[e.name] = g
+        for e in entries:
+            g, m, w = grads[e.name], momentum[e.name], expected[e.name]
+            m.mul_(0.95).add_(g, alpha=0.05)
+            inp = 0.05 * g + 0.95 * m
+            for meta in e.metas:
+                rows = slice(None) if meta.rows is None else slice(*meta.rows)
+                blocks = [(inp[x, rows], w[x, rows]) for x in range(w.shape[0])] if w.dim() == 3 else [(inp[rows], w[rows])]
+                for block_in, block_w in blocks:
+                    step = lr * 0.2 * math.sqrt(max(block_in.shape))
+                    block_w.mul_(1.0 - lr * wd).add_(_newton_schulz_restated(block_in), alpha=-step)
+        trainer.optimizer.step()
+    for e in entries:
+        step = lr * 0.2 * math.sqrt(max(e.param.shape[-2:]))
+        # a momentum of 0.90 instead of 0.95 already moves entries by 0.02 of a step after two updates
+        assert torch.allclose(e.param.detach(), expected[e.name], atol=0.004 * step, rtol=0), e.name
+    # everything else took AdamW: embedding, head, norms, router
+    others = {m.tag for e in trainer.store.entries if e.backend == "adamw" for m in e.metas}
+    assert {"embedding", "lm_head", "final_norm"} <= others
