@@ -238,3 +238,68 @@ def test_muon_step_matches_the_update_rule(tmp_path, kind):
     # everything else took AdamW: embedding, head, norms, router
     others = {m.tag for e in trainer.store.entries if e.backend == "adamw" for m in e.metas}
     assert {"embedding", "lm_head", "final_norm"} <= others
+
+
+def _polar_express_restated(x):
+    x = x.to(torch.bfloat16)
+    x = x / (torch.linalg.matrix_norm(x.float()).to(torch.bfloat16) * 1.02 + 1e-8)
+    tall = x.shape[0] > x.shape[1]
+    for a, b, c in orth.DION2_POLAR_EXPRESS_COEFFICIENTS:
+        gram = x.t() @ x if tall else x @ x.t()
+        poly = b * gram + c * (gram @ gram)
+        x = a * x + (x @ poly if tall else poly @ x)
+    return x.float()
+
+
+def test_dion2_step_matches_the_update_rule(tmp_path):
+    """Momentum takes the whole gradient; the quarter of the rows (or columns) with the largest L1 norm is
+    orthogonalised with Polar Express, applied with ``lr * sqrt(fan_in / fan_out)`` and kept in the momentum at 0.95
+    of its value; the rest of the momentum stays (reference: src/jaxtitan/optim/dion2.py:62-98)."""
+
+    from tests.helpers import tiny_dataset
+    from research_b200.runtime.trainer import Trainer
+
+    manifest = tiny_dataset(tmp_path)
+    raw = tiny_raw_config(manifest, optimizer="dion", clip=None)
+    raw["optimizer"]["schedule"] = {"peak_lr": 1e-2}
+    raw["optimizer"]["weight_decay"] = 0.1
+    trainer = Trainer(run_spec_from_mapping(raw), device="cpu")
+    lr, wd = 1e-2, 0.1
+    routes = {a.name: a for a in trainer.optimizer_build.route_assignments}
+    entries = [e for e in trainer.store.entries if e.backend == "dion2"]
+    assert entries
+    torch.manual_seed(0)
+    momentum = {e.name: torch.zeros_like(e.param) for e in entries}
+    expected = {e.name: e.param.detach().clone() for e in entries}
+    for _ in range(3):
+        trainer.store.zero_grads()
+        grads = {}
+        for e in trainer.store.entries:
+            g = torch.randn_like(e.param) * 0.1
+            e.param.main_grad.copy_(g)
+            grads[e.name] = g
+        for e in entries:
+            momentum[e.name].add_(grads[e.name])
+            for meta in e.metas:
+                rows = slice(None) if meta.rows is None else slice(*meta.rows)
+                m, w = momentum[e.name][rows], expected[e.name][rows]
+                logical_axis = routes[meta.name].matrix_axis or 0
+                axis = (1 - logical_axis) if meta.transposed else logical_axis      # in the stored orientation
+                k = max(1, math.ceil(0.25 * m.shape[axis]))
+                idx = m.abs().sum(dim=1 - axis).topk(k).indices
+                picked = m.index_select(axis, idx)
+                fan_in, fan_out = meta.shape                                         # logical [in, out]
+                w.mul_(1.0 - lr * wd)
+                w.index_add_(axis, idx, _polar_express_restated(picked), alpha=-lr * math.sqrt(fan_in / fan_out))
+                m.index_copy_(axis, idx, picked * 0.95)
+        trainer.optimizer.step()
+    for e in entries:
+        assert torch.allclose(e.param.detach(), expected[e.name], atol=2e-5, rtol=0), e.name
+    # the error-feedback part of the momentum: rows never picked hold the plain sum of their gradients
+    probe = entries[0]
+    state_mom = None
+    for i, sec in enumerate(trainer.store.sections):
+        if probe in sec.entries:
+            lo, _ = trainer.store.local_master_range(sec)
+            state_mom = trainer.optimizer.state[i]["momentum"][probe.offset - lo:probe.offset - lo + probe.numel]
+    assert torch.allclose(state_mom.view(probe.param.shape), momentum[probe.name], atol=1e-6)
