@@ -65,9 +65,23 @@ def require_single_node_runtime(world_size: int) -> None:
         )
 
 
+_group_timeout_s: float | None = None        # the default group's collective timeout, handed on to the axis groups
+
+
+def _axis_group_timeout():
+    """Collective timeout of the per-axis groups: ``RESEARCH_B200_GROUP_TIMEOUT_S`` if set, else the timeout the
+    default group was created with here, else the library's default (30 minutes).  Without it a subgroup ignores
+    the timeout of the default group, and a rank waiting for a peer that left would wait for half an hour."""
+
+    raw = os.environ.get("RESEARCH_B200_GROUP_TIMEOUT_S")
+    seconds = float(raw) if raw else _group_timeout_s
+    return None if seconds is None else datetime.timedelta(seconds=seconds)
+
+
 def init_distributed(backend: str | None = None, timeout_s: float = 600.0) -> tuple[int, int]:
     """Initialise the default process group from the torchrun environment; returns (rank, world_size)."""
 
+    global _group_timeout_s
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     if world == 1:
@@ -84,6 +98,7 @@ def init_distributed(backend: str | None = None, timeout_s: float = 600.0) -> tu
             kwargs["device_id"] = torch.device("cuda", local_rank)
         dist.init_process_group(backend=backend, rank=rank, world_size=world,
                                 timeout=datetime.timedelta(seconds=timeout_s), **kwargs)
+        _group_timeout_s = float(timeout_s)
     return rank, world
 
 
@@ -114,7 +129,7 @@ def build_mesh_context(spec: MeshSpec, *, device: torch.device | None = None) ->
             moved = np.moveaxis(grid, ax, -1).reshape(-1, sizes[ax])
             mine = None
             for ranks in moved:
-                g = dist.new_group(ranks=[int(r) for r in ranks])
+                g = dist.new_group(ranks=[int(r) for r in ranks], timeout=_axis_group_timeout())
                 if rank in ranks:
                     mine = g
             groups[name] = mine

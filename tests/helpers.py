@@ -99,12 +99,19 @@ def write_toml(raw: dict, path: Path) -> Path:
 
 GLOO_COLLECTIVE_TIMEOUT_S = 180
 GLOO_RUN_DEADLINE_S = 420
+GLOO_HANG_DUMP_S = 150
 
 
 def _worker(rank: int, world: int, port: int, fn, args, out_dir: str):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), LOCAL_WORLD_SIZE=str(world),
-                      MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+                      MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                      RESEARCH_B200_GROUP_TIMEOUT_S=str(GLOO_COLLECTIVE_TIMEOUT_S))
     torch.set_num_threads(1)
+    # a rank that is still running shortly before the deadline writes the stack of every thread next to its result
+    import faulthandler
+
+    hang_file = open(os.path.join(out_dir, f"rank{rank}.hang"), "w")
+    faulthandler.dump_traceback_later(GLOO_HANG_DUMP_S, file=hang_file, exit=False)
     try:
         import datetime
 
@@ -117,6 +124,7 @@ def _worker(rank: int, world: int, port: int, fn, args, out_dir: str):
         torch.save(result, os.path.join(out_dir, f"rank{rank}.pt"))
         dist.barrier()
         dist.destroy_process_group()
+        faulthandler.cancel_dump_traceback_later()
     except Exception:
         with open(os.path.join(out_dir, f"rank{rank}.err"), "w") as handle:
             handle.write(traceback.format_exc())
@@ -147,7 +155,9 @@ def _run_gloo_once(world: int, fn, args):
         if err.exists():
             errors.append(f"rank {r}:\n{err.read_text()}")
         elif r in stuck:
-            errors.append(f"rank {r} was still running after {GLOO_RUN_DEADLINE_S} s")
+            hang = Path(out_dir) / f"rank{r}.hang"
+            stacks = hang.read_text() if hang.exists() else ""
+            errors.append(f"rank {r} was still running after {GLOO_RUN_DEADLINE_S} s\n{stacks}")
         elif p.exitcode != 0:
             errors.append(f"rank {r} exited with code {p.exitcode}")
     if errors:
