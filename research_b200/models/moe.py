@@ -140,6 +140,9 @@ class SparseMoE(nn.Module):
                                 f"expert_fsdp axis size ({shards})")
         self.router = Router(spec.hidden_size, moe.num_experts, moe.top_k, moe.route_scale, moe.router)
         self.expert_bias = nn.Parameter(torch.zeros(moe.num_experts, dtype=torch.float32), requires_grad=False)
+        # fp32 master of the bias when the parameter itself is held in a narrower compute precision (set by the
+        # balance policy): selection then sees the exact bias
+        self.bias_master: torch.Tensor | None = None
         self.experts = Experts(spec.hidden_size, moe.expert_intermediate_size // shards, self.num_local)
         self.shared_experts = None
         if moe.num_shared_experts > 0:
@@ -198,7 +201,7 @@ class SparseMoE(nn.Module):
         from research_b200.parallel.expert import dispatch_and_combine
 
         B, S, H = x.shape
-        expert_ids, weights, scores = self.router(x, self.expert_bias)
+        expert_ids, weights, scores = self.router(x, self.expert_bias if self.bias_master is None else self.bias_master)
         dropped = None
         plan = None
         y_routed = None          # set when a path below has already run dispatch, experts and combine

@@ -168,7 +168,7 @@ def iter_state_tensors(trainer, *, writer_only: bool = False):
             yield leaf, (t.cpu().numpy() if want else None)
     if trainer.moe_balance is not None:
         for i, layer in enumerate(trainer.moe_balance.layers):
-            yield f"moe_balance.layers.{i}.momentum", (layer.momentum.detach().cpu().numpy() if want else None)
+            yield f"moe_balance.layers.{i}.momentum", (layer.momentum.detach().float().cpu().numpy() if want else None)
 
 
 def collect_state_tensors(trainer) -> dict[str, np.ndarray]:

@@ -134,7 +134,7 @@ class Trainer:
             self.result.model.layer_prepare = self.store.acquire_layer
         self.optimizer = Optimizer(self.optimizer_build, self.store)
         moe = spec.model.trinity.moe if spec.model.trinity is not None else None
-        self.moe_balance = init_moe_balance(self.result.model, None if moe is None else moe.balance)
+        self.moe_balance = init_moe_balance(self.result.model, None if moe is None else moe.balance, store=self.store)
         self.train_step_fn = TrainStep(spec, self.result, self.store, self.optimizer, self.mesh, self.moe_balance)
         self.eval_step_fn = EvalStep(self.result, self.store, self.mesh)
         self.rng = RngState.from_seed(spec.seed)

@@ -19,8 +19,9 @@ from research_b200.errors import ContractError
 @dataclass
 class MoeBalanceLayer:
     path: str
-    bias: torch.Tensor        # the model's expert_bias parameter data [E]
+    bias: torch.Tensor        # fp32 [E]: the parameter's data, or its fp32 master when the compute copy is narrower
     momentum: torch.Tensor    # [E] fp32
+    entry: Any = None         # the parameter store's entry of the bias when ``bias`` is a master that has a copy
 
 
 @dataclass
@@ -31,21 +32,43 @@ class MoeBalanceState:
     clamp: float
     layers: list[MoeBalanceLayer]
     kernel: Any = None        # device pointer table of the native update, built on first use
+    store: Any = None         # parameter store that holds compute-precision copies of the biases
 
 
-def init_moe_balance(model, balance: MoeBalanceSpec | None) -> MoeBalanceState | None:
+def init_moe_balance(model, balance: MoeBalanceSpec | None, store=None) -> MoeBalanceState | None:
+    """With a parameter store whose compute copies are narrower than fp32 the bias that is balanced is the fp32
+    master of the store (the reference keeps ``expert_bias`` in fp32, models/components/moe.py:165-167): the router
+    reads it through ``mlp.bias_master`` and the compute copy is refreshed after every update."""
+
     if balance is None or balance.name == "none":
         return None
     if balance.name != "smebu":
         raise ContractError(f"unsupported MoE balance policy {balance.name!r}")
+    by_param = {} if store is None else {id(e.param): e for e in store.entries}
     layers = []
     for i, layer in enumerate(model.layers):
         if getattr(layer, "is_moe", False):
-            bias = layer.mlp.expert_bias.data
-            layers.append(MoeBalanceLayer(f"layers.{i}.mlp.expert_bias", bias, torch.zeros_like(bias)))
+            param = layer.mlp.expert_bias
+            bias, entry = param.data, by_param.get(id(param))
+            if entry is not None:
+                master = store.master_view(store.section_of(entry), entry)
+                if master is not None and master.dtype == torch.float32 and param.data.dtype != torch.float32:
+                    bias = master
+                    layer.mlp.bias_master = master
+                else:
+                    entry = None
+            layers.append(MoeBalanceLayer(f"layers.{i}.mlp.expert_bias", bias,
+                                          torch.zeros_like(bias, dtype=torch.float32), entry))
     if not layers:
         return None
-    return MoeBalanceState("smebu", float(balance.load_lr), float(balance.momentum), float(balance.clamp), layers)
+    return MoeBalanceState("smebu", float(balance.load_lr), float(balance.momentum), float(balance.clamp), layers,
+                           store=store)
+
+
+def _refresh_compute_copies(state: MoeBalanceState) -> None:
+    for layer in state.layers:
+        if layer.entry is not None:
+            state.store.write_entry_shadow(layer.entry, layer.bias)
 
 
 @torch.no_grad()
@@ -66,6 +89,7 @@ def apply_moe_balance_update(state: MoeBalanceState | None, router_counts: torch
             state.kernel = router_ops.SmebuKernelState(biases, momenta)
         bias_sq, mom_sq = router_ops.smebu_update(state.kernel, router_counts, state.load_lr, state.clamp,
                                                   state.momentum_factor)
+        _refresh_compute_copies(state)
         return {"smebu_bias_norm": bias_sq.sqrt(), "smebu_momentum_norm": mom_sq.sqrt()}
     bias_sq = torch.zeros((), device=router_counts.device)
     mom_sq = torch.zeros((), device=router_counts.device)
@@ -78,6 +102,7 @@ def apply_moe_balance_update(state: MoeBalanceState | None, router_counts: torch
         layer.bias.add_(layer.momentum.to(layer.bias.dtype))
         bias_sq = bias_sq + layer.bias.float().pow(2).sum()
         mom_sq = mom_sq + layer.momentum.pow(2).sum()
+    _refresh_compute_copies(state)
     return {"smebu_bias_norm": bias_sq.sqrt(), "smebu_momentum_norm": mom_sq.sqrt()}
 
 

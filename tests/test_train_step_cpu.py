@@ -174,3 +174,37 @@ def test_moe_step_reports_router_statistics_and_moves_the_bias(manifest):
     assert row["layer_index"] == 1 and "load_cv" in row and "importance_entropy" in row and row["experts_active"] == 4
     assert not torch.equal(bias.detach(), before) and abs(float(bias.sum())) < 1e-6     # SMEBU: centred update
     assert metrics.smebu["smebu_bias_norm"] > 0
+
+
+def test_narrow_compute_precision_keeps_the_balance_bias_in_fp32_and_in_the_checkpoint(tmp_path, manifest):
+    """With bf16 compute copies the expert bias that SMEBU moves is the fp32 master: the router reads it, the bf16
+    copy follows it, the checkpoint stores it with its momentum, and a resumed run continues from it."""
+
+    from research_b200.runtime.training import run_training
+    from research_b200.services.checkpoints import read_array
+    from tests.helpers import write_toml
+
+    raw = tiny_raw_config(manifest, kind="trinity", run_id="bf", output_dir=(tmp_path / "runs").as_posix(), steps=4,
+                          checkpoint_every=2, evals=True)
+    raw["model"]["compute_dtype"] = "bfloat16"
+    raw["training"]["precision"] = "bf16"
+    seen = {}
+    run_training(write_toml(raw, tmp_path / "bf.toml"), trainer_hook=lambda t: seen.setdefault("first", t))
+    mlp = seen["first"].result.model.layers[1].mlp
+    assert mlp.expert_bias.dtype == torch.bfloat16 and mlp.bias_master.dtype == torch.float32
+    assert float(mlp.bias_master.abs().max()) > 0 and abs(float(mlp.bias_master.sum())) < 1e-6
+    assert torch.equal(mlp.expert_bias.data, mlp.bias_master.to(torch.bfloat16))          # the copy follows the master
+    layer = seen["first"].moe_balance.layers[0]
+    assert layer.bias.data_ptr() == mlp.bias_master.data_ptr() and layer.momentum.dtype == torch.float32
+    leaf = tmp_path / "runs" / "bf" / "checkpoints" / "000004" / "train"
+    assert np.allclose(read_array(leaf / "model.layers.1.mlp.expert_bias"), mlp.bias_master.numpy(), atol=0)
+    assert np.allclose(read_array(leaf / "moe_balance.layers.0.momentum"), layer.momentum.numpy(), atol=0)
+    raw["training"]["target_tokens"] = 32 * 4 * 6
+    before = mlp.bias_master.clone()
+    run_training(write_toml(raw, tmp_path / "bf.toml"), resume=True,
+                 trainer_hook=lambda t: seen.setdefault("second", t))
+    resumed = seen["second"].result.model.layers[1].mlp
+    assert not torch.equal(resumed.bias_master, before) and seen["second"].step == 6
+    # full precision compute: the parameter itself is the fp32 bias, nothing to mirror
+    plain = _trainer(manifest, kind="trinity")
+    assert plain.result.model.layers[1].mlp.bias_master is None and plain.moe_balance.layers[0].entry is None
