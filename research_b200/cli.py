@@ -363,30 +363,15 @@ def _kernels(args: argparse.Namespace) -> int:
     from research_b200.kernels import registry
 
     if args.kernels_command == "list":
-        rows = registry.kernel_registry()
-        if args.json:
-            _print_json({"schema_version": 1, "kernels": rows})
-        else:
-            for r in rows:
-                print(f"{r['op']:<26} {r['symbol']:<32} {r['engine']:<28} built={r['built']}")
+        print(canonical_json(registry.kernel_registry_payload()) if args.json else registry.format_kernel_registry())
     elif args.kernels_command == "check":
-        plan = registry.kernel_plan(load_config(args.path))
-        if args.json:
-            _print_json(plan)
-        else:
-            print(f"kernel plan: active={plan['active']} library_present={plan['library_present']}")
-            for op in plan["ops"]:
-                print(f"  {op['op']:<26} selected={op['selected']} fallback={op['fallback']}")
+        plan = registry.enrich_kernel_plan_with_cache(registry.kernel_plan(load_config(args.path)))
+        print(registry.kernel_plan_to_json(plan) if args.json else registry.format_kernel_plan(plan))
     elif args.kernels_command == "compile":
-        from research_b200.kernels.build import build_all
-
         if args.arch and args.arch.upper() not in ("SM100", "SM_100A", "SM100A"):
             raise ContractError(f"unsupported kernel architecture {args.arch!r}; this build targets SM100 (sm_100a) only")
-        result = build_all()
-        payload = {"schema_version": 1, "arch": "sm_100a", "library": str(result.kernel_lib), "rebuilt": result.rebuilt,
-                   "sources": list(result.sources), "digest": result.digest,
-                   "plan": registry.kernel_plan(load_config(args.path))}
-        _print_json(payload) if args.json else print(f"built {result.kernel_lib} (rebuilt={result.rebuilt})")
+        payload = registry.compile_kernel_plan(load_config(args.path))
+        _print_json(payload) if args.json else print(registry.format_compile_result(payload))
     elif args.kernels_command == "bench":
         from research_b200.kernels.bench import benchmark_kernel
 

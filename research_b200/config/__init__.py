@@ -19,8 +19,11 @@ __all__ = [
     "resolved_config_sha256",
     "run_spec_from_mapping",
     "run_spec_from_resolved",
+    "run_spec_from_resolved_mapping",
     "run_spec_to_dict",
     "run_spec_to_json",
     "source_config_sha256",
     "validate_run_spec",
 ]
+
+run_spec_from_resolved_mapping = run_spec_from_resolved       # the reference's name for it

@@ -117,3 +117,16 @@ def format_inspection(report: dict[str, Any]) -> str:
         out.append(f"records: seq_len={records['seq_len']} train={records['train']:,} val={records['val']:,}")
     out += ["", "training config:", report["data_config_toml"]]
     return "\n".join(out)
+
+
+# the reference's names for the same operations (src/jaxtitan/data/inspect.py)
+inspect_dataset_manifest = inspect_dataset
+format_data_inspection = format_inspection
+
+
+def data_inspection_to_dict(report: dict[str, Any]) -> dict[str, Any]:
+    return dict(report)
+
+
+def data_inspection_to_json(report: dict[str, Any]) -> str:
+    return json.dumps(report, sort_keys=True, separators=(",", ":"))

@@ -32,6 +32,10 @@ STATE_SCHEMA_VERSION = 2
 BACKEND = "blackwell_native"
 NUM_EPOCHS = 1
 DROP_REMAINDER = True
+DEFAULT_ORDER = "sequential"
+DEFAULT_WORKER_COUNT = 0
+DEFAULT_WORKER_BUFFER_SIZE = 1
+DEFAULT_PREFETCH = False
 
 
 def backend_version() -> str:

@@ -126,6 +126,10 @@ def _table(raw: Mapping[str, Any], key: str, required: bool) -> Mapping[str, Any
     return raw[key]
 
 
+TOKEN_BYTES_FILENAME = "token_bytes.bin"
+DOCUMENT_OFFSETS_FILENAME = "document_offsets.u64"
+
+
 def load_prepare_config(path: str | Path) -> PrepareConfig:
     p = Path(path)
     try:
@@ -134,6 +138,12 @@ def load_prepare_config(path: str | Path) -> PrepareConfig:
         raise ConfigError(f"failed to read config {p}: {exc}") from exc
     except tomllib.TOMLDecodeError as exc:
         raise ConfigError(f"failed to parse config {p}: {exc}") from exc
+    return prepare_config_from_mapping(raw)
+
+
+def prepare_config_from_mapping(raw: Mapping[str, Any]) -> PrepareConfig:
+    """The ``[source] / [tokenizer] / [output] / [tokenization]`` tables of a prepare config as a :class:`PrepareConfig`."""
+
     src, tok, out = _table(raw, "source", True), _table(raw, "tokenizer", True), _table(raw, "output", True)
     tz = _table(raw, "tokenization", False)
     for section, key, table in (("source", "type", src), ("tokenizer", "name", tok), ("output", "path", out)):
@@ -425,9 +435,9 @@ def prepare_dataset(config_path: str | Path, *, overwrite: bool = False) -> dict
     pos = int(np.searchsorted(off, val_start, side="left"))
     val_start = int(off[min(pos, len(off) - 1)])
     val_start = min(max(val_start, 1), total - 1)
-    (out_dir / "document_offsets.u64").write_bytes(off.tobytes())
+    (out_dir / DOCUMENT_OFFSETS_FILENAME).write_bytes(off.tobytes())
     tb = tok.token_byte_lengths().astype("<u2")
-    (out_dir / "token_bytes.bin").write_bytes(tb.tobytes())
+    (out_dir / TOKEN_BYTES_FILENAME).write_bytes(tb.tobytes())
     elapsed = time.perf_counter() - started
     from research_b200.services.artifacts import utc_now
 
@@ -460,3 +470,31 @@ def prepare_dataset(config_path: str | Path, *, overwrite: bool = False) -> dict
     summary = dataset_manifest_summary(validated)
     summary["num_tokens"] = total
     return summary
+
+
+def build_token_bytes(tokenizer) -> np.ndarray:
+    """UTF-8 byte length of every token id as ``uint16`` (EOT counts zero): the table behind bits per byte."""
+
+    return tokenizer.token_byte_lengths().astype("<u2")
+
+
+def load_hf_texts(source: PrepareSourceConfig) -> Iterator[str]:
+    """The documents of a Hugging Face source (``source.type = "hf"``) as strings."""
+
+    if source.type != "hf":
+        raise ContractError(f"load_hf_texts needs source.type='hf', got {source.type!r}")
+    return iter_texts(source, Path.cwd())
+
+
+def prepare_result_to_dict(summary: Mapping[str, Any]) -> dict[str, Any]:
+    return dict(summary)
+
+
+def prepare_result_to_json(summary: Mapping[str, Any]) -> str:
+    return json.dumps(dict(summary), sort_keys=True, separators=(",", ":"))
+
+
+def format_prepare_result(summary: Mapping[str, Any]) -> str:
+    return (f"prepared {summary['num_tokens']:,} tokens at {summary['manifest_path']} "
+            f"(train {summary['train_tokens']:,}, val {summary['val_tokens']:,}, shards {summary['shard_count']}, "
+            f"documents {summary['document_count']})")

@@ -185,6 +185,34 @@ def _graph_ok(model, device: torch.device) -> bool:
     return device.type == "cuda" and getattr(model, "compute_dtype", None) == torch.bfloat16
 
 
+KVCache = PagedKVCache
+
+
+@torch.no_grad()
+def prefill(model, prompt_ids: torch.Tensor, cache: PagedKVCache) -> torch.Tensor:
+    """Run the prompt ``[B, P]`` through the model, fill ``cache`` and return the logits of the last position
+    ``[B, V]`` (reference: src/jaxtitan/infer/core.py ``prefill``)."""
+
+    B, P = prompt_ids.shape
+    device = next(model.parameters()).device
+    positions = torch.arange(P, device=device, dtype=torch.int32).expand(B, P).contiguous()
+    logits = model.run_with_cache(prompt_ids.to(device=device, dtype=torch.int32), positions, cache, last_only=True)
+    cache.advance(positions)
+    return logits[:, -1]
+
+
+@torch.no_grad()
+def decode_one(model, token: torch.Tensor, position: int, cache: PagedKVCache) -> torch.Tensor:
+    """One decode step: ``token`` ``[B]`` at ``position`` -> next-token logits ``[B, V]``; the cache grows by one."""
+
+    B = token.shape[0]
+    device = next(model.parameters()).device
+    pos = torch.full((B, 1), int(position), device=device, dtype=torch.int32)
+    logits = model.run_with_cache(token.to(device=device, dtype=torch.int32)[:, None], pos, cache, last_only=True)
+    cache.advance(pos)
+    return logits[:, -1]
+
+
 @dataclass
 class GenerationResult:
     prompt_ids: list[list[int]]

@@ -86,3 +86,70 @@ def require_kernel_plan_supported(plan: dict[str, Any], spec: RunSpec) -> None:
     missing = [op["op"] for op in plan["ops"] if not op["selected"] and op["op"] not in OPTIONAL_OPS]
     if missing:
         raise ContractError(f"kernels.strict=true but these ops would not run natively: {missing}")
+
+
+def kernel_registry_payload() -> dict[str, Any]:
+    return {"schema_version": 1, "kernels": kernel_registry()}
+
+
+def format_kernel_registry(rows: list[dict[str, Any]] | None = None) -> str:
+    rows = kernel_registry() if rows is None else rows
+    return "\n".join(f"{r['op']:<26} {r['symbol']:<32} {r['engine']:<28} built={r['built']}" for r in rows)
+
+
+def kernel_plan_to_json(plan: dict[str, Any]) -> str:
+    import json
+
+    return json.dumps(plan, sort_keys=True, separators=(",", ":"))
+
+
+def format_kernel_plan(plan: dict[str, Any]) -> str:
+    lines = [f"kernel plan: active={plan['active']} library_present={plan['library_present']} "
+             f"active_count={plan['active_count']} fallback={plan['fallback_count']} "
+             f"unavailable={plan['unavailable_count']} device={plan['device_kind']}"]
+    lines += [f"  {op['op']:<26} selected={op['selected']} fallback={op['fallback']}" for op in plan["ops"]]
+    return "\n".join(lines)
+
+
+def load_cache_manifest() -> dict[str, Any] | None:
+    """The manifest the in-tree build wrote next to the libraries (sources, flags, digest), if there is one."""
+
+    import json
+
+    from research_b200.kernels import build
+
+    try:
+        return json.loads(build.MANIFEST.read_text())
+    except (OSError, json.JSONDecodeError):
+        return None
+
+
+def enrich_kernel_plan_with_cache(plan: dict[str, Any]) -> dict[str, Any]:
+    """The plan plus what the build cache says: whether the libraries on disk were built from the sources on disk."""
+
+    from research_b200.kernels import build
+
+    manifest = load_cache_manifest()
+    current = build._digest(build.kernel_sources() + build.host_sources(),
+                            build.ARCH_FLAGS + build.NVCC_FLAGS + build.CXX_FLAGS)
+    out = dict(plan)
+    out.update({"cache_dir": build.LIB_DIR.as_posix(), "cached_count": 0 if manifest is None else len(manifest["sources"]),
+                "cache_digest": None if manifest is None else manifest.get("digest"), "source_digest": current,
+                "stale_cache": manifest is not None and manifest.get("digest") != current,
+                "missing_cache": manifest is None})
+    return out
+
+
+def compile_kernel_plan(spec: RunSpec, *, force: bool = False) -> dict[str, Any]:
+    """Build the kernel and host libraries in the tree (a no-op when they are current) and report the plan."""
+
+    from research_b200.kernels.build import build_all
+
+    result = build_all(force=force)
+    return {"schema_version": 1, "arch": "sm_100a", "library": str(result.kernel_lib), "rebuilt": result.rebuilt,
+            "sources": list(result.sources), "digest": result.digest, "plan": kernel_plan(spec)}
+
+
+def format_compile_result(payload: dict[str, Any]) -> str:
+    return (f"built {payload['library']} (rebuilt={payload['rebuilt']}) from {len(payload['sources'])} sources "
+            f"for {payload['arch']}, digest {payload['digest'][:16]}")

@@ -278,3 +278,32 @@ def build_model(spec: ModelSpec, *, seed: int = 0, execution: ExecutionContext |
     if initialize:
         initialize_parameters(result, seed)
     return result
+
+
+def count_parameters(metadata) -> int:
+    """Number of scalar parameters described by a parameter table."""
+
+    total = 0
+    for meta in metadata:
+        n = 1
+        for d in meta.shape:
+            n *= int(d)
+        total += n
+    return total
+
+
+def dtype_from_name(name: str):
+    """``"float32" | "bfloat16" | "float16"`` -> the torch dtype (the names the run contract uses)."""
+
+    import torch
+
+    table = {"float32": torch.float32, "bfloat16": torch.bfloat16, "float16": torch.float16}
+    if name not in table:
+        raise ContractError(f"unsupported dtype name {name!r}; expected one of {sorted(table)}")
+    return table[name]
+
+
+def apply_model(model, input_ids, token_doc_ids=None):
+    """Forward pass returning the :class:`ModelOutput` (logits, auxiliary losses, router statistics)."""
+
+    return model(input_ids, token_doc_ids)

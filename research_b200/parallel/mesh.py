@@ -78,6 +78,19 @@ def _axis_group_timeout():
     return None if seconds is None else datetime.timedelta(seconds=seconds)
 
 
+def validate_runtime_mesh_spec(spec: MeshSpec) -> None:
+    """What a mesh must satisfy before any process group is made: known axis names only, and as many devices as
+    the launch has ranks (reference: src/jaxtitan/mesh/sharding.py ``validate_runtime_mesh_spec``)."""
+
+    for name in spec.axis_names:
+        if name not in SUPPORTED_AXES:
+            raise ContractError(f"unsupported mesh axis {name!r}; supported axes: {sorted(SUPPORTED_AXES)}")
+    world = dist.get_world_size() if dist.is_initialized() else int(os.environ.get("WORLD_SIZE", "1"))
+    if spec.device_count != world:
+        raise ContractError(f"mesh axis sizes {spec.axis_sizes} need {spec.device_count} devices but the job has "
+                            f"{world} ranks")
+
+
 def init_distributed(backend: str | None = None, timeout_s: float = 600.0) -> tuple[int, int]:
     """Initialise the default process group from the torchrun environment; returns (rank, world_size)."""
 
