@@ -139,7 +139,10 @@ class ParamStore:
                 # through the same expert weights, so their gradients are partial sums over that axis
                 axes.append("tp")
             shard_axis = None
-            if mode in ("zero2", "fsdp") and mesh.size("fsdp") > 1 and not (is_expert and ep_axis == "fsdp"):
+            # parameters that no optimizer moves (the routers' balance bias) keep their whole fp32 value on every
+            # rank: whatever updates them does so identically everywhere and needs no gather to read them
+            if mode in ("zero2", "fsdp") and mesh.size("fsdp") > 1 and not (is_expert and ep_axis == "fsdp") \
+                    and backend != "frozen":
                 shard_axis = "fsdp"
             decays = {bool((decay_of or {}).get(m.name, True)) for m in metas}
             if backend == "adamw" and len(decays) != 1:

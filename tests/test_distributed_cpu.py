@@ -2,6 +2,8 @@
 thing on four fake devices: tests/jaxtitan/test_train_step.py:943-1051): same global batch, same token count,
 loss sums within 1e-4 and the whole updated parameter tree close after a few optimizer steps."""
 
+import math
+
 import pytest
 import torch
 
@@ -126,3 +128,34 @@ def test_expert_parallel_backward_completes_when_a_rank_receives_no_token(routin
         assert torch.allclose(r["y"], ref["y"], atol=1e-5) and torch.allclose(r["dx"], ref["dx"], atol=1e-5)
     if routing == "skewed":
         assert got[0]["dw_norm"] > 0 and not got[1]["dw_norm"]          # the idle rank's experts get no gradient
+
+
+def _bf16_balance_worker(rank, world, raw):
+    import torch
+
+    from research_b200.config import run_spec_from_mapping
+    from research_b200.runtime.trainer import Trainer
+
+    trainer = Trainer(run_spec_from_mapping(raw), device="cpu")
+    losses = [trainer.train_step(diagnostics=True).loss for _ in range(3)]
+    mlp = trainer.result.model.layers[1].mlp
+    return {"losses": losses, "master": mlp.bias_master.clone(), "copy": mlp.expert_bias.data.clone(),
+            "momentum": trainer.moe_balance.layers[0].momentum.clone()}
+
+
+@pytest.mark.parametrize("mesh, parallelism", [
+    ({"ep": 2}, {"mode": "ddp", "expert_parallel": True}),
+    ({"fsdp": 2}, {"mode": "fsdp", "expert_parallel": True}),
+    ({"fsdp": 2}, {"mode": "fsdp", "fsdp_resident": False}),
+], ids=["ep2", "fsdp2_folded_ep", "fsdp2_sharded_at_rest"])
+def test_balance_bias_stays_fp32_and_identical_on_every_rank_with_bf16_compute(tmp_path, mesh, parallelism):
+    manifest = tiny_dataset(tmp_path)
+    raw = tiny_raw_config(manifest, kind="trinity", mesh=mesh, parallelism=parallelism, steps=4)
+    raw["model"]["compute_dtype"] = "bfloat16"
+    raw["training"]["precision"] = "bf16"
+    a, b = run_gloo(2, _bf16_balance_worker, raw)
+    for r in (a, b):
+        assert r["master"].dtype == torch.float32 and r["copy"].dtype == torch.bfloat16
+        assert torch.equal(r["copy"], r["master"].to(torch.bfloat16)) and float(r["master"].abs().max()) > 0
+        assert all(math.isfinite(x) for x in r["losses"])
+    assert torch.equal(a["master"], b["master"]) and torch.equal(a["momentum"], b["momentum"])
