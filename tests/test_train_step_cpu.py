@@ -208,3 +208,41 @@ def test_narrow_compute_precision_keeps_the_balance_bias_in_fp32_and_in_the_chec
     # full precision compute: the parameter itself is the fp32 bias, nothing to mirror
     plain = _trainer(manifest, kind="trinity")
     assert plain.result.model.layers[1].mlp.bias_master is None and plain.moe_balance.layers[0].entry is None
+
+
+@pytest.mark.parametrize("kind, optimizer", [("decoder", "muon"), ("trinity", "dion")])
+def test_bf16_compute_copies_through_the_whole_run_lifecycle(tmp_path, manifest, kind, optimizer):
+    """fp32 masters with bf16 compute copies on the host path: preflight, train with checkpoints and evals, checkpoint
+    eval, sampling and resume all work, and the saved leaves are the fp32 masters."""
+
+    from research_b200.runtime.checkpoint_eval import evaluate_checkpoint
+    from research_b200.runtime.preflight import run_preflight
+    from research_b200.runtime.sampling import sample_checkpoint
+    from research_b200.runtime.training import run_training
+    from research_b200.services.checkpoints import read_array
+    from tests.helpers import write_toml
+
+    raw = tiny_raw_config(manifest, kind=kind, optimizer=optimizer, run_id="half", output_dir=(tmp_path / "runs").as_posix(),
+                          steps=4, checkpoint_every=2, evals=True)
+    raw["model"]["compute_dtype"] = "bfloat16"
+    raw["training"]["precision"] = "bf16"
+    cfg = write_toml(raw, tmp_path / "half.toml")
+    report = run_preflight(cfg)
+    assert report["model"]["compute_dtype"] == "bfloat16" and report["first_step"]["loss"] > 0
+    seen = {}
+    summary = run_training(cfg, trainer_hook=lambda t: seen.setdefault("t", t))
+    trainer = seen["t"]
+    assert summary.steps == 4 and math.isfinite(summary.final_loss)
+    assert all(e.param.dtype == torch.bfloat16 for e in trainer.store.entries)
+    run_dir = tmp_path / "runs" / "half"
+    saved = read_array(run_dir / "checkpoints" / "000004" / "train" / "model.layers.0.attn.o.kernel")
+    assert saved.dtype == np.float32
+    roundtrip = torch.from_numpy(saved).to(torch.bfloat16).float().numpy()
+    assert not np.array_equal(saved, roundtrip)                    # the master carries bits a bf16 copy cannot
+    payload = evaluate_checkpoint(run_dir, "latest")
+    assert payload["loss"] == pytest.approx(summary.final_eval_loss, rel=1e-3)
+    sample = sample_checkpoint(run_dir, "best", prompt_ids=[1, 2, 3], max_new_tokens=4, top_k=1)
+    assert len(sample["generated_ids"]) == 4
+    raw["training"]["target_tokens"] = 32 * 4 * 6
+    again = run_training(write_toml(raw, tmp_path / "half.toml"), resume=True)
+    assert again.steps == 6 and math.isfinite(again.final_loss)
