@@ -7,6 +7,7 @@ nominal per-device peak (B200: 2.25e15); ``mfu_exact`` counts the parameters a t
 
 from __future__ import annotations
 
+import math
 import platform
 import sys
 import time
@@ -187,7 +188,7 @@ def mesh_summary(spec: RunSpec, mesh) -> dict[str, Any]:
            "data_axis_size": data_axis, "data_replica_axis_size": mesh.size("data"),
            "fsdp_axis_size": mesh.size("fsdp"), "ep_axis_size": mesh.size("ep"), "tp_axis_size": mesh.size("tp"),
            "cp_axis_size": mesh.size("cp"), "expert_fsdp_axis_size": mesh.size("expert_fsdp"),
-           "global_mesh_size": int(torch.tensor(list(mesh.axis_sizes)).prod()) if mesh.axis_sizes else 1,
+           "global_mesh_size": math.prod(int(n) for n in mesh.axis_sizes),
            "device_count": mesh.world_size, "selected_device_count": mesh.world_size,
            "rank": mesh.rank, "coords": dict(mesh.coords)}
     out.update(batch_summary(spec, data_axis))
