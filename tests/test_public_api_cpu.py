@@ -96,3 +96,33 @@ def test_importing_the_packages_does_not_import_their_heavy_submodules():
             "if m in sys.modules]; print(heavy)")
     out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=120)
     assert out.returncode == 0 and out.stdout.strip() == "[]", out.stdout + out.stderr
+
+
+def test_packaging_metadata_names_the_package_and_the_command():
+    import tomllib
+    from pathlib import Path
+
+    import research_b200
+
+    meta = tomllib.loads((Path(__file__).resolve().parent.parent / "pyproject.toml").read_text())
+    assert meta["project"]["name"] == "research_b200" and meta["project"]["scripts"] == {"jaxtitan": "research_b200.cli:main"}
+    assert meta["tool"]["setuptools"]["dynamic"]["version"] == {"attr": "research_b200.__version__"}
+    assert isinstance(research_b200.__version__, str) and research_b200.__version__
+    data = meta["tool"]["setuptools"]["package-data"]["research_b200"]
+    assert "ops/csrc/*.cu" in data and "native/*.cpp" in data           # the sources the in-tree build compiles
+    from research_b200.cli import main
+
+    assert callable(main)
+
+
+def test_the_package_imports_nothing_from_outside_itself():
+    """Product code never reaches into tests, benchmarks or scratch folders (the reference keeps the same boundary
+    between its package and its legacy tree: tests/jaxtitan/test_import_boundary.py)."""
+
+    import re
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent / "research_b200"
+    pattern = re.compile(r"^\s*(?:from|import)\s+(tests|bench|_work|__graft_entry__|baseline)\b", re.M)
+    offenders = [p.relative_to(root).as_posix() for p in root.rglob("*.py") if pattern.search(p.read_text())]
+    assert offenders == []
