@@ -69,7 +69,9 @@ def write_array(leaf_dir: Path, arr: np.ndarray) -> None:
     """One zarr-v2 array with a single uncompressed chunk (bfloat16 leaves are stored as uint16 bit patterns)."""
 
     leaf_dir.mkdir(parents=True, exist_ok=False)
-    arr = np.ascontiguousarray(arr)
+    arr = np.asarray(arr)
+    if not arr.flags.c_contiguous:
+        arr = arr.copy(order="C")                 # (``ascontiguousarray`` would turn a scalar into shape [1])
     header = {"chunks": list(arr.shape) if arr.ndim else [], "compressor": None, "dtype": _zarr_dtype(arr),
               "fill_value": None, "filters": None, "order": "C", "shape": list(arr.shape), "zarr_format": 2,
               "dimension_separator": "."}
@@ -87,25 +89,81 @@ def _write_bytes(path: Path, arr: np.ndarray) -> None:
             handle.write(data.tobytes())
 
 
+def _decode_chunk(raw: bytes, compressor: Any, nbytes: int, where: Path) -> bytes:
+    """Undo a zarr-v2 chunk compressor: none, ``zstd`` (through pyarrow's codec), ``gzip`` or ``zlib``."""
+
+    if compressor is None:
+        return raw
+    kind = compressor.get("id") if isinstance(compressor, dict) else None
+    if kind == "zstd":
+        try:
+            import pyarrow as pa
+        except ImportError as exc:
+            raise ContractError(f"checkpoint chunk {where} is zstd-compressed and pyarrow is not installed") from exc
+        try:
+            return pa.Codec("zstd").decompress(raw, decompressed_size=nbytes).to_pybytes()
+        except Exception as exc:
+            raise ContractError(f"checkpoint chunk {where} does not decompress (zstd): {exc}") from exc
+    if kind in ("gzip", "zlib"):
+        import gzip
+        import zlib
+
+        try:
+            return gzip.decompress(raw) if kind == "gzip" else zlib.decompress(raw)
+        except Exception as exc:
+            raise ContractError(f"checkpoint chunk {where} does not decompress ({kind}): {exc}") from exc
+    raise ContractError(f"checkpoint chunk {where} uses the unsupported compressor {compressor!r}")
+
+
 def read_array(leaf_dir: Path) -> np.ndarray:
+    """One zarr-v2 array: the single raw chunk this service writes, and also what other writers of the format produce
+    - a grid of chunks (edge chunks padded to the chunk shape, absent chunks meaning the fill value), ``.`` or ``/``
+    between chunk indices, C or F order inside a chunk, and ``zstd`` / ``gzip`` / ``zlib`` chunk compression - which
+    is the form of an Orbax checkpoint written with ``use_ocdbt=False``.  Filters are not supported."""
+
     try:
         header = json.loads((leaf_dir / ".zarray").read_text())
     except (OSError, json.JSONDecodeError) as exc:
         raise ContractError(f"checkpoint leaf {leaf_dir} has no readable .zarray: {exc}") from exc
-    if header.get("compressor") is not None:
-        raise ContractError(f"checkpoint leaf {leaf_dir} is compressed; only raw chunks are supported")
-    shape = tuple(header["shape"])
-    chunks = tuple(header.get("chunks") or shape)
-    if chunks != shape:
-        raise ContractError(f"checkpoint leaf {leaf_dir} is chunked {chunks} != shape {shape}")
+    if header.get("zarr_format", 2) != 2:
+        raise ContractError(f"checkpoint leaf {leaf_dir} has zarr_format {header.get('zarr_format')}; only 2 is read")
+    if header.get("filters"):
+        raise ContractError(f"checkpoint leaf {leaf_dir} uses filters {header['filters']!r}; none are supported")
+    compressor = header.get("compressor")
+    shape = tuple(int(n) for n in header["shape"])
+    chunks = tuple(int(n) for n in (header.get("chunks") or shape))
+    if len(chunks) != len(shape) or any(c <= 0 for c in chunks):
+        raise ContractError(f"checkpoint leaf {leaf_dir} has chunks {chunks} for shape {shape}")
     sep = header.get("dimension_separator", ".")
-    chunk_name = sep.join("0" for _ in shape) if shape else "0"
-    path = leaf_dir / chunk_name
     dtype = np.dtype(header["dtype"])
-    expected = int(np.prod(shape, dtype=np.int64)) * dtype.itemsize if shape else dtype.itemsize
-    if not path.is_file() or path.stat().st_size != expected:
-        raise ContractError(f"checkpoint chunk {path} is missing or has the wrong size (expected {expected} bytes)")
-    return np.fromfile(path, dtype=dtype).reshape(shape)
+    order = header.get("order", "C")
+    chunk_bytes = (int(np.prod(chunks, dtype=np.int64)) if shape else 1) * dtype.itemsize
+    if compressor is None and chunks == shape:
+        # the form this service writes: one raw file, read without a copy through a staging buffer
+        path = leaf_dir / (sep.join("0" for _ in shape) if shape else "0")
+        if not path.is_file() or path.stat().st_size != chunk_bytes:
+            raise ContractError(f"checkpoint chunk {path} is missing or has the wrong size (expected {chunk_bytes} bytes)")
+        flat = np.fromfile(path, dtype=dtype)
+        return flat.reshape(shape, order=order) if shape else flat.reshape(())
+    fill = header.get("fill_value")
+    out = np.full(shape, 0 if fill is None else fill, dtype=dtype)
+    grid = [range(-(-n // c)) for n, c in zip(shape, chunks)]
+    import itertools
+
+    for index in (itertools.product(*grid) if shape else [()]):
+        path = leaf_dir / (sep.join(str(i) for i in index) if shape else "0")
+        if not path.is_file():
+            continue                                     # zarr: an absent chunk holds the fill value
+        data = _decode_chunk(path.read_bytes(), compressor, chunk_bytes, path)
+        if len(data) != chunk_bytes:
+            raise ContractError(f"checkpoint chunk {path} has {len(data)} bytes after decoding, expected {chunk_bytes}")
+        block = np.frombuffer(data, dtype=dtype).reshape(chunks, order=order) if shape else np.frombuffer(data, dtype=dtype)
+        if not shape:
+            return block.reshape(()).copy()
+        lo = [i * c for i, c in zip(index, chunks)]
+        hi = [min(a + c, n) for a, c, n in zip(lo, chunks, shape)]
+        out[tuple(slice(a, b) for a, b in zip(lo, hi))] = block[tuple(slice(0, b - a) for a, b in zip(lo, hi))]
+    return out
 
 
 def _fsync_dir(path: Path) -> None:

@@ -152,3 +152,85 @@ def test_restore_into_weights_sharded_at_rest(tmp_path):
     assert a[0]["loss"] == pytest.approx(b[0]["loss"], rel=1e-5)           # the step after the restore agrees
     assert a[0]["memory"]["mode"] == "sharded" and b[0]["memory"]["mode"] == "resident"
     assert a[0]["memory"]["compute_bytes"] < b[0]["memory"]["compute_bytes"]
+
+
+def _write_zarr(leaf, arr, *, chunks, compressor=None, sep=".", order="C", skip=(), fill=0):
+    """A zarr-v2 array written by hand, the way another writer of the format would lay it out."""
+
+    import gzip
+    import itertools
+    import json as _json
+    import zlib
+
+    leaf.mkdir(parents=True)
+    (leaf / ".zarray").write_text(_json.dumps({
+        "zarr_format": 2, "shape": list(arr.shape), "chunks": list(chunks), "dtype": arr.dtype.str, "order": order,
+        "compressor": compressor, "filters": None, "fill_value": fill, "dimension_separator": sep}))
+    for index in itertools.product(*[range(-(-n // c)) for n, c in zip(arr.shape, chunks)]):
+        if index in skip:
+            continue
+        block = np.full(chunks, fill, dtype=arr.dtype)
+        lo = [i * c for i, c in zip(index, chunks)]
+        hi = [min(a + c, n) for a, c, n in zip(lo, chunks, arr.shape)]
+        block[tuple(slice(0, b - a) for a, b in zip(lo, hi))] = arr[tuple(slice(a, b) for a, b in zip(lo, hi))]
+        raw = block.tobytes(order=order)
+        kind = None if compressor is None else compressor["id"]
+        if kind == "zstd":
+            import pyarrow as pa
+
+            raw = pa.Codec("zstd").compress(raw).to_pybytes()
+        elif kind == "gzip":
+            raw = gzip.compress(raw)
+        elif kind == "zlib":
+            raw = zlib.compress(raw)
+        path = leaf / sep.join(str(i) for i in index)
+        path.parent.mkdir(parents=True, exist_ok=True)
+        path.write_bytes(raw)
+
+
+@pytest.mark.parametrize("compressor", [None, {"id": "zstd", "level": 1}, {"id": "gzip", "level": 5}, {"id": "zlib", "level": 1}])
+@pytest.mark.parametrize("sep, order", [(".", "C"), ("/", "C"), (".", "F")])
+def test_leaves_written_by_other_zarr_writers_are_read(tmp_path, compressor, sep, order):
+    from research_b200.services.checkpoints import read_array
+
+    rng = np.random.default_rng(0)
+    arr = rng.standard_normal((10, 7)).astype(np.float32)
+    _write_zarr(tmp_path / "leaf", arr, chunks=(4, 3), compressor=compressor, sep=sep, order=order)
+    got = read_array(tmp_path / "leaf")
+    assert got.dtype == np.float32 and np.array_equal(got, arr)             # edge chunks are cut back to the shape
+    ints = np.arange(24, dtype=np.int32).reshape(2, 3, 4)
+    _write_zarr(tmp_path / "ints", ints, chunks=(1, 3, 2), compressor=compressor, sep=sep, order=order)
+    assert np.array_equal(read_array(tmp_path / "ints"), ints)
+
+
+def test_absent_chunks_hold_the_fill_value_and_bad_leaves_are_refused(tmp_path):
+    from research_b200.errors import ContractError
+    from research_b200.services.checkpoints import read_array, write_array
+
+    arr = np.arange(16, dtype=np.float32).reshape(4, 4)
+    _write_zarr(tmp_path / "sparse", arr, chunks=(2, 2), skip={(1, 1)}, fill=-1.0)
+    want = arr.copy()
+    want[2:, 2:] = -1.0
+    assert np.array_equal(read_array(tmp_path / "sparse"), want)
+    write_array(tmp_path / "own", arr)                                       # the form this service writes
+    assert np.array_equal(read_array(tmp_path / "own"), arr)
+    write_array(tmp_path / "scalar", np.asarray(7, dtype=np.int32))
+    assert read_array(tmp_path / "scalar").shape == () and int(read_array(tmp_path / "scalar")) == 7
+    _write_zarr(tmp_path / "blosc", arr, chunks=(2, 2))
+    meta = json.loads((tmp_path / "blosc" / ".zarray").read_text())
+    (tmp_path / "blosc" / ".zarray").write_text(json.dumps({**meta, "compressor": {"id": "blosc", "cname": "lz4"}}))
+    with pytest.raises(ContractError, match="unsupported compressor"):
+        read_array(tmp_path / "blosc")
+    (tmp_path / "blosc" / ".zarray").write_text(json.dumps({**meta, "filters": [{"id": "delta"}]}))
+    with pytest.raises(ContractError, match="uses filters"):
+        read_array(tmp_path / "blosc")
+    (tmp_path / "blosc" / ".zarray").write_text(json.dumps({**meta, "zarr_format": 3}))
+    with pytest.raises(ContractError, match="zarr_format 3"):
+        read_array(tmp_path / "blosc")
+    _write_zarr(tmp_path / "torn", arr, chunks=(2, 2), compressor={"id": "zstd"})
+    (tmp_path / "torn" / "0.0").write_bytes(b"not a zstd frame")
+    with pytest.raises(ContractError, match="does not decompress"):
+        read_array(tmp_path / "torn")
+    (tmp_path / "own" / "0.0").write_bytes(b"short")
+    with pytest.raises(ContractError, match="missing or has the wrong size"):
+        read_array(tmp_path / "own")
