@@ -148,9 +148,15 @@ class Optimizer:
             for i, sec in enumerate(store.sections):
                 if before[i] is not None:
                     _sumsq((sec.master - before[i]).contiguous(), buf, i)
-            for axis in {a for sec in store.sections for a in self._sum_axes(sec)}:
+            # one reduction per axis, in an order that is the same in every process: iterating a set of strings
+            # follows the per-process hash seed, and ranks that reduce over two axes in opposite orders wait on one
+            # another for ever
+            sum_axes: dict[str, list[int]] = {}
+            for i, sec in enumerate(store.sections):
+                for axis in self._sum_axes(sec):
+                    sum_axes.setdefault(axis, []).append(i)
+            for axis, idx in sum_axes.items():
                 group = self.mesh.group(axis)
-                idx = [i for i, sec in enumerate(store.sections) if axis in self._sum_axes(sec)]
                 if group is not None and idx:
                     part = buf[idx].clone()
                     dist.all_reduce(part, group=group)

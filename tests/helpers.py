@@ -131,7 +131,7 @@ def _worker(rank: int, world: int, port: int, fn, args, out_dir: str):
         raise
 
 
-def _run_gloo_once(world: int, fn, args):
+def _run_gloo_once(world: int, fn, args, hash_seeds=None):
     import time
 
     import torch.multiprocessing as mp
@@ -140,8 +140,18 @@ def _run_gloo_once(world: int, fn, args):
     port = free_port()
     ctx = mp.get_context("spawn")
     procs = [ctx.Process(target=_worker, args=(r, world, port, fn, args, out_dir)) for r in range(world)]
-    for p in procs:
-        p.start()
+    saved_seed = os.environ.get("PYTHONHASHSEED")
+    try:
+        for r, p in enumerate(procs):
+            if hash_seeds is not None:
+                os.environ["PYTHONHASHSEED"] = str(hash_seeds[r])     # read by the child interpreter when it starts
+            p.start()
+    finally:
+        if hash_seeds is not None:
+            if saved_seed is None:
+                os.environ.pop("PYTHONHASHSEED", None)
+            else:
+                os.environ["PYTHONHASHSEED"] = saved_seed
     deadline = time.monotonic() + GLOO_RUN_DEADLINE_S
     for p in procs:
         p.join(timeout=max(deadline - time.monotonic(), 0.0))
@@ -161,18 +171,36 @@ def _run_gloo_once(world: int, fn, args):
         elif p.exitcode != 0:
             errors.append(f"rank {r} exited with code {p.exitcode}")
     if errors:
+        _keep_hang_stacks(out_dir, world, fn)
         return None, errors, bool(stuck) or all("Timed out" in e or "timed out" in e for e in errors)
     return [torch.load(os.path.join(out_dir, f"rank{r}.pt"), weights_only=False) for r in range(world)], [], False
 
 
-def run_gloo(world: int, fn, *args):
+def _keep_hang_stacks(out_dir: str, world: int, fn) -> None:
+    """Copy the stack dumps of a failed run into the temporary directory, where they outlive a retry that passes."""
+
+    import time
+
+    stacks = []
+    for r in range(world):
+        hang = Path(out_dir) / f"rank{r}.hang"
+        if hang.exists() and hang.stat().st_size:
+            stacks.append(f"==== rank {r}\n{hang.read_text()}")
+    if stacks:
+        keep = Path(tempfile.gettempdir()) / "research_b200_gloo_hangs"
+        keep.mkdir(exist_ok=True)
+        (keep / f"{int(time.time())}_{getattr(fn, '__name__', 'fn')}_{world}.txt").write_text("\n".join(stacks))
+
+
+def run_gloo(world: int, fn, *args, hash_seeds=None):
     """Run ``fn(rank, world, *args)`` in ``world`` CPU processes over gloo; returns the per-rank results.
+    ``hash_seeds`` gives every rank its own string-hash seed (the order in which a process iterates a set of strings).
 
     A run in which the ranks only timed out on one another (no rank raised anything else) is tried once more: on a
     loaded host the gloo rendezvous of a fresh group occasionally loses a connection."""
 
-    results, errors, only_timeouts = _run_gloo_once(world, fn, args)
-    if errors and only_timeouts:
+    results, errors, only_timeouts = _run_gloo_once(world, fn, args, hash_seeds)
+    if errors and only_timeouts and hash_seeds is None:
         results, errors, _ = _run_gloo_once(world, fn, args)
     if errors:
         raise AssertionError("\n".join(errors))

@@ -159,3 +159,52 @@ def test_balance_bias_stays_fp32_and_identical_on_every_rank_with_bf16_compute(t
         assert torch.equal(r["copy"], r["master"].to(torch.bfloat16)) and float(r["master"].abs().max()) > 0
         assert all(math.isfinite(x) for x in r["losses"])
     assert torch.equal(a["master"], b["master"]) and torch.equal(a["momentum"], b["momentum"])
+
+
+def _seeds_that_order_two_strings_both_ways(a, b):
+    """A hash seed under which a set iterates ``a`` before ``b`` and one under which it iterates ``b`` first."""
+
+    import subprocess
+    import sys
+
+    found = {}
+    for seed in range(64):
+        out = subprocess.run([sys.executable, "-c", f"print(list({{{a!r}, {b!r}}})[0])"], capture_output=True, text=True,
+                             env={"PYTHONHASHSEED": str(seed), "PATH": ""})
+        found.setdefault(out.stdout.strip(), seed)
+        if len(found) == 2:
+            return found[a], found[b]
+    raise AssertionError("no pair of seeds found")
+
+
+def test_collectives_over_two_axes_do_not_depend_on_the_string_hash_seed(tmp_path):
+    """Ranks must reduce over the mesh axes in one order.  With the ranks' hash seeds chosen so that a set of the two
+    axis names iterates ``tp`` first on ranks 0 and 3 and ``fsdp`` first on ranks 1 and 2, code that walks such a set
+    makes every rank wait for a peer that waits for someone else: this run would end in the collective timeout."""
+
+    tp_first, fsdp_first = _seeds_that_order_two_strings_both_ways("tp", "fsdp")
+    manifest = tiny_dataset(tmp_path)
+    raw = tiny_raw_config(manifest, mesh={"fsdp": 2, "tp": 2}, parallelism={"mode": "fsdp", "tensor_parallel": True},
+                          steps=STEPS + 1)
+    results = run_gloo(4, train_and_collect, raw, 2, hash_seeds=[tp_first, fsdp_first, fsdp_first, tp_first])
+    assert all(math.isfinite(x) for r in results for x in r["loss_sum"])
+    assert all(r["loss_sum"] == results[0]["loss_sum"] for r in results)
+
+
+def test_no_loop_over_a_set_in_modules_that_issue_collectives():
+    """The order of a loop that contains a collective must not come from a set (its order is per process)."""
+
+    import re
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent / "research_b200"
+    loop_over_set = re.compile(r"for\s+[\w,\s()]+\s+in\s+(\{|set\(|frozenset\()")
+    offenders = []
+    for path in root.rglob("*.py"):
+        text = path.read_text()
+        if "torch.distributed" not in text and "import dist" not in text:
+            continue
+        for n, line in enumerate(text.splitlines(), 1):
+            if loop_over_set.search(line):
+                offenders.append(f"{path.relative_to(root)}:{n}")
+    assert offenders == []
