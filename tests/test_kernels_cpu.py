@@ -169,3 +169,13 @@ def test_registry_rows_name_a_source_and_an_exported_symbol():
     assert rows and all(r["source"] in sources for r in rows)
     assert all(r["symbol"].startswith(("b200_", "b200c_")) for r in rows)
     assert len({r["op"] for r in rows}) == len(rows)
+
+
+def test_roofline_denominators_come_from_the_measured_file_or_the_stated_fallback(tmp_path, monkeypatch):
+    from research_b200.kernels import microbench
+
+    (tmp_path / "MEASURED_PEAKS.json").write_text(json.dumps({"hbm_gbs": 6500.0, "bf16_tflops": 1600.0, "chip": "B200"}))
+    monkeypatch.setattr(microbench, "ROOT", tmp_path)
+    assert microbench.peaks() == {"hbm_gbs": 6500.0, "bf16_tflops": 1600.0, "source": "measured"}
+    (tmp_path / "MEASURED_PEAKS.json").unlink()
+    assert microbench.peaks() == {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
