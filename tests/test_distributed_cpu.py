@@ -177,18 +177,23 @@ def _seeds_that_order_two_strings_both_ways(a, b):
     raise AssertionError("no pair of seeds found")
 
 
-def test_collectives_over_two_axes_do_not_depend_on_the_string_hash_seed(tmp_path):
+@pytest.mark.parametrize("kind, axes, parallelism", [
+    ("decoder", ("fsdp", "tp"), {"mode": "fsdp", "tensor_parallel": True}),
+    ("trinity", ("tp", "ep"), {"mode": "ddp", "tensor_parallel": True, "expert_parallel": True}),
+], ids=["fsdp2_tp2", "tp2_ep2_moe"])
+def test_collectives_over_two_axes_do_not_depend_on_the_string_hash_seed(tmp_path, kind, axes, parallelism):
     """Ranks must reduce over the mesh axes in one order.  With the ranks' hash seeds chosen so that a set of the two
-    axis names iterates ``tp`` first on ranks 0 and 3 and ``fsdp`` first on ranks 1 and 2, code that walks such a set
-    makes every rank wait for a peer that waits for someone else: this run would end in the collective timeout."""
+    axis names iterates one name first on ranks 0 and 3 and the other first on ranks 1 and 2, code that walks such a
+    set makes every rank wait for a peer that waits for someone else: this run would end in the collective timeout.
+    The result must also be the single-process one whatever the seeds are."""
 
-    tp_first, fsdp_first = _seeds_that_order_two_strings_both_ways("tp", "fsdp")
+    first, second = _seeds_that_order_two_strings_both_ways(*axes)
     manifest = tiny_dataset(tmp_path)
-    raw = tiny_raw_config(manifest, mesh={"fsdp": 2, "tp": 2}, parallelism={"mode": "fsdp", "tensor_parallel": True},
-                          steps=STEPS + 1)
-    results = run_gloo(4, train_and_collect, raw, 2, hash_seeds=[tp_first, fsdp_first, fsdp_first, tp_first])
-    assert all(math.isfinite(x) for r in results for x in r["loss_sum"])
-    assert all(r["loss_sum"] == results[0]["loss_sum"] for r in results)
+    ref = _single(tiny_raw_config(manifest, kind=kind, steps=STEPS + 1))
+    raw = tiny_raw_config(manifest, kind=kind, mesh={axes[0]: 2, axes[1]: 2}, parallelism=parallelism, steps=STEPS + 1)
+    results = run_gloo(4, train_and_collect, raw, STEPS, hash_seeds=[first, second, second, first])
+    for got in results:
+        _compare(ref, got, 2e-4)
 
 
 def test_no_loop_over_a_set_in_modules_that_issue_collectives():
