@@ -133,6 +133,7 @@ class Trainer:
         if not self.store.resident:
             self.result.model.layer_prepare = self.store.acquire_layer
         self.optimizer = Optimizer(self.optimizer_build, self.store)
+        self.check_layout_agreement()
         moe = spec.model.trinity.moe if spec.model.trinity is not None else None
         self.moe_balance = init_moe_balance(self.result.model, None if moe is None else moe.balance, store=self.store)
         self.train_step_fn = TrainStep(spec, self.result, self.store, self.optimizer, self.mesh, self.moe_balance)
@@ -149,6 +150,35 @@ class Trainer:
         if build_data:
             self.data = self.build_pipeline("train")
             self.data_state = self.data.initial_state()
+
+    def layout_fingerprint(self) -> int:
+        """62 bits of the sha256 over what every rank must agree on before the first collective of a step: the mesh,
+        the parameter store's sections (sizes, axes, backends) and, per section, the order in which the optimizer
+        reduces over the mesh axes."""
+
+        import hashlib
+
+        from research_b200.config.canonical import canonical_json
+
+        payload = {"mesh": [list(self.mesh.axis_names), list(self.mesh.axis_sizes)], "store": self.store.describe(),
+                   "sum_axes": [self.optimizer._sum_axes(sec) for sec in self.store.sections],
+                   "routes": [[a.name, a.backend] for a in self.optimizer_build.route_assignments]}
+        return int.from_bytes(hashlib.sha256(canonical_json(payload).encode()).digest()[:8], "big") >> 2
+
+    def check_layout_agreement(self) -> None:
+        """Every rank must have laid the run out in the same way; a rank that did not would not fail, it would wait
+        in a collective that its peers never start.  One small reduction at start-up turns that into an error."""
+
+        if self.mesh.world_size == 1 or not torch.distributed.is_initialized():
+            return
+        mine = self.layout_fingerprint()
+        both = torch.tensor([mine, -mine], dtype=torch.int64, device=self.device)
+        torch.distributed.all_reduce(both, op=torch.distributed.ReduceOp.MAX)
+        highest, lowest = int(both[0]), -int(both[1])
+        if highest != lowest:
+            raise ContractError(
+                f"rank {self.mesh.rank} laid the run out differently from another rank (layout fingerprint "
+                f"{mine:#x}, job-wide {lowest:#x} .. {highest:#x}): the ranks would deadlock in their first step")
 
     # ---- data --------------------------------------------------------------------------------------
     @property

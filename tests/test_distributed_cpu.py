@@ -213,3 +213,31 @@ def test_no_loop_over_a_set_in_modules_that_issue_collectives():
             if loop_over_set.search(line):
                 offenders.append(f"{path.relative_to(root)}:{n}")
     assert offenders == []
+
+
+def _divergent_layout_worker(rank, world, raw):
+    from research_b200.config import run_spec_from_mapping
+    from research_b200.errors import ContractError
+    from research_b200.parallel.sharding import ParamStore
+    from research_b200.runtime.trainer import Trainer
+
+    ok = Trainer(run_spec_from_mapping(raw), device="cpu")
+    agreed = ok.layout_fingerprint()
+    if rank == 1:
+        original = ParamStore.describe
+        ParamStore.describe = lambda self: {**original(self), "arena_elements": original(self)["arena_elements"] + 1}
+    try:
+        Trainer(run_spec_from_mapping(raw), device="cpu")
+    except ContractError as exc:
+        return {"agreed": agreed, "error": str(exc)}
+    return {"agreed": agreed, "error": None}
+
+
+def test_ranks_that_lay_the_run_out_differently_fail_at_start_up_instead_of_waiting(tmp_path):
+    manifest = tiny_dataset(tmp_path)
+    raw = tiny_raw_config(manifest, mesh={"fsdp": 2}, parallelism={"mode": "fsdp"})
+    a, b = run_gloo(2, _divergent_layout_worker, raw)
+    assert a["agreed"] == b["agreed"] and 0 < a["agreed"] < 2 ** 62
+    for r in (a, b):
+        assert r["error"] is not None and "laid the run out differently" in r["error"]
+        assert "would deadlock" in r["error"]
