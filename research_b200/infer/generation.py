@@ -182,7 +182,9 @@ class GraphedDecodeStep:
 
 
 def _graph_ok(model, device: torch.device) -> bool:
-    return device.type == "cuda" and getattr(model, "compute_dtype", None) == torch.bfloat16
+    # collectives of a tensor-parallel step stay outside a captured graph
+    return (device.type == "cuda" and getattr(model, "compute_dtype", None) == torch.bfloat16
+            and getattr(getattr(model, "ex", None), "tp_size", 1) == 1)
 
 
 KVCache = PagedKVCache

@@ -18,6 +18,7 @@ where ``fused`` is enabled and the tensors are CUDA bf16.
 from __future__ import annotations
 
 import os
+from contextlib import contextmanager
 from dataclasses import dataclass, field
 from typing import Any
 
@@ -253,6 +254,19 @@ class ExecutionContext:
     @property
     def sp(self) -> bool:
         return self.tp_size > 1 and self.sequence_parallel and self.cp_size == 1
+
+    @contextmanager
+    def replicated_activations(self):
+        """Inside: every tensor-parallel rank holds the whole activations (no sequence-parallel shards), so a
+        column-parallel projection reads its input as it is and a row-parallel one all-reduces its output.  This
+        is how a few tokens at a time are run with a KV cache: a decode step has one row, nothing to split."""
+
+        before = self.sequence_parallel
+        self.sequence_parallel = False
+        try:
+            yield self
+        finally:
+            self.sequence_parallel = before
 
     # ---- tensor / sequence parallel activations ------------------------------------------------------
     def scatter_sequence(self, x: torch.Tensor) -> torch.Tensor:

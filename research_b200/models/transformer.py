@@ -139,11 +139,17 @@ class Attention(nn.Module):
         v = qkv[:, (self.hq + self.hkv) * D:].reshape(B, T, self.hkv, D)
         return q, k, v, x2
 
-    def finish(self, o: torch.Tensor, x2: torch.Tensor) -> torch.Tensor:
+    def finish(self, o: torch.Tensor, x2: torch.Tensor, ex: ExecutionContext | None = None) -> torch.Tensor:
         B, T = o.shape[0], o.shape[1]
         if self.wgate is not None:
             o = Fn.sigmoid_gate(o.reshape(B * T, -1), Fn.linear(x2, self.wgate)).view(B, T, -1)
-        return Fn.linear(o.reshape(B, T, -1), self.wo)
+        y = Fn.linear(o.reshape(B, T, -1), self.wo)
+        if ex is not None and ex.tp_size > 1:
+            # the output projection is row-parallel: every rank holds the product over its own heads
+            from research_b200.models.execution import all_reduce_sum
+
+            y = all_reduce_sum(y, ex.tp_group)
+        return y
 
 
 class SwiGLU(nn.Module):
@@ -364,18 +370,19 @@ class TransformerLM(nn.Module):
         """token_ids, positions: [B,T].  Writes K/V for those positions into ``cache`` and returns logits [B,T,V]
         (``[B,1,V]`` for the last position only when ``last_only``: a prefill needs no other row)."""
 
-        x = Fn.embedding(token_ids, self.embed, self.embed_scale, self.compute_dtype)
-        delta = None
-        for li, layer in enumerate(self.layers):
-            if self.layer_prepare is not None:
-                self.layer_prepare(li)
-            def attend(attn: Attention, h, li=li):
-                q, k, v, x2 = attn.project_qkv(h, positions)
-                window = attn.cfg.local_window if attn.cfg.mask == "sliding_window" else None
-                o = cache.update_and_attend(li, q, k, v, positions, window)
-                return attn.finish(o, x2)
-            x, delta = self._infer_block(layer, x, delta, positions, attend)
-        h, _ = self.norm.add_forward(x, delta)
-        if last_only:
-            h = h[:, -1:].contiguous()
-        return self.full_logits(Fn.linear(h, self.head_weight()))
+        with self.ex.replicated_activations():
+            x = Fn.embedding(token_ids, self.embed, self.embed_scale, self.compute_dtype)
+            delta = None
+            for li, layer in enumerate(self.layers):
+                if self.layer_prepare is not None:
+                    self.layer_prepare(li)
+                def attend(attn: Attention, h, li=li):
+                    q, k, v, x2 = attn.project_qkv(h, positions)
+                    window = attn.cfg.local_window if attn.cfg.mask == "sliding_window" else None
+                    o = cache.update_and_attend(li, q, k, v, positions, window)
+                    return attn.finish(o, x2, self.ex)
+                x, delta = self._infer_block(layer, x, delta, positions, attend)
+            h, _ = self.norm.add_forward(x, delta)
+            if last_only:
+                h = h[:, -1:].contiguous()
+            return self.full_logits(Fn.linear(h, self.head_weight()))

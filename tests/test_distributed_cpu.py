@@ -241,3 +241,35 @@ def test_ranks_that_lay_the_run_out_differently_fail_at_start_up_instead_of_wait
     for r in (a, b):
         assert r["error"] is not None and "laid the run out differently" in r["error"]
         assert "would deadlock" in r["error"]
+
+
+def _generate_worker(rank, world, raw):
+    import torch
+
+    from research_b200.config import run_spec_from_mapping
+    from research_b200.infer.generation import generate_tokens
+    from research_b200.runtime.trainer import Trainer
+
+    trainer = Trainer(run_spec_from_mapping(raw), device="cpu", build_data=False)
+    prompts = torch.tensor([[3, 1, 4, 1, 5], [9, 2, 6, 5, 3]])
+    out = generate_tokens(trainer.result.model, prompts, max_new_tokens=5, top_k=1, page_size=4)
+    return {"ids": out.generated_ids, "logprobs": out.logprobs}
+
+
+@pytest.mark.parametrize("kind, mesh, parallelism", [
+    ("decoder", {"tp": 2}, {"mode": "ddp", "tensor_parallel": True}),
+    ("trinity", {"tp": 2}, {"mode": "ddp", "tensor_parallel": True}),
+    ("decoder", {"tp": 2}, {"mode": "ddp", "tensor_parallel": True, "vocab_parallel_head": True}),
+    ("trinity", {"ep": 2}, {"mode": "ddp", "expert_parallel": True}),
+    ("decoder", {"cp": 2}, {"mode": "ddp", "context_parallel": True}),
+], ids=["tp2", "tp2_moe", "tp2_vocab_parallel_head", "ep2_moe", "cp2"])
+def test_generation_on_a_split_model_matches_one_process(tmp_path, kind, mesh, parallelism):
+    """Decoding runs a row at a time: no sequence to split, so tensor-parallel ranks hold whole activations and sum
+    their row-parallel products.  Every rank must produce the tokens one process produces."""
+
+    manifest = tiny_dataset(tmp_path)
+    (ref,) = run_gloo(1, _generate_worker, tiny_raw_config(manifest, kind=kind))
+    got = run_gloo(2, _generate_worker, tiny_raw_config(manifest, kind=kind, mesh=mesh, parallelism=parallelism))
+    for r in got:
+        assert r["ids"] == ref["ids"]
+        assert torch.allclose(torch.tensor(r["logprobs"]), torch.tensor(ref["logprobs"]), atol=1e-4)
