@@ -523,3 +523,52 @@ def test_profile_analysis_refuses_unfinished_or_nonfinite_runs(tmp_path):
     (run / "profiles" / "broken.json").write_text("{not json")
     with pytest.raises(ContractError, match="failed to read trace"):
         analyze_profile_root(tmp_path / "three")
+
+
+def test_streaming_data_through_preflight_training_and_resume(tmp_path, monkeypatch):
+    """``data.mode = "hf_streaming"`` end to end with a fake dataset and tokenizer: the dataset state rides in the
+    checkpoint and a resumed run sees the rows a straight run sees."""
+
+    import research_b200.data.prepare as prepare
+    import research_b200.data.streaming as streaming
+    from research_b200.runtime.preflight import run_preflight
+    from research_b200.runtime.training import run_training
+
+    rows = [{"text": f"document {i} says hello to the world " * 3} for i in range(400)]
+    monkeypatch.setattr(streaming, "load_hf_dataset", lambda source: FakeIterableDataset(rows))
+    monkeypatch.setattr(prepare, "load_tokenizer", lambda name: FakeTokenizer())
+    manifest = tiny_dataset(tmp_path)
+
+    def config(run_id, steps):
+        raw = tiny_raw_config(manifest, run_id=run_id, output_dir=(tmp_path / "runs").as_posix(), steps=steps,
+                              checkpoint_every=2)
+        raw["data"] = {"mode": "hf_streaming", "tokenizer_id": "fake", "order": "sequential",
+                       "hf_streaming": {"dataset": "corp/us", "split": "train", "revision": "abc"}}
+        return write_toml(raw, tmp_path / f"{run_id}.toml")
+
+    report = run_preflight(config("pre", 4))
+    assert report["data"]["mode"] == "hf_streaming" and report["data"]["train_split_tokens"] is None
+    assert report["data"]["pipeline"]["exact_resume"] is True and report["first_batch"]["target_tokens"] == 128
+    straight = run_training(config("straight", 6))
+    first = run_training(config("halves", 4))
+    assert first.data_pipeline_backend == "hf_streaming" and first.data_document_aware is False
+    second = run_training(config("halves", 6), resume=True)
+    assert second.steps == 6 and second.final_loss == pytest.approx(straight.final_loss, rel=1e-6)
+
+    def rows_of(run_id):
+        path = tmp_path / "runs" / run_id / "metrics" / "train.jsonl"
+        return [json.loads(line) for line in path.read_text().splitlines()]
+
+    a, b = rows_of("straight"), rows_of("halves")
+    assert [(r["step"], r["token_start"], r["token_end"]) for r in b] == [(r["step"], r["token_start"], r["token_end"]) for r in a]
+    assert [r["loss"] for r in b] == pytest.approx([r["loss"] for r in a], rel=1e-6)
+    ck = LocalCheckpointRestoreProbe(tmp_path / "runs" / "halves")
+    assert ck["backend"] == "hf_streaming" and ck["stream_state"]["tokens_emitted"] == 6 * 128
+
+
+def LocalCheckpointRestoreProbe(run_dir):
+    """The dataset state stored with the newest checkpoint of a run."""
+
+    from research_b200.services.checkpoints import LocalCheckpointService
+
+    return LocalCheckpointService(run_dir, is_writer=False).restore_latest().dataset_state
