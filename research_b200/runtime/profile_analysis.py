@@ -312,7 +312,7 @@ def format_profile_analysis(payload: Mapping[str, Any]) -> str:
             lines.append(f"{'':<47} traced steps {run['trace_window']['start_step']}-{run['trace_window']['end_step']}: "
                          f"train {pct(tax['train_step_sec'])}")
         trace = run.get("trace")
-        if trace:
+        if trace and trace["total_gpu_time_us"] > 0:
             shares = " ".join(f"{k}={100.0 * v:.0f}%" for k, v in sorted(trace["gpu_time_share"].items(),
                                                                           key=lambda kv: -kv[1]) if v >= 0.005)
             lines.append(f"{'':<47} gpu time: {shares}")

@@ -102,6 +102,8 @@ class ProfilingManager:
         return {"schema_version": 1, "enabled": self.spec.enabled, "status": self._status,
                 "trace_start_step": self.spec.trace_start_step, "trace_end_step": self.spec.trace_end_step,
                 "trace_steps": self.spec.trace_steps, "trace_path": self._trace_path, "backend": "torch.profiler",
+                "trace_dir": "profiles", "trace_files": [] if self._trace_path is None else [self._trace_path],
+                "traced_step_range": {"start": self.spec.trace_start_step, "end": self.spec.trace_end_step},
                 "create_perfetto_trace": self.spec.create_perfetto_trace,
                 "create_perfetto_link": self.spec.create_perfetto_link}
 
