@@ -101,6 +101,24 @@ class _AllReduceSum(torch.autograd.Function):
         return g, None
 
 
+class _AllReduceSumSummedObjectives(torch.autograd.Function):
+    """All-reduce forward and backward: for a group whose ranks each add an objective built on the sum to the total
+    (context-parallel ranks - their gradients are added up), so a rank's input reaches every rank's objective."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        out = x.clone()
+        dist.all_reduce(out, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.clone()
+        dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
 class _CopyToGroup(torch.autograd.Function):
     """Identity forward, all-reduce backward (input replicated, consumers hold partial gradients)."""
 
@@ -189,6 +207,10 @@ def reduce_scatter_dim(x, group, dim):
 
 def all_reduce_sum(x, group):
     return x if _world(group) == 1 else _AllReduceSum.apply(x, group)
+
+
+def all_reduce_sum_summed_objectives(x, group):
+    return x if _world(group) == 1 else _AllReduceSumSummedObjectives.apply(x, group)
 
 
 def copy_to_group(x, group):

@@ -35,14 +35,34 @@ def router_stats(name: str, layer_index: int, expert_ids: torch.Tensor, weights:
                        max_vio=max_vio, load_entropy=entropy, dropped=dropped)
 
 
-def sequence_balance_loss(expert_ids: torch.Tensor, scores: torch.Tensor, top_k: int, seq_groups=()) -> torch.Tensor:
-    """``sum_e f_e p_e`` per sequence, averaged over the batch; scores: [B,S,E], expert_ids: [B,S,k].
+def _sum_over_sequence_shards(x: torch.Tensor, replicated_groups, summed_groups) -> tuple[torch.Tensor, int]:
+    """Add ``x`` up over the groups that split the sequence; returns the sum and the number of shards.
 
-    ``seq_groups``: process groups that split the sequence dimension; the per-sequence sums are all-reduced
-    over them so that a sharded sequence gives the same loss as the whole one.
+    ``replicated_groups``: their ranks run one objective in copies (tensor-parallel ranks with a sequence-parallel
+    residual stream): a rank's share of the gradient is the one through its own tokens.  ``summed_groups``: their
+    ranks' objectives are added up (context-parallel ranks), so the gradient comes back from every rank's copy.
     """
 
-    from research_b200.models.execution import all_reduce_sum
+    from research_b200.models.execution import all_reduce_sum, all_reduce_sum_summed_objectives
+
+    shards = 1
+    for group in replicated_groups:
+        x = all_reduce_sum(x, group)
+        shards *= torch.distributed.get_world_size(group)
+    for group in summed_groups:
+        x = all_reduce_sum_summed_objectives(x, group)
+        shards *= torch.distributed.get_world_size(group)
+    return x, shards
+
+
+def sequence_balance_loss(expert_ids: torch.Tensor, scores: torch.Tensor, top_k: int, replicated_groups=(),
+                          summed_groups=()) -> torch.Tensor:
+    """``sum_e f_e p_e`` per sequence, averaged over the batch; scores: [B,S,E], expert_ids: [B,S,k].
+
+    The two group lists name the process groups that split the sequence dimension (see
+    :func:`_sum_over_sequence_shards`): the per-sequence sums are added up over them so that a sharded sequence gives
+    the loss, and the gradient, of the whole one.
+    """
 
     if scores.dim() != 3:
         raise ContractError(f"router scores must have shape [batch, seq, experts], got {tuple(scores.shape)}")
@@ -51,25 +71,28 @@ def sequence_balance_loss(expert_ids: torch.Tensor, scores: torch.Tensor, top_k:
     sel_sum = torch.zeros(B, E, dtype=torch.float32, device=scores.device).scatter_add_(
         1, flat_ids, torch.ones_like(flat_ids, dtype=torch.float32))     # [B,E] picks per sequence and expert
     normalised = scores / scores.sum(dim=-1, keepdim=True).clamp_min(1e-20)
-    p_sum = normalised.sum(dim=1)
-    total_S = S
-    for group in seq_groups:
-        sel_sum = all_reduce_sum(sel_sum, group)
-        p_sum = all_reduce_sum(p_sum, group)
-        total_S *= torch.distributed.get_world_size(group)
-    f = (E / (top_k * total_S)) * sel_sum
-    p = p_sum / total_S
+    both, shards = _sum_over_sequence_shards(torch.stack([sel_sum, normalised.sum(dim=1)]), replicated_groups,
+                                             summed_groups)
+    total_S = S * shards
+    f = (E / (top_k * total_S)) * both[0].detach()
+    p = both[1] / total_S
     return (f * p).sum() / B
 
 
-def switch_balance_loss(expert_ids: torch.Tensor, probs: torch.Tensor, top_k: int) -> torch.Tensor:
-    """Switch-transformer style ``E * sum_e (fraction routed to e) * (mean router probability of e)``."""
+def switch_balance_loss(expert_ids: torch.Tensor, probs: torch.Tensor, top_k: int, replicated_groups=(),
+                        summed_groups=()) -> torch.Tensor:
+    """Switch-transformer style ``E * sum_e (fraction routed to e) * (mean router probability of e)`` over the
+    tokens of this rank's batch rows, whole sequences even where the sequence is split over ranks."""
 
     E = probs.shape[-1]
     flat_ids = expert_ids.reshape(-1).long()
-    f = torch.zeros(E, dtype=torch.float32, device=probs.device).index_add_(
-        0, flat_ids, torch.ones_like(flat_ids, dtype=torch.float32)) / max(flat_ids.numel(), 1)
-    p = probs.reshape(-1, E).float().mean(dim=0)
+    picks = torch.zeros(E, dtype=torch.float32, device=probs.device).index_add_(
+        0, flat_ids, torch.ones_like(flat_ids, dtype=torch.float32))
+    flat_probs = probs.reshape(-1, E).float()
+    both, shards = _sum_over_sequence_shards(torch.stack([picks, flat_probs.sum(dim=0)]), replicated_groups,
+                                             summed_groups)
+    f = both[0].detach() / max(flat_ids.numel() * shards, 1)
+    p = both[1] / max(flat_probs.shape[0] * shards, 1)
     return E * (f * p).sum()
 
 
@@ -260,13 +283,15 @@ class SparseMoE(nn.Module):
         stats = router_stats(name, layer_index, expert_ids, weights, self.num_experts, dropped)
         aux = []
         bal = self.moe.balance
-        seq_groups = [g for g in ((ex.tp_group if ex.sp else None), ex.cp_group) if g is not None]
+        # the sequence is split over tensor-parallel ranks (sequence-parallel stream) and context-parallel ranks
+        replicated = [ex.tp_group] if ex.sp and ex.tp_group is not None else []
+        summed = [ex.cp_group] if ex.cp_group is not None else []
         if bal.name == "smebu" and bal.sequence_aux_loss_weight > 0.0:
             aux.append(AuxLoss("moe_sequence_balance",
-                               sequence_balance_loss(expert_ids, scores, self.moe.top_k, seq_groups),
+                               sequence_balance_loss(expert_ids, scores, self.moe.top_k, replicated, summed),
                                float(bal.sequence_aux_loss_weight)))
         if self.moe.aux_loss_coef > 0.0:
-            aux.append(AuxLoss("moe_load_balance", switch_balance_loss(expert_ids, scores, self.moe.top_k),
+            aux.append(AuxLoss("moe_load_balance", switch_balance_loss(expert_ids, scores, self.moe.top_k, replicated, summed),
                                float(self.moe.aux_loss_coef)))
         return y, tuple(aux), (stats,)
 

@@ -273,3 +273,63 @@ def test_generation_on_a_split_model_matches_one_process(tmp_path, kind, mesh, p
     for r in got:
         assert r["ids"] == ref["ids"]
         assert torch.allclose(torch.tensor(r["logprobs"]), torch.tensor(ref["logprobs"]), atol=1e-4)
+
+
+def _first_step_gradients(rank, world, raw):
+    """The reduced gradient of every parameter as the optimizer first sees it."""
+
+    from research_b200.config import run_spec_from_mapping
+    from research_b200.optim.optimizer import Optimizer
+    from research_b200.runtime.trainer import Trainer
+
+    trainer = Trainer(run_spec_from_mapping(raw), device="cpu")
+    seen = {}
+    step = Optimizer.step
+
+    def spy(self, *args, **kwargs):
+        if not seen:
+            seen.update({e.name: e.param.main_grad.clone() for e in self.store.entries if e.param.main_grad is not None})
+        return step(self, *args, **kwargs)
+
+    Optimizer.step = spy
+    try:
+        trainer.train_on(trainer.next_accumulated_batch())
+    finally:
+        Optimizer.step = step
+    return seen
+
+
+def _trinity_with_loud_balance_losses(manifest, **layout):
+    raw = tiny_raw_config(manifest, kind="trinity", steps=2, **layout)
+    moe = raw["model"]["trinity"]["moe"]
+    # weights a thousand times the usual ones: an error in these terms' gradients shows in the router's
+    moe["balance"]["sequence_aux_loss_weight"] = 0.1
+    moe["aux_loss_coef"] = 0.1
+    return raw
+
+
+@pytest.mark.parametrize("mesh, parallelism", [
+    ({"cp": 2}, {"mode": "ddp", "context_parallel": True, "context_attention": "gather"}),
+    ({"cp": 2}, {"mode": "ddp", "context_parallel": True, "context_attention": "ulysses"}),
+    ({"tp": 2}, {"mode": "ddp", "tensor_parallel": True}),
+], ids=["cp2_gather", "cp2_ulysses", "tp2_sequence_parallel"])
+def test_trinity_gradients_on_a_split_sequence_match_one_process(tmp_path, mesh, parallelism):
+    """Sliding-window and global layers, gated attention, the scaled embedding and both balance losses (statistics of
+    whole sequences) over a split sequence.  Compared on the gradients: after AdamW an element whose gradient is a
+    rounding error away from zero moves by a visible fraction of the learning rate in either direction, which says
+    nothing about the layout.  Tensors a layout splits are left to the parameter comparison above."""
+
+    manifest = tiny_dataset(tmp_path)
+    (ref,) = run_gloo(1, _first_step_gradients, _trinity_with_loud_balance_losses(manifest))
+    got = run_gloo(2, _first_step_gradients,
+                   _trinity_with_loud_balance_losses(manifest, mesh=mesh, parallelism=parallelism))
+    assert ref and set(ref) == set(got[0])
+    compared = 0
+    for name, want in ref.items():
+        for r in got:
+            if r[name].shape != want.shape:
+                continue
+            compared += 1
+            err = (r[name] - want).abs().max().item()
+            assert err <= 1e-4 * max(want.abs().max().item(), 1e-3), (name, err)
+    assert compared >= len(got) * 6 and any("router" in name for name in ref)

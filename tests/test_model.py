@@ -8,7 +8,7 @@ import torch
 from research_b200.config import run_spec_from_mapping
 from research_b200.infer.generation import generate_tokens, sample_next_token
 from research_b200.models.build import build_model
-from research_b200.models.moe import apply_capacity, sequence_balance_loss
+from research_b200.models.moe import apply_capacity, sequence_balance_loss, switch_balance_loss
 from research_b200.ops import functional as Fn
 from tests.helpers import tiny_raw_config
 
@@ -115,6 +115,11 @@ def test_router_weights_bias_and_capacity():
     uniform = torch.full((1, 4, 4), 0.25)
     sel = torch.tensor([[[0, 1], [2, 3], [0, 1], [2, 3]]])
     assert sequence_balance_loss(sel, uniform, 2).item() == pytest.approx(1.0)
+    assert switch_balance_loss(sel, uniform, 2).item() == pytest.approx(1.0)
+    # every pick on one expert whose probability is 1: E times the balanced value
+    one_hot = torch.zeros(1, 4, 4)
+    one_hot[..., 0] = 1.0
+    assert switch_balance_loss(torch.zeros(1, 4, 1, dtype=torch.long), one_hot, 1).item() == pytest.approx(4.0)
 
 
 def test_moe_layer_matches_dense_loop():
