@@ -394,6 +394,8 @@ class Optimizer:
         master = store.master_view(sec, e)
         if master is None or master.dim() not in (2, 3) or any(self.routes[m.name].backend != "dion2" for m in e.metas):
             return False
+        if self.tp_size > 1 and any(m.tp_axis is not None for m in e.metas):
+            return False            # a shard of a logical matrix: the selection runs on the gathered matrix
         lo, _ = store.local_master_range(sec)
         mom = self.state[i]["momentum"][e.offset - lo:e.offset - lo + e.numel].view(e.param.shape)
         grad = e.param.main_grad
@@ -466,15 +468,30 @@ class Optimizer:
 
     def _dion2_matrix(self, meta, route, m, w, lr: float, wd: float) -> None:
         logical_axis = route.matrix_axis if route.matrix_axis is not None else 0
-        if len(meta.shape) == 3:
+        batched = len(meta.shape) == 3
+        if batched:
             logical_axis -= 1
         storage_axis = (1 - logical_axis) if meta.transposed else logical_axis
-        selected, idx = orth.select_dion2_slices(m, select_axis=storage_axis)
-        o = orth.polar_express(selected).to(w.dtype)
         rows, cols = meta.shape[-2], meta.shape[-1]
         if wd != 0.0:
             w.mul_(1.0 - lr * wd)
-        w.index_add_(storage_axis, idx, o, alpha=-lr * math.sqrt(rows / cols))
+        alpha = -lr * math.sqrt(rows / cols)
+        if self.tp_size > 1 and meta.tp_axis is not None:
+            # The rows and columns are picked by their norms over the whole logical matrix, as in one process: every
+            # tensor-parallel rank gathers the momentum, repeats the selection and keeps its own slice of the result.
+            tp_logical = meta.tp_axis - (1 if batched else 0)
+            tp_storage = (1 - tp_logical) if meta.transposed else tp_logical
+            rank = dist.get_rank(self.tp_group)
+            full = _all_gather_axis(m.contiguous(), tp_storage, self.tp_group)
+            selected, idx = orth.select_dion2_slices(full, select_axis=storage_axis)
+            update = torch.zeros_like(full).index_add_(storage_axis, idx, orth.polar_express(selected).to(full.dtype))
+            full.index_copy_(storage_axis, idx, selected * orth.DION2_EF_DECAY)
+            w.add_(update.chunk(self.tp_size, dim=tp_storage)[rank].to(w.dtype), alpha=alpha)
+            m.copy_(full.chunk(self.tp_size, dim=tp_storage)[rank])
+            return
+        selected, idx = orth.select_dion2_slices(m, select_axis=storage_axis)
+        o = orth.polar_express(selected).to(w.dtype)
+        w.index_add_(storage_axis, idx, o, alpha=alpha)
         m.index_copy_(storage_axis, idx, selected * orth.DION2_EF_DECAY)
 
     # ---- checkpoint state ---------------------------------------------------------------------------

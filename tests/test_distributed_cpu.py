@@ -333,3 +333,17 @@ def test_trinity_gradients_on_a_split_sequence_match_one_process(tmp_path, mesh,
             err = (r[name] - want).abs().max().item()
             assert err <= 1e-4 * max(want.abs().max().item(), 1e-3), (name, err)
     assert compared >= len(got) * 6 and any("router" in name for name in ref)
+
+
+@pytest.mark.parametrize("kind", ["decoder", "trinity"])
+def test_dion2_on_tensor_parallel_shards_selects_over_the_logical_matrix(tmp_path, kind):
+    """Dion2 keeps the quarter of a matrix's rows or columns with the largest norms.  On a tensor-parallel shard that
+    choice is made over the whole logical matrix: one step moves every parameter where one process moves it (a
+    choice made shard by shard is off by a third of the learning rate in a tenth of the elements)."""
+
+    manifest = tiny_dataset(tmp_path)
+    (ref,) = run_gloo(1, train_and_collect, tiny_raw_config(manifest, kind=kind, optimizer="dion", steps=2), 1)
+    raw = tiny_raw_config(manifest, kind=kind, optimizer="dion", steps=2, mesh={"tp": 2},
+                          parallelism={"mode": "ddp", "tensor_parallel": True})
+    for got in run_gloo(2, train_and_collect, raw, 1):
+        _compare(ref, got, 2e-4)
