@@ -394,7 +394,7 @@ class Optimizer:
         master = store.master_view(sec, e)
         if master is None or master.dim() not in (2, 3) or any(self.routes[m.name].backend != "dion2" for m in e.metas):
             return False
-        if self.tp_size > 1 and any(m.tp_axis is not None for m in e.metas):
+        if any(self._logical_split(m) is not None for m in e.metas):
             return False            # a shard of a logical matrix: the selection runs on the gathered matrix
         lo, _ = store.local_master_range(sec)
         mom = self.state[i]["momentum"][e.offset - lo:e.offset - lo + e.numel].view(e.param.shape)
@@ -458,6 +458,20 @@ class Optimizer:
             store.write_entry_shadow(e, master)
         return True
 
+    def _logical_split(self, meta):
+        """``(group, axis of the logical shape)`` when this rank holds a slice of the logical matrix along that axis -
+        a tensor-parallel shard, or a routed expert whose intermediate dimension is split over ``expert_fsdp`` -
+        else ``None``."""
+
+        from research_b200.models.build import EXPERT_FSDP_AXIS, ROUTED_EXPERT_TAGS
+
+        ex = self.store.result.execution
+        if meta.tag in ROUTED_EXPERT_TAGS:
+            return (ex.expert_fsdp_group, EXPERT_FSDP_AXIS[meta.tag]) if ex.efsdp_size > 1 else None
+        if self.tp_size > 1 and meta.tp_axis is not None:
+            return self.tp_group, meta.tp_axis
+        return None
+
     def _dion2_update(self, meta, route, g, m, w, lr: float, wd: float) -> None:
         m.add_(g)
         if m.dim() == 3:
@@ -476,18 +490,21 @@ class Optimizer:
         if wd != 0.0:
             w.mul_(1.0 - lr * wd)
         alpha = -lr * math.sqrt(rows / cols)
-        if self.tp_size > 1 and meta.tp_axis is not None:
+        split = self._logical_split(meta)
+        if split is not None:
             # The rows and columns are picked by their norms over the whole logical matrix, as in one process: every
-            # tensor-parallel rank gathers the momentum, repeats the selection and keeps its own slice of the result.
-            tp_logical = meta.tp_axis - (1 if batched else 0)
-            tp_storage = (1 - tp_logical) if meta.transposed else tp_logical
-            rank = dist.get_rank(self.tp_group)
-            full = _all_gather_axis(m.contiguous(), tp_storage, self.tp_group)
+            # rank of the group that splits the matrix gathers the momentum, repeats the selection and keeps its own
+            # slice of the result.
+            group, split_logical = split
+            split_logical -= 1 if batched else 0
+            split_storage = (1 - split_logical) if meta.transposed else split_logical
+            parts, rank = dist.get_world_size(group), dist.get_rank(group)
+            full = _all_gather_axis(m.contiguous(), split_storage, group)
             selected, idx = orth.select_dion2_slices(full, select_axis=storage_axis)
             update = torch.zeros_like(full).index_add_(storage_axis, idx, orth.polar_express(selected).to(full.dtype))
             full.index_copy_(storage_axis, idx, selected * orth.DION2_EF_DECAY)
-            w.add_(update.chunk(self.tp_size, dim=tp_storage)[rank].to(w.dtype), alpha=alpha)
-            m.copy_(full.chunk(self.tp_size, dim=tp_storage)[rank])
+            w.add_(update.chunk(parts, dim=split_storage)[rank].to(w.dtype), alpha=alpha)
+            m.copy_(full.chunk(parts, dim=split_storage)[rank])
             return
         selected, idx = orth.select_dion2_slices(m, select_axis=storage_axis)
         o = orth.polar_express(selected).to(w.dtype)

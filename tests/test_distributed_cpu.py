@@ -335,15 +335,19 @@ def test_trinity_gradients_on_a_split_sequence_match_one_process(tmp_path, mesh,
     assert compared >= len(got) * 6 and any("router" in name for name in ref)
 
 
-@pytest.mark.parametrize("kind", ["decoder", "trinity"])
-def test_dion2_on_tensor_parallel_shards_selects_over_the_logical_matrix(tmp_path, kind):
-    """Dion2 keeps the quarter of a matrix's rows or columns with the largest norms.  On a tensor-parallel shard that
-    choice is made over the whole logical matrix: one step moves every parameter where one process moves it (a
-    choice made shard by shard is off by a third of the learning rate in a tenth of the elements)."""
+@pytest.mark.parametrize("kind, mesh, parallelism", [
+    ("decoder", {"tp": 2}, {"mode": "ddp", "tensor_parallel": True}),
+    ("trinity", {"tp": 2}, {"mode": "ddp", "tensor_parallel": True}),
+    ("trinity", {"fsdp": 1, "ep": 2, "expert_fsdp": 2}, {"mode": "fsdp", "expert_parallel": True}),
+], ids=["tp2", "tp2_moe", "ep2_expert_fsdp2"])
+def test_dion2_on_a_shard_selects_over_the_logical_matrix(tmp_path, kind, mesh, parallelism):
+    """Dion2 keeps the quarter of a matrix's rows or columns with the largest norms.  On a tensor-parallel shard, and
+    on a routed expert whose intermediate dimension is split over ``expert_fsdp``, that choice is made over the whole
+    logical matrix: one step moves every parameter where one process moves it (a choice made shard by shard is off by
+    a third of the learning rate in a tenth of the elements)."""
 
     manifest = tiny_dataset(tmp_path)
     (ref,) = run_gloo(1, train_and_collect, tiny_raw_config(manifest, kind=kind, optimizer="dion", steps=2), 1)
-    raw = tiny_raw_config(manifest, kind=kind, optimizer="dion", steps=2, mesh={"tp": 2},
-                          parallelism={"mode": "ddp", "tensor_parallel": True})
-    for got in run_gloo(2, train_and_collect, raw, 1):
+    raw = tiny_raw_config(manifest, kind=kind, optimizer="dion", steps=2, mesh=mesh, parallelism=parallelism)
+    for got in run_gloo(math.prod(mesh.values()), train_and_collect, raw, 1):
         _compare(ref, got, 2e-4)
